@@ -1,0 +1,214 @@
+/*
+ * tlb200.h - C ABI of libtlb200, a B200 (sm_100a) implementation of TL's quantized
+ * Llama inference path.  Plain pointers and sizes only; no C++ or torch types.
+ *
+ * Each entry point names the reference interface it replaces (path within the TL
+ * repository : line).  Conventions follow the reference's FFI rules
+ * (docs/dev/FFI_IMPLEMENTATION_GUIDE.md:7-23, docs/dev/MEMORY_MANAGEMENT_OVERVIEW.md:36-58):
+ *   - every op returns a NEW tensor handle with reference count 1 in *out;
+ *   - inputs are never consumed or modified;
+ *   - retain = RC+1, release = RC-1 (storage is returned to the stream-ordered pool at 0);
+ *   - integers that travel inside tensors (token ids, indices) are f32 values.
+ * Status codes are the reference's RuntimeErrorCode values
+ * (crates/tl_runtime/src/error.rs:7-18).  On failure *out is NULL and
+ * tlb_last_error() returns a thread-local message (error.rs:161-182).
+ * There is no CPU fallback: every compute entry point fails with TLB_ERR_DEVICE when no
+ * CUDA device is usable.
+ */
+#ifndef TLB200_H
+#define TLB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    TLB_OK = 0, TLB_ERR_SHAPE = 1, TLB_ERR_DEVICE = 2, TLB_ERR_ALLOC = 3, TLB_ERR_NULL = 4,
+    TLB_ERR_INTERNAL = 5, TLB_ERR_INDEX = 6, TLB_ERR_TYPE = 7, TLB_ERR_ARG = 8, TLB_ERR_UNKNOWN = 999
+} tlb_status;
+
+/* crates/tl_backend/src/dtype.rs:5-14 (F32, F64, F16, BF16, I32, I64, U8, U32) */
+typedef enum { TLB_F32 = 0, TLB_F64 = 1, TLB_F16 = 2, TLB_BF16 = 3, TLB_I32 = 4, TLB_I64 = 5,
+               TLB_U8 = 6, TLB_U32 = 7 } tlb_dtype;
+
+/* GGML type ids as stored in GGUF (crates/tl_runtime/src/quantized.rs:10-22) */
+typedef enum { TLB_GGML_F32 = 0, TLB_GGML_F16 = 1, TLB_GGML_Q4_0 = 2, TLB_GGML_Q8_0 = 8,
+               TLB_GGML_Q4_K = 12, TLB_GGML_Q6_K = 14 } tlb_ggml_type;
+
+typedef struct tlb_tensor tlb_tensor;     /* CudaTensor handle (crates/tl_cuda/src/tensor.rs:39-99) */
+typedef struct tlb_qtensor tlb_qtensor;   /* QTensor (crates/tl_runtime/src/quantized.rs:29-40) */
+typedef struct tlb_map tlb_map;           /* OpaqueTensorMap (crates/tl_runtime/src/tensor_map.rs:19-22) */
+typedef struct tlb_kvcache tlb_kvcache;   /* OpaqueKVCache (crates/tl_runtime/src/system.rs:387-615) */
+typedef struct tlb_graph tlb_graph;       /* GpuGraph (crates/tl_backend/src/graph.rs:22-31) */
+typedef struct tlb_decoder tlb_decoder;   /* fused decode session; see below */
+
+/* ---- runtime ------------------------------------------------------------------------- */
+/* crates/tl_cuda/src/device.rs:79-86 get_device(): lazily binds one CUDA device and one
+ * non-blocking stream.  device < 0 selects the LOCAL_RANK / 0 default. */
+tlb_status  tlb_init(int device);
+tlb_status  tlb_shutdown(void);
+const char *tlb_last_error(void);                       /* crates/tl_runtime/src/error.rs:161-182 */
+int         tlb_device_id(void);                        /* crates/tl_cuda/src/ffi_ops.rs:1243-1246 */
+tlb_status  tlb_sync(void);                             /* GpuStream::synchronize, crates/tl_backend/src/stream.rs:12-31 */
+uint64_t    tlb_kernel_launches(void);                  /* kernels launched (or replayed in graphs) so far */
+/* pool statistics, crates/tl_cuda/src/buffer_pool.rs:58-76 */
+tlb_status  tlb_mem_stats(uint64_t *bytes_in_use, uint64_t *bytes_reserved);
+/* CUDA-event timing on the library's stream */
+tlb_status  tlb_event_create(void **ev);
+tlb_status  tlb_event_record(void *ev);
+tlb_status  tlb_event_elapsed_ms(void *start, void *stop, float *ms);  /* synchronises on stop */
+tlb_status  tlb_event_destroy(void *ev);
+/* write `bytes` of zeros to a scratch buffer larger than L2 (evicts cached weights between timed runs) */
+tlb_status  tlb_flush_l2(void);
+
+/* ---- tensors (crates/tl_runtime/src/device_ffi.rs:684-746; crates/tl_backend/src/tensor.rs:7-55) ---- */
+tlb_status tlb_tensor_from_host(tlb_tensor **out, const void *data, tlb_dtype dt, const int64_t *shape, int rank);
+tlb_status tlb_tensor_zeros(tlb_tensor **out, tlb_dtype dt, const int64_t *shape, int rank);
+tlb_status tlb_tensor_to_host(const tlb_tensor *t, void *dst, size_t dst_bytes);       /* syncs */
+tlb_status tlb_tensor_retain(tlb_tensor *t);            /* tl_tensor_acquire */
+tlb_status tlb_tensor_release(tlb_tensor *t);           /* tl_tensor_release / _release_safe / _free */
+int        tlb_tensor_refcount(const tlb_tensor *t);
+int        tlb_tensor_rank(const tlb_tensor *t);        /* tl_tensor_dim */
+int64_t    tlb_tensor_numel(const tlb_tensor *t);       /* tl_tensor_numel / tl_tensor_len */
+tlb_status tlb_tensor_shape(const tlb_tensor *t, int64_t *shape_out, int max_rank);
+tlb_dtype  tlb_tensor_dtype(const tlb_tensor *t);
+void      *tlb_tensor_data(const tlb_tensor *t);        /* device pointer; tl_tensor_data */
+tlb_status tlb_tensor_clone(tlb_tensor **out, const tlb_tensor *t);    /* deep copy (tl_tensor_clone copies on CPU) */
+tlb_status tlb_tensor_item_i64(const tlb_tensor *t, int64_t *value);   /* crates/tl_cuda/src/ffi_ops.rs:340, syncs */
+
+/* ---- elementwise / shape ops (crates/tl_runtime/src/device_ffi.rs, line per op) ------- */
+tlb_status tlb_add(tlb_tensor **out, const tlb_tensor *a, const tlb_tensor *b);          /* :809 tl_tensor_add, :1526 add_4d; numpy broadcast */
+tlb_status tlb_mul(tlb_tensor **out, const tlb_tensor *a, const tlb_tensor *b);          /* :819 */
+tlb_status tlb_silu(tlb_tensor **out, const tlb_tensor *a);                              /* :1070 */
+tlb_status tlb_scale(tlb_tensor **out, const tlb_tensor *a, float s);                    /* :925 */
+tlb_status tlb_softmax(tlb_tensor **out, const tlb_tensor *a, int64_t dim);              /* :1097 */
+tlb_status tlb_matmul(tlb_tensor **out, const tlb_tensor *a, const tlb_tensor *b);       /* :834 tl_tensor_matmul, :1521 matmul_4d */
+tlb_status tlb_narrow(tlb_tensor **out, const tlb_tensor *a, int64_t dim, int64_t start, int64_t len); /* :1235 */
+tlb_status tlb_transpose(tlb_tensor **out, const tlb_tensor *a, int64_t d0, int64_t d1); /* :1207 */
+tlb_status tlb_reshape(tlb_tensor **out, const tlb_tensor *a, const int64_t *shape, int rank); /* :1198 zero-copy view */
+tlb_status tlb_cat(tlb_tensor **out, const tlb_tensor *a, const tlb_tensor *b, int64_t dim); /* :1264 cat_4d, :1259 cat2 */
+tlb_status tlb_repeat_interleave(tlb_tensor **out, const tlb_tensor *a, int64_t repeats, int64_t dim); /* :1275 */
+tlb_status tlb_new_causal_mask(tlb_tensor **out, int64_t size);                          /* :170 */
+tlb_status tlb_embedding(tlb_tensor **out, const tlb_tensor *table, const tlb_tensor *idx); /* :1300; out-of-range id -> TLB_ERR_INDEX */
+
+/* ---- LLM ops --------------------------------------------------------------------------- */
+tlb_status tlb_rms_norm(tlb_tensor **out, const tlb_tensor *x, const tlb_tensor *weight /* may be NULL */, float eps); /* device_ffi.rs:1314 */
+/* RoPE conventions: the CPU and CUDA back ends of the reference disagree, both are provided.
+ * TLB_ROPE_CPU  (crates/tl_cpu/src/ffi.rs:2589-2685): tables [seq, dim] pair-duplicated; adjacent
+ *   pairs (x[i], x[i+1]); row 0 of the table passed in rotates EVERY vector.
+ * TLB_ROPE_HALF (crates/tl_cuda/src/ops/llm.rs:96-177): tables [seq, dim/2]; rotate-half
+ *   (x[i], x[i+dim/2]); x is [.., tokens, heads, dim] and token t uses table row t.
+ * Tables are built on the host with libm powf/cosf/sinf, as both back ends do. */
+typedef enum { TLB_ROPE_CPU = 0, TLB_ROPE_HALF = 1 } tlb_rope_mode;
+tlb_status tlb_rope_new_cos(tlb_tensor **out, int64_t dim, int64_t seq_len, float base, tlb_rope_mode mode); /* device_ffi.rs:1323 */
+tlb_status tlb_rope_new_sin(tlb_tensor **out, int64_t dim, int64_t seq_len, float base, tlb_rope_mode mode); /* device_ffi.rs:1332 */
+tlb_status tlb_apply_rope(tlb_tensor **out, const tlb_tensor *x, const tlb_tensor *cos_t, const tlb_tensor *sin_t, tlb_rope_mode mode); /* device_ffi.rs:1342 */
+/* Tie rule: TLB_TIE_LAST is tl_cpu (crates/tl_cpu/src/tensor.rs:841-846), TLB_TIE_FIRST is the CUDA kernel
+ * (crates/tl_cuda/src/cuda_kernels/autograd.cu:1119-1132). Result: [1] f32 holding the index. */
+typedef enum { TLB_TIE_LAST = 0, TLB_TIE_FIRST = 1 } tlb_tie_rule;
+tlb_status tlb_argmax(tlb_tensor **out, const tlb_tensor *x, tlb_tie_rule tie);           /* device_ffi.rs:1138 (dim ignored, scans all) */
+/* temp <= 0: greedy.  temp > 0: the reference CUDA path ignores temp/top_p and returns the argmax
+ * (crates/tl_cuda/src/ffi_ops.rs:880-884); this entry point does the same. */
+tlb_status tlb_sample(tlb_tensor **out, const tlb_tensor *logits, float temp, float top_p, tlb_tie_rule tie); /* device_ffi.rs:1158 */
+tlb_status tlb_repetition_penalty(tlb_tensor **out, const tlb_tensor *logits, const tlb_tensor *tokens, float penalty); /* device_ffi.rs:563 */
+/* softmax(q k^T / sqrt(d) + mask) v.  mask_mode 0: none; 1: additive (CUDA, autograd.cu:2263-2367);
+ * 2: zero entries become -1e9 (CPU, crates/tl_cpu/src/device_impl.rs:775-870). */
+tlb_status tlb_sdpa(tlb_tensor **out, const tlb_tensor *q, const tlb_tensor *k, const tlb_tensor *v, const tlb_tensor *mask, int mask_mode); /* device_ffi.rs:535 */
+/* GpuFusedOps, crates/tl_backend/src/fused_ops.rs:15-57 */
+tlb_status tlb_fused_silu_mul(tlb_tensor **out, const tlb_tensor *gate, const tlb_tensor *up);
+tlb_status tlb_fused_rms_norm(tlb_tensor **out, const tlb_tensor *x, const tlb_tensor *w, float eps);
+tlb_status tlb_fused_add_rms_norm(tlb_tensor **out, const tlb_tensor *x, const tlb_tensor *residual, const tlb_tensor *w, float eps);
+
+/* ---- quantized weights ------------------------------------------------------------------ */
+/* Upload GGUF bytes of a row-major [n, k] tensor and repack them ONCE into the tiled,
+ * 16-byte-vectorised device layout (same byte count).  Replaces the raw-byte upload cached
+ * in QTensor::gpu_raw_cache (crates/tl_runtime/src/system.rs:316-331). */
+tlb_status tlb_qtensor_from_gguf_bytes(tlb_qtensor **out, tlb_ggml_type type, int64_t n, int64_t k, const void *bytes, size_t nbytes);
+tlb_status tlb_qtensor_retain(tlb_qtensor *q);          /* tl_qtensor_retain, system.rs:142 */
+tlb_status tlb_qtensor_release(tlb_qtensor *q);         /* tl_qtensor_release_safe / _free, system.rs:150-172 */
+tlb_status tlb_qtensor_info(const tlb_qtensor *q, int *type, int64_t *n, int64_t *k, uint64_t *device_bytes);
+/* QTensor::dequantize_to_tensor (quantized.rs:117-165): f32 [n, k], bit-identical to the
+ * reference's CPU dequantisers (quantized.rs:167-415) */
+tlb_status tlb_qtensor_dequantize(tlb_tensor **out, const tlb_qtensor *q);
+/* tl_qtensor_matmul (system.rs:180-382) == tl_cuda_mul_mv_q4_k/_q6_k (crates/tl_cuda/src/ffi_ops.rs:1314-1391)
+ * plus the Q4_0/Q8_0 kernels the reference lacks: y[M,N] = x[M,K] . W^T, x 1-D [K] or 2-D [M,K]. */
+tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, const tlb_qtensor *w);
+
+/* Tiled-layout introspection (no counterpart in the reference; used by the layout tests): byte offset
+ * inside a 16-row unit of byte raw_off of the GGUF bytes of row row16's 256-weight segment; unit size. */
+int tlb_layout_unit_offset(int ggml_type, int row16, int raw_off);
+int tlb_layout_unit_bytes(int ggml_type);
+
+/* ---- GGUF loader and tensor map --------------------------------------------------------- */
+tlb_status tlb_gguf_load(tlb_map **out, const char *path);                                /* crates/tl_runtime/src/gguf.rs:34 */
+/* In-memory form of the loader: an empty map, then one tensor at a time from host bytes in GGUF
+ * block layout with a row-major shape (what gguf.rs:129-190 builds per tensor). */
+tlb_status tlb_map_new(tlb_map **out);
+tlb_status tlb_map_add(tlb_map *m, const char *name, tlb_ggml_type type, const int64_t *shape, int rank, const void *bytes, size_t nbytes);
+tlb_status tlb_map_free(tlb_map *m);                                                      /* tensor_map.rs tl_tensor_map_free */
+int64_t    tlb_map_count(const tlb_map *m);
+const char *tlb_map_name(const tlb_map *m, int64_t i);
+tlb_status tlb_map_get_quantized(tlb_qtensor **out, tlb_map *m, const char *name);        /* tensor_map.rs:279 (retained clone) */
+tlb_status tlb_map_get(tlb_tensor **out, tlb_map *m, const char *name);                   /* tensor_map.rs:110 dequantised f32, cached */
+
+/* ---- KV cache handle table (crates/tl_runtime/src/system.rs:387-615, llm.rs:105-174) ----- */
+tlb_status tlb_kvcache_new(tlb_kvcache **out, int64_t layers);
+tlb_status tlb_kvcache_free(tlb_kvcache *c);
+tlb_status tlb_kvcache_clear(tlb_kvcache *c);
+int64_t    tlb_kvcache_len(const tlb_kvcache *c);
+tlb_status tlb_kvcache_resize(tlb_kvcache *c, int64_t layers);
+tlb_status tlb_kvcache_get_k(tlb_tensor **out, tlb_kvcache *c, int64_t layer);           /* retained */
+tlb_status tlb_kvcache_get_v(tlb_tensor **out, tlb_kvcache *c, int64_t layer);
+tlb_status tlb_kvcache_update(tlb_kvcache *c, int64_t layer, tlb_tensor *k, tlb_tensor *v);
+
+/* ---- stream capture / graphs (crates/tl_backend/src/stream.rs:12-31, graph.rs:22-31) ---- */
+tlb_status tlb_stream_begin_capture(void);
+tlb_status tlb_stream_end_capture(tlb_graph **out);
+int        tlb_stream_is_capturing(void);
+tlb_status tlb_graph_replay(tlb_graph *g);
+int64_t    tlb_graph_node_count(const tlb_graph *g);
+tlb_status tlb_graph_destroy(tlb_graph *g);
+
+/* ---- fused decode session ---------------------------------------------------------------
+ * Runs the op sequence of examples/apps/llama3/chatbot_llama3.tl:66-125,220-236 (and
+ * examples/apps/tinyllama/chatbot.tl:50-113) for one new token as a chain of fused kernels
+ * inside one CUDA graph: norm+QKV, RoPE+KV-append+split-K attention, o_proj, norm+gate/up,
+ * silu*up+down, norm+head, argmax.  KV lives in a preallocated [L][KVH][max_seq][D] cache. */
+typedef struct {
+    int32_t n_layers, d_model, n_heads, n_kv_heads, head_dim, ffn, vocab;
+    float   eps, rope_base, attn_scale;   /* attn_scale: the f32 literal the TL program passes to scale() */
+    int32_t kv_f16;                       /* 1: f16 KV cache; 0: f32 (reference) */
+    int32_t max_seq;
+    int32_t tie_rule;                     /* tlb_tie_rule for the greedy token */
+    /* tensor parallelism: this process holds shard tp_rank of tp_size (column split of q/k/v/gate/up,
+     * row split of attn_output/ffn_down); 1/0 for a single GPU */
+    int32_t tp_size, tp_rank;
+} tlb_decoder_cfg;
+
+tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb_map *weights);
+tlb_status tlb_decoder_destroy(tlb_decoder *d);
+/* overwrite cached K/V rows [pos0, pos0+n) of one layer from host f32 [n, n_kv_heads*head_dim] */
+tlb_status tlb_decoder_kv_write(tlb_decoder *d, int layer, int pos0, int n, const float *k, const float *v);
+/* One token through the model: the token's K/V go to cache row `pos`, attention spans rows [0, pos],
+ * RoPE uses angle position `rope_pos` (the reference CPU path rotates a whole prompt at the position
+ * of its first token; pass rope_pos = pos for plain decoding).  Host in, host out: the token id is
+ * copied to the device, the greedy next token is copied back (*next may be NULL to skip the read). */
+tlb_status tlb_decoder_step(tlb_decoder *d, int32_t token, int32_t pos, int32_t rope_pos, int32_t *next);
+/* n greedy steps with the token fed back on the device, no host round trip in between;
+ * tokens_out (host, n entries, may be NULL) is read back once at the end. */
+tlb_status tlb_decoder_generate(tlb_decoder *d, int32_t first_token, int32_t start_pos, int32_t n, int32_t *tokens_out);
+tlb_status tlb_decoder_logits(tlb_decoder *d, float *logits_out /* host, vocab floats */);
+tlb_status tlb_decoder_hidden(tlb_decoder *d, float *hidden_out /* host, d_model floats: residual stream before output_norm */);
+/* algorithmic bytes one decode step reads at context length ctx (weights + KV), kernels per step */
+tlb_status tlb_decoder_stats(const tlb_decoder *d, int32_t ctx, uint64_t *weight_bytes, uint64_t *kv_bytes, int32_t *kernels_per_step);
+/* time `iters` launches of one named matvec of layer 0 ("qkv", "o", "gate_up", "down", "head") over a
+ * rotating pool of `copies` weight copies; returns mean microseconds per launch and bytes per launch */
+tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies, int iters, float *us_per_launch, uint64_t *bytes_per_launch);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,341 @@
+"""tl_b200 - host-side mirror of TL's tensor / quantized-LLM FFI over libtlb200 (sm_100a).
+
+Names follow the reference's runtime symbols (crates/tl_runtime/src/device_ffi.rs,
+system.rs, llm.rs): Tensor.matmul_quantized = tl_qtensor_matmul, Tensor.rms_norm =
+tl_tensor_rms_norm, KVCache.update = tl_kvcache_update, TensorMap.load = tl_gguf_load, ...
+Every call goes through the C ABI; there is no CPU path in this package.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import synth  # noqa: F401
+from ._lib import DecoderCfg, TlbError, check, declared_symbols, lib  # noqa: F401
+
+F32, F16, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 8, 12, 14
+ROPE_CPU, ROPE_HALF = 0, 1
+TIE_LAST, TIE_FIRST = 0, 1
+_NP_DT = {0: np.float32, 1: np.float64, 2: np.float16, 4: np.int32, 5: np.int64, 6: np.uint8, 7: np.uint32}
+_DT_NP = {np.dtype(v): k for k, v in _NP_DT.items()}
+
+
+def init(device=-1):
+    check(lib().tlb_init(device))
+
+
+def sync():
+    check(lib().tlb_sync())
+
+
+def kernel_launches():
+    return int(lib().tlb_kernel_launches())
+
+
+def _shape_arg(shape):
+    arr = (C.c_int64 * max(1, len(shape)))(*shape)
+    return arr, len(shape)
+
+
+class Tensor:
+    """Reference-counted device tensor handle (one reference owned by this object)."""
+
+    def __init__(self, handle):
+        self.h = C.c_void_p(handle) if not isinstance(handle, C.c_void_p) else handle
+
+    @staticmethod
+    def _wrap(fn, *args):
+        out = C.c_void_p()
+        check(fn(C.byref(out), *args))
+        return Tensor(out)
+
+    @staticmethod
+    def from_numpy(a):
+        a = np.ascontiguousarray(a)
+        if a.dtype not in _DT_NP:
+            a = a.astype(np.float32)
+        shp, rank = _shape_arg(a.shape)
+        return Tensor._wrap(lib().tlb_tensor_from_host, a.ctypes.data_as(C.c_void_p), _DT_NP[a.dtype], shp, rank)
+
+    @staticmethod
+    def zeros(shape, dtype=F32):
+        shp, rank = _shape_arg(shape)
+        return Tensor._wrap(lib().tlb_tensor_zeros, dtype, shp, rank)
+
+    @property
+    def shape(self):
+        r = lib().tlb_tensor_rank(self.h)
+        buf = (C.c_int64 * max(1, r))()
+        check(lib().tlb_tensor_shape(self.h, buf, r))
+        return tuple(buf[i] for i in range(r))
+
+    def numel(self):
+        return int(lib().tlb_tensor_numel(self.h))
+
+    def refcount(self):
+        return int(lib().tlb_tensor_refcount(self.h))
+
+    def numpy(self):
+        dt = _NP_DT[lib().tlb_tensor_dtype(self.h)]
+        out = np.empty(self.shape, dtype=dt)
+        check(lib().tlb_tensor_to_host(self.h, out.ctypes.data_as(C.c_void_p), out.nbytes))
+        return out
+
+    def item_i64(self):
+        v = C.c_int64()
+        check(lib().tlb_tensor_item_i64(self.h, C.byref(v)))
+        return v.value
+
+    def clone(self):
+        return Tensor._wrap(lib().tlb_tensor_clone, self.h)
+
+    # elementwise / shape
+    def add(self, o): return Tensor._wrap(lib().tlb_add, self.h, o.h)
+    def mul(self, o): return Tensor._wrap(lib().tlb_mul, self.h, o.h)
+    def silu(self): return Tensor._wrap(lib().tlb_silu, self.h)
+    def scale(self, s): return Tensor._wrap(lib().tlb_scale, self.h, float(s))
+    def softmax(self, dim): return Tensor._wrap(lib().tlb_softmax, self.h, dim)
+    def matmul(self, o): return Tensor._wrap(lib().tlb_matmul, self.h, o.h)
+    matmul_4d = matmul
+    add_4d = add
+    def narrow(self, dim, start, length): return Tensor._wrap(lib().tlb_narrow, self.h, dim, start, length)
+    def transpose(self, d0, d1): return Tensor._wrap(lib().tlb_transpose, self.h, d0, d1)
+
+    def reshape(self, shape):
+        shp, rank = _shape_arg(shape)
+        return Tensor._wrap(lib().tlb_reshape, self.h, shp, rank)
+
+    def cat(self, o, dim): return Tensor._wrap(lib().tlb_cat, self.h, o.h, dim)
+    cat_4d = cat
+    def repeat_interleave(self, repeats, dim): return Tensor._wrap(lib().tlb_repeat_interleave, self.h, repeats, dim)
+    @staticmethod
+    def new_causal_mask(n): return Tensor._wrap(lib().tlb_new_causal_mask, n)
+    def embedding(self, table): return Tensor._wrap(lib().tlb_embedding, table.h, self.h)
+
+    # LLM ops
+    def rms_norm(self, w, eps): return Tensor._wrap(lib().tlb_rms_norm, self.h, w.h if w is not None else None, float(eps))
+    @staticmethod
+    def rope_new_cos(dim, seq_len, base, mode=ROPE_CPU): return Tensor._wrap(lib().tlb_rope_new_cos, dim, seq_len, float(base), mode)
+    @staticmethod
+    def rope_new_sin(dim, seq_len, base, mode=ROPE_CPU): return Tensor._wrap(lib().tlb_rope_new_sin, dim, seq_len, float(base), mode)
+    def apply_rope(self, cos, sin, mode=ROPE_CPU): return Tensor._wrap(lib().tlb_apply_rope, self.h, cos.h, sin.h, mode)
+    def argmax(self, tie=TIE_LAST): return Tensor._wrap(lib().tlb_argmax, self.h, tie)
+    def sample(self, temp, top_p, tie=TIE_LAST): return Tensor._wrap(lib().tlb_sample, self.h, float(temp), float(top_p), tie)
+    def repetition_penalty(self, tokens, p): return Tensor._wrap(lib().tlb_repetition_penalty, self.h, tokens.h, float(p))
+    def sdpa(self, k, v, mask=None, mask_mode=0):
+        return Tensor._wrap(lib().tlb_sdpa, self.h, k.h, v.h, mask.h if mask is not None else None, mask_mode)
+    def fused_silu_mul(self, up): return Tensor._wrap(lib().tlb_fused_silu_mul, self.h, up.h)
+    def fused_rms_norm(self, w, eps): return Tensor._wrap(lib().tlb_fused_rms_norm, self.h, w.h, float(eps))
+    def fused_add_rms_norm(self, res, w, eps): return Tensor._wrap(lib().tlb_fused_add_rms_norm, self.h, res.h, w.h, float(eps))
+    def matmul_quantized(self, qw): return Tensor._wrap(lib().tlb_qtensor_matmul, self.h, qw.h)
+
+    def release(self):
+        if self.h:
+            lib().tlb_tensor_release(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+class QTensor:
+    """Quantized weight in the tiled device layout (QTensor of crates/tl_runtime/src/quantized.rs:29-40)."""
+
+    def __init__(self, handle):
+        self.h = handle
+
+    @staticmethod
+    def from_gguf_bytes(t, n, k, data):
+        data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        out = C.c_void_p()
+        check(lib().tlb_qtensor_from_gguf_bytes(C.byref(out), t, n, k, data.ctypes.data_as(C.c_void_p), data.size))
+        return QTensor(out)
+
+    def info(self):
+        t, n, k, b = C.c_int(), C.c_int64(), C.c_int64(), C.c_uint64()
+        check(lib().tlb_qtensor_info(self.h, C.byref(t), C.byref(n), C.byref(k), C.byref(b)))
+        return dict(type=t.value, n=n.value, k=k.value, device_bytes=b.value)
+
+    def dequantize(self):
+        return Tensor._wrap(lib().tlb_qtensor_dequantize, self.h)
+
+    def release(self):
+        if self.h:
+            lib().tlb_qtensor_release(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+class TensorMap:
+    """Map name -> tensor as tl_gguf_load returns it (crates/tl_runtime/src/tensor_map.rs:19-22)."""
+
+    def __init__(self, handle):
+        self.h = handle
+
+    @staticmethod
+    def load(path):
+        out = C.c_void_p()
+        check(lib().tlb_gguf_load(C.byref(out), str(path).encode()))
+        return TensorMap(out)
+
+    @staticmethod
+    def new():
+        out = C.c_void_p()
+        check(lib().tlb_map_new(C.byref(out)))
+        return TensorMap(out)
+
+    def add(self, name, t, shape, data):
+        data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        shp, rank = _shape_arg(shape)
+        check(lib().tlb_map_add(self.h, name.encode(), t, shp, rank, data.ctypes.data_as(C.c_void_p), data.size))
+
+    def names(self):
+        return [lib().tlb_map_name(self.h, i).decode() for i in range(lib().tlb_map_count(self.h))]
+
+    def get_quantized(self, name):
+        out = C.c_void_p()
+        check(lib().tlb_map_get_quantized(C.byref(out), self.h, name.encode()))
+        return QTensor(out)
+
+    def get(self, name):
+        return Tensor._wrap(lib().tlb_map_get, self.h, name.encode())
+
+    get_1d = get
+
+    def free(self):
+        if self.h:
+            lib().tlb_map_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class KVCache:
+    """Per-layer (K, V) handle table (crates/tl_runtime/src/llm.rs:105-174)."""
+
+    def __init__(self, layers):
+        self.h = C.c_void_p()
+        check(lib().tlb_kvcache_new(C.byref(self.h), layers))
+
+    def len(self): return int(lib().tlb_kvcache_len(self.h))
+    def clear(self): check(lib().tlb_kvcache_clear(self.h))
+    def resize(self, n): check(lib().tlb_kvcache_resize(self.h, n))
+    def get_k(self, layer): return Tensor._wrap(lib().tlb_kvcache_get_k, self.h, layer)
+    def get_v(self, layer): return Tensor._wrap(lib().tlb_kvcache_get_v, self.h, layer)
+    def update(self, layer, k, v): check(lib().tlb_kvcache_update(self.h, layer, k.h, v.h))
+
+    def free(self):
+        if self.h:
+            lib().tlb_kvcache_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Graph:
+    """Captured stream work (GpuStream::begin_capture/end_capture + GpuGraph::replay)."""
+
+    def __init__(self):
+        self.h = None
+
+    def __enter__(self):
+        check(lib().tlb_stream_begin_capture())
+        return self
+
+    def __exit__(self, *exc):
+        out = C.c_void_p()
+        check(lib().tlb_stream_end_capture(C.byref(out)))
+        self.h = out
+        return False
+
+    def replay(self): check(lib().tlb_graph_replay(self.h))
+    def node_count(self): return int(lib().tlb_graph_node_count(self.h))
+
+    def destroy(self):
+        if self.h:
+            lib().tlb_graph_destroy(self.h)
+            self.h = None
+
+
+class Decoder:
+    """Fused decode session over a TensorMap holding a Llama-shaped model."""
+
+    def __init__(self, cfg, weights, kv_f16=True, max_seq=4096, tie_rule=TIE_LAST):
+        self.cfg = DecoderCfg(n_layers=cfg["n_layers"], d_model=cfg["d_model"], n_heads=cfg["n_heads"],
+                              n_kv_heads=cfg["n_kv_heads"], head_dim=cfg["head_dim"], ffn=cfg["ffn"],
+                              vocab=cfg["vocab"], eps=cfg["eps"], rope_base=cfg["rope_base"],
+                              attn_scale=cfg["attn_scale"], kv_f16=int(kv_f16), max_seq=max_seq,
+                              tie_rule=tie_rule, tp_size=1, tp_rank=0)
+        self.h = C.c_void_p()
+        check(lib().tlb_decoder_create(C.byref(self.h), C.byref(self.cfg), weights.h))
+
+    def kv_write(self, layer, pos0, k, v):
+        k = np.ascontiguousarray(k, dtype=np.float32)
+        v = np.ascontiguousarray(v, dtype=np.float32)
+        check(lib().tlb_decoder_kv_write(self.h, layer, pos0, k.shape[0], k.ctypes.data_as(C.c_void_p),
+                                         v.ctypes.data_as(C.c_void_p)))
+
+    def step(self, token, pos, rope_pos=None, read=True):
+        nxt = C.c_int32(-1)
+        check(lib().tlb_decoder_step(self.h, token, pos, pos if rope_pos is None else rope_pos,
+                                     C.byref(nxt) if read else None))
+        return nxt.value
+
+    def generate(self, first_token, start_pos, n, read=True):
+        out = (C.c_int32 * max(1, n))()
+        check(lib().tlb_decoder_generate(self.h, first_token, start_pos, n, out if read else None))
+        return [out[i] for i in range(n)] if read else None
+
+    def logits(self):
+        out = np.empty(self.cfg.vocab, dtype=np.float32)
+        check(lib().tlb_decoder_logits(self.h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def hidden(self):
+        out = np.empty(self.cfg.d_model, dtype=np.float32)
+        check(lib().tlb_decoder_hidden(self.h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def stats(self, ctx):
+        w, kv, n = C.c_uint64(), C.c_uint64(), C.c_int32()
+        check(lib().tlb_decoder_stats(self.h, ctx, C.byref(w), C.byref(kv), C.byref(n)))
+        return dict(weight_bytes=w.value, kv_bytes=kv.value, kernels_per_step=n.value)
+
+    def time_kernel(self, which, copies, iters):
+        us, b = C.c_float(), C.c_uint64()
+        check(lib().tlb_decoder_time_kernel(self.h, which.encode(), copies, iters, C.byref(us), C.byref(b)))
+        return us.value, b.value
+
+    def destroy(self):
+        if self.h:
+            lib().tlb_decoder_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def map_from_tensors(tensors):
+    """TensorMap from the dict synth.llama_tensors returns (name -> (type, bytes, shape))."""
+    m = TensorMap.new()
+    for name, (t, data, shape) in tensors.items():
+        m.add(name, t, shape, data)
+    return m

@@ -1,0 +1,521 @@
+// Fused decode session: one token through a Llama-shaped decoder as a chain of 5 kernels per layer
+// inside one CUDA graph.  The op order is that of the TL programs
+// (examples/apps/llama3/chatbot_llama3.tl:66-125,220-236; examples/apps/tinyllama/chatbot.tl:50-113),
+// which issue ~40 single-op FFI calls per layer per token, each followed by a device-wide sync
+// (crates/tl_cuda/src/stream.rs:69-73).  Here:
+//   K1  residual add + RMSNorm*w (prologue)  ->  q|k|v matvec            (embedding lookup for layer 0)
+//   K2  RoPE(q, k) + KV append + split-K attention + merge
+//   K3  o_proj matvec
+//   K4  residual add + RMSNorm*w (prologue)  ->  gate|up matvec
+//   K5  SiLU(gate)*up (prologue)             ->  down matvec
+//   ... output_norm (prologue) -> lm_head matvec, argmax + position advance.
+// Matvec outputs accumulate with atomicAdd into buffers that an earlier kernel of the chain has
+// cleared; the residual stream ping-pongs between two buffers so no kernel updates memory that
+// another CTA of the same launch reads.  All kernels are launched with programmatic dependent
+// launch, so a kernel's weight prefetch overlaps its predecessor's tail.
+#include "tlb_internal.h"
+
+#include <cstdlib>
+
+using namespace tlb;
+
+struct LayerW {
+    tlb_qtensor *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
+    tlb_tensor *attn_norm = nullptr, *ffn_norm = nullptr;
+};
+
+struct tlb_decoder {
+    tlb_decoder_cfg cfg;
+    std::vector<LayerW> layers;
+    tlb_tensor *emb = nullptr, *out_norm = nullptr;
+    tlb_qtensor *head = nullptr;
+    // device state
+    float *xa = nullptr, *xb = nullptr, *qkv = nullptr, *attn = nullptr, *o_out = nullptr, *gu = nullptr,
+          *down_out = nullptr, *logits = nullptr, *cos_t = nullptr, *sin_t = nullptr, *partial = nullptr;
+    void *kcache = nullptr, *vcache = nullptr;
+    int *state = nullptr;        // [0] token, [1] pos, [2] rope_pos, [3] output index
+    int *counters = nullptr;     // attention merge counters [KVH], argmax counter at [KVH]
+    int *tokens_out = nullptr;   // device ring of generated tokens
+    int tokens_cap = 0;
+    float *amax_v = nullptr;
+    long long *amax_i = nullptr;
+    int *h_state = nullptr;      // pinned host staging [4]
+    int max_splits = 1;
+    cudaGraphExec_t graph = nullptr;
+    uint64_t graph_kernels = 0;
+    bool pdl = true;
+    std::vector<void *> allocs;
+    size_t kv_layer_elems = 0;
+};
+
+namespace {
+
+constexpr int kArgmaxBlocks = 64;
+
+// argmax over the logits + advance of the decode state, in one launch.  Tie rule as tlb_argmax.
+__global__ void argmax_advance_kernel(const float *__restrict__ x, int n, int tie_first, float *pv, long long *pi,
+                                      int *counter, int *state, int *tokens_out, int tokens_cap, int use_pdl)
+{
+    if (use_pdl) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+    __shared__ float sv[32];
+    __shared__ long long si[32];
+    __shared__ int last;
+    float bv = 0.f;
+    long long bi = -1;
+    auto better = [&](float v, long long i, float cv, long long ci) {
+        if (ci < 0) return true;
+        if (v > cv) return true;
+        if (v < cv) return false;
+        return tie_first ? i < ci : i > ci;
+    };
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+    for (int o = 16; o; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) { sv[w] = bv; si[w] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < (int)(blockDim.x >> 5); i++)
+            if (si[i] >= 0 && better(sv[i], si[i], bv, bi)) { bv = sv[i]; bi = si[i]; }
+        pv[blockIdx.x] = bv;
+        pi[blockIdx.x] = bi;
+        __threadfence();
+        last = (atomicAdd(counter, 1) == (int)gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!last || threadIdx.x != 0) return;
+    __threadfence();
+    bv = 0.f; bi = -1;
+    for (int i = 0; i < (int)gridDim.x; i++) {
+        float v = __ldcg(pv + i);
+        long long ix = __ldcg(pi + i);
+        if (ix >= 0 && better(v, ix, bv, bi)) { bv = v; bi = ix; }
+    }
+    if (bi < 0) bi = 0;
+    int idx = state[3];
+    if (tokens_out && idx < tokens_cap) tokens_out[idx] = (int)bi;
+    state[0] = (int)bi;
+    state[1] += 1;
+    state[2] += 1;
+    state[3] = idx + 1;
+    *counter = 0;
+}
+
+template <typename T>
+tlb_status dalloc(tlb_decoder *d, T **p, size_t count, bool zero = true)
+{
+    TLB_CUDA(cudaMalloc((void **)p, count * sizeof(T) ? count * sizeof(T) : 16));
+    d->allocs.push_back(*p);
+    if (zero) TLB_CUDA(cudaMemsetAsync(*p, 0, count * sizeof(T), ctx()->stream));
+    return TLB_OK;
+}
+
+tlb_status get_q(tlb_map *m, const std::string &name, tlb_qtensor **q, int64_t n, int64_t k, int want_type)
+{
+    TLB_TRY(tlb_map_get_quantized(q, m, name.c_str()));
+    if ((*q)->n != n || (*q)->k != k)
+        return fail(TLB_ERR_SHAPE, "tensor '%s' is [%lld, %lld], expected [%lld, %lld]", name.c_str(), (long long)(*q)->n,
+                    (long long)(*q)->k, (long long)n, (long long)k);
+    if (want_type >= 0 && (*q)->type != want_type)
+        return fail(TLB_ERR_TYPE, "tensor '%s' has GGML type %d; the tensors fused into one launch must share type %d", name.c_str(),
+                    (*q)->type, want_type);
+    return TLB_OK;
+}
+
+tlb_status get_f(tlb_map *m, const std::string &name, tlb_tensor **t, int64_t numel)
+{
+    TLB_TRY(tlb_map_get(t, m, name.c_str()));
+    if ((*t)->numel() != numel) return fail(TLB_ERR_SHAPE, "tensor '%s' has %lld elements, expected %lld", name.c_str(), (long long)(*t)->numel(), (long long)numel);
+    return TLB_OK;
+}
+
+void set_w(MatvecJob &j, int i, const tlb_qtensor *q, float *out)
+{
+    j.w[i] = q->dev();
+    j.n_tiles[i] = q->n_tiles;
+    j.n_rows[i] = q->n;
+    j.out[i] = out;
+}
+
+// the kernel chain of one decode step (launched eagerly or into a capturing stream)
+tlb_status enqueue_step(tlb_decoder *d)
+{
+    const tlb_decoder_cfg &c = d->cfg;
+    const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
+    const int L = c.n_layers;
+    for (int l = 0; l < L; l++) {
+        const LayerW &w = d->layers[l];
+        {   // K1
+            MatvecJob j;
+            j.n_w = 3;
+            set_w(j, 0, w.q, d->qkv);
+            set_w(j, 1, w.k, d->qkv + qd);
+            set_w(j, 2, w.v, d->qkv + qd + kvd);
+            j.type = w.q->type; j.k = dm; j.m = 1;
+            j.prologue = PRO_ADD_NORM;
+            j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
+            if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; j.x = nullptr; j.x2 = nullptr; }
+            else { j.x = d->xa; j.x2 = d->down_out; }
+            j.x_out = d->xb;
+            j.zero_ptr[0] = d->o_out; j.zero_n[0] = dm;
+            j.pdl = d->pdl;
+            TLB_TRY(launch_qmatvec(j));
+        }
+        {   // K2
+            DecodeAttnJob a;
+            a.qkv = d->qkv;
+            a.kcache = (char *)d->kcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
+            a.vcache = (char *)d->vcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
+            a.kv_f16 = c.kv_f16; a.H = c.n_heads; a.KVH = c.n_kv_heads; a.D = c.head_dim; a.max_seq = c.max_seq;
+            a.pos = d->state + 1; a.rope_pos = d->state + 2; a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.scale = c.attn_scale;
+            a.partial = d->partial; a.counters = d->counters; a.splits = d->max_splits; a.out = d->attn; a.pdl = d->pdl;
+            TLB_TRY(launch_decode_attention(a));
+        }
+        {   // K3
+            MatvecJob j;
+            j.n_w = 1;
+            set_w(j, 0, w.o, d->o_out);
+            j.type = w.o->type; j.k = qd; j.m = 1;
+            j.prologue = PRO_PLAIN; j.x = d->attn;
+            j.zero_ptr[0] = d->gu; j.zero_n[0] = 2 * (int64_t)F;
+            j.pdl = d->pdl;
+            TLB_TRY(launch_qmatvec(j));
+        }
+        {   // K4
+            MatvecJob j;
+            j.n_w = 2;
+            set_w(j, 0, w.gate, d->gu);
+            set_w(j, 1, w.up, d->gu + F);
+            j.type = w.gate->type; j.k = dm; j.m = 1;
+            j.prologue = PRO_ADD_NORM; j.x = d->xb; j.x2 = d->o_out; j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
+            j.x_out = d->xa;
+            j.zero_ptr[0] = d->down_out; j.zero_n[0] = dm;
+            j.pdl = d->pdl;
+            TLB_TRY(launch_qmatvec(j));
+        }
+        {   // K5
+            MatvecJob j;
+            j.n_w = 1;
+            set_w(j, 0, w.down, d->down_out);
+            j.type = w.down->type; j.k = F; j.m = 1;
+            j.prologue = PRO_SILU_MUL; j.x = d->gu; j.x2 = d->gu + F;
+            j.zero_ptr[0] = d->qkv; j.zero_n[0] = qd + 2 * kvd;
+            if (l == L - 1) { j.zero_ptr[1] = d->logits; j.zero_n[1] = c.vocab; }
+            j.pdl = d->pdl;
+            TLB_TRY(launch_qmatvec(j));
+        }
+    }
+    {   // output_norm + head
+        MatvecJob j;
+        j.n_w = 1;
+        set_w(j, 0, d->head, d->logits);
+        j.type = d->head->type; j.k = dm; j.m = 1;
+        j.prologue = PRO_ADD_NORM; j.x = d->xa; j.x2 = d->down_out; j.norm_w = d->out_norm->f32(); j.eps = c.eps;
+        j.x_out = d->xb;
+        j.pdl = d->pdl;
+        TLB_TRY(launch_qmatvec(j));
+    }
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kArgmaxBlocks);
+        cfg.blockDim = dim3(256);
+        cfg.stream = ctx()->stream;
+        cudaLaunchAttribute at[1];
+        if (d->pdl) {
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+        }
+        TLB_CUDA(cudaLaunchKernelEx(&cfg, argmax_advance_kernel, (const float *)d->logits, (int)c.vocab, (int)(c.tie_rule == TLB_TIE_FIRST),
+                                    d->amax_v, d->amax_i, d->counters + c.n_kv_heads, d->state, d->tokens_out, d->tokens_cap, (int)d->pdl));
+        count_launch();
+    }
+    return TLB_OK;
+}
+
+tlb_status ensure_graph(tlb_decoder *d)
+{
+    if (d->graph) return TLB_OK;
+    Context *cx = ctx();
+    uint64_t before = cx->launches.load();
+    TLB_CUDA(cudaStreamBeginCapture(cx->stream, cudaStreamCaptureModeThreadLocal));
+    tlb_status st = enqueue_step(d);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(cx->stream, &g);
+    d->graph_kernels = cx->launches.load() - before;
+    cx->launches = before;
+    if (st != TLB_OK) { if (g) cudaGraphDestroy(g); return st; }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
+    e = cudaGraphInstantiate(&d->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+    return TLB_OK;
+}
+
+tlb_status set_state(tlb_decoder *d, int token, int pos, int rope_pos, int out_idx)
+{
+    // pageable source: the runtime stages the 16 bytes before returning, so the next call may reuse the stack
+    int hs[4] = {token, pos, rope_pos, out_idx};
+    TLB_CUDA(cudaMemcpyAsync(d->state, hs, sizeof hs, cudaMemcpyHostToDevice, ctx()->stream));
+    return TLB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+tlb_status tlb_decoder_destroy(tlb_decoder *d)
+{
+    if (!d) return TLB_OK;
+    if (ctx()) cudaStreamSynchronize(ctx()->stream);
+    if (d->graph) cudaGraphExecDestroy(d->graph);
+    for (LayerW &w : d->layers) {
+        tlb_qtensor_release(w.q); tlb_qtensor_release(w.k); tlb_qtensor_release(w.v); tlb_qtensor_release(w.o);
+        tlb_qtensor_release(w.gate); tlb_qtensor_release(w.up); tlb_qtensor_release(w.down);
+        tlb_tensor_release(w.attn_norm); tlb_tensor_release(w.ffn_norm);
+    }
+    tlb_tensor_release(d->emb); tlb_tensor_release(d->out_norm); tlb_qtensor_release(d->head);
+    for (void *p : d->allocs) cudaFree(p);
+    if (d->h_state) cudaFreeHost(d->h_state);
+    delete d;
+    return TLB_OK;
+}
+
+tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb_map *m)
+{
+    if (!out) return fail(TLB_ERR_NULL, "null out");
+    *out = nullptr;
+    if (!cfg || !m) return fail(TLB_ERR_NULL, "null argument");
+    if (!ensure_init()) return TLB_ERR_DEVICE;
+    const tlb_decoder_cfg &c = *cfg;
+    if (c.n_layers < 1 || c.d_model < 1 || c.n_heads < 1 || c.n_kv_heads < 1 || c.head_dim < 1 || c.ffn < 1 || c.vocab < 1 || c.max_seq < 1)
+        return fail(TLB_ERR_ARG, "decoder config has a non-positive size");
+    if (c.tp_size > 1) return fail(TLB_ERR_ARG, "tensor-parallel decode sessions are created with tlb_decoder_create_tp");
+    if (c.n_heads % c.n_kv_heads) return fail(TLB_ERR_SHAPE, "n_heads must be a multiple of n_kv_heads");
+    const int64_t dm = c.d_model, qd = (int64_t)c.n_heads * c.head_dim, kvd = (int64_t)c.n_kv_heads * c.head_dim, F = c.ffn;
+    tlb_decoder *d = new tlb_decoder();
+    d->cfg = c;
+    const char *nopdl = getenv("TLB_NO_PDL");
+    d->pdl = !(nopdl && nopdl[0] == '1');
+    tlb_status st = TLB_OK;
+#define TRY_D(expr) do { st = (expr); if (st != TLB_OK) { tlb_decoder_destroy(d); return st; } } while (0)
+    d->layers.resize(c.n_layers);
+    for (int l = 0; l < c.n_layers; l++) {
+        std::string p = "blk." + std::to_string(l) + ".";
+        LayerW &w = d->layers[l];
+        TRY_D(get_q(m, p + "attn_q.weight", &w.q, qd, dm, -1));
+        TRY_D(get_q(m, p + "attn_k.weight", &w.k, kvd, dm, w.q->type));
+        TRY_D(get_q(m, p + "attn_v.weight", &w.v, kvd, dm, w.q->type));
+        TRY_D(get_q(m, p + "attn_output.weight", &w.o, dm, qd, -1));
+        TRY_D(get_q(m, p + "ffn_gate.weight", &w.gate, F, dm, -1));
+        TRY_D(get_q(m, p + "ffn_up.weight", &w.up, F, dm, w.gate->type));
+        TRY_D(get_q(m, p + "ffn_down.weight", &w.down, dm, F, -1));
+        TRY_D(get_f(m, p + "attn_norm.weight", &w.attn_norm, dm));
+        TRY_D(get_f(m, p + "ffn_norm.weight", &w.ffn_norm, dm));
+    }
+    TRY_D(get_f(m, "token_embd.weight", &d->emb, (int64_t)c.vocab * dm));
+    TRY_D(get_f(m, "output_norm.weight", &d->out_norm, dm));
+    TRY_D(get_q(m, "output.weight", &d->head, c.vocab, dm, -1));
+    size_t kmax = qmatvec_max_k(1);
+    if ((size_t)std::max(std::max(dm, qd), F) > kmax) {
+        tlb_decoder_destroy(d);
+        return fail(TLB_ERR_SHAPE, "inner dimensions up to %zu fit the single-pass matvec", kmax);
+    }
+    TRY_D(dalloc(d, &d->xa, dm)); TRY_D(dalloc(d, &d->xb, dm));
+    TRY_D(dalloc(d, &d->qkv, qd + 2 * kvd)); TRY_D(dalloc(d, &d->attn, qd)); TRY_D(dalloc(d, &d->o_out, dm));
+    TRY_D(dalloc(d, &d->gu, 2 * F)); TRY_D(dalloc(d, &d->down_out, dm)); TRY_D(dalloc(d, &d->logits, c.vocab));
+    d->kv_layer_elems = (size_t)kvd * c.max_seq;
+    size_t kv_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
+    TRY_D(dalloc(d, (char **)&d->kcache, kv_bytes)); TRY_D(dalloc(d, (char **)&d->vcache, kv_bytes));
+    d->max_splits = (c.max_seq + 127) / 128;
+    int rep = c.n_heads / c.n_kv_heads;
+    TRY_D(dalloc(d, &d->partial, (size_t)c.n_kv_heads * d->max_splits * rep * (c.head_dim + 2)));
+    TRY_D(dalloc(d, &d->counters, c.n_kv_heads + 1));
+    TRY_D(dalloc(d, &d->state, 4));
+    d->tokens_cap = c.max_seq;
+    TRY_D(dalloc(d, &d->tokens_out, d->tokens_cap));
+    TRY_D(dalloc(d, &d->amax_v, kArgmaxBlocks)); TRY_D(dalloc(d, &d->amax_i, kArgmaxBlocks));
+    // RoPE tables on the host with libm, pair-duplicated [max_seq, D] (crates/tl_cpu/src/ffi.rs:2589-2627)
+    {
+        tlb_tensor *ct = nullptr, *sn = nullptr;
+        TRY_D(tlb_rope_new_cos(&ct, c.head_dim, c.max_seq, c.rope_base, TLB_ROPE_CPU));
+        st = tlb_rope_new_sin(&sn, c.head_dim, c.max_seq, c.rope_base, TLB_ROPE_CPU);
+        if (st == TLB_OK) st = dalloc(d, &d->cos_t, (size_t)c.max_seq * c.head_dim, false);
+        if (st == TLB_OK) st = dalloc(d, &d->sin_t, (size_t)c.max_seq * c.head_dim, false);
+        if (st == TLB_OK) {
+            size_t b = (size_t)c.max_seq * c.head_dim * 4;
+            cudaMemcpyAsync(d->cos_t, ct->data(), b, cudaMemcpyDeviceToDevice, ctx()->stream);
+            cudaMemcpyAsync(d->sin_t, sn->data(), b, cudaMemcpyDeviceToDevice, ctx()->stream);
+        }
+        tlb_tensor_release(ct); tlb_tensor_release(sn);
+        if (st != TLB_OK) { tlb_decoder_destroy(d); return st; }
+    }
+    cudaError_t e = cudaMallocHost((void **)&d->h_state, 4 * sizeof(int));
+    if (e != cudaSuccess) { tlb_decoder_destroy(d); return cuda_fail(e, "cudaMallocHost"); }
+    TRY_D(tlb_sync());
+#undef TRY_D
+    *out = d;
+    return TLB_OK;
+}
+
+tlb_status tlb_decoder_kv_write(tlb_decoder *d, int layer, int pos0, int n, const float *k, const float *v)
+{
+    if (!d || !k || !v) return fail(TLB_ERR_NULL, "null argument");
+    const tlb_decoder_cfg &c = d->cfg;
+    if (layer < 0 || layer >= c.n_layers || pos0 < 0 || n < 0 || pos0 + n > c.max_seq)
+        return fail(TLB_ERR_INDEX, "kv_write: layer %d rows [%d, %d) out of range", layer, pos0, pos0 + n);
+    if (n == 0) return TLB_OK;
+    const int D = c.head_dim, KVH = c.n_kv_heads;
+    const size_t es = c.kv_f16 ? 2 : 4;
+    // host layout [n][KVH*D] -> cache layout [KVH][max_seq][D]
+    std::vector<uint8_t> buf((size_t)n * D * es);
+    for (int which = 0; which < 2; which++) {
+        const float *src = which ? v : k;
+        char *dst = (char *)(which ? d->vcache : d->kcache) + (size_t)layer * d->kv_layer_elems * es;
+        for (int h = 0; h < KVH; h++) {
+            for (int t = 0; t < n; t++)
+                for (int e = 0; e < D; e++) {
+                    float f = src[((size_t)t * KVH + h) * D + e];
+                    if (c.kv_f16) ((__half *)buf.data())[(size_t)t * D + e] = __float2half_rn(f);
+                    else ((float *)buf.data())[(size_t)t * D + e] = f;
+                }
+            TLB_CUDA(cudaMemcpyAsync(dst + ((size_t)h * c.max_seq + pos0) * D * es, buf.data(), buf.size(), cudaMemcpyHostToDevice, ctx()->stream));
+            TLB_CUDA(cudaStreamSynchronize(ctx()->stream));
+        }
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_decoder_step(tlb_decoder *d, int32_t token, int32_t pos, int32_t rope_pos, int32_t *next)
+{
+    if (!d) return fail(TLB_ERR_NULL, "null decoder");
+    if (token < 0 || token >= d->cfg.vocab) return fail(TLB_ERR_INDEX, "Embedding index %d out of range for vocab size %d", token, d->cfg.vocab);
+    if (pos < 0 || pos >= d->cfg.max_seq || rope_pos < 0 || rope_pos >= d->cfg.max_seq)
+        return fail(TLB_ERR_INDEX, "position %d / %d outside the cache of %d rows", pos, rope_pos, d->cfg.max_seq);
+    TLB_TRY(ensure_graph(d));
+    TLB_TRY(set_state(d, token, pos, rope_pos, 0));
+    TLB_CUDA(cudaGraphLaunch(d->graph, ctx()->stream));
+    ctx()->launches += d->graph_kernels;
+    if (next) {
+        TLB_CUDA(cudaMemcpyAsync(d->h_state, d->state, sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
+        TLB_TRY(tlb_sync());
+        *next = d->h_state[0];
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_decoder_generate(tlb_decoder *d, int32_t first_token, int32_t start_pos, int32_t n, int32_t *tokens_out)
+{
+    if (!d) return fail(TLB_ERR_NULL, "null decoder");
+    if (first_token < 0 || first_token >= d->cfg.vocab) return fail(TLB_ERR_INDEX, "Embedding index %d out of range", first_token);
+    if (n < 0 || start_pos < 0 || start_pos + n > d->cfg.max_seq) return fail(TLB_ERR_INDEX, "positions [%d, %d) outside the cache of %d rows", start_pos, start_pos + n, d->cfg.max_seq);
+    TLB_TRY(ensure_graph(d));
+    TLB_TRY(set_state(d, first_token, start_pos, start_pos, 0));
+    for (int i = 0; i < n; i++) TLB_CUDA(cudaGraphLaunch(d->graph, ctx()->stream));
+    ctx()->launches += d->graph_kernels * (uint64_t)n;
+    if (tokens_out && n) {
+        TLB_CUDA(cudaMemcpyAsync(tokens_out, d->tokens_out, (size_t)n * sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
+        TLB_TRY(tlb_sync());
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_decoder_logits(tlb_decoder *d, float *logits_out)
+{
+    if (!d || !logits_out) return fail(TLB_ERR_NULL, "null argument");
+    TLB_CUDA(cudaMemcpyAsync(logits_out, d->logits, (size_t)d->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx()->stream));
+    return tlb_sync();
+}
+
+tlb_status tlb_decoder_hidden(tlb_decoder *d, float *hidden_out)
+{
+    if (!d || !hidden_out) return fail(TLB_ERR_NULL, "null argument");
+    TLB_CUDA(cudaMemcpyAsync(hidden_out, d->xb, (size_t)d->cfg.d_model * 4, cudaMemcpyDeviceToHost, ctx()->stream));
+    return tlb_sync();
+}
+
+tlb_status tlb_decoder_stats(const tlb_decoder *d, int32_t ctx_len, uint64_t *weight_bytes, uint64_t *kv_bytes, int32_t *kernels_per_step)
+{
+    if (!d) return fail(TLB_ERR_NULL, "null decoder");
+    uint64_t wb = d->head->nbytes() + (uint64_t)d->cfg.d_model * 4 * (2 * d->cfg.n_layers + 2);
+    for (const LayerW &w : d->layers)
+        wb += w.q->nbytes() + w.k->nbytes() + w.v->nbytes() + w.o->nbytes() + w.gate->nbytes() + w.up->nbytes() + w.down->nbytes();
+    if (weight_bytes) *weight_bytes = wb;
+    if (kv_bytes) *kv_bytes = 2ull * d->cfg.n_layers * d->cfg.n_kv_heads * d->cfg.head_dim * (uint64_t)ctx_len * (d->cfg.kv_f16 ? 2 : 4);
+    if (kernels_per_step) *kernels_per_step = 5 * d->cfg.n_layers + 2;
+    return TLB_OK;
+}
+
+tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies, int iters, float *us_per_launch, uint64_t *bytes_per_launch)
+{
+    if (!d || !which || !us_per_launch) return fail(TLB_ERR_NULL, "null argument");
+    const tlb_decoder_cfg &c = d->cfg;
+    const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
+    if (copies < 1) copies = 1;
+    if (copies > c.n_layers) copies = c.n_layers;
+    std::string w(which);
+    int64_t out_n = w == "qkv" ? qd + 2 * kvd : (w == "o" || w == "down") ? dm : w == "gate_up" ? 2 * F : w == "head" ? c.vocab : -1;
+    if (out_n < 0) return fail(TLB_ERR_ARG, "unknown kernel '%s' (qkv, o, gate_up, down, head)", which);
+    int64_t kk = (w == "o") ? qd : (w == "down") ? F : dm;
+    float *xin = nullptr, *outb[2] = {nullptr, nullptr};
+    TLB_CUDA(cudaMalloc(&xin, (size_t)std::max<int64_t>(kk, 2 * F) * 4));
+    TLB_CUDA(cudaMalloc(&outb[0], (size_t)out_n * 4));
+    TLB_CUDA(cudaMalloc(&outb[1], (size_t)out_n * 4));
+    {
+        std::vector<float> hx((size_t)std::max<int64_t>(kk, 2 * F));
+        uint32_t s = 12345u;
+        for (float &v : hx) { s = s * 1664525u + 1013904223u; v = ((s >> 8) / 8388608.0f) - 1.0f; }
+        cudaMemcpy(xin, hx.data(), hx.size() * 4, cudaMemcpyHostToDevice);
+        cudaMemset(outb[0], 0, (size_t)out_n * 4);
+        cudaMemset(outb[1], 0, (size_t)out_n * 4);
+    }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    uint64_t bytes = 0;
+    tlb_status st = TLB_OK;
+    for (int it = -3; it < iters && st == TLB_OK; it++) {   // 3 warm-up launches, then the timed ones
+        if (it == 0) cudaEventRecord(e0, ctx()->stream);
+        const LayerW &lw = d->layers[(it + 3) % copies];
+        MatvecJob j;
+        float *o = outb[(it + 3) & 1];
+        j.m = 1; j.prologue = PRO_PLAIN; j.x = xin;
+        if (w == "qkv") {
+            j.n_w = 3; set_w(j, 0, lw.q, o); set_w(j, 1, lw.k, o + qd); set_w(j, 2, lw.v, o + qd + kvd);
+            j.type = lw.q->type; j.k = dm; bytes = lw.q->nbytes() + lw.k->nbytes() + lw.v->nbytes();
+        } else if (w == "o") {
+            j.n_w = 1; set_w(j, 0, lw.o, o); j.type = lw.o->type; j.k = qd; bytes = lw.o->nbytes();
+        } else if (w == "gate_up") {
+            j.n_w = 2; set_w(j, 0, lw.gate, o); set_w(j, 1, lw.up, o + F); j.type = lw.gate->type; j.k = dm;
+            bytes = lw.gate->nbytes() + lw.up->nbytes();
+        } else if (w == "down") {
+            j.n_w = 1; set_w(j, 0, lw.down, o); j.type = lw.down->type; j.k = F; bytes = lw.down->nbytes();
+        } else {
+            j.n_w = 1; set_w(j, 0, d->head, o); j.type = d->head->type; j.k = dm; bytes = d->head->nbytes();
+        }
+        j.zero_ptr[0] = outb[(it + 4) & 1]; j.zero_n[0] = out_n;
+        st = launch_qmatvec(j);
+    }
+    cudaEventRecord(e1, ctx()->stream);
+    cudaEventSynchronize(e1);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaFree(xin); cudaFree(outb[0]); cudaFree(outb[1]);
+    if (st != TLB_OK) return st;
+    *us_per_launch = ms * 1000.f / (float)std::max(1, iters);
+    if (bytes_per_launch) *bytes_per_launch = bytes + (uint64_t)kk * 4 + (uint64_t)out_n * 4;
+    return tlb_sync();
+}
+
+}  // extern "C"

@@ -1,0 +1,362 @@
+// GGUF loader, tensor map and the KV-cache handle table (host code).
+//   tl_gguf_load        crates/tl_runtime/src/gguf.rs:34-196
+//   OpaqueTensorMap     crates/tl_runtime/src/tensor_map.rs:19-22,110-150,279
+//   OpaqueKVCache       crates/tl_runtime/src/system.rs:387-615
+// Differences from the reference by design: quantized tensors are repacked once into the tiled
+// device layout while loading (the reference copies the raw bytes into a Vec<u8> and uploads them
+// on first use), and host bytes are not kept afterwards.
+#include "tlb_internal.h"
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <map>
+
+using namespace tlb;
+
+struct MapEntry {
+    int type = 0;
+    std::vector<int64_t> shape;   // row-major
+    tlb_qtensor *q = nullptr;     // quantized types
+    tlb_tensor *f32 = nullptr;    // F32 / F16 data, or the cached dequantisation of q
+};
+
+struct tlb_map {
+    std::vector<std::string> names;
+    std::map<std::string, MapEntry> entries;
+};
+
+struct tlb_kvcache {
+    std::vector<std::pair<tlb_tensor *, tlb_tensor *>> layers;
+};
+
+namespace tlb {
+
+__global__ void f16_to_f32_kernel2(const __half *a, float *out, int64_t n)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __half2float(a[i]);
+}
+
+static size_t ggml_nbytes(int type, int64_t nelem)
+{
+    switch (type) {
+    case TLB_GGML_F32: return (size_t)nelem * 4;
+    case TLB_GGML_F16: return (size_t)nelem * 2;
+    case TLB_GGML_Q4_0: return (size_t)(nelem / 32) * 18;
+    case TLB_GGML_Q8_0: return (size_t)(nelem / 32) * 34;
+    case TLB_GGML_Q4_K: return (size_t)(nelem / 256) * 144;
+    case TLB_GGML_Q6_K: return (size_t)(nelem / 256) * 210;
+    default: return 0;
+    }
+}
+
+static bool ggml_known(int type)
+{
+    return type == TLB_GGML_F32 || type == TLB_GGML_F16 || qformat(type) != nullptr;
+}
+
+static tlb_status map_add(tlb_map *m, const std::string &name, int type, const int64_t *shape, int rank,
+                          const void *bytes, size_t nbytes)
+{
+    if (m->entries.count(name)) return fail(TLB_ERR_ARG, "tensor '%s' already in the map", name.c_str());
+    int64_t nelem = 1;
+    for (int i = 0; i < rank; i++) nelem *= shape[i];
+    if (ggml_nbytes(type, nelem) != nbytes)
+        return fail(TLB_ERR_SHAPE, "tensor '%s': %zu bytes do not match type %d x %lld elements", name.c_str(), nbytes, type, (long long)nelem);
+    MapEntry e;
+    e.type = type;
+    e.shape.assign(shape, shape + rank);
+    if (qformat(type)) {
+        if (rank != 2) return fail(TLB_ERR_SHAPE, "quantized tensor '%s' must be 2-D, got %dD", name.c_str(), rank);
+        TLB_TRY(tlb_qtensor_from_gguf_bytes(&e.q, (tlb_ggml_type)type, shape[0], shape[1], bytes, nbytes));
+    } else if (type == TLB_GGML_F32) {
+        TLB_TRY(tlb_tensor_from_host(&e.f32, bytes, TLB_F32, shape, rank));
+    } else {  // F16 -> f32, exact widening (quantized.rs:167-180)
+        tlb_tensor *h = nullptr;
+        TLB_TRY(tlb_tensor_from_host(&h, bytes, TLB_F16, shape, rank));
+        tlb_status st = new_tensor(&e.f32, TLB_F32, shape, rank);
+        if (st == TLB_OK && nelem) {
+            int blocks = (int)std::min<int64_t>((nelem + 255) / 256, 148 * 16);
+            f16_to_f32_kernel2<<<blocks, 256, 0, ctx()->stream>>>((const __half *)h->data(), e.f32->f32(), nelem);
+            count_launch();
+        }
+        tlb_tensor_release(h);
+        TLB_TRY(st);
+    }
+    m->names.push_back(name);
+    m->entries[name] = e;
+    return TLB_OK;
+}
+
+struct Reader {
+    const uint8_t *p;
+    size_t n, off = 0;
+    bool ok = true;
+    template <typename T> T get()
+    {
+        T v{};
+        if (off + sizeof(T) > n) { ok = false; return v; }
+        memcpy(&v, p + off, sizeof(T));
+        off += sizeof(T);
+        return v;
+    }
+    std::string str()
+    {
+        uint64_t len = get<uint64_t>();
+        if (!ok || off + len > n) { ok = false; return ""; }
+        std::string s((const char *)p + off, (size_t)len);
+        off += len;
+        return s;
+    }
+    void skip(size_t b) { if (off + b > n) ok = false; else off += b; }
+};
+
+static size_t gguf_scalar_size(uint32_t t)
+{
+    switch (t) {
+    case 0: case 1: case 7: return 1;
+    case 2: case 3: return 2;
+    case 4: case 5: case 6: return 4;
+    case 10: case 11: case 12: return 8;
+    default: return 0;
+    }
+}
+
+// skips one metadata value; returns its u64 view when it is an unsigned integer (for general.alignment)
+static bool gguf_skip_value(Reader &r, uint32_t t, uint64_t *uint_val)
+{
+    if (t == 8) { r.str(); return r.ok; }
+    if (t == 9) {
+        uint32_t et = r.get<uint32_t>();
+        uint64_t cnt = r.get<uint64_t>();
+        if (!r.ok) return false;
+        if (et == 8) { for (uint64_t i = 0; i < cnt && r.ok; i++) r.str(); return r.ok; }
+        size_t es = gguf_scalar_size(et);
+        if (!es) return false;
+        r.skip((size_t)cnt * es);
+        return r.ok;
+    }
+    size_t s = gguf_scalar_size(t);
+    if (!s) return false;
+    if (uint_val && (t == 0 || t == 2 || t == 4 || t == 10)) {
+        uint64_t v = 0;
+        if (r.off + s <= r.n) memcpy(&v, r.p + r.off, s);
+        *uint_val = v;
+    }
+    r.skip(s);
+    return r.ok;
+}
+
+}  // namespace tlb
+
+extern "C" {
+
+tlb_status tlb_map_new(tlb_map **out)
+{
+    if (!out) return fail(TLB_ERR_NULL, "null out");
+    *out = new tlb_map();
+    return TLB_OK;
+}
+
+tlb_status tlb_map_add(tlb_map *m, const char *name, tlb_ggml_type type, const int64_t *shape, int rank, const void *bytes, size_t nbytes)
+{
+    if (!m || !name || (rank > 0 && !shape)) return fail(TLB_ERR_NULL, "null argument");
+    if (!ggml_known(type)) return fail(TLB_ERR_TYPE, "unsupported GGML type %d for '%s'", (int)type, name);
+    if (!ensure_init()) return TLB_ERR_DEVICE;
+    return map_add(m, name, type, shape, rank, bytes, nbytes);
+}
+
+tlb_status tlb_gguf_load(tlb_map **out, const char *path)
+{
+    if (!out) return fail(TLB_ERR_NULL, "null out");
+    *out = nullptr;
+    if (!path) return fail(TLB_ERR_NULL, "null path");
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(TLB_ERR_ARG, "Failed to open GGUF file %s", path);
+    struct stat sb;
+    if (fstat(fd, &sb) != 0) { close(fd); return fail(TLB_ERR_ARG, "cannot stat %s", path); }
+    size_t fsize = (size_t)sb.st_size;
+    if (fsize < 4) { close(fd); return fail(TLB_ERR_ARG, "File too small"); }
+    void *mm = mmap(nullptr, fsize, PROT_READ, MAP_PRIVATE, fd, 0);
+    close(fd);
+    if (mm == MAP_FAILED) return fail(TLB_ERR_ARG, "Failed to mmap GGUF file");
+    tlb_status st = TLB_OK;
+    tlb_map *m = new tlb_map();
+    do {
+        Reader r{(const uint8_t *)mm, fsize};
+        if (memcmp(r.p, "GGUF", 4) != 0) {
+            st = fail(TLB_ERR_ARG, memcmp(r.p, "FUGG", 4) == 0 ? "big-endian GGUF files are not supported" : "Invalid GGUF magic");
+            break;
+        }
+        r.off = 4;
+        uint32_t version = r.get<uint32_t>();
+        uint64_t n_tensors = r.get<uint64_t>(), n_kv = r.get<uint64_t>();
+        if (!r.ok || version < 2 || version > 3) { st = fail(TLB_ERR_ARG, "unsupported GGUF version %u", version); break; }
+        uint64_t alignment = 32;  // default alignment (gguf.rs:102-110)
+        for (uint64_t i = 0; i < n_kv && r.ok; i++) {
+            std::string key = r.str();
+            uint32_t t = r.get<uint32_t>();
+            uint64_t uv = 0;
+            if (!r.ok || !gguf_skip_value(r, t, &uv)) { r.ok = false; break; }
+            if (key == "general.alignment" && uv) alignment = uv;
+        }
+        if (!r.ok) { st = fail(TLB_ERR_ARG, "Failed to decode GGUF metadata"); break; }
+        struct Info { std::string name; std::vector<int64_t> shape; uint32_t type; uint64_t offset; };
+        std::vector<Info> infos;
+        for (uint64_t i = 0; i < n_tensors && r.ok; i++) {
+            Info inf;
+            inf.name = r.str();
+            uint32_t nd = r.get<uint32_t>();
+            if (!r.ok || nd > kMaxRank) { r.ok = false; break; }
+            for (uint32_t d = 0; d < nd; d++) inf.shape.push_back((int64_t)r.get<uint64_t>());
+            inf.type = r.get<uint32_t>();
+            inf.offset = r.get<uint64_t>();
+            // trailing 1-dims are trimmed, then GGML's fastest-first order is reversed (gguf.rs:129-136)
+            while (inf.shape.size() > 1 && inf.shape.back() == 1) inf.shape.pop_back();
+            std::reverse(inf.shape.begin(), inf.shape.end());
+            infos.push_back(inf);
+        }
+        if (!r.ok) { st = fail(TLB_ERR_ARG, "Failed to decode GGUF tensor infos"); break; }
+        uint64_t data_off = (r.off + alignment - 1) / alignment * alignment;
+        for (const Info &inf : infos) {
+            if (!ggml_known((int)inf.type)) continue;  // unsupported kinds are skipped (gguf.rs:157-177)
+            int64_t nelem = 1;
+            for (int64_t d : inf.shape) nelem *= d;
+            size_t nb = ggml_nbytes((int)inf.type, nelem);
+            if (data_off + inf.offset + nb > fsize) continue;  // "data out of bounds": skipped (gguf.rs:183-186)
+            if (qformat((int)inf.type) && (inf.shape.size() != 2 || inf.shape[1] % 256)) continue;
+            st = map_add(m, inf.name, (int)inf.type, inf.shape.data(), (int)inf.shape.size(), r.p + data_off + inf.offset, nb);
+            if (st != TLB_OK) break;
+        }
+    } while (0);
+    munmap(mm, fsize);
+    if (st != TLB_OK) { tlb_map_free(m); return st; }
+    *out = m;
+    return TLB_OK;
+}
+
+tlb_status tlb_map_free(tlb_map *m)
+{
+    if (!m) return TLB_OK;
+    for (auto &kv : m->entries) {
+        tlb_qtensor_release(kv.second.q);
+        tlb_tensor_release(kv.second.f32);
+    }
+    delete m;
+    return TLB_OK;
+}
+
+int64_t tlb_map_count(const tlb_map *m) { return m ? (int64_t)m->names.size() : -1; }
+
+const char *tlb_map_name(const tlb_map *m, int64_t i)
+{
+    return (m && i >= 0 && i < (int64_t)m->names.size()) ? m->names[(size_t)i].c_str() : nullptr;
+}
+
+tlb_status tlb_map_get_quantized(tlb_qtensor **out, tlb_map *m, const char *name)
+{
+    if (!out) return fail(TLB_ERR_NULL, "null out");
+    *out = nullptr;
+    if (!m || !name) return fail(TLB_ERR_NULL, "null argument");
+    auto it = m->entries.find(name);
+    if (it == m->entries.end()) return fail(TLB_ERR_ARG, "Tensor '%s' not found in map", name);
+    if (!it->second.q) return fail(TLB_ERR_TYPE, "Tensor '%s' has GGML type %d, which has no quantized kernel", name, it->second.type);
+    tlb_qtensor_retain(it->second.q);
+    *out = it->second.q;
+    return TLB_OK;
+}
+
+tlb_status tlb_map_get(tlb_tensor **out, tlb_map *m, const char *name)
+{
+    if (!out) return fail(TLB_ERR_NULL, "null out");
+    *out = nullptr;
+    if (!m || !name) return fail(TLB_ERR_NULL, "null argument");
+    auto it = m->entries.find(name);
+    if (it == m->entries.end()) return fail(TLB_ERR_ARG, "Tensor '%s' not found in map", name);
+    MapEntry &e = it->second;
+    if (!e.f32) TLB_TRY(tlb_qtensor_dequantize(&e.f32, e.q));  // cached, as QTensor::cache does
+    tlb_tensor_retain(e.f32);
+    *out = e.f32;
+    return TLB_OK;
+}
+
+/* ---- KV cache handle table ---- */
+
+tlb_status tlb_kvcache_new(tlb_kvcache **out, int64_t layers)
+{
+    if (!out) return fail(TLB_ERR_NULL, "null out");
+    *out = nullptr;
+    if (layers < 0) return fail(TLB_ERR_ARG, "negative layer count");
+    tlb_kvcache *c = new tlb_kvcache();
+    c->layers.assign((size_t)layers, {nullptr, nullptr});
+    *out = c;
+    return TLB_OK;
+}
+
+tlb_status tlb_kvcache_clear(tlb_kvcache *c)
+{
+    if (!c) return fail(TLB_ERR_NULL, "null cache");
+    for (auto &l : c->layers) {
+        tlb_tensor_release(l.first);
+        tlb_tensor_release(l.second);
+        l = {nullptr, nullptr};
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_kvcache_free(tlb_kvcache *c)
+{
+    if (!c) return TLB_OK;
+    tlb_kvcache_clear(c);
+    delete c;
+    return TLB_OK;
+}
+
+int64_t tlb_kvcache_len(const tlb_kvcache *c) { return c ? (int64_t)c->layers.size() : -1; }
+
+tlb_status tlb_kvcache_resize(tlb_kvcache *c, int64_t layers)
+{
+    if (!c) return fail(TLB_ERR_NULL, "null cache");
+    if (layers < 0) return fail(TLB_ERR_ARG, "negative layer count");
+    for (size_t i = (size_t)layers; i < c->layers.size(); i++) {
+        tlb_tensor_release(c->layers[i].first);
+        tlb_tensor_release(c->layers[i].second);
+    }
+    c->layers.resize((size_t)layers, {nullptr, nullptr});
+    return TLB_OK;
+}
+
+static tlb_status kv_get(tlb_tensor **out, tlb_kvcache *c, int64_t layer, bool want_v)
+{
+    if (!out) return fail(TLB_ERR_NULL, "null out");
+    *out = nullptr;
+    if (!c) return fail(TLB_ERR_NULL, "null cache");
+    if (layer < 0 || layer >= (int64_t)c->layers.size()) return fail(TLB_ERR_INDEX, "KV cache layer %lld out of range", (long long)layer);
+    tlb_tensor *t = want_v ? c->layers[(size_t)layer].second : c->layers[(size_t)layer].first;
+    if (!t) return fail(TLB_ERR_NULL, "KV cache layer %lld is empty", (long long)layer);
+    tlb_tensor_retain(t);  // the caller owns one reference (system.rs:513-553)
+    *out = t;
+    return TLB_OK;
+}
+
+tlb_status tlb_kvcache_get_k(tlb_tensor **out, tlb_kvcache *c, int64_t layer) { return kv_get(out, c, layer, false); }
+tlb_status tlb_kvcache_get_v(tlb_tensor **out, tlb_kvcache *c, int64_t layer) { return kv_get(out, c, layer, true); }
+
+tlb_status tlb_kvcache_update(tlb_kvcache *c, int64_t layer, tlb_tensor *k, tlb_tensor *v)
+{
+    if (!c || !k || !v) return fail(TLB_ERR_NULL, "null argument");
+    if (layer < 0) return fail(TLB_ERR_INDEX, "negative layer");
+    if (layer >= (int64_t)c->layers.size()) c->layers.resize((size_t)layer + 1, {nullptr, nullptr});  // grows on demand (system.rs:555-580)
+    tlb_tensor_retain(k);
+    tlb_tensor_retain(v);
+    tlb_tensor_release(c->layers[(size_t)layer].first);
+    tlb_tensor_release(c->layers[(size_t)layer].second);
+    c->layers[(size_t)layer] = {k, v};
+    return TLB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,184 @@
+// Internal declarations shared by the translation units of libtlb200.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/tlb200.h"
+
+namespace tlb {
+
+constexpr int kMaxRank = 8;
+
+// One device, one non-blocking stream (the reference uses the legacy NULL stream and a
+// device-wide sync after every launch, crates/tl_cuda/src/stream.rs:17-22,63-73).
+struct Context {
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    cudaMemPool_t pool = nullptr;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    std::atomic<uint64_t> launches{0};
+    std::atomic<int64_t> bytes_in_use{0};
+    void *flush_buf = nullptr;
+    size_t flush_bytes = 0;
+    int *err_flag = nullptr;  // device word set by kernels whose bounded waits ran out
+    bool capturing = false;
+    uint64_t capture_launches = 0;
+};
+Context *ctx();          // nullptr + error set when no device
+bool ensure_init();
+
+tlb_status fail(tlb_status code, const char *fmt, ...);
+tlb_status cuda_fail(cudaError_t e, const char *what);
+#define TLB_CUDA(expr)                                                   \
+    do {                                                                 \
+        cudaError_t _e = (expr);                                         \
+        if (_e != cudaSuccess) return ::tlb::cuda_fail(_e, #expr);       \
+    } while (0)
+#define TLB_TRY(expr)                                \
+    do {                                             \
+        tlb_status _s = (expr);                      \
+        if (_s != TLB_OK) return _s;                 \
+    } while (0)
+
+inline void count_launch(int n = 1) { Context *c = ctx(); if (c) c->launches += n; }
+
+// Reference-counted device storage (Arc<CudaBuffer>, crates/tl_cuda/src/tensor.rs:39-99).
+struct Storage {
+    std::atomic<int> rc{1};
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+Storage *storage_alloc(size_t bytes);   // nullptr on failure (error set)
+void storage_release(Storage *s);
+
+size_t dtype_size(tlb_dtype dt);
+
+}  // namespace tlb
+
+struct tlb_tensor {
+    std::atomic<int> rc{1};
+    tlb::Storage *st = nullptr;
+    size_t offset = 0;  // bytes into st->ptr (always contiguous row-major)
+    tlb_dtype dt = TLB_F32;
+    int rank = 0;
+    int64_t shape[tlb::kMaxRank] = {0};
+    int64_t numel() const { int64_t n = 1; for (int i = 0; i < rank; i++) n *= shape[i]; return n; }
+    void *data() const { return st ? (char *)st->ptr + offset : nullptr; }
+    float *f32() const { return (float *)data(); }
+};
+
+namespace tlb {
+
+tlb_status new_tensor(tlb_tensor **out, tlb_dtype dt, const int64_t *shape, int rank);
+tlb_status new_view(tlb_tensor **out, const tlb_tensor *src, const int64_t *shape, int rank, size_t extra_off);
+
+// ---- quantized weights ---------------------------------------------------------------
+// Device layout: the [n, k] tensor is cut into units of 16 rows x 256 weights, stored
+// [n/16][k/256][unit bytes]; unit bytes = 16 * 256 * bytes-per-weight (2304 / 4352 / 3360).
+struct QFormat { int type; int unit_bytes; int raw_block; int raw_block_bytes; };
+const QFormat *qformat(int ggml_type);
+
+}  // namespace tlb
+
+struct tlb_qtensor {
+    std::atomic<int> rc{1};
+    int type = 0;
+    int64_t n = 0, k = 0;       // logical rows / cols
+    int64_t n_tiles = 0, upt = 0; // 16-row tiles, units per tile (k/256)
+    tlb::Storage *st = nullptr; // tiled device bytes
+    uint8_t *dev() const { return (uint8_t *)st->ptr; }
+    uint64_t nbytes() const { return (uint64_t)n_tiles * upt * tlb::qformat(type)->unit_bytes; }
+};
+
+namespace tlb {
+
+// ---- kernel launchers (all on ctx()->stream) ------------------------------------------
+// quant.cu
+tlb_status launch_repack(int type, const uint8_t *raw, uint8_t *tiled, int64_t n, int64_t k);
+tlb_status launch_dequant_tiled(int type, const uint8_t *tiled, float *out, int64_t n, int64_t k);
+
+// qmatvec.cu ---------------------------------------------------------------------------
+// How the activation vector of a streaming matvec is produced inside the kernel.
+enum Prologue { PRO_PLAIN = 0, PRO_ADD_NORM = 1, PRO_SILU_MUL = 2 };
+struct MatvecJob {
+    // up to 3 weight tensors sharing K and the same activation (q|k|v, gate|up)
+    int n_w = 0;
+    const uint8_t *w[3] = {nullptr, nullptr, nullptr};
+    int64_t n_tiles[3] = {0, 0, 0};
+    int64_t n_rows[3] = {0, 0, 0};                 // valid output rows (<= n_tiles*16)
+    float *out[3] = {nullptr, nullptr, nullptr};   // each [M, n_rows], must be zero on entry
+    int type = 0;
+    int64_t k = 0;
+    int m = 1;
+    // prologue inputs
+    int prologue = PRO_PLAIN;
+    const float *x = nullptr;        // PLAIN: x [M,K]; ADD_NORM: residual [K]; SILU_MUL: gate [M,K]
+    const float *x2 = nullptr;       // ADD_NORM: delta added to x (may be null); SILU_MUL: up
+    const float *norm_w = nullptr;   // ADD_NORM: weight [K]
+    float eps = 0.f;
+    float *x_out = nullptr;          // ADD_NORM: x + x2 written here by block 0 (may be null)
+    const float *emb_table = nullptr; // ADD_NORM with token lookup: x = emb_table[*token * K ...]
+    const int *token = nullptr;
+    // buffers the kernel clears for later kernels of a chain (may be null)
+    float *zero_ptr[2] = {nullptr, nullptr};
+    int64_t zero_n[2] = {0, 0};
+    bool pdl = false;                // launch with programmatic stream serialization
+};
+tlb_status launch_qmatvec(const MatvecJob &job);
+size_t qmatvec_max_k(int m);   // largest K the single-pass kernel supports for m activation rows
+
+// ops.cu
+tlb_status launch_binary(int op, const float *a, const float *b, float *out, const int64_t *oshape,
+                         const int64_t *astr, const int64_t *bstr, int rank, int64_t n);
+tlb_status launch_unary(int op, const float *a, float *out, int64_t n, float s);
+tlb_status launch_softmax(const float *a, float *out, int64_t outer, int64_t axis, int64_t inner);
+tlb_status launch_matmul(const float *a, const float *b, float *out, int64_t batch, int64_t m,
+                         int64_t k, int64_t n, bool b_batched);
+tlb_status launch_copy_strided(const float *a, float *out, const int64_t *oshape, const int64_t *astr,
+                               int rank, int64_t n, int64_t a_off);
+tlb_status launch_rms_norm(const float *x, const float *res, const float *w, float eps, float *out,
+                           int64_t rows, int64_t d);
+tlb_status launch_rope_cpu(const float *x, const float *cos_t, const float *sin_t, int64_t tab_len,
+                           float *out, int64_t nvec, int64_t d);
+tlb_status launch_rope_half(const float *x, const float *cos_t, const float *sin_t, float *out,
+                            int64_t tokens, int64_t heads, int64_t d);
+tlb_status launch_embedding(const float *table, const float *idx, float *out, int64_t n, int64_t vocab,
+                            int64_t dim, int *oob_flag);
+tlb_status launch_argmax(const float *x, int64_t n, int tie_first, float *out_f32, int *out_i32);
+tlb_status launch_causal_mask(float *out, int64_t size);
+tlb_status launch_rep_penalty(float *logits, const float *tokens, int64_t rows, int64_t vocab, int64_t nt,
+                              float penalty);
+tlb_status launch_silu_mul(const float *g, const float *u, float *out, int64_t n);
+tlb_status launch_f32_to_f16(const float *a, __half *out, int64_t n);
+
+// attention.cu
+struct DecodeAttnJob {
+    const float *qkv;      // [q (H*D) | k (KVH*D) | v (KVH*D)] raw projections of the new token
+    void *kcache, *vcache; // [KVH][max_seq][D] of this layer, f16 or f32
+    int kv_f16;
+    int H, KVH, D, max_seq;
+    const int *pos;        // device: cache row of the new token (attend to rows 0..pos)
+    const int *rope_pos;   // device: angle position
+    const float *cos_t, *sin_t; // [max_seq, D] pair-duplicated tables (CPU convention)
+    float scale;
+    float *partial;        // scratch [KVH][splits][rep][D+2]
+    int *counters;         // [KVH], zero on entry, reset by the kernel
+    int splits;
+    float *out;            // [H*D]
+    bool pdl;
+};
+tlb_status launch_decode_attention(const DecodeAttnJob &j);
+tlb_status launch_sdpa(const float *q, const float *k, const float *v, const float *mask, int mask_mode,
+                       float *out, int64_t bh, int64_t sq, int64_t sk, int64_t d, int64_t mask_bh);
+
+}  // namespace tlb
