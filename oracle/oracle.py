@@ -50,6 +50,8 @@ def lib():
         L.orc_matmul_wt.restype = None
         L.orc_matmul_cached_t.argtypes = [fp, sz, sz, fp, sz, fp]
         L.orc_matmul_cached_t.restype = None
+        L.orc_matmul_cached_t_cols.argtypes = [fp, sz, sz, fp, sz, sz, sz, fp]
+        L.orc_matmul_cached_t_cols.restype = None
         L.orc_rms_norm.argtypes = [fp, fp, C.c_float, sz, sz, fp]
         L.orc_rms_norm.restype = None
         L.orc_rope_table_cpu.argtypes = [sz, sz, C.c_float, fp, fp]
@@ -140,6 +142,16 @@ def qmatmul(t, w, n, k, x):
     rc = lib().orc_qmatmul(t, wp, n, k, xp, m, out.ctypes.data_as(C.POINTER(C.c_float)))
     if rc:
         raise ValueError("orc_qmatmul failed")
+    return out
+
+
+def matmul_cached_t_cols(w_kn, x, j0, j1):
+    """x [k] . w_kn[:, j0:j1] with the reference's strided inner loop; w_kn is [k, n] f32."""
+    k, n = w_kn.shape
+    x, xp = _f(x)
+    out = np.empty(j1 - j0, dtype=np.float32)
+    lib().orc_matmul_cached_t_cols(w_kn.ctypes.data_as(C.POINTER(C.c_float)), n, k, xp, 1, j0, j1,
+                                   out.ctypes.data_as(C.POINTER(C.c_float)))
     return out
 
 

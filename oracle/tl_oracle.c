@@ -682,3 +682,17 @@ done:
     free(t1); free(g); free(u); free(nw);
     return rc;
 }
+
+/* Columns [j0, j1) of orc_matmul_cached_t: the same inner loop (stride n through the cached
+ * transposed weights, crates/tl_cpu/src/tensor.rs:1284-1306) over a subset of the outputs.
+ * Used to time a bounded sample of a large matvec; out has (j1 - j0) entries per row. */
+void orc_matmul_cached_t_cols(const float *w_kn, size_t n, size_t k, const float *x, size_t m,
+                              size_t j0, size_t j1, float *out)
+{
+    for (size_t i = 0; i < m; i++)
+        for (size_t j = j0; j < j1; j++) {
+            float sum = 0.0f;
+            for (size_t p = 0; p < k; p++) sum += x[i * k + p] * w_kn[p * n + j];
+            out[i * (j1 - j0) + (j - j0)] = sum;
+        }
+}

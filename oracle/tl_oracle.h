@@ -56,6 +56,10 @@ void orc_matmul_wt(const float *w_nk, size_t n, size_t k, const float *x, size_t
  * weights [K,N], inner loop strides by N (tensor.rs:1284-1306).  Used for timing. */
 void orc_matmul_cached_t(const float *w_kn, size_t n, size_t k, const float *x, size_t m, float *out);
 
+/* columns [j0, j1) of the same loop: a bounded sample for timing */
+void orc_matmul_cached_t_cols(const float *w_kn, size_t n, size_t k, const float *x, size_t m,
+                              size_t j0, size_t j1, float *out);
+
 /* crates/tl_cpu/src/ffi.rs:2444-2486 (weight may be NULL) */
 void orc_rms_norm(const float *x, const float *w, float eps, size_t rows, size_t d, float *out);
 

@@ -1,0 +1,129 @@
+"""GPU parity of the fused decode session against the oracle's Llama driver: logits within
+max-abs-rel 2e-2 (the stated gate) and identical greedy tokens over the first 32 steps."""
+import numpy as np
+import pytest
+
+import tl_b200 as tl
+from tl_b200 import synth
+
+pytestmark = pytest.mark.gpu
+LOGIT_TOL = 2e-2
+
+
+def relerr(a, b):
+    return float(np.max(np.abs(a - b)) / max(np.max(np.abs(b)), 1e-30))
+
+
+def build(orc, cfg, seed, linear_type, head_type, kv_f16, max_seq, sigma=None):
+    tens = synth.llama_tensors(cfg, seed, linear_type, head_type, scale_sigma=sigma)
+    ref = orc.Llama(dict(cfg, kv_f16=int(kv_f16), max_seq=max_seq), {k: (t, d) for k, (t, d, s) in tens.items()})
+    wmap = tl.map_from_tensors(tens)
+    dec = tl.Decoder(cfg, wmap, kv_f16=kv_f16, max_seq=max_seq)
+    return ref, dec, wmap
+
+
+def run_parity(orc, ref, dec, prompt, steps, ctx0=0):
+    # prompt: the reference CPU path rotates every prompt token at the position of the first one and
+    # masks causally; fed token by token that is rope_pos = ctx0 for all of them
+    if ctx0 == 0:
+        ref_logits = ref.forward(prompt, 0)
+        for i, t in enumerate(prompt):
+            nxt = dec.step(t, i, rope_pos=0)
+        pos = len(prompt)
+    else:
+        assert len(prompt) == 1
+        ref_logits = ref.forward(prompt, ctx0)
+        nxt = dec.step(prompt[0], ctx0)
+        pos = ctx0 + 1
+    worst = relerr(dec.logits(), ref_logits)
+    toks_ref, toks = [], []
+    tok = orc.argmax_last(ref_logits)
+    assert nxt == tok
+    for s in range(steps):
+        ref_logits = ref.forward([tok], pos)
+        nxt = dec.step(tok, pos)
+        worst = max(worst, relerr(dec.logits(), ref_logits))
+        tok = orc.argmax_last(ref_logits)
+        toks_ref.append(tok)
+        toks.append(nxt)
+        pos += 1
+    assert toks == toks_ref
+    assert worst < LOGIT_TOL, worst
+    return toks, worst
+
+
+SMALL = dict(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=320,
+             eps=1e-5, rope_base=10000.0, attn_scale=0.125)
+
+
+@pytest.mark.parametrize("linear,head,kv_f16", [(synth.Q4_K, synth.Q6_K, True), (synth.Q4_K, synth.Q6_K, False),
+                                                 (synth.Q4_0, synth.Q4_0, False), (synth.Q8_0, synth.Q8_0, True)])
+def test_small_model_logits_and_tokens(orc, linear, head, kv_f16):
+    ref, dec, wmap = build(orc, SMALL, 21, linear, head, kv_f16, 64)
+    toks, worst = run_parity(orc, ref, dec, [5, 17, 300, 9, 41], 32)
+    # device-side feedback loop reproduces the host-driven one
+    ref2, dec2, wmap2 = build(orc, SMALL, 21, linear, head, kv_f16, 64)
+    for i, t in enumerate([5, 17, 300, 9, 41]):
+        first = dec2.step(t, i, rope_pos=0)
+    gen = dec2.generate(first, 5, 32)
+    assert gen == toks
+    st = dec.stats(16)
+    assert st["kernels_per_step"] == 5 * 2 + 2
+
+
+def test_tinyllama_shaped_two_layers(orc):
+    """Config C0's shapes (d 2048, 32 heads / 4 KV heads of 64, FFN 5632, vocab 32000, Q4_0, f32 KV), 2 layers."""
+    cfg = dict(synth.TINYLLAMA, n_layers=2)
+    ref, dec, wmap = build(orc, cfg, 3, synth.Q4_0, synth.Q4_0, False, 64)
+    rng = np.random.default_rng(0)
+    run_parity(orc, ref, dec, [int(t) for t in rng.integers(0, cfg["vocab"], 6)], 32)
+
+
+def test_llama3_shaped_one_layer_long_context(orc):
+    """Config C2's shapes (d 4096, 32 / 8 heads of 128, FFN 14336, vocab 128256, Q4_K + Q6_K head, f16 KV),
+    one layer, with a random 300-token context already in the cache (three attention splits)."""
+    cfg = dict(synth.LLAMA3_8B, n_layers=1)
+    ref, dec, wmap = build(orc, cfg, 4, synth.Q4_K, synth.Q6_K, True, 384)
+    rng = np.random.default_rng(1)
+    kvd = cfg["n_kv_heads"] * cfg["head_dim"]
+    k = rng.standard_normal((300, kvd)).astype(np.float16).astype(np.float32)
+    v = rng.standard_normal((300, kvd)).astype(np.float16).astype(np.float32)
+    dec.kv_write(0, 0, k, v)
+    for p in range(300):
+        ref.kv_write(0, p, k[p], v[p])
+    run_parity(orc, ref, dec, [12345], 8, ctx0=300)
+
+
+def test_decoder_argument_errors(orc):
+    ref, dec, wmap = build(orc, SMALL, 5, synth.Q4_K, synth.Q6_K, True, 32)
+    with pytest.raises(tl.TlbError) as e:
+        dec.step(320, 0)
+    assert e.value.code == 6
+    with pytest.raises(tl.TlbError) as e:
+        dec.step(1, 32)
+    assert e.value.code == 6
+    bad = dict(SMALL, d_model=512)
+    with pytest.raises(tl.TlbError):
+        tl.Decoder(bad, wmap, kv_f16=True, max_seq=32)
+
+
+def test_gguf_file_round_trip(orc, tmp_path):
+    """Weights written as a GGUF v3 file and loaded through tlb_gguf_load give the same session."""
+    tens = synth.llama_tensors(SMALL, 9, synth.Q4_K, synth.Q6_K)
+    path = tmp_path / "small.gguf"
+    synth.write_gguf(path, tens, metadata={"general.architecture": "llama", "general.alignment": 32,
+                                           "tokenizer.ggml.tokens": [1, 2, 3]})
+    m = tl.TensorMap.load(path)
+    assert sorted(m.names()) == sorted(tens.keys())
+    t, d, s = tens["blk.1.ffn_down.weight"]
+    got = m.get("blk.1.ffn_down.weight").numpy()
+    np.testing.assert_array_equal(got.view(np.uint32), orc.dequantize(t, d, got.size).reshape(s).view(np.uint32))
+    np.testing.assert_array_equal(m.get("token_embd.weight").numpy().reshape(-1), tens["token_embd.weight"][1].view(np.float32))
+    dec = tl.Decoder(SMALL, m, kv_f16=True, max_seq=32)
+    dec2 = tl.Decoder(SMALL, tl.map_from_tensors(tens), kv_f16=True, max_seq=32)
+    assert dec.step(7, 0) == dec2.step(7, 0)
+    np.testing.assert_array_equal(dec.logits(), dec2.logits())
+    with pytest.raises(tl.TlbError):
+        m.get_quantized("token_embd.weight")   # F32 tensors have no quantized kernel
+    with pytest.raises(tl.TlbError):
+        m.get("missing.weight")

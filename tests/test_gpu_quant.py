@@ -1,0 +1,143 @@
+"""GPU parity: dequantisation (bit-exact) and the dequant-fused matvec against the CPU oracle,
+through the C ABI."""
+import numpy as np
+import pytest
+
+import tl_b200 as tl
+from tl_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+TYPES = [synth.Q4_0, synth.Q8_0, synth.Q4_K, synth.Q6_K]
+MATVEC_TOL = 1e-4   # our own bar; the required gate is 2e-2 max-abs-rel
+
+
+def relerr(a, b):
+    return float(np.max(np.abs(a - b)) / max(np.max(np.abs(b)), 1e-30))
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("n,k", [(16, 256), (48, 1024), (33, 512), (1, 256)])
+def test_dequant_bit_exact(orc, t, n, k):
+    rng = np.random.default_rng(1000 + t + n)
+    w = synth.random_quant(t, n, k, rng)
+    q = tl.QTensor.from_gguf_bytes(t, n, k, w)
+    info = q.info()
+    assert (info["type"], info["n"], info["k"]) == (t, n, k)
+    assert info["device_bytes"] == (n + 15) // 16 * 16 * k * synth.bytes_per_weight(t)
+    got = q.dequantize().numpy()
+    ref = orc.dequantize(t, w.reshape(-1), n * k).reshape(n, k)
+    np.testing.assert_array_equal(got.view(np.uint32), ref.view(np.uint32))
+
+
+def test_dequant_extreme_blocks(orc):
+    """f16 scales that are subnormal, zero, negative and the largest finite value; all-ones quants."""
+    for t in TYPES:
+        blk, nb = synth.BLOCK[t]
+        n, k = 16, 256
+        w = np.full((n * k // blk, nb), 0xFF, dtype=np.uint8)
+        scales = np.array([0x0001, 0x0000, 0x8001, 0x7BFF, 0x03FF, 0xFBFF, 0x3C00, 0x0400], dtype=np.uint16)
+        pos = {synth.Q4_0: 0, synth.Q8_0: 0, synth.Q4_K: 0, synth.Q6_K: 208}[t]
+        for i in range(w.shape[0]):
+            w[i, pos:pos + 2] = np.array([scales[i % 8]], dtype=np.uint16).view(np.uint8)
+            if t == synth.Q4_K:
+                w[i, 2:4] = np.array([scales[(i + 3) % 8]], dtype=np.uint16).view(np.uint8)
+        got = tl.QTensor.from_gguf_bytes(t, n, k, w).dequantize().numpy()
+        ref = orc.dequantize(t, w.reshape(-1), n * k).reshape(n, k)
+        np.testing.assert_array_equal(got.view(np.uint32), ref.view(np.uint32))
+
+
+def test_dequant_full_size_rows_checksum(orc):
+    """A Llama-3-8B sized projection (4096 x 4096, Q4_K): bit-exact on sampled rows + u32 checksum of all."""
+    rng = np.random.default_rng(7)
+    n = k = 4096
+    w = synth.random_quant(synth.Q4_K, n, k, rng)
+    got = tl.QTensor.from_gguf_bytes(synth.Q4_K, n, k, w).dequantize().numpy()
+    ref = orc.dequantize(synth.Q4_K, w.reshape(-1), n * k).reshape(n, k)
+    assert int(got.view(np.uint32).sum(dtype=np.uint64)) == int(ref.view(np.uint32).sum(dtype=np.uint64))
+    np.testing.assert_array_equal(got[::97].view(np.uint32), ref[::97].view(np.uint32))
+
+
+def test_qtensor_rejects_bad_input():
+    with pytest.raises(tl.TlbError) as e:
+        tl.QTensor.from_gguf_bytes(synth.Q4_K, 16, 256, np.zeros(100, dtype=np.uint8))
+    assert e.value.code == 1
+    with pytest.raises(tl.TlbError) as e:
+        tl.QTensor.from_gguf_bytes(synth.Q4_0, 16, 96, np.zeros(16 * 3 * 18, dtype=np.uint8))
+    assert e.value.code == 1
+    with pytest.raises(tl.TlbError) as e:
+        tl.QTensor.from_gguf_bytes(5, 16, 256, np.zeros(16, dtype=np.uint8))  # Q4_1: recognised by GGUF, no kernel
+    assert e.value.code == 7
+    q = tl.QTensor.from_gguf_bytes(synth.Q4_K, 0, 256, np.zeros(0, dtype=np.uint8))  # empty tensor
+    assert q.dequantize().numpy().shape == (0, 256)
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("n,k,m", [(16, 256, 1), (48, 1024, 1), (33, 512, 2), (256, 2048, 4), (64, 512, 6), (40, 768, 3)])
+def test_qmatvec_matches_oracle(orc, t, n, k, m):
+    rng = np.random.default_rng(2000 + t + n + m)
+    w = synth.random_quant(t, n, k, rng)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    q = tl.QTensor.from_gguf_bytes(t, n, k, w)
+    got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+    ref = orc.qmatmul(t, w.reshape(-1), n, k, x)
+    assert got.shape == (m, n)
+    assert relerr(got, ref) < MATVEC_TOL
+
+
+@pytest.mark.parametrize("t,n,k", [(synth.Q4_K, 4096, 4096), (synth.Q4_K, 4096, 14336), (synth.Q6_K, 8192, 4096),
+                                   (synth.Q8_0, 2048, 2048), (synth.Q4_0, 5632, 2048)])
+def test_qmatvec_model_shapes(orc, t, n, k):
+    rng = np.random.default_rng(3000 + t + n)
+    w = synth.random_quant(t, n, k, rng)
+    x = rng.standard_normal(k, dtype=np.float32)
+    q = tl.QTensor.from_gguf_bytes(t, n, k, w)
+    xt = tl.Tensor.from_numpy(x)
+    got = xt.matmul_quantized(q).numpy()
+    rows = np.unique(np.concatenate([np.arange(0, n, 61), [n - 1]]))
+    wrows = w[rows]
+    ref = orc.qmatmul(t, wrows.reshape(-1), len(rows), k, x)[0]
+    assert got.shape == (n,)
+    assert relerr(got[rows], ref) < MATVEC_TOL
+    again = xt.matmul_quantized(q).numpy()      # scheduling-independent: bitwise repeatable
+    np.testing.assert_array_equal(got.view(np.uint32), again.view(np.uint32))
+
+
+def test_qmatvec_linearity_and_scale_invariance():
+    """Size-independent properties on a full-size shape: W(a x + b y) = a Wx + b Wy, and the internal
+    power-of-two activation scaling is invisible (W(2^20 x) = 2^20 Wx exactly)."""
+    rng = np.random.default_rng(11)
+    n, k = 4096, 4096
+    q = tl.QTensor.from_gguf_bytes(synth.Q4_K, n, k, synth.random_quant(synth.Q4_K, n, k, rng))
+    x = rng.standard_normal(k, dtype=np.float32)
+    y = rng.standard_normal(k, dtype=np.float32)
+    f = lambda v: tl.Tensor.from_numpy(v).matmul_quantized(q).numpy()
+    wx, wy = f(x), f(y)
+    assert relerr(f(np.float32(0.5) * x + np.float32(2) * y), np.float32(0.5) * wx + np.float32(2) * wy) < 1e-5
+    np.testing.assert_array_equal(f(x * np.float32(2 ** 20)), wx * np.float32(2 ** 20))
+    z = f(np.zeros(k, dtype=np.float32))
+    assert not z.any()
+
+
+def test_qmatvec_wide_dynamic_range(orc):
+    """Activations spanning 12 orders of magnitude and huge values (no f16 overflow inside)."""
+    rng = np.random.default_rng(12)
+    n, k = 64, 1024
+    w = synth.random_quant(synth.Q4_K, n, k, rng)
+    x = (rng.standard_normal(k) * 10.0 ** rng.uniform(-6, 6, k)).astype(np.float32)
+    q = tl.QTensor.from_gguf_bytes(synth.Q4_K, n, k, w)
+    got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+    ref = orc.qmatmul(synth.Q4_K, w.reshape(-1), n, k, x)[0]
+    assert relerr(got, ref) < MATVEC_TOL
+    big = (x * np.float32(1e20)).astype(np.float32)
+    got = tl.Tensor.from_numpy(big).matmul_quantized(q).numpy()
+    assert np.isfinite(got).all()
+
+
+def test_qmatvec_shape_errors():
+    q = tl.QTensor.from_gguf_bytes(synth.Q4_K, 16, 256, np.zeros(16 * 144, dtype=np.uint8))
+    with pytest.raises(tl.TlbError) as e:
+        tl.Tensor.from_numpy(np.zeros(128, dtype=np.float32)).matmul_quantized(q)
+    assert e.value.code == 1
+    out = tl.Tensor.from_numpy(np.zeros((0, 256), dtype=np.float32)).matmul_quantized(q)  # empty batch
+    assert out.shape == (0, 16)

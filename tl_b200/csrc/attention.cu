@@ -259,12 +259,12 @@ static tlb_status launch_decode_t(const AttnParams &p, int max_splits, int KVH, 
 {
     int NG = kAttnThreads / (p.D / 2);
     size_t smem = (size_t)2 * kKeysPerCta * p.row_stride + (size_t)(REP * p.D + kKeysPerCta * REP + REP * 2 + NG * REP * p.D) * sizeof(float);
-    static bool set = false;
-    if (!set) {
-        TLB_CUDA(cudaFuncSetAttribute(decode_attention_kernel<T, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx()->smem_optin));
-        set = true;
+    if (smem + 1024 > ctx()->smem_optin) return fail(TLB_ERR_SHAPE, "decode attention needs %zu bytes of shared memory", smem);
+    static size_t set_bytes = 0;   // the kernel also has a few bytes of static shared memory
+    if (smem > set_bytes) {
+        TLB_CUDA(cudaFuncSetAttribute(decode_attention_kernel<T, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        set_bytes = smem;
     }
-    if (smem > ctx()->smem_optin) return fail(TLB_ERR_SHAPE, "decode attention needs %zu bytes of shared memory", smem);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(max_splits, KVH);
     cfg.blockDim = dim3(kAttnThreads);

@@ -536,7 +536,6 @@ __global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_const
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    if (p.use_pdl) pdl_launch_dependents();
     volatile int *abortp = &sh->abort_flag;
 
     if (warp == kConsumerWarps) {
@@ -557,7 +556,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_const
     }
 
     // ---- consumers
-    if (p.use_pdl) pdl_wait();   // everything below may read what the previous kernel wrote
+    if (p.use_pdl) {
+        pdl_wait();                // everything below may read what the previous kernel wrote
+        // Released only after our own wait: a dependent's early part then runs with every kernel
+        // before our predecessor complete, so it may read state those kernels wrote.
+        pdl_launch_dependents();
+    }
     for (int z = 0; z < 2; z++)
         if (p.zero_ptr[z])
             for (long long idx = (long long)b * kConsumerThreads + tid; idx < p.zero_n[z]; idx += (long long)G * kConsumerThreads)
