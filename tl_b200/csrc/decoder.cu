@@ -164,9 +164,9 @@ tlb_status enqueue_step(tlb_decoder *d)
             j.prologue = PRO_ADD_NORM;
             j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
             if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; j.x = nullptr; j.x2 = nullptr; }
-            else { j.x = d->xa; j.x2 = d->down_out; }
+            else { j.x = d->xa; j.x2 = d->down_out; j.x3 = d->down_out + dm; }
             j.x_out = d->xb;
-            j.zero_ptr[0] = d->o_out; j.zero_n[0] = dm;
+            j.zero_ptr[0] = d->o_out; j.zero_n[0] = 2 * dm;
             j.pdl = d->pdl;
             TLB_TRY(launch_qmatvec(j));
         }
@@ -184,6 +184,7 @@ tlb_status enqueue_step(tlb_decoder *d)
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.o, d->o_out);
+            j.out_alt[0] = d->o_out + dm;
             j.type = w.o->type; j.k = qd; j.m = 1;
             j.prologue = PRO_PLAIN; j.x = d->attn;
             j.zero_ptr[0] = d->gu; j.zero_n[0] = 2 * (int64_t)F;
@@ -196,9 +197,9 @@ tlb_status enqueue_step(tlb_decoder *d)
             set_w(j, 0, w.gate, d->gu);
             set_w(j, 1, w.up, d->gu + F);
             j.type = w.gate->type; j.k = dm; j.m = 1;
-            j.prologue = PRO_ADD_NORM; j.x = d->xb; j.x2 = d->o_out; j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
+            j.prologue = PRO_ADD_NORM; j.x = d->xb; j.x2 = d->o_out; j.x3 = d->o_out + dm; j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
             j.x_out = d->xa;
-            j.zero_ptr[0] = d->down_out; j.zero_n[0] = dm;
+            j.zero_ptr[0] = d->down_out; j.zero_n[0] = 2 * dm;
             j.pdl = d->pdl;
             TLB_TRY(launch_qmatvec(j));
         }
@@ -206,6 +207,7 @@ tlb_status enqueue_step(tlb_decoder *d)
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.down, d->down_out);
+            j.out_alt[0] = d->down_out + dm;
             j.type = w.down->type; j.k = F; j.m = 1;
             j.prologue = PRO_SILU_MUL; j.x = d->gu; j.x2 = d->gu + F;
             j.zero_ptr[0] = d->qkv; j.zero_n[0] = qd + 2 * kvd;
@@ -219,7 +221,7 @@ tlb_status enqueue_step(tlb_decoder *d)
         j.n_w = 1;
         set_w(j, 0, d->head, d->logits);
         j.type = d->head->type; j.k = dm; j.m = 1;
-        j.prologue = PRO_ADD_NORM; j.x = d->xa; j.x2 = d->down_out; j.norm_w = d->out_norm->f32(); j.eps = c.eps;
+        j.prologue = PRO_ADD_NORM; j.x = d->xa; j.x2 = d->down_out; j.x3 = d->down_out + dm; j.norm_w = d->out_norm->f32(); j.eps = c.eps;
         j.x_out = d->xb;
         j.pdl = d->pdl;
         TLB_TRY(launch_qmatvec(j));
@@ -332,8 +334,8 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
         return fail(TLB_ERR_SHAPE, "inner dimensions up to %zu fit the single-pass matvec", kmax);
     }
     TRY_D(dalloc(d, &d->xa, dm)); TRY_D(dalloc(d, &d->xb, dm));
-    TRY_D(dalloc(d, &d->qkv, qd + 2 * kvd)); TRY_D(dalloc(d, &d->attn, qd)); TRY_D(dalloc(d, &d->o_out, dm));
-    TRY_D(dalloc(d, &d->gu, 2 * F)); TRY_D(dalloc(d, &d->down_out, dm)); TRY_D(dalloc(d, &d->logits, c.vocab));
+    TRY_D(dalloc(d, &d->qkv, qd + 2 * kvd)); TRY_D(dalloc(d, &d->attn, qd)); TRY_D(dalloc(d, &d->o_out, 2 * dm));   // two accumulation slots
+    TRY_D(dalloc(d, &d->gu, 2 * F)); TRY_D(dalloc(d, &d->down_out, 2 * dm)); TRY_D(dalloc(d, &d->logits, c.vocab));
     d->kv_layer_elems = (size_t)kvd * c.max_seq;
     size_t kv_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
     TRY_D(dalloc(d, (char **)&d->kcache, kv_bytes)); TRY_D(dalloc(d, (char **)&d->vcache, kv_bytes));
@@ -469,16 +471,18 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
     int64_t kk = (w == "o") ? qd : (w == "down") ? F : dm;
     float *xin = nullptr, *outb[2] = {nullptr, nullptr};
     TLB_CUDA(cudaMalloc(&xin, (size_t)std::max<int64_t>(kk, 2 * F) * 4));
-    TLB_CUDA(cudaMalloc(&outb[0], (size_t)out_n * 4));
-    TLB_CUDA(cudaMalloc(&outb[1], (size_t)out_n * 4));
+    TLB_CUDA(cudaMalloc(&outb[0], (size_t)out_n * 8));   // room for the second accumulation slot
+    TLB_CUDA(cudaMalloc(&outb[1], (size_t)out_n * 8));
     {
         std::vector<float> hx((size_t)std::max<int64_t>(kk, 2 * F));
         uint32_t s = 12345u;
         for (float &v : hx) { s = s * 1664525u + 1013904223u; v = ((s >> 8) / 8388608.0f) - 1.0f; }
         cudaMemcpy(xin, hx.data(), hx.size() * 4, cudaMemcpyHostToDevice);
-        cudaMemset(outb[0], 0, (size_t)out_n * 4);
-        cudaMemset(outb[1], 0, (size_t)out_n * 4);
+        cudaMemset(outb[0], 0, (size_t)out_n * 8);
+        cudaMemset(outb[1], 0, (size_t)out_n * 8);
     }
+    long long *trace = nullptr;   // TLB_TRACE=1: per-CTA clock stamps of the last timed launch, printed to stderr
+    if (getenv("TLB_TRACE")) { cudaMalloc(&trace, 512 * 10 * sizeof(long long)); cudaMemset(trace, 0, 512 * 10 * sizeof(long long)); }
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
@@ -503,7 +507,9 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         } else {
             j.n_w = 1; set_w(j, 0, d->head, o); j.type = d->head->type; j.k = dm; bytes = d->head->nbytes();
         }
-        j.zero_ptr[0] = outb[(it + 4) & 1]; j.zero_n[0] = out_n;
+        j.zero_ptr[0] = outb[(it + 4) & 1]; j.zero_n[0] = 2 * out_n;
+        if (w == "o" || w == "down") j.out_alt[0] = o + out_n;   // as in the decode chain
+        if (trace && it == iters - 1) j.trace = trace;
         st = launch_qmatvec(j);
     }
     cudaEventRecord(e1, ctx()->stream);
@@ -511,6 +517,20 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
     float ms = 0.f;
     cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (trace) {
+        std::vector<long long> h(512 * 10);
+        cudaMemcpy(h.data(), trace, h.size() * sizeof(long long), cudaMemcpyDeviceToHost);
+        long long t_first = -1, t_last = 0;
+        for (int b = 0; b < 512; b++) if (h[b * 10 + 8]) { if (t_first < 0 || h[b * 10 + 8] < t_first) t_first = h[b * 10 + 8]; t_last = std::max(t_last, h[b * 10 + 9]); }
+        fprintf(stderr, "[tlb trace] %s: grid span %lld ns\n", which, t_last - t_first);
+        for (int b : {0, 1, 147, 148, 295}) {
+            const long long *t = &h[b * 10];
+            if (!t[8]) continue;
+            fprintf(stderr, "[tlb trace] cta %3d: start +%lld ns; cycles: init %lld, wait+zero %lld, prologue %lld, first unit ready %lld, first unit %lld, rest %lld; end +%lld ns\n",
+                    b, t[8] - t_first, t[1] - t[0], t[2] - t[1], t[3] - t[2], t[4] - t[3], t[5] - t[4], t[6] - t[5], t[9] - t_first);
+        }
+        cudaFree(trace);
+    }
     cudaFree(xin); cudaFree(outb[0]); cudaFree(outb[1]);
     if (st != TLB_OK) return st;
     *us_per_launch = ms * 1000.f / (float)std::max(1, iters);

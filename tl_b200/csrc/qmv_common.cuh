@@ -1,0 +1,219 @@
+// Shared pieces of the streaming quantized matvec: PTX wrappers, kernel parameters, and the prologue
+// that turns the f32 activation into int8 MMA operands in shared memory.
+#pragma once
+#include "tlb_internal.h"
+
+namespace tlb {
+
+constexpr int kMaxCols = 8;        // columns of the MMA B operand (n = 8)
+
+// ---------------------------------------------------------------- PTX helpers
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: gives up after ~2 s, records the reason and raises the CTA-wide abort flag.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err, int code)
+{
+    unsigned long long t0 = global_ns();
+    for (int it = 0;; it++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63) == 63) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > 2000000000ull) {
+                *abort_flag = 1;
+                atomicExch(err, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err, int code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, err, code);
+}
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity)
+{
+    unsigned long long t0 = global_ns();
+    for (int it = 0;; it++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63) == 63 && global_ns() - t0 > 1000000000ull) return false;
+    }
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void named_bar(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 lds128(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b)
+{
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+// (a & m) | o in one LOP3 (register operands: two immediates cannot be encoded in one instruction)
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t m, uint32_t o)
+{
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(m), "r"(o));
+    return d;
+}
+__device__ __forceinline__ float2 h2_to_f2(uint32_t h)
+{
+    return __half22float2(*reinterpret_cast<const __half2 *>(&h));
+}
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i)
+{
+    return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+// D(16x8 f32) += A(16x16 f16, row) * B(16x8 f16, col)
+__device__ __forceinline__ void hmma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// D(16x8 s32) = A(16x32 u8 or s8, row) * B(32x8 s8, col); exact integer sums
+template <bool A_SIGNED>
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    if (A_SIGNED)
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+    else
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// ---------------------------------------------------------------- kernel parameters
+
+struct MvParams {
+    const uint8_t *w[3];
+    float *out[3];          // out[i] (+ out_alt[i] when split over two accumulation slots)
+    float *out_alt[3];
+    int tiles_end[3];       // cumulative tile counts
+    int n_rows[3];          // valid output rows per tensor
+    int n_w;
+    int upt;                // units per tile = K / 256
+    int k;
+    int m;                  // activation rows, 1..4
+    int nl;                 // int8 levels per activation row (3 for m <= 2, else 2)
+    int total_units;
+    int unit_bytes, stage_bytes, n_stages;
+    int prologue;
+    const float *x, *x2, *x3, *norm_w;
+    float eps;
+    float *x_out;
+    const float *emb_table;
+    const int *token;
+    float *zero_ptr[3];
+    long long zero_n[3];
+    int *err;
+    int use_pdl;
+    long long *trace;       // optional: [grid][8] SM clock stamps of thread 0 of every CTA (timing studies)
+    // shared-memory offsets (bytes from the start of dynamic shared memory)
+    int off_xq, off_alam, off_xsum, off_sa, off_red, off_bars, off_misc;
+    int col_stride;         // bytes between int8 activation columns (K + 64)
+};
+
+// Scratch of the prologue.
+struct MvShared {
+    float red_sum[32];
+    float red_max[32];
+    float inv_scale;             // 1 / (power-of-two scale of the f16 sub-block sums)
+    int abort_flag;
+};
+
+__device__ __forceinline__ float silu_f(float g) { return g * (1.0f / (1.0f + expf(-g))); }
+
+// Activation elements 4*k4 .. 4*k4+3 of row `mrow` as the matvec consumes them.  inv_rms == 0 selects
+// the statistics pass of PRO_ADD_NORM (returns the un-normalised residual sum).
+__device__ __forceinline__ float4 prologue_value(const MvParams &p, const float *xbase, int mrow, int k4, float inv_rms)
+{
+    const size_t row4 = (size_t)mrow * (p.k / 4) + k4;
+    float4 v = __ldg(reinterpret_cast<const float4 *>(xbase) + row4);
+    if (p.prologue == PRO_ADD_NORM) {
+        if (p.x2) {
+            float4 d = __ldg(reinterpret_cast<const float4 *>(p.x2) + row4);
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        }
+        if (p.x3) {
+            float4 d = __ldg(reinterpret_cast<const float4 *>(p.x3) + row4);
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        }
+        if (inv_rms != 0.f) {  // (x / rms) * weight (crates/tl_cpu/src/ffi.rs:2444-2486), the division as a multiply by 1/rms
+            float4 w = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + k4);
+            v.x = (v.x * inv_rms) * w.x; v.y = (v.y * inv_rms) * w.y;
+            v.z = (v.z * inv_rms) * w.z; v.w = (v.w * inv_rms) * w.w;
+        }
+    } else if (p.prologue == PRO_SILU_MUL) {
+        float4 u = __ldg(reinterpret_cast<const float4 *>(p.x2) + row4);
+        v.x = silu_f(v.x) * u.x; v.y = silu_f(v.y) * u.y; v.z = silu_f(v.z) * u.z; v.w = silu_f(v.w) * u.w;
+    }
+    return v;
+}
+
+}  // namespace tlb
+

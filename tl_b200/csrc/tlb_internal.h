@@ -117,6 +117,10 @@ struct MatvecJob {
     int64_t n_tiles[3] = {0, 0, 0};
     int64_t n_rows[3] = {0, 0, 0};                 // valid output rows (<= n_tiles*16)
     float *out[3] = {nullptr, nullptr, nullptr};   // each [M, n_rows], must be zero on entry
+    // Optional second accumulation slot per output (also zero on entry): odd CTAs add there, the reader
+    // sums both.  Lets twice as many CTAs share a tile with scheduling-independent sums.
+    float *out_alt[3] = {nullptr, nullptr, nullptr};
+    int force_warps = 0;             // 16: one CTA of 16 consumer warps per SM even where two of 8 would fit
     int type = 0;
     int64_t k = 0;
     int m = 1;
@@ -124,15 +128,17 @@ struct MatvecJob {
     int prologue = PRO_PLAIN;
     const float *x = nullptr;        // PLAIN: x [M,K]; ADD_NORM: residual [K]; SILU_MUL: gate [M,K]
     const float *x2 = nullptr;       // ADD_NORM: delta added to x (may be null); SILU_MUL: up
+    const float *x3 = nullptr;       // ADD_NORM: second delta (the other accumulation slot; may be null)
     const float *norm_w = nullptr;   // ADD_NORM: weight [K]
     float eps = 0.f;
     float *x_out = nullptr;          // ADD_NORM: x + x2 written here by block 0 (may be null)
     const float *emb_table = nullptr; // ADD_NORM with token lookup: x = emb_table[*token * K ...]
     const int *token = nullptr;
     // buffers the kernel clears for later kernels of a chain (may be null)
-    float *zero_ptr[2] = {nullptr, nullptr};
-    int64_t zero_n[2] = {0, 0};
+    float *zero_ptr[3] = {nullptr, nullptr, nullptr};
+    int64_t zero_n[3] = {0, 0, 0};
     bool pdl = false;                // launch with programmatic stream serialization
+    long long *trace = nullptr;      // optional device buffer [grid][8] of SM clock stamps (timing studies)
 };
 tlb_status launch_qmatvec(const MatvecJob &job);
 size_t qmatvec_max_k(int m);   // largest K the single-pass kernel supports for m activation rows
