@@ -57,10 +57,11 @@ __global__ void __launch_bounds__(NW * 32 + 32, (NW <= 8) ? 2 : 1) qmatvec_kerne
     STAMP(0);
     if (p.trace && tid == 0) p.trace[(size_t)b * 10 + 8] = (long long)global_ns();
 
+    const uint32_t act_bar = full0 + 2 * nst * 8;   // completion of the activation-image copy
     if (tid < nst) {   // one thread per stage: the inits run in parallel
         mbar_init(full0 + tid * 8, 1);
         mbar_init(empty0 + tid * 8, 1);
-        if (tid == 0) sh->abort_flag = 0;
+        if (tid == 0) { sh->abort_flag = 0; mbar_init(act_bar, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -102,9 +103,9 @@ __global__ void __launch_bounds__(NW * 32 + 32, (NW <= 8) ? 2 : 1) qmatvec_kerne
         if (p.zero_ptr[z])
             for (long long idx = (long long)b * NT + tid; idx < p.zero_n[z]; idx += (long long)G * NT) p.zero_ptr[z][idx] = 0.f;
     STAMP(2);
-    build_activation<FMT>(p, sh, smem, tid, NT);
+    const bool act_ok = build_activation<FMT>(p, sh, smem, tid, NT, act_bar, abortp);
     STAMP(3);
-    const float inv_s = sh->inv_scale;
+    if (!act_ok) return;   // a bounded wait gave up: the error word is set, outputs stay untouched
     const int ncols = p.m * p.nl;
     LaneCtx L;
     L.lane = lane; L.r = lane >> 2; L.c = lane & 3;
@@ -117,6 +118,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, (NW <= 8) ? 2 : 1) qmatvec_kerne
         L.sa_b = smem_u32(smem + p.off_sa) + colr * 32;
         L.sa_c0 = smem_u32(smem + p.off_sa) + c0 * 4;
         L.sa_c1 = smem_u32(smem + p.off_sa) + c1 * 4;
+        L.minv_b = smem_u32(smem + p.off_minv) + (c < p.m ? c : 0) * 4;
     }
 
     // Ring cursor of this warp, advanced incrementally (no integer division in the unit loop):
@@ -143,26 +145,36 @@ __global__ void __launch_bounds__(NW * 32 + 32, (NW <= 8) ? 2 : 1) qmatvec_kerne
         rp[(2 * L.c + 1) * 16 + L.r] = master[1];
         rp[(2 * L.c) * 16 + L.r + 8] = master[2];
         rp[(2 * L.c + 1) * 16 + L.r + 8] = master[3];
-        if (FMT == TLB_GGML_Q4_K) {   // min term of activation row c: columns (hi, lo) summed, undo the power-of-two scale
-            rp[(8 + L.c) * 16 + L.r] = -(mm[0] + mm[1]) * inv_s;
-            rp[(8 + L.c) * 16 + L.r + 8] = -(mm[2] + mm[3]) * inv_s;
+        if (FMT == TLB_GGML_Q4_K) {   // min term of activation row c: columns (hi, lo) summed
+            rp[(8 + L.c) * 16 + L.r] = -(mm[0] + mm[1]);
+            rp[(8 + L.c) * 16 + L.r + 8] = -(mm[2] + mm[3]);
         }
         named_bar(1, NT);
-        if (tid < p.m * 16) {
-            const int mi = tid >> 4, row = tid & 15;
-            const float *rq = red + (size_t)par * NW * (kRedCols * 16) + row;
-            float sum = 0.f;
-            for (int w = 0; w < NW; w++) {
-                const float *rw = rq + w * (kRedCols * 16);
-                float s = (FMT == TLB_GGML_Q4_K) ? rw[(8 + mi) * 16] : 0.f;
-                for (int l = 0; l < p.nl; l++) s += rw[(mi * p.nl + l) * 16];
-                sum += s;
-            }
+        {
+            // Every warp reduces its share of the 16 rows: lane = (source warp, column slot); the
+            // butterfly adds in a fixed order, so the sum does not depend on timing.
+            constexpr int RPW = 16 / NW, CSL = 32 / NW;   // rows per warp, column slots per pass
+            const int w_src = lane % NW, cs = lane / NW;
             const int wi = (tile >= p.tiles_end[0]) + (tile >= p.tiles_end[1]);
             const int t0 = wi == 0 ? 0 : p.tiles_end[wi - 1];
-            const int grow = (tile - t0) * 16 + row;
             float *dst = (p.out_alt[wi] && (b & 1)) ? p.out_alt[wi] : p.out[wi];
-            if (grow < p.n_rows[wi]) atomicAdd(dst + (size_t)mi * p.n_rows[wi] + grow, sum);
+            const float *rsrc = red + ((size_t)par * NW + w_src) * (kRedCols * 16);
+#pragma unroll
+            for (int rr = 0; rr < RPW; rr++) {
+                const int row = warp * RPW + rr;
+                for (int mi = 0; mi < p.m; mi++) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int c0 = 0; c0 < 4; c0 += CSL) {
+                        const int slot = c0 + cs;
+                        if (slot < p.nl) v += rsrc[(mi * p.nl + slot) * 16 + row];
+                        else if (FMT == TLB_GGML_Q4_K && slot == p.nl) v += rsrc[(8 + mi) * 16 + row];
+                    }
+                    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    const int grow = (tile - t0) * 16 + row;
+                    if (lane == 0 && grow < p.n_rows[wi]) atomicAdd(dst + (size_t)mi * p.n_rows[wi] + grow, v);
+                }
+            }
         }
         u = seg_end;
         tile++;
@@ -175,7 +187,7 @@ __global__ void __launch_bounds__(NW * 32 + 32, (NW <= 8) ? 2 : 1) qmatvec_kerne
 
 // ---------------------------------------------------------------- host side
 
-struct SmemPlan { int off_xq, off_alam, off_xsum, off_sa, off_red, off_bars, off_misc, col_stride; size_t fixed; };
+struct SmemPlan { int off_xq, off_alam, off_xsum, off_sa, off_minv, off_red, off_bars, off_misc, col_stride; size_t fixed; };
 
 static SmemPlan plan_smem(int type, int m, int nl, int64_t k, int nw)
 {
@@ -188,6 +200,7 @@ static SmemPlan plan_smem(int type, int m, int nl, int64_t k, int nw)
     s.off_alam = take((size_t)(k / 256) * kMaxCols * 4);
     s.off_xsum = take(type == TLB_GGML_Q4_K ? (size_t)2 * m * (k / 32) * 2 : 0);
     s.off_sa = take(type == TLB_GGML_Q6_K ? (size_t)(k / 256) * kMaxCols * 32 : type == TLB_GGML_Q4_0 ? (size_t)(k / 32) * kMaxCols * 4 : 0);
+    s.off_minv = take(type == TLB_GGML_Q4_K ? (size_t)(k / 256) * 4 * 4 : 0);
     s.off_red = take((size_t)2 * nw * kRedCols * 16 * 4);
     s.off_misc = take((size_t)m * (k / 128) * 4 + sizeof(MvShared));
     s.off_bars = take(0);
@@ -285,7 +298,7 @@ tlb_status launch_qmatvec(const MatvecJob &job)
             return fail(TLB_ERR_SHAPE, "K = %lld with %d rows needs more shared memory than one SM has (max K %zu)",
                         (long long)job.k, job.m, qmatvec_max_k(job.m));
     }
-    int nst = (int)((budget - sp.fixed) / (p.stage_bytes + 16));
+    int nst = (int)((budget - sp.fixed - 16) / (p.stage_bytes + 16));
     if (nst > 64) nst = 64;
     // A multiple of the consumer-warp count (itself a multiple of kProducerLanes): a stage is then
     // always consumed by the same warp and armed by the same producer lane, so a parity wait can
@@ -294,10 +307,15 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.n_stages = nst;
     const size_t ring = (size_t)nst * p.stage_bytes;
     p.off_xq = (int)ring + sp.off_xq; p.off_alam = (int)ring + sp.off_alam; p.off_xsum = (int)ring + sp.off_xsum;
-    p.off_sa = (int)ring + sp.off_sa; p.off_red = (int)ring + sp.off_red; p.off_misc = (int)ring + sp.off_misc;
+    p.off_sa = (int)ring + sp.off_sa; p.off_minv = (int)ring + sp.off_minv; p.off_red = (int)ring + sp.off_red;
+    p.off_misc = (int)ring + sp.off_misc;
     p.off_bars = (int)ring + sp.off_bars;
     p.col_stride = sp.col_stride;
-    const size_t smem = ring + sp.fixed + (size_t)nst * 16;
+    const size_t smem = ring + sp.fixed + (size_t)nst * 16 + 16;   // ring barriers + the image-copy barrier
+    if ((size_t)(sp.off_red - sp.off_xq) > c->act_bytes)
+        return fail(TLB_ERR_SHAPE, "activation image of %d bytes exceeds the %zu-byte scratch", sp.off_red - sp.off_xq, c->act_bytes);
+    p.act_img = c->act_img;
+    p.grid_sync = c->grid_sync;
     p.prologue = job.prologue;
     p.x = job.x; p.x2 = job.x2; p.x3 = job.x3; p.norm_w = job.norm_w; p.eps = job.eps; p.x_out = job.x_out;
     p.emb_table = job.emb_table; p.token = job.token;

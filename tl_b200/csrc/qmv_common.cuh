@@ -172,9 +172,11 @@ struct MvParams {
     long long zero_n[3];
     int *err;
     int use_pdl;
-    long long *trace;       // optional: [grid][8] SM clock stamps of thread 0 of every CTA (timing studies)
-    // shared-memory offsets (bytes from the start of dynamic shared memory)
-    int off_xq, off_alam, off_xsum, off_sa, off_red, off_bars, off_misc;
+    long long *trace;       // optional: [grid][10] SM clock stamps of thread 0 of every CTA (timing studies)
+    uint8_t *act_img;       // global scratch: image of the shared tables [off_xq, off_red), built once per launch
+    int *grid_sync;         // [2] arrival / departure counters of the grid-wide meeting point (zero between launches)
+    // shared-memory offsets (bytes from the start of dynamic shared memory); [off_xq, off_red) is one contiguous image
+    int off_xq, off_alam, off_xsum, off_sa, off_minv, off_red, off_bars, off_misc;
     int col_stride;         // bytes between int8 activation columns (K + 64)
 };
 

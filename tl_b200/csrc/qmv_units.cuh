@@ -18,6 +18,7 @@ struct LaneCtx {
     uint32_t xsum_b;   // Q4_K: f16 sub-block sums, column (hi / lo) read by this lane
     uint32_t sa_b;     // Q6_K: f16 level sums of column r (clamped)
     uint32_t sa_c0, sa_c1;  // Q4_0: int32 level sums of columns 2c and 2c+1 (clamped)
+    uint32_t minv_b;   // Q4_K: inverse power-of-two scale of the sub-block sums of activation row c (clamped)
 };
 
 #define NIB 0x0F0F0F0Fu
@@ -72,8 +73,10 @@ __device__ __forceinline__ void unit_q4k(uint32_t up, int u, const LaneCtx &L, f
     master[1] = fmaf(dA.x * al1, (float)acc[1], master[1]);
     master[2] = fmaf(dB.x * al0, (float)acc[2], master[2]);
     master[3] = fmaf(dB.x * al1, (float)acc[3], master[3]);
-    mm[0] = fmaf(dA.y, accm[0], mm[0]); mm[1] = fmaf(dA.y, accm[1], mm[1]);
-    mm[2] = fmaf(dB.y, accm[2], mm[2]); mm[3] = fmaf(dB.y, accm[3], mm[3]);
+    const float minv = __uint_as_float(lds32(L.minv_b + u * 16));   // undoes the power-of-two scale of the sums
+    const float mA = dA.y * minv, mB = dB.y * minv;
+    mm[0] = fmaf(mA, accm[0], mm[0]); mm[1] = fmaf(mA, accm[1], mm[1]);
+    mm[2] = fmaf(mB, accm[2], mm[2]); mm[3] = fmaf(mB, accm[3], mm[3]);
 }
 
 // ---- Q6_K: w = d * sc_j * (q - 32), sc_j int8 per 16 weights (quantized.rs:268-329) -------------

@@ -31,6 +31,11 @@ struct Context {
     void *flush_buf = nullptr;
     size_t flush_bytes = 0;
     int *err_flag = nullptr;  // device word set by kernels whose bounded waits ran out
+    // scratch of the streaming matvec: global image of its activation tables, built once per launch,
+    // and the two counters of its grid-wide meeting point (all launches are ordered on `stream`)
+    uint8_t *act_img = nullptr;
+    size_t act_bytes = 0;
+    int *grid_sync = nullptr;
     bool capturing = false;
     uint64_t capture_launches = 0;
 };
