@@ -110,6 +110,16 @@ tlb_status tlb_apply_rope(tlb_tensor **out, const tlb_tensor *x, const tlb_tenso
  * (crates/tl_cuda/src/cuda_kernels/autograd.cu:1119-1132). Result: [1] f32 holding the index. */
 typedef enum { TLB_TIE_LAST = 0, TLB_TIE_FIRST = 1 } tlb_tie_rule;
 tlb_status tlb_argmax(tlb_tensor **out, const tlb_tensor *x, tlb_tie_rule tie);           /* device_ffi.rs:1138 (dim ignored, scans all) */
+/* No counterpart in the reference.  tlb_argmax for callers that must not allocate device memory (a
+ * sampling loop on a thread that may not take the allocator's locks or fail for lack of memory, a
+ * process whose memory was handed out completely at start-up): the index is written, as f32, into
+ * element 0 of `out`, an f32 tensor the caller already owns, and the kernel's partial results live in a
+ * fixed 16 KB array inside the library, so nothing is allocated or freed.  Limits: x holds at most
+ * 4,194,304 elements (TLB_ERR_ARG beyond that; tlb_argmax has no limit); tlb_init must have run
+ * (TLB_ERR_DEVICE otherwise).  The first call on a device looks up the array's address and should
+ * be made outside any stream capture.  All calls share the array: they are ordered on the library's
+ * stream, and nothing in the array needs clearing between calls. */
+tlb_status tlb_argmax_into(tlb_tensor *out, const tlb_tensor *x, tlb_tie_rule tie);
 /* temp <= 0: greedy.  temp > 0: the reference CUDA path ignores temp/top_p and returns the argmax
  * (crates/tl_cuda/src/ffi_ops.rs:880-884); this entry point does the same. */
 tlb_status tlb_sample(tlb_tensor **out, const tlb_tensor *logits, float temp, float top_p, tlb_tie_rule tie); /* device_ffi.rs:1158 */

@@ -119,6 +119,10 @@ class Tensor:
     def rope_new_sin(dim, seq_len, base, mode=ROPE_CPU): return Tensor._wrap(lib().tlb_rope_new_sin, dim, seq_len, float(base), mode)
     def apply_rope(self, cos, sin, mode=ROPE_CPU): return Tensor._wrap(lib().tlb_apply_rope, self.h, cos.h, sin.h, mode)
     def argmax(self, tie=TIE_LAST): return Tensor._wrap(lib().tlb_argmax, self.h, tie)
+    def argmax_into(self, out, tie=TIE_LAST):
+        """Allocation-free argmax: writes the index (as f32) into element 0 of the existing tensor `out`."""
+        check(lib().tlb_argmax_into(out.h, self.h, tie))
+        return out
     def sample(self, temp, top_p, tie=TIE_LAST): return Tensor._wrap(lib().tlb_sample, self.h, float(temp), float(top_p), tie)
     def repetition_penalty(self, tokens, p): return Tensor._wrap(lib().tlb_repetition_penalty, self.h, tokens.h, float(p))
     def sdpa(self, k, v, mask=None, mask_mode=0):
