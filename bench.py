@@ -33,6 +33,8 @@ WORKLOADS = {
     # name: (config, linear type, head type, kv_f16, context, description)
     "c2": ("LLAMA3_8B", 12, 14, True, 2048, "Llama-3-8B-shaped decode, Q4_K + Q6_K head, f16 KV, ctx 2048, batch 1"),
     "c0": ("TINYLLAMA", 2, 2, False, 128, "TinyLlama-1.1B-shaped decode, Q4_0, f32 KV, ctx 128, batch 1"),
+    # the c2 shapes with 4 layers instead of 32: about 1.3 GB on the device, for profiler captures
+    "c2-4layer": ("LLAMA3_8B:4", 12, 14, True, 2048, "Llama-3-8B-shaped decode cut to 4 layers, Q4_K + Q6_K head, f16 KV, ctx 2048, batch 1"),
     "small": (None, 12, 14, True, 64, "2-layer d512 test model, Q4_K + Q6_K head, f16 KV, ctx 64, batch 1"),
 }
 SMALL_CFG = dict(n_layers=2, d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=1000,
@@ -42,7 +44,13 @@ SMALL_CFG = dict(n_layers=2, d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, 
 def workload_cfg(name):
     from tl_b200 import synth
     cfg_name, lt, ht, kv16, ctx, desc = WORKLOADS[name]
-    cfg = SMALL_CFG if cfg_name is None else getattr(synth, cfg_name)
+    if cfg_name is None:
+        cfg = SMALL_CFG
+    elif ":" in cfg_name:
+        base, layers = cfg_name.split(":")
+        cfg = dict(getattr(synth, base), n_layers=int(layers))
+    else:
+        cfg = getattr(synth, cfg_name)
     return cfg, lt, ht, kv16, ctx, desc
 
 
