@@ -47,7 +47,9 @@ template <> struct KvTraits<float> {
 };
 
 struct AttnParams {
-    const float *qkv;
+    const float *qkv;        // K-slices of the projection output, added in index order when read
+    int qkv_slices;
+    long long qkv_stride;
     void *kcache, *vcache;
     int H, KVH, D, max_seq;
     const int *pos, *rope_pos;
@@ -60,6 +62,13 @@ struct AttnParams {
     int use_pdl;
     int row_stride;   // shared-memory row stride in bytes (16-byte chunks, count = 4 mod 8: conflict-free)
 };
+
+__device__ __forceinline__ float ld_qkv(const AttnParams &p, size_t i)
+{
+    float a = __ldcg(p.qkv + i);
+    for (int s = 1; s < p.qkv_slices; s++) a += __ldcg(p.qkv + (size_t)s * p.qkv_stride + i);
+    return a;
+}
 
 template <typename T, int REP>
 __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const AttnParams p)
@@ -108,24 +117,23 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
     const float *cs = p.cos_t + (size_t)rp * D, *sn = p.sin_t + (size_t)rp * D;
     for (int i = tid; i < REP * (D / 2); i += kAttnThreads) {
         int h = i / (D / 2), j = (i - h * (D / 2)) * 2;
-        const float *qv = p.qkv + (size_t)(kvh * REP + h) * D;
-        float x0 = qv[j], x1 = qv[j + 1], c = cs[j], s = sn[j];
+        const size_t qi = (size_t)(kvh * REP + h) * D + j;
+        float x0 = ld_qkv(p, qi), x1 = ld_qkv(p, qi + 1), c = cs[j], s = sn[j];
         qs[h * D + j] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
         qs[h * D + j + 1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
     }
     // the CTA whose range holds row `pos` appends the new token's K (roped) and V
     if (pos >= t0 && pos < t1) {
-        const float *kn = p.qkv + (size_t)p.H * D + (size_t)kvh * D;
-        const float *vn = p.qkv + (size_t)(p.H + p.KVH) * D + (size_t)kvh * D;
+        const size_t kn = (size_t)p.H * D + (size_t)kvh * D, vn = (size_t)(p.H + p.KVH) * D + (size_t)kvh * D;
         T *kc = reinterpret_cast<T *>(p.kcache) + ((size_t)kvh * p.max_seq + pos) * D;
         T *vc = reinterpret_cast<T *>(p.vcache) + ((size_t)kvh * p.max_seq + pos) * D;
         T *krow = reinterpret_cast<T *>(Ks + (size_t)(pos - t0) * RS), *vrow = reinterpret_cast<T *>(Vs + (size_t)(pos - t0) * RS);
         for (int i = tid; i < D / 2; i += kAttnThreads) {
             int j = 2 * i;
-            float x0 = kn[j], x1 = kn[j + 1], c = cs[j], s = sn[j];
+            float x0 = ld_qkv(p, kn + j), x1 = ld_qkv(p, kn + j + 1), c = cs[j], s = sn[j];
             T k0 = KvTraits<T>::store(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
             T k1 = KvTraits<T>::store(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
-            T v0 = KvTraits<T>::store(vn[j]), v1 = KvTraits<T>::store(vn[j + 1]);
+            T v0 = KvTraits<T>::store(ld_qkv(p, vn + j)), v1 = KvTraits<T>::store(ld_qkv(p, vn + j + 1));
             krow[j] = k0; krow[j + 1] = k1; vrow[j] = v0; vrow[j + 1] = v1;
             kc[j] = k0; kc[j + 1] = k1; vc[j] = v0; vc[j + 1] = v1;
         }
@@ -288,7 +296,7 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     if (j.H % j.KVH) return fail(TLB_ERR_SHAPE, "query heads must be a multiple of KV heads");
     int rep = j.H / j.KVH;
     AttnParams p;
-    p.qkv = j.qkv; p.kcache = j.kcache; p.vcache = j.vcache;
+    p.qkv = j.qkv.p; p.qkv_slices = j.qkv.slices < 1 ? 1 : j.qkv.slices; p.qkv_stride = j.qkv.stride; p.kcache = j.kcache; p.vcache = j.vcache;
     p.H = j.H; p.KVH = j.KVH; p.D = j.D; p.max_seq = j.max_seq;
     p.pos = j.pos; p.rope_pos = j.rope_pos; p.cos_t = j.cos_t; p.sin_t = j.sin_t; p.scale = j.scale;
     p.partial = j.partial; p.counters = j.counters; p.max_splits = j.splits; p.out = j.out;

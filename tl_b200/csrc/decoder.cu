@@ -9,10 +9,11 @@
 //   K4  residual add + RMSNorm*w (prologue)  ->  gate|up matvec
 //   K5  SiLU(gate)*up (prologue)             ->  down matvec
 //   ... output_norm (prologue) -> lm_head matvec, argmax + position advance.
-// Matvec outputs accumulate with atomicAdd into buffers that an earlier kernel of the chain has
-// cleared; the residual stream ping-pongs between two buffers so no kernel updates memory that
-// another CTA of the same launch reads.  All kernels are launched with programmatic dependent
-// launch, so a kernel's weight prefetch overlaps its predecessor's tail.
+// A matvec leaves its output as a few K-slices (one array per slice, each element written exactly
+// once, nothing accumulated or cleared); the kernel that consumes it adds the slices as it loads.
+// The residual stream ping-pongs between two buffers so no kernel updates memory that another CTA
+// of the same launch reads.  All kernels are launched with programmatic dependent launch, so a
+// kernel's weight prefetch overlaps its predecessor's tail.
 #include "tlb_internal.h"
 
 #include <cstdlib>
@@ -40,6 +41,8 @@ struct tlb_decoder {
     float *amax_v = nullptr;
     long long *amax_i = nullptr;
     int *h_state = nullptr;      // pinned host staging [4]
+    float *logits_sl = nullptr;  // K-slices of the head matvec; `logits` holds their sum after the argmax kernel
+    int s_qkv = 1, s_o = 1, s_gu = 1, s_down = 1, s_head = 1;   // K-slices of each matvec of the chain
     int max_splits = 1;
     cudaGraphExec_t graph = nullptr;
     uint64_t graph_kernels = 0;
@@ -53,8 +56,9 @@ namespace {
 constexpr int kArgmaxBlocks = 64;
 
 // argmax over the logits + advance of the decode state, in one launch.  Tie rule as tlb_argmax.
-__global__ void argmax_advance_kernel(const float *__restrict__ x, int n, int tie_first, float *pv, long long *pi,
-                                      int *counter, int *state, int *tokens_out, int tokens_cap, int use_pdl)
+__global__ void argmax_advance_kernel(const float *__restrict__ xs, int slices, long long stride, float *__restrict__ x_sum, int n,
+                                      int tie_first, float *pv, long long *pi, int *counter, int *state, int *tokens_out,
+                                      int tokens_cap, int use_pdl)
 {
     if (use_pdl) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -72,7 +76,9 @@ __global__ void argmax_advance_kernel(const float *__restrict__ x, int n, int ti
         return tie_first ? i < ci : i > ci;
     };
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        float v = x[i];
+        float v = __ldcg(xs + i);
+        for (int s = 1; s < slices; s++) v += __ldcg(xs + (size_t)s * stride + i);   // the head's K-slices, index order
+        x_sum[i] = v;
         if (better(v, i, bv, bi)) { bv = v; bi = i; }
     }
     for (int o = 16; o; o >>= 1) {
@@ -138,12 +144,20 @@ tlb_status get_f(tlb_map *m, const std::string &name, tlb_tensor **t, int64_t nu
     return TLB_OK;
 }
 
-void set_w(MatvecJob &j, int i, const tlb_qtensor *q, float *out)
+void set_w(MatvecJob &j, int i, const tlb_qtensor *q, float *out, int64_t out_stride)
 {
     j.w[i] = q->dev();
     j.n_tiles[i] = q->n_tiles;
     j.n_rows[i] = q->n;
     j.out[i] = out;
+    j.out_stride[i] = out_stride;
+}
+
+SlicedVec sliced(const float *p, int slices, int64_t stride)
+{
+    SlicedVec v;
+    v.p = p; v.slices = slices; v.stride = stride;
+    return v;
 }
 
 // the kernel chain of one decode step (launched eagerly or into a capturing stream)
@@ -152,27 +166,28 @@ tlb_status enqueue_step(tlb_decoder *d)
     const tlb_decoder_cfg &c = d->cfg;
     const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
     const int L = c.n_layers;
+    const int64_t nqkv = qd + 2 * kvd;
     for (int l = 0; l < L; l++) {
         const LayerW &w = d->layers[l];
         {   // K1
             MatvecJob j;
             j.n_w = 3;
-            set_w(j, 0, w.q, d->qkv);
-            set_w(j, 1, w.k, d->qkv + qd);
-            set_w(j, 2, w.v, d->qkv + qd + kvd);
+            set_w(j, 0, w.q, d->qkv, nqkv);
+            set_w(j, 1, w.k, d->qkv + qd, nqkv);
+            set_w(j, 2, w.v, d->qkv + qd + kvd, nqkv);
+            j.slices = d->s_qkv;
             j.type = w.q->type; j.k = dm; j.m = 1;
             j.prologue = PRO_ADD_NORM;
             j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
-            if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; j.x = nullptr; j.x2 = nullptr; }
-            else { j.x = d->xa; j.x2 = d->down_out; j.x3 = d->down_out + dm; }
+            if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; }
+            else { j.x = sliced(d->xa, 1, 0); j.x2 = sliced(d->down_out, d->s_down, dm); }
             j.x_out = d->xb;
-            j.zero_ptr[0] = d->o_out; j.zero_n[0] = 2 * dm;
             j.pdl = d->pdl;
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K2
             DecodeAttnJob a;
-            a.qkv = d->qkv;
+            a.qkv = sliced(d->qkv, d->s_qkv, nqkv);
             a.kcache = (char *)d->kcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
             a.vcache = (char *)d->vcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
             a.kv_f16 = c.kv_f16; a.H = c.n_heads; a.KVH = c.n_kv_heads; a.D = c.head_dim; a.max_seq = c.max_seq;
@@ -183,35 +198,34 @@ tlb_status enqueue_step(tlb_decoder *d)
         {   // K3
             MatvecJob j;
             j.n_w = 1;
-            set_w(j, 0, w.o, d->o_out);
-            j.out_alt[0] = d->o_out + dm;
+            set_w(j, 0, w.o, d->o_out, dm);
+            j.slices = d->s_o;
             j.type = w.o->type; j.k = qd; j.m = 1;
-            j.prologue = PRO_PLAIN; j.x = d->attn;
-            j.zero_ptr[0] = d->gu; j.zero_n[0] = 2 * (int64_t)F;
+            j.prologue = PRO_PLAIN; j.x = sliced(d->attn, 1, 0);
             j.pdl = d->pdl;
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K4
             MatvecJob j;
             j.n_w = 2;
-            set_w(j, 0, w.gate, d->gu);
-            set_w(j, 1, w.up, d->gu + F);
+            set_w(j, 0, w.gate, d->gu, 2 * (int64_t)F);
+            set_w(j, 1, w.up, d->gu + F, 2 * (int64_t)F);
+            j.slices = d->s_gu;
             j.type = w.gate->type; j.k = dm; j.m = 1;
-            j.prologue = PRO_ADD_NORM; j.x = d->xb; j.x2 = d->o_out; j.x3 = d->o_out + dm; j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
+            j.prologue = PRO_ADD_NORM; j.x = sliced(d->xb, 1, 0); j.x2 = sliced(d->o_out, d->s_o, dm);
+            j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
             j.x_out = d->xa;
-            j.zero_ptr[0] = d->down_out; j.zero_n[0] = 2 * dm;
             j.pdl = d->pdl;
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K5
             MatvecJob j;
             j.n_w = 1;
-            set_w(j, 0, w.down, d->down_out);
-            j.out_alt[0] = d->down_out + dm;
+            set_w(j, 0, w.down, d->down_out, dm);
+            j.slices = d->s_down;
             j.type = w.down->type; j.k = F; j.m = 1;
-            j.prologue = PRO_SILU_MUL; j.x = d->gu; j.x2 = d->gu + F;
-            j.zero_ptr[0] = d->qkv; j.zero_n[0] = qd + 2 * kvd;
-            if (l == L - 1) { j.zero_ptr[1] = d->logits; j.zero_n[1] = c.vocab; }
+            j.prologue = PRO_SILU_MUL;
+            j.x = sliced(d->gu, d->s_gu, 2 * (int64_t)F); j.x2 = sliced(d->gu + F, d->s_gu, 2 * (int64_t)F);
             j.pdl = d->pdl;
             TLB_TRY(launch_qmatvec(j));
         }
@@ -219,9 +233,11 @@ tlb_status enqueue_step(tlb_decoder *d)
     {   // output_norm + head
         MatvecJob j;
         j.n_w = 1;
-        set_w(j, 0, d->head, d->logits);
+        set_w(j, 0, d->head, d->logits_sl, c.vocab);
+        j.slices = d->s_head;
         j.type = d->head->type; j.k = dm; j.m = 1;
-        j.prologue = PRO_ADD_NORM; j.x = d->xa; j.x2 = d->down_out; j.x3 = d->down_out + dm; j.norm_w = d->out_norm->f32(); j.eps = c.eps;
+        j.prologue = PRO_ADD_NORM; j.x = sliced(d->xa, 1, 0); j.x2 = sliced(d->down_out, d->s_down, dm);
+        j.norm_w = d->out_norm->f32(); j.eps = c.eps;
         j.x_out = d->xb;
         j.pdl = d->pdl;
         TLB_TRY(launch_qmatvec(j));
@@ -238,8 +254,9 @@ tlb_status enqueue_step(tlb_decoder *d)
             cfg.attrs = at;
             cfg.numAttrs = 1;
         }
-        TLB_CUDA(cudaLaunchKernelEx(&cfg, argmax_advance_kernel, (const float *)d->logits, (int)c.vocab, (int)(c.tie_rule == TLB_TIE_FIRST),
-                                    d->amax_v, d->amax_i, d->counters + c.n_kv_heads, d->state, d->tokens_out, d->tokens_cap, (int)d->pdl));
+        TLB_CUDA(cudaLaunchKernelEx(&cfg, argmax_advance_kernel, (const float *)d->logits_sl, d->s_head, (long long)c.vocab, d->logits,
+                                    (int)c.vocab, (int)(c.tie_rule == TLB_TIE_FIRST), d->amax_v, d->amax_i, d->counters + c.n_kv_heads,
+                                    d->state, d->tokens_out, d->tokens_cap, (int)d->pdl));
         count_launch();
     }
     return TLB_OK;
@@ -333,9 +350,28 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
         tlb_decoder_destroy(d);
         return fail(TLB_ERR_SHAPE, "inner dimensions up to %zu fit the single-pass matvec", kmax);
     }
+    {
+        const LayerW &w0 = d->layers[0];
+        d->s_qkv = qmatvec_plan_slices(w0.q->type, dm, 1, w0.q->n_tiles + w0.k->n_tiles + w0.v->n_tiles, kMaxSlices);
+        d->s_o = qmatvec_plan_slices(w0.o->type, qd, 1, w0.o->n_tiles, kMaxSlices);
+        d->s_gu = qmatvec_plan_slices(w0.gate->type, dm, 1, w0.gate->n_tiles + w0.up->n_tiles, kMaxSlices);
+        d->s_down = qmatvec_plan_slices(w0.down->type, F, 1, w0.down->n_tiles, kMaxSlices);
+        d->s_head = qmatvec_plan_slices(d->head->type, dm, 1, d->head->n_tiles, kMaxSlices);
+        for (const LayerW &w : d->layers)
+            if (w.q->type != w0.q->type || w.o->type != w0.o->type || w.gate->type != w0.gate->type || w.down->type != w0.down->type) {
+                tlb_decoder_destroy(d);
+                return fail(TLB_ERR_TYPE, "all layers must use the same GGML type per projection");
+            }
+        if (dm % 4 || F % 4 || (qd + 2 * kvd) % 4) {
+            tlb_decoder_destroy(d);
+            return fail(TLB_ERR_SHAPE, "model widths must be multiples of 4");
+        }
+    }
     TRY_D(dalloc(d, &d->xa, dm)); TRY_D(dalloc(d, &d->xb, dm));
-    TRY_D(dalloc(d, &d->qkv, qd + 2 * kvd)); TRY_D(dalloc(d, &d->attn, qd)); TRY_D(dalloc(d, &d->o_out, 2 * dm));   // two accumulation slots
-    TRY_D(dalloc(d, &d->gu, 2 * F)); TRY_D(dalloc(d, &d->down_out, 2 * dm)); TRY_D(dalloc(d, &d->logits, c.vocab));
+    TRY_D(dalloc(d, &d->qkv, (size_t)d->s_qkv * (qd + 2 * kvd))); TRY_D(dalloc(d, &d->attn, qd));
+    TRY_D(dalloc(d, &d->o_out, (size_t)d->s_o * dm)); TRY_D(dalloc(d, &d->gu, (size_t)d->s_gu * 2 * F));
+    TRY_D(dalloc(d, &d->down_out, (size_t)d->s_down * dm));
+    TRY_D(dalloc(d, &d->logits_sl, (size_t)d->s_head * c.vocab)); TRY_D(dalloc(d, &d->logits, c.vocab));
     d->kv_layer_elems = (size_t)kvd * c.max_seq;
     size_t kv_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
     TRY_D(dalloc(d, (char **)&d->kcache, kv_bytes)); TRY_D(dalloc(d, (char **)&d->vcache, kv_bytes));
@@ -469,17 +505,14 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
     int64_t out_n = w == "qkv" ? qd + 2 * kvd : (w == "o" || w == "down") ? dm : w == "gate_up" ? 2 * F : w == "head" ? c.vocab : -1;
     if (out_n < 0) return fail(TLB_ERR_ARG, "unknown kernel '%s' (qkv, o, gate_up, down, head)", which);
     int64_t kk = (w == "o") ? qd : (w == "down") ? F : dm;
-    float *xin = nullptr, *outb[2] = {nullptr, nullptr};
+    float *xin = nullptr, *outb = nullptr;
     TLB_CUDA(cudaMalloc(&xin, (size_t)std::max<int64_t>(kk, 2 * F) * 4));
-    TLB_CUDA(cudaMalloc(&outb[0], (size_t)out_n * 8));   // room for the second accumulation slot
-    TLB_CUDA(cudaMalloc(&outb[1], (size_t)out_n * 8));
+    TLB_CUDA(cudaMalloc(&outb, (size_t)out_n * kMaxSlices * 4));
     {
         std::vector<float> hx((size_t)std::max<int64_t>(kk, 2 * F));
         uint32_t s = 12345u;
         for (float &v : hx) { s = s * 1664525u + 1013904223u; v = ((s >> 8) / 8388608.0f) - 1.0f; }
         cudaMemcpy(xin, hx.data(), hx.size() * 4, cudaMemcpyHostToDevice);
-        cudaMemset(outb[0], 0, (size_t)out_n * 8);
-        cudaMemset(outb[1], 0, (size_t)out_n * 8);
     }
     long long *trace = nullptr;   // TLB_TRACE=1: per-CTA clock stamps of the last timed launch, printed to stderr
     if (getenv("TLB_TRACE")) { cudaMalloc(&trace, 512 * 10 * sizeof(long long)); cudaMemset(trace, 0, 512 * 10 * sizeof(long long)); }
@@ -492,23 +525,21 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         if (it == 0) cudaEventRecord(e0, ctx()->stream);
         const LayerW &lw = d->layers[(it + 3) % copies];
         MatvecJob j;
-        float *o = outb[(it + 3) & 1];
-        j.m = 1; j.prologue = PRO_PLAIN; j.x = xin;
+        float *o = outb;
+        j.m = 1; j.prologue = PRO_PLAIN; j.x = sliced(xin, 1, 0);
         if (w == "qkv") {
-            j.n_w = 3; set_w(j, 0, lw.q, o); set_w(j, 1, lw.k, o + qd); set_w(j, 2, lw.v, o + qd + kvd);
-            j.type = lw.q->type; j.k = dm; bytes = lw.q->nbytes() + lw.k->nbytes() + lw.v->nbytes();
+            j.n_w = 3; set_w(j, 0, lw.q, o, out_n); set_w(j, 1, lw.k, o + qd, out_n); set_w(j, 2, lw.v, o + qd + kvd, out_n);
+            j.slices = d->s_qkv; j.type = lw.q->type; j.k = dm; bytes = lw.q->nbytes() + lw.k->nbytes() + lw.v->nbytes();
         } else if (w == "o") {
-            j.n_w = 1; set_w(j, 0, lw.o, o); j.type = lw.o->type; j.k = qd; bytes = lw.o->nbytes();
+            j.n_w = 1; set_w(j, 0, lw.o, o, out_n); j.slices = d->s_o; j.type = lw.o->type; j.k = qd; bytes = lw.o->nbytes();
         } else if (w == "gate_up") {
-            j.n_w = 2; set_w(j, 0, lw.gate, o); set_w(j, 1, lw.up, o + F); j.type = lw.gate->type; j.k = dm;
+            j.n_w = 2; set_w(j, 0, lw.gate, o, out_n); set_w(j, 1, lw.up, o + F, out_n); j.slices = d->s_gu; j.type = lw.gate->type; j.k = dm;
             bytes = lw.gate->nbytes() + lw.up->nbytes();
         } else if (w == "down") {
-            j.n_w = 1; set_w(j, 0, lw.down, o); j.type = lw.down->type; j.k = F; bytes = lw.down->nbytes();
+            j.n_w = 1; set_w(j, 0, lw.down, o, out_n); j.slices = d->s_down; j.type = lw.down->type; j.k = F; bytes = lw.down->nbytes();
         } else {
-            j.n_w = 1; set_w(j, 0, d->head, o); j.type = d->head->type; j.k = dm; bytes = d->head->nbytes();
+            j.n_w = 1; set_w(j, 0, d->head, o, out_n); j.slices = d->s_head; j.type = d->head->type; j.k = dm; bytes = d->head->nbytes();
         }
-        j.zero_ptr[0] = outb[(it + 4) & 1]; j.zero_n[0] = 2 * out_n;
-        if (w == "o" || w == "down") j.out_alt[0] = o + out_n;   // as in the decode chain
         if (trace && it == iters - 1) j.trace = trace;
         st = launch_qmatvec(j);
     }
@@ -531,7 +562,7 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         }
         cudaFree(trace);
     }
-    cudaFree(xin); cudaFree(outb[0]); cudaFree(outb[1]);
+    cudaFree(xin); cudaFree(outb);
     if (st != TLB_OK) return st;
     *us_per_launch = ms * 1000.f / (float)std::max(1, iters);
     if (bytes_per_launch) *bytes_per_launch = bytes + (uint64_t)kk * 4 + (uint64_t)out_n * 4;

@@ -4,234 +4,299 @@
 // re-read once per activation row) and the dequantise-then-naive-matmul route the reference takes
 // for Q4_0 / Q8_0 (crates/tl_runtime/src/system.rs:236-264).
 //
-// Shape of the kernel (persistent CTAs, one or two per SM):
-//   * the weight bytes of all tensors of a launch form ONE linear stream of units (16 rows x 256
-//     weights, quant.cu); CTA b takes the contiguous range [U*b/G, U*(b+1)/G): equal bytes per CTA
-//     whatever the row count;
-//   * a producer warp moves units global -> shared with 1-D bulk async copies (cp.async.bulk +
-//     mbarrier complete_tx) through a ring of stages; it does not depend on the activations, so
-//     the HBM stream starts while the prologue is still running (and, under programmatic dependent
-//     launch, while the previous kernel is still finishing);
-//   * the prologue quantises the activation to int8 levels in shared memory (qmv_common.cuh) and
-//     can fuse what precedes the matvec in the decode chain: residual add + RMSNorm * weight,
-//     SiLU(gate) * up, or the embedding lookup;
-//   * consumer warps take one unit at a time: conflict-free 128-bit shared loads, one AND per four
-//     weights, integer tensor-core MMAs (qmv_units.cuh);
-//   * per output tile the warps' fragments are summed in fixed order in shared memory and added to
-//     the output with one atomicAdd per row.  A tile is touched by at most two CTAs per
-//     accumulation slot and a + b == b + a, so results do not depend on scheduling.
+// Shape of the kernel (one persistent CTA of 16 warps per SM):
+//   * work is cut into ITEMS: one tile of 16 output rows x one K-slice of `upi` consecutive units
+//     (a unit = 16 rows x 256 weights, quant.cu).  Items are numbered slice-major and dealt out in
+//     contiguous ranges, first to CTAs and then to the warps of a CTA, so every warp gets the same
+//     number of bytes to within one item;
+//   * a warp owns its items from the first byte to the stored result.  It streams their units
+//     global -> shared itself with 1-D bulk async copies (cp.async.bulk + mbarrier complete_tx) through
+//     a ring of stages that belongs to it alone: after consuming a stage the warp refills it with the
+//     unit `spw` positions ahead.  No other warp is ever waited for - there is no block-wide barrier,
+//     no shared-memory reduction and no atomic in the streaming phase;
+//   * the copies do not depend on the activations, so the first `spw` are issued before the kernel
+//     waits for its predecessor (programmatic dependent launch): the HBM stream starts while the
+//     previous kernel is still finishing;
+//   * the prologue quantises the activation to int8 levels in shared memory (qmv_prologue.cuh) -
+//     only the 256-blocks the CTA's K-slices cover - and can fuse what precedes the matvec in the
+//     decode chain: residual add + RMSNorm * weight, SiLU(gate) * up, or the embedding lookup;
+//   * per unit: conflict-free 128-bit shared loads, one AND per four weights, integer tensor-core
+//     MMAs (qmv_units.cuh);
+//   * the result of item (slice, tile) is written to out[slice][m][row].  Every element of every
+//     slice is written by exactly one warp, so nothing has to be cleared beforehand and the sums do
+//     not depend on scheduling; whoever reads the output adds the slices in index order.
 #include "qmv_prologue.cuh"
 #include "qmv_units.cuh"
 
-#include <map>
+#include <algorithm>
 
 namespace tlb {
 
-constexpr int kRedCols = 12;   // 8 MMA columns + 4 min-term columns (one per activation row)
-constexpr int kProducerLanes = 8;
+constexpr int kWarps = 16;
+constexpr int kThreads = kWarps * 32;
 
-__device__ __forceinline__ const uint8_t *unit_src(const MvParams &p, int u)
+struct ItemRef {
+    const uint8_t *src;   // first unit of the item
+    int wi, row0, slice;  // tensor, first output row within the tensor, K-slice
+};
+
+// Position in the slice-major item order, advanced without divisions.
+struct ItemCursor { int slice, tile; };
+
+__device__ __forceinline__ ItemCursor cursor_at(const MvParams &p, int item)
 {
-    int tile = u / p.upt, uk = u - tile * p.upt;
-    int wi = (tile >= p.tiles_end[0]) + (tile >= p.tiles_end[1]);
-    int t0 = wi == 0 ? 0 : p.tiles_end[wi - 1];
-    return p.w[wi] + ((size_t)(tile - t0) * p.upt + uk) * p.unit_bytes;
+    ItemCursor c;
+    c.slice = item / p.tiles;
+    c.tile = item - c.slice * p.tiles;
+    return c;
+}
+__device__ __forceinline__ void cursor_next(const MvParams &p, ItemCursor &c)
+{
+    if (++c.tile == p.tiles) { c.tile = 0; c.slice++; }
+}
+__device__ __forceinline__ ItemRef item_ref(const MvParams &p, const ItemCursor &c)
+{
+    ItemRef r;
+    r.slice = c.slice;
+    r.wi = (c.tile >= p.tiles_end[0]) + (c.tile >= p.tiles_end[1]);
+    const int t0 = r.wi == 0 ? 0 : p.tiles_end[r.wi - 1];
+    r.row0 = (c.tile - t0) * 16;
+    r.src = p.w[r.wi] + ((size_t)(c.tile - t0) * p.upt + (size_t)c.slice * p.upi) * p.unit_bytes;
+    return r;
 }
 
-template <int FMT, int NW>
-__global__ void __launch_bounds__(NW * 32 + 32, (NW <= 8) ? 2 : 1) qmatvec_kernel(const __grid_constant__ MvParams p)
+template <int FMT>
+__global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_constant__ MvParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int NT = NW * 32;   // consumer threads
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nst = p.n_stages;
-    float *red = reinterpret_cast<float *>(smem + p.off_red);            // [2][NW][kRedCols][16]
-    MvShared *sh = reinterpret_cast<MvShared *>(smem + p.off_misc + p.m * (p.k / 128) * 4);
-    const uint32_t full0 = smem_u32(smem + p.off_bars), empty0 = full0 + nst * 8;
-    const uint32_t ring_u32 = smem_u32(smem);
-
+    MvShared *sh = reinterpret_cast<MvShared *>(smem + p.off_misc);
+    const int spw = p.spw;
+    const uint32_t ring = smem_u32(smem) + (uint32_t)(warp * spw) * p.stage_bytes;   // this warp's stages
+    const uint32_t bars = smem_u32(smem + p.off_bars) + (uint32_t)(warp * spw) * 8;  // and their barriers
     const int G = gridDim.x, b = blockIdx.x;
-    const int u0 = (int)((long long)p.total_units * b / G), u1 = (int)((long long)p.total_units * (b + 1) / G);
-    const int n_units = u1 - u0;
 #define STAMP(i) do { if (p.trace && tid == 0) p.trace[(size_t)b * 10 + (i)] = clock64(); } while (0)
     STAMP(0);
     if (p.trace && tid == 0) p.trace[(size_t)b * 10 + 8] = (long long)global_ns();
 
-    const uint32_t act_bar = full0 + 2 * nst * 8;   // completion of the activation-image copy
-    if (tid < nst) {   // one thread per stage: the inits run in parallel
-        mbar_init(full0 + tid * 8, 1);
-        mbar_init(empty0 + tid * 8, 1);
-        if (tid == 0) { sh->abort_flag = 0; mbar_init(act_bar, 1); }
+    // items of this CTA, then of this warp
+    const int ci0 = (int)((long long)p.n_items * b / G), ci1 = (int)((long long)p.n_items * (b + 1) / G);
+    const int nci = ci1 - ci0;
+    const int i0 = ci0 + nci * warp / kWarps, i1 = ci0 + nci * (warp + 1) / kWarps;
+    const int n_units = (i1 - i0) * p.upi;
+    // activation blocks the CTA's items cover
+    const int s_first = nci > 0 ? ci0 / p.tiles : 0, s_last = nci > 0 ? (ci1 - 1) / p.tiles : 0;
+    const int blk0 = s_first * p.upi, nb = nci > 0 ? (s_last + 1) * p.upi - blk0 : 0;
+
+    if (lane == 0) {
+        for (int s = 0; s < spw; s++) mbar_init(bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    __syncthreads();
-    volatile int *abortp = &sh->abort_flag;
+    if (tid == 0) sh->abort_flag = 0;
+    __syncwarp();
+
+    // Copy cursor (meaningful in lane 0 only): the next unit to request and how many remain.
+    ItemCursor pf_cur = cursor_at(p, i0);
+    int pf_left_in_item = 0, pf_remaining = n_units, issued = 0;
+    const uint8_t *pf_src = nullptr;
+    auto issue_copy = [&](int stage) {
+        if (pf_left_in_item == 0) { pf_src = item_ref(p, pf_cur).src; cursor_next(p, pf_cur); pf_left_in_item = p.upi; }
+        mbar_expect_tx(bars + stage * 8, p.unit_bytes);
+        bulk_g2s(ring + stage * p.stage_bytes, pf_src, p.unit_bytes, bars + stage * 8);
+        pf_src += p.unit_bytes;
+        pf_left_in_item--; pf_remaining--; issued++;
+    };
+    if (lane == 0)
+        for (int s = 0; s < spw && pf_remaining > 0; s++) issue_copy(s);
     STAMP(1);
 
-    if (warp == NW) {
-        // ---- producer: lane i < kProducerLanes streams the units i, i + kProducerLanes, ... of this
-        // CTA's range.  The stage count is a multiple of kProducerLanes, so every stage is always
-        // armed by the same lane: a lane reuses a stage only after ITS previous use of that stage
-        // was released, which keeps the parity waits unambiguous.  Weights do not depend on the
-        // previous kernel, so there is no dependency wait here.
-        if (lane >= kProducerLanes) return;
-        int i = lane, slot = lane, use = 0;
-        for (; i < n_units; i += kProducerLanes) {
-            if (use > 0 && !mbar_wait(empty0 + slot * 8, (use - 1) & 1, abortp, p.err, 1)) break;
-            mbar_expect_tx(full0 + slot * 8, p.unit_bytes);
-            bulk_g2s(ring_u32 + slot * p.stage_bytes, unit_src(p, u0 + i), p.unit_bytes, full0 + slot * 8);
-            slot += kProducerLanes;
-            if (slot >= nst) { slot -= nst; use++; }
-        }
-        if (*abortp) {
-            // give the copies this lane still has in flight a bounded time to land before the CTA exits
-            for (int k = i - kProducerLanes, n = 0; k >= 0 && n < nst; k -= kProducerLanes, n++)
-                mbar_wait_drain(full0 + (k % nst) * 8, (k / nst) & 1);
-        }
-        return;
-    }
-
-    // ---- consumers
     if (p.use_pdl) {
         pdl_wait();                // everything below may read what the previous kernel wrote
         // Released only after our own wait: a dependent's early part then runs with every kernel
         // before our predecessor complete, so it may read state those kernels wrote.
         pdl_launch_dependents();
     }
-    for (int z = 0; z < 3; z++)
-        if (p.zero_ptr[z])
-            for (long long idx = (long long)b * NT + tid; idx < p.zero_n[z]; idx += (long long)G * NT) p.zero_ptr[z][idx] = 0.f;
+    __syncthreads();               // abort_flag initialised; also keeps the CTA together for the prologue
     STAMP(2);
-    const bool act_ok = build_activation<FMT>(p, sh, smem, tid, NT, act_bar, abortp);
+    build_activation<FMT>(p, sh, smem, tid, kThreads, blk0, nb);
     STAMP(3);
-    if (!act_ok) return;   // a bounded wait gave up: the error word is set, outputs stay untouched
+    volatile int *abortp = &sh->abort_flag;
+
     const int ncols = p.m * p.nl;
     LaneCtx L;
     L.lane = lane; L.r = lane >> 2; L.c = lane & 3;
     {
         const int r = L.r, c = L.c;
         const int colr = r < ncols ? r : 0, c0 = 2 * c < ncols ? 2 * c : 0, c1 = 2 * c + 1 < ncols ? 2 * c + 1 : 0;
+        L.bvalid = r < ncols;
         L.xq_b = smem_u32(smem + p.off_xq) + colr * p.col_stride;
         L.alam_b = smem_u32(smem + p.off_alam) + 2 * c * 4;
-        L.xsum_b = smem_u32(smem + p.off_xsum) + ((r < 2 * p.m) ? r : (r & 1)) * (p.k / 32) * 2;
+        L.xsum_b = smem_u32(smem + p.off_xsum) + ((r < 2 * p.m) ? r : (r & 1)) * (p.nb_max * 8) * 2;
         L.sa_b = smem_u32(smem + p.off_sa) + colr * 32;
         L.sa_c0 = smem_u32(smem + p.off_sa) + c0 * 4;
         L.sa_c1 = smem_u32(smem + p.off_sa) + c1 * 4;
         L.minv_b = smem_u32(smem + p.off_minv) + (c < p.m ? c : 0) * 4;
     }
 
-    // Ring cursor of this warp, advanced incrementally (no integer division in the unit loop):
-    // the unit with CTA-relative index cur_rel sits in stage `slot`, in use number `phase` (mod 2).
-    int u = u0, par = 0, tile = u0 / p.upt;
-    int cur_rel = 0, slot = 0, phase = 0;
-    while (u < u1) {
-        const int tile_first = tile * p.upt;
-        const int seg_end = min(u1, tile_first + p.upt);
+    int stage = 0, phase = 0, consumed = 0;
+    bool ok = true;
+    ItemCursor cur = cursor_at(p, i0);
+    for (int item = i0; item < i1 && ok; item++, cursor_next(p, cur)) {
+        const ItemRef ir = item_ref(p, cur);
+        const int lb0 = ir.slice * p.upi - blk0;
         float master[4] = {0.f, 0.f, 0.f, 0.f}, mm[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int uu = u + warp; uu < seg_end; uu += NW) {
-            slot += (uu - u0) - cur_rel;
-            cur_rel = uu - u0;
-            while (slot >= nst) { slot -= nst; phase ^= 1; }
-            if (!mbar_wait(full0 + slot * 8, phase, abortp, p.err, 2)) break;
-            if (cur_rel == 0) STAMP(4);
-            process_unit<FMT>(ring_u32 + slot * p.stage_bytes, uu - tile_first, L, master, mm);
-            if (cur_rel == 0) STAMP(5);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + slot * 8);
+        for (int uo = 0; uo < p.upi; uo++) {
+            bool got = mbar_try_wait(bars + stage * 8, phase);
+            if (!got) got = mbar_wait_slow(bars + stage * 8, phase, abortp, p.err, 2);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }   // warp-uniform: all lanes leave together
+            if (consumed == 0 && warp == 0) STAMP(4);
+            process_unit<FMT>(ring + stage * p.stage_bytes, lb0 + uo, L, master, mm);
+            if (consumed == 0 && warp == 0) STAMP(5);
+            consumed++;
+            __syncwarp();          // every lane has read the stage: it may be overwritten
+            if (lane == 0 && pf_remaining > 0) issue_copy(stage);
+            if (++stage == spw) { stage = 0; phase ^= 1; }
         }
-        float *rp = red + ((size_t)par * NW + warp) * (kRedCols * 16);
-        rp[(2 * L.c) * 16 + L.r] = master[0];
-        rp[(2 * L.c + 1) * 16 + L.r] = master[1];
-        rp[(2 * L.c) * 16 + L.r + 8] = master[2];
-        rp[(2 * L.c + 1) * 16 + L.r + 8] = master[3];
-        if (FMT == TLB_GGML_Q4_K) {   // min term of activation row c: columns (hi, lo) summed
-            rp[(8 + L.c) * 16 + L.r] = -(mm[0] + mm[1]);
-            rp[(8 + L.c) * 16 + L.r + 8] = -(mm[2] + mm[3]);
-        }
-        named_bar(1, NT);
-        {
-            // Every warp reduces its share of the 16 rows: lane = (source warp, column slot); the
-            // butterfly adds in a fixed order, so the sum does not depend on timing.
-            constexpr int RPW = 16 / NW, CSL = 32 / NW;   // rows per warp, column slots per pass
-            const int w_src = lane % NW, cs = lane / NW;
-            const int wi = (tile >= p.tiles_end[0]) + (tile >= p.tiles_end[1]);
-            const int t0 = wi == 0 ? 0 : p.tiles_end[wi - 1];
-            float *dst = (p.out_alt[wi] && (b & 1)) ? p.out_alt[wi] : p.out[wi];
-            const float *rsrc = red + ((size_t)par * NW + w_src) * (kRedCols * 16);
-#pragma unroll
-            for (int rr = 0; rr < RPW; rr++) {
-                const int row = warp * RPW + rr;
-                for (int mi = 0; mi < p.m; mi++) {
-                    float v = 0.f;
-#pragma unroll
-                    for (int c0 = 0; c0 < 4; c0 += CSL) {
-                        const int slot = c0 + cs;
-                        if (slot < p.nl) v += rsrc[(mi * p.nl + slot) * 16 + row];
-                        else if (FMT == TLB_GGML_Q4_K && slot == p.nl) v += rsrc[(8 + mi) * 16 + row];
-                    }
-                    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                    const int grow = (tile - t0) * 16 + row;
-                    if (lane == 0 && grow < p.n_rows[wi]) atomicAdd(dst + (size_t)mi * p.n_rows[wi] + grow, v);
-                }
+        if (!ok) break;
+        // Fold the level columns of each activation row (they sit in the four lanes of a quad) and
+        // store the 16 rows of the item.  The Q4_K min term of activation row mi lives in lane c == mi.
+        float *dst = p.out[ir.wi] + (size_t)ir.slice * p.out_stride[ir.wi];
+        const int nrows = p.n_rows[ir.wi];
+        for (int mi = 0; mi < p.m; mi++) {
+            const int lo = mi * p.nl, hi = lo + p.nl, cA = 2 * L.c, cB = 2 * L.c + 1;
+            const bool inA = cA >= lo && cA < hi, inB = cB >= lo && cB < hi;
+            float v0 = (inA ? master[0] : 0.f) + (inB ? master[1] : 0.f);   // row r
+            float v1 = (inA ? master[2] : 0.f) + (inB ? master[3] : 0.f);   // row r + 8
+            v0 += __shfl_xor_sync(0xffffffffu, v0, 1); v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+            if (L.c == mi) {
+                if (FMT == TLB_GGML_Q4_K) { v0 -= mm[0] + mm[1]; v1 -= mm[2] + mm[3]; }
+                const int g0 = ir.row0 + L.r, g1 = g0 + 8;
+                if (g0 < nrows) dst[(size_t)mi * nrows + g0] = v0;
+                if (g1 < nrows) dst[(size_t)mi * nrows + g1] = v1;
             }
         }
-        u = seg_end;
-        tile++;
-        par ^= 1;
+    }
+    if (!ok && lane == 0) {
+        // a bounded wait gave up (error word set): give the copies still in flight a bounded time to land
+        for (int q = consumed; q < issued; q++) mbar_wait_drain(bars + (q % spw) * 8, (q / spw) & 1);
     }
     STAMP(6);
     if (p.trace && tid == 0) p.trace[(size_t)b * 10 + 9] = (long long)global_ns();
 #undef STAMP
 }
 
+// out[i] = slice 0 + slice 1 + ... (index order)
+__global__ void sum_slices_kernel(const float *__restrict__ src, int slices, long long stride, float *__restrict__ out, long long n)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float a = src[i];
+        for (int s = 1; s < slices; s++) a += src[(size_t)s * stride + i];
+        out[i] = a;
+    }
+}
+
+tlb_status launch_sum_slices(const float *src, int slices, int64_t stride, float *out, int64_t n)
+{
+    if (n == 0) return TLB_OK;
+    int blocks = (int)std::min<int64_t>(1184, (n + 255) / 256);
+    sum_slices_kernel<<<blocks, 256, 0, ctx()->stream>>>(src, slices, (long long)stride, out, (long long)n);
+    TLB_CUDA(cudaGetLastError());
+    count_launch();
+    return TLB_OK;
+}
+
 // ---------------------------------------------------------------- host side
 
-struct SmemPlan { int off_xq, off_alam, off_xsum, off_sa, off_minv, off_red, off_bars, off_misc, col_stride; size_t fixed; };
+struct SmemPlan { int off_xq, off_alam, off_xsum, off_sa, off_minv, off_misc, col_stride; size_t fixed; };
 
-static SmemPlan plan_smem(int type, int m, int nl, int64_t k, int nw)
+static SmemPlan plan_smem(int type, int m, int nl, int nb)
 {
-    // everything except the ring; offsets are relative to the end of the ring
+    // everything except the ring and its barriers; offsets are relative to the end of the ring
     SmemPlan s;
     size_t o = 0;
     auto take = [&](size_t bytes) { size_t at = o; o += (bytes + 127) / 128 * 128; return (int)at; };
-    s.col_stride = (int)k + 64;   // == 64 mod 128: two columns never share a bank group
+    s.col_stride = nb * 256 + 64;   // == 64 mod 128: two neighbouring columns never share a bank group
     s.off_xq = take((size_t)m * nl * s.col_stride);
-    s.off_alam = take((size_t)(k / 256) * kMaxCols * 4);
-    s.off_xsum = take(type == TLB_GGML_Q4_K ? (size_t)2 * m * (k / 32) * 2 : 0);
-    s.off_sa = take(type == TLB_GGML_Q6_K ? (size_t)(k / 256) * kMaxCols * 32 : type == TLB_GGML_Q4_0 ? (size_t)(k / 32) * kMaxCols * 4 : 0);
-    s.off_minv = take(type == TLB_GGML_Q4_K ? (size_t)(k / 256) * 4 * 4 : 0);
-    s.off_red = take((size_t)2 * nw * kRedCols * 16 * 4);
-    s.off_misc = take((size_t)m * (k / 128) * 4 + sizeof(MvShared));
-    s.off_bars = take(0);
+    s.off_alam = take((size_t)nb * kMaxCols * 4);
+    s.off_xsum = take(type == TLB_GGML_Q4_K ? (size_t)2 * m * (nb * 8) * 2 : 0);
+    s.off_sa = take(type == TLB_GGML_Q6_K ? (size_t)nb * kMaxCols * 32 : type == TLB_GGML_Q4_0 ? (size_t)(nb * 8) * kMaxCols * 4 : 0);
+    s.off_minv = take(type == TLB_GGML_Q4_K ? (size_t)nb * 4 * 4 : 0);
+    s.off_misc = take(sizeof(MvShared));
     s.fixed = o;
     return s;
 }
 
+static int stage_bytes_of(const QFormat *f) { return (f->unit_bytes + 127) / 128 * 128; }
+
 size_t qmatvec_max_k(int m)
 {
+    // the unsplit worst case: all blocks of K resident with two ring stages per warp
     Context *c = ctx();
     size_t budget = c ? c->smem_optin : 232448;
     int nl = m <= 2 ? 3 : 2;
     size_t k = 256;
-    while (plan_smem(TLB_GGML_Q6_K, m, nl, (int64_t)(k + 256), 16).fixed + 16 * (4352 + 128 + 16) <= budget) k += 256;
+    while (plan_smem(TLB_GGML_Q6_K, m, nl, (int)(k / 256) + 1).fixed + (size_t)kWarps * 2 * (4352 + 8) + 128 <= budget) k += 256;
     return k;
 }
 
-template <int FMT, int NW>
+// Blocks of 256 a CTA may have to quantise when `n_items` slice-major items are dealt to `grid` CTAs.
+static int blocks_per_cta(int64_t n_items, int grid, int64_t tiles, int upi, int upt)
+{
+    const int64_t ipc = (n_items + grid - 1) / grid;
+    const int64_t touched = (ipc + tiles - 2) / tiles + 1;   // a range of ipc items straddles at most this many slices
+    return (int)std::min<int64_t>(upt, touched * upi);
+}
+
+// Relative cost (warp instructions on the critical path) of cutting K into upt / upi slices.
+static double slice_cost(int type, int m, int64_t tiles, int upt, int upi, int sm_count)
+{
+    const int kb = upt / upi;
+    const int64_t n_items = tiles * kb;
+    const int grid = (int)std::min<int64_t>(sm_count, n_items);
+    const int64_t ipc = (n_items + grid - 1) / grid, ipw = (ipc + kWarps - 1) / kWarps;
+    const int nb = blocks_per_cta(n_items, grid, tiles, upi, upt);
+    const double unit = type == TLB_GGML_Q6_K ? 300.0 : type == TLB_GGML_Q8_0 ? 150.0 : 210.0;
+    const double stream = (double)ipw * (upi * unit + 60.0);
+    const double quant = 300.0 * ((m * nb + 7) / 8);
+    const double reader = 30.0 * kb;
+    return stream + quant + reader;
+}
+
+int qmatvec_plan_slices(int type, int64_t k, int m, int64_t tiles, int max_slices)
+{
+    Context *c = ctx();
+    const int sm = c ? c->sm_count : 148;
+    const int upt = (int)(k / 256);
+    if (upt < 1 || tiles < 1) return 1;
+    max_slices = std::max(1, std::min(max_slices, kMaxSlices));
+    int best = 1;
+    double best_cost = 0.0;
+    for (int upi = upt; upi >= 1; upi--) {
+        if (upt % upi) continue;
+        const int kb = upt / upi;
+        if (kb > max_slices) break;
+        const double cost = slice_cost(type, m, tiles, upt, upi, sm);
+        if (kb == 1 || cost < best_cost) { best = kb; best_cost = cost; }
+    }
+    return best;
+}
+
+template <int FMT>
 static tlb_status launch_fmt(const MvParams &p, int grid, size_t smem, bool pdl)
 {
     static size_t set_bytes = 0;
     if (smem > set_bytes) {
-        TLB_CUDA(cudaFuncSetAttribute(qmatvec_kernel<FMT, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TLB_CUDA(cudaFuncSetAttribute(qmatvec_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set_bytes = smem;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(NW * 32 + 32);
+    cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx()->stream;
-    cudaLaunchAttribute at[2];
+    cudaLaunchAttribute at[1];
     int na = 0;
     if (pdl) {
         at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -240,11 +305,11 @@ static tlb_status launch_fmt(const MvParams &p, int grid, size_t smem, bool pdl)
     }
     static const bool debug = getenv("TLB_DEBUG") != nullptr;
     if (debug)
-        fprintf(stderr, "[tlb] qmatvec fmt %d warps %d grid %d stages %d smem %zu k %d units %d\n", FMT, NW, grid,
-                p.n_stages, smem, p.k, p.total_units);
+        fprintf(stderr, "[tlb] qmatvec fmt %d grid %d stages/warp %d smem %zu k %d tiles %d upi %d slices %d blocks/cta %d\n", FMT, grid,
+                p.spw, smem, p.k, p.tiles, p.upi, p.kb, p.nb_max);
     cfg.attrs = at;
     cfg.numAttrs = na;
-    TLB_CUDA(cudaLaunchKernelEx(&cfg, qmatvec_kernel<FMT, NW>, p));
+    TLB_CUDA(cudaLaunchKernelEx(&cfg, qmatvec_kernel<FMT>, p));
     count_launch();
     return TLB_OK;
 }
@@ -267,7 +332,7 @@ tlb_status launch_qmatvec(const MatvecJob &job)
             tiles += job.n_tiles[i];
             p.w[i] = job.w[i];
             p.out[i] = job.out[i];
-            p.out_alt[i] = job.out_alt[i];
+            p.out_stride[i] = job.out_stride[i];
             p.n_rows[i] = (int)job.n_rows[i];
         }
         p.tiles_end[i] = (int)tiles;
@@ -278,62 +343,52 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.k = (int)job.k;
     p.m = job.m;
     p.nl = job.m <= 2 ? 3 : 2;
-    if (tiles * p.upt > INT32_MAX) return fail(TLB_ERR_SHAPE, "too many units for one launch");
-    p.total_units = (int)(tiles * p.upt);
+    p.kb = job.slices;
+    if (p.kb < 1 || p.kb > kMaxSlices || p.upt % p.kb) return fail(TLB_ERR_ARG, "%d slices do not divide the %d units of K", p.kb, p.upt);
+    p.upi = p.upt / p.kb;
+    if (tiles * p.kb > INT32_MAX / 64) return fail(TLB_ERR_SHAPE, "too many items for one launch");
+    p.tiles = (int)tiles;
+    p.n_items = (int)(tiles * p.kb);
     p.unit_bytes = f->unit_bytes;
-    p.stage_bytes = (f->unit_bytes + 127) / 128 * 128;
-    // Two CTAs of 8 consumer warps per SM when shared memory allows a useful ring for each, else one of 16.
-    const bool two_slots = job.out_alt[0] != nullptr;
-    // CTAs: every CTA must own at least one tile's worth of units per accumulation slot, so that a
-    // tile gets at most two contributions per slot (deterministic sums).
-    const int64_t max_ctas = two_slots ? 2 * tiles : tiles;
-    int nw = 8;
-    size_t budget = (c->smem_optin + 1024) / 2 - 1024;   // per-CTA share when two CTAs are resident
-    SmemPlan sp = plan_smem(job.type, job.m, p.nl, job.k, nw);
-    if (job.force_warps == 16 || max_ctas < 2 * (int64_t)c->sm_count || sp.fixed + 12 * (size_t)(p.stage_bytes + 16) > budget) {
-        nw = 16;
-        budget = c->smem_optin;
-        sp = plan_smem(job.type, job.m, p.nl, job.k, nw);
-        if (sp.fixed + 16 * (size_t)(p.stage_bytes + 16) > budget)
-            return fail(TLB_ERR_SHAPE, "K = %lld with %d rows needs more shared memory than one SM has (max K %zu)",
-                        (long long)job.k, job.m, qmatvec_max_k(job.m));
-    }
-    int nst = (int)((budget - sp.fixed - 16) / (p.stage_bytes + 16));
-    if (nst > 64) nst = 64;
-    // A multiple of the consumer-warp count (itself a multiple of kProducerLanes): a stage is then
-    // always consumed by the same warp and armed by the same producer lane, so a parity wait can
-    // never be satisfied by a phase two uses back.
-    nst = nst / nw * nw;
-    p.n_stages = nst;
-    const size_t ring = (size_t)nst * p.stage_bytes;
+    p.stage_bytes = stage_bytes_of(f);
+    const int grid = (int)std::min<int64_t>(c->sm_count, p.n_items);
+    p.nb_max = blocks_per_cta(p.n_items, grid, tiles, p.upi, p.upt);
+    const SmemPlan sp = plan_smem(job.type, job.m, p.nl, p.nb_max);
+    const size_t budget = c->smem_optin;
+    const size_t per_stage = (size_t)kWarps * (p.stage_bytes + 8);
+    if (sp.fixed + 128 + 2 * per_stage > budget)
+        return fail(TLB_ERR_SHAPE, "K = %lld with %d rows needs more shared memory than one SM has (max K %zu)",
+                    (long long)job.k, job.m, qmatvec_max_k(job.m));
+    int spw = (int)((budget - sp.fixed - 128) / per_stage);
+    // no more stages than the longest warp has units, and no more than keeps ~1.5 us of HBM latency covered
+    const int64_t ipc = (p.n_items + grid - 1) / grid;
+    const int64_t upw = (ipc + kWarps - 1) / kWarps * p.upi;
+    spw = (int)std::min<int64_t>(std::min(spw, 8), std::max<int64_t>(2, upw));
+    p.spw = spw;
+    const size_t ring = (size_t)kWarps * spw * p.stage_bytes;
     p.off_xq = (int)ring + sp.off_xq; p.off_alam = (int)ring + sp.off_alam; p.off_xsum = (int)ring + sp.off_xsum;
-    p.off_sa = (int)ring + sp.off_sa; p.off_minv = (int)ring + sp.off_minv; p.off_red = (int)ring + sp.off_red;
-    p.off_misc = (int)ring + sp.off_misc;
-    p.off_bars = (int)ring + sp.off_bars;
+    p.off_sa = (int)ring + sp.off_sa; p.off_minv = (int)ring + sp.off_minv; p.off_misc = (int)ring + sp.off_misc;
+    p.off_bars = (int)(ring + sp.fixed);
     p.col_stride = sp.col_stride;
-    const size_t smem = ring + sp.fixed + (size_t)nst * 16 + 16;   // ring barriers + the image-copy barrier
-    if ((size_t)(sp.off_red - sp.off_xq) > c->act_bytes)
-        return fail(TLB_ERR_SHAPE, "activation image of %d bytes exceeds the %zu-byte scratch", sp.off_red - sp.off_xq, c->act_bytes);
-    p.act_img = c->act_img;
-    p.grid_sync = c->grid_sync;
+    const size_t smem = ring + sp.fixed + (size_t)kWarps * spw * 8;
     p.prologue = job.prologue;
-    p.x = job.x; p.x2 = job.x2; p.x3 = job.x3; p.norm_w = job.norm_w; p.eps = job.eps; p.x_out = job.x_out;
+    p.x = job.x; p.x2 = job.x2; p.norm_w = job.norm_w; p.eps = job.eps; p.x_out = job.x_out;
     p.emb_table = job.emb_table; p.token = job.token;
-    for (int z = 0; z < 3; z++) { p.zero_ptr[z] = job.zero_ptr[z]; p.zero_n[z] = job.zero_n[z]; }
+    if (p.x.slices < 1) p.x.slices = 1;
+    if (p.x2.slices < 1) p.x2.slices = 1;
+    if ((p.x.slices > 1 && p.x.stride % 4) || (p.x2.slices > 1 && p.x2.stride % 4))
+        return fail(TLB_ERR_ARG, "slice strides of the activation must be multiples of 4 floats");
     p.err = c->err_flag;
     p.use_pdl = job.pdl ? 1 : 0;
     p.trace = job.trace;
-    if (!p.x && !(p.prologue == PRO_ADD_NORM && p.token)) return fail(TLB_ERR_NULL, "null activation");
-    const int grid = (int)std::min<int64_t>((int64_t)c->sm_count * (nw == 8 ? 2 : 1), max_ctas);
-#define LAUNCH(FMTV)                                                                  \
-    return nw == 8 ? launch_fmt<FMTV, 8>(p, grid, smem, job.pdl) : launch_fmt<FMTV, 16>(p, grid, smem, job.pdl)
+    if (!p.x.p && !(p.prologue == PRO_ADD_NORM && p.token)) return fail(TLB_ERR_NULL, "null activation");
+    if (p.prologue == PRO_SILU_MUL && !p.x2.p) return fail(TLB_ERR_NULL, "null activation");
     switch (job.type) {
-    case TLB_GGML_Q4_K: LAUNCH(TLB_GGML_Q4_K);
-    case TLB_GGML_Q6_K: LAUNCH(TLB_GGML_Q6_K);
-    case TLB_GGML_Q8_0: LAUNCH(TLB_GGML_Q8_0);
-    default: LAUNCH(TLB_GGML_Q4_0);
+    case TLB_GGML_Q4_K: return launch_fmt<TLB_GGML_Q4_K>(p, grid, smem, job.pdl);
+    case TLB_GGML_Q6_K: return launch_fmt<TLB_GGML_Q6_K>(p, grid, smem, job.pdl);
+    case TLB_GGML_Q8_0: return launch_fmt<TLB_GGML_Q8_0>(p, grid, smem, job.pdl);
+    default: return launch_fmt<TLB_GGML_Q4_0>(p, grid, smem, job.pdl);
     }
-#undef LAUNCH
 }
 
 }  // namespace tlb
@@ -356,21 +411,32 @@ extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, 
     TLB_TRY(new_tensor(out, TLB_F32, oshape, x->rank));
     if (m * w->n == 0) return TLB_OK;
     tlb_status st = TLB_OK;
-    cudaError_t e = cudaMemsetAsync((*out)->data(), 0, (size_t)m * w->n * 4, ctx()->stream);
-    if (e != cudaSuccess) st = cuda_fail(e, "memset");
+    Storage *scratch = nullptr;   // the K-slices of one group of 4 rows, summed into the result afterwards
     for (int64_t m0 = 0; m0 < m && st == TLB_OK; m0 += 4) {   // the weight stream is repeated per group of 4 rows
         MatvecJob job;
         job.n_w = 1;
         job.w[0] = w->dev();
         job.n_tiles[0] = w->n_tiles;
         job.n_rows[0] = w->n;
-        job.out[0] = (*out)->f32() + m0 * w->n;
         job.type = w->type;
         job.k = k;
         job.m = (int)std::min<int64_t>(4, m - m0);
-        job.x = x->f32() + m0 * k;
+        job.slices = qmatvec_plan_slices(w->type, k, job.m, w->n_tiles, kMaxSlices);
+        float *dst = (*out)->f32() + m0 * w->n;
+        if (job.slices > 1) {
+            if (!scratch) scratch = storage_alloc((size_t)kMaxSlices * 4 * w->n * sizeof(float));
+            if (!scratch) { st = TLB_ERR_ALLOC; break; }
+            job.out[0] = (float *)scratch->ptr;
+            job.out_stride[0] = (int64_t)job.m * w->n;
+        } else {
+            job.out[0] = dst;
+        }
+        job.x.p = x->f32() + m0 * k;
         st = launch_qmatvec(job);
+        if (st == TLB_OK && job.slices > 1)
+            st = launch_sum_slices((const float *)scratch->ptr, job.slices, job.out_stride[0], dst, (int64_t)job.m * w->n);
     }
+    if (scratch) storage_release(scratch);   // stream-ordered: freed after the kernels above have run
     if (st != TLB_OK) { tlb_tensor_release(*out); *out = nullptr; }
     return st;
 }

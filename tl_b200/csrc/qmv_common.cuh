@@ -151,58 +151,73 @@ __device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1,
 
 struct MvParams {
     const uint8_t *w[3];
-    float *out[3];          // out[i] (+ out_alt[i] when split over two accumulation slots)
-    float *out_alt[3];
-    int tiles_end[3];       // cumulative tile counts
-    int n_rows[3];          // valid output rows per tensor
+    float *out[3];            // slice s of tensor i is stored at out[i] + s * out_stride[i], laid out [m][n_rows]
+    long long out_stride[3];
+    int tiles_end[3];         // cumulative tile counts
+    int n_rows[3];            // valid output rows per tensor
     int n_w;
-    int upt;                // units per tile = K / 256
+    int upt;                  // units per tile = K / 256
     int k;
-    int m;                  // activation rows, 1..4
-    int nl;                 // int8 levels per activation row (3 for m <= 2, else 2)
-    int total_units;
-    int unit_bytes, stage_bytes, n_stages;
+    int m;                    // activation rows, 1..4
+    int nl;                   // int8 levels per activation row (3 for m <= 2, else 2)
+    // Work decomposition.  An ITEM is one tile (16 rows) x one K-slice of `upi` consecutive units; item
+    // index = slice * tiles + tile (slice-major), so the contiguous item range of a CTA touches one or two
+    // slices and needs only those blocks of the activation.  One warp owns an item from the first byte to
+    // the stored result: out[slice][m][row] is WRITTEN, never added to, by exactly one warp.
+    int upi;                  // units per item (divides upt)
+    int kb;                   // K-slices = output slices = upt / upi
+    int tiles;                // tiles of the launch (all tensors)
+    int n_items;              // kb * tiles
+    int nb_max;               // 256-blocks of activation a CTA may need: the shared tables are sized for it
+    int unit_bytes, stage_bytes;
+    int spw;                  // ring stages private to each warp
     int prologue;
-    const float *x, *x2, *x3, *norm_w;
+    SlicedVec x;              // PLAIN: x [M,K]; ADD_NORM: residual; SILU_MUL: gate
+    SlicedVec x2;             // ADD_NORM: delta added to x (p == null: none); SILU_MUL: up
+    const float *norm_w;
     float eps;
-    float *x_out;
+    float *x_out;             // ADD_NORM: residual + delta written here by CTA 0 (may be null)
     const float *emb_table;
     const int *token;
-    float *zero_ptr[3];
-    long long zero_n[3];
     int *err;
     int use_pdl;
-    long long *trace;       // optional: [grid][10] SM clock stamps of thread 0 of every CTA (timing studies)
-    uint8_t *act_img;       // global scratch: image of the shared tables [off_xq, off_red), built once per launch
-    int *grid_sync;         // [2] arrival / departure counters of the grid-wide meeting point (zero between launches)
-    // shared-memory offsets (bytes from the start of dynamic shared memory); [off_xq, off_red) is one contiguous image
-    int off_xq, off_alam, off_xsum, off_sa, off_minv, off_red, off_bars, off_misc;
-    int col_stride;         // bytes between int8 activation columns (K + 64)
+    long long *trace;         // optional: [grid][10] stamps of thread 0 of every CTA (timing studies)
+    // shared-memory offsets (bytes from the start of dynamic shared memory)
+    int off_xq, off_alam, off_xsum, off_sa, off_minv, off_bars, off_misc;
+    int col_stride;           // bytes between int8 activation columns (nb_max * 256 + 64)
 };
 
 // Scratch of the prologue.
 struct MvShared {
     float red_sum[32];
     float red_max[32];
-    float inv_scale;             // 1 / (power-of-two scale of the f16 sub-block sums)
     int abort_flag;
 };
 
 __device__ __forceinline__ float silu_f(float g) { return g * (1.0f / (1.0f + expf(-g))); }
 
+// Elements 4*i4 .. 4*i4+3 of a sliced vector: slice 0 + slice 1 + ... in that fixed order.  The data was
+// written by an earlier kernel of the stream, hence the L2-coherent loads.
+__device__ __forceinline__ float4 ld_sliced4(const SlicedVec &v, size_t i4)
+{
+    float4 a = __ldcg(reinterpret_cast<const float4 *>(v.p) + i4);
+    for (int s = 1; s < v.slices; s++) {
+        const float4 d = __ldcg(reinterpret_cast<const float4 *>(v.p + (size_t)s * v.stride) + i4);
+        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
+    }
+    return a;
+}
+
 // Activation elements 4*k4 .. 4*k4+3 of row `mrow` as the matvec consumes them.  inv_rms == 0 selects
-// the statistics pass of PRO_ADD_NORM (returns the un-normalised residual sum).
-__device__ __forceinline__ float4 prologue_value(const MvParams &p, const float *xbase, int mrow, int k4, float inv_rms)
+// the statistics pass of PRO_ADD_NORM (returns the un-normalised residual sum).  `emb` replaces p.x
+// when the residual is an embedding row.
+__device__ __forceinline__ float4 prologue_value(const MvParams &p, const float *emb, int mrow, int k4, float inv_rms)
 {
     const size_t row4 = (size_t)mrow * (p.k / 4) + k4;
-    float4 v = __ldg(reinterpret_cast<const float4 *>(xbase) + row4);
+    float4 v = emb ? __ldg(reinterpret_cast<const float4 *>(emb) + row4) : ld_sliced4(p.x, row4);
     if (p.prologue == PRO_ADD_NORM) {
-        if (p.x2) {
-            float4 d = __ldg(reinterpret_cast<const float4 *>(p.x2) + row4);
-            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-        }
-        if (p.x3) {
-            float4 d = __ldg(reinterpret_cast<const float4 *>(p.x3) + row4);
+        if (p.x2.p) {
+            const float4 d = ld_sliced4(p.x2, row4);
             v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         }
         if (inv_rms != 0.f) {  // (x / rms) * weight (crates/tl_cpu/src/ffi.rs:2444-2486), the division as a multiply by 1/rms
@@ -211,7 +226,7 @@ __device__ __forceinline__ float4 prologue_value(const MvParams &p, const float 
             v.z = (v.z * inv_rms) * w.z; v.w = (v.w * inv_rms) * w.w;
         }
     } else if (p.prologue == PRO_SILU_MUL) {
-        float4 u = __ldg(reinterpret_cast<const float4 *>(p.x2) + row4);
+        const float4 u = ld_sliced4(p.x2, row4);
         v.x = silu_f(v.x) * u.x; v.y = silu_f(v.y) * u.y; v.z = silu_f(v.z) * u.z; v.w = silu_f(v.w) * u.w;
     }
     return v;

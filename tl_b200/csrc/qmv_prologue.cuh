@@ -1,21 +1,15 @@
-// Prologue of the streaming matvec: builds the int8 B operands of the MMAs.
+// Prologue of the streaming matvec: builds the int8 B operands of the MMAs in shared memory.
 //
 // int8 levels: per activation row m and per block of 256 k (one weight super-block) the values are
 // written as  x ~ alpha * (l0 + l1/254 + l2/254^2),  l_i in [-127, 127], alpha = max|x| / 127 over the
 // block; every level is the rounded residual of the previous ones, so three levels carry ~23 bits
 // and the integer MMAs downstream are exact.  Level l of row m is column m*nl + l, stored at
-//   xq[col][64*G + 16*c + 8*sub + 4*h + byte]   for k = 64*G + 32*sub + 16*h + 4*c + byte,
-// i.e. the two words a lane needs for one m16n8k32 MMA are adjacent.  alam[u][col] = alpha * 254^-l
-// (0 for unused columns).  Also written: per-32 sums of x as an (hi, lo) pair of f16 scaled by a
-// per-block power of two whose inverse goes to minv[u][m] (Q4_K mins), per-16 sums of the levels as
-// f16 (Q6_K offset term) or per-32 sums as int32 (Q4_0 offset term).
-//
-// Every CTA of the grid needs the whole activation, but quantising it costs far more than reading
-// it, so the work is done ONCE per launch: block (m, u) is quantised by one group of 64 threads of
-// CTA (m*nsb + u) % grid into a global scratch image of the shared-memory tables; the CTAs then
-// meet at a grid-wide arrival counter (bounded wait) and each pulls the finished image into its own
-// shared memory with one bulk async copy.  The grid is persistent and fully resident, so the
-// counter always completes.
+//   xq[col][256*lb + 64*G + 16*c + 8*sub + 4*h + byte]   for k = 256*blk + 64*G + 32*sub + 16*h + 4*c + byte,
+// i.e. the two words a lane needs for one m16n8k32 MMA are adjacent.  lb = blk - blk0 is the block
+// index local to the CTA: a CTA quantises only the blocks its K-slices cover.  alam[lb][col] =
+// alpha * 254^-l (0 for unused columns).  Also written: per-32 sums of x as an (hi, lo) pair of f16
+// scaled by a per-block power of two whose inverse goes to minv[lb][m] (Q4_K mins), per-16 sums of
+// the levels as f16 (Q6_K offset term) or per-32 sums as int32 (Q4_0 offset term).
 //
 // Rounding uses the 1.5 * 2^23 trick: t = x * inv + MAGIC rounds to the nearest integer in the
 // FMA pipe, the level is the low byte of t's bit pattern, and no conversion instruction is issued.
@@ -26,21 +20,14 @@ namespace tlb {
 
 #define MAGIC_RN 12582912.0f
 
-__device__ __forceinline__ int ld_acquire_gpu(const int *p)
-{
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// Quantises block (mrow, u) with the 64 threads whose index in the group is j; writes into `img`
-// (global image of the shared tables, offsets relative to off_xq).
+// Quantises block (mrow, blk) with a group of 64 threads (index j in the group) into the shared tables
+// at local block index lb.
 template <int FMT>
-__device__ __forceinline__ void quantise_block(const MvParams &p, const float *xbase, uint8_t *img, float *pair_max,
-                                               int mrow, int u, int j, int lane, float inv_rms, int pair_bar)
+__device__ __forceinline__ void quantise_block(const MvParams &p, const float *emb, uint8_t *smem, float *pair_max,
+                                               int mrow, int blk, int lb, int j, int lane, float inv_rms, int pair_bar)
 {
-    const int k4 = u * 64 + j;
-    const float4 v = prologue_value(p, xbase, mrow, k4, inv_rms);
+    const int k4 = blk * 64 + j;
+    const float4 v = prologue_value(p, emb, mrow, k4, inv_rms);
     float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) pair_max[j >> 5] = mx;
@@ -69,20 +56,21 @@ __device__ __forceinline__ void quantise_block(const MvParams &p, const float *x
             inv *= 254.f;
         }
     }
-    // k = 4*k4 + byte  ->  G = k4 >> 4, t = k4 & 15: sub = t >> 3, h = (t >> 2) & 1, c = t & 3
-    const int G = k4 >> 4, t = k4 & 15;
-    const int off = G * 64 + (t & 3) * 16 + (t >> 3) * 8 + ((t >> 2) & 1) * 4;
+    // k = 256*blk + 4*j + byte  ->  G = j >> 4, t = j & 15: sub = t >> 3, h = (t >> 2) & 1, c = t & 3
+    const int G = j >> 4, t = j & 15;
+    const int off = lb * 256 + G * 64 + (t & 3) * 16 + (t >> 3) * 8 + ((t >> 2) & 1) * 4;
 #pragma unroll
     for (int l = 0; l < 3; l++)
-        if (l < p.nl) *reinterpret_cast<uint32_t *>(img + (size_t)(mrow * p.nl + l) * p.col_stride + off) = words[l];
-    if (j < kMaxCols) {   // alam[u][0..7]: this row's levels; other rows' columns are written by their own groups
+        if (l < p.nl) *reinterpret_cast<uint32_t *>(smem + p.off_xq + (size_t)(mrow * p.nl + l) * p.col_stride + off) = words[l];
+    if (j < kMaxCols) {   // alam[lb][0..7]: this row's levels; other rows' columns are written by their own groups
         const int col = j, l = col - mrow * p.nl;
+        float *alam = reinterpret_cast<float *>(smem + p.off_alam);
         if (l >= 0 && l < p.nl) {
             float a = alpha;
             for (int i = 0; i < l; i++) a *= (1.f / 254.f);
-            reinterpret_cast<float *>(img + (p.off_alam - p.off_xq))[u * kMaxCols + col] = a;
+            alam[lb * kMaxCols + col] = a;
         } else if (col >= p.m * p.nl && mrow == 0) {
-            reinterpret_cast<float *>(img + (p.off_alam - p.off_xq))[u * kMaxCols + col] = 0.f;   // unused columns
+            alam[lb * kMaxCols + col] = 0.f;   // unused columns
         }
     }
     if (FMT == TLB_GGML_Q4_K) {   // sums of x over sub-blocks of 32 = 8 consecutive k4 = 8 consecutive lanes
@@ -97,28 +85,28 @@ __device__ __forceinline__ void quantise_block(const MvParams &p, const float *x
         t4 += __shfl_xor_sync(0xffffffffu, t4, 1);
         t4 += __shfl_xor_sync(0xffffffffu, t4, 2);
         t4 += __shfl_xor_sync(0xffffffffu, t4, 4);
-        __half *xsum = reinterpret_cast<__half *>(img + (p.off_xsum - p.off_xq));
+        __half *xsum = reinterpret_cast<__half *>(smem + p.off_xsum);
         if ((lane & 7) == 0) {
             const __half hi = __float2half_rn(t4);
             const __half lo = __float2half_rn(t4 - __half2float(hi));
-            xsum[(size_t)(2 * mrow) * (p.k / 32) + (k4 >> 3)] = hi;
-            xsum[(size_t)(2 * mrow + 1) * (p.k / 32) + (k4 >> 3)] = lo;
+            xsum[(size_t)(2 * mrow) * (p.nb_max * 8) + lb * 8 + (j >> 3)] = hi;
+            xsum[(size_t)(2 * mrow + 1) * (p.nb_max * 8) + lb * 8 + (j >> 3)] = lo;
         }
-        if (j == 0) reinterpret_cast<float *>(img + (p.off_minv - p.off_xq))[u * 4 + mrow] = 1.f / S;
+        if (j == 0) reinterpret_cast<float *>(smem + p.off_minv)[lb * 4 + mrow] = 1.f / S;
     }
-    if (FMT == TLB_GGML_Q6_K) {   // level sums over groups of 16 = 4 consecutive lanes, as f16 (|sum| <= 2032: exact); [u][col][16]
-        __half *sa = reinterpret_cast<__half *>(img + (p.off_sa - p.off_xq));
+    if (FMT == TLB_GGML_Q6_K) {   // level sums over groups of 16 = 4 consecutive lanes, as f16 (|sum| <= 2032: exact); [lb][col][16]
+        __half *sa = reinterpret_cast<__half *>(smem + p.off_sa);
 #pragma unroll
         for (int l = 0; l < 3; l++)
             if (l < p.nl) {
                 float s = lsum[l];
                 s += __shfl_xor_sync(0xffffffffu, s, 1);
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
-                if ((lane & 3) == 0) sa[((size_t)u * kMaxCols + mrow * p.nl + l) * 16 + ((k4 >> 2) & 15)] = __float2half_rn(s);
+                if ((lane & 3) == 0) sa[((size_t)lb * kMaxCols + mrow * p.nl + l) * 16 + (j >> 2)] = __float2half_rn(s);
             }
     }
-    if (FMT == TLB_GGML_Q4_0) {   // level sums over blocks of 32 = 8 consecutive lanes, int32; [k/32][8 cols]
-        int *sa = reinterpret_cast<int *>(img + (p.off_sa - p.off_xq));
+    if (FMT == TLB_GGML_Q4_0) {   // level sums over blocks of 32 = 8 consecutive lanes, int32; [lb*8 + j/8][8 cols]
+        int *sa = reinterpret_cast<int *>(smem + p.off_sa);
 #pragma unroll
         for (int l = 0; l < 3; l++)
             if (l < p.nl) {
@@ -126,75 +114,54 @@ __device__ __forceinline__ void quantise_block(const MvParams &p, const float *x
                 s += __shfl_xor_sync(0xffffffffu, s, 1);
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
                 s += __shfl_xor_sync(0xffffffffu, s, 4);
-                if ((lane & 7) == 0) sa[(size_t)(k4 >> 3) * kMaxCols + mrow * p.nl + l] = __float2int_rn(s);
+                if ((lane & 7) == 0) sa[(size_t)(lb * 8 + (j >> 3)) * kMaxCols + mrow * p.nl + l] = __float2int_rn(s);
             }
     }
     named_bar(pair_bar, 64);   // pair_max may be rewritten by this group's next block
 }
 
-// Returns false if a bounded wait gave up (the CTA then skips its units).
+// Fills the shared tables for activation blocks [blk0, blk0 + nb) of every row.  All `nthreads`
+// threads of the CTA call it; it ends with a CTA-wide barrier.
 template <int FMT>
-__device__ bool build_activation(const MvParams &p, MvShared *sh, uint8_t *smem, int tid, int nthreads, uint32_t act_bar,
-                                 volatile int *abort_flag)
+__device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem, int tid, int nthreads, int blk0, int nb)
 {
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
-    const int k4n = p.k / 4, nsb = p.k / 256;
-    const int G = gridDim.x, b = blockIdx.x;
-    const float *xbase = p.x;
-    if (p.prologue == PRO_ADD_NORM && p.token) xbase = p.emb_table + (size_t)__ldg(p.token) * p.k;
+    const int k4n = p.k / 4;
+    const float *emb = nullptr;
+    if (p.prologue == PRO_ADD_NORM && p.token) emb = p.emb_table + (size_t)__ldg(p.token) * p.k;
 
-    // RMSNorm statistic: every CTA sums the squares itself (cheap next to the quantisation)
+    // RMSNorm statistic over the whole row: every CTA sums the squares itself
     float inv_rms = 0.f;
     if (p.prologue == PRO_ADD_NORM) {
-        constexpr int kBatch = 4;   // loads issued in batches so that their latencies overlap
+        constexpr int kBatch = 2;   // loads issued in batches so that their latencies overlap
         float ssq = 0.f;
         for (int base = tid; base < k4n; base += nthreads * kBatch) {
             float4 vv[kBatch];
 #pragma unroll
             for (int j = 0; j < kBatch; j++)
-                if (base + j * nthreads < k4n) vv[j] = prologue_value(p, xbase, 0, base + j * nthreads, 0.f);
+                if (base + j * nthreads < k4n) vv[j] = prologue_value(p, emb, 0, base + j * nthreads, 0.f);
 #pragma unroll
             for (int j = 0; j < kBatch; j++)
                 if (base + j * nthreads < k4n) {
                     const float4 v = vv[j];
                     ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                    if (p.x_out && b == 0) reinterpret_cast<float4 *>(p.x_out)[base + j * nthreads] = v;
+                    if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out)[base + j * nthreads] = v;
                 }
         }
         for (int o = 16; o; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
         if (lane == 0) sh->red_sum[warp] = ssq;
-        named_bar(1, nthreads);
+        __syncthreads();
         ssq = 0.f;
         for (int w = 0; w < nwarps; w++) ssq += sh->red_sum[w];
         inv_rms = 1.f / sqrtf(ssq / (float)p.k + p.eps);
     }
-    // this CTA's blocks: groups of 64 threads, one block each
+    // groups of 64 threads, one block each
     const int ngroups = nthreads >> 6, grp = tid >> 6;
-    for (int item = b * ngroups + grp; item < p.m * nsb; item += G * ngroups)
-        quantise_block<FMT>(p, xbase, p.act_img, &sh->red_max[grp * 2], item / nsb, item % nsb, tid & 63, lane, inv_rms, 2 + grp);
-    // grid-wide arrival: everything every CTA wrote is visible before anyone copies the image
-    __threadfence();
-    named_bar(1, nthreads);
-    if (tid == 0) {
-        atomicAdd(p.grid_sync, 1);
-        unsigned long long t0 = 0;
-        for (int it = 0; ld_acquire_gpu(p.grid_sync) < G; it++) {
-            if ((it & 255) == 255) {
-                if (t0 == 0) t0 = global_ns();
-                if (global_ns() - t0 > 2000000000ull) { *abort_flag = 1; atomicExch(p.err, 3); break; }
-            }
-        }
-        if (!*abort_flag) {
-            asm volatile("fence.proxy.async;" ::: "memory");
-            mbar_expect_tx(act_bar, (uint32_t)(p.off_red - p.off_xq));
-            bulk_g2s(smem_u32(smem + p.off_xq), p.act_img, (uint32_t)(p.off_red - p.off_xq), act_bar);
-        }
-        // the last CTA to leave resets the counters for the next launch on this stream
-        if (atomicAdd(p.grid_sync + 1, 1) == G - 1) { p.grid_sync[0] = 0; p.grid_sync[1] = 0; __threadfence(); }
+    for (int item = grp; item < p.m * nb; item += ngroups) {
+        const int mrow = item / nb, lb = item - mrow * nb;
+        quantise_block<FMT>(p, emb, smem, &sh->red_max[grp * 2], mrow, blk0 + lb, lb, tid & 63, lane, inv_rms, 2 + grp);
     }
-    named_bar(1, nthreads);
-    if (*abort_flag) return false;
-    return mbar_wait(act_bar, 0, abort_flag, p.err, 4);
+    __syncthreads();
 }
 
 }  // namespace tlb

@@ -1,7 +1,7 @@
 // Per-unit consumers of the streaming matvec: one warp turns one unit (16 rows x 256 weights, layout
 // in qlayout.cuh) into 16 x 8 partial sums with integer tensor-core MMAs.
 //
-// Common frame.  Lane (r, c) = (lane >> 2, lane & 3) owns rows r and r+8; its C fragment holds
+// Common frame.  `u` is the unit's block index local to the CTA (row of the activation tables).  Lane (r, c) = (lane >> 2, lane & 3) owns rows r and r+8; its C fragment holds
 // columns 2c and 2c+1: acc[0], acc[1] for row r, acc[2], acc[3] for row r+8.  A column is one int8
 // level of one activation row (see build_activation).  Quants enter the MMA as raw integers:
 // nibbles are separated with one AND per four weights, nothing is converted to floating point
@@ -19,9 +19,14 @@ struct LaneCtx {
     uint32_t sa_b;     // Q6_K: f16 level sums of column r (clamped)
     uint32_t sa_c0, sa_c1;  // Q4_0: int32 level sums of columns 2c and 2c+1 (clamped)
     uint32_t minv_b;   // Q4_K: inverse power-of-two scale of the sub-block sums of activation row c (clamped)
+    bool bvalid;       // MMA column r carries a level: lanes of unused columns feed zeros and skip the shared loads
 };
 
+__device__ __forceinline__ uint4 ldb128(const LaneCtx &L, uint32_t a) { return L.bvalid ? lds128(a) : make_uint4(0u, 0u, 0u, 0u); }
+__device__ __forceinline__ uint2 ldb64(const LaneCtx &L, uint32_t a) { return L.bvalid ? lds64(a) : make_uint2(0u, 0u); }
+
 #define NIB 0x0F0F0F0Fu
+#define NIBH 0xF0F0F0F0u
 #define H2_1024 0x64006400u
 
 __device__ __forceinline__ int byte_u(uint32_t w, int i) { return (int)prmt(w, 0u, 0x4440u + i); }
@@ -52,8 +57,10 @@ __device__ __forceinline__ void unit_q4k(uint32_t up, int u, const LaneCtx &L, f
               lds32(L.xsum_b + (8 * u + 2 * c) * 2), 0u);
     uint4 xbs[4];
 #pragma unroll
-    for (int G = 0; G < 4; G++) xbs[G] = lds128(L.xq_b + (4 * u + G) * 64 + c * 16);
-    int acc[4] = {0, 0, 0, 0};
+    for (int G = 0; G < 4; G++) xbs[G] = ldb128(L, L.xq_b + (4 * u + G) * 64 + c * 16);
+    // The high nibbles enter their MMA in place (q << 4, still an exact u8): their sums are kept in a
+    // second accumulator and scaled by 1/16 once per unit, which saves the shift per four weights.
+    int acc[4] = {0, 0, 0, 0}, acch[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int G = 0; G < 4; G++) {
         const uint4 xb = xbs[G];
@@ -62,17 +69,17 @@ __device__ __forceinline__ void unit_q4k(uint32_t up, int u, const LaneCtx &L, f
         imma16832<false>(c4, q[G].x & NIB, q[G].z & NIB, q[G].y & NIB, q[G].w & NIB, xb.x, xb.y);
         int sA = byte_u(sw_A, 2 * (G & 1)), sB = byte_u(sw_B, 2 * (G & 1));
         acc[0] += sA * c4[0]; acc[1] += sA * c4[1]; acc[2] += sB * c4[2]; acc[3] += sB * c4[3];
-        imma16832<false>(c4, (q[G].x >> 4) & NIB, (q[G].z >> 4) & NIB, (q[G].y >> 4) & NIB, (q[G].w >> 4) & NIB, xb.z, xb.w);
+        imma16832<false>(c4, q[G].x & NIBH, q[G].z & NIBH, q[G].y & NIBH, q[G].w & NIBH, xb.z, xb.w);
         sA = byte_u(sw_A, 2 * (G & 1) + 1); sB = byte_u(sw_B, 2 * (G & 1) + 1);
-        acc[0] += sA * c4[0]; acc[1] += sA * c4[1]; acc[2] += sB * c4[2]; acc[3] += sB * c4[3];
+        acch[0] += sA * c4[0]; acch[1] += sA * c4[1]; acch[2] += sB * c4[2]; acch[3] += sB * c4[3];
     }
     const uint2 alw = lds64(L.alam_b + u * (kMaxCols * 4));
     const float al0 = __uint_as_float(alw.x), al1 = __uint_as_float(alw.y);
     const float2 dA = h2_to_f2(hA.x), dB = h2_to_f2(hB.x);   // (d, dmin)
-    master[0] = fmaf(dA.x * al0, (float)acc[0], master[0]);
-    master[1] = fmaf(dA.x * al1, (float)acc[1], master[1]);
-    master[2] = fmaf(dB.x * al0, (float)acc[2], master[2]);
-    master[3] = fmaf(dB.x * al1, (float)acc[3], master[3]);
+    master[0] = fmaf(dA.x * al0, fmaf((float)acch[0], 0.0625f, (float)acc[0]), master[0]);
+    master[1] = fmaf(dA.x * al1, fmaf((float)acch[1], 0.0625f, (float)acc[1]), master[1]);
+    master[2] = fmaf(dB.x * al0, fmaf((float)acch[2], 0.0625f, (float)acc[2]), master[2]);
+    master[3] = fmaf(dB.x * al1, fmaf((float)acch[3], 0.0625f, (float)acc[3]), master[3]);
     const float minv = __uint_as_float(lds32(L.minv_b + u * 16));   // undoes the power-of-two scale of the sums
     const float mA = dA.y * minv, mB = dB.y * minv;
     mm[0] = fmaf(mA, accm[0], mm[0]); mm[1] = fmaf(mA, accm[1], mm[1]);
@@ -93,13 +100,13 @@ __device__ __forceinline__ uint32_t q6k_bytes(uint32_t W, uint32_t H)
 }
 
 template <int QUARTER>
-__device__ __forceinline__ void q6k_pair(const uint4 &Pr, const uint4 &Pq, uint32_t Hr0, uint32_t Hr1, uint32_t Hq0, uint32_t Hq1,
+__device__ __forceinline__ void q6k_pair(const LaneCtx &L, const uint4 &Pr, const uint4 &Pq, uint32_t Hr0, uint32_t Hr1, uint32_t Hq0, uint32_t Hq1,
                                          uint32_t xaddr, uint32_t scA, uint32_t scB, int (&acc)[4])
 {
     // words: slot q1*2 + h with q1 = QUARTER & 1
     const uint32_t a0 = q6k_bytes<QUARTER>(word_of(Pr, (QUARTER & 1) * 2), Hr0), a2 = q6k_bytes<QUARTER>(word_of(Pr, (QUARTER & 1) * 2 + 1), Hr1);
     const uint32_t a1 = q6k_bytes<QUARTER>(word_of(Pq, (QUARTER & 1) * 2), Hq0), a3 = q6k_bytes<QUARTER>(word_of(Pq, (QUARTER & 1) * 2 + 1), Hq1);
-    const uint2 xb = lds64(xaddr);
+    const uint2 xb = ldb64(L, xaddr);
     int c4[4];
     imma16832<false>(c4, a0, a1, 0u, 0u, xb.x, 0u);          // scale group 2*QUARTER (k 0..15 of the 32)
     int sA = byte_s(scA, (QUARTER & 1) * 2), sB = byte_s(scB, (QUARTER & 1) * 2);
@@ -138,10 +145,10 @@ __device__ __forceinline__ void unit_q6k(uint32_t up, int u, const LaneCtx &L, f
         const uint32_t Hr0 = word_of(H0, n * 2), Hr1 = word_of(H0, n * 2 + 1), Hq0 = word_of(H1, n * 2), Hq1 = word_of(H1, n * 2 + 1);
         // MMA (n, quarter) covers k = 128n + 32*quarter + [0, 32): activation group 4u + 2n + quarter/2, sub = quarter & 1
         const uint32_t xg = L.xq_b + (4 * u + 2 * n) * 64 + c * 16;
-        q6k_pair<0>(P[n], P[2 + n], Hr0, Hr1, Hq0, Hq1, xg, word_of(sA, 2 * n), word_of(sB, 2 * n), acc);
-        q6k_pair<1>(P[n], P[2 + n], Hr0, Hr1, Hq0, Hq1, xg + 8, word_of(sA, 2 * n), word_of(sB, 2 * n), acc);
-        q6k_pair<2>(P[n], P[2 + n], Hr0, Hr1, Hq0, Hq1, xg + 64, word_of(sA, 2 * n + 1), word_of(sB, 2 * n + 1), acc);
-        q6k_pair<3>(P[n], P[2 + n], Hr0, Hr1, Hq0, Hq1, xg + 72, word_of(sA, 2 * n + 1), word_of(sB, 2 * n + 1), acc);
+        q6k_pair<0>(L, P[n], P[2 + n], Hr0, Hr1, Hq0, Hq1, xg, word_of(sA, 2 * n), word_of(sB, 2 * n), acc);
+        q6k_pair<1>(L, P[n], P[2 + n], Hr0, Hr1, Hq0, Hq1, xg + 8, word_of(sA, 2 * n), word_of(sB, 2 * n), acc);
+        q6k_pair<2>(L, P[n], P[2 + n], Hr0, Hr1, Hq0, Hq1, xg + 64, word_of(sA, 2 * n + 1), word_of(sB, 2 * n + 1), acc);
+        q6k_pair<3>(L, P[n], P[2 + n], Hr0, Hr1, Hq0, Hq1, xg + 72, word_of(sA, 2 * n + 1), word_of(sB, 2 * n + 1), acc);
     }
     const uint2 alw = lds64(L.alam_b + u * (kMaxCols * 4));
     const float al0 = __uint_as_float(alw.x), al1 = __uint_as_float(alw.y);
@@ -161,7 +168,7 @@ __device__ __forceinline__ void unit_q40(uint32_t up, int u, const LaneCtx &L, f
 #pragma unroll
     for (int p = 0; p < 4; p++) {
         const uint4 q = lds128(up + p * 512 + L.lane * 16);   // (row r, blk 2p), (row r, blk 2p+1), (row r+8, blk 2p), (row r+8, blk 2p+1)
-        const uint4 xb = lds128(L.xq_b + (4 * u + p) * 64 + c * 16);
+        const uint4 xb = ldb128(L, L.xq_b + (4 * u + p) * 64 + c * 16);
         const float2 sA = h2_to_f2(word_of(hA, p)), sB = h2_to_f2(word_of(hB, p));
 #pragma unroll
         for (int e = 0; e < 2; e++) {
@@ -189,7 +196,7 @@ __device__ __forceinline__ void unit_q80(uint32_t up, int u, const LaneCtx &L, f
 #pragma unroll
     for (int b = 0; b < 8; b++) {
         const uint4 q = lds128(up + b * 512 + L.lane * 16);   // (row r, k 4c..), (row r, k 16+4c..), (row r+8, ...), (row r+8, ...)
-        const uint2 xb = lds64(L.xq_b + (4 * u + (b >> 1)) * 64 + c * 16 + (b & 1) * 8);
+        const uint2 xb = ldb64(L, L.xq_b + (4 * u + (b >> 1)) * 64 + c * 16 + (b & 1) * 8);
         int c4[4];
         imma16832<true>(c4, q.x, q.z, q.y, q.w, xb.x, xb.y);
         const float2 sA = h2_to_f2(word_of(hA, b >> 1)), sB = h2_to_f2(word_of(hB, b >> 1));

@@ -56,10 +56,6 @@ static tlb_status do_init(int device)
     TLB_CUDA(cudaMemPoolSetAttribute(g_ctx.pool, cudaMemPoolAttrReleaseThreshold, &thresh));
     TLB_CUDA(cudaMalloc(&g_ctx.err_flag, sizeof(int)));
     TLB_CUDA(cudaMemset(g_ctx.err_flag, 0, sizeof(int)));
-    g_ctx.act_bytes = (size_t)1 << 20;
-    TLB_CUDA(cudaMalloc(&g_ctx.act_img, g_ctx.act_bytes));
-    TLB_CUDA(cudaMalloc(&g_ctx.grid_sync, 2 * sizeof(int)));
-    TLB_CUDA(cudaMemset(g_ctx.grid_sync, 0, 2 * sizeof(int)));
     g_inited = true;
     return TLB_OK;
 }
@@ -186,7 +182,6 @@ tlb_status tlb_sync(void)
     TLB_CUDA(cudaMemcpy(&flag, g_ctx.err_flag, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag) {
         cudaMemset(g_ctx.err_flag, 0, sizeof(int));
-        cudaMemset(g_ctx.grid_sync, 0, 2 * sizeof(int));   // an abandoned meeting point may have left them non-zero
         return fail(TLB_ERR_DEVICE, "a kernel gave up a bounded wait (code %d)", flag);
     }
     return TLB_OK;

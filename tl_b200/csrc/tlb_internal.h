@@ -31,11 +31,6 @@ struct Context {
     void *flush_buf = nullptr;
     size_t flush_bytes = 0;
     int *err_flag = nullptr;  // device word set by kernels whose bounded waits ran out
-    // scratch of the streaming matvec: global image of its activation tables, built once per launch,
-    // and the two counters of its grid-wide meeting point (all launches are ordered on `stream`)
-    uint8_t *act_img = nullptr;
-    size_t act_bytes = 0;
-    int *grid_sync = nullptr;
     bool capturing = false;
     uint64_t capture_launches = 0;
 };
@@ -115,38 +110,47 @@ tlb_status launch_dequant_tiled(int type, const uint8_t *tiled, float *out, int6
 // qmatvec.cu ---------------------------------------------------------------------------
 // How the activation vector of a streaming matvec is produced inside the kernel.
 enum Prologue { PRO_PLAIN = 0, PRO_ADD_NORM = 1, PRO_SILU_MUL = 2 };
+constexpr int kMaxSlices = 16;   // most K-slices a matvec may split its output into
+// A vector kept as the element-wise sum of `slices` arrays `stride` floats apart: the form in which
+// the streaming matvec leaves its output (one array per K-slice, each element written exactly once).
+// Readers add the slices in index order when they load.  slices == 1 is a plain array.
+struct SlicedVec {
+    const float *p = nullptr;
+    int slices = 1;
+    long long stride = 0;
+};
 struct MatvecJob {
     // up to 3 weight tensors sharing K and the same activation (q|k|v, gate|up)
     int n_w = 0;
     const uint8_t *w[3] = {nullptr, nullptr, nullptr};
     int64_t n_tiles[3] = {0, 0, 0};
     int64_t n_rows[3] = {0, 0, 0};                 // valid output rows (<= n_tiles*16)
-    float *out[3] = {nullptr, nullptr, nullptr};   // each [M, n_rows], must be zero on entry
-    // Optional second accumulation slot per output (also zero on entry): odd CTAs add there, the reader
-    // sums both.  Lets twice as many CTAs share a tile with scheduling-independent sums.
-    float *out_alt[3] = {nullptr, nullptr, nullptr};
-    int force_warps = 0;             // 16: one CTA of 16 consumer warps per SM even where two of 8 would fit
+    // Output of tensor i: `slices` arrays [M, n_rows] spaced out_stride[i] floats apart, every element
+    // of every slice written (no clearing needed); the logical result is their sum.
+    float *out[3] = {nullptr, nullptr, nullptr};
+    int64_t out_stride[3] = {0, 0, 0};
+    int slices = 1;                  // from qmatvec_plan_slices() for this shape
     int type = 0;
     int64_t k = 0;
     int m = 1;
     // prologue inputs
     int prologue = PRO_PLAIN;
-    const float *x = nullptr;        // PLAIN: x [M,K]; ADD_NORM: residual [K]; SILU_MUL: gate [M,K]
-    const float *x2 = nullptr;       // ADD_NORM: delta added to x (may be null); SILU_MUL: up
-    const float *x3 = nullptr;       // ADD_NORM: second delta (the other accumulation slot; may be null)
+    SlicedVec x;                     // PLAIN: x [M,K]; ADD_NORM: residual [K]; SILU_MUL: gate [M,K]
+    SlicedVec x2;                    // ADD_NORM: delta added to x (p may be null); SILU_MUL: up
     const float *norm_w = nullptr;   // ADD_NORM: weight [K]
     float eps = 0.f;
     float *x_out = nullptr;          // ADD_NORM: x + x2 written here by block 0 (may be null)
     const float *emb_table = nullptr; // ADD_NORM with token lookup: x = emb_table[*token * K ...]
     const int *token = nullptr;
-    // buffers the kernel clears for later kernels of a chain (may be null)
-    float *zero_ptr[3] = {nullptr, nullptr, nullptr};
-    int64_t zero_n[3] = {0, 0, 0};
     bool pdl = false;                // launch with programmatic stream serialization
-    long long *trace = nullptr;      // optional device buffer [grid][8] of SM clock stamps (timing studies)
+    long long *trace = nullptr;      // optional device buffer [grid][10] of stamps (timing studies)
 };
 tlb_status launch_qmatvec(const MatvecJob &job);
+// K-slices the kernel wants for a launch of `tiles` 16-row tiles (all tensors) over inner dimension k,
+// at most max_slices; a pure function of its arguments, so producer and consumer agree without talking.
+int qmatvec_plan_slices(int type, int64_t k, int m, int64_t tiles, int max_slices);
 size_t qmatvec_max_k(int m);   // largest K the single-pass kernel supports for m activation rows
+tlb_status launch_sum_slices(const float *src, int slices, int64_t stride, float *out, int64_t n);
 
 // ops.cu
 tlb_status launch_binary(int op, const float *a, const float *b, float *out, const int64_t *oshape,
@@ -174,7 +178,7 @@ tlb_status launch_f32_to_f16(const float *a, __half *out, int64_t n);
 
 // attention.cu
 struct DecodeAttnJob {
-    const float *qkv;      // [q (H*D) | k (KVH*D) | v (KVH*D)] raw projections of the new token
+    SlicedVec qkv;         // [q (H*D) | k (KVH*D) | v (KVH*D)] raw projections of the new token
     void *kcache, *vcache; // [KVH][max_seq][D] of this layer, f16 or f32
     int kv_f16;
     int H, KVH, D, max_seq;
