@@ -10,6 +10,7 @@
 //
 // sdpa_kernel: the generic tl_tensor_sdpa entry (flash_attention_kernel, autograd.cu:2263-2367).
 #include "tlb_internal.h"
+#include "span_trace.cuh"
 
 namespace tlb {
 
@@ -61,6 +62,7 @@ struct AttnParams {
     float *out;       // [H * D]
     int use_pdl;
     int row_stride;   // shared-memory row stride in bytes (16-byte chunks, count = 4 mod 8: conflict-free)
+    unsigned long long *span;
 };
 
 __device__ __forceinline__ float ld_qkv(const AttnParams &p, size_t i)
@@ -89,6 +91,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
 
     // Cache length and this CTA's key range.  pos was written at the end of the previous decode
     // step, which every predecessor of this launch has already waited for.
+    if (tid == 0) span_start(p.span);
     const int pos = *p.pos;
     const int Tlen = pos + 1;
     const int nsplit = (Tlen + kKeysPerCta - 1) / kKeysPerCta;
@@ -112,6 +115,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
+    if (tid == 0) span_event(p.span, 1);
     // RoPE (crates/tl_cpu/src/ffi.rs:2629-2685: adjacent pairs, one table row) of the REP query heads
     const int rp = *p.rope_pos;
     const float *cs = p.cos_t + (size_t)rp * D, *sn = p.sin_t + (size_t)rp * D;
@@ -140,6 +144,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
     }
     cp_async_wait_all();
     __syncthreads();
+    if (tid == 0) span_event(p.span, 2);
 
     // scores: thread (key = tid/4, dq = tid%4) covers chunks dq, dq+4, ... of its key row, all REP heads
     {
@@ -226,7 +231,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
             part[h * (D + 2) + d] = s;
         }
     }
-    if (nsplit == 1) return;
+    if (nsplit == 1) { if (tid == 0) span_event(p.span, 3); return; }
     if (tid < REP) { part[tid * (D + 2) + D] = ml[tid * 2]; part[tid * (D + 2) + D + 1] = ml[tid * 2 + 1]; }
     // the last CTA of this KV head to finish merges all splits
     __threadfence();
@@ -236,6 +241,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
         is_last = (old == nsplit - 1);
     }
     __syncthreads();
+    if (tid == 0) span_event(p.span, 3);
     if (!is_last) return;
     __threadfence();
     const float *base = p.partial + (size_t)kvh * p.max_splits * REP * (D + 2);
@@ -252,7 +258,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
         }
         p.out[(size_t)(kvh * REP + h) * D + d] = O / L;
     }
-    if (tid == 0) p.counters[kvh] = 0;
+    if (tid == 0) { p.counters[kvh] = 0; span_event(p.span, 3); }
 }
 
 static int attn_row_stride(int D, int esize)
@@ -271,6 +277,8 @@ static tlb_status launch_decode_t(const AttnParams &p, int max_splits, int KVH, 
     static size_t set_bytes = 0;   // the kernel also has a few bytes of static shared memory
     if (smem > set_bytes) {
         TLB_CUDA(cudaFuncSetAttribute(decode_attention_kernel<T, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // same L1 / shared-memory split as the matvec kernels around it: the SMs never re-partition between launches
+        TLB_CUDA(cudaFuncSetAttribute(decode_attention_kernel<T, REP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         set_bytes = smem;
     }
     cudaLaunchConfig_t cfg = {};
@@ -301,6 +309,7 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     p.pos = j.pos; p.rope_pos = j.rope_pos; p.cos_t = j.cos_t; p.sin_t = j.sin_t; p.scale = j.scale;
     p.partial = j.partial; p.counters = j.counters; p.max_splits = j.splits; p.out = j.out;
     p.use_pdl = j.pdl ? 1 : 0;
+    p.span = j.span;
     p.row_stride = attn_row_stride(j.D, j.kv_f16 ? 2 : 4);
 #define DISPATCH(REPV)                                                                         \
     if (rep == REPV)                                                                           \

@@ -9,8 +9,7 @@
 //   K4  residual add + RMSNorm*w (prologue)  ->  gate|up matvec
 //   K5  SiLU(gate)*up (prologue)             ->  down matvec
 //   ... output_norm (prologue) -> lm_head matvec, argmax + position advance.
-// A matvec leaves its output as a few K-slices (one array per slice, each element written exactly
-// once, nothing accumulated or cleared); the kernel that consumes it adds the slices as it loads.
+// Every buffer of the chain is written in full by its producer (no accumulation, no clearing).
 // The residual stream ping-pongs between two buffers so no kernel updates memory that another CTA
 // of the same launch reads.  All kernels are launched with programmatic dependent launch, so a
 // kernel's weight prefetch overlaps its predecessor's tail.
@@ -161,9 +160,11 @@ SlicedVec sliced(const float *p, int slices, int64_t stride)
 }
 
 // the kernel chain of one decode step (launched eagerly or into a capturing stream)
-tlb_status enqueue_step(tlb_decoder *d)
+tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
 {
     const tlb_decoder_cfg &c = d->cfg;
+    int span_i = 0;
+    auto next_span = [&]() { return span ? span + 8 * (span_i++) : nullptr; };   // timeline slot of the next launch
     const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
     const int L = c.n_layers;
     const int64_t nqkv = qd + 2 * kvd;
@@ -175,7 +176,7 @@ tlb_status enqueue_step(tlb_decoder *d)
             set_w(j, 0, w.q, d->qkv, nqkv);
             set_w(j, 1, w.k, d->qkv + qd, nqkv);
             set_w(j, 2, w.v, d->qkv + qd + kvd, nqkv);
-            j.slices = d->s_qkv;
+           
             j.type = w.q->type; j.k = dm; j.m = 1;
             j.prologue = PRO_ADD_NORM;
             j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
@@ -183,6 +184,7 @@ tlb_status enqueue_step(tlb_decoder *d)
             else { j.x = sliced(d->xa, 1, 0); j.x2 = sliced(d->down_out, d->s_down, dm); }
             j.x_out = d->xb;
             j.pdl = d->pdl;
+            j.span = next_span();
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K2
@@ -193,16 +195,18 @@ tlb_status enqueue_step(tlb_decoder *d)
             a.kv_f16 = c.kv_f16; a.H = c.n_heads; a.KVH = c.n_kv_heads; a.D = c.head_dim; a.max_seq = c.max_seq;
             a.pos = d->state + 1; a.rope_pos = d->state + 2; a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.scale = c.attn_scale;
             a.partial = d->partial; a.counters = d->counters; a.splits = d->max_splits; a.out = d->attn; a.pdl = d->pdl;
+            a.span = next_span();
             TLB_TRY(launch_decode_attention(a));
         }
         {   // K3
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.o, d->o_out, dm);
-            j.slices = d->s_o;
+           
             j.type = w.o->type; j.k = qd; j.m = 1;
             j.prologue = PRO_PLAIN; j.x = sliced(d->attn, 1, 0);
             j.pdl = d->pdl;
+            j.span = next_span();
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K4
@@ -210,23 +214,25 @@ tlb_status enqueue_step(tlb_decoder *d)
             j.n_w = 2;
             set_w(j, 0, w.gate, d->gu, 2 * (int64_t)F);
             set_w(j, 1, w.up, d->gu + F, 2 * (int64_t)F);
-            j.slices = d->s_gu;
+           
             j.type = w.gate->type; j.k = dm; j.m = 1;
             j.prologue = PRO_ADD_NORM; j.x = sliced(d->xb, 1, 0); j.x2 = sliced(d->o_out, d->s_o, dm);
             j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
             j.x_out = d->xa;
             j.pdl = d->pdl;
+            j.span = next_span();
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K5
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.down, d->down_out, dm);
-            j.slices = d->s_down;
+           
             j.type = w.down->type; j.k = F; j.m = 1;
             j.prologue = PRO_SILU_MUL;
             j.x = sliced(d->gu, d->s_gu, 2 * (int64_t)F); j.x2 = sliced(d->gu + F, d->s_gu, 2 * (int64_t)F);
             j.pdl = d->pdl;
+            j.span = next_span();
             TLB_TRY(launch_qmatvec(j));
         }
     }
@@ -234,12 +240,14 @@ tlb_status enqueue_step(tlb_decoder *d)
         MatvecJob j;
         j.n_w = 1;
         set_w(j, 0, d->head, d->logits_sl, c.vocab);
-        j.slices = d->s_head;
+       
         j.type = d->head->type; j.k = dm; j.m = 1;
         j.prologue = PRO_ADD_NORM; j.x = sliced(d->xa, 1, 0); j.x2 = sliced(d->down_out, d->s_down, dm);
         j.norm_w = d->out_norm->f32(); j.eps = c.eps;
         j.x_out = d->xb;
+        j.last_of_chain = true;
         j.pdl = d->pdl;
+        j.span = next_span();
         TLB_TRY(launch_qmatvec(j));
     }
     {
@@ -253,6 +261,11 @@ tlb_status enqueue_step(tlb_decoder *d)
             at[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = at;
             cfg.numAttrs = 1;
+        }
+        static bool carveout_set = false;
+        if (!carveout_set) {
+            TLB_CUDA(cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            carveout_set = true;
         }
         TLB_CUDA(cudaLaunchKernelEx(&cfg, argmax_advance_kernel, (const float *)d->logits_sl, d->s_head, (long long)c.vocab, d->logits,
                                     (int)c.vocab, (int)(c.tie_rule == TLB_TIE_FIRST), d->amax_v, d->amax_i, d->counters + c.n_kv_heads,
@@ -352,11 +365,8 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     }
     {
         const LayerW &w0 = d->layers[0];
-        d->s_qkv = qmatvec_plan_slices(w0.q->type, dm, 1, w0.q->n_tiles + w0.k->n_tiles + w0.v->n_tiles, kMaxSlices);
-        d->s_o = qmatvec_plan_slices(w0.o->type, qd, 1, w0.o->n_tiles, kMaxSlices);
-        d->s_gu = qmatvec_plan_slices(w0.gate->type, dm, 1, w0.gate->n_tiles + w0.up->n_tiles, kMaxSlices);
-        d->s_down = qmatvec_plan_slices(w0.down->type, F, 1, w0.down->n_tiles, kMaxSlices);
-        d->s_head = qmatvec_plan_slices(d->head->type, dm, 1, d->head->n_tiles, kMaxSlices);
+        // The matvec folds its K-slices itself (last warp of a tile), so every buffer of the chain is a
+        // plain vector: one slice each.
         for (const LayerW &w : d->layers)
             if (w.q->type != w0.q->type || w.o->type != w0.o->type || w.gate->type != w0.gate->type || w.down->type != w0.down->type) {
                 tlb_decoder_destroy(d);
@@ -502,6 +512,55 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
     if (copies < 1) copies = 1;
     if (copies > c.n_layers) copies = c.n_layers;
     std::string w(which);
+    if (w == "chain") {
+        // Timeline of one whole decode step launched eagerly (same launches as the graph): `copies` is the
+        // cache position, `iters` the warm-up steps.  Printed to stderr: per launch, microseconds from the
+        // start of the step to first CTA start / last dependency wait passed / last prologue done / end.
+        const int nk = 5 * c.n_layers + 1;
+        unsigned long long *span = nullptr;
+        TLB_CUDA(cudaMalloc(&span, (size_t)nk * 8 * sizeof(unsigned long long)));
+        int pos = std::min(std::max(copies, 0), c.max_seq - iters - 2);
+        tlb_status st = set_state(d, 1, pos, pos, 0);
+        for (int i = 0; i < iters && st == TLB_OK; i++) st = enqueue_step(d);
+        std::vector<unsigned long long> h((size_t)nk * 8, 0ull);
+        for (int i = 0; i < nk; i++) h[(size_t)i * 8] = ~0ull;
+        cudaMemcpyAsync(span, h.data(), h.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice, ctx()->stream);
+        cudaStreamSynchronize(ctx()->stream);
+        cudaEvent_t e0, e1;
+        cudaEventCreate(&e0); cudaEventCreate(&e1);
+        cudaEventRecord(e0, ctx()->stream);
+        if (st == TLB_OK) st = enqueue_step(d, span);
+        cudaEventRecord(e1, ctx()->stream);
+        cudaEventSynchronize(e1);
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        cudaMemcpy(h.data(), span, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+        cudaFree(span);
+        cudaEventDestroy(e0); cudaEventDestroy(e1);
+        if (st != TLB_OK) return st;
+        const unsigned long long t0 = h[0];
+        const char *names[5] = {"qkv", "attn", "o", "gate_up", "down"};
+        double busy[6] = {0, 0, 0, 0, 0, 0}, gap[6] = {0, 0, 0, 0, 0, 0};
+        unsigned long long prev_end = t0;
+        for (int i = 0; i < nk; i++) {
+            const unsigned long long *t = &h[(size_t)i * 8];
+            const int kind = i == nk - 1 ? 5 : i % 5;
+            if (i < 10 || i >= nk - 6)
+                fprintf(stderr, "[tlb chain] %3d %-8s start %9.2f (last %9.2f, set up %9.2f)  waited %9.2f  prologue %9.2f  end %9.2f   (us)\n", i,
+                        kind == 5 ? "head" : names[kind], (t[0] - t0) / 1e3, t[4] ? (t[4] - t0) / 1e3 : 0.0, t[5] ? (t[5] - t0) / 1e3 : 0.0,
+                        (t[1] - t0) / 1e3, (t[2] - t0) / 1e3, (t[3] - t0) / 1e3);
+            busy[kind] += (t[3] - std::max(t[1], prev_end)) / 1e3;   // from (dependency met) to end
+            gap[kind] += ((double)std::max(t[1], prev_end) - (double)prev_end) / 1e3;
+            prev_end = t[3];
+        }
+        for (int kd = 0; kd < 6; kd++)
+            fprintf(stderr, "[tlb chain] %-8s total after-dependency time %9.1f us, dependency gaps %8.1f us\n", kd == 5 ? "head" : names[kd], busy[kd], gap[kd]);
+        fprintf(stderr, "[tlb chain] step %.1f us by events, %.1f us first start to last end (argmax not probed)\n", ms * 1e3,
+                (h[(size_t)(nk - 1) * 8 + 3] - t0) / 1e3);
+        *us_per_launch = ms * 1e3f;
+        if (bytes_per_launch) *bytes_per_launch = 0;
+        return tlb_sync();
+    }
     int64_t out_n = w == "qkv" ? qd + 2 * kvd : (w == "o" || w == "down") ? dm : w == "gate_up" ? 2 * F : w == "head" ? c.vocab : -1;
     if (out_n < 0) return fail(TLB_ERR_ARG, "unknown kernel '%s' (qkv, o, gate_up, down, head)", which);
     int64_t kk = (w == "o") ? qd : (w == "down") ? F : dm;
@@ -529,17 +588,19 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         j.m = 1; j.prologue = PRO_PLAIN; j.x = sliced(xin, 1, 0);
         if (w == "qkv") {
             j.n_w = 3; set_w(j, 0, lw.q, o, out_n); set_w(j, 1, lw.k, o + qd, out_n); set_w(j, 2, lw.v, o + qd + kvd, out_n);
-            j.slices = d->s_qkv; j.type = lw.q->type; j.k = dm; bytes = lw.q->nbytes() + lw.k->nbytes() + lw.v->nbytes();
+            j.type = lw.q->type; j.k = dm; bytes = lw.q->nbytes() + lw.k->nbytes() + lw.v->nbytes();
         } else if (w == "o") {
-            j.n_w = 1; set_w(j, 0, lw.o, o, out_n); j.slices = d->s_o; j.type = lw.o->type; j.k = qd; bytes = lw.o->nbytes();
+            j.n_w = 1; set_w(j, 0, lw.o, o, out_n); j.type = lw.o->type; j.k = qd; bytes = lw.o->nbytes();
         } else if (w == "gate_up") {
-            j.n_w = 2; set_w(j, 0, lw.gate, o, out_n); set_w(j, 1, lw.up, o + F, out_n); j.slices = d->s_gu; j.type = lw.gate->type; j.k = dm;
+            j.n_w = 2; set_w(j, 0, lw.gate, o, out_n); set_w(j, 1, lw.up, o + F, out_n); j.type = lw.gate->type; j.k = dm;
             bytes = lw.gate->nbytes() + lw.up->nbytes();
         } else if (w == "down") {
-            j.n_w = 1; set_w(j, 0, lw.down, o, out_n); j.slices = d->s_down; j.type = lw.down->type; j.k = F; bytes = lw.down->nbytes();
+            j.n_w = 1; set_w(j, 0, lw.down, o, out_n); j.type = lw.down->type; j.k = F; bytes = lw.down->nbytes();
         } else {
-            j.n_w = 1; set_w(j, 0, d->head, o, out_n); j.slices = d->s_head; j.type = d->head->type; j.k = dm; bytes = d->head->nbytes();
+            j.n_w = 1; set_w(j, 0, d->head, o, out_n); j.type = d->head->type; j.k = dm; bytes = d->head->nbytes();
+            j.last_of_chain = true;
         }
+        j.pdl = d->pdl;   // as in the decode chain: a launch's set-up overlaps its predecessor
         if (trace && it == iters - 1) j.trace = trace;
         st = launch_qmatvec(j);
     }

@@ -4,7 +4,9 @@
 // re-read once per activation row) and the dequantise-then-naive-matmul route the reference takes
 // for Q4_0 / Q8_0 (crates/tl_runtime/src/system.rs:236-264).
 //
-// Shape of the kernel (one persistent CTA of 16 warps per SM):
+// Shape of the kernel (one persistent CTA of 16 warps per SM, the whole register file at 128 per thread;
+// a variant of two 8-warp CTAs that leaves room for a CTA of the next kernel measured 35 % slower
+// per step: at 80 registers the unit loop no longer keeps its shared loads in flight):
 //   * work is cut into ITEMS: one tile of 16 output rows x one K-slice of `upi` consecutive units
 //     (a unit = 16 rows x 256 weights, quant.cu).  Items are numbered slice-major and dealt out in
 //     contiguous ranges, first to CTAs and then to the warps of a CTA, so every warp gets the same
@@ -15,29 +17,38 @@
 //     unit `spw` positions ahead.  No other warp is ever waited for - there is no block-wide barrier,
 //     no shared-memory reduction and no atomic in the streaming phase;
 //   * the copies do not depend on the activations, so the first `spw` are issued before the kernel
-//     waits for its predecessor (programmatic dependent launch): the HBM stream starts while the
-//     previous kernel is still finishing;
+//     waits for its predecessor (programmatic dependent launch);
 //   * the prologue quantises the activation to int8 levels in shared memory (qmv_prologue.cuh) -
 //     only the 256-blocks the CTA's K-slices cover - and can fuse what precedes the matvec in the
 //     decode chain: residual add + RMSNorm * weight, SiLU(gate) * up, or the embedding lookup;
 //   * per unit: conflict-free 128-bit shared loads, one AND per four weights, integer tensor-core
 //     MMAs (qmv_units.cuh);
-//   * the result of item (slice, tile) is written to out[slice][m][row].  Every element of every
-//     slice is written by exactly one warp, so nothing has to be cleared beforehand and the sums do
-//     not depend on scheduling; whoever reads the output adds the slices in index order.
+//   * the 16 * m partial results of item (slice, tile) are written - not added - to a scratch slot of
+//     their own; the warp that finishes the last slice of a tile (a per-tile counter tells) adds the
+//     slices in index order and writes the output rows.  Nothing is accumulated atomically and nothing
+//     has to be cleared beforehand, so results do not depend on scheduling.
 #include "qmv_prologue.cuh"
 #include "qmv_units.cuh"
+#include "span_trace.cuh"
 
 #include <algorithm>
 
 namespace tlb {
 
-constexpr int kWarps = 16;
+#ifndef TLB_MV_WARPS
+#define TLB_MV_WARPS 16
+#define TLB_MV_CTAS 1
+#define TLB_MV_RESIDENT 1
+#endif
+constexpr int kWarps = TLB_MV_WARPS;
 constexpr int kThreads = kWarps * 32;
+constexpr int kCtasPerSm = TLB_MV_CTAS;           // CTAs a launch brings per SM
+constexpr int kResidentPerSm = TLB_MV_RESIDENT;   // CTAs the register and shared-memory budgets allow per SM
 
 struct ItemRef {
     const uint8_t *src;   // first unit of the item
     int wi, row0, slice;  // tensor, first output row within the tensor, K-slice
+    int tile;             // tile index within the launch
 };
 
 // Position in the slice-major item order, advanced without divisions.
@@ -58,6 +69,7 @@ __device__ __forceinline__ ItemRef item_ref(const MvParams &p, const ItemCursor 
 {
     ItemRef r;
     r.slice = c.slice;
+    r.tile = c.tile;
     r.wi = (c.tile >= p.tiles_end[0]) + (c.tile >= p.tiles_end[1]);
     const int t0 = r.wi == 0 ? 0 : p.tiles_end[r.wi - 1];
     r.row0 = (c.tile - t0) * 16;
@@ -66,7 +78,7 @@ __device__ __forceinline__ ItemRef item_ref(const MvParams &p, const ItemCursor 
 }
 
 template <int FMT>
-__global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_constant__ MvParams p)
+__global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const __grid_constant__ MvParams p)
 {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -74,32 +86,57 @@ __global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_const
     const int spw = p.spw;
     const uint32_t ring = smem_u32(smem) + (uint32_t)(warp * spw) * p.stage_bytes;   // this warp's stages
     const uint32_t bars = smem_u32(smem + p.off_bars) + (uint32_t)(warp * spw) * 8;  // and their barriers
-    const int G = gridDim.x, b = blockIdx.x;
+    const int b = blockIdx.x;
 #define STAMP(i) do { if (p.trace && tid == 0) p.trace[(size_t)b * 10 + (i)] = clock64(); } while (0)
     STAMP(0);
+    if (tid == 0) { span_start(p.span); span_event(p.span, 4); }
     if (p.trace && tid == 0) p.trace[(size_t)b * 10 + 8] = (long long)global_ns();
 
     // items of this CTA, then of this warp
-    const int ci0 = (int)((long long)p.n_items * b / G), ci1 = (int)((long long)p.n_items * (b + 1) / G);
-    const int nci = ci1 - ci0;
+    const int ci0 = b * p.ipc_q + min(b, p.ipc_r), nci = p.ipc_q + (b < p.ipc_r ? 1 : 0), ci1 = ci0 + nci;
     const int i0 = ci0 + nci * warp / kWarps, i1 = ci0 + nci * (warp + 1) / kWarps;
     const int n_units = (i1 - i0) * p.upi;
     // activation blocks the CTA's items cover
     const int s_first = nci > 0 ? ci0 / p.tiles : 0, s_last = nci > 0 ? (ci1 - 1) / p.tiles : 0;
     const int blk0 = s_first * p.upi, nb = nci > 0 ? (s_last + 1) * p.upi - blk0 : 0;
 
-    if (lane == 0) {
-        for (int s = 0; s < spw; s++) mbar_init(bars + s * 8, 1);
+    // Ring set-up, one lane per stage so that it takes one round of latencies instead of `spw`:
+    // lane s initialises the barrier of stage s and requests the warp's unit s.
+    // Only the first kEarly units are requested before the prologue: the activation loads of the
+    // prologue share the SM's path from L2 with these copies and would otherwise queue behind a whole
+    // ring of weights.  The rest of the ring is requested once the activation values have arrived.
+    constexpr int kEarly = 2;
+    const int n_first = min(spw, n_units);
+    const uint8_t *first_src = nullptr;
+    if (lane < spw) {
+        mbar_init(bars + lane * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (lane < n_first) {
+            const int it = lane / p.upi, uo = lane - it * p.upi;
+            first_src = item_ref(p, cursor_at(p, i0 + it)).src + (size_t)uo * p.unit_bytes;
+            if (lane < kEarly) {
+                mbar_expect_tx(bars + lane * 8, p.unit_bytes);
+                bulk_g2s(ring + lane * p.stage_bytes, first_src, p.unit_bytes, bars + lane * 8);
+            }
+        }
     }
     if (tid == 0) sh->abort_flag = 0;
     __syncwarp();
 
-    // Copy cursor (meaningful in lane 0 only): the next unit to request and how many remain.
-    ItemCursor pf_cur = cursor_at(p, i0);
-    int pf_left_in_item = 0, pf_remaining = n_units, issued = 0;
+    // Copy cursor (used by lane 0 only): the next unit to request and how many remain.
+    int pf_left_in_item = 0, pf_remaining = n_units - n_first, issued = n_first;
     const uint8_t *pf_src = nullptr;
+    ItemCursor pf_cur;
+    {
+        const int it = n_first / p.upi, uo = n_first - it * p.upi;
+        pf_cur = cursor_at(p, i0 + it);
+        if (uo && pf_remaining > 0) {   // in the middle of an item
+            pf_src = item_ref(p, pf_cur).src + (size_t)uo * p.unit_bytes;
+            cursor_next(p, pf_cur);
+            pf_left_in_item = p.upi - uo;
+        }
+    }
     auto issue_copy = [&](int stage) {
         if (pf_left_in_item == 0) { pf_src = item_ref(p, pf_cur).src; cursor_next(p, pf_cur); pf_left_in_item = p.upi; }
         mbar_expect_tx(bars + stage * 8, p.unit_bytes);
@@ -107,9 +144,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_const
         pf_src += p.unit_bytes;
         pf_left_in_item--; pf_remaining--; issued++;
     };
-    if (lane == 0)
-        for (int s = 0; s < spw && pf_remaining > 0; s++) issue_copy(s);
     STAMP(1);
+    if (tid == 0) span_event(p.span, 5);
 
     if (p.use_pdl) {
         pdl_wait();                // everything below may read what the previous kernel wrote
@@ -119,8 +155,16 @@ __global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_const
     }
     __syncthreads();               // abort_flag initialised; also keeps the CTA together for the prologue
     STAMP(2);
-    build_activation<FMT>(p, sh, smem, tid, kThreads, blk0, nb);
+    if (tid == 0) span_event(p.span, 1);
+    build_activation<FMT>(p, sh, smem, tid, kThreads, blk0, nb, [&](float dep) {
+        // the rest of the ring's first round; the test on `dep` only ties the requests to the arrival of the loads
+        if (lane >= kEarly && lane < n_first && __float_as_uint(dep) != 0x7fedcba9u) {
+            mbar_expect_tx(bars + lane * 8, p.unit_bytes);
+            bulk_g2s(ring + lane * p.stage_bytes, first_src, p.unit_bytes, bars + lane * 8);
+        }
+    });
     STAMP(3);
+    if (tid == 0) span_event(p.span, 2);
     volatile int *abortp = &sh->abort_flag;
 
     const int ncols = p.m * p.nl;
@@ -159,10 +203,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_const
             if (++stage == spw) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        // Fold the level columns of each activation row (they sit in the four lanes of a quad) and
-        // store the 16 rows of the item.  The Q4_K min term of activation row mi lives in lane c == mi.
-        float *dst = p.out[ir.wi] + (size_t)ir.slice * p.out_stride[ir.wi];
+        // Fold the level columns of each activation row (they sit in the four lanes of a quad).  The
+        // Q4_K min term of activation row mi lives in lane c == mi.  With one K-slice the 16 rows go
+        // straight to the output; otherwise to this item's 16*m floats of the slice scratch.
+        float *out = p.out[ir.wi];
         const int nrows = p.n_rows[ir.wi];
+        float *part = p.part + ((size_t)ir.slice * p.tiles + ir.tile) * (16 * p.m);
         for (int mi = 0; mi < p.m; mi++) {
             const int lo = mi * p.nl, hi = lo + p.nl, cA = 2 * L.c, cB = 2 * L.c + 1;
             const bool inA = cA >= lo && cA < hi, inB = cB >= lo && cB < hi;
@@ -172,9 +218,48 @@ __global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_const
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
             if (L.c == mi) {
                 if (FMT == TLB_GGML_Q4_K) { v0 -= mm[0] + mm[1]; v1 -= mm[2] + mm[3]; }
-                const int g0 = ir.row0 + L.r, g1 = g0 + 8;
-                if (g0 < nrows) dst[(size_t)mi * nrows + g0] = v0;
-                if (g1 < nrows) dst[(size_t)mi * nrows + g1] = v1;
+                if (p.kb == 1) {
+                    const int g0 = ir.row0 + L.r, g1 = g0 + 8;
+                    if (g0 < nrows) out[(size_t)mi * nrows + g0] = v0;
+                    if (g1 < nrows) out[(size_t)mi * nrows + g1] = v1;
+                } else {
+                    part[mi * 16 + L.r] = v0;
+                    part[mi * 16 + L.r + 8] = v1;
+                }
+            }
+        }
+    }
+    if (ok && p.kb > 1 && i1 > i0) {
+        // All partial results of this warp are out.  One fence, then one count per item (lane j counts
+        // item j); the warp that completes a tile's last K-slice adds the slices in index order and
+        // writes the output rows, so the sum is the same whichever warp does it.  It also clears the
+        // tile's counter for the next launch on this stream.
+        __threadfence();                                      // our slices are visible before the counts say so
+        __syncwarp();
+        for (int base = i0; base < i1; base += 32) {
+            const int mine = base + lane;
+            ItemCursor cj = cursor_at(p, mine < i1 ? mine : base);
+            bool last = false;
+            if (mine < i1) last = atomicAdd(p.tile_cnt + cj.tile, 1) == p.kb - 1;
+            const unsigned lasts = __ballot_sync(0xffffffffu, last);
+            if (lasts) __threadfence();                       // the other slices are visible once their counts are
+            for (unsigned rest = lasts; rest; rest &= rest - 1) {
+                const int j = __ffs(rest) - 1;
+                ItemCursor cf;
+                cf.slice = 0;
+                cf.tile = __shfl_sync(0xffffffffu, cj.tile, j);
+                const ItemRef fr = item_ref(p, cf);
+                float *out = p.out[fr.wi];
+                const int nrows = p.n_rows[fr.wi];
+                const float *src = p.part + (size_t)fr.tile * (16 * p.m);
+                const size_t sstride = (size_t)p.tiles * (16 * p.m);
+                for (int e = lane; e < 16 * p.m; e += 32) {
+                    float a = __ldcg(src + e);
+                    for (int s = 1; s < p.kb; s++) a += __ldcg(src + s * sstride + e);
+                    const int mi = e >> 4, g = fr.row0 + (e & 15);
+                    if (g < nrows) out[(size_t)mi * nrows + g] = a;
+                }
+                if (lane == 0) p.tile_cnt[fr.tile] = 0;
             }
         }
     }
@@ -183,6 +268,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmatvec_kernel(const __grid_const
         for (int q = consumed; q < issued; q++) mbar_wait_drain(bars + (q % spw) * 8, (q / spw) & 1);
     }
     STAMP(6);
+    if (lane == 0) span_event(p.span, 3);
     if (p.trace && tid == 0) p.trace[(size_t)b * 10 + 9] = (long long)global_ns();
 #undef STAMP
 }
@@ -254,14 +340,16 @@ static double slice_cost(int type, int m, int64_t tiles, int upt, int upi, int s
 {
     const int kb = upt / upi;
     const int64_t n_items = tiles * kb;
-    const int grid = (int)std::min<int64_t>(sm_count, n_items);
+    const int grid = (int)std::min<int64_t>((int64_t)sm_count * kCtasPerSm, n_items);
     const int64_t ipc = (n_items + grid - 1) / grid, ipw = (ipc + kWarps - 1) / kWarps;
     const int nb = blocks_per_cta(n_items, grid, tiles, upi, upt);
     const double unit = type == TLB_GGML_Q6_K ? 300.0 : type == TLB_GGML_Q8_0 ? 150.0 : 210.0;
     const double stream = (double)ipw * (upi * unit + 60.0);
-    const double quant = 300.0 * ((m * nb + 7) / 8);
-    const double reader = 30.0 * kb;
-    return stream + quant + reader;
+    const double quant = 300.0 * ((m * nb + kThreads / 64 - 1) / (kThreads / 64));
+    // measured on the Llama-3-8B shapes: cheaper-looking models that cut the small launches into 14-16
+    // slices made the whole decode step 25 % slower, so folding is priced per item and per slice
+    const double fold = kb > 1 ? (double)ipw * 80.0 + 16.0 * kb : 0.0;
+    return stream + quant + fold;
 }
 
 int qmatvec_plan_slices(int type, int64_t k, int m, int64_t tiles, int max_slices)
@@ -289,6 +377,8 @@ static tlb_status launch_fmt(const MvParams &p, int grid, size_t smem, bool pdl)
     static size_t set_bytes = 0;
     if (smem > set_bytes) {
         TLB_CUDA(cudaFuncSetAttribute(qmatvec_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // always the largest shared-memory split, whatever this launch needs: SMs do not re-partition between launches
+        TLB_CUDA(cudaFuncSetAttribute(qmatvec_kernel<FMT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         set_bytes = smem;
     }
     cudaLaunchConfig_t cfg = {};
@@ -332,7 +422,6 @@ tlb_status launch_qmatvec(const MatvecJob &job)
             tiles += job.n_tiles[i];
             p.w[i] = job.w[i];
             p.out[i] = job.out[i];
-            p.out_stride[i] = job.out_stride[i];
             p.n_rows[i] = (int)job.n_rows[i];
         }
         p.tiles_end[i] = (int)tiles;
@@ -343,18 +432,32 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.k = (int)job.k;
     p.m = job.m;
     p.nl = job.m <= 2 ? 3 : 2;
-    p.kb = job.slices;
-    if (p.kb < 1 || p.kb > kMaxSlices || p.upt % p.kb) return fail(TLB_ERR_ARG, "%d slices do not divide the %d units of K", p.kb, p.upt);
+    if (tiles > INT32_MAX / (64 * kMaxSlices)) return fail(TLB_ERR_SHAPE, "too many tiles for one launch");
+    // K-slices: as many as the cost model likes and the slice scratch and tile counters hold
+    int max_slices = kMaxSlices;
+    if (tiles > (int64_t)c->mv_cnt_n) max_slices = 1;
+    while (max_slices > 1 && (size_t)max_slices * tiles * 16 * job.m > c->mv_part_floats) max_slices--;
+    p.kb = job.slices > 0 ? std::min(job.slices, max_slices) : qmatvec_plan_slices(job.type, job.k, job.m, tiles, max_slices);
+    if (p.kb < 1 || p.upt % p.kb) return fail(TLB_ERR_ARG, "%d slices do not divide the %d units of K", p.kb, p.upt);
     p.upi = p.upt / p.kb;
-    if (tiles * p.kb > INT32_MAX / 64) return fail(TLB_ERR_SHAPE, "too many items for one launch");
+    p.part = c->mv_part;
+    p.tile_cnt = c->mv_cnt;
     p.tiles = (int)tiles;
     p.n_items = (int)(tiles * p.kb);
     p.unit_bytes = f->unit_bytes;
     p.stage_bytes = stage_bytes_of(f);
-    const int grid = (int)std::min<int64_t>(c->sm_count, p.n_items);
+    const int grid = (int)std::min<int64_t>((int64_t)c->sm_count * kCtasPerSm, p.n_items);
+    p.ipc_q = p.n_items / grid;
+    p.ipc_r = p.n_items % grid;
     p.nb_max = blocks_per_cta(p.n_items, grid, tiles, p.upi, p.upt);
     const SmemPlan sp = plan_smem(job.type, job.m, p.nl, p.nb_max);
-    const size_t budget = c->smem_optin;
+    // Shared memory per CTA: a third of the SM (1 KB per CTA is reserved by the system), so that a CTA of
+    // the next kernel can be resident beside this launch's two; a launch nothing worthwhile follows may
+    // take half, and a shape whose tables need more takes what it needs.
+    const size_t sm_total = c->smem_optin + 1024;
+    size_t budget = sm_total / (job.last_of_chain ? kCtasPerSm : kResidentPerSm) - 1024;
+    if (sp.fixed + 128 + 2 * (size_t)kWarps * (p.stage_bytes + 8) > budget) budget = sm_total / kCtasPerSm - 1024;
+    if (sp.fixed + 128 + 2 * (size_t)kWarps * (p.stage_bytes + 8) > budget) budget = c->smem_optin;
     const size_t per_stage = (size_t)kWarps * (p.stage_bytes + 8);
     if (sp.fixed + 128 + 2 * per_stage > budget)
         return fail(TLB_ERR_SHAPE, "K = %lld with %d rows needs more shared memory than one SM has (max K %zu)",
@@ -381,6 +484,7 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.err = c->err_flag;
     p.use_pdl = job.pdl ? 1 : 0;
     p.trace = job.trace;
+    p.span = job.span;
     if (!p.x.p && !(p.prologue == PRO_ADD_NORM && p.token)) return fail(TLB_ERR_NULL, "null activation");
     if (p.prologue == PRO_SILU_MUL && !p.x2.p) return fail(TLB_ERR_NULL, "null activation");
     switch (job.type) {
@@ -411,32 +515,19 @@ extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, 
     TLB_TRY(new_tensor(out, TLB_F32, oshape, x->rank));
     if (m * w->n == 0) return TLB_OK;
     tlb_status st = TLB_OK;
-    Storage *scratch = nullptr;   // the K-slices of one group of 4 rows, summed into the result afterwards
     for (int64_t m0 = 0; m0 < m && st == TLB_OK; m0 += 4) {   // the weight stream is repeated per group of 4 rows
         MatvecJob job;
         job.n_w = 1;
         job.w[0] = w->dev();
         job.n_tiles[0] = w->n_tiles;
         job.n_rows[0] = w->n;
+        job.out[0] = (*out)->f32() + m0 * w->n;
         job.type = w->type;
         job.k = k;
         job.m = (int)std::min<int64_t>(4, m - m0);
-        job.slices = qmatvec_plan_slices(w->type, k, job.m, w->n_tiles, kMaxSlices);
-        float *dst = (*out)->f32() + m0 * w->n;
-        if (job.slices > 1) {
-            if (!scratch) scratch = storage_alloc((size_t)kMaxSlices * 4 * w->n * sizeof(float));
-            if (!scratch) { st = TLB_ERR_ALLOC; break; }
-            job.out[0] = (float *)scratch->ptr;
-            job.out_stride[0] = (int64_t)job.m * w->n;
-        } else {
-            job.out[0] = dst;
-        }
         job.x.p = x->f32() + m0 * k;
         st = launch_qmatvec(job);
-        if (st == TLB_OK && job.slices > 1)
-            st = launch_sum_slices((const float *)scratch->ptr, job.slices, job.out_stride[0], dst, (int64_t)job.m * w->n);
     }
-    if (scratch) storage_release(scratch);   // stream-ordered: freed after the kernels above have run
     if (st != TLB_OK) { tlb_tensor_release(*out); *out = nullptr; }
     return st;
 }

@@ -151,8 +151,9 @@ __device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1,
 
 struct MvParams {
     const uint8_t *w[3];
-    float *out[3];            // slice s of tensor i is stored at out[i] + s * out_stride[i], laid out [m][n_rows]
-    long long out_stride[3];
+    float *out[3];            // [m][n_rows] per tensor
+    float *part;              // slice scratch [kb][tiles][m][16] (kb > 1): the partial result of every item
+    int *tile_cnt;            // [tiles] slices of a tile finished so far; zero between launches
     int tiles_end[3];         // cumulative tile counts
     int n_rows[3];            // valid output rows per tensor
     int n_w;
@@ -163,11 +164,13 @@ struct MvParams {
     // Work decomposition.  An ITEM is one tile (16 rows) x one K-slice of `upi` consecutive units; item
     // index = slice * tiles + tile (slice-major), so the contiguous item range of a CTA touches one or two
     // slices and needs only those blocks of the activation.  One warp owns an item from the first byte to
-    // the stored result: out[slice][m][row] is WRITTEN, never added to, by exactly one warp.
+    // its 16 * m partial results, which it WRITES (never adds) to part[slice][tile]; the warp that
+    // finishes a tile's last slice adds the slices in index order into the output.
     int upi;                  // units per item (divides upt)
     int kb;                   // K-slices = output slices = upt / upi
     int tiles;                // tiles of the launch (all tensors)
     int n_items;              // kb * tiles
+    int ipc_q, ipc_r;         // n_items = grid * ipc_q + ipc_r: CTA b takes ipc_q (+1 if b < ipc_r) consecutive items
     int nb_max;               // 256-blocks of activation a CTA may need: the shared tables are sized for it
     int unit_bytes, stage_bytes;
     int spw;                  // ring stages private to each warp
@@ -182,6 +185,7 @@ struct MvParams {
     int *err;
     int use_pdl;
     long long *trace;         // optional: [grid][10] stamps of thread 0 of every CTA (timing studies)
+    unsigned long long *span; // optional: [4] launch-wide timeline stamps (span_trace.cuh)
     // shared-memory offsets (bytes from the start of dynamic shared memory)
     int off_xq, off_alam, off_xsum, off_sa, off_minv, off_bars, off_misc;
     int col_stride;           // bytes between int8 activation columns (nb_max * 256 + 64)

@@ -23,11 +23,9 @@ namespace tlb {
 // Quantises block (mrow, blk) with a group of 64 threads (index j in the group) into the shared tables
 // at local block index lb.
 template <int FMT>
-__device__ __forceinline__ void quantise_block(const MvParams &p, const float *emb, uint8_t *smem, float *pair_max,
-                                               int mrow, int blk, int lb, int j, int lane, float inv_rms, int pair_bar)
+__device__ __forceinline__ void quantise_block(const MvParams &p, uint8_t *smem, float *pair_max, const float4 v,
+                                               int mrow, int lb, int j, int lane, int pair_bar)
 {
-    const int k4 = blk * 64 + j;
-    const float4 v = prologue_value(p, emb, mrow, k4, inv_rms);
     float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) pair_max[j >> 5] = mx;
@@ -122,44 +120,91 @@ __device__ __forceinline__ void quantise_block(const MvParams &p, const float *e
 
 // Fills the shared tables for activation blocks [blk0, blk0 + nb) of every row.  All `nthreads`
 // threads of the CTA call it; it ends with a CTA-wide barrier.
-template <int FMT>
-__device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem, int tid, int nthreads, int blk0, int nb)
+//
+// Groups of 64 threads take one block each.  Everything a group needs from global memory is
+// requested up front - the values of its own blocks (kept in registers), their norm weights, and
+// for the fused RMSNorm its share of the REST of the row, which enters only the sum of squares - so
+// the prologue costs one round trip to L2, not one per step.
+//
+// `after_loads(dep)` is called once per thread when the values it requested have arrived (dep is
+// computed from them): the caller uses it to start traffic that should not delay those loads.
+template <int FMT, typename AfterLoads>
+__device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem, int tid, int nthreads, int blk0, int nb,
+                                 AfterLoads after_loads)
 {
+    constexpr int kKeep = 2;   // blocks per group handled in one pass
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
-    const int k4n = p.k / 4;
+    const int ngroups = nthreads >> 6, grp = tid >> 6, j = tid & 63;
+    const int nblk = p.k / 256, n_mine = p.m * nb;
+    const bool norm = p.prologue == PRO_ADD_NORM;
     const float *emb = nullptr;
-    if (p.prologue == PRO_ADD_NORM && p.token) emb = p.emb_table + (size_t)__ldg(p.token) * p.k;
+    if (norm && p.token) emb = p.emb_table + (size_t)__ldg(p.token) * p.k;
 
-    // RMSNorm statistic over the whole row: every CTA sums the squares itself
     float inv_rms = 0.f;
-    if (p.prologue == PRO_ADD_NORM) {
-        constexpr int kBatch = 2;   // loads issued in batches so that their latencies overlap
+    for (int first = 0; first < n_mine || (norm && first == 0); first += ngroups * kKeep) {
+        float4 keep[kKeep], wgt[kKeep];
         float ssq = 0.f;
-        for (int base = tid; base < k4n; base += nthreads * kBatch) {
-            float4 vv[kBatch];
 #pragma unroll
-            for (int j = 0; j < kBatch; j++)
-                if (base + j * nthreads < k4n) vv[j] = prologue_value(p, emb, 0, base + j * nthreads, 0.f);
-#pragma unroll
-            for (int j = 0; j < kBatch; j++)
-                if (base + j * nthreads < k4n) {
-                    const float4 v = vv[j];
-                    ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                    if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out)[base + j * nthreads] = v;
-                }
+        for (int i = 0; i < kKeep; i++) {
+            const int item = first + grp + i * ngroups;
+            if (item < n_mine) {
+                const int mrow = item / nb, lb = item - mrow * nb, k4 = (blk0 + lb) * 64 + j;
+                keep[i] = prologue_value(p, emb, mrow, k4, 0.f);
+                if (norm) wgt[i] = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + k4);
+            }
         }
-        for (int o = 16; o; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-        if (lane == 0) sh->red_sum[warp] = ssq;
-        __syncthreads();
-        ssq = 0.f;
-        for (int w = 0; w < nwarps; w++) ssq += sh->red_sum[w];
-        inv_rms = 1.f / sqrtf(ssq / (float)p.k + p.eps);
-    }
-    // groups of 64 threads, one block each
-    const int ngroups = nthreads >> 6, grp = tid >> 6;
-    for (int item = grp; item < p.m * nb; item += ngroups) {
-        const int mrow = item / nb, lb = item - mrow * nb;
-        quantise_block<FMT>(p, emb, smem, &sh->red_max[grp * 2], mrow, blk0 + lb, lb, tid & 63, lane, inv_rms, 2 + grp);
+        if (norm && first == 0) {
+            // the blocks outside [blk0, blk0 + nb): only their squares are needed (m == 1 with this prologue)
+            for (int o = grp; o < nblk - nb; o += ngroups) {
+                const int k4 = (o < blk0 ? o : o + nb) * 64 + j;
+                const float4 v = prologue_value(p, emb, 0, k4, 0.f);
+                ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out)[k4] = v;
+            }
+            for (int it = grp; it < n_mine; it += ngroups) {   // own blocks beyond the first pass, if any
+                if (it < ngroups * kKeep) continue;
+                const int k4 = (blk0 + it) * 64 + j;
+                const float4 v = prologue_value(p, emb, 0, k4, 0.f);
+                ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out)[k4] = v;
+            }
+#pragma unroll
+            for (int i = 0; i < kKeep; i++) {
+                const int item = grp + i * ngroups;
+                if (item < n_mine) {
+                    const float4 v = keep[i];
+                    ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                    if (p.x_out && blockIdx.x == 0) reinterpret_cast<float4 *>(p.x_out)[(blk0 + item) * 64 + j] = v;
+                }
+            }
+            after_loads(ssq);
+            for (int o = 16; o; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+            if (lane == 0) sh->red_sum[warp] = ssq;
+            __syncthreads();
+            ssq = 0.f;
+            for (int w = 0; w < nwarps; w++) ssq += sh->red_sum[w];
+            inv_rms = 1.f / sqrtf(ssq / (float)p.k + p.eps);
+        }
+        if (!norm && first == 0) {
+            float dep = 0.f;
+#pragma unroll
+            for (int i = 0; i < kKeep; i++)
+                if (grp + i * ngroups < n_mine) dep += keep[i].x;
+            after_loads(dep);
+        }
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+            const int item = first + grp + i * ngroups;
+            if (item < n_mine) {
+                const int mrow = item / nb, lb = item - mrow * nb;
+                float4 v = keep[i];
+                if (norm) {   // (x / rms) * weight (crates/tl_cpu/src/ffi.rs:2444-2486), the division as a multiply by 1/rms
+                    v.x = (v.x * inv_rms) * wgt[i].x; v.y = (v.y * inv_rms) * wgt[i].y;
+                    v.z = (v.z * inv_rms) * wgt[i].z; v.w = (v.w * inv_rms) * wgt[i].w;
+                }
+                quantise_block<FMT>(p, smem, &sh->red_max[grp * 2], v, mrow, lb, j, lane, 2 + grp);
+            }
+        }
     }
     __syncthreads();
 }

@@ -56,6 +56,11 @@ static tlb_status do_init(int device)
     TLB_CUDA(cudaMemPoolSetAttribute(g_ctx.pool, cudaMemPoolAttrReleaseThreshold, &thresh));
     TLB_CUDA(cudaMalloc(&g_ctx.err_flag, sizeof(int)));
     TLB_CUDA(cudaMemset(g_ctx.err_flag, 0, sizeof(int)));
+    g_ctx.mv_part_floats = (size_t)12 << 20;   // 48 MB: 16 slices of a 128k-row head with 3 activation rows
+    TLB_CUDA(cudaMalloc(&g_ctx.mv_part, g_ctx.mv_part_floats * sizeof(float)));
+    g_ctx.mv_cnt_n = (size_t)1 << 20;
+    TLB_CUDA(cudaMalloc(&g_ctx.mv_cnt, g_ctx.mv_cnt_n * sizeof(int)));
+    TLB_CUDA(cudaMemset(g_ctx.mv_cnt, 0, g_ctx.mv_cnt_n * sizeof(int)));
     g_inited = true;
     return TLB_OK;
 }
@@ -182,6 +187,7 @@ tlb_status tlb_sync(void)
     TLB_CUDA(cudaMemcpy(&flag, g_ctx.err_flag, sizeof(int), cudaMemcpyDeviceToHost));
     if (flag) {
         cudaMemset(g_ctx.err_flag, 0, sizeof(int));
+        cudaMemset(g_ctx.mv_cnt, 0, g_ctx.mv_cnt_n * sizeof(int));   // an abandoned launch may have left counts behind
         return fail(TLB_ERR_DEVICE, "a kernel gave up a bounded wait (code %d)", flag);
     }
     return TLB_OK;

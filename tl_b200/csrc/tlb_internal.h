@@ -31,6 +31,12 @@ struct Context {
     void *flush_buf = nullptr;
     size_t flush_bytes = 0;
     int *err_flag = nullptr;  // device word set by kernels whose bounded waits ran out
+    // scratch of the streaming matvec (launches are ordered on `stream`, so one set serves all):
+    // partial results per K-slice, and per-tile counts of finished slices (zero between launches)
+    float *mv_part = nullptr;
+    size_t mv_part_floats = 0;
+    int *mv_cnt = nullptr;
+    size_t mv_cnt_n = 0;
     bool capturing = false;
     uint64_t capture_launches = 0;
 };
@@ -125,11 +131,10 @@ struct MatvecJob {
     const uint8_t *w[3] = {nullptr, nullptr, nullptr};
     int64_t n_tiles[3] = {0, 0, 0};
     int64_t n_rows[3] = {0, 0, 0};                 // valid output rows (<= n_tiles*16)
-    // Output of tensor i: `slices` arrays [M, n_rows] spaced out_stride[i] floats apart, every element
-    // of every slice written (no clearing needed); the logical result is their sum.
+    // Output of tensor i: [M, n_rows], every element written (no clearing needed).
     float *out[3] = {nullptr, nullptr, nullptr};
     int64_t out_stride[3] = {0, 0, 0};
-    int slices = 1;                  // from qmatvec_plan_slices() for this shape
+    int slices = 0;                  // K-slices the launch is cut into; 0: chosen by qmatvec_plan_slices()
     int type = 0;
     int64_t k = 0;
     int m = 1;
@@ -143,7 +148,9 @@ struct MatvecJob {
     const float *emb_table = nullptr; // ADD_NORM with token lookup: x = emb_table[*token * K ...]
     const int *token = nullptr;
     bool pdl = false;                // launch with programmatic stream serialization
+    bool last_of_chain = false;      // no matvec follows closely: take half an SM's shared memory instead of a third
     long long *trace = nullptr;      // optional device buffer [grid][10] of stamps (timing studies)
+    unsigned long long *span = nullptr;   // optional device buffer [4]: timeline of the launch (span_trace.cuh)
 };
 tlb_status launch_qmatvec(const MatvecJob &job);
 // K-slices the kernel wants for a launch of `tiles` 16-row tiles (all tensors) over inner dimension k,
@@ -191,6 +198,7 @@ struct DecodeAttnJob {
     int splits;
     float *out;            // [H*D]
     bool pdl;
+    unsigned long long *span = nullptr;   // optional timeline of the launch (span_trace.cuh)
 };
 tlb_status launch_decode_attention(const DecodeAttnJob &j);
 tlb_status launch_sdpa(const float *q, const float *k, const float *v, const float *mask, int mask_mode,
