@@ -546,9 +546,9 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
             const unsigned long long *t = &h[(size_t)i * 8];
             const int kind = i == nk - 1 ? 5 : i % 5;
             if (i < 10 || i >= nk - 6)
-                fprintf(stderr, "[tlb chain] %3d %-8s start %9.2f (last %9.2f, set up %9.2f)  waited %9.2f  prologue %9.2f  end %9.2f   (us)\n", i,
+                fprintf(stderr, "[tlb chain] %3d %-8s start %9.2f (last %9.2f, set up %9.2f)  waited %9.2f  (loads %9.2f, norm %9.2f) prologue %9.2f  end %9.2f   (us)\n", i,
                         kind == 5 ? "head" : names[kind], (t[0] - t0) / 1e3, t[4] ? (t[4] - t0) / 1e3 : 0.0, t[5] ? (t[5] - t0) / 1e3 : 0.0,
-                        (t[1] - t0) / 1e3, (t[2] - t0) / 1e3, (t[3] - t0) / 1e3);
+                        (t[1] - t0) / 1e3, t[6] ? (t[6] - t0) / 1e3 : 0.0, t[7] ? (t[7] - t0) / 1e3 : 0.0, (t[2] - t0) / 1e3, (t[3] - t0) / 1e3);
             busy[kind] += (t[3] - std::max(t[1], prev_end)) / 1e3;   // from (dependency met) to end
             gap[kind] += ((double)std::max(t[1], prev_end) - (double)prev_end) / 1e3;
             prev_end = t[3];

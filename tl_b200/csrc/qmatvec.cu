@@ -105,7 +105,10 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
     // Only the first kEarly units are requested before the prologue: the activation loads of the
     // prologue share the SM's path from L2 with these copies and would otherwise queue behind a whole
     // ring of weights.  The rest of the ring is requested once the activation values have arrived.
-    constexpr int kEarly = 2;
+#ifndef TLB_EARLY
+#define TLB_EARLY 2
+#endif
+    constexpr int kEarly = TLB_EARLY;
     const int n_first = min(spw, n_units);
     const uint8_t *first_src = nullptr;
     if (lane < spw) {
@@ -173,7 +176,6 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
     {
         const int r = L.r, c = L.c;
         const int colr = r < ncols ? r : 0, c0 = 2 * c < ncols ? 2 * c : 0, c1 = 2 * c + 1 < ncols ? 2 * c + 1 : 0;
-        L.bvalid = r < ncols;
         L.xq_b = smem_u32(smem + p.off_xq) + colr * p.col_stride;
         L.alam_b = smem_u32(smem + p.off_alam) + 2 * c * 4;
         L.xsum_b = smem_u32(smem + p.off_xsum) + ((r < 2 * p.m) ? r : (r & 1)) * (p.nb_max * 8) * 2;
@@ -190,17 +192,38 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         const ItemRef ir = item_ref(p, cur);
         const int lb0 = ir.slice * p.upi - blk0;
         float master[4] = {0.f, 0.f, 0.f, 0.f}, mm[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int uo = 0; uo < p.upi; uo++) {
+        int uo = 0;
+        // two units per trip: the two bodies are independent, so one warp has two instruction streams
+        // to interleave, and the loop bookkeeping is paid once
+        for (; uo + 1 < p.upi; uo += 2) {
+            const int st1 = stage + 1 == spw ? 0 : stage + 1, ph1 = stage + 1 == spw ? phase ^ 1 : phase;
             bool got = mbar_try_wait(bars + stage * 8, phase);
             if (!got) got = mbar_wait_slow(bars + stage * 8, phase, abortp, p.err, 2);
-            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }   // warp-uniform: all lanes leave together
-            if (consumed == 0 && warp == 0) STAMP(4);
+            bool got1 = mbar_try_wait(bars + st1 * 8, ph1);
+            if (!got1) got1 = mbar_wait_slow(bars + st1 * 8, ph1, abortp, p.err, 2);
+            if (!__all_sync(0xffffffffu, got && got1)) { ok = false; break; }   // warp-uniform: all lanes leave together
             process_unit<FMT>(ring + stage * p.stage_bytes, lb0 + uo, L, master, mm);
-            if (consumed == 0 && warp == 0) STAMP(5);
-            consumed++;
-            __syncwarp();          // every lane has read the stage: it may be overwritten
-            if (lane == 0 && pf_remaining > 0) issue_copy(stage);
-            if (++stage == spw) { stage = 0; phase ^= 1; }
+            process_unit<FMT>(ring + st1 * p.stage_bytes, lb0 + uo + 1, L, master, mm);
+            consumed += 2;
+            __syncwarp();          // every lane has read the stages: they may be overwritten
+            if (lane == 0) {
+                if (pf_remaining > 0) issue_copy(stage);
+                if (pf_remaining > 0) issue_copy(st1);
+            }
+            stage = st1 + 1 == spw ? 0 : st1 + 1;
+            phase = st1 + 1 == spw ? ph1 ^ 1 : ph1;
+        }
+        if (ok && uo < p.upi) {
+            bool got = mbar_try_wait(bars + stage * 8, phase);
+            if (!got) got = mbar_wait_slow(bars + stage * 8, phase, abortp, p.err, 2);
+            if (!__all_sync(0xffffffffu, got)) ok = false;
+            else {
+                process_unit<FMT>(ring + stage * p.stage_bytes, lb0 + uo, L, master, mm);
+                consumed++;
+                __syncwarp();
+                if (lane == 0 && pf_remaining > 0) issue_copy(stage);
+                if (++stage == spw) { stage = 0; phase ^= 1; }
+            }
         }
         if (!ok) break;
         // Fold the level columns of each activation row (they sit in the four lanes of a quad).  The

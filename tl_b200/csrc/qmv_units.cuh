@@ -19,11 +19,13 @@ struct LaneCtx {
     uint32_t sa_b;     // Q6_K: f16 level sums of column r (clamped)
     uint32_t sa_c0, sa_c1;  // Q4_0: int32 level sums of columns 2c and 2c+1 (clamped)
     uint32_t minv_b;   // Q4_K: inverse power-of-two scale of the sub-block sums of activation row c (clamped)
-    bool bvalid;       // MMA column r carries a level: lanes of unused columns feed zeros and skip the shared loads
 };
 
-__device__ __forceinline__ uint4 ldb128(const LaneCtx &L, uint32_t a) { return L.bvalid ? lds128(a) : make_uint4(0u, 0u, 0u, 0u); }
-__device__ __forceinline__ uint2 ldb64(const LaneCtx &L, uint32_t a) { return L.bvalid ? lds64(a) : make_uint2(0u, 0u); }
+// B-operand loads.  Lanes whose MMA column carries no level read column 0 instead (xq_b is clamped):
+// same address as the lanes of column 0, so the load costs no extra shared-memory wavefront, and
+// what those columns accumulate is multiplied by alam == 0 at the end.
+__device__ __forceinline__ uint4 ldb128(const LaneCtx &, uint32_t a) { return lds128(a); }
+__device__ __forceinline__ uint2 ldb64(const LaneCtx &, uint32_t a) { return lds64(a); }
 
 #define NIB 0x0F0F0F0Fu
 #define NIBH 0xF0F0F0F0u
