@@ -22,6 +22,7 @@ using namespace tlb;
 struct LayerW {
     tlb_qtensor *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
     tlb_tensor *attn_norm = nullptr, *ffn_norm = nullptr;
+    tlb_qtensor *gu = nullptr;   // gate and up interleaved by groups of 8 rows (launch_interleave8): [2 * ffn, d_model]
 };
 
 struct tlb_decoder {
@@ -41,6 +42,8 @@ struct tlb_decoder {
     long long *amax_i = nullptr;
     int *h_state = nullptr;      // pinned host staging [4]
     float *logits_sl = nullptr;  // K-slices of the head matvec; `logits` holds their sum after the argmax kernel
+    float *hbuf = nullptr;       // silu(gate) * up, written by the gate|up launch
+    float *ssq_o = nullptr, *ssq_d = nullptr;   // per-tile sums of squares of the residual after o_proj / down
     int s_qkv = 1, s_o = 1, s_gu = 1, s_down = 1, s_head = 1;   // K-slices of each matvec of the chain
     int max_splits = 1;
     cudaGraphExec_t graph = nullptr;
@@ -180,9 +183,9 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             j.type = w.q->type; j.k = dm; j.m = 1;
             j.prologue = PRO_ADD_NORM;
             j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
-            if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; }
-            else { j.x = sliced(d->xa, 1, 0); j.x2 = sliced(d->down_out, d->s_down, dm); }
-            j.x_out = d->xb;
+            // the residual lives in xb here: the embedding row for layer 0, else what the last down launch left
+            if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; j.x_out = d->xb; }
+            else { j.x = sliced(d->xb, 1, 0); j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16; }
             j.pdl = d->pdl;
             j.span = next_span();
             TLB_TRY(launch_qmatvec(j));
@@ -201,24 +204,22 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         {   // K3
             MatvecJob j;
             j.n_w = 1;
-            set_w(j, 0, w.o, d->o_out, dm);
-           
+            set_w(j, 0, w.o, d->xa, dm);
             j.type = w.o->type; j.k = qd; j.m = 1;
             j.prologue = PRO_PLAIN; j.x = sliced(d->attn, 1, 0);
+            j.finish = FIN_RESID; j.resid = d->xb; j.ssq_out = d->ssq_o;   // xa = xb + o_proj(attn)
             j.pdl = d->pdl;
             j.span = next_span();
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K4
             MatvecJob j;
-            j.n_w = 2;
-            set_w(j, 0, w.gate, d->gu, 2 * (int64_t)F);
-            set_w(j, 1, w.up, d->gu + F, 2 * (int64_t)F);
-           
-            j.type = w.gate->type; j.k = dm; j.m = 1;
-            j.prologue = PRO_ADD_NORM; j.x = sliced(d->xb, 1, 0); j.x2 = sliced(d->o_out, d->s_o, dm);
+            j.n_w = 1;
+            set_w(j, 0, w.gu, d->hbuf, F);
+            j.type = w.gu->type; j.k = dm; j.m = 1;
+            j.prologue = PRO_ADD_NORM; j.x = sliced(d->xa, 1, 0); j.ssq_parts = d->ssq_o; j.n_parts = (dm + 15) / 16;
             j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
-            j.x_out = d->xa;
+            j.finish = FIN_SILU;
             j.pdl = d->pdl;
             j.span = next_span();
             TLB_TRY(launch_qmatvec(j));
@@ -226,11 +227,10 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         {   // K5
             MatvecJob j;
             j.n_w = 1;
-            set_w(j, 0, w.down, d->down_out, dm);
-           
+            set_w(j, 0, w.down, d->xb, dm);
             j.type = w.down->type; j.k = F; j.m = 1;
-            j.prologue = PRO_SILU_MUL;
-            j.x = sliced(d->gu, d->s_gu, 2 * (int64_t)F); j.x2 = sliced(d->gu + F, d->s_gu, 2 * (int64_t)F);
+            j.prologue = PRO_PLAIN; j.x = sliced(d->hbuf, 1, 0);
+            j.finish = FIN_RESID; j.resid = d->xa; j.ssq_out = d->ssq_d;   // xb = xa + down(h)
             j.pdl = d->pdl;
             j.span = next_span();
             TLB_TRY(launch_qmatvec(j));
@@ -240,11 +240,9 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         MatvecJob j;
         j.n_w = 1;
         set_w(j, 0, d->head, d->logits_sl, c.vocab);
-       
         j.type = d->head->type; j.k = dm; j.m = 1;
-        j.prologue = PRO_ADD_NORM; j.x = sliced(d->xa, 1, 0); j.x2 = sliced(d->down_out, d->s_down, dm);
+        j.prologue = PRO_ADD_NORM; j.x = sliced(d->xb, 1, 0); j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16;
         j.norm_w = d->out_norm->f32(); j.eps = c.eps;
-        j.x_out = d->xb;
         j.last_of_chain = true;
         j.pdl = d->pdl;
         j.span = next_span();
@@ -313,7 +311,7 @@ tlb_status tlb_decoder_destroy(tlb_decoder *d)
     if (d->graph) cudaGraphExecDestroy(d->graph);
     for (LayerW &w : d->layers) {
         tlb_qtensor_release(w.q); tlb_qtensor_release(w.k); tlb_qtensor_release(w.v); tlb_qtensor_release(w.o);
-        tlb_qtensor_release(w.gate); tlb_qtensor_release(w.up); tlb_qtensor_release(w.down);
+        tlb_qtensor_release(w.gate); tlb_qtensor_release(w.up); tlb_qtensor_release(w.down); tlb_qtensor_release(w.gu);
         tlb_tensor_release(w.attn_norm); tlb_tensor_release(w.ffn_norm);
     }
     tlb_tensor_release(d->emb); tlb_tensor_release(d->out_norm); tlb_qtensor_release(d->head);
@@ -372,15 +370,24 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
                 tlb_decoder_destroy(d);
                 return fail(TLB_ERR_TYPE, "all layers must use the same GGML type per projection");
             }
-        if (dm % 4 || F % 4 || (qd + 2 * kvd) % 4) {
+        if (dm % 4 || F % 16 || (qd + 2 * kvd) % 4) {
             tlb_decoder_destroy(d);
-            return fail(TLB_ERR_SHAPE, "model widths must be multiples of 4");
+            return fail(TLB_ERR_SHAPE, "d_model and the q|k|v width must be multiples of 4, ffn a multiple of 16");
+        }
+        // gate | up of every layer, interleaved by groups of 8 rows into one tensor of its own
+        for (LayerW &w : d->layers) {
+            tlb_qtensor *g = new tlb_qtensor();
+            g->type = w.gate->type; g->n = 2 * F; g->k = dm; g->n_tiles = 2 * F / 16; g->upt = dm / 256;
+            g->st = storage_alloc((size_t)g->nbytes());
+            w.gu = g;
+            if (!g->st) { tlb_decoder_destroy(d); return TLB_ERR_ALLOC; }
+            TRY_D(launch_interleave8(g->type, w.gate->dev(), w.up->dev(), g->dev(), F, dm));
         }
     }
     TRY_D(dalloc(d, &d->xa, dm)); TRY_D(dalloc(d, &d->xb, dm));
     TRY_D(dalloc(d, &d->qkv, (size_t)d->s_qkv * (qd + 2 * kvd))); TRY_D(dalloc(d, &d->attn, qd));
-    TRY_D(dalloc(d, &d->o_out, (size_t)d->s_o * dm)); TRY_D(dalloc(d, &d->gu, (size_t)d->s_gu * 2 * F));
-    TRY_D(dalloc(d, &d->down_out, (size_t)d->s_down * dm));
+    TRY_D(dalloc(d, &d->hbuf, F));
+    TRY_D(dalloc(d, &d->ssq_o, (dm + 15) / 16)); TRY_D(dalloc(d, &d->ssq_d, (dm + 15) / 16));
     TRY_D(dalloc(d, &d->logits_sl, (size_t)d->s_head * c.vocab)); TRY_D(dalloc(d, &d->logits, c.vocab));
     d->kv_layer_elems = (size_t)kvd * c.max_seq;
     size_t kv_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
@@ -592,8 +599,8 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         } else if (w == "o") {
             j.n_w = 1; set_w(j, 0, lw.o, o, out_n); j.type = lw.o->type; j.k = qd; bytes = lw.o->nbytes();
         } else if (w == "gate_up") {
-            j.n_w = 2; set_w(j, 0, lw.gate, o, out_n); set_w(j, 1, lw.up, o + F, out_n); j.type = lw.gate->type; j.k = dm;
-            bytes = lw.gate->nbytes() + lw.up->nbytes();
+            j.n_w = 1; set_w(j, 0, lw.gu, o, out_n); j.type = lw.gu->type; j.k = dm; j.finish = FIN_SILU;
+            bytes = lw.gu->nbytes();
         } else if (w == "down") {
             j.n_w = 1; set_w(j, 0, lw.down, o, out_n); j.type = lw.down->type; j.k = F; bytes = lw.down->nbytes();
         } else {

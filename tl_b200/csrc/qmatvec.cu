@@ -77,6 +77,35 @@ __device__ __forceinline__ ItemRef item_ref(const MvParams &p, const ItemCursor 
     return r;
 }
 
+// The fused ways of finishing a tile (one activation row, one tensor).  Lane e < 16 holds the
+// result y of row e of the tile; all 32 lanes call.
+//   FIN_RESID  out[row] = resid[row] + y; the squares of the 16 sums, added in a fixed tree, go to
+//              ssq_out[tile]: the next RMSNorm adds the tiles instead of re-reading the row
+//              (crates/tl_cpu/src/ffi.rs:2444-2486 sums the squares of the whole row).
+//   FIN_SILU   rows 0..7 are gate and rows 8..15 up of hidden units 8*tile .. 8*tile+7:
+//              out[8*tile + e] = silu(gate) * up (crates/tl_cpu/src/ffi.rs:2083-2103 then an elementwise mul).
+__device__ __forceinline__ void finish_tile_fused(const MvParams &p, const ItemRef &fr, float y, int lane)
+{
+    float *out = p.out[0];
+    const int nrows = p.n_rows[0];
+    if (p.finish == FIN_RESID) {
+        const int g = fr.row0 + lane;
+        const bool valid = lane < 16 && g < nrows;
+        const float xn = valid ? __ldcg(p.resid + g) + y : 0.f;
+        if (valid) out[g] = xn;
+        float s = xn * xn;
+        s += __shfl_xor_sync(0xffffffffu, s, 8);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        if (lane == 0) p.ssq_out[fr.tile] = s;
+    } else {   // FIN_SILU
+        const float up = __shfl_down_sync(0xffffffffu, y, 8);
+        const int h = fr.tile * 8 + lane;
+        if (lane < 8 && 2 * h < nrows) out[h] = silu_f(y) * up;
+    }
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const __grid_constant__ MvParams p)
 {
@@ -241,14 +270,19 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
             if (L.c == mi) {
                 if (FMT == TLB_GGML_Q4_K) { v0 -= mm[0] + mm[1]; v1 -= mm[2] + mm[3]; }
-                if (p.kb == 1) {
+                if (p.kb > 1) {
+                    part[mi * 16 + L.r] = v0;
+                    part[mi * 16 + L.r + 8] = v1;
+                } else if (p.finish == FIN_PLAIN) {
                     const int g0 = ir.row0 + L.r, g1 = g0 + 8;
                     if (g0 < nrows) out[(size_t)mi * nrows + g0] = v0;
                     if (g1 < nrows) out[(size_t)mi * nrows + g1] = v1;
-                } else {
-                    part[mi * 16 + L.r] = v0;
-                    part[mi * 16 + L.r + 8] = v1;
                 }
+            }
+            if (p.kb == 1 && p.finish != FIN_PLAIN) {   // m == 1: bring row e to lane e and finish the tile
+                const int srcl = (lane & 7) * 4;
+                const float a0 = __shfl_sync(0xffffffffu, v0, srcl), a1 = __shfl_sync(0xffffffffu, v1, srcl);
+                finish_tile_fused(p, ir, lane < 8 ? a0 : a1, lane);
             }
         }
     }
@@ -276,11 +310,20 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
                 const int nrows = p.n_rows[fr.wi];
                 const float *src = p.part + (size_t)fr.tile * (16 * p.m);
                 const size_t sstride = (size_t)p.tiles * (16 * p.m);
-                for (int e = lane; e < 16 * p.m; e += 32) {
-                    float a = __ldcg(src + e);
-                    for (int s = 1; s < p.kb; s++) a += __ldcg(src + s * sstride + e);
-                    const int mi = e >> 4, g = fr.row0 + (e & 15);
-                    if (g < nrows) out[(size_t)mi * nrows + g] = a;
+                if (p.finish == FIN_PLAIN) {
+                    for (int e = lane; e < 16 * p.m; e += 32) {
+                        float a = __ldcg(src + e);
+                        for (int s = 1; s < p.kb; s++) a += __ldcg(src + s * sstride + e);
+                        const int mi = e >> 4, g = fr.row0 + (e & 15);
+                        if (g < nrows) out[(size_t)mi * nrows + g] = a;
+                    }
+                } else {   // m == 1
+                    float a = 0.f;
+                    if (lane < 16) {
+                        a = __ldcg(src + lane);
+                        for (int s = 1; s < p.kb; s++) a += __ldcg(src + s * sstride + lane);
+                    }
+                    finish_tile_fused(p, fr, a, lane);
                 }
                 if (lane == 0) p.tile_cnt[fr.tile] = 0;
             }
@@ -500,6 +543,11 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.prologue = job.prologue;
     p.x = job.x; p.x2 = job.x2; p.norm_w = job.norm_w; p.eps = job.eps; p.x_out = job.x_out;
     p.emb_table = job.emb_table; p.token = job.token;
+    p.ssq_parts = job.ssq_parts; p.n_parts = job.n_parts;
+    p.finish = job.finish; p.resid = job.resid; p.ssq_out = job.ssq_out;
+    if (job.finish != FIN_PLAIN && (job.m != 1 || job.n_w != 1)) return fail(TLB_ERR_ARG, "fused tile finishing takes one tensor and one activation row");
+    if (job.finish == FIN_RESID && (!job.resid || !job.ssq_out)) return fail(TLB_ERR_NULL, "null residual or statistics buffer");
+    if (job.ssq_parts && (job.prologue != PRO_ADD_NORM || job.n_parts < 1)) return fail(TLB_ERR_ARG, "partial sums of squares go with the fused RMSNorm prologue");
     if (p.x.slices < 1) p.x.slices = 1;
     if (p.x2.slices < 1) p.x2.slices = 1;
     if ((p.x.slices > 1 && p.x.stride % 4) || (p.x2.slices > 1 && p.x2.stride % 4))

@@ -178,6 +178,11 @@ struct MvParams {
     SlicedVec x;              // PLAIN: x [M,K]; ADD_NORM: residual; SILU_MUL: gate
     SlicedVec x2;             // ADD_NORM: delta added to x (p == null: none); SILU_MUL: up
     const float *norm_w;
+    const float *ssq_parts;   // ADD_NORM: partial sums of squares of x left by its producer (null: computed here)
+    int n_parts;
+    int finish;               // FIN_*: what the warp completing a tile does with its results
+    const float *resid;       // FIN_RESID: added to the result
+    float *ssq_out;           // FIN_RESID: [tiles] sum of squares of each finished tile
     float eps;
     float *x_out;             // ADD_NORM: residual + delta written here by CTA 0 (may be null)
     const float *emb_table;

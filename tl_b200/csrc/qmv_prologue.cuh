@@ -153,7 +153,18 @@ __device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem,
                 if (norm) wgt[i] = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + k4);
             }
         }
-        if (norm && first == 0) {
+        if (norm && first == 0 && p.ssq_parts) {
+            // The producer of x left partial sums of squares: every warp adds them itself, in one fixed
+            // order, so no block-wide exchange is needed and nothing of the row is re-read.
+            for (int i = lane; i < p.n_parts; i += 32) ssq += __ldcg(p.ssq_parts + i);
+            float dep = ssq;
+#pragma unroll
+            for (int i = 0; i < kKeep; i++)
+                if (grp + i * ngroups < n_mine) dep += keep[i].x;
+            after_loads(dep);
+            for (int o = 16; o; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+            inv_rms = 1.f / sqrtf(ssq / (float)p.k + p.eps);
+        } else if (norm && first == 0) {
             // the blocks outside [blk0, blk0 + nb): only their squares are needed (m == 1 with this prologue)
             for (int o = grp; o < nblk - nb; o += ngroups) {
                 const int k4 = (o < blk0 ? o : o + nb) * 64 + j;

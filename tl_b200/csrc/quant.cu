@@ -63,6 +63,44 @@ tlb_status launch_repack(int type, const uint8_t *raw, uint8_t *tiled, int64_t n
     return TLB_OK;
 }
 
+// Builds, from two tiled tensors a and b of equal shape [n, k], the tiled tensor of 2n rows whose
+// tile t holds rows 8t..8t+7 of a followed by rows 8t..8t+7 of b.  The decode chain uses it for
+// gate | up: one MMA tile then yields gate and up of the same 8 hidden units, so SiLU(gate) * up
+// can be taken where the tile is finished.  One thread per byte of a row segment.
+__global__ void interleave8_kernel(int type, const uint8_t *__restrict__ a, const uint8_t *__restrict__ b,
+                                   uint8_t *__restrict__ dst, int64_t n, int64_t k, int seg_bytes, int unit_bytes)
+{
+    const int64_t upt = k / 256;
+    const int64_t total = 2 * n * upt * seg_bytes;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int raw_off = (int)(idx % seg_bytes);
+        const int64_t seg = idx / seg_bytes;          // drow * upt + u
+        const int64_t drow = seg / upt, u = seg % upt;
+        const int64_t dtile = drow / 16;
+        const int di = (int)(drow % 16);
+        const int64_t srow = dtile * 8 + (di & 7);     // row of a (di < 8) or b (di >= 8)
+        const uint8_t *src = di < 8 ? a : b;
+        dst[(dtile * upt + u) * unit_bytes + unit_offset(type, di, raw_off)] =
+            src[((srow / 16) * upt + u) * unit_bytes + unit_offset(type, (int)(srow % 16), raw_off)];
+    }
+}
+
+tlb_status launch_interleave8(int type, const uint8_t *a, const uint8_t *b, uint8_t *dst, int64_t n, int64_t k)
+{
+    const QFormat *f = qformat(type);
+    if (!f) return fail(TLB_ERR_TYPE, "unsupported GGML type %d", type);
+    if (n % 16) return fail(TLB_ERR_SHAPE, "interleaving needs a row count that is a multiple of 16, got %lld", (long long)n);
+    int seg = 256 / f->raw_block * f->raw_block_bytes;
+    int64_t total = 2 * n * (k / 256) * seg;
+    if (total == 0) return TLB_OK;
+    int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 64);
+    interleave8_kernel<<<blocks, 256, 0, ctx()->stream>>>(type, a, b, dst, n, k, seg, f->unit_bytes);
+    count_launch();
+    TLB_CUDA(cudaGetLastError());
+    return TLB_OK;
+}
+
 // ---- bit-exact dequantisation ------------------------------------------------------------
 // Expression shapes follow crates/tl_runtime/src/quantized.rs:182-415 exactly: separate
 // f32 multiplies and subtracts (__fmul_rn / __fsub_rn are never contracted into an FMA).

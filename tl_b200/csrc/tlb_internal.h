@@ -112,10 +112,12 @@ namespace tlb {
 // quant.cu
 tlb_status launch_repack(int type, const uint8_t *raw, uint8_t *tiled, int64_t n, int64_t k);
 tlb_status launch_dequant_tiled(int type, const uint8_t *tiled, float *out, int64_t n, int64_t k);
+tlb_status launch_interleave8(int type, const uint8_t *a, const uint8_t *b, uint8_t *dst, int64_t n, int64_t k);
 
 // qmatvec.cu ---------------------------------------------------------------------------
 // How the activation vector of a streaming matvec is produced inside the kernel.
 enum Prologue { PRO_PLAIN = 0, PRO_ADD_NORM = 1, PRO_SILU_MUL = 2 };
+enum Finish { FIN_PLAIN = 0, FIN_RESID = 1, FIN_SILU = 2 };
 constexpr int kMaxSlices = 16;   // most K-slices a matvec may split its output into
 // A vector kept as the element-wise sum of `slices` arrays `stride` floats apart: the form in which
 // the streaming matvec leaves its output (one array per K-slice, each element written exactly once).
@@ -148,6 +150,18 @@ struct MatvecJob {
     const float *emb_table = nullptr; // ADD_NORM with token lookup: x = emb_table[*token * K ...]
     const int *token = nullptr;
     bool pdl = false;                // launch with programmatic stream serialization
+    // ADD_NORM without the statistics pass: x already holds the whole residual and ssq_parts[0 .. n_parts)
+    // are partial sums of its squares left by the launch that produced it (finish == FIN_RESID there)
+    const float *ssq_parts = nullptr;
+    int n_parts = 0;
+    // What the warp that completes a tile does with its 16 results (m == 1, one tensor, for the fused forms):
+    //   FIN_PLAIN  out[row] = y
+    //   FIN_RESID  out[row] = resid[row] + y, and ssq_out[tile] = sum of the squares of those 16 values
+    //   FIN_SILU   rows 0..7 of a tile are gate, rows 8..15 up of the same 8 units (launch_interleave8):
+    //              out[8 * tile + i] = silu(y[i]) * y[8 + i]
+    int finish = 0;
+    const float *resid = nullptr;
+    float *ssq_out = nullptr;
     bool last_of_chain = false;      // no matvec follows closely: take half an SM's shared memory instead of a third
     long long *trace = nullptr;      // optional device buffer [grid][10] of stamps (timing studies)
     unsigned long long *span = nullptr;   // optional device buffer [4]: timeline of the launch (span_trace.cuh)
