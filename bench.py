@@ -140,6 +140,17 @@ def barrier(dist):
         dist.barrier()
 
 
+def whole_job_rate(world, steps, ms_max):
+    """Tokens per second of the whole job: every rank decodes `steps` tokens of its own replica in the
+    same (slowest rank's) time."""
+    return world * steps / (ms_max / 1e3)
+
+
+# DRAM bytes moved per algorithmic byte by the streaming matvec, from the ncu capture summarised in
+# profiles/qmatvec_q4k_llama3-8b-shapes_4layer_ncu-full.md (dram__bytes_read + dram__bytes_write over the weight bytes)
+NCU_TRAFFIC_RATIO = 1.003
+
+
 # ---------------------------------------------------------------- CPU baseline (oracle port of the reference CPU path)
 
 def cpu_token_time(cfg, frac, rng, cache):
@@ -278,9 +289,10 @@ def run_ours(args, dist, rank, world):
             tot_us += us
     achieved = tot_b / tot_us / 1e3
     st = dec.stats(ctx + W + K // 2)
-    tok_s = world * K / (ms_max / 1e3)
+    tok_s = whole_job_rate(world, K, ms_max)
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "peak_kind": peak_kind,
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": int(tot_b * NCU_TRAFFIC_RATIO), "peak_kind": peak_kind,
+                "traffic_note": "bytes of the same four launches; ncu capture of a 4-layer case, scaled by the weight bytes",
                 "kernel": "qmatvec_kernel over one layer's four launches (qkv, o, gate|up, down), weights of %d layers rotated"
                           % cfg["n_layers"],
                 "per_launch": kern,
@@ -290,13 +302,13 @@ def run_ours(args, dist, rank, world):
     line = {"metric": "Q4_K Llama-3-8B decode tok/s @bs1" if args.workload == "c2" else "decode tok/s @bs1",
             "value": round(tok_s, 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": round(ms_max / K, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
+            "dtype": "int8 MMA (s32 sums) + f32", "data": "synthetic",
             "config": {"workload": args.workload + ": " + desc, "l2": "inputs larger than L2: %.2f GB of weights streamed per step"
                        % (st["weight_bytes"] / 1e9), "parallelism": "replicas x%d" % world if world > 1 else "single GPU",
                        "weight_bytes_per_token": st["weight_bytes"], "kv_bytes_per_token": st["kv_bytes"],
                        "greedy_tokens_head": toks[:8], "setup_s": round(time.time() - t_start, 1)},
             "clocks": clocks,
-            "e2e": {"value": round(world * K / (e2e_ms / 1e3), 2), "unit": "tokens/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4},
+            "e2e": {"value": round(whole_job_rate(world, K, e2e_ms), 2), "unit": "tokens/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
             "roofline": roofline, "cpu_baseline": cpu}
     return line
