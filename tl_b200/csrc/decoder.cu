@@ -49,6 +49,7 @@ struct tlb_decoder {
     cudaGraphExec_t graph = nullptr;
     uint64_t graph_kernels = 0;
     bool pdl = true;
+    bool dry = false;            // enqueue_step only validates the matvec launches
     std::vector<void *> allocs;
     size_t kv_layer_elems = 0;
 };
@@ -188,6 +189,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             else { j.x = sliced(d->xb, 1, 0); j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16; }
             j.pdl = d->pdl;
             j.span = next_span();
+            j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K2
@@ -199,7 +201,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             a.pos = d->state + 1; a.rope_pos = d->state + 2; a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.scale = c.attn_scale;
             a.partial = d->partial; a.counters = d->counters; a.splits = d->max_splits; a.out = d->attn; a.pdl = d->pdl;
             a.span = next_span();
-            TLB_TRY(launch_decode_attention(a));
+            if (!d->dry) TLB_TRY(launch_decode_attention(a));
         }
         {   // K3
             MatvecJob j;
@@ -210,6 +212,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             j.finish = FIN_RESID; j.resid = d->xb; j.ssq_out = d->ssq_o;   // xa = xb + o_proj(attn)
             j.pdl = d->pdl;
             j.span = next_span();
+            j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K4
@@ -222,6 +225,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             j.finish = FIN_SILU;
             j.pdl = d->pdl;
             j.span = next_span();
+            j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
         {   // K5
@@ -233,6 +237,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             j.finish = FIN_RESID; j.resid = d->xa; j.ssq_out = d->ssq_d;   // xb = xa + down(h)
             j.pdl = d->pdl;
             j.span = next_span();
+            j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
     }
@@ -246,9 +251,10 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         j.last_of_chain = true;
         j.pdl = d->pdl;
         j.span = next_span();
+        j.dry_run = d->dry;
         TLB_TRY(launch_qmatvec(j));
     }
-    {
+    if (!d->dry) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(kArgmaxBlocks);
         cfg.blockDim = dim3(256);
@@ -356,11 +362,6 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     TRY_D(get_f(m, "token_embd.weight", &d->emb, (int64_t)c.vocab * dm));
     TRY_D(get_f(m, "output_norm.weight", &d->out_norm, dm));
     TRY_D(get_q(m, "output.weight", &d->head, c.vocab, dm, -1));
-    size_t kmax = qmatvec_max_k(1);
-    if ((size_t)std::max(std::max(dm, qd), F) > kmax) {
-        tlb_decoder_destroy(d);
-        return fail(TLB_ERR_SHAPE, "inner dimensions up to %zu fit the single-pass matvec", kmax);
-    }
     {
         const LayerW &w0 = d->layers[0];
         // The matvec folds its K-slices itself (last warp of a tile), so every buffer of the chain is a
@@ -417,6 +418,10 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     }
     cudaError_t e = cudaMallocHost((void **)&d->h_state, 4 * sizeof(int));
     if (e != cudaSuccess) { tlb_decoder_destroy(d); return cuda_fail(e, "cudaMallocHost"); }
+    d->dry = true;                 // every matvec shape of the chain must be launchable
+    st = enqueue_step(d);
+    d->dry = false;
+    if (st != TLB_OK) { tlb_decoder_destroy(d); return st; }
     TRY_D(tlb_sync());
 #undef TRY_D
     *out = d;

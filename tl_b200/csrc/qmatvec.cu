@@ -558,6 +558,7 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.span = job.span;
     if (!p.x.p && !(p.prologue == PRO_ADD_NORM && p.token)) return fail(TLB_ERR_NULL, "null activation");
     if (p.prologue == PRO_SILU_MUL && !p.x2.p) return fail(TLB_ERR_NULL, "null activation");
+    if (job.dry_run) return TLB_OK;   // the shape is launchable
     switch (job.type) {
     case TLB_GGML_Q4_K: return launch_fmt<TLB_GGML_Q4_K>(p, grid, smem, job.pdl);
     case TLB_GGML_Q6_K: return launch_fmt<TLB_GGML_Q6_K>(p, grid, smem, job.pdl);

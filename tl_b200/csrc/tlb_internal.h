@@ -162,6 +162,7 @@ struct MatvecJob {
     int finish = 0;
     const float *resid = nullptr;
     float *ssq_out = nullptr;
+    bool dry_run = false;            // validate and plan only: tells whether the launch would be accepted
     bool last_of_chain = false;      // no matvec follows closely: take half an SM's shared memory instead of a third
     long long *trace = nullptr;      // optional device buffer [grid][10] of stamps (timing studies)
     unsigned long long *span = nullptr;   // optional device buffer [4]: timeline of the launch (span_trace.cuh)
