@@ -50,6 +50,7 @@ struct tlb_decoder {
     uint64_t graph_kernels = 0;
     bool pdl = true;
     bool dry = false;            // enqueue_step only validates the matvec launches
+    int force_slices[5] = {0, 0, 0, 0, 0};   // K-slices of qkv, o, gate|up, down, head; 0: the kernel's own choice (TLB_SLICES=a,b,c,d,e)
     std::vector<void *> allocs;
     size_t kv_layer_elems = 0;
 };
@@ -181,7 +182,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             set_w(j, 1, w.k, d->qkv + qd, nqkv);
             set_w(j, 2, w.v, d->qkv + qd + kvd, nqkv);
            
-            j.type = w.q->type; j.k = dm; j.m = 1;
+            j.type = w.q->type; j.k = dm; j.m = 1; j.slices = d->force_slices[0];
             j.prologue = PRO_ADD_NORM;
             j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
             // the residual lives in xb here: the embedding row for layer 0, else what the last down launch left
@@ -207,7 +208,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.o, d->xa, dm);
-            j.type = w.o->type; j.k = qd; j.m = 1;
+            j.type = w.o->type; j.k = qd; j.m = 1; j.slices = d->force_slices[1];
             j.prologue = PRO_PLAIN; j.x = sliced(d->attn, 1, 0);
             j.finish = FIN_RESID; j.resid = d->xb; j.ssq_out = d->ssq_o;   // xa = xb + o_proj(attn)
             j.pdl = d->pdl;
@@ -219,7 +220,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.gu, d->hbuf, F);
-            j.type = w.gu->type; j.k = dm; j.m = 1;
+            j.type = w.gu->type; j.k = dm; j.m = 1; j.slices = d->force_slices[2];
             j.prologue = PRO_ADD_NORM; j.x = sliced(d->xa, 1, 0); j.ssq_parts = d->ssq_o; j.n_parts = (dm + 15) / 16;
             j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
             j.finish = FIN_SILU;
@@ -232,7 +233,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.down, d->xb, dm);
-            j.type = w.down->type; j.k = F; j.m = 1;
+            j.type = w.down->type; j.k = F; j.m = 1; j.slices = d->force_slices[3];
             j.prologue = PRO_PLAIN; j.x = sliced(d->hbuf, 1, 0);
             j.finish = FIN_RESID; j.resid = d->xa; j.ssq_out = d->ssq_d;   // xb = xa + down(h)
             j.pdl = d->pdl;
@@ -245,7 +246,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         MatvecJob j;
         j.n_w = 1;
         set_w(j, 0, d->head, d->logits_sl, c.vocab);
-        j.type = d->head->type; j.k = dm; j.m = 1;
+        j.type = d->head->type; j.k = dm; j.m = 1; j.slices = d->force_slices[4];
         j.prologue = PRO_ADD_NORM; j.x = sliced(d->xb, 1, 0); j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16;
         j.norm_w = d->out_norm->f32(); j.eps = c.eps;
         j.last_of_chain = true;
@@ -341,6 +342,8 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     const int64_t dm = c.d_model, qd = (int64_t)c.n_heads * c.head_dim, kvd = (int64_t)c.n_kv_heads * c.head_dim, F = c.ffn;
     tlb_decoder *d = new tlb_decoder();
     d->cfg = c;
+    if (const char *fs = getenv("TLB_SLICES"))   // tuning aid: K-slices per launch kind instead of the cost model's choice
+        sscanf(fs, "%d,%d,%d,%d,%d", &d->force_slices[0], &d->force_slices[1], &d->force_slices[2], &d->force_slices[3], &d->force_slices[4]);
     const char *nopdl = getenv("TLB_NO_PDL");
     d->pdl = !(nopdl && nopdl[0] == '1');
     tlb_status st = TLB_OK;

@@ -121,10 +121,16 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
     if (tid == 0) { span_start(p.span); span_event(p.span, 4); }
     if (p.trace && tid == 0) p.trace[(size_t)b * 10 + 8] = (long long)global_ns();
 
-    // items of this CTA, then of this warp
+    // Work of this CTA: a contiguous range of items.  Work of this warp: a contiguous range [wu0, wu1) of
+    // the CTA's units in item order.  With K-slices (kb > 1) the ranges are whole items; with one
+    // slice (kb == 1, an item is a whole tile) they are cut to equal unit counts, may start and end
+    // inside a tile, and the pieces of a tile meet in shared memory at the end ("local" mode).
     const int ci0 = b * p.ipc_q + min(b, p.ipc_r), nci = p.ipc_q + (b < p.ipc_r ? 1 : 0), ci1 = ci0 + nci;
-    const int i0 = ci0 + nci * warp / kWarps, i1 = ci0 + nci * (warp + 1) / kWarps;
-    const int n_units = (i1 - i0) * p.upi;
+    const bool local = p.kb == 1;
+    const int cta_units = nci * p.upi;
+    const int wu0 = local ? cta_units * warp / kWarps : (nci * warp / kWarps) * p.upi;
+    const int wu1 = local ? cta_units * (warp + 1) / kWarps : (nci * (warp + 1) / kWarps) * p.upi;
+    const int n_units = wu1 - wu0;
     // activation blocks the CTA's items cover
     const int s_first = nci > 0 ? ci0 / p.tiles : 0, s_last = nci > 0 ? (ci1 - 1) / p.tiles : 0;
     const int blk0 = s_first * p.upi, nb = nci > 0 ? (s_last + 1) * p.upi - blk0 : 0;
@@ -145,8 +151,8 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         if (lane < n_first) {
-            const int it = lane / p.upi, uo = lane - it * p.upi;
-            first_src = item_ref(p, cursor_at(p, i0 + it)).src + (size_t)uo * p.unit_bytes;
+            const int g = wu0 + lane, it = g / p.upi, uo = g - it * p.upi;
+            first_src = item_ref(p, cursor_at(p, ci0 + it)).src + (size_t)uo * p.unit_bytes;
             if (lane < kEarly) {
                 mbar_expect_tx(bars + lane * 8, p.unit_bytes);
                 bulk_g2s(ring + lane * p.stage_bytes, first_src, p.unit_bytes, bars + lane * 8);
@@ -161,8 +167,8 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
     const uint8_t *pf_src = nullptr;
     ItemCursor pf_cur;
     {
-        const int it = n_first / p.upi, uo = n_first - it * p.upi;
-        pf_cur = cursor_at(p, i0 + it);
+        const int g = wu0 + n_first, it = g / p.upi, uo = g - it * p.upi;
+        pf_cur = cursor_at(p, ci0 + it);
         if (uo && pf_remaining > 0) {   // in the middle of an item
             pf_src = item_ref(p, pf_cur).src + (size_t)uo * p.unit_bytes;
             cursor_next(p, pf_cur);
@@ -213,18 +219,23 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         L.sa_c1 = smem_u32(smem + p.off_sa) + c1 * 4;
         L.minv_b = smem_u32(smem + p.off_minv) + (c < p.m ? c : 0) * 4;
     }
+    float *segbuf = reinterpret_cast<float *>(smem + p.off_seg);   // local mode: [warp][run][16 * m] partial results
 
     int stage = 0, phase = 0, consumed = 0;
     bool ok = true;
-    ItemCursor cur = cursor_at(p, i0);
-    for (int item = i0; item < i1 && ok; item++, cursor_next(p, cur)) {
+    int remaining = n_units, seg = 0;
+    const int it0 = wu0 / p.upi;
+    int uo0 = wu0 - it0 * p.upi;          // the first run may start inside an item (local mode)
+    ItemCursor cur = cursor_at(p, ci0 + it0);
+    while (remaining > 0 && ok) {
         const ItemRef ir = item_ref(p, cur);
-        const int lb0 = ir.slice * p.upi - blk0;
+        const int run = min(remaining, p.upi - uo0);
+        const int lb0 = ir.slice * p.upi + uo0 - blk0;
         float master[4] = {0.f, 0.f, 0.f, 0.f}, mm[4] = {0.f, 0.f, 0.f, 0.f};
         int uo = 0;
         // two units per trip: the two bodies are independent, so one warp has two instruction streams
         // to interleave, and the loop bookkeeping is paid once
-        for (; uo + 1 < p.upi; uo += 2) {
+        for (; uo + 1 < run; uo += 2) {
             const int st1 = stage + 1 == spw ? 0 : stage + 1, ph1 = stage + 1 == spw ? phase ^ 1 : phase;
             bool got = mbar_try_wait(bars + stage * 8, phase);
             if (!got) got = mbar_wait_slow(bars + stage * 8, phase, abortp, p.err, 2);
@@ -242,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
             stage = st1 + 1 == spw ? 0 : st1 + 1;
             phase = st1 + 1 == spw ? ph1 ^ 1 : ph1;
         }
-        if (ok && uo < p.upi) {
+        if (ok && uo < run) {
             bool got = mbar_try_wait(bars + stage * 8, phase);
             if (!got) got = mbar_wait_slow(bars + stage * 8, phase, abortp, p.err, 2);
             if (!__all_sync(0xffffffffu, got)) ok = false;
@@ -256,11 +267,10 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         }
         if (!ok) break;
         // Fold the level columns of each activation row (they sit in the four lanes of a quad).  The
-        // Q4_K min term of activation row mi lives in lane c == mi.  With one K-slice the 16 rows go
-        // straight to the output; otherwise to this item's 16*m floats of the slice scratch.
-        float *out = p.out[ir.wi];
-        const int nrows = p.n_rows[ir.wi];
-        float *part = p.part + ((size_t)ir.slice * p.tiles + ir.tile) * (16 * p.m);
+        // Q4_K min term of activation row mi lives in lane c == mi.  The 16 * m partial results of the run
+        // go to this warp's slot in shared memory (local mode) or to the item's slot of the slice scratch.
+        float *part = local ? segbuf + ((size_t)warp * p.max_seg + seg) * (16 * p.m)
+                            : p.part + ((size_t)ir.slice * p.tiles + ir.tile) * (16 * p.m);
         for (int mi = 0; mi < p.m; mi++) {
             const int lo = mi * p.nl, hi = lo + p.nl, cA = 2 * L.c, cB = 2 * L.c + 1;
             const bool inA = cA >= lo && cA < hi, inB = cB >= lo && cB < hi;
@@ -270,27 +280,52 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1); v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
             if (L.c == mi) {
                 if (FMT == TLB_GGML_Q4_K) { v0 -= mm[0] + mm[1]; v1 -= mm[2] + mm[3]; }
-                if (p.kb > 1) {
-                    part[mi * 16 + L.r] = v0;
-                    part[mi * 16 + L.r + 8] = v1;
-                } else if (p.finish == FIN_PLAIN) {
-                    const int g0 = ir.row0 + L.r, g1 = g0 + 8;
-                    if (g0 < nrows) out[(size_t)mi * nrows + g0] = v0;
-                    if (g1 < nrows) out[(size_t)mi * nrows + g1] = v1;
-                }
-            }
-            if (p.kb == 1 && p.finish != FIN_PLAIN) {   // m == 1: bring row e to lane e and finish the tile
-                const int srcl = (lane & 7) * 4;
-                const float a0 = __shfl_sync(0xffffffffu, v0, srcl), a1 = __shfl_sync(0xffffffffu, v1, srcl);
-                finish_tile_fused(p, ir, lane < 8 ? a0 : a1, lane);
+                part[mi * 16 + L.r] = v0;
+                part[mi * 16 + L.r + 8] = v1;
             }
         }
+        seg++;
+        remaining -= run;
+        uo0 = 0;
+        cursor_next(p, cur);
     }
-    if (ok && p.kb > 1 && i1 > i0) {
+    if (local) {
+        // The pieces of every tile of this CTA are in shared memory.  Tile t (CTA-local) is finished by
+        // warp t % kWarps: it adds the pieces in the order of the warps that produced them - a fixed
+        // order - and writes the rows.  No global scratch, fence or counter is involved.
+        __syncthreads();           // every warp gets here: its waits are bounded
+        if (!*abortp) {
+            for (int tl = warp; tl < nci; tl += kWarps) {
+                const int a0 = tl * p.upi, a1 = a0 + p.upi;
+                float acc0 = 0.f, acc1 = 0.f;   // elements lane and lane + 32 of the 16 * m results
+                for (int w = 0; w < kWarps; w++) {
+                    const int b0 = cta_units * w / kWarps, b1 = cta_units * (w + 1) / kWarps;
+                    if (b1 <= a0 || b0 >= a1 || b1 == b0) continue;
+                    const float *sp = segbuf + ((size_t)w * p.max_seg + (tl - b0 / p.upi)) * (16 * p.m);
+                    if (lane < 16 * p.m) acc0 += sp[lane];
+                    if (lane + 32 < 16 * p.m) acc1 += sp[lane + 32];
+                }
+                ItemCursor cf;
+                cf.slice = 0;
+                cf.tile = ci0 + tl;
+                const ItemRef fr = item_ref(p, cf);
+                if (p.finish == FIN_PLAIN) {
+                    float *out = p.out[fr.wi];
+                    const int nrows = p.n_rows[fr.wi];
+                    const int g = fr.row0 + (lane & 15);
+                    if (lane < 16 * p.m && g < nrows) out[(size_t)(lane >> 4) * nrows + g] = acc0;
+                    if (lane + 32 < 16 * p.m && g < nrows) out[(size_t)((lane >> 4) + 2) * nrows + g] = acc1;
+                } else {
+                    finish_tile_fused(p, fr, lane < 16 ? acc0 : 0.f, lane);
+                }
+            }
+        }
+    } else if (ok && wu1 > wu0) {
         // All partial results of this warp are out.  One fence, then one count per item (lane j counts
         // item j); the warp that completes a tile's last K-slice adds the slices in index order and
         // writes the output rows, so the sum is the same whichever warp does it.  It also clears the
         // tile's counter for the next launch on this stream.
+        const int i0 = ci0 + it0, i1 = ci0 + wu1 / p.upi;
         __threadfence();                                      // our slices are visible before the counts say so
         __syncwarp();
         for (int base = i0; base < i1; base += 32) {
@@ -410,11 +445,15 @@ static double slice_cost(int type, int m, int64_t tiles, int upt, int upi, int s
     const int64_t ipc = (n_items + grid - 1) / grid, ipw = (ipc + kWarps - 1) / kWarps;
     const int nb = blocks_per_cta(n_items, grid, tiles, upi, upt);
     const double unit = type == TLB_GGML_Q6_K ? 300.0 : type == TLB_GGML_Q8_0 ? 150.0 : 210.0;
-    const double stream = (double)ipw * (upi * unit + 60.0);
+    // one slice: the CTA's units are cut evenly over its warps whatever the tile borders
+    const double stream = kb == 1 ? (double)((ipc * upi + kWarps - 1) / kWarps) * unit + 60.0 * ((ipc + kWarps - 1) / kWarps + 1)
+                                  : (double)ipw * (upi * unit + 60.0);
     const double quant = 300.0 * ((m * nb + kThreads / 64 - 1) / (kThreads / 64));
-    // measured on the Llama-3-8B shapes: cheaper-looking models that cut the small launches into 14-16
-    // slices made the whole decode step 25 % slower, so folding is priced per item and per slice
-    const double fold = kb > 1 ? (double)ipw * 80.0 + 16.0 * kb : 0.0;
+    // Measured on the Llama-3-8B shapes: the end of a sliced launch (fence, counts, reading the slices back)
+    // costs ~3 us; assembling tiles in shared memory costs a block barrier, which shows (~2 us of waiting
+    // for the slowest warp) only when warps have so few units that their skew matters.
+    const bool few = (ipc * upi + kWarps - 1) / kWarps < 4;
+    const double fold = kb > 1 ? 600.0 + 16.0 * kb : (few ? 600.0 : 100.0);
     return stream + quant + fold;
 }
 
@@ -528,7 +567,9 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     if (sp.fixed + 128 + 2 * per_stage > budget)
         return fail(TLB_ERR_SHAPE, "K = %lld with %d rows needs more shared memory than one SM has (max K %zu)",
                     (long long)job.k, job.m, qmatvec_max_k(job.m));
-    int spw = (int)((budget - sp.fixed - 128) / per_stage);
+    // (room for the local-mode slots: at most ~6 per warp)
+    const size_t seg_room = p.kb == 1 ? (size_t)kWarps * 8 * 16 * job.m * sizeof(float) + 128 : 0;
+    int spw = (int)((budget - sp.fixed - 128 - seg_room) / per_stage);
     // no more stages than the longest warp has units, and no more than keeps ~1.5 us of HBM latency covered
     const int64_t ipc = (p.n_items + grid - 1) / grid;
     const int64_t upw = (ipc + kWarps - 1) / kWarps * p.upi;
@@ -539,7 +580,17 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.off_sa = (int)ring + sp.off_sa; p.off_minv = (int)ring + sp.off_minv; p.off_misc = (int)ring + sp.off_misc;
     p.off_bars = (int)(ring + sp.fixed);
     p.col_stride = sp.col_stride;
-    const size_t smem = ring + sp.fixed + (size_t)kWarps * spw * 8;
+    size_t smem = ring + sp.fixed + (size_t)kWarps * spw * 8;
+    // local mode (one K-slice): per warp, one slot of 16 * m partial results per tile its unit range touches
+    p.max_seg = 1;
+    p.off_seg = 0;
+    if (p.kb == 1) {
+        const int64_t n_max = (ipc * p.upi + kWarps - 1) / kWarps;           // most units a warp gets
+        p.max_seg = (int)((n_max + p.upi - 2) / p.upi + 1);
+        p.off_seg = (int)((smem + 127) / 128 * 128);
+        smem = (size_t)p.off_seg + (size_t)kWarps * p.max_seg * 16 * job.m * sizeof(float);
+        if (smem > c->smem_optin) return fail(TLB_ERR_SHAPE, "launch needs %zu bytes of shared memory", smem);
+    }
     p.prologue = job.prologue;
     p.x = job.x; p.x2 = job.x2; p.norm_w = job.norm_w; p.eps = job.eps; p.x_out = job.x_out;
     p.emb_table = job.emb_table; p.token = job.token;

@@ -174,6 +174,7 @@ struct MvParams {
     int nb_max;               // 256-blocks of activation a CTA may need: the shared tables are sized for it
     int unit_bytes, stage_bytes;
     int spw;                  // ring stages private to each warp
+    int max_seg, off_seg;     // kb == 1: slots of partial results per warp in shared memory, and where they start
     int prologue;
     SlicedVec x;              // PLAIN: x [M,K]; ADD_NORM: residual; SILU_MUL: gate
     SlicedVec x2;             // ADD_NORM: delta added to x (p == null: none); SILU_MUL: up

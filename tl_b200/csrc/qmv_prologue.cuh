@@ -20,18 +20,24 @@ namespace tlb {
 
 #define MAGIC_RN 12582912.0f
 
-// Quantises block (mrow, blk) with a group of 64 threads (index j in the group) into the shared tables
-// at local block index lb.
-template <int FMT>
-__device__ __forceinline__ void quantise_block(const MvParams &p, uint8_t *smem, float *pair_max, const float4 v,
-                                               int mrow, int lb, int j, int lane, int pair_bar)
+// A block (mrow, blk) is quantised by a group of 64 threads (index j in the group) in two steps with a
+// group barrier between them, so that a group can run the steps of two blocks side by side:
+// warp_absmax() gives the largest magnitude among a warp's 128 values; quantise_block() takes the
+// block's maximum and writes the shared tables at local block index lb.
+__device__ __forceinline__ float warp_absmax(const float4 v)
 {
     float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) pair_max[j >> 5] = mx;
-    named_bar(pair_bar, 64);
-    const float amax = fmaxf(pair_max[0], pair_max[1]);
-    const float alpha = amax > 0.f ? amax * (1.f / 127.f) : 1.f;
+    return mx;
+}
+
+template <int FMT>
+__device__ __forceinline__ void quantise_block(const MvParams &p, uint8_t *smem, const float amax, const float4 v,
+                                               int mrow, int lb, int j, int lane)
+{
+    // blocks whose largest magnitude is below 2^-100 (or not finite) quantise to zero levels: their
+    // contribution is below f32 resolution of any realistic result, and 1 / alpha stays finite
+    const float alpha = (amax > 7.9e-31f && amax < 3.0e38f) ? amax * (1.f / 127.f) : 1.f;
     float res[4] = {v.x, v.y, v.z, v.w};
     float scale = alpha, inv = __frcp_rn(alpha);
     uint32_t words[3] = {0u, 0u, 0u};
@@ -42,8 +48,9 @@ __device__ __forceinline__ void quantise_block(const MvParams &p, uint8_t *smem,
             uint32_t tb[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                float t = fmaf(res[e], inv, MAGIC_RN);
-                t = fminf(fmaxf(t, MAGIC_RN - 127.f), MAGIC_RN + 127.f);
+                // |res * inv| <= 127 by construction at every level (alpha = max / 127; a residual is at most
+                // half a step of the level before), so no clamp is needed
+                const float t = fmaf(res[e], inv, MAGIC_RN);
                 const float qf = t - MAGIC_RN;
                 res[e] = fmaf(-qf, scale, res[e]);
                 lsum[l] += qf;
@@ -115,7 +122,6 @@ __device__ __forceinline__ void quantise_block(const MvParams &p, uint8_t *smem,
                 if ((lane & 7) == 0) sa[(size_t)(lb * 8 + (j >> 3)) * kMaxCols + mrow * p.nl + l] = __float2int_rn(s);
             }
     }
-    named_bar(pair_bar, 64);   // pair_max may be rewritten by this group's next block
 }
 
 // Fills the shared tables for activation blocks [blk0, blk0 + nb) of every row.  All `nthreads`
@@ -203,19 +209,33 @@ __device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem,
                 if (grp + i * ngroups < n_mine) dep += keep[i].x;
             after_loads(dep);
         }
+        // step 1 of this pass's blocks: final values and each warp's maximum
+        float *pair_max = &sh->red_max[grp * 2 * kKeep];
 #pragma unroll
         for (int i = 0; i < kKeep; i++) {
             const int item = first + grp + i * ngroups;
             if (item < n_mine) {
-                const int mrow = item / nb, lb = item - mrow * nb;
                 float4 v = keep[i];
                 if (norm) {   // (x / rms) * weight (crates/tl_cpu/src/ffi.rs:2444-2486), the division as a multiply by 1/rms
                     v.x = (v.x * inv_rms) * wgt[i].x; v.y = (v.y * inv_rms) * wgt[i].y;
                     v.z = (v.z * inv_rms) * wgt[i].z; v.w = (v.w * inv_rms) * wgt[i].w;
                 }
-                quantise_block<FMT>(p, smem, &sh->red_max[grp * 2], v, mrow, lb, j, lane, 2 + grp);
+                keep[i] = v;
+                const float mx = warp_absmax(v);
+                if (lane == 0) pair_max[2 * i + (j >> 5)] = mx;
             }
         }
+        if (first + grp < n_mine) named_bar(2 + grp, 64);
+        // step 2: the blocks are independent from here on, their instruction streams interleave
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+            const int item = first + grp + i * ngroups;
+            if (item < n_mine) {
+                const int mrow = item / nb, lb = item - mrow * nb;
+                quantise_block<FMT>(p, smem, fmaxf(pair_max[2 * i], pair_max[2 * i + 1]), keep[i], mrow, lb, j, lane);
+            }
+        }
+        if (first + grp < n_mine && first + ngroups * kKeep < n_mine) named_bar(2 + grp, 64);   // pair_max is reused by the next pass
     }
     __syncthreads();
 }
