@@ -111,38 +111,49 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
             cp_async16(vs + key * RS + ch * 16, reinterpret_cast<const uint8_t *>(vc) + ((size_t)key * RC + ch) * 16);
         }
     }
+    // What does not depend on the projections is fetched before the dependency wait: the RoPE position
+    // (written at the end of the previous step, like pos) and this thread's entries of the static tables.
+    // Thread i < REP * D/2 rotates pair i of the REP query heads; in the CTA whose range holds row `pos`,
+    // thread i < D/2 also rotates pair i of the new K and appends K and V.
+    static_assert(REP * 64 <= kAttnThreads, "one query pair per thread");
+    const int rp = *p.rope_pos;
+    const float *cs = p.cos_t + (size_t)rp * D, *sn = p.sin_t + (size_t)rp * D;
+    const bool rot_q = tid < REP * (D / 2);
+    const bool app = pos >= t0 && pos < t1 && tid < D / 2;
+    const int hq = tid / (D / 2), jq = (tid - hq * (D / 2)) * 2, jk = 2 * tid;
+    float cq = 0.f, sq = 0.f, ck = 0.f, sk = 0.f;
+    if (rot_q) { cq = __ldg(cs + jq); sq = __ldg(sn + jq); }
+    if (app) { ck = __ldg(cs + jk); sk = __ldg(sn + jk); }
     if (p.use_pdl) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
     if (tid == 0) span_event(p.span, 1);
+    // all loads of the new projections first (one round trip), then the arithmetic
+    float q0 = 0.f, q1 = 0.f, k0f = 0.f, k1f = 0.f, v0f = 0.f, v1f = 0.f;
+    const size_t qi = (size_t)(kvh * REP + hq) * D + jq;
+    const size_t kn = (size_t)p.H * D + (size_t)kvh * D, vn = (size_t)(p.H + p.KVH) * D + (size_t)kvh * D;
+    if (rot_q) { q0 = ld_qkv(p, qi); q1 = ld_qkv(p, qi + 1); }
+    if (app) { k0f = ld_qkv(p, kn + jk); k1f = ld_qkv(p, kn + jk + 1); v0f = ld_qkv(p, vn + jk); v1f = ld_qkv(p, vn + jk + 1); }
     // RoPE (crates/tl_cpu/src/ffi.rs:2629-2685: adjacent pairs, one table row) of the REP query heads
-    const int rp = *p.rope_pos;
-    const float *cs = p.cos_t + (size_t)rp * D, *sn = p.sin_t + (size_t)rp * D;
-    for (int i = tid; i < REP * (D / 2); i += kAttnThreads) {
-        int h = i / (D / 2), j = (i - h * (D / 2)) * 2;
-        const size_t qi = (size_t)(kvh * REP + h) * D + j;
-        float x0 = ld_qkv(p, qi), x1 = ld_qkv(p, qi + 1), c = cs[j], s = sn[j];
-        qs[h * D + j] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        qs[h * D + j + 1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    if (rot_q) {
+        qs[hq * D + jq] = __fsub_rn(__fmul_rn(q0, cq), __fmul_rn(q1, sq));
+        qs[hq * D + jq + 1] = __fadd_rn(__fmul_rn(q0, sq), __fmul_rn(q1, cq));
     }
     // the CTA whose range holds row `pos` appends the new token's K (roped) and V
-    if (pos >= t0 && pos < t1) {
-        const size_t kn = (size_t)p.H * D + (size_t)kvh * D, vn = (size_t)(p.H + p.KVH) * D + (size_t)kvh * D;
+    if (app) {
         T *kc = reinterpret_cast<T *>(p.kcache) + ((size_t)kvh * p.max_seq + pos) * D;
         T *vc = reinterpret_cast<T *>(p.vcache) + ((size_t)kvh * p.max_seq + pos) * D;
         T *krow = reinterpret_cast<T *>(Ks + (size_t)(pos - t0) * RS), *vrow = reinterpret_cast<T *>(Vs + (size_t)(pos - t0) * RS);
-        for (int i = tid; i < D / 2; i += kAttnThreads) {
-            int j = 2 * i;
-            float x0 = ld_qkv(p, kn + j), x1 = ld_qkv(p, kn + j + 1), c = cs[j], s = sn[j];
-            T k0 = KvTraits<T>::store(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
-            T k1 = KvTraits<T>::store(__fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c)));
-            T v0 = KvTraits<T>::store(ld_qkv(p, vn + j)), v1 = KvTraits<T>::store(ld_qkv(p, vn + j + 1));
-            krow[j] = k0; krow[j + 1] = k1; vrow[j] = v0; vrow[j + 1] = v1;
-            kc[j] = k0; kc[j + 1] = k1; vc[j] = v0; vc[j + 1] = v1;
-        }
+        T k0 = KvTraits<T>::store(__fsub_rn(__fmul_rn(k0f, ck), __fmul_rn(k1f, sk)));
+        T k1 = KvTraits<T>::store(__fadd_rn(__fmul_rn(k0f, sk), __fmul_rn(k1f, ck)));
+        T v0 = KvTraits<T>::store(v0f), v1 = KvTraits<T>::store(v1f);
+        krow[jk] = k0; krow[jk + 1] = k1; vrow[jk] = v0; vrow[jk + 1] = v1;
+        kc[jk] = k0; kc[jk + 1] = k1; vc[jk] = v0; vc[jk + 1] = v1;
     }
+    if (tid == 0) span_event(p.span, 6);
     cp_async_wait_all();
+    if (tid == 0) span_event(p.span, 7);
     __syncthreads();
     if (tid == 0) span_event(p.span, 2);
 

@@ -57,7 +57,7 @@ struct tlb_decoder {
 
 namespace {
 
-constexpr int kArgmaxBlocks = 64;
+constexpr int kArgmaxBlocks = 148;
 
 // argmax over the logits + advance of the decode state, in one launch.  Tie rule as tlb_argmax.
 __global__ void argmax_advance_kernel(const float *__restrict__ xs, int slices, long long stride, float *__restrict__ x_sum, int n,
@@ -102,14 +102,21 @@ __global__ void argmax_advance_kernel(const float *__restrict__ xs, int slices, 
         last = (atomicAdd(counter, 1) == (int)gridDim.x - 1);
     }
     __syncthreads();
-    if (!last || threadIdx.x != 0) return;
+    if (!last || threadIdx.x >= 32) return;
+    // the last block's first warp folds the per-block winners: one round of loads, then shuffles
     __threadfence();
     bv = 0.f; bi = -1;
-    for (int i = 0; i < (int)gridDim.x; i++) {
+    for (int i = lane; i < (int)gridDim.x; i += 32) {
         float v = __ldcg(pv + i);
         long long ix = __ldcg(pi + i);
         if (ix >= 0 && better(v, ix, bv, bi)) { bv = v; bi = ix; }
     }
+    for (int o = 16; o; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane != 0) return;
     if (bi < 0) bi = 0;
     int idx = state[3];
     if (tokens_out && idx < tokens_cap) tokens_out[idx] = (int)bi;
@@ -183,6 +190,14 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             set_w(j, 2, w.v, d->qkv + qd + kvd, nqkv);
            
             j.type = w.q->type; j.k = dm; j.m = 1; j.slices = d->force_slices[0];
+            {   // while q|k|v streams, this layer's KV rows are pulled into L2 for the attention kernel that follows
+                const size_t es = c.kv_f16 ? 2 : 4;
+                j.pf_base[0] = (char *)d->kcache + (size_t)l * d->kv_layer_elems * es;
+                j.pf_base[1] = (char *)d->vcache + (size_t)l * d->kv_layer_elems * es;
+                j.pf_rows = d->state + 1;
+                j.pf_heads = c.n_kv_heads; j.pf_row_bytes = (int)(c.head_dim * es);
+                j.pf_head_stride = (int64_t)c.max_seq * c.head_dim * es;
+            }
             j.prologue = PRO_ADD_NORM;
             j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
             // the residual lives in xb here: the embedding row for layer 0, else what the last down launch left

@@ -134,11 +134,27 @@ __device__ __forceinline__ void quantise_block(const MvParams &p, uint8_t *smem,
 //
 // `after_loads(dep)` is called once per thread when the values it requested have arrived (dep is
 // computed from them): the caller uses it to start traffic that should not delay those loads.
+//
+// The norm weights are static, so the caller fetches those of the first pass with
+// load_norm_weights() BEFORE it waits for the previous kernel: they are read once per token and
+// always miss L2, which would otherwise be the longest latency of the prologue.
+constexpr int kKeep = 2;   // blocks per group handled in one pass
+
+__device__ __forceinline__ void load_norm_weights(const MvParams &p, int tid, int nthreads, int blk0, int nb, float4 (&wgt)[kKeep])
+{
+    const int ngroups = nthreads >> 6, grp = tid >> 6, j = tid & 63;
+#pragma unroll
+    for (int i = 0; i < kKeep; i++) {
+        wgt[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int item = grp + i * ngroups;     // ADD_NORM has one activation row: item == local block
+        if (p.prologue == PRO_ADD_NORM && item < nb) wgt[i] = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + (blk0 + item) * 64 + j);
+    }
+}
+
 template <int FMT, typename AfterLoads>
 __device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem, int tid, int nthreads, int blk0, int nb,
-                                 AfterLoads after_loads)
+                                 const float4 (&wgt_first)[kKeep], AfterLoads after_loads)
 {
-    constexpr int kKeep = 2;   // blocks per group handled in one pass
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
     const int ngroups = nthreads >> 6, grp = tid >> 6, j = tid & 63;
     const int nblk = p.k / 256, n_mine = p.m * nb;
@@ -156,7 +172,7 @@ __device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem,
             if (item < n_mine) {
                 const int mrow = item / nb, lb = item - mrow * nb, k4 = (blk0 + lb) * 64 + j;
                 keep[i] = prologue_value(p, emb, mrow, k4, 0.f);
-                if (norm) wgt[i] = __ldg(reinterpret_cast<const float4 *>(p.norm_w) + k4);
+                if (norm) wgt[i] = first == 0 ? wgt_first[i] : __ldg(reinterpret_cast<const float4 *>(p.norm_w) + k4);
             }
         }
         if (norm && first == 0 && p.ssq_parts) {
