@@ -48,9 +48,7 @@ template <> struct KvTraits<float> {
 };
 
 struct AttnParams {
-    const float *qkv;        // K-slices of the projection output, added in index order when read
-    int qkv_slices;
-    long long qkv_stride;
+    const float *qkv;
     void *kcache, *vcache;
     int H, KVH, D, max_seq;
     const int *pos, *rope_pos;
@@ -65,12 +63,7 @@ struct AttnParams {
     unsigned long long *span;
 };
 
-__device__ __forceinline__ float ld_qkv(const AttnParams &p, size_t i)
-{
-    float a = __ldcg(p.qkv + i);
-    for (int s = 1; s < p.qkv_slices; s++) a += __ldcg(p.qkv + (size_t)s * p.qkv_stride + i);
-    return a;
-}
+__device__ __forceinline__ float ld_qkv(const AttnParams &p, size_t i) { return __ldcg(p.qkv + i); }
 
 template <typename T, int REP>
 __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const AttnParams p)
@@ -315,7 +308,7 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     if (j.H % j.KVH) return fail(TLB_ERR_SHAPE, "query heads must be a multiple of KV heads");
     int rep = j.H / j.KVH;
     AttnParams p;
-    p.qkv = j.qkv.p; p.qkv_slices = j.qkv.slices < 1 ? 1 : j.qkv.slices; p.qkv_stride = j.qkv.stride; p.kcache = j.kcache; p.vcache = j.vcache;
+    p.qkv = j.qkv; p.kcache = j.kcache; p.vcache = j.vcache;
     p.H = j.H; p.KVH = j.KVH; p.D = j.D; p.max_seq = j.max_seq;
     p.pos = j.pos; p.rope_pos = j.rope_pos; p.cos_t = j.cos_t; p.sin_t = j.sin_t; p.scale = j.scale;
     p.partial = j.partial; p.counters = j.counters; p.max_splits = j.splits; p.out = j.out;

@@ -3,16 +3,19 @@
 // (examples/apps/llama3/chatbot_llama3.tl:66-125,220-236; examples/apps/tinyllama/chatbot.tl:50-113),
 // which issue ~40 single-op FFI calls per layer per token, each followed by a device-wide sync
 // (crates/tl_cuda/src/stream.rs:69-73).  Here:
-//   K1  residual add + RMSNorm*w (prologue)  ->  q|k|v matvec            (embedding lookup for layer 0)
+//   K1  RMSNorm*w (prologue)  ->  q|k|v matvec        (layer 0: embedding lookup + sum of squares here too;
+//                                                      side job: this layer's KV rows are pulled into L2)
 //   K2  RoPE(q, k) + KV append + split-K attention + merge
-//   K3  o_proj matvec
-//   K4  residual add + RMSNorm*w (prologue)  ->  gate|up matvec
-//   K5  SiLU(gate)*up (prologue)             ->  down matvec
+//   K3  o_proj matvec         ->  residual add, per-tile sums of squares (tile finishing)
+//   K4  RMSNorm*w (prologue)  ->  gate|up matvec over interleaved rows  ->  SiLU(gate)*up (tile finishing)
+//   K5  down matvec           ->  residual add, per-tile sums of squares (tile finishing)
 //   ... output_norm (prologue) -> lm_head matvec, argmax + position advance.
-// Every buffer of the chain is written in full by its producer (no accumulation, no clearing).
-// The residual stream ping-pongs between two buffers so no kernel updates memory that another CTA
-// of the same launch reads.  All kernels are launched with programmatic dependent launch, so a
-// kernel's weight prefetch overlaps its predecessor's tail.
+// A residual add thus happens where the projection's rows are finished, and the RMSNorm that follows
+// adds up d_model/16 partial sums instead of re-reading the row in every CTA.  Every buffer of the chain
+// is written in full by its producer (no accumulation, no clearing).  The residual stream ping-pongs
+// between two buffers so no kernel updates memory that another CTA of the same launch reads.  All
+// kernels are launched with programmatic dependent launch: what a kernel can fetch without its
+// predecessor's results (weights, norm weights, RoPE tables, older KV rows) is requested before it waits.
 #include "tlb_internal.h"
 
 #include <cstdlib>
@@ -31,8 +34,8 @@ struct tlb_decoder {
     tlb_tensor *emb = nullptr, *out_norm = nullptr;
     tlb_qtensor *head = nullptr;
     // device state
-    float *xa = nullptr, *xb = nullptr, *qkv = nullptr, *attn = nullptr, *o_out = nullptr, *gu = nullptr,
-          *down_out = nullptr, *logits = nullptr, *cos_t = nullptr, *sin_t = nullptr, *partial = nullptr;
+    float *xa = nullptr, *xb = nullptr;   // residual stream, ping-pong: xb enters a layer and leaves it, xa holds it after o_proj
+    float *qkv = nullptr, *attn = nullptr, *logits = nullptr, *cos_t = nullptr, *sin_t = nullptr, *partial = nullptr;
     void *kcache = nullptr, *vcache = nullptr;
     int *state = nullptr;        // [0] token, [1] pos, [2] rope_pos, [3] output index
     int *counters = nullptr;     // attention merge counters [KVH], argmax counter at [KVH]
@@ -41,10 +44,8 @@ struct tlb_decoder {
     float *amax_v = nullptr;
     long long *amax_i = nullptr;
     int *h_state = nullptr;      // pinned host staging [4]
-    float *logits_sl = nullptr;  // K-slices of the head matvec; `logits` holds their sum after the argmax kernel
     float *hbuf = nullptr;       // silu(gate) * up, written by the gate|up launch
     float *ssq_o = nullptr, *ssq_d = nullptr;   // per-tile sums of squares of the residual after o_proj / down
-    int s_qkv = 1, s_o = 1, s_gu = 1, s_down = 1, s_head = 1;   // K-slices of each matvec of the chain
     int max_splits = 1;
     cudaGraphExec_t graph = nullptr;
     uint64_t graph_kernels = 0;
@@ -60,9 +61,8 @@ namespace {
 constexpr int kArgmaxBlocks = 148;
 
 // argmax over the logits + advance of the decode state, in one launch.  Tie rule as tlb_argmax.
-__global__ void argmax_advance_kernel(const float *__restrict__ xs, int slices, long long stride, float *__restrict__ x_sum, int n,
-                                      int tie_first, float *pv, long long *pi, int *counter, int *state, int *tokens_out,
-                                      int tokens_cap, int use_pdl)
+__global__ void argmax_advance_kernel(const float *__restrict__ x, int n, int tie_first, float *pv, long long *pi, int *counter,
+                                      int *state, int *tokens_out, int tokens_cap, int use_pdl)
 {
     if (use_pdl) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -80,9 +80,7 @@ __global__ void argmax_advance_kernel(const float *__restrict__ xs, int slices, 
         return tie_first ? i < ci : i > ci;
     };
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        float v = __ldcg(xs + i);
-        for (int s = 1; s < slices; s++) v += __ldcg(xs + (size_t)s * stride + i);   // the head's K-slices, index order
-        x_sum[i] = v;
+        const float v = __ldcg(x + i);
         if (better(v, i, bv, bi)) { bv = v; bi = i; }
     }
     for (int o = 16; o; o >>= 1) {
@@ -155,20 +153,12 @@ tlb_status get_f(tlb_map *m, const std::string &name, tlb_tensor **t, int64_t nu
     return TLB_OK;
 }
 
-void set_w(MatvecJob &j, int i, const tlb_qtensor *q, float *out, int64_t out_stride)
+void set_w(MatvecJob &j, int i, const tlb_qtensor *q, float *out)
 {
     j.w[i] = q->dev();
     j.n_tiles[i] = q->n_tiles;
     j.n_rows[i] = q->n;
     j.out[i] = out;
-    j.out_stride[i] = out_stride;
-}
-
-SlicedVec sliced(const float *p, int slices, int64_t stride)
-{
-    SlicedVec v;
-    v.p = p; v.slices = slices; v.stride = stride;
-    return v;
 }
 
 // the kernel chain of one decode step (launched eagerly or into a capturing stream)
@@ -179,15 +169,14 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
     auto next_span = [&]() { return span ? span + 8 * (span_i++) : nullptr; };   // timeline slot of the next launch
     const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
     const int L = c.n_layers;
-    const int64_t nqkv = qd + 2 * kvd;
     for (int l = 0; l < L; l++) {
         const LayerW &w = d->layers[l];
         {   // K1
             MatvecJob j;
             j.n_w = 3;
-            set_w(j, 0, w.q, d->qkv, nqkv);
-            set_w(j, 1, w.k, d->qkv + qd, nqkv);
-            set_w(j, 2, w.v, d->qkv + qd + kvd, nqkv);
+            set_w(j, 0, w.q, d->qkv);
+            set_w(j, 1, w.k, d->qkv + qd);
+            set_w(j, 2, w.v, d->qkv + qd + kvd);
            
             j.type = w.q->type; j.k = dm; j.m = 1; j.slices = d->force_slices[0];
             {   // while q|k|v streams, this layer's KV rows are pulled into L2 for the attention kernel that follows
@@ -202,7 +191,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
             // the residual lives in xb here: the embedding row for layer 0, else what the last down launch left
             if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; j.x_out = d->xb; }
-            else { j.x = sliced(d->xb, 1, 0); j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16; }
+            else { j.x = d->xb; j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16; }
             j.pdl = d->pdl;
             j.span = next_span();
             j.dry_run = d->dry;
@@ -210,7 +199,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         }
         {   // K2
             DecodeAttnJob a;
-            a.qkv = sliced(d->qkv, d->s_qkv, nqkv);
+            a.qkv = d->qkv;
             a.kcache = (char *)d->kcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
             a.vcache = (char *)d->vcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
             a.kv_f16 = c.kv_f16; a.H = c.n_heads; a.KVH = c.n_kv_heads; a.D = c.head_dim; a.max_seq = c.max_seq;
@@ -222,9 +211,9 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         {   // K3
             MatvecJob j;
             j.n_w = 1;
-            set_w(j, 0, w.o, d->xa, dm);
+            set_w(j, 0, w.o, d->xa);
             j.type = w.o->type; j.k = qd; j.m = 1; j.slices = d->force_slices[1];
-            j.prologue = PRO_PLAIN; j.x = sliced(d->attn, 1, 0);
+            j.prologue = PRO_PLAIN; j.x = d->attn;
             j.finish = FIN_RESID; j.resid = d->xb; j.ssq_out = d->ssq_o;   // xa = xb + o_proj(attn)
             j.pdl = d->pdl;
             j.span = next_span();
@@ -234,9 +223,9 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         {   // K4
             MatvecJob j;
             j.n_w = 1;
-            set_w(j, 0, w.gu, d->hbuf, F);
+            set_w(j, 0, w.gu, d->hbuf);
             j.type = w.gu->type; j.k = dm; j.m = 1; j.slices = d->force_slices[2];
-            j.prologue = PRO_ADD_NORM; j.x = sliced(d->xa, 1, 0); j.ssq_parts = d->ssq_o; j.n_parts = (dm + 15) / 16;
+            j.prologue = PRO_ADD_NORM; j.x = d->xa; j.ssq_parts = d->ssq_o; j.n_parts = (dm + 15) / 16;
             j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
             j.finish = FIN_SILU;
             j.pdl = d->pdl;
@@ -247,9 +236,9 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
         {   // K5
             MatvecJob j;
             j.n_w = 1;
-            set_w(j, 0, w.down, d->xb, dm);
+            set_w(j, 0, w.down, d->xb);
             j.type = w.down->type; j.k = F; j.m = 1; j.slices = d->force_slices[3];
-            j.prologue = PRO_PLAIN; j.x = sliced(d->hbuf, 1, 0);
+            j.prologue = PRO_PLAIN; j.x = d->hbuf;
             j.finish = FIN_RESID; j.resid = d->xa; j.ssq_out = d->ssq_d;   // xb = xa + down(h)
             j.pdl = d->pdl;
             j.span = next_span();
@@ -260,9 +249,9 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
     {   // output_norm + head
         MatvecJob j;
         j.n_w = 1;
-        set_w(j, 0, d->head, d->logits_sl, c.vocab);
+        set_w(j, 0, d->head, d->logits);
         j.type = d->head->type; j.k = dm; j.m = 1; j.slices = d->force_slices[4];
-        j.prologue = PRO_ADD_NORM; j.x = sliced(d->xb, 1, 0); j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16;
+        j.prologue = PRO_ADD_NORM; j.x = d->xb; j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16;
         j.norm_w = d->out_norm->f32(); j.eps = c.eps;
         j.last_of_chain = true;
         j.pdl = d->pdl;
@@ -287,8 +276,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             TLB_CUDA(cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
             carveout_set = true;
         }
-        TLB_CUDA(cudaLaunchKernelEx(&cfg, argmax_advance_kernel, (const float *)d->logits_sl, d->s_head, (long long)c.vocab, d->logits,
-                                    (int)c.vocab, (int)(c.tie_rule == TLB_TIE_FIRST), d->amax_v, d->amax_i, d->counters + c.n_kv_heads,
+        TLB_CUDA(cudaLaunchKernelEx(&cfg, argmax_advance_kernel, (const float *)d->logits, (int)c.vocab, (int)(c.tie_rule == TLB_TIE_FIRST), d->amax_v, d->amax_i, d->counters + c.n_kv_heads,
                                     d->state, d->tokens_out, d->tokens_cap, (int)d->pdl));
         count_launch();
     }
@@ -382,8 +370,6 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     TRY_D(get_q(m, "output.weight", &d->head, c.vocab, dm, -1));
     {
         const LayerW &w0 = d->layers[0];
-        // The matvec folds its K-slices itself (last warp of a tile), so every buffer of the chain is a
-        // plain vector: one slice each.
         for (const LayerW &w : d->layers)
             if (w.q->type != w0.q->type || w.o->type != w0.o->type || w.gate->type != w0.gate->type || w.down->type != w0.down->type) {
                 tlb_decoder_destroy(d);
@@ -404,10 +390,10 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
         }
     }
     TRY_D(dalloc(d, &d->xa, dm)); TRY_D(dalloc(d, &d->xb, dm));
-    TRY_D(dalloc(d, &d->qkv, (size_t)d->s_qkv * (qd + 2 * kvd))); TRY_D(dalloc(d, &d->attn, qd));
+    TRY_D(dalloc(d, &d->qkv, qd + 2 * kvd)); TRY_D(dalloc(d, &d->attn, qd));
     TRY_D(dalloc(d, &d->hbuf, F));
     TRY_D(dalloc(d, &d->ssq_o, (dm + 15) / 16)); TRY_D(dalloc(d, &d->ssq_d, (dm + 15) / 16));
-    TRY_D(dalloc(d, &d->logits_sl, (size_t)d->s_head * c.vocab)); TRY_D(dalloc(d, &d->logits, c.vocab));
+    TRY_D(dalloc(d, &d->logits, c.vocab));
     d->kv_layer_elems = (size_t)kvd * c.max_seq;
     size_t kv_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
     TRY_D(dalloc(d, (char **)&d->kcache, kv_bytes)); TRY_D(dalloc(d, (char **)&d->vcache, kv_bytes));
@@ -542,7 +528,7 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
     if (copies < 1) copies = 1;
     if (copies > c.n_layers) copies = c.n_layers;
     std::string w(which);
-    if (w == "chain") {
+    if (w == "chain" || w == "chain_graph") {
         // Timeline of one whole decode step launched eagerly (same launches as the graph): `copies` is the
         // cache position, `iters` the warm-up steps.  Printed to stderr: per launch, microseconds from the
         // start of the step to first CTA start / last dependency wait passed / last prologue done / end.
@@ -558,8 +544,24 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         cudaStreamSynchronize(ctx()->stream);
         cudaEvent_t e0, e1;
         cudaEventCreate(&e0); cudaEventCreate(&e1);
+        cudaGraphExec_t gexec = nullptr;
+        if (w == "chain_graph" && st == TLB_OK) {   // the same step as one graph launch, probes baked in
+            cudaGraph_t g = nullptr;
+            TLB_CUDA(cudaStreamBeginCapture(ctx()->stream, cudaStreamCaptureModeThreadLocal));
+            st = enqueue_step(d, span);
+            cudaError_t ce = cudaStreamEndCapture(ctx()->stream, &g);
+            if (st == TLB_OK && ce != cudaSuccess) st = cuda_fail(ce, "cudaStreamEndCapture");
+            if (st == TLB_OK) { ce = cudaGraphInstantiate(&gexec, g, 0); if (ce != cudaSuccess) st = cuda_fail(ce, "cudaGraphInstantiate"); }
+            if (g) cudaGraphDestroy(g);
+            for (int i = 0; i < 3 && st == TLB_OK; i++) cudaGraphLaunch(gexec, ctx()->stream);   // warm-up replays
+            cudaMemcpyAsync(span, h.data(), h.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice, ctx()->stream);
+            cudaStreamSynchronize(ctx()->stream);
+        }
         cudaEventRecord(e0, ctx()->stream);
-        if (st == TLB_OK) st = enqueue_step(d, span);
+        if (st == TLB_OK) {
+            if (gexec) { cudaGraphLaunch(gexec, ctx()->stream); cudaGraphLaunch(gexec, ctx()->stream); }   // two back-to-back replays
+            else st = enqueue_step(d, span);
+        }
         cudaEventRecord(e1, ctx()->stream);
         cudaEventSynchronize(e1);
         float ms = 0.f;
@@ -567,6 +569,7 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         cudaMemcpy(h.data(), span, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
         cudaFree(span);
         cudaEventDestroy(e0); cudaEventDestroy(e1);
+        if (gexec) { cudaGraphExecDestroy(gexec); ms *= 0.5f; }
         if (st != TLB_OK) return st;
         const unsigned long long t0 = h[0];
         const char *names[5] = {"qkv", "attn", "o", "gate_up", "down"};
@@ -615,19 +618,19 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         const LayerW &lw = d->layers[(it + 3) % copies];
         MatvecJob j;
         float *o = outb;
-        j.m = 1; j.prologue = PRO_PLAIN; j.x = sliced(xin, 1, 0);
+        j.m = 1; j.prologue = PRO_PLAIN; j.x = xin;
         if (w == "qkv") {
-            j.n_w = 3; set_w(j, 0, lw.q, o, out_n); set_w(j, 1, lw.k, o + qd, out_n); set_w(j, 2, lw.v, o + qd + kvd, out_n);
+            j.n_w = 3; set_w(j, 0, lw.q, o); set_w(j, 1, lw.k, o + qd); set_w(j, 2, lw.v, o + qd + kvd);
             j.type = lw.q->type; j.k = dm; bytes = lw.q->nbytes() + lw.k->nbytes() + lw.v->nbytes();
         } else if (w == "o") {
-            j.n_w = 1; set_w(j, 0, lw.o, o, out_n); j.type = lw.o->type; j.k = qd; bytes = lw.o->nbytes();
+            j.n_w = 1; set_w(j, 0, lw.o, o); j.type = lw.o->type; j.k = qd; bytes = lw.o->nbytes();
         } else if (w == "gate_up") {
-            j.n_w = 1; set_w(j, 0, lw.gu, o, out_n); j.type = lw.gu->type; j.k = dm; j.finish = FIN_SILU;
+            j.n_w = 1; set_w(j, 0, lw.gu, o); j.type = lw.gu->type; j.k = dm; j.finish = FIN_SILU;
             bytes = lw.gu->nbytes();
         } else if (w == "down") {
-            j.n_w = 1; set_w(j, 0, lw.down, o, out_n); j.type = lw.down->type; j.k = F; bytes = lw.down->nbytes();
+            j.n_w = 1; set_w(j, 0, lw.down, o); j.type = lw.down->type; j.k = F; bytes = lw.down->nbytes();
         } else {
-            j.n_w = 1; set_w(j, 0, d->head, o, out_n); j.type = d->head->type; j.k = dm; bytes = d->head->nbytes();
+            j.n_w = 1; set_w(j, 0, d->head, o); j.type = d->head->type; j.k = dm; bytes = d->head->nbytes();
             j.last_of_chain = true;
         }
         j.pdl = d->pdl;   // as in the decode chain: a launch's set-up overlaps its predecessor

@@ -401,26 +401,6 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
 #undef STAMP
 }
 
-// out[i] = slice 0 + slice 1 + ... (index order)
-__global__ void sum_slices_kernel(const float *__restrict__ src, int slices, long long stride, float *__restrict__ out, long long n)
-{
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        float a = src[i];
-        for (int s = 1; s < slices; s++) a += src[(size_t)s * stride + i];
-        out[i] = a;
-    }
-}
-
-tlb_status launch_sum_slices(const float *src, int slices, int64_t stride, float *out, int64_t n)
-{
-    if (n == 0) return TLB_OK;
-    int blocks = (int)std::min<int64_t>(1184, (n + 255) / 256);
-    sum_slices_kernel<<<blocks, 256, 0, ctx()->stream>>>(src, slices, (long long)stride, out, (long long)n);
-    TLB_CUDA(cudaGetLastError());
-    count_launch();
-    return TLB_OK;
-}
-
 // ---------------------------------------------------------------- host side
 
 struct SmemPlan { int off_xq, off_alam, off_xsum, off_sa, off_minv, off_misc, col_stride; size_t fixed; };
@@ -630,16 +610,12 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     if (job.finish != FIN_PLAIN && (job.m != 1 || job.n_w != 1)) return fail(TLB_ERR_ARG, "fused tile finishing takes one tensor and one activation row");
     if (job.finish == FIN_RESID && (!job.resid || !job.ssq_out)) return fail(TLB_ERR_NULL, "null residual or statistics buffer");
     if (job.ssq_parts && (job.prologue != PRO_ADD_NORM || job.n_parts < 1)) return fail(TLB_ERR_ARG, "partial sums of squares go with the fused RMSNorm prologue");
-    if (p.x.slices < 1) p.x.slices = 1;
-    if (p.x2.slices < 1) p.x2.slices = 1;
-    if ((p.x.slices > 1 && p.x.stride % 4) || (p.x2.slices > 1 && p.x2.stride % 4))
-        return fail(TLB_ERR_ARG, "slice strides of the activation must be multiples of 4 floats");
     p.err = c->err_flag;
     p.use_pdl = job.pdl ? 1 : 0;
     p.trace = job.trace;
     p.span = job.span;
-    if (!p.x.p && !(p.prologue == PRO_ADD_NORM && p.token)) return fail(TLB_ERR_NULL, "null activation");
-    if (p.prologue == PRO_SILU_MUL && !p.x2.p) return fail(TLB_ERR_NULL, "null activation");
+    if (!p.x && !(p.prologue == PRO_ADD_NORM && p.token)) return fail(TLB_ERR_NULL, "null activation");
+    if (p.prologue == PRO_SILU_MUL && !p.x2) return fail(TLB_ERR_NULL, "null activation");
     if (job.dry_run) return TLB_OK;   // the shape is launchable
     switch (job.type) {
     case TLB_GGML_Q4_K: return launch_fmt<TLB_GGML_Q4_K>(p, grid, smem, job.pdl);
@@ -679,7 +655,7 @@ extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, 
         job.type = w->type;
         job.k = k;
         job.m = (int)std::min<int64_t>(4, m - m0);
-        job.x.p = x->f32() + m0 * k;
+        job.x = x->f32() + m0 * k;
         st = launch_qmatvec(job);
     }
     if (st != TLB_OK) { tlb_tensor_release(*out); *out = nullptr; }

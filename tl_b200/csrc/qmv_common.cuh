@@ -182,8 +182,8 @@ struct MvParams {
     int pf_heads, pf_row_bytes;
     long long pf_head_stride;  // bytes between heads
     int prologue;
-    SlicedVec x;              // PLAIN: x [M,K]; ADD_NORM: residual; SILU_MUL: gate
-    SlicedVec x2;             // ADD_NORM: delta added to x (p == null: none); SILU_MUL: up
+    const float *x;           // PLAIN: x [M,K]; ADD_NORM: residual; SILU_MUL: gate
+    const float *x2;          // ADD_NORM: delta added to x (null: none); SILU_MUL: up
     const float *norm_w;
     const float *ssq_parts;   // ADD_NORM: partial sums of squares of x left by its producer (null: computed here)
     int n_parts;
@@ -212,16 +212,11 @@ struct MvShared {
 
 __device__ __forceinline__ float silu_f(float g) { return g * (1.0f / (1.0f + expf(-g))); }
 
-// Elements 4*i4 .. 4*i4+3 of a sliced vector: slice 0 + slice 1 + ... in that fixed order.  The data was
-// written by an earlier kernel of the stream, hence the L2-coherent loads.
-__device__ __forceinline__ float4 ld_sliced4(const SlicedVec &v, size_t i4)
+// Elements 4*i4 .. 4*i4+3 of an activation written by an earlier kernel of the stream, hence the
+// L2-coherent load.
+__device__ __forceinline__ float4 ld_act4(const float *v, size_t i4)
 {
-    float4 a = __ldcg(reinterpret_cast<const float4 *>(v.p) + i4);
-    for (int s = 1; s < v.slices; s++) {
-        const float4 d = __ldcg(reinterpret_cast<const float4 *>(v.p + (size_t)s * v.stride) + i4);
-        a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
-    }
-    return a;
+    return __ldcg(reinterpret_cast<const float4 *>(v) + i4);
 }
 
 // Activation elements 4*k4 .. 4*k4+3 of row `mrow` as the matvec consumes them.  inv_rms == 0 selects
@@ -230,10 +225,10 @@ __device__ __forceinline__ float4 ld_sliced4(const SlicedVec &v, size_t i4)
 __device__ __forceinline__ float4 prologue_value(const MvParams &p, const float *emb, int mrow, int k4, float inv_rms)
 {
     const size_t row4 = (size_t)mrow * (p.k / 4) + k4;
-    float4 v = emb ? __ldg(reinterpret_cast<const float4 *>(emb) + row4) : ld_sliced4(p.x, row4);
+    float4 v = emb ? __ldg(reinterpret_cast<const float4 *>(emb) + row4) : ld_act4(p.x, row4);
     if (p.prologue == PRO_ADD_NORM) {
-        if (p.x2.p) {
-            const float4 d = ld_sliced4(p.x2, row4);
+        if (p.x2) {
+            const float4 d = ld_act4(p.x2, row4);
             v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
         }
         if (inv_rms != 0.f) {  // (x / rms) * weight (crates/tl_cpu/src/ffi.rs:2444-2486), the division as a multiply by 1/rms
@@ -242,7 +237,7 @@ __device__ __forceinline__ float4 prologue_value(const MvParams &p, const float 
             v.z = (v.z * inv_rms) * w.z; v.w = (v.w * inv_rms) * w.w;
         }
     } else if (p.prologue == PRO_SILU_MUL) {
-        const float4 u = ld_sliced4(p.x2, row4);
+        const float4 u = ld_act4(p.x2, row4);
         v.x = silu_f(v.x) * u.x; v.y = silu_f(v.y) * u.y; v.z = silu_f(v.z) * u.z; v.w = silu_f(v.w) * u.w;
     }
     return v;

@@ -118,15 +118,7 @@ tlb_status launch_interleave8(int type, const uint8_t *a, const uint8_t *b, uint
 // How the activation vector of a streaming matvec is produced inside the kernel.
 enum Prologue { PRO_PLAIN = 0, PRO_ADD_NORM = 1, PRO_SILU_MUL = 2 };
 enum Finish { FIN_PLAIN = 0, FIN_RESID = 1, FIN_SILU = 2 };
-constexpr int kMaxSlices = 16;   // most K-slices a matvec may split its output into
-// A vector kept as the element-wise sum of `slices` arrays `stride` floats apart: the form in which
-// the streaming matvec leaves its output (one array per K-slice, each element written exactly once).
-// Readers add the slices in index order when they load.  slices == 1 is a plain array.
-struct SlicedVec {
-    const float *p = nullptr;
-    int slices = 1;
-    long long stride = 0;
-};
+constexpr int kMaxSlices = 16;   // most K-slices a matvec may cut its launch into
 struct MatvecJob {
     // up to 3 weight tensors sharing K and the same activation (q|k|v, gate|up)
     int n_w = 0;
@@ -135,15 +127,14 @@ struct MatvecJob {
     int64_t n_rows[3] = {0, 0, 0};                 // valid output rows (<= n_tiles*16)
     // Output of tensor i: [M, n_rows], every element written (no clearing needed).
     float *out[3] = {nullptr, nullptr, nullptr};
-    int64_t out_stride[3] = {0, 0, 0};
     int slices = 0;                  // K-slices the launch is cut into; 0: chosen by qmatvec_plan_slices()
     int type = 0;
     int64_t k = 0;
     int m = 1;
     // prologue inputs
     int prologue = PRO_PLAIN;
-    SlicedVec x;                     // PLAIN: x [M,K]; ADD_NORM: residual [K]; SILU_MUL: gate [M,K]
-    SlicedVec x2;                    // ADD_NORM: delta added to x (p may be null); SILU_MUL: up
+    const float *x = nullptr;        // PLAIN: x [M,K]; ADD_NORM: residual [K]; SILU_MUL: gate [M,K]
+    const float *x2 = nullptr;       // ADD_NORM: delta added to x (may be null); SILU_MUL: up
     const float *norm_w = nullptr;   // ADD_NORM: weight [K]
     float eps = 0.f;
     float *x_out = nullptr;          // ADD_NORM: x + x2 written here by block 0 (may be null)
@@ -178,7 +169,6 @@ tlb_status launch_qmatvec(const MatvecJob &job);
 // at most max_slices; a pure function of its arguments, so producer and consumer agree without talking.
 int qmatvec_plan_slices(int type, int64_t k, int m, int64_t tiles, int max_slices);
 size_t qmatvec_max_k(int m);   // largest K the single-pass kernel supports for m activation rows
-tlb_status launch_sum_slices(const float *src, int slices, int64_t stride, float *out, int64_t n);
 
 // ops.cu
 tlb_status launch_binary(int op, const float *a, const float *b, float *out, const int64_t *oshape,
@@ -206,7 +196,7 @@ tlb_status launch_f32_to_f16(const float *a, __half *out, int64_t n);
 
 // attention.cu
 struct DecodeAttnJob {
-    SlicedVec qkv;         // [q (H*D) | k (KVH*D) | v (KVH*D)] raw projections of the new token
+    const float *qkv;      // [q (H*D) | k (KVH*D) | v (KVH*D)] raw projections of the new token
     void *kcache, *vcache; // [KVH][max_seq][D] of this layer, f16 or f32
     int kv_f16;
     int H, KVH, D, max_seq;
