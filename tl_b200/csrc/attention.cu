@@ -15,7 +15,7 @@
 namespace tlb {
 
 constexpr int kAttnThreads = 512;
-constexpr int kKeysPerCta = 128;
+constexpr int kKeysPerCta = kAttnKeysPerSplit;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
 {
@@ -54,7 +54,8 @@ struct AttnParams {
     const int *pos, *rope_pos;
     const float *cos_t, *sin_t;
     float scale;
-    float *partial;   // [KVH][max_splits][rep][D + 2]
+    float *partial;   // [KVH][max_splits][rep][D + 4]: D weighted sums, then the split's maximum and sum of exponentials (rows stay 16-byte aligned)
+    int defer_merge;  // the consumer (o_proj prologue) merges the splits: write partial results only
     int *counters;    // [KVH]
     int max_splits;
     float *out;       // [H * D]
@@ -224,19 +225,20 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
             *reinterpret_cast<float2 *>(accbuf + ((size_t)kg * REP + h) * D + 2 * dp) = make_float2(acc[h][0], acc[h][1]);
     }
     __syncthreads();
-    float *part = p.partial + ((size_t)kvh * p.max_splits + split) * REP * (D + 2);
+    float *part = p.partial + ((size_t)kvh * p.max_splits + split) * REP * (D + 4);
     for (int i = tid; i < REP * D; i += kAttnThreads) {
         float s = 0.f;
         for (int g = 0; g < NG; g++) s += accbuf[(size_t)g * REP * D + i];
         int h = i / D, d = i - h * D;
-        if (nsplit == 1) {
+        if (nsplit == 1 && !p.defer_merge) {
             p.out[(size_t)(kvh * REP + h) * D + d] = s / ml[h * 2 + 1];
         } else {
-            part[h * (D + 2) + d] = s;
+            part[h * (D + 4) + d] = s;
         }
     }
-    if (nsplit == 1) { if (tid == 0) span_event(p.span, 3); return; }
-    if (tid < REP) { part[tid * (D + 2) + D] = ml[tid * 2]; part[tid * (D + 2) + D + 1] = ml[tid * 2 + 1]; }
+    if (nsplit == 1 && !p.defer_merge) { if (tid == 0) span_event(p.span, 3); return; }
+    if (tid < REP) { part[tid * (D + 4) + D] = ml[tid * 2]; part[tid * (D + 4) + D + 1] = ml[tid * 2 + 1]; }
+    if (p.defer_merge) { if (tid == 0) span_event(p.span, 3); return; }
     // the last CTA of this KV head to finish merges all splits
     __threadfence();
     __syncthreads();
@@ -248,14 +250,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
     if (tid == 0) span_event(p.span, 3);
     if (!is_last) return;
     __threadfence();
-    const float *base = p.partial + (size_t)kvh * p.max_splits * REP * (D + 2);
+    const float *base = p.partial + (size_t)kvh * p.max_splits * REP * (D + 4);
     for (int i = tid; i < REP * D; i += kAttnThreads) {
         int h = i / D, d = i - h * D;
         float M = -INFINITY;
-        for (int s = 0; s < nsplit; s++) M = fmaxf(M, __ldcg(base + ((size_t)s * REP + h) * (D + 2) + D));
+#pragma unroll 8
+        for (int s = 0; s < nsplit; s++) M = fmaxf(M, __ldcg(base + ((size_t)s * REP + h) * (D + 4) + D));
         float L = 0.f, O = 0.f;
+#pragma unroll 8
         for (int s = 0; s < nsplit; s++) {
-            const float *ps = base + ((size_t)s * REP + h) * (D + 2);
+            const float *ps = base + ((size_t)s * REP + h) * (D + 4);
             float w = expf(__ldcg(ps + D) - M);
             L += __ldcg(ps + D + 1) * w;
             O += __ldcg(ps + d) * w;
@@ -311,6 +315,7 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     p.qkv = j.qkv; p.kcache = j.kcache; p.vcache = j.vcache;
     p.H = j.H; p.KVH = j.KVH; p.D = j.D; p.max_seq = j.max_seq;
     p.pos = j.pos; p.rope_pos = j.rope_pos; p.cos_t = j.cos_t; p.sin_t = j.sin_t; p.scale = j.scale;
+    p.defer_merge = j.defer_merge ? 1 : 0;
     p.partial = j.partial; p.counters = j.counters; p.max_splits = j.splits; p.out = j.out;
     p.use_pdl = j.pdl ? 1 : 0;
     p.span = j.span;

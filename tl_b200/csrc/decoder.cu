@@ -205,6 +205,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             a.kv_f16 = c.kv_f16; a.H = c.n_heads; a.KVH = c.n_kv_heads; a.D = c.head_dim; a.max_seq = c.max_seq;
             a.pos = d->state + 1; a.rope_pos = d->state + 2; a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.scale = c.attn_scale;
             a.partial = d->partial; a.counters = d->counters; a.splits = d->max_splits; a.out = d->attn; a.pdl = d->pdl;
+            a.defer_merge = true;
             a.span = next_span();
             if (!d->dry) TLB_TRY(launch_decode_attention(a));
         }
@@ -213,7 +214,10 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             j.n_w = 1;
             set_w(j, 0, w.o, d->xa);
             j.type = w.o->type; j.k = qd; j.m = 1; j.slices = d->force_slices[1];
-            j.prologue = PRO_PLAIN; j.x = d->attn;
+            // the attention launch leaves its per-split results; they are combined here, as the activation is loaded
+            j.prologue = PRO_ATTN_MERGE;
+            j.att_part = d->partial; j.att_pos = d->state + 1; j.att_max_splits = d->max_splits;
+            j.att_rep = c.n_heads / c.n_kv_heads; j.att_dim = c.head_dim; j.att_keys = kAttnKeysPerSplit;
             j.finish = FIN_RESID; j.resid = d->xb; j.ssq_out = d->ssq_o;   // xa = xb + o_proj(attn)
             j.pdl = d->pdl;
             j.span = next_span();
@@ -397,9 +401,9 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     d->kv_layer_elems = (size_t)kvd * c.max_seq;
     size_t kv_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
     TRY_D(dalloc(d, (char **)&d->kcache, kv_bytes)); TRY_D(dalloc(d, (char **)&d->vcache, kv_bytes));
-    d->max_splits = (c.max_seq + 127) / 128;
+    d->max_splits = (c.max_seq + kAttnKeysPerSplit - 1) / kAttnKeysPerSplit;
     int rep = c.n_heads / c.n_kv_heads;
-    TRY_D(dalloc(d, &d->partial, (size_t)c.n_kv_heads * d->max_splits * rep * (c.head_dim + 2)));
+    TRY_D(dalloc(d, &d->partial, (size_t)c.n_kv_heads * d->max_splits * rep * (c.head_dim + 4)));
     TRY_D(dalloc(d, &d->counters, c.n_kv_heads + 1));
     TRY_D(dalloc(d, &d->state, 4));
     d->tokens_cap = c.max_seq;
@@ -525,6 +529,7 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
     if (!d || !which || !us_per_launch) return fail(TLB_ERR_NULL, "null argument");
     const tlb_decoder_cfg &c = d->cfg;
     const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
+    const int pos_arg = copies;    // the chain modes take the cache position in this argument
     if (copies < 1) copies = 1;
     if (copies > c.n_layers) copies = c.n_layers;
     std::string w(which);
@@ -535,7 +540,7 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         const int nk = 5 * c.n_layers + 1;
         unsigned long long *span = nullptr;
         TLB_CUDA(cudaMalloc(&span, (size_t)nk * 8 * sizeof(unsigned long long)));
-        int pos = std::min(std::max(copies, 0), c.max_seq - iters - 2);
+        int pos = std::min(std::max(pos_arg, 0), c.max_seq - iters - 8);
         tlb_status st = set_state(d, 1, pos, pos, 0);
         for (int i = 0; i < iters && st == TLB_OK; i++) st = enqueue_step(d);
         std::vector<unsigned long long> h((size_t)nk * 8, 0ull);
@@ -544,11 +549,24 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         cudaStreamSynchronize(ctx()->stream);
         cudaEvent_t e0, e1;
         cudaEventCreate(&e0); cudaEventCreate(&e1);
+        float ms = 0.f;
         cudaGraphExec_t gexec = nullptr;
+        const int n_replays = getenv("TLB_REPLAYS") ? std::max(1, atoi(getenv("TLB_REPLAYS"))) : 2;
+        if (w == "chain_graph" && getenv("TLB_USE_SESSION_GRAPH") && st == TLB_OK) {
+            st = ensure_graph(d);
+            for (int i = 0; i < 3 && st == TLB_OK; i++) cudaGraphLaunch(d->graph, ctx()->stream);
+            cudaStreamSynchronize(ctx()->stream);
+            cudaEventRecord(e0, ctx()->stream);
+            for (int i = 0; i < n_replays && st == TLB_OK; i++) cudaGraphLaunch(d->graph, ctx()->stream);
+            cudaEventRecord(e1, ctx()->stream);
+            cudaEventSynchronize(e1);
+            cudaEventElapsedTime(&ms, e0, e1);
+            fprintf(stderr, "[tlb chain] session graph: %.1f us per replay\n", ms * 1e3 / n_replays);
+        }
         if (w == "chain_graph" && st == TLB_OK) {   // the same step as one graph launch, probes baked in
             cudaGraph_t g = nullptr;
             TLB_CUDA(cudaStreamBeginCapture(ctx()->stream, cudaStreamCaptureModeThreadLocal));
-            st = enqueue_step(d, span);
+            st = enqueue_step(d, getenv("TLB_NOSPAN") ? nullptr : span);
             cudaError_t ce = cudaStreamEndCapture(ctx()->stream, &g);
             if (st == TLB_OK && ce != cudaSuccess) st = cuda_fail(ce, "cudaStreamEndCapture");
             if (st == TLB_OK) { ce = cudaGraphInstantiate(&gexec, g, 0); if (ce != cudaSuccess) st = cuda_fail(ce, "cudaGraphInstantiate"); }
@@ -559,17 +577,16 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         }
         cudaEventRecord(e0, ctx()->stream);
         if (st == TLB_OK) {
-            if (gexec) { cudaGraphLaunch(gexec, ctx()->stream); cudaGraphLaunch(gexec, ctx()->stream); }   // two back-to-back replays
+            if (gexec) { for (int i = 0; i < n_replays; i++) cudaGraphLaunch(gexec, ctx()->stream); }   // back-to-back replays
             else st = enqueue_step(d, span);
         }
         cudaEventRecord(e1, ctx()->stream);
         cudaEventSynchronize(e1);
-        float ms = 0.f;
         cudaEventElapsedTime(&ms, e0, e1);
         cudaMemcpy(h.data(), span, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
         cudaFree(span);
         cudaEventDestroy(e0); cudaEventDestroy(e1);
-        if (gexec) { cudaGraphExecDestroy(gexec); ms *= 0.5f; }
+        if (gexec) { cudaGraphExecDestroy(gexec); ms /= (float)n_replays; }
         if (st != TLB_OK) return st;
         const unsigned long long t0 = h[0];
         const char *names[5] = {"qkv", "attn", "o", "gate_up", "down"};

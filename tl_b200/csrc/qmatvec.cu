@@ -486,12 +486,15 @@ int qmatvec_plan_slices(int type, int64_t k, int m, int64_t tiles, int max_slice
 template <int FMT>
 static tlb_status launch_fmt(const MvParams &p, int grid, size_t smem, bool pdl)
 {
-    static size_t set_bytes = 0;
-    if (smem > set_bytes) {
-        TLB_CUDA(cudaFuncSetAttribute(qmatvec_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        // always the largest shared-memory split, whatever this launch needs: SMs do not re-partition between launches
+    // Function attributes are set once, to their final values, before the first launch: a graph whose
+    // kernel nodes were captured while the limit was still growing replayed 25 % slower than the same
+    // launches issued one by one.  Always the largest shared-memory split, whatever a launch needs, so
+    // that SMs do not re-partition between launches.
+    static bool prepared = false;
+    if (!prepared) {
+        TLB_CUDA(cudaFuncSetAttribute(qmatvec_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx()->smem_optin));
         TLB_CUDA(cudaFuncSetAttribute(qmatvec_kernel<FMT>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        set_bytes = smem;
+        prepared = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
@@ -575,7 +578,8 @@ tlb_status launch_qmatvec(const MatvecJob &job)
         return fail(TLB_ERR_SHAPE, "K = %lld with %d rows needs more shared memory than one SM has (max K %zu)",
                     (long long)job.k, job.m, qmatvec_max_k(job.m));
     // (room for the local-mode slots: at most ~6 per warp)
-    const size_t seg_room = p.kb == 1 ? (size_t)kWarps * 8 * 16 * job.m * sizeof(float) + 128 : 0;
+    const size_t seg_room = (p.kb == 1 ? (size_t)kWarps * 8 * 16 * job.m * sizeof(float) + 128 : 0) +
+                            (job.prologue == PRO_ATTN_MERGE ? (size_t)p.nb_max * 4 * std::max(1, job.att_max_splits) * sizeof(float) + 128 : 0);
     int spw = (int)((budget - sp.fixed - 128 - seg_room) / per_stage);
     // no more stages than the longest warp has units, and no more than keeps ~1.5 us of HBM latency covered
     const int64_t ipc = (p.n_items + grid - 1) / grid;
@@ -602,6 +606,17 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.x = job.x; p.x2 = job.x2; p.norm_w = job.norm_w; p.eps = job.eps; p.x_out = job.x_out;
     p.emb_table = job.emb_table; p.token = job.token;
     p.ssq_parts = job.ssq_parts; p.n_parts = job.n_parts;
+    p.att_part = job.att_part; p.att_pos = job.att_pos;
+    p.att_max_splits = job.att_max_splits; p.att_rep = job.att_rep; p.att_dim = job.att_dim; p.att_keys = job.att_keys;
+    if (job.prologue == PRO_ATTN_MERGE) {
+        if (!job.att_part || !job.att_pos || job.att_max_splits < 1 || job.att_rep < 1 || job.att_keys < 1 ||
+            (job.att_dim != 64 && job.att_dim != 128) || job.k % job.att_dim)
+            return fail(TLB_ERR_ARG, "attention-merge prologue: incomplete or unsupported description of the split results");
+        // softmax weights of the splits, one row per query head of the CTA's blocks, after everything else
+        p.off_wtab = (int)((smem + 127) / 128 * 128);
+        smem = (size_t)p.off_wtab + (size_t)p.nb_max * (256 / job.att_dim) * job.att_max_splits * sizeof(float);
+        if (smem > c->smem_optin) return fail(TLB_ERR_SHAPE, "launch needs %zu bytes of shared memory", smem);
+    }
     p.finish = job.finish; p.resid = job.resid; p.ssq_out = job.ssq_out;
     p.pf_base[0] = (const uint8_t *)job.pf_base[0]; p.pf_base[1] = (const uint8_t *)job.pf_base[1];
     p.pf_rows = job.pf_base[0] && job.pf_base[1] ? job.pf_rows : nullptr;
@@ -614,7 +629,7 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.use_pdl = job.pdl ? 1 : 0;
     p.trace = job.trace;
     p.span = job.span;
-    if (!p.x && !(p.prologue == PRO_ADD_NORM && p.token)) return fail(TLB_ERR_NULL, "null activation");
+    if (!p.x && !(p.prologue == PRO_ADD_NORM && p.token) && p.prologue != PRO_ATTN_MERGE) return fail(TLB_ERR_NULL, "null activation");
     if (p.prologue == PRO_SILU_MUL && !p.x2) return fail(TLB_ERR_NULL, "null activation");
     if (job.dry_run) return TLB_OK;   // the shape is launchable
     switch (job.type) {

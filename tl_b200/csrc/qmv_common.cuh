@@ -187,6 +187,10 @@ struct MvParams {
     const float *norm_w;
     const float *ssq_parts;   // ADD_NORM: partial sums of squares of x left by its producer (null: computed here)
     int n_parts;
+    const float *att_part;    // ATTN_MERGE: per-split attention results [kv head][att_max_splits][att_rep][att_dim + 4]
+    const int *att_pos;
+    int att_max_splits, att_rep, att_dim, att_keys;
+    int off_wtab;             // ATTN_MERGE: softmax weights of the splits per query head of this CTA
     int finish;               // FIN_*: what the warp completing a tile does with its results
     const float *resid;       // FIN_RESID: added to the result
     float *ssq_out;           // FIN_RESID: [tiles] sum of squares of each finished tile

@@ -162,6 +162,52 @@ __device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem,
     const float *emb = nullptr;
     if (norm && p.token) emb = p.emb_table + (size_t)__ldg(p.token) * p.k;
 
+    // Attention output still split over the keys: first the softmax weight of every split for each query
+    // head this CTA needs - w[head][s] = exp(m_s - M) / sum_t l_t exp(m_t - M), one warp per head - then the
+    // values are the weighted sums of the splits' rows (attn_value below).
+    const bool attn = p.prologue == PRO_ATTN_MERGE;
+    int nsplit = 1;
+    float *wtab = reinterpret_cast<float *>(smem + p.off_wtab);   // [heads of this CTA][att_max_splits]
+    if (attn) {
+        const int hpb = 256 / p.att_dim;     // query heads per block of 256
+        nsplit = (__ldcg(p.att_pos) + p.att_keys) / p.att_keys;   // ceil((pos + 1) / keys per split)
+        const size_t sstride = (size_t)p.att_rep * (p.att_dim + 4);
+        for (int hl = warp; hl < nb * hpb; hl += nwarps) {
+            const int head = blk0 * hpb + hl, kvh = head / p.att_rep, hr = head - kvh * p.att_rep;
+            const float *row0 = p.att_part + ((size_t)kvh * p.att_max_splits * p.att_rep + hr) * (p.att_dim + 4) + p.att_dim;
+            // lane s holds split s (and s + 32, ... for very long contexts, re-read in the later passes)
+            const float m0 = lane < nsplit ? __ldcg(row0 + lane * sstride) : -INFINITY;
+            const float l0 = lane < nsplit ? __ldcg(row0 + lane * sstride + 1) : 0.f;
+            float mx = m0;
+            for (int sp = lane + 32; sp < nsplit; sp += 32) mx = fmaxf(mx, __ldcg(row0 + sp * sstride));
+            for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float w0 = lane < nsplit ? expf(m0 - mx) : 0.f;
+            float lsum = l0 * w0;
+            for (int sp = lane + 32; sp < nsplit; sp += 32) lsum += __ldcg(row0 + sp * sstride + 1) * expf(__ldcg(row0 + sp * sstride) - mx);
+            for (int o = 16; o; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+            const float inv_l = 1.f / lsum;
+            if (lane < nsplit) wtab[hl * p.att_max_splits + lane] = w0 * inv_l;
+            for (int sp = lane + 32; sp < nsplit; sp += 32) wtab[hl * p.att_max_splits + sp] = expf(__ldcg(row0 + sp * sstride) - mx) * inv_l;
+        }
+        __syncthreads();
+    }
+    auto attn_value = [&](int lb) {   // elements 4j .. 4j+3 of local block lb
+        const int e = ((blk0 + lb) * 64 + j) * 4;
+        const int head = e / p.att_dim, d = e - head * p.att_dim;
+        const int kvh = head / p.att_rep, hr = head - kvh * p.att_rep, hl = head - blk0 * (256 / p.att_dim);
+        const float *row = p.att_part + ((size_t)kvh * p.att_max_splits * p.att_rep + hr) * (p.att_dim + 4) + d;
+        const size_t sstride = (size_t)p.att_rep * (p.att_dim + 4);
+        const float *wr = wtab + hl * p.att_max_splits;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int sp = 0; sp < nsplit; sp++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(row + sp * sstride));
+            const float w = wr[sp];
+            acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+        }
+        return acc;
+    };
+
     float inv_rms = 0.f;
     for (int first = 0; first < n_mine || (norm && first == 0); first += ngroups * kKeep) {
         float4 keep[kKeep], wgt[kKeep];
@@ -171,7 +217,7 @@ __device__ void build_activation(const MvParams &p, MvShared *sh, uint8_t *smem,
             const int item = first + grp + i * ngroups;
             if (item < n_mine) {
                 const int mrow = item / nb, lb = item - mrow * nb, k4 = (blk0 + lb) * 64 + j;
-                keep[i] = prologue_value(p, emb, mrow, k4, 0.f);
+                keep[i] = attn ? attn_value(lb) : prologue_value(p, emb, mrow, k4, 0.f);
                 if (norm) wgt[i] = first == 0 ? wgt_first[i] : __ldg(reinterpret_cast<const float4 *>(p.norm_w) + k4);
             }
         }

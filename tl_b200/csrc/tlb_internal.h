@@ -116,7 +116,7 @@ tlb_status launch_interleave8(int type, const uint8_t *a, const uint8_t *b, uint
 
 // qmatvec.cu ---------------------------------------------------------------------------
 // How the activation vector of a streaming matvec is produced inside the kernel.
-enum Prologue { PRO_PLAIN = 0, PRO_ADD_NORM = 1, PRO_SILU_MUL = 2 };
+enum Prologue { PRO_PLAIN = 0, PRO_ADD_NORM = 1, PRO_SILU_MUL = 2, PRO_ATTN_MERGE = 3 };
 enum Finish { FIN_PLAIN = 0, FIN_RESID = 1, FIN_SILU = 2 };
 constexpr int kMaxSlices = 16;   // most K-slices a matvec may cut its launch into
 struct MatvecJob {
@@ -145,6 +145,13 @@ struct MatvecJob {
     // are partial sums of its squares left by the launch that produced it (finish == FIN_RESID there)
     const float *ssq_parts = nullptr;
     int n_parts = 0;
+    // PRO_ATTN_MERGE: the activation is the output of decode attention still split over the keys: per
+    // (kv head, split, query head of the group) att_dim weighted sums, the split's score maximum and its sum
+    // of exponentials, rows of att_dim + 4 floats; splits = ceil((*att_pos + 1) / att_keys).  The prologue
+    // combines them (softmax over all keys) while it loads.
+    const float *att_part = nullptr;
+    const int *att_pos = nullptr;
+    int att_max_splits = 0, att_rep = 0, att_dim = 0, att_keys = 0;
     // What the warp that completes a tile does with its 16 results (m == 1, one tensor, for the fused forms):
     //   FIN_PLAIN  out[row] = y
     //   FIN_RESID  out[row] = resid[row] + y, and ssq_out[tile] = sum of the squares of those 16 values
@@ -195,6 +202,7 @@ tlb_status launch_silu_mul(const float *g, const float *u, float *out, int64_t n
 tlb_status launch_f32_to_f16(const float *a, __half *out, int64_t n);
 
 // attention.cu
+constexpr int kAttnKeysPerSplit = 128;   // keys one CTA of the decode attention covers; splits = ceil((pos + 1) / this)
 struct DecodeAttnJob {
     const float *qkv;      // [q (H*D) | k (KVH*D) | v (KVH*D)] raw projections of the new token
     void *kcache, *vcache; // [KVH][max_seq][D] of this layer, f16 or f32
@@ -204,7 +212,8 @@ struct DecodeAttnJob {
     const int *rope_pos;   // device: angle position
     const float *cos_t, *sin_t; // [max_seq, D] pair-duplicated tables (CPU convention)
     float scale;
-    float *partial;        // scratch [KVH][splits][rep][D+2]
+    float *partial;        // scratch [KVH][splits][rep][D+4]
+    bool defer_merge = false;   // leave the per-split results in `partial`; the o_proj launch merges them in its prologue
     int *counters;         // [KVH], zero on entry, reset by the kernel
     int splits;
     float *out;            // [H*D]
