@@ -3,10 +3,9 @@
 // (examples/apps/llama3/chatbot_llama3.tl:66-125,220-236; examples/apps/tinyllama/chatbot.tl:50-113),
 // which issue ~40 single-op FFI calls per layer per token, each followed by a device-wide sync
 // (crates/tl_cuda/src/stream.rs:69-73).  Here:
-//   K1  RMSNorm*w (prologue)  ->  q|k|v matvec        (layer 0: embedding lookup + sum of squares here too;
-//                                                      side job: this layer's KV rows are pulled into L2)
-//   K2  RoPE(q, k) + KV append + split-K attention + merge
-//   K3  o_proj matvec         ->  residual add, per-tile sums of squares (tile finishing)
+//   K1  RMSNorm*w (prologue)  ->  q|k|v matvec        (layer 0: embedding lookup + sum of squares here too)
+//   K2  RoPE(q, k) + KV append + attention split over the keys (per-split results are left as they are)
+//   K3  softmax over the splits (prologue)  ->  o_proj matvec  ->  residual add, per-tile sums of squares (tile finishing)
 //   K4  RMSNorm*w (prologue)  ->  gate|up matvec over interleaved rows  ->  SiLU(gate)*up (tile finishing)
 //   K5  down matvec           ->  residual add, per-tile sums of squares (tile finishing)
 //   ... output_norm (prologue) -> lm_head matvec, argmax + position advance.
@@ -179,14 +178,6 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             set_w(j, 2, w.v, d->qkv + qd + kvd);
            
             j.type = w.q->type; j.k = dm; j.m = 1; j.slices = d->force_slices[0];
-            {   // while q|k|v streams, this layer's KV rows are pulled into L2 for the attention kernel that follows
-                const size_t es = c.kv_f16 ? 2 : 4;
-                j.pf_base[0] = (char *)d->kcache + (size_t)l * d->kv_layer_elems * es;
-                j.pf_base[1] = (char *)d->vcache + (size_t)l * d->kv_layer_elems * es;
-                j.pf_rows = d->state + 1;
-                j.pf_heads = c.n_kv_heads; j.pf_row_bytes = (int)(c.head_dim * es);
-                j.pf_head_stride = (int64_t)c.max_seq * c.head_dim * es;
-            }
             j.prologue = PRO_ADD_NORM;
             j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
             // the residual lives in xb here: the embedding row for layer 0, else what the last down launch left

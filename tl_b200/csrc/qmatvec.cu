@@ -192,24 +192,6 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
     STAMP(1);
     if (tid == 0) span_event(p.span, 5);
 
-    if (p.pf_rows) {
-        // L2 prefetch of what the next kernel reads first (the KV cache rows of this layer): the rows are
-        // older than any kernel still running, so this needs no dependency wait.  8 KB per request, the
-        // requests of all heads and both arrays dealt round-robin over the grid's threads.
-        const int rows = *p.pf_rows + 1;
-        const long long head_bytes = (long long)rows * p.pf_row_bytes;
-        const int per_head = (int)((head_bytes + 8191) / 8192);
-        const int total = 2 * p.pf_heads * per_head;
-        for (int q = b * kThreads + tid; q < total; q += gridDim.x * kThreads) {
-            const int arr = q / (p.pf_heads * per_head), rem = q - arr * (p.pf_heads * per_head);
-            const int head = rem / per_head, piece = rem - head * per_head;
-            const long long off = (long long)piece * 8192;
-            const unsigned bytes = (unsigned)min(8192ll, (head_bytes - off + 15) / 16 * 16);
-            const uint8_t *src = p.pf_base[arr] + (long long)head * p.pf_head_stride + off;
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-        }
-    }
-
     float4 wgt_first[kKeep];       // static inputs of the prologue, fetched while the previous kernel finishes
     load_norm_weights(p, tid, kThreads, blk0, nb, wgt_first);
     if (p.use_pdl) {
@@ -618,10 +600,6 @@ tlb_status launch_qmatvec(const MatvecJob &job)
         if (smem > c->smem_optin) return fail(TLB_ERR_SHAPE, "launch needs %zu bytes of shared memory", smem);
     }
     p.finish = job.finish; p.resid = job.resid; p.ssq_out = job.ssq_out;
-    p.pf_base[0] = (const uint8_t *)job.pf_base[0]; p.pf_base[1] = (const uint8_t *)job.pf_base[1];
-    p.pf_rows = job.pf_base[0] && job.pf_base[1] ? job.pf_rows : nullptr;
-    p.pf_heads = job.pf_heads; p.pf_row_bytes = job.pf_row_bytes; p.pf_head_stride = job.pf_head_stride;
-    if (p.pf_rows && (p.pf_row_bytes % 16 || p.pf_head_stride % 16 || p.pf_heads < 1)) return fail(TLB_ERR_ARG, "prefetch rows must be multiples of 16 bytes");
     if (job.finish != FIN_PLAIN && (job.m != 1 || job.n_w != 1)) return fail(TLB_ERR_ARG, "fused tile finishing takes one tensor and one activation row");
     if (job.finish == FIN_RESID && (!job.resid || !job.ssq_out)) return fail(TLB_ERR_NULL, "null residual or statistics buffer");
     if (job.ssq_parts && (job.prologue != PRO_ADD_NORM || job.n_parts < 1)) return fail(TLB_ERR_ARG, "partial sums of squares go with the fused RMSNorm prologue");

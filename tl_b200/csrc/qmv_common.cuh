@@ -175,12 +175,6 @@ struct MvParams {
     int unit_bytes, stage_bytes;
     int spw;                  // ring stages private to each warp
     int max_seg, off_seg;     // kb == 1: slots of partial results per warp in shared memory, and where they start
-    // Side job: bring into L2 what the NEXT kernel will read first - for the q|k|v launch, this layer's
-    // K and V cache rows [0, *pf_rows) of every KV head ([heads][pf_row_stride rows][pf_row_bytes]).
-    const uint8_t *pf_base[2];
-    const int *pf_rows;
-    int pf_heads, pf_row_bytes;
-    long long pf_head_stride;  // bytes between heads
     int prologue;
     const float *x;           // PLAIN: x [M,K]; ADD_NORM: residual; SILU_MUL: gate
     const float *x2;          // ADD_NORM: delta added to x (null: none); SILU_MUL: up

@@ -160,12 +160,6 @@ struct MatvecJob {
     int finish = 0;
     const float *resid = nullptr;
     float *ssq_out = nullptr;
-    // optional side job: L2 prefetch of rows [0, *pf_rows] of `pf_heads` heads of two arrays laid out
-    // [heads][...][pf_row_bytes] with pf_head_stride bytes between heads (the KV cache the next kernel reads)
-    const void *pf_base[2] = {nullptr, nullptr};
-    const int *pf_rows = nullptr;
-    int pf_heads = 0, pf_row_bytes = 0;
-    int64_t pf_head_stride = 0;
     bool dry_run = false;            // validate and plan only: tells whether the launch would be accepted
     bool last_of_chain = false;      // no matvec follows closely: take half an SM's shared memory instead of a third
     long long *trace = nullptr;      // optional device buffer [grid][10] of stamps (timing studies)
