@@ -91,14 +91,15 @@ __device__ __forceinline__ ItemRef item_ref(const MvParams &p, const ItemCursor 
 //              (crates/tl_cpu/src/ffi.rs:2444-2486 sums the squares of the whole row).
 //   FIN_SILU   rows 0..7 are gate and rows 8..15 up of hidden units 8*tile .. 8*tile+7:
 //              out[8*tile + e] = silu(gate) * up (crates/tl_cpu/src/ffi.rs:2083-2103 then an elementwise mul).
-__device__ __forceinline__ void finish_tile_fused(const MvParams &p, const ItemRef &fr, float y, int lane)
+// `res` is the residual of row e, loaded by the caller (so that it can be in flight with other loads).
+__device__ __forceinline__ void finish_tile_fused(const MvParams &p, const ItemRef &fr, float y, float res, int lane)
 {
     float *out = p.out[0];
     const int nrows = p.n_rows[0];
     if (p.finish == FIN_RESID) {
         const int g = fr.row0 + lane;
         const bool valid = lane < 16 && g < nrows;
-        const float xn = valid ? __ldcg(p.resid + g) + y : 0.f;
+        const float xn = valid ? res + y : 0.f;
         if (valid) out[g] = xn;
         float s = xn * xn;
         s += __shfl_xor_sync(0xffffffffu, s, 8);
@@ -325,7 +326,8 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
                     if (lane < 16 * p.m && g < nrows) out[(size_t)(lane >> 4) * nrows + g] = acc0;
                     if (lane + 32 < 16 * p.m && g < nrows) out[(size_t)((lane >> 4) + 2) * nrows + g] = acc1;
                 } else {
-                    finish_tile_fused(p, fr, lane < 16 ? acc0 : 0.f, lane);
+                    const float res = (p.finish == FIN_RESID && lane < 16 && fr.row0 + lane < p.n_rows[0]) ? __ldcg(p.resid + fr.row0 + lane) : 0.f;
+                    finish_tile_fused(p, fr, lane < 16 ? acc0 : 0.f, res, lane);
                 }
             }
         }
@@ -361,13 +363,16 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
                         const int mi = e >> 4, g = fr.row0 + (e & 15);
                         if (g < nrows) out[(size_t)mi * nrows + g] = a;
                     }
-                } else {   // m == 1
-                    float a = 0.f;
-                    if (lane < 16) {
-                        a = __ldcg(src + lane);
-                        for (int s = 1; s < p.kb; s++) a += __ldcg(src + s * sstride + lane);
-                    }
-                    finish_tile_fused(p, fr, a, lane);
+                } else {   // m == 1: all slices (and the residual) are requested at once, then added in slice order
+                    float sl[kMaxSlices];
+                    float res = 0.f;
+                    if (p.finish == FIN_RESID && lane < 16 && fr.row0 + lane < nrows) res = __ldcg(p.resid + fr.row0 + lane);
+#pragma unroll
+                    for (int s = 0; s < kMaxSlices; s++) sl[s] = (lane < 16 && s < p.kb) ? __ldcg(src + s * sstride + lane) : 0.f;
+                    float a = sl[0];
+#pragma unroll
+                    for (int s = 1; s < kMaxSlices; s++) a += sl[s];
+                    finish_tile_fused(p, fr, a, res, lane);
                 }
                 if (lane == 0) p.tile_cnt[fr.tile] = 0;
             }
