@@ -141,3 +141,64 @@ def test_qmatvec_shape_errors():
     assert e.value.code == 1
     out = tl.Tensor.from_numpy(np.zeros((0, 256), dtype=np.float32)).matmul_quantized(q)  # empty batch
     assert out.shape == (0, 16)
+
+
+# ---- many activation rows: the tensor-core GEMM behind the same entry point (rows > 16) ----------------
+GEMM_TOL = 2e-3      # f16 operands (2^-12 relative rounding each), f32 accumulation; the required gate is 2e-2
+GEMM_EMU_TOL = 2e-5  # against the same arithmetic done in numpy: only the summation order differs
+
+
+def _f16_emulation(x, wd):
+    amax = np.abs(x).max(axis=1)
+    e = np.frexp(amax)[1]
+    sc = np.where((amax > 0) & np.isfinite(amax), np.ldexp(1.0, 14 - e), 1.0).astype(np.float32)
+    xs = (x * sc[:, None]).astype(np.float16).astype(np.float64)
+    return (xs @ wd.astype(np.float16).astype(np.float64).T) / sc[:, None]
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("n,k,m", [(128, 256, 17), (33, 512, 40), (256, 1024, 100), (384, 2048, 300), (1024, 1024, 520)])
+def test_qgemm_matches_oracle(orc, t, n, k, m):
+    rng = np.random.default_rng(5000 + t + n + m)
+    w = synth.random_quant(t, n, k, rng)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    x[0] *= 1000.0       # rows of very different magnitude: each row carries its own power-of-two scale
+    x[-1] *= 1e-3
+    x[1] = 0.0           # an all-zero row
+    q = tl.QTensor.from_gguf_bytes(t, n, k, w)
+    got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+    ref = orc.qmatmul(t, w.reshape(-1), n, k, x)
+    assert got.shape == (m, n)
+    assert np.all(got[1] == 0.0)
+    for i in range(m):
+        if i != 1:
+            assert relerr(got[i], ref[i]) < GEMM_TOL, i
+    emu = _f16_emulation(x, q.dequantize().numpy())
+    assert relerr(got, emu) < GEMM_EMU_TOL
+
+
+def test_qgemm_full_size_agrees_with_matvec():
+    """Llama-3-8B q_proj shape, 512 rows: sampled rows of the GEMM against the streaming matvec on the same rows."""
+    n = k = 4096
+    rng = np.random.default_rng(77)
+    q = tl.QTensor.from_gguf_bytes(synth.Q4_K, n, k, synth.random_quant(synth.Q4_K, n, k, rng))
+    x = rng.standard_normal((512, k), dtype=np.float32)
+    got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+    again = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+    np.testing.assert_array_equal(got.view(np.uint32), again.view(np.uint32))   # bitwise repeatable
+    for i in (0, 1, 255, 256, 300, 511):
+        one = tl.Tensor.from_numpy(x[i]).matmul_quantized(q).numpy()
+        assert relerr(got[i], one) < GEMM_TOL, i
+
+
+def test_qgemm_rank3_input_and_shape_error():
+    rng = np.random.default_rng(78)
+    q = tl.QTensor.from_gguf_bytes(synth.Q8_0, 64, 256, synth.random_quant(synth.Q8_0, 64, 256, rng))
+    x = rng.standard_normal((2, 20, 256), dtype=np.float32)
+    got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+    assert got.shape == (2, 20, 64)
+    flat = tl.Tensor.from_numpy(x.reshape(40, 256)).matmul_quantized(q).numpy()
+    np.testing.assert_array_equal(got.reshape(40, 64), flat)
+    with pytest.raises(tl.TlbError) as e:
+        tl.Tensor.from_numpy(np.zeros((40, 512), dtype=np.float32)).matmul_quantized(q)
+    assert e.value.code == 1

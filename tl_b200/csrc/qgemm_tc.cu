@@ -1,0 +1,558 @@
+// Quantized-weight GEMM for many activation rows (prompt processing, M > 16):
+//     Y[M, N] = X[M, K] . W^T,   W = GGUF Q4_K / Q6_K / Q4_0 / Q8_0 bytes in the tiled unit layout.
+// It stands behind the same entry point as the streaming matvec (tl_qtensor_matmul,
+// crates/tl_runtime/src/system.rs:180-382, which dequantises the whole weight to f32, transposes it
+// and calls a one-thread-per-output matmul); here the weight is read once per tile of 256 activation
+// rows and never exists in f32.
+//
+// One CTA computes 128 weight rows x NT activation rows (NT <= 256) on the 5th-generation tensor cores:
+//   * the weight tile is the A operand (MMA M = 128): eight producer warps read the quantized units
+//     with coalesced 16-byte loads, dequantise in registers (f32 fma, then round to f16) and store the
+//     128 x 64 f16 tile into shared memory in the K-major 128-byte-swizzled layout tcgen05 reads;
+//   * the activation tile is the B operand (MMA N = NT): f16 rows, brought in by TMA
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past M filled with zeros);
+//   * one thread issues tcgen05.mma (kind::f16, f32 accumulate) for each 64-wide K step as soon as both
+//     halves of the stage have arrived on its mbarrier; tcgen05.commit frees the stage for the producers;
+//   * the accumulator lives in tensor memory (128 lanes x NT columns f32); after the last K step the
+//     producer warps read it back with tcgen05.ld, undo the per-row activation scaling and write
+//     Y[token][row] (32 consecutive floats per warp store).
+// Activations are converted to f16 once per call with a power-of-two scale per row (so the largest
+// element sits near 2^14 and nothing overflows or underflows); the scale is removed exactly in the
+// epilogue.  Operand rounding is therefore 2^-12 relative per element, accumulated in f32.
+//
+// Every wait on an mbarrier is bounded (qmv_common.cuh: mbar_wait); when one runs out the CTA sets the
+// context's error word, lets its outstanding copies land (bounded), frees its tensor memory and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+
+#include "qmv_common.cuh"
+
+namespace tlb {
+
+namespace {
+
+constexpr int kGemmRows = 128;      // weight rows per CTA (MMA M)
+constexpr int kGemmBK = 64;         // K per stage: one 128-byte swizzle row of f16
+constexpr int kGemmStages = 4;
+constexpr int kGemmMaxTok = 256;    // activation rows per CTA (MMA N), multiple of 16
+constexpr int kStageA = kGemmRows * kGemmBK * 2;      // 16 KB
+constexpr int kStageB = kGemmMaxTok * kGemmBK * 2;    // 32 KB
+constexpr int kGemmThreads = 320;   // warps 0-7: dequantise + epilogue, warp 8: TMA, warp 9: MMA + tensor memory
+constexpr int kTmemCols = 256;
+
+struct GemmParams {
+    const uint8_t *w;       // tiled units
+    int64_t upt;            // units per 16-row tile (K / 256)
+    int n_tiles16;          // 16-row tiles of the weight
+    int n;                  // weight rows (output features)
+    int m;                  // activation rows
+    int nt;                 // activation rows per CTA
+    int kt_total;           // K / 64
+    int unit_bytes;
+    float *out;             // [m, n]
+    const float *inv_scale; // [m]
+    int *err;
+};
+
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b)
+{
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b)
+{
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+// Byte t of `bytes` (each 0..255) as an exact f32: the byte becomes the low mantissa bits of 2^23.
+__device__ __forceinline__ float byte_f32(uint32_t bytes, int t)
+{
+    return __uint_as_float(prmt(bytes, 0x4B000000u, 0x7540u | (uint32_t)t)) - 8388608.0f;
+}
+// Four weights w = q * ds - dm from the four bytes of `bytes`, rounded to f16 and stored as 8 bytes.
+__device__ __forceinline__ void store4(uint32_t addr, uint32_t bytes, float ds, float dm)
+{
+    const float f0 = fmaf(byte_f32(bytes, 0), ds, -dm), f1 = fmaf(byte_f32(bytes, 1), ds, -dm);
+    const float f2 = fmaf(byte_f32(bytes, 2), ds, -dm), f3 = fmaf(byte_f32(bytes, 3), ds, -dm);
+    sts64(addr, pack_h2(f0, f1), pack_h2(f2, f3));
+}
+// Byte offset, inside a 128-row x 128-byte stage, of the 8-byte piece that holds k..k+3 of `row`
+// (k a multiple of 4): rows are 128 bytes apart and the 16-byte chunk index is XORed with row % 8.
+__device__ __forceinline__ uint32_t swz(int row, int k)
+{
+    return (uint32_t)(row * 128 + ((((k >> 3) ^ (row & 7)) << 4) | ((k & 4) << 1)));
+}
+
+// ---- Q4_K: byte i of the 12 packed scale bytes; (scale, min) of sub-block j as get_scale_min_k4 does
+// (crates/tl_runtime/src/quantized.rs:337-356)
+__device__ __forceinline__ uint32_t q4k_sbyte(const uint4 &h, int i)
+{
+    const uint32_t wd = i < 4 ? h.y : (i < 8 ? h.z : h.w);
+    return (wd >> (8 * (i & 3))) & 0xFFu;
+}
+__device__ __forceinline__ void q4k_scale_min(const uint4 &h, int j, float &ds, float &dm)
+{
+    const float2 dd = h2_to_f2(h.x);   // (d, dmin)
+    uint32_t sc, mn;
+    if (j < 4) {
+        sc = q4k_sbyte(h, j) & 63u;
+        mn = q4k_sbyte(h, j + 4) & 63u;
+    } else {
+        sc = (q4k_sbyte(h, j + 4) & 0xFu) | ((q4k_sbyte(h, j - 4) >> 6) << 4);
+        mn = (q4k_sbyte(h, j + 4) >> 4) | ((q4k_sbyte(h, j) >> 6) << 4);
+    }
+    ds = dd.x * (float)sc;
+    dm = dd.y * (float)mn;
+}
+
+// One warp's registers for one Q4_K unit (16 rows x 256 weights): lane (r, c) = (lane / 4, lane % 4)
+// holds, per 64-group G, the words [row r: bytes 4c..4c+3 | row r: bytes 16+4c.. | row r+8: same two],
+// plus the 16-byte headers (d, dmin, packed scales) of rows r and r + 8.
+struct Q4KRegs {
+    uint4 q[4];
+    uint4 h[2];
+};
+__device__ __forceinline__ void q4k_load(Q4KRegs &u, const uint8_t *unit, int lane)
+{
+    const int r = lane >> 2;
+#pragma unroll
+    for (int g = 0; g < 4; g++) u.q[g] = __ldg(reinterpret_cast<const uint4 *>(unit + g * 512 + lane * 16));
+    u.h[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + r * 16));
+    u.h[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + (r + 8) * 16));
+}
+// Dequantise 64-group g of the unit into rows row0 + r and row0 + r + 8 of the stage at `stage`.
+__device__ __forceinline__ void q4k_emit(const Q4KRegs &u, int g, uint32_t stage, int row0, int lane)
+{
+    const int r = lane >> 2, c = lane & 3;
+#pragma unroll
+    for (int rs = 0; rs < 2; rs++) {
+        float ds_lo, dm_lo, ds_hi, dm_hi;
+        q4k_scale_min(u.h[rs], 2 * g, ds_lo, dm_lo);
+        q4k_scale_min(u.h[rs], 2 * g + 1, ds_hi, dm_hi);
+        const int row = row0 + r + 8 * rs;
+#pragma unroll
+        for (int hs = 0; hs < 2; hs++) {
+            const uint32_t wd = word_of(u.q[g], rs * 2 + hs);
+            const int k = hs * 16 + 4 * c;   // position of the word's first byte among the group's 32 bytes
+            store4(stage + swz(row, k), wd & 0x0F0F0F0Fu, ds_lo, dm_lo);              // low nibbles: k
+            store4(stage + swz(row, 32 + k), (wd >> 4) & 0x0F0F0F0Fu, ds_hi, dm_hi);  // high nibbles: 32 + k
+        }
+    }
+}
+
+// ---- Q6_K (crates/tl_runtime/src/quantized.rs:268-329): w = d * sc * (q6 - 32).  Per lane and unit: the four
+// ql pieces (row half hi, block half n), the two qh pieces (hi), sixteen int8 scales and d of rows r, r + 8.
+struct Q6KRegs {
+    uint4 ql[4];
+    uint4 qh[2];
+    uint4 sc[2];
+    float d[2];
+};
+__device__ __forceinline__ void q6k_load(Q6KRegs &u, const uint8_t *unit, int lane)
+{
+    const int r = lane >> 2;
+#pragma unroll
+    for (int i = 0; i < 4; i++) u.ql[i] = __ldg(reinterpret_cast<const uint4 *>(unit + i * 512 + lane * 16));
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+        u.qh[hi] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + hi * 512 + lane * 16));
+        u.sc[hi] = __ldg(reinterpret_cast<const uint4 *>(unit + 3072 + (r + 8 * hi) * 16));
+        u.d[hi] = __half2float(__ldg(reinterpret_cast<const __half *>(unit + 3328 + (r + 8 * hi) * 2)));
+    }
+}
+// 64-group g = (n, sub): k = 128 n + 64 sub + [0, 64).  sub 0 takes the low nibbles of ql and bits 0-3 of qh,
+// sub 1 the high nibbles and bits 4-7; inside the group, q1 = 0 / 1 selects ql[l] / ql[l + 32].
+__device__ __forceinline__ void q6k_emit(const Q6KRegs &u, int g, uint32_t stage, int row0, int lane)
+{
+    const int r = lane >> 2, c = lane & 3;
+    const int n = g >> 1, sub = g & 1;
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+        const int row = row0 + r + 8 * hi;
+#pragma unroll
+        for (int q1 = 0; q1 < 2; q1++) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint32_t qlw = word_of(u.ql[hi * 2 + n], q1 * 2 + h);
+                const uint32_t qhw = word_of(u.qh[hi], n * 2 + h);
+                const uint32_t nib = (sub ? (qlw >> 4) : qlw) & 0x0F0F0F0Fu;
+                const uint32_t two = (qhw >> (2 * (sub * 2 + q1))) & 0x03030303u;
+                const int si = 8 * n + h + 2 * (sub * 2 + q1);
+                const int sbyte = (int)(int8_t)((word_of(u.sc[hi], si >> 2) >> (8 * (si & 3))) & 0xFFu);
+                const float ds = u.d[hi] * (float)sbyte;
+                store4(stage + swz(row, q1 * 32 + h * 16 + 4 * c), nib | (two << 4), ds, 32.f * ds);
+            }
+        }
+    }
+}
+
+// ---- Q4_0 (quantized.rs:182-225): blocks of 32, w = d * (nibble - 8); low nibble of byte j is k = j, high k = 16 + j
+struct Q40Regs {
+    uint4 q[4];
+    uint4 d[2];   // eight f16 block scales of rows r and r + 8
+};
+__device__ __forceinline__ void q40_load(Q40Regs &u, const uint8_t *unit, int lane)
+{
+    const int r = lane >> 2;
+#pragma unroll
+    for (int i = 0; i < 4; i++) u.q[i] = __ldg(reinterpret_cast<const uint4 *>(unit + i * 512 + lane * 16));
+    u.d[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + r * 16));
+    u.d[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + (r + 8) * 16));
+}
+__device__ __forceinline__ float f16_of(const uint4 &v, int i)   // i-th f16 of the 16 bytes
+{
+    const float2 f = h2_to_f2(word_of(v, i >> 1));
+    return (i & 1) ? f.y : f.x;
+}
+__device__ __forceinline__ void q40_emit(const Q40Regs &u, int g, uint32_t stage, int row0, int lane)
+{
+    const int r = lane >> 2, c = lane & 3;
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+        const int row = row0 + r + 8 * hi;
+#pragma unroll
+        for (int b = 0; b < 2; b++) {   // blocks 2g and 2g + 1 of the row's eight
+            const float d = f16_of(u.d[hi], 2 * g + b);
+            const uint32_t wd = word_of(u.q[g], hi * 2 + b);
+            store4(stage + swz(row, b * 32 + 4 * c), wd & 0x0F0F0F0Fu, d, 8.f * d);
+            store4(stage + swz(row, b * 32 + 16 + 4 * c), (wd >> 4) & 0x0F0F0F0Fu, d, 8.f * d);
+        }
+    }
+}
+
+// ---- Q8_0 (quantized.rs:227-260): blocks of 32 int8, w = d * q
+struct Q80Regs {
+    uint4 q[8];
+    uint4 d[2];
+};
+__device__ __forceinline__ void q80_load(Q80Regs &u, const uint8_t *unit, int lane)
+{
+    const int r = lane >> 2;
+#pragma unroll
+    for (int i = 0; i < 8; i++) u.q[i] = __ldg(reinterpret_cast<const uint4 *>(unit + i * 512 + lane * 16));
+    u.d[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 4096 + r * 16));
+    u.d[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 4096 + (r + 8) * 16));
+}
+__device__ __forceinline__ void q80_emit(const Q80Regs &u, int g, uint32_t stage, int row0, int lane)
+{
+    const int r = lane >> 2, c = lane & 3;
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+        const int row = row0 + r + 8 * hi;
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const float d = f16_of(u.d[hi], 2 * g + b);
+#pragma unroll
+            for (int h = 0; h < 2; h++)   // q + 128 as an unsigned byte, then w = d * u - 128 d
+                store4(stage + swz(row, b * 32 + 16 * h + 4 * c), word_of(u.q[2 * g + b], hi * 2 + h) ^ 0x80808080u, d, 128.f * d);
+        }
+    }
+}
+
+template <int FMT> struct UnitRegs;
+template <> struct UnitRegs<12> { using type = Q4KRegs; };
+template <> struct UnitRegs<14> { using type = Q6KRegs; };
+template <> struct UnitRegs<2> { using type = Q40Regs; };
+template <> struct UnitRegs<8> { using type = Q80Regs; };
+__device__ __forceinline__ void unit_load(Q4KRegs &u, const uint8_t *p, int lane) { q4k_load(u, p, lane); }
+__device__ __forceinline__ void unit_load(Q6KRegs &u, const uint8_t *p, int lane) { q6k_load(u, p, lane); }
+__device__ __forceinline__ void unit_load(Q40Regs &u, const uint8_t *p, int lane) { q40_load(u, p, lane); }
+__device__ __forceinline__ void unit_load(Q80Regs &u, const uint8_t *p, int lane) { q80_load(u, p, lane); }
+__device__ __forceinline__ void unit_emit(const Q4KRegs &u, int g, uint32_t st, int row0, int lane) { q4k_emit(u, g, st, row0, lane); }
+__device__ __forceinline__ void unit_emit(const Q6KRegs &u, int g, uint32_t st, int row0, int lane) { q6k_emit(u, g, st, row0, lane); }
+__device__ __forceinline__ void unit_emit(const Q40Regs &u, int g, uint32_t st, int row0, int lane) { q40_emit(u, g, st, row0, lane); }
+__device__ __forceinline__ void unit_emit(const Q80Regs &u, int g, uint32_t st, int row0, int lane) { q80_emit(u, g, st, row0, lane); }
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
+{
+    // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart (stride offset), leading offset unused (1),
+    // descriptor version 1, layout type 2 (SWIZZLE_128B)
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// ---- the kernel
+template <int FMT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ int abort_word;
+    __shared__ uint32_t tmem_slot;
+    volatile int *abort_flag = &abort_word;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
+    const uint32_t sA = base, sB = base + kGemmStages * kStageA;
+    const uint32_t bars = sB + kGemmStages * kStageB;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kGemmStages + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * kGemmStages);
+
+    const int tok0 = blockIdx.y * p.nt;
+    const int KT = p.kt_total;
+
+    if (tid == 0) {
+        abort_word = 0;
+        for (int s = 0; s < kGemmStages; s++) {
+            mbar_init(full_bar(s), 9);    // eight dequantising warps + the TMA thread's arrive.expect_tx
+            mbar_init(empty_bar(s), 1);   // one tcgen05.commit
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp < 8) {
+        // ------------------------------------------------ dequantise the weight tile, stage by stage
+        const int tile16 = blockIdx.x * 8 + warp;
+        const bool have = tile16 < p.n_tiles16;
+        const uint8_t *ub = p.w + (size_t)(have ? tile16 : 0) * p.upt * p.unit_bytes;
+        const int units = (int)p.upt;
+        typename UnitRegs<FMT>::type cur, nxt;
+        if (have) unit_load(nxt, ub, lane);
+        bool ok = true;
+        for (int u = 0; u < units && ok; u++) {
+            if (have) {
+                cur = nxt;
+                if (u + 1 < units) unit_load(nxt, ub + (size_t)(u + 1) * p.unit_bytes, lane);
+            }
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                const int kt = u * 4 + g, s = kt % kGemmStages, round = kt / kGemmStages;
+                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, p.err, 21)) { ok = false; break; }
+                if (have) unit_emit(cur, g, sA + s * kStageA, warp * 16, lane);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> visible to the MMA's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_bar(s));
+            }
+        }
+        // ------------------------------------------------ epilogue: tensor memory -> Y[token][row]
+        if (ok && mbar_wait(accum_bar, 0, abort_flag, p.err, 22)) {
+            tc_fence_after();
+            const int quad = warp & 3, halfsel = warp >> 2;
+            const int row = blockIdx.x * kGemmRows + quad * 32 + lane;
+            const int c_begin = halfsel * (p.nt >> 1), c_end = c_begin + (p.nt >> 1);
+            for (int c0 = c_begin; c0 < c_end; c0 += 8) {
+                uint32_t v[8];
+                tmem_ld8(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int tok = tok0 + c0 + j;
+                    if (tok < p.m && row < p.n) p.out[(size_t)tok * p.n + row] = __uint_as_float(v[j]) * __ldg(p.inv_scale + tok);
+                }
+            }
+        }
+    } else if (warp == 8) {
+        // ------------------------------------------------ TMA: activation tile of each stage
+        if (lane == 0) {
+            int issued = 0;
+            for (int kt = 0; kt < KT; kt++) {
+                const int s = kt % kGemmStages, round = kt / kGemmStages;
+                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, p.err, 23)) break;
+                mbar_expect_tx(full_bar(s), (uint32_t)p.nt * 128u);
+                tma_load_2d(sB + s * kStageB, &xmap, kt * kGemmBK, tok0, full_bar(s));
+                issued = kt + 1;
+            }
+            if (*abort_flag) {
+                // let copies that were already requested land before the CTA gives its shared memory back
+                for (int kt = max(0, issued - kGemmStages); kt < issued; kt++)
+                    mbar_wait_drain(full_bar(kt % kGemmStages), (kt / kGemmStages) & 1);
+            }
+        }
+    } else {
+        // ------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(p.nt >> 3) << 17) | ((uint32_t)(kGemmRows >> 4) << 24);   // f32 D, f16 A/B, K-major both
+            bool ok = true;
+            for (int kt = 0; kt < KT; kt++) {
+                const int s = kt % kGemmStages, round = kt / kGemmStages;
+                if (!mbar_wait(full_bar(s), round & 1, abort_flag, p.err, 24)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t ad = smem_desc_sw128(sA + s * kStageA), bd = smem_desc_sw128(sB + s * kStageB);
+#pragma unroll
+                for (int k16 = 0; k16 < kGemmBK / 16; k16++)   // 16 f16 = 32 bytes further along the swizzle row
+                    umma_f16(tmem, ad + 2u * k16, bd + 2u * k16, idesc, (kt | k16) != 0);
+                umma_commit(empty_bar(s));   // arrives when the MMAs above have read the stage
+            }
+            umma_commit(accum_bar);
+            if (!ok) mbar_wait_drain(accum_bar, 0);   // MMAs already issued finish before the tensor memory is freed
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- activations: f32 rows -> f16 rows scaled by a power of two, and the inverse scale per row
+__global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__ x, __half *__restrict__ xh,
+                                                        float *__restrict__ inv_scale, int64_t k)
+{
+    __shared__ float red[8];
+    const float *row = x + (size_t)blockIdx.x * k;
+    __half *orow = xh + (size_t)blockIdx.x * k;
+    float amax = 0.f;
+    for (int64_t i = threadIdx.x * 4; i < k; i += 1024) {
+        const float4 v = *reinterpret_cast<const float4 *>(row + i);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+    for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
+    // amax = f * 2^e with f in [0.5, 1): scale by 2^(14 - e), so the largest element lands in [2^13, 2^14)
+    float scale = 1.f, inv = 1.f;
+    if (amax > 0.f && amax < 3.0e38f) {
+        int e;
+        frexpf(amax, &e);
+        scale = ldexpf(1.f, 14 - e);
+        inv = ldexpf(1.f, e - 14);
+    }
+    for (int64_t i = threadIdx.x * 4; i < k; i += 1024) {
+        const float4 v = *reinterpret_cast<const float4 *>(row + i);
+        __half2 a = __floats2half2_rn(v.x * scale, v.y * scale), b = __floats2half2_rn(v.z * scale, v.w * scale);
+        uint2 o2;
+        o2.x = *reinterpret_cast<uint32_t *>(&a);
+        o2.y = *reinterpret_cast<uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>(orow + i) = o2;
+    }
+    if (threadIdx.x == 0) inv_scale[blockIdx.x] = inv;
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder()
+{
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+        void *f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (PFN_cuTensorMapEncodeTiled_v12000)f;
+    }();
+    return fn;
+}
+
+// Activation rows per CTA: the widest tile that still gives every SM work, else 128 (more, smaller CTAs).
+int pick_token_tile(int64_t m, int64_t n, int sms)
+{
+    const int64_t row_tiles = (n + kGemmRows - 1) / kGemmRows;
+    if (m <= 128) return (int)((m + 15) / 16 * 16);
+    const int64_t ctas256 = row_tiles * ((m + 255) / 256);
+    if (m > 128 && ctas256 >= sms) return 256;
+    return 128;
+}
+
+}  // namespace
+
+bool qgemm_supported(int type) { return type == 12 || type == 14 || type == 2 || type == 8; }
+
+namespace {
+template <int FMT>
+tlb_status launch_fmt_gemm(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &map, const GemmParams &p)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        TLB_CUDA(cudaFuncSetAttribute(qgemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    qgemm_kernel<FMT><<<grid, kGemmThreads, smem, stream>>>(map, p);
+    return TLB_OK;
+}
+}  // namespace
+
+tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out)
+{
+    Context *c = ctx();
+    if (!c) return TLB_ERR_DEVICE;
+    if (!qgemm_supported(w->type)) return fail(TLB_ERR_TYPE, "tensor-core GEMM: GGML type %d is not supported", w->type);
+    if (w->k % 256 != 0 || m < 1 || m > INT32_MAX || w->n > INT32_MAX) return fail(TLB_ERR_SHAPE, "tensor-core GEMM: bad shape");
+    auto encode = tensor_map_encoder();
+    if (!encode) return fail(TLB_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+
+    Storage *xh = storage_alloc((size_t)m * w->k * sizeof(__half));
+    if (!xh) return TLB_ERR_ALLOC;
+    Storage *inv = storage_alloc((size_t)m * sizeof(float));
+    if (!inv) { storage_release(xh); return TLB_ERR_ALLOC; }
+    auto done = [&](tlb_status st) { storage_release(xh); storage_release(inv); return st; };
+
+    x_to_f16_kernel<<<(unsigned)m, 256, 0, c->stream>>>(x, (__half *)xh->ptr, (float *)inv->ptr, w->k);
+    count_launch();
+
+    const int nt = pick_token_tile(m, w->n, c->sm_count);
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)w->k, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)w->k * sizeof(__half)};
+    const cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)nt};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return done(fail(TLB_ERR_DEVICE, "cuTensorMapEncodeTiled failed (%d)", (int)r));
+
+    GemmParams p;
+    p.w = w->dev();
+    p.upt = w->upt;
+    p.n_tiles16 = (int)w->n_tiles;
+    p.n = (int)w->n;
+    p.m = (int)m;
+    p.nt = nt;
+    p.kt_total = (int)(w->k / kGemmBK);
+    p.unit_bytes = qformat(w->type)->unit_bytes;
+    p.out = out;
+    p.inv_scale = (const float *)inv->ptr;
+    p.err = c->err_flag;
+
+    const size_t smem = (size_t)kGemmStages * (kStageA + kStageB) + 1024 + 128;
+    dim3 grid((unsigned)((w->n + kGemmRows - 1) / kGemmRows), (unsigned)((m + nt - 1) / nt));
+    tlb_status ls;
+    switch (w->type) {
+        case 12: ls = launch_fmt_gemm<12>(grid, smem, c->stream, map, p); break;
+        case 14: ls = launch_fmt_gemm<14>(grid, smem, c->stream, map, p); break;
+        case 2: ls = launch_fmt_gemm<2>(grid, smem, c->stream, map, p); break;
+        default: ls = launch_fmt_gemm<8>(grid, smem, c->stream, map, p); break;
+    }
+    if (ls != TLB_OK) return done(ls);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return done(cuda_fail(e, "qgemm launch"));
+    return done(TLB_OK);
+}
+
+}  // namespace tlb

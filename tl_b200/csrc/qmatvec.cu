@@ -643,6 +643,12 @@ extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, 
     TLB_TRY(new_tensor(out, TLB_F32, oshape, x->rank));
     if (m * w->n == 0) return TLB_OK;
     tlb_status st = TLB_OK;
+    if (m > kGemmMinRows && qgemm_supported(w->type) && ((uintptr_t)x->f32() & 15) == 0) {
+        // many rows (prompt processing): tensor-core GEMM, the weight is read once per 256 rows
+        st = launch_qgemm(w, x->f32(), m, (*out)->f32());
+        if (st != TLB_OK) { tlb_tensor_release(*out); *out = nullptr; }
+        return st;
+    }
     for (int64_t m0 = 0; m0 < m && st == TLB_OK; m0 += 4) {   // the weight stream is repeated per group of 4 rows
         MatvecJob job;
         job.n_w = 1;

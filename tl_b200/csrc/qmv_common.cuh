@@ -40,7 +40,7 @@ __device__ __forceinline__ unsigned long long global_ns()
     return t;
 }
 // Bounded wait: gives up after ~2 s, records the reason and raises the CTA-wide abort flag.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err, int code)
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err, int code)
 {
     unsigned long long t0 = global_ns();
     for (int it = 0;; it++) {

@@ -110,6 +110,10 @@ namespace tlb {
 
 // ---- kernel launchers (all on ctx()->stream) ------------------------------------------
 // quant.cu
+// qgemm_tc.cu: Y[m, n] = X[m, k] . W^T on the tensor cores (tcgen05), for m above kGemmMinRows
+constexpr int kGemmMinRows = 16;
+bool qgemm_supported(int ggml_type);
+tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out);
 tlb_status launch_repack(int type, const uint8_t *raw, uint8_t *tiled, int64_t n, int64_t k);
 tlb_status launch_dequant_tiled(int type, const uint8_t *tiled, float *out, int64_t n, int64_t k);
 tlb_status launch_interleave8(int type, const uint8_t *a, const uint8_t *b, uint8_t *dst, int64_t n, int64_t k);
