@@ -210,6 +210,14 @@ tlb_status tlb_decoder_step(tlb_decoder *d, int32_t token, int32_t pos, int32_t 
 /* n greedy steps with the token fed back on the device, no host round trip in between;
  * tokens_out (host, n entries, may be NULL) is read back once at the end. */
 tlb_status tlb_decoder_generate(tlb_decoder *d, int32_t first_token, int32_t start_pos, int32_t n, int32_t *tokens_out);
+/* A whole prompt at once: token i goes to cache row pos0 + i and is rotated by table row rope_pos0 + i * rope_step
+ * (rope_step 1: every token at its own position; rope_step 0: the whole prompt at rope_pos0, which is what the
+ * reference CPU path does, crates/tl_cpu/src/ffi.rs:2661-2674).  Same result as n calls of tlb_decoder_step within
+ * the f16 operand rounding of the tensor-core GEMMs (examples/apps/llama3/chatbot_llama3.tl:220-236 runs the same
+ * layers on the whole prompt); *next (may be NULL) receives the greedy token after the last prompt token, and
+ * tlb_decoder_logits / tlb_decoder_hidden then describe that last token.  Prompts of 16 tokens or fewer, and
+ * shapes the GEMM does not take, run token by token through the fused chain. */
+tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens, int32_t n, int32_t pos0, int32_t rope_pos0, int32_t rope_step, int32_t *next);
 tlb_status tlb_decoder_logits(tlb_decoder *d, float *logits_out /* host, vocab floats */);
 tlb_status tlb_decoder_hidden(tlb_decoder *d, float *hidden_out /* host, d_model floats: residual stream before output_norm */);
 /* algorithmic bytes one decode step reads at context length ctx (weights + KV), kernels per step */

@@ -127,3 +127,83 @@ def test_gguf_file_round_trip(orc, tmp_path):
         m.get_quantized("token_embd.weight")   # F32 tensors have no quantized kernel
     with pytest.raises(tl.TlbError):
         m.get("missing.weight")
+
+
+# ---- whole prompts at once (tensor-core GEMMs + prompt attention) ---------------------------------------
+PROMPT = 70   # > 64: two query tiles of the prompt attention, ragged second tile
+
+
+@pytest.mark.parametrize("linear,head,kv_f16", [(synth.Q4_K, synth.Q6_K, True), (synth.Q4_K, synth.Q6_K, False),
+                                                 (synth.Q4_0, synth.Q4_0, False), (synth.Q8_0, synth.Q8_0, True)])
+def test_prefill_matches_oracle_and_continues(orc, linear, head, kv_f16):
+    """The prompt in one call (reference CPU rotation: every prompt token at row 0), then greedy decoding."""
+    ref, dec, wmap = build(orc, SMALL, 11, linear, head, kv_f16, 128)
+    rng = np.random.default_rng(5)
+    prompt = [int(t) for t in rng.integers(0, SMALL["vocab"], PROMPT)]
+    ref_logits = ref.forward(prompt, 0)
+    nxt = dec.prefill(prompt, 0, rope_pos0=0, rope_step=0)
+    assert relerr(dec.logits(), ref_logits) < LOGIT_TOL
+    tok = orc.argmax_last(ref_logits)
+    assert nxt == tok
+    pos, worst = PROMPT, 0.0
+    for s in range(16):
+        ref_logits = ref.forward([tok], pos)
+        nxt = dec.step(tok, pos)
+        worst = max(worst, relerr(dec.logits(), ref_logits))
+        tok = orc.argmax_last(ref_logits)
+        assert nxt == tok
+        pos += 1
+    # The cache rows a prompt leaves carry the f16 operand rounding of the GEMMs (~5e-4).  The synthetic Q8_0
+    # model (uniform int8 weights) amplifies that in its near-one-hot attention; its gate is on tokens only.
+    if linear != synth.Q8_0:
+        assert worst < LOGIT_TOL, worst
+
+
+def test_prefill_in_chunks_equals_token_by_token(orc):
+    """Per-position rotation; a prompt given as two calls at consecutive cache rows against single-token steps."""
+    ref, dec, wmap = build(orc, SMALL, 12, synth.Q4_K, synth.Q6_K, True, 128)
+    rng = np.random.default_rng(6)
+    prompt = [int(t) for t in rng.integers(0, SMALL["vocab"], PROMPT)]
+    dec.prefill(prompt[:30], 0)
+    a = dec.prefill(prompt[30:], 30)
+    la, ha = dec.logits(), dec.hidden()
+    dec2 = tl.Decoder(SMALL, wmap, kv_f16=True, max_seq=128)
+    for i, t in enumerate(prompt):
+        b = dec2.step(t, i)
+    assert a == b
+    assert relerr(la, dec2.logits()) < 2e-3
+    assert relerr(ha, dec2.hidden()) < 2e-3
+    # both sessions go on identically
+    assert dec.generate(a, PROMPT, 8) == dec2.generate(b, PROMPT, 8)
+
+
+def test_prefill_short_prompt_and_errors(orc):
+    ref, dec, wmap = build(orc, SMALL, 13, synth.Q4_K, synth.Q6_K, True, 64)
+    dec2 = tl.Decoder(SMALL, wmap, kv_f16=True, max_seq=64)
+    prompt = [3, 1, 4, 1, 5]
+    a = dec.prefill(prompt, 0)             # 16 tokens or fewer: the single-token chain, bit for bit
+    for i, t in enumerate(prompt):
+        b = dec2.step(t, i)
+    assert a == b
+    np.testing.assert_array_equal(dec.logits().view(np.uint32), dec2.logits().view(np.uint32))
+    with pytest.raises(tl.TlbError) as e:
+        dec.prefill([SMALL["vocab"]] * 20, 0)          # token out of range
+    assert e.value.code == 6
+    with pytest.raises(tl.TlbError) as e:
+        dec.prefill([1] * 40, 30)                      # rows 30..69 do not fit a cache of 64
+    assert e.value.code == 6
+    with pytest.raises(tl.TlbError) as e:
+        dec.prefill([], 0)
+    assert e.value.code == 8
+
+
+def test_prefill_llama3_shaped_one_layer(orc):
+    """Llama-3-8B layer shapes (head_dim 128, GQA 4, Q4_K + Q6_K head): 300-token prompt against the oracle."""
+    cfg = dict(synth.LLAMA3_8B, n_layers=1)
+    ref, dec, wmap = build(orc, cfg, 4, synth.Q4_K, synth.Q6_K, True, 384)
+    rng = np.random.default_rng(7)
+    prompt = [int(t) for t in rng.integers(0, cfg["vocab"], 300)]
+    ref_logits = ref.forward(prompt, 0)
+    nxt = dec.prefill(prompt, 0, rope_pos0=0, rope_step=0)
+    assert relerr(dec.logits(), ref_logits) < LOGIT_TOL
+    assert nxt == orc.argmax_last(ref_logits)

@@ -300,6 +300,14 @@ class Decoder:
                                      C.byref(nxt) if read else None))
         return nxt.value
 
+    def prefill(self, tokens, pos0=0, rope_pos0=None, rope_step=1, read=True):
+        """All prompt tokens at once (cache rows pos0.., rotation rows rope_pos0 + i * rope_step); returns the greedy next token."""
+        toks = (C.c_int32 * max(1, len(tokens)))(*[int(t) for t in tokens])
+        nxt = C.c_int32(-1)
+        check(lib().tlb_decoder_prefill(self.h, toks, len(tokens), pos0, pos0 if rope_pos0 is None else rope_pos0, rope_step,
+                                        C.byref(nxt) if read else None))
+        return nxt.value
+
     def generate(self, first_token, start_pos, n, read=True):
         out = (C.c_int32 * max(1, n))()
         check(lib().tlb_decoder_generate(self.h, first_token, start_pos, n, out if read else None))

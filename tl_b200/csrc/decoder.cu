@@ -161,6 +161,49 @@ void set_w(MatvecJob &j, int i, const tlb_qtensor *q, float *out)
 }
 
 // the kernel chain of one decode step (launched eagerly or into a capturing stream)
+// output_norm + head + greedy token (with the advance of the decode state) on the residual in xb.
+// ssq_parts: per-tile sums of squares of xb left by the launch that wrote it, or null (the head launch sums itself).
+tlb_status enqueue_head(tlb_decoder *d, const float *ssq_parts, unsigned long long *span)
+{
+    const tlb_decoder_cfg &c = d->cfg;
+    const int dm = c.d_model;
+    {   // output_norm + head
+        MatvecJob j;
+        j.n_w = 1;
+        set_w(j, 0, d->head, d->logits);
+        j.type = d->head->type; j.k = dm; j.m = 1; j.slices = d->force_slices[4];
+        j.prologue = PRO_ADD_NORM; j.x = d->xb; j.ssq_parts = ssq_parts; j.n_parts = ssq_parts ? (dm + 15) / 16 : 0;
+        j.norm_w = d->out_norm->f32(); j.eps = c.eps;
+        j.last_of_chain = true;
+        j.pdl = d->pdl;
+        j.span = span;
+        j.dry_run = d->dry;
+        TLB_TRY(launch_qmatvec(j));
+    }
+    if (!d->dry) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kArgmaxBlocks);
+        cfg.blockDim = dim3(256);
+        cfg.stream = ctx()->stream;
+        cudaLaunchAttribute at[1];
+        if (d->pdl) {
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+        }
+        static bool carveout_set = false;
+        if (!carveout_set) {
+            TLB_CUDA(cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            carveout_set = true;
+        }
+        TLB_CUDA(cudaLaunchKernelEx(&cfg, argmax_advance_kernel, (const float *)d->logits, (int)c.vocab, (int)(c.tie_rule == TLB_TIE_FIRST), d->amax_v, d->amax_i, d->counters + c.n_kv_heads,
+                                    d->state, d->tokens_out, d->tokens_cap, (int)d->pdl));
+        count_launch();
+    }
+    return TLB_OK;
+}
+
 tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
 {
     const tlb_decoder_cfg &c = d->cfg;
@@ -241,40 +284,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             TLB_TRY(launch_qmatvec(j));
         }
     }
-    {   // output_norm + head
-        MatvecJob j;
-        j.n_w = 1;
-        set_w(j, 0, d->head, d->logits);
-        j.type = d->head->type; j.k = dm; j.m = 1; j.slices = d->force_slices[4];
-        j.prologue = PRO_ADD_NORM; j.x = d->xb; j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16;
-        j.norm_w = d->out_norm->f32(); j.eps = c.eps;
-        j.last_of_chain = true;
-        j.pdl = d->pdl;
-        j.span = next_span();
-        j.dry_run = d->dry;
-        TLB_TRY(launch_qmatvec(j));
-    }
-    if (!d->dry) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(kArgmaxBlocks);
-        cfg.blockDim = dim3(256);
-        cfg.stream = ctx()->stream;
-        cudaLaunchAttribute at[1];
-        if (d->pdl) {
-            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            at[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = at;
-            cfg.numAttrs = 1;
-        }
-        static bool carveout_set = false;
-        if (!carveout_set) {
-            TLB_CUDA(cudaFuncSetAttribute(argmax_advance_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-            carveout_set = true;
-        }
-        TLB_CUDA(cudaLaunchKernelEx(&cfg, argmax_advance_kernel, (const float *)d->logits, (int)c.vocab, (int)(c.tie_rule == TLB_TIE_FIRST), d->amax_v, d->amax_i, d->counters + c.n_kv_heads,
-                                    d->state, d->tokens_out, d->tokens_cap, (int)d->pdl));
-        count_launch();
-    }
+    TLB_TRY(enqueue_head(d, d->ssq_d, next_span()));
     return TLB_OK;
 }
 
@@ -672,3 +682,116 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
 }
 
 }  // extern "C"
+
+// Prompt processing: `n` tokens at once.  Per layer: norm -> q, k, v GEMMs -> RoPE + cache append -> causal
+// attention over the cache -> o GEMM (+ residual) -> norm -> gate, up GEMMs -> silu * up -> down GEMM (+ residual);
+// then the decode head on the last token.  Prompts are cut into chunks so the f32 work space stays bounded.
+namespace {
+constexpr int kPrefillChunk = 2048;
+
+bool prefill_batched_ok(const tlb_decoder *d)
+{
+    const tlb_decoder_cfg &c = d->cfg;
+    const LayerW &w = d->layers[0];
+    const int qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim;
+    return qgemm_supported(w.q->type) && qgemm_supported(w.o->type) && qgemm_supported(w.gate->type) && qgemm_supported(w.down->type) &&
+           prefill_attention_supported(c.head_dim) && c.d_model % 256 == 0 && qd % 256 == 0 && c.ffn % 256 == 0 && kvd % 4 == 0;
+}
+
+struct Scratch {
+    std::vector<Storage *> all;
+    template <typename T> tlb_status get(T **p, size_t count)
+    {
+        Storage *s = storage_alloc(count * sizeof(T));
+        if (!s) return TLB_ERR_ALLOC;
+        all.push_back(s);
+        *p = (T *)s->ptr;
+        return TLB_OK;
+    }
+    ~Scratch() { for (Storage *s : all) storage_release(s); }
+};
+
+tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0, int rope0, int rope_step, bool last)
+{
+    const tlb_decoder_cfg &c = d->cfg;
+    const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
+    const size_t esz = c.kv_f16 ? 2 : 4;
+    Scratch ws;
+    int *tok_d;
+    float *x, *x2, *q, *k, *v, *att, *g, *u;
+    TLB_TRY(ws.get(&tok_d, (size_t)T));
+    TLB_TRY(ws.get(&x, (size_t)T * dm)); TLB_TRY(ws.get(&x2, (size_t)T * dm));
+    TLB_TRY(ws.get(&q, (size_t)T * qd)); TLB_TRY(ws.get(&k, (size_t)T * kvd)); TLB_TRY(ws.get(&v, (size_t)T * kvd));
+    TLB_TRY(ws.get(&att, (size_t)T * qd));
+    TLB_TRY(ws.get(&g, (size_t)T * F)); TLB_TRY(ws.get(&u, (size_t)T * F));
+    TLB_CUDA(cudaMemcpyAsync(tok_d, tokens, (size_t)T * sizeof(int), cudaMemcpyHostToDevice, ctx()->stream));
+    TLB_TRY(launch_embed_rows(tok_d, d->emb->f32(), x, T, dm));
+    for (int l = 0; l < c.n_layers; l++) {
+        const LayerW &w = d->layers[l];
+        void *kc = (char *)d->kcache + (size_t)l * d->kv_layer_elems * esz, *vc = (char *)d->vcache + (size_t)l * d->kv_layer_elems * esz;
+        GemmAct a;
+        tlb_status st;
+        TLB_TRY(qgemm_prepare(&a, x, T, dm, w.attn_norm->f32(), c.eps));
+        {
+            const tlb_qtensor *ws3[3] = {w.q, w.k, w.v};
+            float *outs3[3] = {q, k, v};
+            st = qgemm_run_multi(ws3, 3, a, outs3, nullptr);
+        }
+        qgemm_release(&a);
+        TLB_TRY(st);
+        TLB_TRY(launch_rope_append(q, k, v, kc, vc, c.kv_f16, d->cos_t, d->sin_t, T, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, pos0, rope0, rope_step));
+        TLB_TRY(launch_prefill_attention(q, kc, vc, c.kv_f16, att, T, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, pos0, c.attn_scale));
+        TLB_TRY(qgemm_prepare(&a, att, T, qd, nullptr, 0.f));
+        st = qgemm_run(w.o, a, x2, x);                 // x2 = x + o_proj(attention)
+        qgemm_release(&a);
+        TLB_TRY(st);
+        TLB_TRY(qgemm_prepare(&a, x2, T, dm, w.ffn_norm->f32(), c.eps));
+        {
+            const tlb_qtensor *ws2[2] = {w.gate, w.up};
+            float *outs2[2] = {g, u};
+            st = qgemm_run_multi(ws2, 2, a, outs2, nullptr);
+        }
+        qgemm_release(&a);
+        TLB_TRY(st);
+        TLB_TRY(launch_silu_mul(g, u, g, (size_t)T * F));
+        TLB_TRY(qgemm_prepare(&a, g, T, F, nullptr, 0.f));
+        st = qgemm_run(w.down, a, x, x2);              // x = x2 + down(silu(gate) * up)
+        qgemm_release(&a);
+        TLB_TRY(st);
+    }
+    if (last) TLB_CUDA(cudaMemcpyAsync(d->xb, x + (size_t)(T - 1) * dm, (size_t)dm * sizeof(float), cudaMemcpyDeviceToDevice, ctx()->stream));
+    return TLB_OK;
+}
+}  // namespace
+
+extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens, int32_t n, int32_t pos0, int32_t rope_pos0, int32_t rope_step, int32_t *next)
+{
+    if (!d || !tokens) return fail(TLB_ERR_NULL, "null argument");
+    const tlb_decoder_cfg &c = d->cfg;
+    if (n < 1) return fail(TLB_ERR_ARG, "prefill needs at least one token");
+    for (int i = 0; i < n; i++)
+        if (tokens[i] < 0 || tokens[i] >= c.vocab) return fail(TLB_ERR_INDEX, "Embedding index %d out of range for vocab size %d", tokens[i], c.vocab);
+    const int64_t last_rope = (int64_t)rope_pos0 + (int64_t)(n - 1) * rope_step;
+    if (pos0 < 0 || (int64_t)pos0 + n > c.max_seq || rope_pos0 < 0 || rope_step < 0 || last_rope >= c.max_seq)
+        return fail(TLB_ERR_INDEX, "positions [%d, %d) / rotation rows up to %lld outside the cache of %d rows", pos0, pos0 + n, (long long)last_rope, c.max_seq);
+    if (n <= kGemmMinRows || !prefill_batched_ok(d)) {
+        // few tokens, or a shape the GEMM path does not take: the fused single-token chain, token by token
+        int32_t tok = 0;
+        for (int i = 0; i < n; i++) TLB_TRY(tlb_decoder_step(d, tokens[i], pos0 + i, rope_pos0 + i * rope_step, i == n - 1 ? &tok : nullptr));
+        if (next) *next = tok;
+        return TLB_OK;
+    }
+    for (int off = 0; off < n; off += kPrefillChunk) {
+        const int T = std::min(kPrefillChunk, n - off);
+        TLB_TRY(prefill_chunk(d, tokens + off, T, pos0 + off, rope_pos0 + off * rope_step, rope_step, off + T == n));
+    }
+    // head on the last token; the state then names the next token and the row it will occupy
+    TLB_TRY(set_state(d, tokens[n - 1], pos0 + n - 1, (int)last_rope, 0));
+    TLB_TRY(enqueue_head(d, nullptr, nullptr));
+    if (next) {
+        TLB_CUDA(cudaMemcpyAsync(d->h_state, d->state, sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
+        TLB_TRY(tlb_sync());
+        *next = d->h_state[0];
+    }
+    return TLB_OK;
+}

@@ -42,17 +42,22 @@ constexpr int kStageB = kGemmMaxTok * kGemmBK * 2;    // 32 KB
 constexpr int kGemmThreads = 320;   // warps 0-7: dequantise + epilogue, warp 8: TMA, warp 9: MMA + tensor memory
 constexpr int kTmemCols = 256;
 
+constexpr int kGemmMaxW = 3;        // weights of one launch (q | k | v share their activations)
+
 struct GemmParams {
-    const uint8_t *w;       // tiled units
+    const uint8_t *w[kGemmMaxW];   // tiled units of each weight
+    float *out[kGemmMaxW];         // [m, n[i]]
+    int n[kGemmMaxW];              // weight rows (output features)
+    int n_tiles16[kGemmMaxW];      // 16-row tiles
+    int rt_end[kGemmMaxW];         // CTA row tiles (128 rows) up to and including weight i
+    int n_w;
     int64_t upt;            // units per 16-row tile (K / 256)
-    int n_tiles16;          // 16-row tiles of the weight
-    int n;                  // weight rows (output features)
     int m;                  // activation rows
     int nt;                 // activation rows per CTA
     int kt_total;           // K / 64
     int unit_bytes;
-    float *out;             // [m, n]
     const float *inv_scale; // [m]
+    const float *resid;     // [m, n] added to the result, or null
     int *err;
 };
 
@@ -73,6 +78,10 @@ __device__ __forceinline__ float byte_f32(uint32_t bytes, int t)
 // Four weights w = q * ds - dm from the four bytes of `bytes`, rounded to f16 and stored as 8 bytes.
 __device__ __forceinline__ void store4(uint32_t addr, uint32_t bytes, float ds, float dm)
 {
+#ifdef QG_NODEQ
+    sts64(addr, bytes, __float_as_uint(ds) ^ __float_as_uint(dm));
+    return;
+#endif
     const float f0 = fmaf(byte_f32(bytes, 0), ds, -dm), f1 = fmaf(byte_f32(bytes, 1), ds, -dm);
     const float f2 = fmaf(byte_f32(bytes, 2), ds, -dm), f3 = fmaf(byte_f32(bytes, 3), ds, -dm);
     sts64(addr, pack_h2(f0, f1), pack_h2(f2, f3));
@@ -318,6 +327,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
 
     const int tok0 = blockIdx.y * p.nt;
     const int KT = p.kt_total;
+    int wi = 0;
+    while (wi + 1 < p.n_w && (int)blockIdx.x >= p.rt_end[wi]) wi++;
+    const int rt = (int)blockIdx.x - (wi ? p.rt_end[wi - 1] : 0);   // 128-row tile inside weight wi
+    const int n_rows = p.n[wi];
 
     if (tid == 0) {
         abort_word = 0;
@@ -340,9 +353,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
 
     if (warp < 8) {
         // ------------------------------------------------ dequantise the weight tile, stage by stage
-        const int tile16 = blockIdx.x * 8 + warp;
-        const bool have = tile16 < p.n_tiles16;
-        const uint8_t *ub = p.w + (size_t)(have ? tile16 : 0) * p.upt * p.unit_bytes;
+        const int tile16 = rt * 8 + warp;
+        const bool have = tile16 < p.n_tiles16[wi];
+        const uint8_t *ub = p.w[wi] + (size_t)(have ? tile16 : 0) * p.upt * p.unit_bytes;
         const int units = (int)p.upt;
         typename UnitRegs<FMT>::type cur, nxt;
         if (have) unit_load(nxt, ub, lane);
@@ -366,15 +379,28 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
         if (ok && mbar_wait(accum_bar, 0, abort_flag, p.err, 22)) {
             tc_fence_after();
             const int quad = warp & 3, halfsel = warp >> 2;
-            const int row = blockIdx.x * kGemmRows + quad * 32 + lane;
+            const int row = rt * kGemmRows + quad * 32 + lane;
+            float *out = p.out[wi];
             const int c_begin = halfsel * (p.nt >> 1), c_end = c_begin + (p.nt >> 1);
             for (int c0 = c_begin; c0 < c_end; c0 += 8) {
+                // the residual and the row scales first (independent loads in flight together), then the accumulator
+                float rs[8], sc[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int tok = tok0 + c0 + j;
+                    const bool live = tok < p.m && row < n_rows;
+                    sc[j] = tok < p.m ? __ldg(p.inv_scale + tok) : 0.f;
+                    rs[j] = (live && p.resid) ? __ldg(p.resid + (size_t)tok * n_rows + row) : 0.f;
+                }
                 uint32_t v[8];
                 tmem_ld8(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int tok = tok0 + c0 + j;
-                    if (tok < p.m && row < p.n) p.out[(size_t)tok * p.n + row] = __uint_as_float(v[j]) * __ldg(p.inv_scale + tok);
+#ifdef QG_NOEPI
+                    if (v[j] == 0x12345678u)
+#endif
+                    if (tok < p.m && row < n_rows) out[(size_t)tok * n_rows + row] = rs[j] + __uint_as_float(v[j]) * sc[j];
                 }
             }
         }
@@ -385,6 +411,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
             for (int kt = 0; kt < KT; kt++) {
                 const int s = kt % kGemmStages, round = kt / kGemmStages;
                 if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, p.err, 23)) break;
+#ifdef QG_NOTMA
+                if (kt >= kGemmStages) { mbar_arrive(full_bar(s)); issued = kt + 1; continue; }
+#endif
                 mbar_expect_tx(full_bar(s), (uint32_t)p.nt * 128u);
                 tma_load_2d(sB + s * kStageB, &xmap, kt * kGemmBK, tok0, full_bar(s));
                 issued = kt + 1;
@@ -422,23 +451,36 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     }
 }
 
-// ---- activations: f32 rows -> f16 rows scaled by a power of two, and the inverse scale per row
-__global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__ x, __half *__restrict__ xh,
-                                                        float *__restrict__ inv_scale, int64_t k)
+// ---- activations: f32 rows -> f16 rows scaled by a power of two, and the inverse scale per row.
+// With norm_w the row is RMS-normalised first: v = x / sqrt(mean(x^2) + eps) * w
+// (crates/tl_cpu/src/ffi.rs:2444-2486).
+__global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__ x, const float *__restrict__ norm_w, float eps,
+                                                        __half *__restrict__ xh, float *__restrict__ inv_scale, int64_t k)
 {
-    __shared__ float red[8];
+    __shared__ float red[2][8];
     const float *row = x + (size_t)blockIdx.x * k;
     __half *orow = xh + (size_t)blockIdx.x * k;
-    float amax = 0.f;
+    float amax = 0.f, ssq = 0.f;
     for (int64_t i = threadIdx.x * 4; i < k; i += 1024) {
-        const float4 v = *reinterpret_cast<const float4 *>(row + i);
+        float4 v = *reinterpret_cast<const float4 *>(row + i);
+        if (norm_w) {
+            ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            const float4 w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
+            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+        }
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
     }
-    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    for (int o = 16; o; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    }
+    if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = amax; red[1][threadIdx.x >> 5] = ssq; }
     __syncthreads();
-    amax = red[0];
-    for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
+    amax = red[0][0];
+    ssq = red[1][0];
+    for (int i = 1; i < 8; i++) { amax = fmaxf(amax, red[0][i]); ssq += red[1][i]; }
+    const float inv_rms = norm_w ? 1.0f / sqrtf(ssq / (float)k + eps) : 1.0f;
+    amax *= inv_rms;
     // amax = f * 2^e with f in [0.5, 1): scale by 2^(14 - e), so the largest element lands in [2^13, 2^14)
     float scale = 1.f, inv = 1.f;
     if (amax > 0.f && amax < 3.0e38f) {
@@ -448,7 +490,11 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__
         inv = ldexpf(1.f, e - 14);
     }
     for (int64_t i = threadIdx.x * 4; i < k; i += 1024) {
-        const float4 v = *reinterpret_cast<const float4 *>(row + i);
+        float4 v = *reinterpret_cast<const float4 *>(row + i);
+        if (norm_w) {
+            const float4 w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
+            v.x = v.x * inv_rms * w.x; v.y = v.y * inv_rms * w.y; v.z = v.z * inv_rms * w.z; v.w = v.w * inv_rms * w.w;
+        }
         __half2 a = __floats2half2_rn(v.x * scale, v.y * scale), b = __floats2half2_rn(v.z * scale, v.w * scale);
         uint2 o2;
         o2.x = *reinterpret_cast<uint32_t *>(&a);
@@ -498,61 +544,101 @@ tlb_status launch_fmt_gemm(dim3 grid, size_t smem, cudaStream_t stream, const CU
 }
 }  // namespace
 
-tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out)
+tlb_status qgemm_prepare(GemmAct *a, const float *x, int64_t m, int64_t k, const float *norm_w, float eps)
 {
     Context *c = ctx();
     if (!c) return TLB_ERR_DEVICE;
-    if (!qgemm_supported(w->type)) return fail(TLB_ERR_TYPE, "tensor-core GEMM: GGML type %d is not supported", w->type);
-    if (w->k % 256 != 0 || m < 1 || m > INT32_MAX || w->n > INT32_MAX) return fail(TLB_ERR_SHAPE, "tensor-core GEMM: bad shape");
+    a->xh = a->inv = nullptr;
+    a->m = m; a->k = k;
+    if (k % 256 != 0 || m < 1 || m > INT32_MAX) return fail(TLB_ERR_SHAPE, "tensor-core GEMM: bad activation shape");
+    if (((uintptr_t)x & 15) || (norm_w && ((uintptr_t)norm_w & 15))) return fail(TLB_ERR_ARG, "tensor-core GEMM: activations must be 16-byte aligned");
+    a->xh = storage_alloc((size_t)m * k * sizeof(__half));
+    if (!a->xh) return TLB_ERR_ALLOC;
+    a->inv = storage_alloc((size_t)m * sizeof(float));
+    if (!a->inv) { storage_release(a->xh); a->xh = nullptr; return TLB_ERR_ALLOC; }
+    x_to_f16_kernel<<<(unsigned)m, 256, 0, c->stream>>>(x, norm_w, eps, (__half *)a->xh->ptr, (float *)a->inv->ptr, k);
+    count_launch();
+    return TLB_OK;
+}
+
+void qgemm_release(GemmAct *a)
+{
+    if (a->xh) storage_release(a->xh);
+    if (a->inv) storage_release(a->inv);
+    a->xh = a->inv = nullptr;
+}
+
+tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct &a, float *const *outs, const float *resid)
+{
+    Context *c = ctx();
+    if (!c) return TLB_ERR_DEVICE;
+    if (n_w < 1 || n_w > kGemmMaxW || (resid && n_w != 1)) return fail(TLB_ERR_ARG, "tensor-core GEMM: %d weights in one launch", n_w);
+    const tlb_qtensor *w0 = ws[0];
+    if (!qgemm_supported(w0->type)) return fail(TLB_ERR_TYPE, "tensor-core GEMM: GGML type %d is not supported", w0->type);
+    GemmParams p;
+    int64_t row_tiles = 0, n_max = 0;
+    for (int i = 0; i < kGemmMaxW; i++) {
+        const tlb_qtensor *w = i < n_w ? ws[i] : nullptr;
+        if (w && (w->type != w0->type || w->k != a.k || w->n > INT32_MAX))
+            return fail(TLB_ERR_SHAPE, "tensor-core GEMM: weight K %lld vs activation K %lld, or mixed types", (long long)w->k, (long long)a.k);
+        if (w) { row_tiles += (w->n + kGemmRows - 1) / kGemmRows; n_max = std::max(n_max, row_tiles * kGemmRows); }
+        p.w[i] = w ? w->dev() : nullptr;
+        p.out[i] = w ? outs[i] : nullptr;
+        p.n[i] = w ? (int)w->n : 0;
+        p.n_tiles16[i] = w ? (int)w->n_tiles : 0;
+        p.rt_end[i] = (int)row_tiles;
+    }
     auto encode = tensor_map_encoder();
     if (!encode) return fail(TLB_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-
-    Storage *xh = storage_alloc((size_t)m * w->k * sizeof(__half));
-    if (!xh) return TLB_ERR_ALLOC;
-    Storage *inv = storage_alloc((size_t)m * sizeof(float));
-    if (!inv) { storage_release(xh); return TLB_ERR_ALLOC; }
-    auto done = [&](tlb_status st) { storage_release(xh); storage_release(inv); return st; };
-
-    x_to_f16_kernel<<<(unsigned)m, 256, 0, c->stream>>>(x, (__half *)xh->ptr, (float *)inv->ptr, w->k);
-    count_launch();
-
-    const int nt = pick_token_tile(m, w->n, c->sm_count);
+    const int64_t m = a.m;
+    const int nt = pick_token_tile(m, n_max, c->sm_count);
     CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)w->k, (cuuint64_t)m};
-    const cuuint64_t strides[1] = {(cuuint64_t)w->k * sizeof(__half)};
+    const cuuint64_t dims[2] = {(cuuint64_t)a.k, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)a.k * sizeof(__half)};
     const cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)nt};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.xh->ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return done(fail(TLB_ERR_DEVICE, "cuTensorMapEncodeTiled failed (%d)", (int)r));
+    if (r != CUDA_SUCCESS) return fail(TLB_ERR_DEVICE, "cuTensorMapEncodeTiled failed (%d)", (int)r);
 
-    GemmParams p;
-    p.w = w->dev();
-    p.upt = w->upt;
-    p.n_tiles16 = (int)w->n_tiles;
-    p.n = (int)w->n;
+    p.n_w = n_w;
+    p.upt = w0->upt;
     p.m = (int)m;
     p.nt = nt;
-    p.kt_total = (int)(w->k / kGemmBK);
-    p.unit_bytes = qformat(w->type)->unit_bytes;
-    p.out = out;
-    p.inv_scale = (const float *)inv->ptr;
+    p.kt_total = (int)(a.k / kGemmBK);
+    p.unit_bytes = qformat(w0->type)->unit_bytes;
+    p.inv_scale = (const float *)a.inv->ptr;
+    p.resid = resid;
     p.err = c->err_flag;
 
     const size_t smem = (size_t)kGemmStages * (kStageA + kStageB) + 1024 + 128;
-    dim3 grid((unsigned)((w->n + kGemmRows - 1) / kGemmRows), (unsigned)((m + nt - 1) / nt));
+    dim3 grid((unsigned)row_tiles, (unsigned)((m + nt - 1) / nt));
     tlb_status ls;
-    switch (w->type) {
+    switch (w0->type) {
         case 12: ls = launch_fmt_gemm<12>(grid, smem, c->stream, map, p); break;
         case 14: ls = launch_fmt_gemm<14>(grid, smem, c->stream, map, p); break;
         case 2: ls = launch_fmt_gemm<2>(grid, smem, c->stream, map, p); break;
         default: ls = launch_fmt_gemm<8>(grid, smem, c->stream, map, p); break;
     }
-    if (ls != TLB_OK) return done(ls);
+    if (ls != TLB_OK) return ls;
     count_launch();
     cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return done(cuda_fail(e, "qgemm launch"));
-    return done(TLB_OK);
+    if (e != cudaSuccess) return cuda_fail(e, "qgemm launch");
+    return TLB_OK;
+}
+
+tlb_status qgemm_run(const tlb_qtensor *w, const GemmAct &a, float *out, const float *resid)
+{
+    return qgemm_run_multi(&w, 1, a, &out, resid);
+}
+
+tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out)
+{
+    GemmAct a;
+    TLB_TRY(qgemm_prepare(&a, x, m, w->k, nullptr, 0.f));
+    tlb_status st = qgemm_run(w, a, out, nullptr);
+    qgemm_release(&a);
+    return st;
 }
 
 }  // namespace tlb
