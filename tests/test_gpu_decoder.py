@@ -198,12 +198,21 @@ def test_prefill_short_prompt_and_errors(orc):
 
 
 def test_prefill_llama3_shaped_one_layer(orc):
-    """Llama-3-8B layer shapes (head_dim 128, GQA 4, Q4_K + Q6_K head): 300-token prompt against the oracle."""
+    """Llama-3-8B layer shapes (head_dim 128, GQA 4, Q4_K + Q6_K head): a 72-token prompt (two attention tiles)
+    against the oracle."""
     cfg = dict(synth.LLAMA3_8B, n_layers=1)
     ref, dec, wmap = build(orc, cfg, 4, synth.Q4_K, synth.Q6_K, True, 384)
     rng = np.random.default_rng(7)
-    prompt = [int(t) for t in rng.integers(0, cfg["vocab"], 300)]
+    prompt = [int(t) for t in rng.integers(0, cfg["vocab"], 72)]
     ref_logits = ref.forward(prompt, 0)
     nxt = dec.prefill(prompt, 0, rope_pos0=0, rope_step=0)
     assert relerr(dec.logits(), ref_logits) < LOGIT_TOL
     assert nxt == orc.argmax_last(ref_logits)
+    # a long prompt on the same weights: chunked at 2048 tokens, against itself token by token at the end
+    long_prompt = [int(t) for t in rng.integers(0, cfg["vocab"], 2100)]
+    dec3 = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=2176)
+    a = dec3.prefill(long_prompt, 0)
+    la = dec3.logits()
+    b = dec3.step(long_prompt[-1], 2099)     # the same last token again over the cache the prompt left
+    assert a == b
+    assert relerr(la, dec3.logits()) < 2e-3

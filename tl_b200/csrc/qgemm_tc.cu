@@ -1,4 +1,4 @@
-// Quantized-weight GEMM for many activation rows (prompt processing, M > 16):
+// Quantized-weight GEMM for many activation rows (prompt processing, M > 16), up to three weights per launch:
 //     Y[M, N] = X[M, K] . W^T,   W = GGUF Q4_K / Q6_K / Q4_0 / Q8_0 bytes in the tiled unit layout.
 // It stands behind the same entry point as the streaming matvec (tl_qtensor_matmul,
 // crates/tl_runtime/src/system.rs:180-382, which dequantises the whole weight to f32, transposes it
@@ -6,9 +6,10 @@
 // rows and never exists in f32.
 //
 // One CTA computes 128 weight rows x NT activation rows (NT <= 256) on the 5th-generation tensor cores:
-//   * the weight tile is the A operand (MMA M = 128): eight producer warps read the quantized units
-//     with coalesced 16-byte loads, dequantise in registers (f32 fma, then round to f16) and store the
-//     128 x 64 f16 tile into shared memory in the K-major 128-byte-swizzled layout tcgen05 reads;
+//   * the weight tile is the A operand (MMA M = 128): sixteen producer warps (two per 16 weight rows, each
+//     taking two of a unit's four 64-wide groups) read the quantized units with coalesced 16-byte loads,
+//     dequantise in registers (f32 fma, then round to f16) and store the 128 x 64 f16 tile into shared
+//     memory in the K-major 128-byte-swizzled layout tcgen05 reads, in a bank-conflict-free order;
 //   * the activation tile is the B operand (MMA N = NT): f16 rows, brought in by TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past M filled with zeros);
 //   * one thread issues tcgen05.mma (kind::f16, f32 accumulate) for each 64-wide K step as soon as both
@@ -39,7 +40,8 @@ constexpr int kGemmStages = 4;
 constexpr int kGemmMaxTok = 256;    // activation rows per CTA (MMA N), multiple of 16
 constexpr int kStageA = kGemmRows * kGemmBK * 2;      // 16 KB
 constexpr int kStageB = kGemmMaxTok * kGemmBK * 2;    // 32 KB
-constexpr int kGemmThreads = 320;   // warps 0-7: dequantise + epilogue, warp 8: TMA, warp 9: MMA + tensor memory
+constexpr int kGemmProducers = 16;  // dequantising warps: warp w and w + 8 share 16 weight rows, two 64-groups of every unit each
+constexpr int kGemmThreads = (kGemmProducers + 2) * 32;   // + the TMA warp and the MMA / tensor-memory warp
 constexpr int kTmemCols = 256;
 
 constexpr int kGemmMaxW = 3;        // weights of one launch (q | k | v share their activations)
@@ -86,6 +88,11 @@ __device__ __forceinline__ void store4(uint32_t addr, uint32_t bytes, float ds, 
     const float f2 = fmaf(byte_f32(bytes, 2), ds, -dm), f3 = fmaf(byte_f32(bytes, 3), ds, -dm);
     sts64(addr, pack_h2(f0, f1), pack_h2(f2, f3));
 }
+// Store order.  Lane (r, c) owns four 4-weight pieces per row and 64-group, at k = 16 t + 4 c, t = 0..3.  If all
+// lanes stored piece t in the same instruction, rows r and r ^ 1 of a half-warp would hit the same banks (the
+// swizzle XORs the 16-byte chunk index 2 t + c / 2 with r).  In step s, even rows store piece s and odd rows piece
+// s ^ 2: the sixteen lanes of every half-warp then cover 128 distinct bytes of the bank space.
+//
 // Byte offset, inside a 128-row x 128-byte stage, of the 8-byte piece that holds k..k+3 of `row`
 // (k a multiple of 4): rows are 128 bytes apart and the 16-byte chunk index is XORed with row % 8.
 __device__ __forceinline__ uint32_t swz(int row, int k)
@@ -119,21 +126,22 @@ __device__ __forceinline__ void q4k_scale_min(const uint4 &h, int j, float &ds, 
 // holds, per 64-group G, the words [row r: bytes 4c..4c+3 | row r: bytes 16+4c.. | row r+8: same two],
 // plus the 16-byte headers (d, dmin, packed scales) of rows r and r + 8.
 struct Q4KRegs {
-    uint4 q[4];
+    uint4 q[2];
     uint4 h[2];
 };
-__device__ __forceinline__ void q4k_load(Q4KRegs &u, const uint8_t *unit, int lane)
+template <int HALF>
+__device__ __forceinline__ void unit_load(Q4KRegs &u, const uint8_t *unit, int lane)
 {
     const int r = lane >> 2;
 #pragma unroll
-    for (int g = 0; g < 4; g++) u.q[g] = __ldg(reinterpret_cast<const uint4 *>(unit + g * 512 + lane * 16));
+    for (int gg = 0; gg < 2; gg++) u.q[gg] = __ldg(reinterpret_cast<const uint4 *>(unit + (HALF * 2 + gg) * 512 + lane * 16));
     u.h[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + r * 16));
     u.h[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + (r + 8) * 16));
 }
 // Dequantise 64-group g of the unit into rows row0 + r and row0 + r + 8 of the stage at `stage`.
-__device__ __forceinline__ void q4k_emit(const Q4KRegs &u, int g, uint32_t stage, int row0, int lane)
+__device__ __forceinline__ void unit_emit(const Q4KRegs &u, int g, uint32_t stage, int row0, int lane)
 {
-    const int r = lane >> 2, c = lane & 3;
+    const int r = lane >> 2, c = lane & 3, odd = r & 1;
 #pragma unroll
     for (int rs = 0; rs < 2; rs++) {
         float ds_lo, dm_lo, ds_hi, dm_hi;
@@ -141,11 +149,11 @@ __device__ __forceinline__ void q4k_emit(const Q4KRegs &u, int g, uint32_t stage
         q4k_scale_min(u.h[rs], 2 * g + 1, ds_hi, dm_hi);
         const int row = row0 + r + 8 * rs;
 #pragma unroll
-        for (int hs = 0; hs < 2; hs++) {
-            const uint32_t wd = word_of(u.q[g], rs * 2 + hs);
-            const int k = hs * 16 + 4 * c;   // position of the word's first byte among the group's 32 bytes
-            store4(stage + swz(row, k), wd & 0x0F0F0F0Fu, ds_lo, dm_lo);              // low nibbles: k
-            store4(stage + swz(row, 32 + k), (wd >> 4) & 0x0F0F0F0Fu, ds_hi, dm_hi);  // high nibbles: 32 + k
+        for (int st = 0; st < 4; st++) {   // store order rotated per row (note above swz): bank-conflict free
+            const int hs = st & 1, nib = (st >> 1) ^ odd;
+            const uint32_t wd = word_of(u.q[g & 1], rs * 2 + hs);   // bytes hs * 16 + 4c .. of the group's 32
+            // low nibbles are k = byte index, high nibbles k = 32 + byte index
+            store4(stage + swz(row, nib * 32 + hs * 16 + 4 * c), (wd >> (4 * nib)) & 0x0F0F0F0Fu, nib ? ds_hi : ds_lo, nib ? dm_hi : dm_lo);
         }
     }
 }
@@ -153,18 +161,18 @@ __device__ __forceinline__ void q4k_emit(const Q4KRegs &u, int g, uint32_t stage
 // ---- Q6_K (crates/tl_runtime/src/quantized.rs:268-329): w = d * sc * (q6 - 32).  Per lane and unit: the four
 // ql pieces (row half hi, block half n), the two qh pieces (hi), sixteen int8 scales and d of rows r, r + 8.
 struct Q6KRegs {
-    uint4 ql[4];
+    uint4 ql[2];
     uint4 qh[2];
     uint4 sc[2];
     float d[2];
 };
-__device__ __forceinline__ void q6k_load(Q6KRegs &u, const uint8_t *unit, int lane)
+template <int HALF>
+__device__ __forceinline__ void unit_load(Q6KRegs &u, const uint8_t *unit, int lane)
 {
     const int r = lane >> 2;
 #pragma unroll
-    for (int i = 0; i < 4; i++) u.ql[i] = __ldg(reinterpret_cast<const uint4 *>(unit + i * 512 + lane * 16));
-#pragma unroll
     for (int hi = 0; hi < 2; hi++) {
+        u.ql[hi] = __ldg(reinterpret_cast<const uint4 *>(unit + (hi * 2 + HALF) * 512 + lane * 16));
         u.qh[hi] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + hi * 512 + lane * 16));
         u.sc[hi] = __ldg(reinterpret_cast<const uint4 *>(unit + 3072 + (r + 8 * hi) * 16));
         u.d[hi] = __half2float(__ldg(reinterpret_cast<const __half *>(unit + 3328 + (r + 8 * hi) * 2)));
@@ -172,40 +180,39 @@ __device__ __forceinline__ void q6k_load(Q6KRegs &u, const uint8_t *unit, int la
 }
 // 64-group g = (n, sub): k = 128 n + 64 sub + [0, 64).  sub 0 takes the low nibbles of ql and bits 0-3 of qh,
 // sub 1 the high nibbles and bits 4-7; inside the group, q1 = 0 / 1 selects ql[l] / ql[l + 32].
-__device__ __forceinline__ void q6k_emit(const Q6KRegs &u, int g, uint32_t stage, int row0, int lane)
+__device__ __forceinline__ void unit_emit(const Q6KRegs &u, int g, uint32_t stage, int row0, int lane)
 {
-    const int r = lane >> 2, c = lane & 3;
+    const int r = lane >> 2, c = lane & 3, odd = r & 1;
     const int n = g >> 1, sub = g & 1;
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
         const int row = row0 + r + 8 * hi;
 #pragma unroll
-        for (int q1 = 0; q1 < 2; q1++) {
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const uint32_t qlw = word_of(u.ql[hi * 2 + n], q1 * 2 + h);
-                const uint32_t qhw = word_of(u.qh[hi], n * 2 + h);
-                const uint32_t nib = (sub ? (qlw >> 4) : qlw) & 0x0F0F0F0Fu;
-                const uint32_t two = (qhw >> (2 * (sub * 2 + q1))) & 0x03030303u;
-                const int si = 8 * n + h + 2 * (sub * 2 + q1);
-                const int sbyte = (int)(int8_t)((word_of(u.sc[hi], si >> 2) >> (8 * (si & 3))) & 0xFFu);
-                const float ds = u.d[hi] * (float)sbyte;
-                store4(stage + swz(row, q1 * 32 + h * 16 + 4 * c), nib | (two << 4), ds, 32.f * ds);
-            }
+        for (int st = 0; st < 4; st++) {
+            const int h = st & 1, q1 = (st >> 1) ^ odd;
+            const uint32_t qlw = q1 ? word_of(u.ql[hi], 2 + h) : word_of(u.ql[hi], h);
+            const uint32_t qhw = word_of(u.qh[hi], n * 2 + h);
+            const uint32_t nib = (sub ? (qlw >> 4) : qlw) & 0x0F0F0F0Fu;
+            const uint32_t two = (qhw >> (2 * (sub * 2 + q1))) & 0x03030303u;
+            const int s0 = 8 * n + h + 4 * sub;   // scale index for q1 = 0; q1 = 1 is two further
+            const uint32_t sb = q1 ? (word_of(u.sc[hi], (s0 + 2) >> 2) >> (8 * ((s0 + 2) & 3))) : (word_of(u.sc[hi], s0 >> 2) >> (8 * (s0 & 3)));
+            const float ds = u.d[hi] * (float)(int)(int8_t)(sb & 0xFFu);
+            store4(stage + swz(row, q1 * 32 + h * 16 + 4 * c), nib | (two << 4), ds, 32.f * ds);
         }
     }
 }
 
 // ---- Q4_0 (quantized.rs:182-225): blocks of 32, w = d * (nibble - 8); low nibble of byte j is k = j, high k = 16 + j
 struct Q40Regs {
-    uint4 q[4];
+    uint4 q[2];
     uint4 d[2];   // eight f16 block scales of rows r and r + 8
 };
-__device__ __forceinline__ void q40_load(Q40Regs &u, const uint8_t *unit, int lane)
+template <int HALF>
+__device__ __forceinline__ void unit_load(Q40Regs &u, const uint8_t *unit, int lane)
 {
     const int r = lane >> 2;
 #pragma unroll
-    for (int i = 0; i < 4; i++) u.q[i] = __ldg(reinterpret_cast<const uint4 *>(unit + i * 512 + lane * 16));
+    for (int gg = 0; gg < 2; gg++) u.q[gg] = __ldg(reinterpret_cast<const uint4 *>(unit + (HALF * 2 + gg) * 512 + lane * 16));
     u.d[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + r * 16));
     u.d[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + (r + 8) * 16));
 }
@@ -214,47 +221,50 @@ __device__ __forceinline__ float f16_of(const uint4 &v, int i)   // i-th f16 of 
     const float2 f = h2_to_f2(word_of(v, i >> 1));
     return (i & 1) ? f.y : f.x;
 }
-__device__ __forceinline__ void q40_emit(const Q40Regs &u, int g, uint32_t stage, int row0, int lane)
+__device__ __forceinline__ void unit_emit(const Q40Regs &u, int g, uint32_t stage, int row0, int lane)
 {
-    const int r = lane >> 2, c = lane & 3;
+    const int r = lane >> 2, c = lane & 3, odd = r & 1;
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
         const int row = row0 + r + 8 * hi;
+        const float d0 = f16_of(u.d[hi], 2 * g), d1 = f16_of(u.d[hi], 2 * g + 1);   // blocks 2g and 2g + 1 of the row's eight
 #pragma unroll
-        for (int b = 0; b < 2; b++) {   // blocks 2g and 2g + 1 of the row's eight
-            const float d = f16_of(u.d[hi], 2 * g + b);
-            const uint32_t wd = word_of(u.q[g], hi * 2 + b);
-            store4(stage + swz(row, b * 32 + 4 * c), wd & 0x0F0F0F0Fu, d, 8.f * d);
-            store4(stage + swz(row, b * 32 + 16 + 4 * c), (wd >> 4) & 0x0F0F0F0Fu, d, 8.f * d);
+        for (int st = 0; st < 4; st++) {
+            const int nib = st & 1, b = (st >> 1) ^ odd;
+            const float d = b ? d1 : d0;
+            const uint32_t wd = b ? word_of(u.q[g & 1], hi * 2 + 1) : word_of(u.q[g & 1], hi * 2);
+            store4(stage + swz(row, b * 32 + nib * 16 + 4 * c), (nib ? (wd >> 4) : wd) & 0x0F0F0F0Fu, d, 8.f * d);
         }
     }
 }
 
 // ---- Q8_0 (quantized.rs:227-260): blocks of 32 int8, w = d * q
 struct Q80Regs {
-    uint4 q[8];
+    uint4 q[4];
     uint4 d[2];
 };
-__device__ __forceinline__ void q80_load(Q80Regs &u, const uint8_t *unit, int lane)
+template <int HALF>
+__device__ __forceinline__ void unit_load(Q80Regs &u, const uint8_t *unit, int lane)
 {
     const int r = lane >> 2;
 #pragma unroll
-    for (int i = 0; i < 8; i++) u.q[i] = __ldg(reinterpret_cast<const uint4 *>(unit + i * 512 + lane * 16));
+    for (int i = 0; i < 4; i++) u.q[i] = __ldg(reinterpret_cast<const uint4 *>(unit + (HALF * 4 + i) * 512 + lane * 16));
     u.d[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 4096 + r * 16));
     u.d[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 4096 + (r + 8) * 16));
 }
-__device__ __forceinline__ void q80_emit(const Q80Regs &u, int g, uint32_t stage, int row0, int lane)
+__device__ __forceinline__ void unit_emit(const Q80Regs &u, int g, uint32_t stage, int row0, int lane)
 {
-    const int r = lane >> 2, c = lane & 3;
+    const int r = lane >> 2, c = lane & 3, odd = r & 1;
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
         const int row = row0 + r + 8 * hi;
+        const float d0 = f16_of(u.d[hi], 2 * g), d1 = f16_of(u.d[hi], 2 * g + 1);
 #pragma unroll
-        for (int b = 0; b < 2; b++) {
-            const float d = f16_of(u.d[hi], 2 * g + b);
-#pragma unroll
-            for (int h = 0; h < 2; h++)   // q + 128 as an unsigned byte, then w = d * u - 128 d
-                store4(stage + swz(row, b * 32 + 16 * h + 4 * c), word_of(u.q[2 * g + b], hi * 2 + h) ^ 0x80808080u, d, 128.f * d);
+        for (int st = 0; st < 4; st++) {   // q + 128 as an unsigned byte, then w = d * u - 128 d
+            const int h = st & 1, b = (st >> 1) ^ odd;
+            const float d = b ? d1 : d0;
+            const uint32_t wd = b ? word_of(u.q[2 * (g & 1) + 1], hi * 2 + h) : word_of(u.q[2 * (g & 1)], hi * 2 + h);
+            store4(stage + swz(row, b * 32 + 16 * h + 4 * c), wd ^ 0x80808080u, d, 128.f * d);
         }
     }
 }
@@ -264,14 +274,6 @@ template <> struct UnitRegs<12> { using type = Q4KRegs; };
 template <> struct UnitRegs<14> { using type = Q6KRegs; };
 template <> struct UnitRegs<2> { using type = Q40Regs; };
 template <> struct UnitRegs<8> { using type = Q80Regs; };
-__device__ __forceinline__ void unit_load(Q4KRegs &u, const uint8_t *p, int lane) { q4k_load(u, p, lane); }
-__device__ __forceinline__ void unit_load(Q6KRegs &u, const uint8_t *p, int lane) { q6k_load(u, p, lane); }
-__device__ __forceinline__ void unit_load(Q40Regs &u, const uint8_t *p, int lane) { q40_load(u, p, lane); }
-__device__ __forceinline__ void unit_load(Q80Regs &u, const uint8_t *p, int lane) { q80_load(u, p, lane); }
-__device__ __forceinline__ void unit_emit(const Q4KRegs &u, int g, uint32_t st, int row0, int lane) { q4k_emit(u, g, st, row0, lane); }
-__device__ __forceinline__ void unit_emit(const Q6KRegs &u, int g, uint32_t st, int row0, int lane) { q6k_emit(u, g, st, row0, lane); }
-__device__ __forceinline__ void unit_emit(const Q40Regs &u, int g, uint32_t st, int row0, int lane) { q40_emit(u, g, st, row0, lane); }
-__device__ __forceinline__ void unit_emit(const Q80Regs &u, int g, uint32_t st, int row0, int lane) { q80_emit(u, g, st, row0, lane); }
 
 // ---- tcgen05 wrappers
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
@@ -305,6 +307,33 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// ---- one dequantising warp: 64-groups 2 HALF and 2 HALF + 1 of every unit of its 16 rows
+template <int FMT, int HALF>
+__device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, bool have, int row0, int lane, uint32_t sA,
+                                        uint32_t full0, uint32_t empty0, volatile int *abort_flag)
+{
+    const int units = (int)p.upt;
+    typename UnitRegs<FMT>::type cur, nxt;
+    if (have) unit_load<HALF>(nxt, ub, lane);
+    for (int u = 0; u < units; u++) {
+        if (have) {
+            cur = nxt;
+            if (u + 1 < units) unit_load<HALF>(nxt, ub + (size_t)(u + 1) * p.unit_bytes, lane);
+        }
+#pragma unroll
+        for (int gg = 0; gg < 2; gg++) {
+            const int g = HALF * 2 + gg;
+            const int kt = u * 4 + g, s = kt % kGemmStages, round = kt / kGemmStages;
+            if (round > 0 && !mbar_wait(empty0 + 8u * s, (round - 1) & 1, abort_flag, p.err, 21)) return false;
+            if (have) unit_emit(cur, g, sA + s * kStageA, row0, lane);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> visible to the MMA's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8u * s);
+        }
+    }
+    return true;
 }
 
 // ---- the kernel
@@ -342,7 +371,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 9) {
+    if (warp == kGemmProducers + 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -351,37 +380,22 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
 
-    if (warp < 8) {
+    if (warp < kGemmProducers) {
         // ------------------------------------------------ dequantise the weight tile, stage by stage
-        const int tile16 = rt * 8 + warp;
+        const int sub = warp & 7;
+        const int tile16 = rt * 8 + sub;
         const bool have = tile16 < p.n_tiles16[wi];
         const uint8_t *ub = p.w[wi] + (size_t)(have ? tile16 : 0) * p.upt * p.unit_bytes;
-        const int units = (int)p.upt;
-        typename UnitRegs<FMT>::type cur, nxt;
-        if (have) unit_load(nxt, ub, lane);
-        bool ok = true;
-        for (int u = 0; u < units && ok; u++) {
-            if (have) {
-                cur = nxt;
-                if (u + 1 < units) unit_load(nxt, ub + (size_t)(u + 1) * p.unit_bytes, lane);
-            }
-#pragma unroll
-            for (int g = 0; g < 4; g++) {
-                const int kt = u * 4 + g, s = kt % kGemmStages, round = kt / kGemmStages;
-                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, p.err, 21)) { ok = false; break; }
-                if (have) unit_emit(cur, g, sA + s * kStageA, warp * 16, lane);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> visible to the MMA's reads
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full_bar(s));
-            }
-        }
+        const bool ok = warp < 8 ? produce<FMT, 0>(p, ub, have, sub * 16, lane, sA, full_bar(0), empty_bar(0), abort_flag)
+                                 : produce<FMT, 1>(p, ub, have, sub * 16, lane, sA, full_bar(0), empty_bar(0), abort_flag);
         // ------------------------------------------------ epilogue: tensor memory -> Y[token][row]
         if (ok && mbar_wait(accum_bar, 0, abort_flag, p.err, 22)) {
             tc_fence_after();
-            const int quad = warp & 3, halfsel = warp >> 2;
+            const int quad = warp & 3, part = warp >> 2;    // tensor-memory lanes 32 quad .., a quarter of the columns
             const int row = rt * kGemmRows + quad * 32 + lane;
             float *out = p.out[wi];
-            const int c_begin = halfsel * (p.nt >> 1), c_end = c_begin + (p.nt >> 1);
+            const int chunks = p.nt >> 3;
+            const int c_begin = 8 * (part * chunks / 4), c_end = 8 * ((part + 1) * chunks / 4);
             for (int c0 = c_begin; c0 < c_end; c0 += 8) {
                 // the residual and the row scales first (independent loads in flight together), then the accumulator
                 float rs[8], sc[8];
@@ -404,7 +418,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
                 }
             }
         }
-    } else if (warp == 8) {
+    } else if (warp == kGemmProducers) {
         // ------------------------------------------------ TMA: activation tile of each stage
         if (lane == 0) {
             int issued = 0;
@@ -445,7 +459,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kGemmProducers + 1) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
