@@ -173,8 +173,11 @@ def test_qgemm_matches_oracle(orc, t, n, k, m):
     for i in range(m):
         if i != 1:
             assert relerr(got[i], ref[i]) < GEMM_TOL, i
-    emu = _f16_emulation(x, q.dequantize().numpy())
-    assert relerr(got, emu) < GEMM_EMU_TOL
+    if t in (synth.Q4_0, synth.Q8_0):
+        # these weights are one f16 rounding of the f32 value, so numpy can redo the arithmetic
+        # (the K formats round d * sc and dmin * m to f16 before the last multiply-add)
+        emu = _f16_emulation(x, q.dequantize().numpy())
+        assert relerr(got, emu) < GEMM_EMU_TOL
 
 
 def test_qgemm_full_size_agrees_with_matvec():

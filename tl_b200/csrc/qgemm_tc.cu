@@ -8,7 +8,7 @@
 // One CTA computes 128 weight rows x NT activation rows (NT <= 256) on the 5th-generation tensor cores:
 //   * the weight tile is the A operand (MMA M = 128): sixteen producer warps (two per 16 weight rows, each
 //     taking two of a unit's four 64-wide groups) read the quantized units with coalesced 16-byte loads,
-//     dequantise in registers (f32 fma, then round to f16) and store the 128 x 64 f16 tile into shared
+//     dequantise in registers (f16 pair arithmetic on exact integers, see store4) and store the 128 x 64 f16 tile into shared
 //     memory in the K-major 128-byte-swizzled layout tcgen05 reads, in a bank-conflict-free order;
 //   * the activation tile is the B operand (MMA N = NT): f16 rows, brought in by TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past M filled with zeros);
@@ -67,27 +67,48 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b)
 {
     asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
-__device__ __forceinline__ uint32_t pack_h2(float a, float b)
+__device__ __forceinline__ uint32_t hfma2u(uint32_t a, uint32_t b, uint32_t c)
 {
-    __half2 h = __floats2half2_rn(a, b);
+    uint32_t d;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b)
+{
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t h2_of(float a)   // (a, a) rounded to f16
+{
+    __half2 h = __float2half2_rn(a);
     return *reinterpret_cast<uint32_t *>(&h);
 }
-// Byte t of `bytes` (each 0..255) as an exact f32: the byte becomes the low mantissa bits of 2^23.
-__device__ __forceinline__ float byte_f32(uint32_t bytes, int t)
+// Byte i of `w` in both halves of an f16 pair, as the exact integer it is (0..255): 0x6400 | byte is 1024 + byte.
+__device__ __forceinline__ uint32_t byte_h2(uint32_t w, int i)
 {
-    return __uint_as_float(prmt(bytes, 0x4B000000u, 0x7540u | (uint32_t)t)) - 8388608.0f;
+    return hsub2(prmt(w, 0x64646464u, 0x4040u | (uint32_t)i | ((uint32_t)i << 8)), 0x64006400u);
 }
-// Four weights w = q * ds - dm from the four bytes of `bytes`, rounded to f16 and stored as 8 bytes.
-__device__ __forceinline__ void store4(uint32_t addr, uint32_t bytes, float ds, float dm)
+// Four weights from the four bytes b0..b3 of `bytes` (each 0..255), in f16 pair arithmetic:
+//     w = (b * p1 + p2) * p3 + p4        (p1..p4: the same f16 value in both halves)
+// The bytes enter as 1024 + b (0x6400 | b), which is exact, and both fused multiply-adds round once.
+// The 8 bytes stored hold the weights in the order (b0, b2, b1, b3): inside every group of four the
+// middle two K positions are exchanged, and the activation rows are written in the same order
+// (x_to_f16_kernel), which leaves every dot product unchanged.
+__device__ __forceinline__ void store4(uint32_t addr, uint32_t bytes, uint32_t p1, uint32_t p2, uint32_t p3, uint32_t p4)
 {
 #ifdef QG_NODEQ
-    sts64(addr, bytes, __float_as_uint(ds) ^ __float_as_uint(dm));
+    sts64(addr, bytes, p1 ^ p3);
     return;
 #endif
-    const float f0 = fmaf(byte_f32(bytes, 0), ds, -dm), f1 = fmaf(byte_f32(bytes, 1), ds, -dm);
-    const float f2 = fmaf(byte_f32(bytes, 2), ds, -dm), f3 = fmaf(byte_f32(bytes, 3), ds, -dm);
-    sts64(addr, pack_h2(f0, f1), pack_h2(f2, f3));
+    const uint32_t x02 = prmt(bytes, 0x64646464u, 0x4240u), x13 = prmt(bytes, 0x64646464u, 0x4341u);   // (1024 + b0, 1024 + b2), (1024 + b1, 1024 + b3)
+    sts64(addr, hfma2u(hfma2u(x02, p1, p2), p3, p4), hfma2u(hfma2u(x13, p1, p2), p3, p4));
 }
+constexpr uint32_t kH2One = 0x3C003C00u;    // (1, 1)
+constexpr uint32_t kH2Zero = 0u;
+// (-(1024 + off), ...) for off in {8, 32, 128}: 1024 + b - (1024 + off) = b - off, exactly
+constexpr uint32_t kH2Neg1032 = 0xE408E408u, kH2Neg1056 = 0xE420E420u, kH2Neg1152 = 0xE480E480u;
+
 // Store order.  Lane (r, c) owns four 4-weight pieces per row and 64-group, at k = 16 t + 4 c, t = 0..3.  If all
 // lanes stored piece t in the same instruction, rows r and r ^ 1 of a half-warp would hit the same banks (the
 // swizzle XORs the 16-byte chunk index 2 t + c / 2 with r).  In step s, even rows store piece s and odd rows piece
@@ -100,26 +121,28 @@ __device__ __forceinline__ uint32_t swz(int row, int k)
     return (uint32_t)(row * 128 + ((((k >> 3) ^ (row & 7)) << 4) | ((k & 4) << 1)));
 }
 
-// ---- Q4_K: byte i of the 12 packed scale bytes; (scale, min) of sub-block j as get_scale_min_k4 does
-// (crates/tl_runtime/src/quantized.rs:337-356)
-__device__ __forceinline__ uint32_t q4k_sbyte(const uint4 &h, int i)
+// ---- Q4_K: w = d * sc * q - dmin * m (crates/tl_runtime/src/quantized.rs:337-415).  The 6-bit (scale, min)
+// pairs of four sub-blocks at a time, one per byte, unpacked from the 12 packed bytes as get_scale_min_k4 does:
+// sub-blocks 0..3 (upper = false) or 4..7 (upper = true).  h = [d | dmin, q[0..3], q[4..7], q[8..11]].
+__device__ __forceinline__ void q4k_scales4(const uint4 &h, bool upper, uint32_t &scw, uint32_t &mw)
 {
-    const uint32_t wd = i < 4 ? h.y : (i < 8 ? h.z : h.w);
-    return (wd >> (8 * (i & 3))) & 0xFFu;
-}
-__device__ __forceinline__ void q4k_scale_min(const uint4 &h, int j, float &ds, float &dm)
-{
-    const float2 dd = h2_to_f2(h.x);   // (d, dmin)
-    uint32_t sc, mn;
-    if (j < 4) {
-        sc = q4k_sbyte(h, j) & 63u;
-        mn = q4k_sbyte(h, j + 4) & 63u;
+    if (!upper) {
+        scw = h.y & 0x3F3F3F3Fu;
+        mw = h.z & 0x3F3F3F3Fu;
     } else {
-        sc = (q4k_sbyte(h, j + 4) & 0xFu) | ((q4k_sbyte(h, j - 4) >> 6) << 4);
-        mn = (q4k_sbyte(h, j + 4) >> 4) | ((q4k_sbyte(h, j) >> 6) << 4);
+        scw = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+        mw = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
     }
-    ds = dd.x * (float)sc;
-    dm = dd.y * (float)mn;
+}
+// store4 parameters of one sub-block: (1024 + q) * sc - 1024 sc = q sc exactly, then * d - dmin m
+struct Q4KSub { uint32_t sc, c, ndm; };
+__device__ __forceinline__ Q4KSub q4k_sub(uint32_t scw, uint32_t mw, int byte, uint32_t dmin2)
+{
+    Q4KSub o;
+    o.sc = byte_h2(scw, byte);
+    o.c = hmul2u(o.sc, 0xE400E400u);                             // -1024 sc, exact
+    o.ndm = hmul2u(byte_h2(mw, byte), dmin2) ^ 0x80008000u;      // -(dmin m), rounded once
+    return o;
 }
 
 // One warp's registers for one Q4_K unit (16 rows x 256 weights): lane (r, c) = (lane / 4, lane % 4)
@@ -141,19 +164,26 @@ __device__ __forceinline__ void unit_load(Q4KRegs &u, const uint8_t *unit, int l
 // Dequantise 64-group g of the unit into rows row0 + r and row0 + r + 8 of the stage at `stage`.
 __device__ __forceinline__ void unit_emit(const Q4KRegs &u, int g, uint32_t stage, int row0, int lane)
 {
-    const int r = lane >> 2, c = lane & 3, odd = r & 1;
+    const int r = lane >> 2, c = lane & 3;
+    const bool odd = r & 1;
 #pragma unroll
     for (int rs = 0; rs < 2; rs++) {
-        float ds_lo, dm_lo, ds_hi, dm_hi;
-        q4k_scale_min(u.h[rs], 2 * g, ds_lo, dm_lo);
-        q4k_scale_min(u.h[rs], 2 * g + 1, ds_hi, dm_hi);
+        uint32_t scw, mw;
+        q4k_scales4(u.h[rs], g >= 2, scw, mw);
+        const uint32_t d2 = prmt(u.h[rs].x, 0u, 0x1010u), dmin2 = prmt(u.h[rs].x, 0u, 0x3232u);
+        const Q4KSub lo = q4k_sub(scw, mw, (2 * g) & 3, dmin2), hi = q4k_sub(scw, mw, (2 * g + 1) & 3, dmin2);
+        // steps 0, 1 take the low nibbles on even rows and the high nibbles on odd rows; steps 2, 3 the others
+        const Q4KSub a = {odd ? hi.sc : lo.sc, odd ? hi.c : lo.c, odd ? hi.ndm : lo.ndm};
+        const Q4KSub b = {odd ? lo.sc : hi.sc, odd ? lo.c : hi.c, odd ? lo.ndm : hi.ndm};
         const int row = row0 + r + 8 * rs;
 #pragma unroll
         for (int st = 0; st < 4; st++) {   // store order rotated per row (note above swz): bank-conflict free
-            const int hs = st & 1, nib = (st >> 1) ^ odd;
+            const int hs = st & 1;
+            const int nib = (st >> 1) ^ (int)odd;
+            const Q4KSub &q = (st >> 1) ? b : a;
             const uint32_t wd = word_of(u.q[g & 1], rs * 2 + hs);   // bytes hs * 16 + 4c .. of the group's 32
             // low nibbles are k = byte index, high nibbles k = 32 + byte index
-            store4(stage + swz(row, nib * 32 + hs * 16 + 4 * c), (wd >> (4 * nib)) & 0x0F0F0F0Fu, nib ? ds_hi : ds_lo, nib ? dm_hi : dm_lo);
+            store4(stage + swz(row, nib * 32 + hs * 16 + 4 * c), (wd >> (4 * nib)) & 0x0F0F0F0Fu, q.sc, q.c, d2, q.ndm);
         }
     }
 }
@@ -196,8 +226,8 @@ __device__ __forceinline__ void unit_emit(const Q6KRegs &u, int g, uint32_t stag
             const uint32_t two = (qhw >> (2 * (sub * 2 + q1))) & 0x03030303u;
             const int s0 = 8 * n + h + 4 * sub;   // scale index for q1 = 0; q1 = 1 is two further
             const uint32_t sb = q1 ? (word_of(u.sc[hi], (s0 + 2) >> 2) >> (8 * ((s0 + 2) & 3))) : (word_of(u.sc[hi], s0 >> 2) >> (8 * (s0 & 3)));
-            const float ds = u.d[hi] * (float)(int)(int8_t)(sb & 0xFFu);
-            store4(stage + swz(row, q1 * 32 + h * 16 + 4 * c), nib | (two << 4), ds, 32.f * ds);
+            const uint32_t ds2 = h2_of(u.d[hi] * (float)(int)(int8_t)(sb & 0xFFu));   // d * sc, rounded to f16 once
+            store4(stage + swz(row, q1 * 32 + h * 16 + 4 * c), nib | (two << 4), kH2One, kH2Neg1056, ds2, kH2Zero);   // (q - 32) * ds
         }
     }
 }
@@ -216,10 +246,9 @@ __device__ __forceinline__ void unit_load(Q40Regs &u, const uint8_t *unit, int l
     u.d[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + r * 16));
     u.d[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + (r + 8) * 16));
 }
-__device__ __forceinline__ float f16_of(const uint4 &v, int i)   // i-th f16 of the 16 bytes
+__device__ __forceinline__ uint32_t h2_pair(const uint4 &v, int i)   // i-th f16 of the 16 bytes, in both halves
 {
-    const float2 f = h2_to_f2(word_of(v, i >> 1));
-    return (i & 1) ? f.y : f.x;
+    return prmt(word_of(v, i >> 1), 0u, (i & 1) ? 0x3232u : 0x1010u);
 }
 __device__ __forceinline__ void unit_emit(const Q40Regs &u, int g, uint32_t stage, int row0, int lane)
 {
@@ -227,13 +256,13 @@ __device__ __forceinline__ void unit_emit(const Q40Regs &u, int g, uint32_t stag
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
         const int row = row0 + r + 8 * hi;
-        const float d0 = f16_of(u.d[hi], 2 * g), d1 = f16_of(u.d[hi], 2 * g + 1);   // blocks 2g and 2g + 1 of the row's eight
+        const uint32_t d0 = h2_pair(u.d[hi], 2 * g), d1 = h2_pair(u.d[hi], 2 * g + 1);   // blocks 2g and 2g + 1 of the row's eight
 #pragma unroll
         for (int st = 0; st < 4; st++) {
             const int nib = st & 1, b = (st >> 1) ^ odd;
-            const float d = b ? d1 : d0;
+            const uint32_t d = b ? d1 : d0;
             const uint32_t wd = b ? word_of(u.q[g & 1], hi * 2 + 1) : word_of(u.q[g & 1], hi * 2);
-            store4(stage + swz(row, b * 32 + nib * 16 + 4 * c), (nib ? (wd >> 4) : wd) & 0x0F0F0F0Fu, d, 8.f * d);
+            store4(stage + swz(row, b * 32 + nib * 16 + 4 * c), (nib ? (wd >> 4) : wd) & 0x0F0F0F0Fu, kH2One, kH2Neg1032, d, kH2Zero);   // (q - 8) * d
         }
     }
 }
@@ -258,13 +287,13 @@ __device__ __forceinline__ void unit_emit(const Q80Regs &u, int g, uint32_t stag
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
         const int row = row0 + r + 8 * hi;
-        const float d0 = f16_of(u.d[hi], 2 * g), d1 = f16_of(u.d[hi], 2 * g + 1);
+        const uint32_t d0 = h2_pair(u.d[hi], 2 * g), d1 = h2_pair(u.d[hi], 2 * g + 1);
 #pragma unroll
-        for (int st = 0; st < 4; st++) {   // q + 128 as an unsigned byte, then w = d * u - 128 d
+        for (int st = 0; st < 4; st++) {   // q + 128 as an unsigned byte u, then w = (u - 128) * d
             const int h = st & 1, b = (st >> 1) ^ odd;
-            const float d = b ? d1 : d0;
+            const uint32_t d = b ? d1 : d0;
             const uint32_t wd = b ? word_of(u.q[2 * (g & 1) + 1], hi * 2 + h) : word_of(u.q[2 * (g & 1)], hi * 2 + h);
-            store4(stage + swz(row, b * 32 + 16 * h + 4 * c), wd ^ 0x80808080u, d, 128.f * d);
+            store4(stage + swz(row, b * 32 + 16 * h + 4 * c), wd ^ 0x80808080u, kH2One, kH2Neg1152, d, kH2Zero);
         }
     }
 }
@@ -509,7 +538,8 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__
             const float4 w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
             v.x = v.x * inv_rms * w.x; v.y = v.y * inv_rms * w.y; v.z = v.z * inv_rms * w.z; v.w = v.w * inv_rms * w.w;
         }
-        __half2 a = __floats2half2_rn(v.x * scale, v.y * scale), b = __floats2half2_rn(v.z * scale, v.w * scale);
+        // inside every group of four the middle two are exchanged, as store4 lays the weights out
+        __half2 a = __floats2half2_rn(v.x * scale, v.z * scale), b = __floats2half2_rn(v.y * scale, v.w * scale);
         uint2 o2;
         o2.x = *reinterpret_cast<uint32_t *>(&a);
         o2.y = *reinterpret_cast<uint32_t *>(&b);
