@@ -225,6 +225,33 @@ def fill_context(dec, cfg, ctx, seed=99):
         dec.kv_write(layer, 0, k, v)
 
 
+def measure_prefill(tl, dec, cfg, tokens, ev, peaks):
+    """Secondary figure: one prompt of `tokens` random ids through tlb_decoder_prefill (tensor-core GEMMs),
+    timed with CUDA events after one warm-up run; arithmetic = linear layers + causal attention."""
+    import ctypes as C
+    if tokens <= 0:
+        return None
+    L = tl.lib()
+    rng = np.random.default_rng(4321)
+    prompt = [int(t) for t in rng.integers(0, cfg["vocab"], tokens)]
+    dec.prefill(prompt, 0, read=False)
+    tl.sync()
+    tl.check(L.tlb_event_record(ev[0]))
+    dec.prefill(prompt, 0, read=False)
+    tl.check(L.tlb_event_record(ev[1]))
+    tl.sync()
+    ms = C.c_float()
+    tl.check(L.tlb_event_elapsed_ms(ev[0], ev[1], C.byref(ms)))
+    dm, qd, kvd, F = cfg["d_model"], cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"], cfg["ffn"]
+    lin = 2.0 * tokens * cfg["n_layers"] * (dm * (qd + 2 * kvd) + qd * dm + 3 * dm * F)
+    att = 4.0 * cfg["n_layers"] * cfg["n_heads"] * cfg["head_dim"] * tokens * (tokens + 1) / 2
+    tf = (lin + att) / (ms.value * 1e-3) / 1e12
+    peak = peaks.get("bf16_tflops", 1590.0)
+    return {"tokens": tokens, "ms": round(float(ms.value), 2), "tokens_per_s": round(tokens / (ms.value * 1e-3), 0),
+            "tflops": round(tf, 1), "bound": "tensor", "peak_tflops": peak, "frac": round(tf / peak, 4),
+            "note": "f16 tcgen05 GEMMs with on-the-fly dequantisation + mma.sync attention; all layers, head on the last token"}
+
+
 def run_ours(args, dist, rank, world):
     import ctypes as C
     t_start = time.time()
@@ -298,6 +325,7 @@ def run_ours(args, dist, rank, world):
                 "per_launch": kern,
                 "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
                 "whole_step_GBs": round((st["weight_bytes"] + st["kv_bytes"]) * (tok_s / world) / 1e9, 1)}
+    prefill = measure_prefill(tl, dec, cfg, min(ctx, 2048) if ctx >= 32 else 0, ev, peaks)
     cpu, _ = cpu_baseline(cfg, args.cpu_budget)
     line = {"metric": "Q4_K Llama-3-8B decode tok/s @bs1" if args.workload == "c2" else "decode tok/s @bs1",
             "value": round(tok_s, 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -311,6 +339,8 @@ def run_ours(args, dist, rank, world):
             "e2e": {"value": round(whole_job_rate(world, K, e2e_ms), 2), "unit": "tokens/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
             "roofline": roofline, "cpu_baseline": cpu}
+    if prefill:
+        line["prefill"] = prefill
     return line
 
 
