@@ -97,10 +97,6 @@ __device__ __forceinline__ uint32_t byte_h2(uint32_t w, int i)
 // (x_to_f16_kernel), which leaves every dot product unchanged.
 __device__ __forceinline__ void store4(uint32_t addr, uint32_t bytes, uint32_t p1, uint32_t p2, uint32_t p3, uint32_t p4)
 {
-#ifdef QG_NODEQ
-    sts64(addr, bytes, p1 ^ p3);
-    return;
-#endif
     const uint32_t x02 = prmt(bytes, 0x64646464u, 0x4240u), x13 = prmt(bytes, 0x64646464u, 0x4341u);   // (1024 + b0, 1024 + b2), (1024 + b1, 1024 + b3)
     sts64(addr, hfma2u(hfma2u(x02, p1, p2), p3, p4), hfma2u(hfma2u(x13, p1, p2), p3, p4));
 }
@@ -440,9 +436,6 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int tok = tok0 + c0 + j;
-#ifdef QG_NOEPI
-                    if (v[j] == 0x12345678u)
-#endif
                     if (tok < p.m && row < n_rows) out[(size_t)tok * n_rows + row] = rs[j] + __uint_as_float(v[j]) * sc[j];
                 }
             }
@@ -454,9 +447,6 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
             for (int kt = 0; kt < KT; kt++) {
                 const int s = kt % kGemmStages, round = kt / kGemmStages;
                 if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, p.err, 23)) break;
-#ifdef QG_NOTMA
-                if (kt >= kGemmStages) { mbar_arrive(full_bar(s)); issued = kt + 1; continue; }
-#endif
                 mbar_expect_tx(full_bar(s), (uint32_t)p.nt * 128u);
                 tma_load_2d(sB + s * kStageB, &xmap, kt * kGemmBK, tok0, full_bar(s));
                 issued = kt + 1;

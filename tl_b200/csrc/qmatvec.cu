@@ -627,6 +627,21 @@ tlb_status launch_qmatvec(const MatvecJob &job)
 
 using namespace tlb;
 
+// More than 4 activation rows: the matvec re-streams the weight once per group of 4 rows, the tensor-core GEMM
+// reads it once but pays a fixed ~0.4 us per 64-wide K step and wave of 148 CTAs.  Above kGemmMinRows rows the
+// GEMM always wins; from 5 rows on the cheaper of the two estimates (fitted to timings on the Llama-3-8B shapes:
+// 4096 x 4096 switches at 9 rows, 14336 x 4096 at 5, 4096 x 14336 at 16).
+static bool prefer_gemm(int64_t m, const tlb_qtensor *w)
+{
+    if (m <= 4 || !qgemm_supported(w->type) || w->k % 256) return false;
+    if (m > kGemmMinRows) return true;
+    const double waves = (double)(((w->n + 127) / 128 + 147) / 148);
+    const double gemm_us = 12.0 + 0.4 * (double)(w->k / 64) * waves;
+    const double per_mb = w->n >= w->k ? 1.0 : 0.5;   // wide-K weights stream faster with 4 rows: fewer results per byte
+    const double matvec_us = (double)((m + 3) / 4) * (6.0 + (double)w->nbytes() * 1e-6 * per_mb);
+    return gemm_us < matvec_us;
+}
+
 extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, const tlb_qtensor *w)
 {
     if (!out) return fail(TLB_ERR_NULL, "null out");
@@ -643,7 +658,7 @@ extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, 
     TLB_TRY(new_tensor(out, TLB_F32, oshape, x->rank));
     if (m * w->n == 0) return TLB_OK;
     tlb_status st = TLB_OK;
-    if (m > kGemmMinRows && qgemm_supported(w->type) && ((uintptr_t)x->f32() & 15) == 0) {
+    if (prefer_gemm(m, w) && ((uintptr_t)x->f32() & 15) == 0) {
         // many rows (prompt processing): tensor-core GEMM, the weight is read once per 256 rows
         st = launch_qgemm(w, x->f32(), m, (*out)->f32());
         if (st != TLB_OK) { tlb_tensor_release(*out); *out = nullptr; }

@@ -111,7 +111,10 @@ namespace tlb {
 // ---- kernel launchers (all on ctx()->stream) ------------------------------------------
 // quant.cu
 // qgemm_tc.cu: Y[m, n] = X[m, k] . W^T on the tensor cores (tcgen05), for m above kGemmMinRows
-constexpr int kGemmMinRows = 16;
+#ifndef TLB_GEMM_MIN_ROWS
+#define TLB_GEMM_MIN_ROWS 16
+#endif
+constexpr int kGemmMinRows = TLB_GEMM_MIN_ROWS;
 bool qgemm_supported(int ggml_type);
 tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out);
 // the same in steps, so that several weights can share one conversion of the activations:
