@@ -205,3 +205,19 @@ def test_qgemm_rank3_input_and_shape_error():
     with pytest.raises(tl.TlbError) as e:
         tl.Tensor.from_numpy(np.zeros((40, 512), dtype=np.float32)).matmul_quantized(q)
     assert e.value.code == 1
+
+
+def test_mid_row_counts_on_a_wide_weight(orc):
+    """5 to 16 rows on 14336 x 4096 (gate / up shape) run through the GEMM: sampled output rows against the oracle."""
+    n, k = 14336, 4096
+    rng = np.random.default_rng(79)
+    w = synth.random_quant(synth.Q4_K, n, k, rng)
+    q = tl.QTensor.from_gguf_bytes(synth.Q4_K, n, k, w)
+    rows = np.unique(np.concatenate([np.arange(0, n, 257), [n - 1]]))
+    for m in (5, 8, 16):
+        x = rng.standard_normal((m, k), dtype=np.float32)
+        got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+        ref = orc.qmatmul(synth.Q4_K, w[rows].reshape(-1), len(rows), k, x)
+        assert got.shape == (m, n)
+        for i in range(m):
+            assert relerr(got[i][rows], ref[i]) < GEMM_TOL, (m, i)

@@ -731,7 +731,7 @@ tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0,
         void *kc = (char *)d->kcache + (size_t)l * d->kv_layer_elems * esz, *vc = (char *)d->vcache + (size_t)l * d->kv_layer_elems * esz;
         GemmAct a;
         tlb_status st;
-        TLB_TRY(qgemm_prepare(&a, x, T, dm, w.attn_norm->f32(), c.eps));
+        TLB_TRY(qgemm_prepare(&a, x, nullptr, T, dm, w.attn_norm->f32(), c.eps));
         {
             const tlb_qtensor *ws3[3] = {w.q, w.k, w.v};
             float *outs3[3] = {q, k, v};
@@ -741,11 +741,11 @@ tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0,
         TLB_TRY(st);
         TLB_TRY(launch_rope_append(q, k, v, kc, vc, c.kv_f16, d->cos_t, d->sin_t, T, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, pos0, rope0, rope_step));
         TLB_TRY(launch_prefill_attention(q, kc, vc, c.kv_f16, att, T, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, pos0, c.attn_scale));
-        TLB_TRY(qgemm_prepare(&a, att, T, qd, nullptr, 0.f));
+        TLB_TRY(qgemm_prepare(&a, att, nullptr, T, qd, nullptr, 0.f));
         st = qgemm_run(w.o, a, x2, x);                 // x2 = x + o_proj(attention)
         qgemm_release(&a);
         TLB_TRY(st);
-        TLB_TRY(qgemm_prepare(&a, x2, T, dm, w.ffn_norm->f32(), c.eps));
+        TLB_TRY(qgemm_prepare(&a, x2, nullptr, T, dm, w.ffn_norm->f32(), c.eps));
         {
             const tlb_qtensor *ws2[2] = {w.gate, w.up};
             float *outs2[2] = {g, u};
@@ -753,8 +753,10 @@ tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0,
         }
         qgemm_release(&a);
         TLB_TRY(st);
-        TLB_TRY(launch_silu_mul(g, u, g, (size_t)T * F));
-        TLB_TRY(qgemm_prepare(&a, g, T, F, nullptr, 0.f));
+        // silu(gate) * up as a pass of its own: fused into the conversion it was slower (the exponentials ran twice
+        // or the row of 14336 had to stay in registers)
+        TLB_TRY(launch_silu_mul(g, u, g, (int64_t)T * F));
+        TLB_TRY(qgemm_prepare(&a, g, nullptr, T, F, nullptr, 0.f));
         st = qgemm_run(w.down, a, x, x2);              // x = x2 + down(silu(gate) * up)
         qgemm_release(&a);
         TLB_TRY(st);

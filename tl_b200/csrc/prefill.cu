@@ -61,17 +61,6 @@ __global__ void rope_append_kernel(float *__restrict__ q, const float *__restric
     }
 }
 
-// ---- h = silu(gate) * up, elementwise (crates/tl_cpu/src/ffi.rs:2097-2103 then mul)
-__global__ void silu_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, float *__restrict__ h, size_t n4)
-{
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-        const float4 a = reinterpret_cast<const float4 *>(g)[i], b = reinterpret_cast<const float4 *>(u)[i];
-        float4 o;
-        o.x = silu_f(a.x) * b.x; o.y = silu_f(a.y) * b.y; o.z = silu_f(a.z) * b.z; o.w = silu_f(a.w) * b.w;
-        reinterpret_cast<float4 *>(h)[i] = o;
-    }
-}
-
 // ---- causal attention of T new tokens over the cache
 constexpr int kPfQ = 64;     // queries per CTA
 constexpr int kPfK = 64;     // cache rows per tile
@@ -81,6 +70,10 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b)
 {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t *>(&h);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
 {
@@ -100,11 +93,13 @@ template <typename CT, int D>
 __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const PfAttnParams p)
 {
     constexpr int RS = D + 8;                   // shared row stride in halves: 16-byte aligned rows, conflict-free fragments
-    __shared__ __align__(16) __half Ks[kPfK * RS];
-    __shared__ __align__(16) __half Vs[kPfK * RS];
+    constexpr bool kAsync = sizeof(CT) == 2;    // f16 cache rows go to shared memory with cp.async, one tile ahead
+    constexpr int kBuf = kAsync ? 2 : 1;
+    extern __shared__ __align__(16) __half pf_smem[];   // [kBuf][K tile | V tile]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const int h = blockIdx.y, kvh = h / (p.H / p.KVH);
-    const int q0 = blockIdx.x * kPfQ + warp * 16;           // first query row of this warp
+    const int qtile = (int)(gridDim.x - 1 - blockIdx.x);    // late query tiles see the most cache rows: they start first
+    const int q0 = qtile * kPfQ + warp * 16;                // first query row of this warp
     const int qd = p.H * D;
     const CT *kc = reinterpret_cast<const CT *>(p.kcache) + (size_t)kvh * p.max_seq * D;
     const CT *vc = reinterpret_cast<const CT *>(p.vcache) + (size_t)kvh * p.max_seq * D;
@@ -128,26 +123,40 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const PfA
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
     const int pq0 = p.pos0 + q0 + g, pq1 = pq0 + 8;          // cache positions of this thread's two query rows
 
-    const int last_q = min(blockIdx.x * kPfQ + kPfQ, p.T) - 1;
+    const int last_q = min(qtile * kPfQ + kPfQ, p.T) - 1;
     const int n_tiles = (p.pos0 + last_q) / kPfK + 1;        // tiles that hold a key <= the CTA's last query
-    for (int t = 0; t < n_tiles; t++) {
-        const int key0 = t * kPfK;
-        __syncthreads();                                     // the previous tile has been consumed
+    auto tile_async = [&](int t) {   // cache rows of tile t -> buffer t % 2, asynchronously
+        __half *ks = pf_smem + (size_t)(t & 1) * 2 * kPfK * RS, *vs = ks + kPfK * RS;
         for (int i = tid; i < kPfK * (D / 8); i += kPfThreads) {
             const int key = i / (D / 8), ch = i - key * (D / 8);
-            const int row = min(key0 + key, p.max_seq - 1);
-            uint4 kk, vv;
-            if constexpr (sizeof(CT) == 2) {
-                kk = *reinterpret_cast<const uint4 *>(kc + (size_t)row * D + ch * 8);
-                vv = *reinterpret_cast<const uint4 *>(vc + (size_t)row * D + ch * 8);
+            const int row = min(t * kPfK + key, p.max_seq - 1);
+            cp_async16(smem_u32(ks + key * RS + ch * 8), kc + (size_t)row * D + ch * 8);
+            cp_async16(smem_u32(vs + key * RS + ch * 8), vc + (size_t)row * D + ch * 8);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if constexpr (kAsync) tile_async(0);
+    for (int t = 0; t < n_tiles; t++) {
+        const int key0 = t * kPfK;
+        const __half *Ks = pf_smem + (size_t)(kAsync ? (t & 1) : 0) * 2 * kPfK * RS, *Vs = Ks + kPfK * RS;
+        if constexpr (kAsync) {
+            // the buffer tile t + 1 goes to was read in iteration t - 1, which ended with a barrier
+            if (t + 1 < n_tiles) {
+                tile_async(t + 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
             } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+        } else {
+            __half *ks = pf_smem, *vs = pf_smem + kPfK * RS;
+            for (int i = tid; i < kPfK * (D / 8); i += kPfThreads) {
+                const int key = i / (D / 8), ch = i - key * (D / 8);
+                const int row = min(key0 + key, p.max_seq - 1);
                 const float4 a = *reinterpret_cast<const float4 *>(kc + (size_t)row * D + ch * 8), b = *reinterpret_cast<const float4 *>(kc + (size_t)row * D + ch * 8 + 4);
                 const float4 e = *reinterpret_cast<const float4 *>(vc + (size_t)row * D + ch * 8), f = *reinterpret_cast<const float4 *>(vc + (size_t)row * D + ch * 8 + 4);
-                kk = make_uint4(pack_half2(a.x, a.y), pack_half2(a.z, a.w), pack_half2(b.x, b.y), pack_half2(b.z, b.w));
-                vv = make_uint4(pack_half2(e.x, e.y), pack_half2(e.z, e.w), pack_half2(f.x, f.y), pack_half2(f.z, f.w));
+                *reinterpret_cast<uint4 *>(ks + key * RS + ch * 8) = make_uint4(pack_half2(a.x, a.y), pack_half2(a.z, a.w), pack_half2(b.x, b.y), pack_half2(b.z, b.w));
+                *reinterpret_cast<uint4 *>(vs + key * RS + ch * 8) = make_uint4(pack_half2(e.x, e.y), pack_half2(e.z, e.w), pack_half2(f.x, f.y), pack_half2(f.z, f.w));
             }
-            *reinterpret_cast<uint4 *>(Ks + key * RS + ch * 8) = kk;
-            *reinterpret_cast<uint4 *>(Vs + key * RS + ch * 8) = vv;
         }
         __syncthreads();
 
@@ -214,6 +223,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const PfA
                 hmma16816(o[nb + 1], pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b2, b3);
             }
         }
+        __syncthreads();   // the tile has been consumed: its buffer may be refilled
     }
 #pragma unroll
     for (int r = 0; r < 2; r++) {
@@ -251,17 +261,6 @@ tlb_status launch_rope_append(float *q, const float *k, const float *v, void *kc
     return TLB_OK;
 }
 
-tlb_status launch_silu_mul(const float *g, const float *u, float *h, size_t n)
-{
-    if (n == 0) return TLB_OK;
-    if (n % 4) return fail(TLB_ERR_SHAPE, "silu*mul: element count must be a multiple of 4");
-    const size_t n4 = n / 4;
-    const unsigned blocks = (unsigned)std::min<size_t>((n4 + 255) / 256, 148 * 16);
-    silu_mul_kernel<<<blocks, 256, 0, ctx()->stream>>>(g, u, h, n4);
-    count_launch();
-    return TLB_OK;
-}
-
 bool prefill_attention_supported(int D) { return D == 64 || D == 128; }
 
 tlb_status launch_prefill_attention(const float *q, const void *kcache, const void *vcache, int kv_f16, float *out, int n_tokens, int H,
@@ -273,12 +272,19 @@ tlb_status launch_prefill_attention(const float *q, const void *kcache, const vo
     p.q = q; p.kcache = kcache; p.vcache = vcache; p.out = out;
     p.T = n_tokens; p.H = H; p.KVH = KVH; p.max_seq = max_seq; p.pos0 = pos0; p.scale = scale;
     dim3 grid((unsigned)((n_tokens + kPfQ - 1) / kPfQ), (unsigned)H);
+    const size_t tile_bytes = (size_t)2 * kPfK * (D + 8) * sizeof(__half);      // one K tile + one V tile
+    const size_t smem = tile_bytes * (kv_f16 ? 2 : 1);
+    static bool attr_set = false;
+    if (!attr_set) {   // the double-buffered variants need more than the default 48 KB at head_dim 128
+        TLB_CUDA(cudaFuncSetAttribute(prefill_attention_kernel<__half, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(4 * kPfK * 136 * sizeof(__half))));
+        attr_set = true;
+    }
     if (D == 128) {
-        if (kv_f16) prefill_attention_kernel<__half, 128><<<grid, kPfThreads, 0, ctx()->stream>>>(p);
-        else prefill_attention_kernel<float, 128><<<grid, kPfThreads, 0, ctx()->stream>>>(p);
+        if (kv_f16) prefill_attention_kernel<__half, 128><<<grid, kPfThreads, smem, ctx()->stream>>>(p);
+        else prefill_attention_kernel<float, 128><<<grid, kPfThreads, smem, ctx()->stream>>>(p);
     } else {
-        if (kv_f16) prefill_attention_kernel<__half, 64><<<grid, kPfThreads, 0, ctx()->stream>>>(p);
-        else prefill_attention_kernel<float, 64><<<grid, kPfThreads, 0, ctx()->stream>>>(p);
+        if (kv_f16) prefill_attention_kernel<__half, 64><<<grid, kPfThreads, smem, ctx()->stream>>>(p);
+        else prefill_attention_kernel<float, 64><<<grid, kPfThreads, smem, ctx()->stream>>>(p);
     }
     count_launch();
     cudaError_t e = cudaGetLastError();

@@ -485,23 +485,49 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
 }
 
 // ---- activations: f32 rows -> f16 rows scaled by a power of two, and the inverse scale per row.
-// With norm_w the row is RMS-normalised first: v = x / sqrt(mean(x^2) + eps) * w
-// (crates/tl_cpu/src/ffi.rs:2444-2486).
-__global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__ x, const float *__restrict__ norm_w, float eps,
-                                                        __half *__restrict__ xh, float *__restrict__ inv_scale, int64_t k)
+// Fused in front of the conversion, as the caller asks:
+//   x2:     v = silu(x) * x2                               (crates/tl_cpu/src/ffi.rs:2097-2103, then mul)
+//   norm_w: v = v / sqrt(mean(v^2) + eps) * norm_w         (crates/tl_cpu/src/ffi.rs:2444-2486)
+// NC > 0: the row (k <= 4 NT NC) stays in registers, NC float4 per thread, between the pass that finds its scale and
+// the pass that writes; NC = 0 reads (and recomputes) it twice.
+template <int NT, int NC>
+__global__ void __launch_bounds__(NT) x_to_f16_kernel(const float *__restrict__ x, const float *__restrict__ x2, const float *__restrict__ norm_w,
+                                                        float eps, __half *__restrict__ xh, float *__restrict__ inv_scale, int64_t k)
 {
-    __shared__ float red[2][8];
+    constexpr bool CACHED = NC > 0;
+    constexpr int kActCache = NC;
+    __shared__ float red[2][NT / 32];
     const float *row = x + (size_t)blockIdx.x * k;
+    const float *row2 = x2 ? x2 + (size_t)blockIdx.x * k : nullptr;
     __half *orow = xh + (size_t)blockIdx.x * k;
-    float amax = 0.f, ssq = 0.f;
-    for (int64_t i = threadIdx.x * 4; i < k; i += 1024) {
+    auto value = [&](int64_t i) {
         float4 v = *reinterpret_cast<const float4 *>(row + i);
+        if (row2) {
+            const float4 u = *reinterpret_cast<const float4 *>(row2 + i);
+            v.x = silu_f(v.x) * u.x; v.y = silu_f(v.y) * u.y; v.z = silu_f(v.z) * u.z; v.w = silu_f(v.w) * u.w;
+        }
+        return v;
+    };
+    float4 cache[CACHED ? kActCache : 1];
+    float amax = 0.f, ssq = 0.f;
+    auto pass1 = [&](int64_t i, int slot) {
+        float4 v = value(i);
+        if (CACHED) cache[slot] = v;
         if (norm_w) {
             ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             const float4 w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
             v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
         }
         amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    };
+    if (CACHED) {
+#pragma unroll
+        for (int it = 0; it < kActCache; it++) {
+            const int64_t i = threadIdx.x * 4 + it * (NT * 4);
+            if (i < k) pass1(i, it);
+        }
+    } else {
+        for (int64_t i = threadIdx.x * 4; i < k; i += NT * 4) pass1(i, 0);
     }
     for (int o = 16; o; o >>= 1) {
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -511,7 +537,7 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__
     __syncthreads();
     amax = red[0][0];
     ssq = red[1][0];
-    for (int i = 1; i < 8; i++) { amax = fmaxf(amax, red[0][i]); ssq += red[1][i]; }
+    for (int i = 1; i < NT / 32; i++) { amax = fmaxf(amax, red[0][i]); ssq += red[1][i]; }
     const float inv_rms = norm_w ? 1.0f / sqrtf(ssq / (float)k + eps) : 1.0f;
     amax *= inv_rms;
     // amax = f * 2^e with f in [0.5, 1): scale by 2^(14 - e), so the largest element lands in [2^13, 2^14)
@@ -522,8 +548,8 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__
         scale = ldexpf(1.f, 14 - e);
         inv = ldexpf(1.f, e - 14);
     }
-    for (int64_t i = threadIdx.x * 4; i < k; i += 1024) {
-        float4 v = *reinterpret_cast<const float4 *>(row + i);
+    auto pass2 = [&](int64_t i, int slot) {
+        float4 v = CACHED ? cache[slot] : value(i);
         if (norm_w) {
             const float4 w = __ldg(reinterpret_cast<const float4 *>(norm_w + i));
             v.x = v.x * inv_rms * w.x; v.y = v.y * inv_rms * w.y; v.z = v.z * inv_rms * w.z; v.w = v.w * inv_rms * w.w;
@@ -534,6 +560,15 @@ __global__ void __launch_bounds__(256) x_to_f16_kernel(const float *__restrict__
         o2.x = *reinterpret_cast<uint32_t *>(&a);
         o2.y = *reinterpret_cast<uint32_t *>(&b);
         *reinterpret_cast<uint2 *>(orow + i) = o2;
+    };
+    if (CACHED) {
+#pragma unroll
+        for (int it = 0; it < kActCache; it++) {
+            const int64_t i = threadIdx.x * 4 + it * (NT * 4);
+            if (i < k) pass2(i, it);
+        }
+    } else {
+        for (int64_t i = threadIdx.x * 4; i < k; i += NT * 4) pass2(i, 0);
     }
     if (threadIdx.x == 0) inv_scale[blockIdx.x] = inv;
 }
@@ -578,19 +613,24 @@ tlb_status launch_fmt_gemm(dim3 grid, size_t smem, cudaStream_t stream, const CU
 }
 }  // namespace
 
-tlb_status qgemm_prepare(GemmAct *a, const float *x, int64_t m, int64_t k, const float *norm_w, float eps)
+tlb_status qgemm_prepare(GemmAct *a, const float *x, const float *x2, int64_t m, int64_t k, const float *norm_w, float eps)
 {
     Context *c = ctx();
     if (!c) return TLB_ERR_DEVICE;
     a->xh = a->inv = nullptr;
     a->m = m; a->k = k;
     if (k % 256 != 0 || m < 1 || m > INT32_MAX) return fail(TLB_ERR_SHAPE, "tensor-core GEMM: bad activation shape");
-    if (((uintptr_t)x & 15) || (norm_w && ((uintptr_t)norm_w & 15))) return fail(TLB_ERR_ARG, "tensor-core GEMM: activations must be 16-byte aligned");
+    if (((uintptr_t)x & 15) || ((uintptr_t)x2 & 15) || ((uintptr_t)norm_w & 15)) return fail(TLB_ERR_ARG, "tensor-core GEMM: activations must be 16-byte aligned");
     a->xh = storage_alloc((size_t)m * k * sizeof(__half));
     if (!a->xh) return TLB_ERR_ALLOC;
     a->inv = storage_alloc((size_t)m * sizeof(float));
     if (!a->inv) { storage_release(a->xh); a->xh = nullptr; return TLB_ERR_ALLOC; }
-    x_to_f16_kernel<<<(unsigned)m, 256, 0, c->stream>>>(x, norm_w, eps, (__half *)a->xh->ptr, (float *)a->inv->ptr, k);
+    __half *xh = (__half *)a->xh->ptr;
+    float *inv = (float *)a->inv->ptr;
+    // short rows stay in registers between the two passes; long ones are read twice (measured faster than 512
+    // threads x 8 float4 at k = 14336, where the second read comes from L2)
+    if (k <= 4096) x_to_f16_kernel<256, 4><<<(unsigned)m, 256, 0, c->stream>>>(x, x2, norm_w, eps, xh, inv, k);
+    else x_to_f16_kernel<256, 0><<<(unsigned)m, 256, 0, c->stream>>>(x, x2, norm_w, eps, xh, inv, k);
     count_launch();
     return TLB_OK;
 }
@@ -669,7 +709,7 @@ tlb_status qgemm_run(const tlb_qtensor *w, const GemmAct &a, float *out, const f
 tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out)
 {
     GemmAct a;
-    TLB_TRY(qgemm_prepare(&a, x, m, w->k, nullptr, 0.f));
+    TLB_TRY(qgemm_prepare(&a, x, nullptr, m, w->k, nullptr, 0.f));
     tlb_status st = qgemm_run(w, a, out, nullptr);
     qgemm_release(&a);
     return st;

@@ -118,9 +118,9 @@ constexpr int kGemmMinRows = TLB_GEMM_MIN_ROWS;
 bool qgemm_supported(int ggml_type);
 tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out);
 // the same in steps, so that several weights can share one conversion of the activations:
-// f32 rows (optionally RMS-normalised with norm_w) -> scaled f16 rows; then out = [resid +] act . W^T
+// f32 rows (optionally silu(x) * x2, optionally RMS-normalised with norm_w) -> scaled f16 rows; then out = [resid +] act . W^T
 struct GemmAct { Storage *xh = nullptr, *inv = nullptr; int64_t m = 0, k = 0; };
-tlb_status qgemm_prepare(GemmAct *a, const float *x, int64_t m, int64_t k, const float *norm_w, float eps);
+tlb_status qgemm_prepare(GemmAct *a, const float *x, const float *x2, int64_t m, int64_t k, const float *norm_w, float eps);
 tlb_status qgemm_run(const tlb_qtensor *w, const GemmAct &a, float *out, const float *resid);
 // up to three weights of one type and K (q | k | v, gate | up) in one launch: outs[i] = act . ws[i]^T
 tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct &a, float *const *outs, const float *resid);
@@ -129,7 +129,6 @@ void qgemm_release(GemmAct *a);
 tlb_status launch_embed_rows(const int *tokens, const float *table, float *x, int n_tokens, int dm);
 tlb_status launch_rope_append(float *q, const float *k, const float *v, void *kcache, void *vcache, int kv_f16, const float *cos_t,
                               const float *sin_t, int n_tokens, int H, int KVH, int D, int max_seq, int pos0, int rope0, int rope_step);
-tlb_status launch_silu_mul(const float *g, const float *u, float *h, size_t n);
 bool prefill_attention_supported(int head_dim);
 tlb_status launch_prefill_attention(const float *q, const void *kcache, const void *vcache, int kv_f16, float *out, int n_tokens, int H,
                                     int KVH, int D, int max_seq, int pos0, float scale);
