@@ -216,3 +216,20 @@ def test_prefill_llama3_shaped_one_layer(orc):
     b = dec3.step(long_prompt[-1], 2099)     # the same last token again over the cache the prompt left
     assert a == b
     assert relerr(la, dec3.logits()) < 2e-3
+
+
+def test_prefill_f32_cache_head_dim_128():
+    """f32 KV cache with head_dim 128 (the tile conversion path of the prompt attention): prompt in one call against
+    the same session fed token by token."""
+    cfg = dict(synth.LLAMA3_8B, n_layers=1, vocab=1024)
+    wmap = tl.map_from_tensors(synth.llama_tensors(cfg, 8, synth.Q4_K, synth.Q6_K))
+    rng = np.random.default_rng(9)
+    prompt = [int(t) for t in rng.integers(0, cfg["vocab"], 150)]
+    a_dec = tl.Decoder(cfg, wmap, kv_f16=False, max_seq=192)
+    b_dec = tl.Decoder(cfg, wmap, kv_f16=False, max_seq=192)
+    a = a_dec.prefill(prompt, 0)
+    for i, t in enumerate(prompt):
+        b = b_dec.step(t, i)
+    assert a == b
+    assert relerr(a_dec.logits(), b_dec.logits()) < 2e-3
+    assert a_dec.generate(a, 150, 6) == b_dec.generate(b, 150, 6)

@@ -75,6 +75,17 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ float exp2_approx(float x)   // 2^x, relative error 2^-22; 2^-inf = 0
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
 {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -121,6 +132,7 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const PfA
 #pragma unroll
     for (int i = 0; i < D / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+    const float scale2 = p.scale * 1.4426950408889634f;
     const int pq0 = p.pos0 + q0 + g, pq1 = pq0 + 8;          // cache positions of this thread's two query rows
 
     const int last_q = min(qtile * kPfQ + kPfQ, p.T) - 1;
@@ -165,21 +177,25 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const PfA
 #pragma unroll
         for (int nb = 0; nb < kPfK / 8; nb++) {
             s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
-            const __half *krow = Ks + (nb * 8 + g) * RS + 2 * c;
+            // K fragments of two 16-wide steps per ldmatrix: matrices = dims +0, +8, +16, +24 of keys nb * 8 ..
+            const __half *krow = Ks + (nb * 8 + (lane & 7)) * RS + (lane >> 3) * 8;
 #pragma unroll
-            for (int ks = 0; ks < D / 16; ks++) {
-                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(krow + ks * 16), b1 = *reinterpret_cast<const uint32_t *>(krow + ks * 16 + 8);
+            for (int ks = 0; ks < D / 16; ks += 2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(smem_u32(krow + ks * 16), b0, b1, b2, b3);
                 hmma16816(s[nb], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+                hmma16816(s[nb], qa[ks + 1][0], qa[ks + 1][1], qa[ks + 1][2], qa[ks + 1][3], b2, b3);
             }
         }
-        // scale, causal mask, running max
+        // scale (times log2 e: the exponentials below are base 2), causal mask, running max
         float tmax[2] = {-INFINITY, -INFINITY};
+        const bool diagonal = key0 + kPfK - 1 > p.pos0 + q0;   // some key of the tile is ahead of some query of this warp
 #pragma unroll
         for (int nb = 0; nb < kPfK / 8; nb++) {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const int key = key0 + nb * 8 + 2 * c + (e & 1), pq = (e < 2) ? pq0 : pq1;
-                const float v = key <= pq ? s[nb][e] * p.scale : -INFINITY;
+                const float v = (!diagonal || key <= pq) ? s[nb][e] * scale2 : -INFINITY;
                 s[nb][e] = v;
                 tmax[e >> 1] = fmaxf(tmax[e >> 1], v);
             }
@@ -190,15 +206,15 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const PfA
             tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
             tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
             mnew[r] = fmaxf(mrow[r], tmax[r]);               // finite from the first tile on: key 0 is visible to every query
-            corr[r] = expf(mrow[r] - mnew[r]);
+            corr[r] = exp2_approx(mrow[r] - mnew[r]);
             mrow[r] = mnew[r];
         }
         float tsum[2] = {0.f, 0.f};
         uint32_t pa[kPfK / 16][4];
 #pragma unroll
         for (int nb = 0; nb < kPfK / 8; nb++) {
-            const float e0 = expf(s[nb][0] - mnew[0]), e1 = expf(s[nb][1] - mnew[0]);
-            const float e2 = expf(s[nb][2] - mnew[1]), e3 = expf(s[nb][3] - mnew[1]);
+            const float e0 = exp2_approx(s[nb][0] - mnew[0]), e1 = exp2_approx(s[nb][1] - mnew[0]);
+            const float e2 = exp2_approx(s[nb][2] - mnew[1]), e3 = exp2_approx(s[nb][3] - mnew[1]);
             tsum[0] += e0 + e1;
             tsum[1] += e2 + e3;
             pa[nb >> 1][(nb & 1) * 2] = pack_half2(e0, e1);
