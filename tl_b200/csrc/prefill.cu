@@ -101,7 +101,7 @@ struct PfAttnParams {
 };
 
 template <typename CT, int D>
-__global__ void __launch_bounds__(kPfThreads) prefill_attention_kernel(const PfAttnParams p)
+__global__ void __launch_bounds__(kPfThreads, 3) prefill_attention_kernel(const PfAttnParams p)
 {
     constexpr int RS = D + 8;                   // shared row stride in halves: 16-byte aligned rows, conflict-free fragments
     constexpr bool kAsync = sizeof(CT) == 2;    // f16 cache rows go to shared memory with cp.async, one tile ahead
