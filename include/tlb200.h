@@ -123,6 +123,10 @@ tlb_status tlb_argmax_into(tlb_tensor *out, const tlb_tensor *x, tlb_tie_rule ti
 /* temp <= 0: greedy.  temp > 0: the reference CUDA path ignores temp/top_p and returns the argmax
  * (crates/tl_cuda/src/ffi_ops.rs:880-884); this entry point does the same. */
 tlb_status tlb_sample(tlb_tensor **out, const tlb_tensor *logits, float temp, float top_p, tlb_tie_rule tie); /* device_ffi.rs:1158 */
+/* What the reference CPU back end's sampler computes (crates/tl_cpu/src/tensor.rs:1625-1680: softmax(logits / temp),
+ * stable descending order, prefix up to the first running sum above top_p, draw inside it), with the random number
+ * u in [0, 1) given by the caller instead of rand::thread_rng(); temp <= 0 is the greedy branch.  Result: [1] f32. */
+tlb_status tlb_sample_top_p(tlb_tensor **out, const tlb_tensor *logits, float temp, float top_p, double u, tlb_tie_rule tie);
 tlb_status tlb_repetition_penalty(tlb_tensor **out, const tlb_tensor *logits, const tlb_tensor *tokens, float penalty); /* device_ffi.rs:563 */
 /* softmax(q k^T / sqrt(d) + mask) v.  mask_mode 0: none; 1: additive (CUDA, autograd.cu:2263-2367);
  * 2: zero entries become -1e9 (CPU, crates/tl_cpu/src/device_impl.rs:775-870). */

@@ -80,6 +80,8 @@ def lib():
         L.orc_argmax_last.restype = sz
         L.orc_argmax_first.argtypes = [fp, sz]
         L.orc_argmax_first.restype = sz
+        L.orc_sample_top_p.argtypes = [fp, sz, C.c_float, C.c_float, C.c_double]
+        L.orc_sample_top_p.restype = sz
         L.orc_repetition_penalty.argtypes = [fp, sz, fp, sz, C.c_float, fp]
         L.orc_repetition_penalty.restype = None
         L.orc_sdpa_cpu.argtypes = [fp, fp, fp, fp, sz, sz, sz, sz, fp]
@@ -275,6 +277,12 @@ def causal_mask(n):
 def argmax_last(x):
     x, xp = _f(x)
     return int(lib().orc_argmax_last(xp, x.size))
+
+
+def sample_top_p(x, temp, top_p, u):
+    """sample_impl of the reference CPU back end with the random number u in [0, 1) supplied."""
+    x, xp = _f(x)
+    return int(lib().orc_sample_top_p(xp, x.size, temp, top_p, u))
 
 
 def argmax_first(x):

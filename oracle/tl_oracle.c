@@ -429,6 +429,52 @@ size_t orc_argmax_first(const float *x, size_t n)
     return best;
 }
 
+/* CpuTensor::sample_impl, crates/tl_cpu/src/tensor.rs:1625-1680, with the random number u in [0, 1) passed in
+ * (the reference draws it from rand::thread_rng()).  temp <= 0: the greedy branch (last maximum). */
+static const float *g_sort_probs;
+static int cmp_prob_desc(const void *a, const void *b)
+{
+    size_t ia = *(const size_t *)a, ib = *(const size_t *)b;
+    float pa = g_sort_probs[ia], pb = g_sort_probs[ib];
+    if (pb > pa) return 1;
+    if (pb < pa) return -1;
+    return ia < ib ? -1 : (ia > ib ? 1 : 0); /* slice::sort_by is stable: equal probabilities keep index order */
+}
+size_t orc_sample_top_p(const float *logits, size_t n, float temp, float top_p, double u)
+{
+    if (n == 0) return 0;
+    if (temp <= 0.0f) return orc_argmax_last(logits, n);
+    float *probs = (float *)malloc(n * sizeof(float));
+    size_t *indices = (size_t *)malloc(n * sizeof(size_t));
+    float max_val = -INFINITY;
+    for (size_t i = 0; i < n; i++) {
+        probs[i] = logits[i] / temp;
+        if (!(max_val > probs[i])) max_val = probs[i];
+    }
+    float sum_exp = 0.0f;
+    for (size_t i = 0; i < n; i++) sum_exp += expf(probs[i] - max_val);
+    for (size_t i = 0; i < n; i++) probs[i] = expf(probs[i] - max_val) / sum_exp;
+    for (size_t i = 0; i < n; i++) indices[i] = i;
+    g_sort_probs = probs;
+    qsort(indices, n, sizeof(size_t), cmp_prob_desc);
+    float cum_prob = 0.0f;
+    size_t cutoff_index = n - 1;
+    for (size_t i = 0; i < n; i++) {
+        cum_prob += probs[indices[i]];
+        if (cum_prob > top_p) { cutoff_index = i; break; }
+    }
+    float r = (float)u * cum_prob;
+    float acc = 0.0f;
+    size_t selected = indices[0];
+    for (size_t i = 0; i <= cutoff_index; i++) {
+        acc += probs[indices[i]];
+        if (acc >= r) { selected = indices[i]; break; }
+    }
+    free(probs);
+    free(indices);
+    return selected;
+}
+
 void orc_repetition_penalty(const float *logits, size_t n, const float *tokens, size_t nt,
                             float penalty, float *out)
 {

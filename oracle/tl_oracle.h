@@ -96,6 +96,8 @@ void orc_causal_mask(size_t size, float *out);
 size_t orc_argmax_last(const float *x, size_t n);
 /* crates/tl_cuda/src/cuda_kernels/autograd.cu:1119-1132: FIRST maximal index */
 size_t orc_argmax_first(const float *x, size_t n);
+/* tl_cpu tensor.rs:1625-1680 sample_impl with the random number u in [0, 1) as an argument */
+size_t orc_sample_top_p(const float *logits, size_t n, float temp, float top_p, double u);
 /* crates/tl_cpu/src/device_impl.rs:967-1000 */
 void orc_repetition_penalty(const float *logits, size_t n, const float *tokens, size_t nt,
                             float penalty, float *out);

@@ -164,3 +164,34 @@ def test_stream_capture_and_graph_replay():
     g.replay()
     np.testing.assert_array_equal(c.numpy(), np.arange(8) * 3)
     g.destroy()
+
+
+@pytest.mark.parametrize("n,temp,top_p", [(5, 1.0, 0.9), (1000, 0.7, 0.9), (1000, 1.3, 1.0), (32000, 0.8, 0.5),
+                                          (128256, 1.0, 0.95), (128256, 0.6, 0.1)])
+def test_sample_top_p_matches_oracle(orc, n, temp, top_p):
+    """Device sampler against the restated CPU sampler for the same random numbers.  The device sums the
+    exponentials in parallel, so its running sums differ from the sequential ones in the last bits: the token must
+    be the oracle's, or one whose interval of the running sum (in the oracle's order) holds the drawn point within
+    3e-6 (in the far tail of a flat distribution, tokens are narrower than that)."""
+    rng = np.random.default_rng(100 + n)
+    logits = (rng.standard_normal(n) * 3.0).astype(np.float32)
+    t = tl.Tensor.from_numpy(logits)
+    z = logits.astype(np.float64) / temp
+    p = np.exp(z - z.max()); p /= p.sum()
+    order = np.argsort(-p.astype(np.float32), kind="stable")
+    cum = np.cumsum(p[order])
+    above = np.nonzero(cum.astype(np.float32) > np.float32(top_p))[0]
+    cutoff = int(above[0]) if len(above) else n - 1
+    pos_of = np.empty(n, dtype=np.int64); pos_of[order] = np.arange(n)
+    for u in list(rng.random(12)) + [0.0, 0.999999]:
+        got = int(t.sample_top_p(temp, top_p, float(u)).numpy()[0])
+        want = orc.sample_top_p(logits, temp, top_p, float(u))
+        if got != want:
+            r, pos = u * cum[cutoff], int(pos_of[got])
+            assert pos <= cutoff + 1, (u, got, want)
+            lo = cum[pos - 1] if pos else 0.0
+            assert lo - 3e-6 <= r <= cum[pos] + 3e-6, (u, got, want, lo, r, cum[pos])
+    assert int(t.sample_top_p(0.0, top_p, 0.5).numpy()[0]) == orc.argmax_last(logits)      # greedy branch
+    with pytest.raises(tl.TlbError) as e:
+        t.sample_top_p(1.0, top_p, 1.0)
+    assert e.value.code == 8

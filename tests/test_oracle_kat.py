@@ -269,3 +269,25 @@ def test_llama_driver_matches_op_by_op(orc):
     ref2 = run(orc.embedding(emb, np.array([9.0])), 3, kc, vc)
     np.testing.assert_array_equal(ref2.view(np.uint32), step.view(np.uint32))
     model.close()
+
+
+def test_sample_top_p_restatement(orc):
+    """sample_impl (crates/tl_cpu/src/tensor.rs:1625-1680) with the random number passed in.  The reference's own
+    sampler test only pins the dominated case (one logit far above the rest returns that token, whatever is drawn)."""
+    dominated = np.array([1.0, 100.0, 2.0], dtype=np.float32)
+    for u in (0.0, 0.3, 0.999):
+        assert orc.sample_top_p(dominated, 1.0, 0.9, u) == 1
+    # temp <= 0: greedy branch, last maximum
+    assert orc.sample_top_p(np.array([7.0, 1.0, 7.0], dtype=np.float32), 0.0, 0.9, 0.5) == 2
+    # equal probabilities keep index order in the stable descending sort; the draw walks that order
+    x = np.array([0.1, 2.0, 2.0, -1.0, 0.5], dtype=np.float32)
+    p = np.exp(x - x.max()); p /= p.sum()
+    order = [1, 2, 4, 0, 3]
+    cum = np.cumsum(p[order])
+    cutoff = int(np.argmax(cum > 0.9))            # first running sum above top_p
+    for u in (0.0, 0.2, 0.45, 0.7, 0.95, 0.999):
+        r = u * cum[cutoff]
+        want = order[int(np.argmax(cum[:cutoff + 1] >= r))]
+        assert orc.sample_top_p(x, 1.0, 0.9, u) == want
+    # top_p = 1.0: the running sum never exceeds it, every token stays
+    assert orc.sample_top_p(x, 1.0, 1.0, 0.9999) in (0, 3)

@@ -124,6 +124,8 @@ class Tensor:
         check(lib().tlb_argmax_into(out.h, self.h, tie))
         return out
     def sample(self, temp, top_p, tie=TIE_LAST): return Tensor._wrap(lib().tlb_sample, self.h, float(temp), float(top_p), tie)
+    def sample_top_p(self, temp, top_p, u, tie=TIE_LAST):
+        return Tensor._wrap(lib().tlb_sample_top_p, self.h, float(temp), float(top_p), float(u), tie)
     def repetition_penalty(self, tokens, p): return Tensor._wrap(lib().tlb_repetition_penalty, self.h, tokens.h, float(p))
     def sdpa(self, k, v, mask=None, mask_mode=0):
         return Tensor._wrap(lib().tlb_sdpa, self.h, k.h, v.h, mask.h if mask is not None else None, mask_mode)

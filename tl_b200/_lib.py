@@ -74,6 +74,7 @@ def lib():
     d("tlb_apply_rope", S, pvp, vp, vp, vp, C.c_int); d("tlb_argmax", S, pvp, vp, C.c_int)
     d("tlb_argmax_into", S, vp, vp, C.c_int)
     d("tlb_sample", S, pvp, vp, f32, f32, C.c_int); d("tlb_repetition_penalty", S, pvp, vp, vp, f32)
+    d("tlb_sample_top_p", S, pvp, vp, f32, f32, C.c_double, C.c_int)
     d("tlb_sdpa", S, pvp, vp, vp, vp, vp, C.c_int)
     d("tlb_qtensor_from_gguf_bytes", S, pvp, C.c_int, i64, i64, vp, sz); d("tlb_qtensor_retain", S, vp)
     d("tlb_qtensor_release", S, vp)
