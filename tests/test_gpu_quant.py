@@ -180,11 +180,11 @@ def test_qgemm_matches_oracle(orc, t, n, k, m):
         assert relerr(got, emu) < GEMM_EMU_TOL
 
 
-def test_qgemm_full_size_agrees_with_matvec():
-    """Llama-3-8B q_proj shape, 512 rows: sampled rows of the GEMM against the streaming matvec on the same rows."""
-    n = k = 4096
-    rng = np.random.default_rng(77)
-    q = tl.QTensor.from_gguf_bytes(synth.Q4_K, n, k, synth.random_quant(synth.Q4_K, n, k, rng))
+@pytest.mark.parametrize("t,n,k", [(synth.Q4_K, 4096, 4096), (synth.Q6_K, 16384, 4096), (synth.Q4_0, 2048, 5632), (synth.Q8_0, 2048, 2048)])
+def test_qgemm_full_size_agrees_with_matvec(t, n, k):
+    """Model-sized weights, 512 rows: sampled rows of the GEMM against the streaming matvec on the same rows."""
+    rng = np.random.default_rng(77 + t)
+    q = tl.QTensor.from_gguf_bytes(t, n, k, synth.random_quant(t, n, k, rng))
     x = rng.standard_normal((512, k), dtype=np.float32)
     got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
     again = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
