@@ -13,6 +13,10 @@ decoder_vectors.npz - a 2-layer Llama-shaped model from tl_b200.synth (seed in t
 after a 3-token prompt and the next 8 greedy tokens with their logits' checksums, from the oracle's
 op-by-op driver (the op sequence of examples/apps/llama3/chatbot_llama3.tl:66-125,220-236).
 
+prompt_vectors.npz - the same model, a 40-token seeded prompt in one oracle pass (logits of the last token, the
+greedy token after it) and, per GGUF format, the oracle's product of the quant_vectors tensor with 24 seeded
+activation rows: what the many-row (tensor-core) paths must reproduce within their f16 operand rounding.
+
 The reference itself (Rust + LLVM JIT) cannot run here, so these pin this repository's restatement
 against itself over time and against the independent numpy statement; the reference's own
 known-answer values are asserted separately in tests/test_oracle_kat.py.
@@ -80,8 +84,29 @@ def decoder_vectors():
     return out
 
 
+LONG_PROMPT = 40
+ROWS = 24
+
+
+def prompt_vectors(qv):
+    tens = synth.llama_tensors(DECODER_CFG, DECODER_SEED, synth.Q4_K, synth.Q6_K)
+    ref = oracle.Llama(dict(DECODER_CFG, kv_f16=1, max_seq=64), {k: (t, d) for k, (t, d, s) in tens.items()})
+    prompt = np.random.default_rng(DECODER_SEED).integers(0, DECODER_CFG["vocab"], LONG_PROMPT).astype(np.int32)
+    logits = ref.forward([int(t) for t in prompt], 0)
+    out = {"prompt": prompt, "seed": np.array([DECODER_SEED], np.int32), "prompt_logits": logits.astype(np.float32),
+           "first_token": np.array([oracle.argmax_last(logits)], np.int32)}
+    ref.close()
+    for t in (synth.Q4_0, synth.Q8_0, synth.Q4_K, synth.Q6_K):
+        x = np.random.default_rng(777 + t).standard_normal((ROWS, 512)).astype(np.float32)
+        out["xrows_%d" % t] = x
+        out["yrows_%d" % t] = oracle.qmatmul(t, qv["w_%d" % t].reshape(-1), 16, 512, x)
+    return out
+
+
 if __name__ == "__main__":
-    np.savez_compressed(os.path.join(HERE, "quant_vectors.npz"), **quant_vectors())
+    qv = quant_vectors()
+    np.savez_compressed(os.path.join(HERE, "quant_vectors.npz"), **qv)
     np.savez_compressed(os.path.join(HERE, "decoder_vectors.npz"), **decoder_vectors())
-    for f in ("quant_vectors.npz", "decoder_vectors.npz"):
+    np.savez_compressed(os.path.join(HERE, "prompt_vectors.npz"), **prompt_vectors(qv))
+    for f in ("quant_vectors.npz", "decoder_vectors.npz", "prompt_vectors.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

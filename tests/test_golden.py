@@ -28,6 +28,11 @@ def dv():
     return np.load(os.path.join(GOLD, "decoder_vectors.npz"))
 
 
+@pytest.fixture(scope="module")
+def pv():
+    return np.load(os.path.join(GOLD, "prompt_vectors.npz"))
+
+
 @pytest.mark.parametrize("t", TYPES)
 def test_oracle_reproduces_quant_fixtures(orc, qv, t):
     w, x = qv["w_%d" % t], qv["x_%d" % t]
@@ -85,3 +90,32 @@ def test_gpu_matches_decoder_fixture(dv):
         assert tok == int(want)
         pos += 1
     assert relerr(dec.logits(), dv["last_logits"]) < 2e-2
+
+
+def test_oracle_reproduces_prompt_fixture(orc, qv, pv):
+    tens = synth.llama_tensors(DECODER_CFG, int(pv["seed"][0]), synth.Q4_K, synth.Q6_K)
+    ref = orc.Llama(dict(DECODER_CFG, kv_f16=1, max_seq=64), {k: (t, d) for k, (t, d, s) in tens.items()})
+    logits = ref.forward([int(t) for t in pv["prompt"]], 0)
+    ref.close()
+    np.testing.assert_array_equal(logits.view(np.uint32), pv["prompt_logits"].view(np.uint32))
+    assert orc.argmax_last(logits) == int(pv["first_token"][0])
+    for t in TYPES:
+        y = orc.qmatmul(t, qv["w_%d" % t].reshape(-1), 16, 512, pv["xrows_%d" % t])
+        np.testing.assert_array_equal(y.view(np.uint32), pv["yrows_%d" % t].view(np.uint32))
+
+
+@pytest.mark.gpu
+def test_gpu_matches_prompt_fixture(qv, pv):
+    """The many-row paths: 24 activation rows through the tensor-core GEMM (2e-3 per row: f16 operands), the
+    40-token prompt through tlb_decoder_prefill (logits within the 2e-2 gate, the same greedy token)."""
+    import tl_b200 as tl
+    for t in TYPES:
+        q = tl.QTensor.from_gguf_bytes(t, 16, 512, qv["w_%d" % t])
+        y = tl.Tensor.from_numpy(pv["xrows_%d" % t]).matmul_quantized(q).numpy()
+        for i in range(y.shape[0]):
+            assert relerr(y[i], pv["yrows_%d" % t][i]) < 2e-3, (t, i)
+    tens = synth.llama_tensors(DECODER_CFG, int(pv["seed"][0]), synth.Q4_K, synth.Q6_K)
+    dec = tl.Decoder(DECODER_CFG, tl.map_from_tensors(tens), kv_f16=True, max_seq=64)
+    nxt = dec.prefill([int(t) for t in pv["prompt"]], 0, rope_pos0=0, rope_step=0)
+    assert relerr(dec.logits(), pv["prompt_logits"]) < 2e-2
+    assert nxt == int(pv["first_token"][0])
