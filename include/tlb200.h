@@ -222,6 +222,9 @@ tlb_status tlb_decoder_generate(tlb_decoder *d, int32_t first_token, int32_t sta
  * tlb_decoder_logits / tlb_decoder_hidden then describe that last token.  Prompts of 16 tokens or fewer, and
  * shapes the GEMM does not take, run token by token through the fused chain. */
 tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens, int32_t n, int32_t pos0, int32_t rope_pos0, int32_t rope_step, int32_t *next);
+/* tlb_sample_top_p on the logits of the last step or prompt, without bringing them to the host; temp <= 0 returns the
+ * greedy token the step chose.  The caller feeds *token to the next tlb_decoder_step. */
+tlb_status tlb_decoder_sample_top_p(tlb_decoder *d, float temp, float top_p, double u, int32_t *token);
 tlb_status tlb_decoder_logits(tlb_decoder *d, float *logits_out /* host, vocab floats */);
 tlb_status tlb_decoder_hidden(tlb_decoder *d, float *hidden_out /* host, d_model floats: residual stream before output_norm */);
 /* algorithmic bytes one decode step reads at context length ctx (weights + KV), kernels per step */

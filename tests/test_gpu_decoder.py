@@ -233,3 +233,18 @@ def test_prefill_f32_cache_head_dim_128():
     assert a == b
     assert relerr(a_dec.logits(), b_dec.logits()) < 2e-3
     assert a_dec.generate(a, 150, 6) == b_dec.generate(b, 150, 6)
+
+
+def test_decoder_sampling_on_device(orc):
+    """tlb_decoder_sample_top_p on the session's logits = the tensor-level sampler on the same logits = the oracle."""
+    ref, dec, wmap = build(orc, SMALL, 21, synth.Q4_K, synth.Q6_K, True, 32)
+    greedy = dec.step(7, 0)
+    lg = dec.logits()
+    assert dec.sample_top_p(0.0, 0.9, 0.3) == greedy
+    for u in (0.0, 0.11, 0.5, 0.83, 0.97):
+        tok = dec.sample_top_p(0.8, 0.9, u)
+        assert tok == int(tl.Tensor.from_numpy(lg).sample_top_p(0.8, 0.9, u).numpy()[0])
+        assert tok == orc.sample_top_p(lg, 0.8, 0.9, u)
+    with pytest.raises(tl.TlbError) as e:
+        dec.sample_top_p(1.0, 0.9, 1.5)
+    assert e.value.code == 8

@@ -310,6 +310,12 @@ class Decoder:
                                         C.byref(nxt) if read else None))
         return nxt.value
 
+    def sample_top_p(self, temp, top_p, u):
+        """Sample from the logits of the last step / prompt on the device; returns the token id."""
+        tok = C.c_int32(-1)
+        check(lib().tlb_decoder_sample_top_p(self.h, float(temp), float(top_p), float(u), C.byref(tok)))
+        return tok.value
+
     def generate(self, first_token, start_pos, n, read=True):
         out = (C.c_int32 * max(1, n))()
         check(lib().tlb_decoder_generate(self.h, first_token, start_pos, n, out if read else None))

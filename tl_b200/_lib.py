@@ -96,6 +96,7 @@ def lib():
     d("tlb_decoder_step", S, vp, i32, i32, i32, C.POINTER(i32))
     d("tlb_decoder_generate", S, vp, i32, i32, i32, C.POINTER(i32))
     d("tlb_decoder_prefill", S, vp, C.POINTER(i32), i32, i32, i32, i32, C.POINTER(i32))
+    d("tlb_decoder_sample_top_p", S, vp, f32, f32, C.c_double, C.POINTER(i32))
     d("tlb_decoder_logits", S, vp, vp); d("tlb_decoder_hidden", S, vp, vp)
     d("tlb_decoder_stats", S, vp, i32, C.POINTER(u64), C.POINTER(u64), C.POINTER(i32))
     d("tlb_decoder_time_kernel", S, vp, C.c_char_p, C.c_int, C.c_int, C.POINTER(f32), C.POINTER(u64))

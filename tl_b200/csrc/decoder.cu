@@ -797,3 +797,23 @@ extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens,
     }
     return TLB_OK;
 }
+
+// Temperature / top-p sampling from the logits of the last step or prompt, on the device: only the token id crosses
+// to the host (the logits are 4 bytes x vocab).  The caller feeds the token to the next tlb_decoder_step.
+extern "C" tlb_status tlb_decoder_sample_top_p(tlb_decoder *d, float temp, float top_p, double u, int32_t *token)
+{
+    if (!d || !token) return fail(TLB_ERR_NULL, "null argument");
+    if (!(u >= 0.0 && u < 1.0)) return fail(TLB_ERR_ARG, "sample: the random number must lie in [0, 1)");
+    if (temp <= 0.f) {   // greedy: what the step itself chose
+        TLB_CUDA(cudaMemcpyAsync(d->h_state, d->state, sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
+        TLB_TRY(tlb_sync());
+        *token = d->h_state[0];
+        return TLB_OK;
+    }
+    TLB_TRY(launch_sample_top_p(d->logits, d->cfg.vocab, temp, top_p, (float)u, d->amax_v));   // amax_v: free between steps
+    float h = 0.f;
+    TLB_CUDA(cudaMemcpyAsync(&h, d->amax_v, sizeof(float), cudaMemcpyDeviceToHost, ctx()->stream));
+    TLB_TRY(tlb_sync());
+    *token = (int32_t)h;
+    return TLB_OK;
+}
