@@ -248,3 +248,21 @@ def test_decoder_sampling_on_device(orc):
     with pytest.raises(tl.TlbError) as e:
         dec.sample_top_p(1.0, 0.9, 1.5)
     assert e.value.code == 8
+
+
+def test_mixed_weight_types_per_tensor_and_layer(orc):
+    """A Q4_K_M-like file: attn_v and ffn_down of layer 0 in Q6_K, attn_k of layer 1 in Q8_0, the rest Q4_K.
+    Decode steps and a whole prompt against the oracle."""
+    mixed = {"blk.0.attn_v.weight": synth.Q6_K, "blk.0.ffn_down.weight": synth.Q6_K, "blk.1.attn_k.weight": synth.Q8_0}
+    tens = synth.llama_tensors(SMALL, 31, synth.Q4_K, synth.Q6_K, overrides=mixed)
+    ref = orc.Llama(dict(SMALL, kv_f16=1, max_seq=128), {k: (t, d) for k, (t, d, s) in tens.items()})
+    wmap = tl.map_from_tensors(tens)
+    dec = tl.Decoder(SMALL, wmap, kv_f16=True, max_seq=128)
+    run_parity(orc, ref, dec, [3, 200, 41], 12)
+    ref2 = orc.Llama(dict(SMALL, kv_f16=1, max_seq=128), {k: (t, d) for k, (t, d, s) in tens.items()})
+    dec2 = tl.Decoder(SMALL, wmap, kv_f16=True, max_seq=128)
+    prompt = [int(t) for t in np.random.default_rng(32).integers(0, SMALL["vocab"], 50)]
+    ref_logits = ref2.forward(prompt, 0)
+    nxt = dec2.prefill(prompt, 0, rope_pos0=0, rope_step=0)
+    assert relerr(dec2.logits(), ref_logits) < LOGIT_TOL
+    assert nxt == orc.argmax_last(ref_logits)

@@ -213,23 +213,31 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
     const int L = c.n_layers;
     for (int l = 0; l < L; l++) {
         const LayerW &w = d->layers[l];
-        {   // K1
-            MatvecJob j;
-            j.n_w = 3;
-            set_w(j, 0, w.q, d->qkv);
-            set_w(j, 1, w.k, d->qkv + qd);
-            set_w(j, 2, w.v, d->qkv + qd + kvd);
-           
-            j.type = w.q->type; j.k = dm; j.m = 1; j.slices = d->force_slices[0];
-            j.prologue = PRO_ADD_NORM;
-            j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
-            // the residual lives in xb here: the embedding row for layer 0, else what the last down launch left
-            if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; j.x_out = d->xb; }
-            else { j.x = d->xb; j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16; }
-            j.pdl = d->pdl;
-            j.span = next_span();
-            j.dry_run = d->dry;
-            TLB_TRY(launch_qmatvec(j));
+        {   // K1: q | k | v in one launch when they share a type, else one launch per type
+            const tlb_qtensor *ws[3] = {w.q, w.k, w.v};
+            float *outs[3] = {d->qkv, d->qkv + qd, d->qkv + qd + kvd};
+            bool done[3] = {false, false, false};
+            bool first = true;
+            for (int a = 0; a < 3; a++) {
+                if (done[a]) continue;
+                MatvecJob j;
+                j.n_w = 0;
+                for (int b = a; b < 3; b++)
+                    if (!done[b] && ws[b]->type == ws[a]->type) { set_w(j, j.n_w++, ws[b], outs[b]); done[b] = true; }
+                j.type = ws[a]->type; j.k = dm; j.m = 1; j.slices = j.n_w == 3 ? d->force_slices[0] : 0;
+                j.prologue = PRO_ADD_NORM;
+                j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
+                // the residual lives in xb here: the embedding row for layer 0 (the first launch stores it), else what
+                // the last down launch left
+                if (l == 0 && first) { j.emb_table = d->emb->f32(); j.token = d->state; j.x_out = d->xb; }
+                else if (l == 0) { j.x = d->xb; }
+                else { j.x = d->xb; j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16; }
+                j.pdl = d->pdl;
+                j.span = next_span();
+                j.dry_run = d->dry;
+                TLB_TRY(launch_qmatvec(j));
+                first = false;
+            }
         }
         {   // K2
             DecodeAttnJob a;
@@ -361,8 +369,8 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
         std::string p = "blk." + std::to_string(l) + ".";
         LayerW &w = d->layers[l];
         TRY_D(get_q(m, p + "attn_q.weight", &w.q, qd, dm, -1));
-        TRY_D(get_q(m, p + "attn_k.weight", &w.k, kvd, dm, w.q->type));
-        TRY_D(get_q(m, p + "attn_v.weight", &w.v, kvd, dm, w.q->type));
+        TRY_D(get_q(m, p + "attn_k.weight", &w.k, kvd, dm, -1));
+        TRY_D(get_q(m, p + "attn_v.weight", &w.v, kvd, dm, -1));
         TRY_D(get_q(m, p + "attn_output.weight", &w.o, dm, qd, -1));
         TRY_D(get_q(m, p + "ffn_gate.weight", &w.gate, F, dm, -1));
         TRY_D(get_q(m, p + "ffn_up.weight", &w.up, F, dm, w.gate->type));
@@ -374,12 +382,8 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     TRY_D(get_f(m, "output_norm.weight", &d->out_norm, dm));
     TRY_D(get_q(m, "output.weight", &d->head, c.vocab, dm, -1));
     {
-        const LayerW &w0 = d->layers[0];
-        for (const LayerW &w : d->layers)
-            if (w.q->type != w0.q->type || w.o->type != w0.o->type || w.gate->type != w0.gate->type || w.down->type != w0.down->type) {
-                tlb_decoder_destroy(d);
-                return fail(TLB_ERR_TYPE, "all layers must use the same GGML type per projection");
-            }
+        // Types may differ from tensor to tensor and from layer to layer (Q4_K_M files keep attn_v and ffn_down of
+        // some layers in Q6_K); only gate and up of one layer must agree, since they are interleaved into one tensor.
         if (dm % 4 || F % 16 || (qd + 2 * kvd) % 4) {
             tlb_decoder_destroy(d);
             return fail(TLB_ERR_SHAPE, "d_model and the q|k|v width must be multiples of 4, ffn a multiple of 16");
@@ -533,12 +537,27 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
     const int pos_arg = copies;    // the chain modes take the cache position in this argument
     if (copies < 1) copies = 1;
     if (copies > c.n_layers) copies = c.n_layers;
+    {   // the rotation below launches one kernel shape: only the leading layers typed like layer 0 take part
+        const LayerW &a = d->layers[0];
+        int same = 1;
+        while (same < copies) {
+            const LayerW &b = d->layers[same];
+            if (b.q->type != a.q->type || b.k->type != a.q->type || b.v->type != a.q->type || a.k->type != a.q->type || a.v->type != a.q->type ||
+                b.o->type != a.o->type || b.gu->type != a.gu->type || b.down->type != a.down->type) break;
+            same++;
+        }
+        copies = same;
+    }
     std::string w(which);
     if (w == "chain" || w == "chain_graph") {
         // Timeline of one whole decode step launched eagerly (same launches as the graph): `copies` is the
         // cache position, `iters` the warm-up steps.  Printed to stderr: per launch, microseconds from the
         // start of the step to first CTA start / last dependency wait passed / last prologue done / end.
-        const int nk = 5 * c.n_layers + 1;
+        int nk = 1;   // launches of one step: per layer one q | k | v launch per weight type among the three, and four more
+        for (const LayerW &lw : d->layers) {
+            const int kinds = 1 + (lw.k->type != lw.q->type) + (lw.v->type != lw.q->type && lw.v->type != lw.k->type);
+            nk += 4 + kinds;
+        }
         unsigned long long *span = nullptr;
         TLB_CUDA(cudaMalloc(&span, (size_t)nk * 8 * sizeof(unsigned long long)));
         int pos = std::min(std::max(pos_arg, 0), c.max_seq - iters - 8);
@@ -638,6 +657,7 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         float *o = outb;
         j.m = 1; j.prologue = PRO_PLAIN; j.x = xin;
         if (w == "qkv") {
+            if (lw.k->type != lw.q->type || lw.v->type != lw.q->type) { st = fail(TLB_ERR_TYPE, "time_kernel(qkv): q, k, v of layer 0 differ in type"); break; }
             j.n_w = 3; set_w(j, 0, lw.q, o); set_w(j, 1, lw.k, o + qd); set_w(j, 2, lw.v, o + qd + kvd);
             j.type = lw.q->type; j.k = dm; bytes = lw.q->nbytes() + lw.k->nbytes() + lw.v->nbytes();
         } else if (w == "o") {
@@ -692,10 +712,12 @@ constexpr int kPrefillChunk = 2048;
 bool prefill_batched_ok(const tlb_decoder *d)
 {
     const tlb_decoder_cfg &c = d->cfg;
-    const LayerW &w = d->layers[0];
     const int qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim;
-    return qgemm_supported(w.q->type) && qgemm_supported(w.o->type) && qgemm_supported(w.gate->type) && qgemm_supported(w.down->type) &&
-           prefill_attention_supported(c.head_dim) && c.d_model % 256 == 0 && qd % 256 == 0 && c.ffn % 256 == 0 && kvd % 4 == 0;
+    for (const LayerW &w : d->layers)
+        if (!qgemm_supported(w.q->type) || !qgemm_supported(w.k->type) || !qgemm_supported(w.v->type) || !qgemm_supported(w.o->type) ||
+            !qgemm_supported(w.gate->type) || !qgemm_supported(w.down->type))
+            return false;
+    return prefill_attention_supported(c.head_dim) && c.d_model % 256 == 0 && qd % 256 == 0 && c.ffn % 256 == 0 && kvd % 4 == 0;
 }
 
 struct Scratch {
@@ -732,10 +754,20 @@ tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0,
         GemmAct a;
         tlb_status st;
         TLB_TRY(qgemm_prepare(&a, x, nullptr, T, dm, w.attn_norm->f32(), c.eps));
-        {
+        {   // q | k | v: one launch per weight type (one launch when they agree)
             const tlb_qtensor *ws3[3] = {w.q, w.k, w.v};
             float *outs3[3] = {q, k, v};
-            st = qgemm_run_multi(ws3, 3, a, outs3, nullptr);
+            bool done3[3] = {false, false, false};
+            st = TLB_OK;
+            for (int i = 0; i < 3 && st == TLB_OK; i++) {
+                if (done3[i]) continue;
+                const tlb_qtensor *gw[3];
+                float *go[3];
+                int gn = 0;
+                for (int b = i; b < 3; b++)
+                    if (!done3[b] && ws3[b]->type == ws3[i]->type) { gw[gn] = ws3[b]; go[gn++] = outs3[b]; done3[b] = true; }
+                st = qgemm_run_multi(gw, gn, a, go, nullptr);
+            }
         }
         qgemm_release(&a);
         TLB_TRY(st);

@@ -98,10 +98,12 @@ def make_tensor(name, t, shape, seed, scale_sigma=None):
     return random_quant(t, n, k, rng, scale_sigma).reshape(-1)
 
 
-def llama_tensors(cfg, seed, linear_type, head_type=None, embd_type=F32, scale_sigma=None):
-    """dict name -> (type, uint8 bytes, row-major shape)."""
+def llama_tensors(cfg, seed, linear_type, head_type=None, embd_type=F32, scale_sigma=None, overrides=None):
+    """dict name -> (type, uint8 bytes, row-major shape).  overrides: name -> GGML type for single tensors
+    (mixed files such as Q4_K_M keep attn_v / ffn_down of some layers in Q6_K)."""
     out = {}
     for name, t, shape in llama_tensor_specs(cfg, linear_type, head_type, embd_type):
+        t = (overrides or {}).get(name, t)
         out[name] = (t, make_tensor(name, t, shape, seed, scale_sigma), shape)
     return out
 
