@@ -165,6 +165,10 @@ tlb_status tlb_map_add(tlb_map *m, const char *name, tlb_ggml_type type, const i
 tlb_status tlb_map_free(tlb_map *m);                                                      /* tensor_map.rs tl_tensor_map_free */
 int64_t    tlb_map_count(const tlb_map *m);
 const char *tlb_map_name(const tlb_map *m, int64_t i);
+/* Scalar (integer, float, bool) and string metadata of a loaded GGUF file, by key (gguf.rs:61-110 reads and drops them
+ * except general.alignment).  TLB_ERR_INDEX / NULL when the key is absent or of another kind. */
+tlb_status tlb_map_meta_number(const tlb_map *m, const char *key, double *out);
+const char *tlb_map_meta_string(const tlb_map *m, const char *key);
 tlb_status tlb_map_get_quantized(tlb_qtensor **out, tlb_map *m, const char *name);        /* tensor_map.rs:279 (retained clone) */
 tlb_status tlb_map_get(tlb_tensor **out, tlb_map *m, const char *name);                   /* tensor_map.rs:110 dequantised f32, cached */
 
@@ -202,6 +206,10 @@ typedef struct {
     int32_t tp_size, tp_rank;
 } tlb_decoder_cfg;
 
+/* Fills the model sizes of *cfg from the GGUF metadata of a loaded file (<arch>.block_count, .embedding_length, ...;
+ * the reference programs hard-code them, examples/apps/llama3/chatbot_llama3.tl:67-71,95,106,196); kv_f16, max_seq, tie_rule and
+ * the tp fields stay as the caller set them. */
+tlb_status tlb_decoder_cfg_from_map(const tlb_map *m, tlb_decoder_cfg *cfg);
 tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb_map *weights);
 tlb_status tlb_decoder_destroy(tlb_decoder *d);
 /* overwrite cached K/V rows [pos0, pos0+n) of one layer from host f32 [n, n_kv_heads*head_dim] */

@@ -266,3 +266,32 @@ def test_mixed_weight_types_per_tensor_and_layer(orc):
     nxt = dec2.prefill(prompt, 0, rope_pos0=0, rope_step=0)
     assert relerr(dec2.logits(), ref_logits) < LOGIT_TOL
     assert nxt == orc.argmax_last(ref_logits)
+
+
+def test_decoder_sizes_from_gguf_metadata(tmp_path):
+    """Model sizes read from the file's metadata give the session the hard-coded sizes give."""
+    tens = synth.llama_tensors(SMALL, 10, synth.Q4_K, synth.Q6_K)
+    path = tmp_path / "meta.gguf"
+    synth.write_gguf(path, tens, metadata={
+        "general.architecture": "llama", "general.alignment": 32, "llama.block_count": SMALL["n_layers"],
+        "llama.embedding_length": SMALL["d_model"], "llama.attention.head_count": SMALL["n_heads"],
+        "llama.attention.head_count_kv": SMALL["n_kv_heads"], "llama.feed_forward_length": SMALL["ffn"],
+        "llama.attention.layer_norm_rms_epsilon": 1e-5, "llama.rope.freq_base": 10000.0,
+        "llama.rope.dimension_count": SMALL["head_dim"]})
+    m = tl.TensorMap.load(path)
+    assert m.meta_string("general.architecture") == "llama"
+    assert m.meta_number("llama.block_count") == SMALL["n_layers"]
+    assert m.meta_string("llama.block_count") is None
+    with pytest.raises(tl.TlbError) as e:
+        m.meta_number("llama.no_such_key")
+    assert e.value.code == 6
+    cfg = m.decoder_cfg()
+    for k, v in SMALL.items():
+        assert cfg[k] == pytest.approx(v, rel=1e-6), k      # attn_scale: the literal 0.125 for head_dim 64
+    dec = tl.Decoder(cfg, m, kv_f16=True, max_seq=32)
+    dec2 = tl.Decoder(SMALL, tl.map_from_tensors(tens), kv_f16=True, max_seq=32)
+    assert dec.step(7, 0) == dec2.step(7, 0)
+    np.testing.assert_array_equal(dec.logits(), dec2.logits())
+    with pytest.raises(tl.TlbError) as e:
+        tl.map_from_tensors(tens).decoder_cfg()        # no metadata in a map built tensor by tensor
+    assert e.value.code == 8

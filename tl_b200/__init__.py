@@ -197,6 +197,22 @@ class TensorMap:
         check(lib().tlb_map_new(C.byref(out)))
         return TensorMap(out)
 
+    def meta_number(self, key):
+        v = C.c_double()
+        check(lib().tlb_map_meta_number(self.h, key.encode(), C.byref(v)))
+        return v.value
+
+    def meta_string(self, key):
+        v = lib().tlb_map_meta_string(self.h, key.encode())
+        return v.decode() if v is not None else None
+
+    def decoder_cfg(self):
+        """Model sizes from the file's metadata, as a dict a Decoder takes."""
+        c = DecoderCfg()
+        check(lib().tlb_decoder_cfg_from_map(self.h, C.byref(c)))
+        return {k: getattr(c, k) for k in ("n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab",
+                                           "eps", "rope_base", "attn_scale")}
+
     def add(self, name, t, shape, data):
         data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
         shp, rank = _shape_arg(shape)

@@ -27,6 +27,8 @@ struct MapEntry {
 struct tlb_map {
     std::vector<std::string> names;
     std::map<std::string, MapEntry> entries;
+    std::map<std::string, double> meta_num;        // scalar numeric / bool metadata of the GGUF file
+    std::map<std::string, std::string> meta_str;   // string metadata
 };
 
 struct tlb_kvcache {
@@ -126,10 +128,33 @@ static size_t gguf_scalar_size(uint32_t t)
     }
 }
 
-// skips one metadata value; returns its u64 view when it is an unsigned integer (for general.alignment)
-static bool gguf_skip_value(Reader &r, uint32_t t, uint64_t *uint_val)
+// skips one metadata value; returns its u64 view when it is an unsigned integer (for general.alignment);
+// scalar numbers and strings are also kept (num / str, when given) for tlb_map_meta_*
+static bool gguf_skip_value(Reader &r, uint32_t t, uint64_t *uint_val, double *num = nullptr, bool *has_num = nullptr,
+                            std::string *str = nullptr)
 {
-    if (t == 8) { r.str(); return r.ok; }
+    if (t == 8) { std::string v = r.str(); if (str) *str = v; return r.ok; }
+    if (num && has_num && t != 9 && r.ok) {
+        const size_t sz = gguf_scalar_size(t);
+        if (sz && r.off + sz <= r.n) {
+            const uint8_t *q = r.p + r.off;
+            *has_num = true;
+            switch (t) {
+            case 0: { uint8_t v; memcpy(&v, q, 1); *num = v; break; }
+            case 1: { int8_t v; memcpy(&v, q, 1); *num = v; break; }
+            case 2: { uint16_t v; memcpy(&v, q, 2); *num = v; break; }
+            case 3: { int16_t v; memcpy(&v, q, 2); *num = v; break; }
+            case 4: { uint32_t v; memcpy(&v, q, 4); *num = v; break; }
+            case 5: { int32_t v; memcpy(&v, q, 4); *num = v; break; }
+            case 6: { float v; memcpy(&v, q, 4); *num = v; break; }
+            case 7: { uint8_t v; memcpy(&v, q, 1); *num = v ? 1.0 : 0.0; break; }
+            case 10: { uint64_t v; memcpy(&v, q, 8); *num = (double)v; break; }
+            case 11: { int64_t v; memcpy(&v, q, 8); *num = (double)v; break; }
+            case 12: { double v; memcpy(&v, q, 8); *num = v; break; }
+            default: *has_num = false;
+            }
+        }
+    }
     if (t == 9) {
         uint32_t et = r.get<uint32_t>();
         uint64_t cnt = r.get<uint64_t>();
@@ -159,6 +184,56 @@ tlb_status tlb_map_new(tlb_map **out)
 {
     if (!out) return fail(TLB_ERR_NULL, "null out");
     *out = new tlb_map();
+    return TLB_OK;
+}
+
+tlb_status tlb_map_meta_number(const tlb_map *m, const char *key, double *out)
+{
+    if (!m || !key || !out) return fail(TLB_ERR_NULL, "null argument");
+    auto it = m->meta_num.find(key);
+    if (it == m->meta_num.end()) return fail(TLB_ERR_INDEX, "no numeric metadata '%s'", key);
+    *out = it->second;
+    return TLB_OK;
+}
+
+const char *tlb_map_meta_string(const tlb_map *m, const char *key)
+{
+    if (!m || !key) return nullptr;
+    auto it = m->meta_str.find(key);
+    return it == m->meta_str.end() ? nullptr : it->second.c_str();
+}
+
+// Decoder sizes from the file instead of literals in the caller: `<arch>.block_count`, `.embedding_length`,
+// `.attention.head_count`, `.attention.head_count_kv`, `.feed_forward_length`, `.attention.layer_norm_rms_epsilon`,
+// `.rope.freq_base`, `.rope.dimension_count` (arch = general.architecture, "llama" if absent); vocab from the shape of
+// token_embd.weight.  The reference programs hard-code these (examples/apps/llama3/chatbot_llama3.tl:67-71,95,106,196) and
+// scale the scores by the literals 0.08839 (head_dim 128) / 0.125 (head_dim 64): the same literals are used here,
+// 1 / sqrt(head_dim) for other sizes.  kv_f16, max_seq, tie_rule and the tp fields are left as the caller set them.
+tlb_status tlb_decoder_cfg_from_map(const tlb_map *m, tlb_decoder_cfg *cfg)
+{
+    if (!m || !cfg) return fail(TLB_ERR_NULL, "null argument");
+    const char *a = tlb_map_meta_string(m, "general.architecture");
+    const std::string arch = a ? a : "llama";
+    auto num = [&](const std::string &key, double *v) {
+        auto it = m->meta_num.find(arch + "." + key);
+        if (it == m->meta_num.end()) return false;
+        *v = it->second;
+        return true;
+    };
+    double layers, dm, heads, kvh, ffn, eps = 1e-5, base = 10000.0, rdim = 0;
+    if (!num("block_count", &layers) || !num("embedding_length", &dm) || !num("attention.head_count", &heads) || !num("feed_forward_length", &ffn))
+        return fail(TLB_ERR_ARG, "GGUF metadata lacks %s.block_count / embedding_length / attention.head_count / feed_forward_length", arch.c_str());
+    if (!num("attention.head_count_kv", &kvh)) kvh = heads;
+    num("attention.layer_norm_rms_epsilon", &eps);
+    num("rope.freq_base", &base);
+    if (heads < 1 || layers < 1 || dm < 1) return fail(TLB_ERR_ARG, "GGUF metadata holds a non-positive size");
+    if (!num("rope.dimension_count", &rdim) || rdim < 1) rdim = dm / heads;
+    auto emb = m->entries.find("token_embd.weight");
+    if (emb == m->entries.end() || emb->second.shape.size() != 2) return fail(TLB_ERR_ARG, "token_embd.weight is missing or not a matrix");
+    cfg->n_layers = (int32_t)layers; cfg->d_model = (int32_t)dm; cfg->n_heads = (int32_t)heads; cfg->n_kv_heads = (int32_t)kvh;
+    cfg->head_dim = (int32_t)rdim; cfg->ffn = (int32_t)ffn; cfg->vocab = (int32_t)emb->second.shape[0];
+    cfg->eps = (float)eps; cfg->rope_base = (float)base;
+    cfg->attn_scale = cfg->head_dim == 128 ? 0.08839f : (cfg->head_dim == 64 ? 0.125f : 1.0f / sqrtf((float)cfg->head_dim));
     return TLB_OK;
 }
 
@@ -201,8 +276,13 @@ tlb_status tlb_gguf_load(tlb_map **out, const char *path)
             std::string key = r.str();
             uint32_t t = r.get<uint32_t>();
             uint64_t uv = 0;
-            if (!r.ok || !gguf_skip_value(r, t, &uv)) { r.ok = false; break; }
+            double num = 0.0;
+            bool has_num = false;
+            std::string sv;
+            if (!r.ok || !gguf_skip_value(r, t, &uv, &num, &has_num, &sv)) { r.ok = false; break; }
             if (key == "general.alignment" && uv) alignment = uv;
+            if (has_num) m->meta_num[key] = num;
+            else if (t == 8) m->meta_str[key] = sv;
         }
         if (!r.ok) { st = fail(TLB_ERR_ARG, "Failed to decode GGUF metadata"); break; }
         struct Info { std::string name; std::vector<int64_t> shape; uint32_t type; uint64_t offset; };
