@@ -148,7 +148,9 @@ tlb_status tlb_qtensor_info(const tlb_qtensor *q, int *type, int64_t *n, int64_t
  * reference's CPU dequantisers (quantized.rs:167-415) */
 tlb_status tlb_qtensor_dequantize(tlb_tensor **out, const tlb_qtensor *q);
 /* tl_qtensor_matmul (system.rs:180-382) == tl_cuda_mul_mv_q4_k/_q6_k (crates/tl_cuda/src/ffi_ops.rs:1314-1391)
- * plus the Q4_0/Q8_0 kernels the reference lacks: y[M,N] = x[M,K] . W^T, x 1-D [K] or 2-D [M,K]. */
+ * plus the Q4_0/Q8_0 kernels the reference lacks: y[M,N] = x[M,K] . W^T, x 1-D [K] or 2-D [M,K].
+ * Up to 4 rows: the streaming matvec (int8 MMA, max-abs-rel ~1e-5).  More than 16 rows, and 5-16 rows where it is
+ * the faster of the two: the tensor-core GEMM with f16 operands and f32 accumulation (~5e-4 of the row maximum). */
 tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, const tlb_qtensor *w);
 
 /* Tiled-layout introspection (no counterpart in the reference; used by the layout tests): byte offset
