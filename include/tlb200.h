@@ -35,8 +35,8 @@ typedef enum { TLB_F32 = 0, TLB_F64 = 1, TLB_F16 = 2, TLB_BF16 = 3, TLB_I32 = 4,
                TLB_U8 = 6, TLB_U32 = 7 } tlb_dtype;
 
 /* GGML type ids as stored in GGUF (crates/tl_runtime/src/quantized.rs:10-22) */
-typedef enum { TLB_GGML_F32 = 0, TLB_GGML_F16 = 1, TLB_GGML_Q4_0 = 2, TLB_GGML_Q8_0 = 8,
-               TLB_GGML_Q4_K = 12, TLB_GGML_Q6_K = 14 } tlb_ggml_type;
+typedef enum { TLB_GGML_F32 = 0, TLB_GGML_F16 = 1, TLB_GGML_Q4_0 = 2, TLB_GGML_Q4_1 = 3, TLB_GGML_Q5_0 = 6, TLB_GGML_Q5_1 = 7,
+               TLB_GGML_Q8_0 = 8, TLB_GGML_Q8_1 = 9, TLB_GGML_Q4_K = 12, TLB_GGML_Q6_K = 14 } tlb_ggml_type;
 
 typedef struct tlb_tensor tlb_tensor;     /* CudaTensor handle (crates/tl_cuda/src/tensor.rs:39-99) */
 typedef struct tlb_qtensor tlb_qtensor;   /* QTensor (crates/tl_runtime/src/quantized.rs:29-40) */
@@ -139,7 +139,13 @@ tlb_status tlb_fused_add_rms_norm(tlb_tensor **out, const tlb_tensor *x, const t
 /* ---- quantized weights ------------------------------------------------------------------ */
 /* Upload GGUF bytes of a row-major [n, k] tensor and repack them ONCE into the tiled,
  * 16-byte-vectorised device layout (same byte count).  Replaces the raw-byte upload cached
- * in QTensor::gpu_raw_cache (crates/tl_runtime/src/system.rs:316-331). */
+ * in QTensor::gpu_raw_cache (crates/tl_runtime/src/system.rs:316-331).
+ * Q4_0 / Q8_0 / Q4_K / Q6_K with k a multiple of 256 take the tiled layout and the fused kernels.  Every other
+ * case the reference wraps in a QTensor (crates/tl_runtime/src/gguf.rs:157-177) - F32, F16, Q4_1, Q5_0, Q5_1, Q8_1,
+ * and Q4_0 / Q8_0 with k only a multiple of 32 - is kept DENSE: dequantised once to f32 and multiplied through
+ * the f32 matmul, the reference's own route for types without a fused kernel (system.rs:236-264).  The reference's
+ * dequantiser rejects Q4_1 / Q5_0 / Q5_1 / Q8_1 (crates/tl_runtime/src/quantized.rs:108); here they follow the
+ * published GGML block definitions. */
 tlb_status tlb_qtensor_from_gguf_bytes(tlb_qtensor **out, tlb_ggml_type type, int64_t n, int64_t k, const void *bytes, size_t nbytes);
 tlb_status tlb_qtensor_retain(tlb_qtensor *q);          /* tl_qtensor_retain, system.rs:142 */
 tlb_status tlb_qtensor_release(tlb_qtensor *q);         /* tl_qtensor_release_safe / _free, system.rs:150-172 */

@@ -13,13 +13,15 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
 F32, F16, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 8, 12, 14
+Q4_1, Q5_0, Q5_1, Q8_1 = 3, 6, 7, 9
 
 
 def build(force=False):
     """Compile liboracle.so in place (gcc, a second or two)."""
     so = os.path.join(_HERE, "liboracle.so")
     src = os.path.join(_HERE, "tl_oracle.c")
-    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+    hdr = os.path.join(_HERE, "tl_oracle.h")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < max(os.path.getmtime(src), os.path.getmtime(hdr)):
         subprocess.check_call(["make", "-C", _HERE, "-s"])
     return so
 

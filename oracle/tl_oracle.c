@@ -93,7 +93,61 @@ size_t orc_type_nbytes(int type, size_t nelem)
     case ORC_Q8_0: return (nelem % 32) ? 0 : nelem / 32 * 34;
     case ORC_Q4_K: return (nelem % 256) ? 0 : nelem / 256 * 144;
     case ORC_Q6_K: return (nelem % 256) ? 0 : nelem / 256 * 210;
+    case ORC_Q4_1: return (nelem % 32) ? 0 : nelem / 32 * 20;
+    case ORC_Q5_0: return (nelem % 32) ? 0 : nelem / 32 * 22;
+    case ORC_Q5_1: return (nelem % 32) ? 0 : nelem / 32 * 24;
+    case ORC_Q8_1: return (nelem % 32) ? 0 : nelem / 32 * 36;
     default: return 0;
+    }
+}
+
+/* The four block types the reference's loader accepts (crates/tl_runtime/src/gguf.rs:160-165) but its
+ * dequantiser rejects (crates/tl_runtime/src/quantized.rs:108 "Unsupported quantization type"): there
+ * is no reference arithmetic to follow, so these restate the published GGML block definitions in the
+ * same style as the reference's Q4_0 / Q8_0 code (integer to f32, one multiply, then one add, never
+ * fused).  PARITY UNPINNED for these four.
+ *   Q4_1: f16 d, f16 m, 16 nibble bytes           w[j] = d*(b&15) + m, w[j+16] = d*(b>>4) + m
+ *   Q5_0: f16 d, u32 qh, 16 nibble bytes          q = (nibble | bit j of qh << 4) - 16, w = d*q
+ *   Q5_1: f16 d, f16 m, u32 qh, 16 nibble bytes   q = nibble | bit << 4,               w = d*q + m
+ *   Q8_1: f16 d, f16 s (d * sum of quants, unused here), 32 int8                       w = d*q      */
+static void dequant_q4_1(const uint8_t *data, size_t nblocks, float *out)
+{
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *p = data + b * 20;
+        float d = f16_at(p), m = f16_at(p + 2);
+        float *y = out + b * 32;
+        for (int j = 0; j < 16; j++) {
+            uint8_t byte = p[4 + j];
+            y[j] = d * (float)(byte & 0x0F) + m;
+            y[j + 16] = d * (float)(byte >> 4) + m;
+        }
+    }
+}
+
+static void dequant_q5(const uint8_t *data, size_t nblocks, float *out, int with_min)
+{
+    size_t bb = with_min ? 24 : 22;
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *p = data + b * bb;
+        float d = f16_at(p), m = with_min ? f16_at(p + 2) : 0.0f;
+        const uint8_t *qhp = p + (with_min ? 4 : 2), *qs = qhp + 4;
+        uint32_t qh = (uint32_t)qhp[0] | ((uint32_t)qhp[1] << 8) | ((uint32_t)qhp[2] << 16) | ((uint32_t)qhp[3] << 24);
+        float *y = out + b * 32;
+        for (int j = 0; j < 16; j++) {
+            int x0 = (int)(qs[j] & 0x0F) | (int)(((qh >> j) & 1u) << 4);
+            int x1 = (int)(qs[j] >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4);
+            if (with_min) { y[j] = d * (float)x0 + m; y[j + 16] = d * (float)x1 + m; }
+            else { y[j] = d * (float)(x0 - 16); y[j + 16] = d * (float)(x1 - 16); }
+        }
+    }
+}
+
+static void dequant_q8_1(const uint8_t *data, size_t nblocks, float *out)
+{
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *p = data + b * 36;
+        float d = f16_at(p);
+        for (int j = 0; j < 32; j++) out[b * 32 + j] = d * (float)(int8_t)p[4 + j];
     }
 }
 
@@ -204,6 +258,10 @@ int orc_dequantize(int type, const uint8_t *data, size_t nbytes, size_t nelem, f
     case ORC_Q8_0: dequant_q8_0(data, nelem / 32, out); return 0;
     case ORC_Q4_K: dequant_q4_k(data, nelem / 256, out); return 0;
     case ORC_Q6_K: dequant_q6_k(data, nelem / 256, out); return 0;
+    case ORC_Q4_1: dequant_q4_1(data, nelem / 32, out); return 0;
+    case ORC_Q5_0: dequant_q5(data, nelem / 32, out, 0); return 0;
+    case ORC_Q5_1: dequant_q5(data, nelem / 32, out, 1); return 0;
+    case ORC_Q8_1: dequant_q8_1(data, nelem / 32, out); return 0;
     default: return -1;
     }
 }
@@ -226,8 +284,12 @@ void orc_matmul(const float *a, const float *b, float *out,
     }
 }
 
+/* Output columns are independent, so they are spread over the host threads (OpenMP); every dot product
+ * still runs in the reference's sequential order, so results do not depend on the thread count.  The timed
+ * CPU baseline (orc_matmul_cached_t_cols) stays single-threaded, as the reference is. */
 void orc_matmul_wt(const float *w, size_t n, size_t k, const float *x, size_t m, float *out)
 {
+#pragma omp parallel for schedule(static)
     for (size_t j = 0; j < n; j++) {
         const float *wr = w + j * k;
         for (size_t i = 0; i < m; i++) {
@@ -251,19 +313,32 @@ int orc_qmatmul(int type, const uint8_t *w, size_t n, size_t k,
 {
     size_t rb = type_row_bytes(type, k);
     if (rb == 0) return -1;
-    float *row = (float *)malloc(k * sizeof(float));
-    if (!row) return -2;
-    for (size_t j = 0; j < n; j++) {
-        if (orc_dequantize(type, w + j * rb, rb, k, row)) { free(row); return -1; }
-        for (size_t i = 0; i < m; i++) {
-            const float *xr = x + i * k;
-            float sum = 0.0f;
-            for (size_t p = 0; p < k; p++) sum += xr[p] * row[p];
-            out[i * n + j] = sum;
+    int bad = 0;
+#pragma omp parallel
+    {
+        float *row = (float *)malloc(k * sizeof(float));
+        if (!row) {
+#pragma omp atomic write
+            bad = 2;
         }
+#pragma omp for schedule(static)
+        for (size_t j = 0; j < n; j++) {
+            if (!row) continue;
+            if (orc_dequantize(type, w + j * rb, rb, k, row)) {
+#pragma omp atomic write
+                bad = 1;
+                continue;
+            }
+            for (size_t i = 0; i < m; i++) {
+                const float *xr = x + i * k;
+                float sum = 0.0f;
+                for (size_t p = 0; p < k; p++) sum += xr[p] * row[p];
+                out[i * n + j] = sum;
+            }
+        }
+        free(row);
     }
-    free(row);
-    return 0;
+    return bad ? -bad : 0;
 }
 
 /* ---------------------------------------------------------------- norm / rope / misc */

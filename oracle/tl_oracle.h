@@ -28,7 +28,8 @@ extern "C" {
 
 /* GGML type ids as stored in a GGUF tensor-info record. */
 enum {
-    ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q6_K = 14
+    ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q4_1 = 3, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q8_1 = 9,
+    ORC_Q4_K = 12, ORC_Q6_K = 14
 };
 
 float    orc_f16_to_f32(uint16_t h);

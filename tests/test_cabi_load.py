@@ -83,3 +83,47 @@ def test_gguf_writer_layout(tmp_path):
     raw = p.read_bytes()
     i = raw.index(b"\x01\x00\x00\x00\x00\x00\x00\x00w") + 9
     assert struct.unpack_from("<IQQI", raw, i) == (2, 512, 32, 12)
+
+
+def _gguf_header(n_tensors, kvs=b"", n_kv=0, infos=b""):
+    return b"GGUF" + struct.pack("<IQQ", 3, n_tensors, n_kv) + kvs + infos
+
+
+def _load(tmp_path, raw):
+    p = tmp_path / "h.gguf"
+    p.write_bytes(raw)
+    out = C.c_void_p()
+    st = _lib.lib().tlb_gguf_load(C.byref(out), str(p).encode())
+    n = _lib.lib().tlb_map_count(out) if st == 0 else None
+    if st == 0:
+        _lib.lib().tlb_map_free(out)
+    return st, n
+
+
+def test_gguf_hostile_headers_are_clean_errors(tmp_path):
+    """Lengths and offsets of an untrusted file can neither wrap the bounds checks nor reach an allocation: truncated
+    files and absurd string / array lengths give TLB_ERR_ARG; tensors whose data lies outside the file are skipped, as the
+    reference skips them (crates/tl_runtime/src/gguf.rs:183-186).  None of this needs a device."""
+    s = lambda b: struct.pack("<Q", len(b)) + b
+    huge = 0xFFFFFFFFFFFFFFF0
+    assert _load(tmp_path, b"GGUF")[0] == 8                                    # ends after the magic
+    assert _load(tmp_path, b"GGUF" + struct.pack("<I", 3))[0] == 8             # truncated counts
+    assert _load(tmp_path, b"GGML" + b"\0" * 40)[0] == 8                       # bad magic
+    assert _load(tmp_path, _gguf_header(0, struct.pack("<Q", huge) + b"k", 1))[0] == 8        # key length wraps off + len
+    kv_str = s(b"general.name") + struct.pack("<I", 8) + struct.pack("<Q", huge)
+    assert _load(tmp_path, _gguf_header(0, kv_str, 1))[0] == 8                                # string value length
+    kv_arr = s(b"tokens") + struct.pack("<IIQ", 9, 4, huge)
+    assert _load(tmp_path, _gguf_header(0, kv_arr + b"\0" * 64, 1))[0] == 8                   # cnt * element size wraps
+    kv_sarr = s(b"tokens") + struct.pack("<IIQ", 9, 8, huge)
+    assert _load(tmp_path, _gguf_header(0, kv_sarr + b"\0" * 64, 1))[0] == 8                  # array of strings, absurd count
+    assert _load(tmp_path, _gguf_header(5))[0] == 8                                           # tensor infos missing
+    info = s(b"t") + struct.pack("<I", 1) + struct.pack("<Q", 8) + struct.pack("<IQ", 0, huge)
+    assert _load(tmp_path, _gguf_header(1, infos=info) + b"\0" * 128) == (0, 0)               # offset beyond the file: skipped
+    info = s(b"t") + struct.pack("<I", 2) + struct.pack("<QQ", 1 << 40, 1 << 40) + struct.pack("<IQ", 0, 0)
+    assert _load(tmp_path, _gguf_header(1, infos=info) + b"\0" * 128) == (0, 0)               # shape product leaves int64: skipped
+    info = s(b"t") + struct.pack("<I", 1) + struct.pack("<Q", 1 << 63) + struct.pack("<IQ", 0, 0)
+    assert _load(tmp_path, _gguf_header(1, infos=info) + b"\0" * 128)[0] == 8                 # dimension above int64
+    info = s(b"t") + struct.pack("<I", 1) + struct.pack("<Q", 64) + struct.pack("<IQ", 2, 0)
+    assert _load(tmp_path, _gguf_header(1, infos=info) + b"\0" * 16) == (0, 0)                # Q4_0 data cut short: skipped
+    kv_al = s(b"general.alignment") + struct.pack("<II", 4, 0x80000000)
+    assert _load(tmp_path, _gguf_header(0, kv_al, 1))[0] == 8                                 # absurd alignment

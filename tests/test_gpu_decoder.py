@@ -123,8 +123,11 @@ def test_gguf_file_round_trip(orc, tmp_path):
     dec2 = tl.Decoder(SMALL, tl.map_from_tensors(tens), kv_f16=True, max_seq=32)
     assert dec.step(7, 0) == dec2.step(7, 0)
     np.testing.assert_array_equal(dec.logits(), dec2.logits())
-    with pytest.raises(tl.TlbError):
-        m.get_quantized("token_embd.weight")   # F32 tensors have no quantized kernel
+    emb_q = m.get_quantized("token_embd.weight")   # an F32 tensor as a (dense) QTensor: a tied output head
+    assert emb_q.info()["type"] == synth.F32
+    with pytest.raises(tl.TlbError) as e:          # the fused session itself takes tiled weights only
+        tl.Decoder(SMALL, tl.map_from_tensors(synth.llama_tensors(SMALL, 9, synth.Q4_K, synth.F16)), kv_f16=True, max_seq=32)
+    assert e.value.code == 7
     with pytest.raises(tl.TlbError):
         m.get("missing.weight")
 
@@ -136,8 +139,13 @@ PROMPT = 70   # > 64: two query tiles of the prompt attention, ragged second til
 @pytest.mark.parametrize("linear,head,kv_f16", [(synth.Q4_K, synth.Q6_K, True), (synth.Q4_K, synth.Q6_K, False),
                                                  (synth.Q4_0, synth.Q4_0, False), (synth.Q8_0, synth.Q8_0, True)])
 def test_prefill_matches_oracle_and_continues(orc, linear, head, kv_f16):
-    """The prompt in one call (reference CPU rotation: every prompt token at row 0), then greedy decoding."""
-    ref, dec, wmap = build(orc, SMALL, 11, linear, head, kv_f16, 128)
+    """The prompt in one call (reference CPU rotation: every prompt token at row 0), then greedy decoding.
+    Q8_0 block scales are drawn as |N(0, 0.002)| here: with the operator sweep's |N(0, 0.01)| and uniform int8 quants a
+    weight is ~0.7 in magnitude (a trained model's is ~0.02), attention scores reach the hundreds, and the f16 operand
+    rounding of the prompt GEMMs (4e-4 of a row's maximum, carried by the residual stream into every later layer's cache
+    rows) moves logits by the same 5-7e-2 as the model's own f16 rounding of cached K/V does.  At a trained model's
+    magnitudes every format stays inside the 2e-2 gate, prompt rows in the cache included."""
+    ref, dec, wmap = build(orc, SMALL, 11, linear, head, kv_f16, 128, sigma=0.002 if linear == synth.Q8_0 else None)
     rng = np.random.default_rng(5)
     prompt = [int(t) for t in rng.integers(0, SMALL["vocab"], PROMPT)]
     ref_logits = ref.forward(prompt, 0)
@@ -153,10 +161,7 @@ def test_prefill_matches_oracle_and_continues(orc, linear, head, kv_f16):
         tok = orc.argmax_last(ref_logits)
         assert nxt == tok
         pos += 1
-    # The cache rows a prompt leaves carry the f16 operand rounding of the GEMMs (~5e-4).  The synthetic Q8_0
-    # model (uniform int8 weights) amplifies that in its near-one-hot attention; its gate is on tokens only.
-    if linear != synth.Q8_0:
-        assert worst < LOGIT_TOL, worst
+    assert worst < LOGIT_TOL, worst
 
 
 def test_prefill_in_chunks_equals_token_by_token(orc):

@@ -63,10 +63,13 @@ def test_qtensor_rejects_bad_input():
         tl.QTensor.from_gguf_bytes(synth.Q4_K, 16, 256, np.zeros(100, dtype=np.uint8))
     assert e.value.code == 1
     with pytest.raises(tl.TlbError) as e:
-        tl.QTensor.from_gguf_bytes(synth.Q4_0, 16, 96, np.zeros(16 * 3 * 18, dtype=np.uint8))
+        tl.QTensor.from_gguf_bytes(synth.Q4_0, 16, 48, np.zeros(16 * 27, dtype=np.uint8))      # K not a whole number of blocks
     assert e.value.code == 1
     with pytest.raises(tl.TlbError) as e:
-        tl.QTensor.from_gguf_bytes(5, 16, 256, np.zeros(16, dtype=np.uint8))  # Q4_1: recognised by GGUF, no kernel
+        tl.QTensor.from_gguf_bytes(synth.Q4_K, 16, 128, np.zeros(16 * 72, dtype=np.uint8))     # K-quants need K % 256 == 0
+    assert e.value.code == 1
+    with pytest.raises(tl.TlbError) as e:
+        tl.QTensor.from_gguf_bytes(5, 16, 256, np.zeros(16, dtype=np.uint8))  # type 5: a GGML id neither side knows
     assert e.value.code == 7
     q = tl.QTensor.from_gguf_bytes(synth.Q4_K, 0, 256, np.zeros(0, dtype=np.uint8))  # empty tensor
     assert q.dequantize().numpy().shape == (0, 256)
@@ -221,3 +224,72 @@ def test_mid_row_counts_on_a_wide_weight(orc):
         assert got.shape == (m, n)
         for i in range(m):
             assert relerr(got[i][rows], ref[i]) < GEMM_TOL, (m, i)
+
+
+# ---- dense QTensors: every other tensor type the reference's loader wraps in a QTensor ---------------------
+DENSE = [(synth.F32, 24, 80), (synth.F16, 24, 80), (synth.Q4_1, 24, 96), (synth.Q5_0, 24, 96), (synth.Q5_1, 40, 320),
+         (synth.Q8_1, 24, 64), (synth.Q4_0, 24, 96), (synth.Q8_0, 33, 160)]
+
+
+@pytest.mark.parametrize("t,n,k", DENSE)
+def test_dense_qtensor_dequant_bit_exact_and_matmul(orc, t, n, k):
+    """F32 / F16 / Q4_1 / Q5_0 / Q5_1 / Q8_1, and Q4_0 / Q8_0 rows that are not a multiple of 256 long: dequantised once,
+    bit-exact against the oracle, and multiplied through the f32 matmul (the reference's route for types without a
+    fused kernel, crates/tl_runtime/src/system.rs:236-264)."""
+    rng = np.random.default_rng(4000 + t + n)
+    w = synth.random_quant(t, n, k, rng)
+    q = tl.QTensor.from_gguf_bytes(t, n, k, w)
+    info = q.info()
+    assert (info["type"], info["n"], info["k"]) == (t, n, k)
+    ref = orc.dequantize(t, w.reshape(-1), n * k).reshape(n, k)
+    np.testing.assert_array_equal(q.dequantize().numpy().view(np.uint32), ref.view(np.uint32))
+    for m in (1, 3, 20):
+        x = rng.standard_normal((m, k), dtype=np.float32)
+        got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+        want = orc.qmatmul(t, w.reshape(-1), n, k, x)
+        assert got.shape == (m, n) and relerr(got, want) < 1e-5
+
+
+def test_f16_and_f32_tensors_through_the_map(orc):
+    """An F16 tensor through tlb_map_add / tlb_map_get is widened exactly (all 63488 finite bit patterns and both zeros,
+    crates/tl_runtime/src/quantized.rs:167-180); tlb_map_get_quantized wraps F32 / F16 tensors too
+    (crates/tl_runtime/src/tensor_map.rs:279)."""
+    bits = np.array([b for b in range(65536) if (b & 0x7C00) != 0x7C00], dtype=np.uint16)
+    bits = np.concatenate([bits, bits[:(-len(bits)) % 64]]).reshape(-1, 64)
+    m = tl.TensorMap.new()
+    m.add("h.weight", synth.F16, bits.shape, bits)
+    got = m.get("h.weight").numpy()
+    want = orc.dequantize(synth.F16, bits.view(np.uint8).reshape(-1), bits.size).reshape(bits.shape)
+    np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32))
+    np.testing.assert_array_equal(got, bits.view(np.float16).astype(np.float32))
+    rng = np.random.default_rng(5)
+    emb = (rng.standard_normal((50, 64), dtype=np.float32) * 0.02)
+    m.add("token_embd.weight", synth.F32, emb.shape, emb)
+    x = rng.standard_normal((2, 64), dtype=np.float32)
+    tied = tl.Tensor.from_numpy(x).matmul_quantized(m.get_quantized("token_embd.weight")).numpy()   # a tied output head
+    assert relerr(tied, orc.qmatmul(synth.F32, emb.view(np.uint8).reshape(-1), 50, 64, x)) < 1e-5
+    hq = m.get_quantized("h.weight")
+    assert hq.info()["type"] == synth.F16
+    np.testing.assert_array_equal(hq.dequantize().numpy().view(np.uint32), want.view(np.uint32))
+    xh = rng.standard_normal((1, 64), dtype=np.float32)
+    finite = np.abs(want).max(axis=1) < 1e3            # rows without huge f16 values: a well-conditioned product
+    gh = tl.Tensor.from_numpy(xh).matmul_quantized(hq).numpy()[0][finite]
+    wh = orc.qmatmul(synth.F16, bits.view(np.uint8).reshape(-1), bits.shape[0], 64, xh)[0][finite]
+    np.testing.assert_allclose(gh, wh, rtol=1e-4, atol=1e-3)
+
+
+def test_misaligned_activation_view(orc):
+    """A zero-copy view that starts at an odd element (tlb_narrow) is not 16-byte aligned: the matmul copies it first."""
+    rng = np.random.default_rng(6)
+    n, k = 64, 512
+    w = synth.random_quant(synth.Q4_K, n, k, rng)
+    q = tl.QTensor.from_gguf_bytes(synth.Q4_K, n, k, w)
+    buf = rng.standard_normal(k + 3, dtype=np.float32)
+    view = tl.Tensor.from_numpy(buf).narrow(0, 1, k)            # starts 4 bytes into the buffer
+    got = view.matmul_quantized(q).numpy()
+    assert relerr(got, orc.qmatmul(synth.Q4_K, w.reshape(-1), n, k, buf[1:k + 1])[0]) < MATVEC_TOL
+    many = rng.standard_normal((40, k + 1), dtype=np.float32)   # the tensor-core route, rows at odd offsets
+    v2 = tl.Tensor.from_numpy(many.reshape(-1)).narrow(0, 1, 40 * k).reshape([40, k])
+    got2 = v2.matmul_quantized(q).numpy()
+    want2 = orc.qmatmul(synth.Q4_K, w.reshape(-1), n, k, many.reshape(-1)[1:40 * k + 1].reshape(40, k))
+    assert relerr(got2, want2) < 5e-3

@@ -291,3 +291,24 @@ def test_sample_top_p_restatement(orc):
         assert orc.sample_top_p(x, 1.0, 0.9, u) == want
     # top_p = 1.0: the running sum never exceeds it, every token stays
     assert orc.sample_top_p(x, 1.0, 1.0, 0.9999) in (0, 3)
+
+
+def test_extra_block_types_hand_built(orc):
+    """Q4_1 / Q5_0 / Q5_1 / Q8_1 (no dequantiser in the reference, crates/tl_runtime/src/quantized.rs:108): single blocks
+    with d = 2.0, m = 0.5 and ramp quants, worked out by hand from the published block definitions."""
+    from tl_b200 import synth
+    h = lambda v: np.array([v], dtype=np.float16).view(np.uint8)
+    nib = np.array([(j & 15) | (((15 - j) & 15) << 4) for j in range(16)], dtype=np.uint8)   # low nibble j, high nibble 15 - j
+    lo, hi = np.arange(16), 15 - np.arange(16)
+    q41 = np.concatenate([h(2.0), h(0.5), nib])
+    np.testing.assert_array_equal(orc.dequantize(synth.Q4_1, q41, 32), np.concatenate([2.0 * lo + 0.5, 2.0 * hi + 0.5]).astype(np.float32))
+    qh = np.array([0x0000FFFF], dtype=np.uint32).view(np.uint8)                              # fifth bit set for the first 16 weights only
+    q50 = np.concatenate([h(2.0), qh, nib])
+    np.testing.assert_array_equal(orc.dequantize(synth.Q5_0, q50, 32), np.concatenate([2.0 * (lo + 16 - 16), 2.0 * (hi - 16)]).astype(np.float32))
+    q51 = np.concatenate([h(2.0), h(0.5), qh, nib])
+    np.testing.assert_array_equal(orc.dequantize(synth.Q5_1, q51, 32), np.concatenate([2.0 * (lo + 16) + 0.5, 2.0 * hi + 0.5]).astype(np.float32))
+    q = np.arange(-16, 16, dtype=np.int8)
+    q81 = np.concatenate([h(2.0), h(123.0), q.view(np.uint8)])
+    np.testing.assert_array_equal(orc.dequantize(synth.Q8_1, q81, 32), (2.0 * q).astype(np.float32))
+    assert orc.type_nbytes(synth.Q4_1, 64) == 40 and orc.type_nbytes(synth.Q5_0, 64) == 44
+    assert orc.type_nbytes(synth.Q5_1, 64) == 48 and orc.type_nbytes(synth.Q8_1, 64) == 72 and orc.type_nbytes(synth.Q5_0, 48) == 0

@@ -13,6 +13,7 @@ from . import synth  # noqa: F401
 from ._lib import DecoderCfg, TlbError, check, declared_symbols, lib  # noqa: F401
 
 F32, F16, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 8, 12, 14
+Q4_1, Q5_0, Q5_1, Q8_1 = 3, 6, 7, 9
 ROPE_CPU, ROPE_HALF = 0, 1
 TIE_LAST, TIE_FIRST = 0, 1
 _NP_DT = {0: np.float32, 1: np.float64, 2: np.float16, 4: np.int32, 5: np.int64, 6: np.uint8, 7: np.uint32}

@@ -136,6 +136,9 @@ tlb_status dalloc(tlb_decoder *d, T **p, size_t count, bool zero = true)
 tlb_status get_q(tlb_map *m, const std::string &name, tlb_qtensor **q, int64_t n, int64_t k, int want_type)
 {
     TLB_TRY(tlb_map_get_quantized(q, m, name.c_str()));
+    if (!(*q)->tiled())
+        return fail(TLB_ERR_TYPE, "tensor '%s' (GGML type %d, K = %lld) has no fused kernel: the decode session takes Q4_0 / Q8_0 / Q4_K / Q6_K with K a multiple of 256",
+                    name.c_str(), (*q)->type, (long long)(*q)->k);
     if ((*q)->n != n || (*q)->k != k)
         return fail(TLB_ERR_SHAPE, "tensor '%s' is [%lld, %lld], expected [%lld, %lld]", name.c_str(), (long long)(*q)->n,
                     (long long)(*q)->k, (long long)n, (long long)k);

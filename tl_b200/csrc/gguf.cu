@@ -43,41 +43,39 @@ __global__ void f16_to_f32_kernel2(const __half *a, float *out, int64_t n)
         out[i] = __half2float(a[i]);
 }
 
-static size_t ggml_nbytes(int type, int64_t nelem)
-{
-    switch (type) {
-    case TLB_GGML_F32: return (size_t)nelem * 4;
-    case TLB_GGML_F16: return (size_t)nelem * 2;
-    case TLB_GGML_Q4_0: return (size_t)(nelem / 32) * 18;
-    case TLB_GGML_Q8_0: return (size_t)(nelem / 32) * 34;
-    case TLB_GGML_Q4_K: return (size_t)(nelem / 256) * 144;
-    case TLB_GGML_Q6_K: return (size_t)(nelem / 256) * 210;
-    default: return 0;
-    }
-}
-
 static bool ggml_known(int type)
 {
-    return type == TLB_GGML_F32 || type == TLB_GGML_F16 || qformat(type) != nullptr;
+    return type == TLB_GGML_F32 || type == TLB_GGML_F16 || type == TLB_GGML_Q4_0 || type == TLB_GGML_Q4_1 || type == TLB_GGML_Q5_0 ||
+           type == TLB_GGML_Q5_1 || type == TLB_GGML_Q8_0 || type == TLB_GGML_Q8_1 || type == TLB_GGML_Q4_K || type == TLB_GGML_Q6_K;
+}
+
+// Product of the dimensions, or -1 when a dimension is negative or the product leaves int64.
+static int64_t checked_numel(const int64_t *shape, int rank)
+{
+    int64_t n = 1;
+    for (int i = 0; i < rank; i++) {
+        if (shape[i] < 0) return -1;
+        if (shape[i] && n > INT64_MAX / shape[i]) return -1;
+        n *= shape[i];
+    }
+    return n;
 }
 
 static tlb_status map_add(tlb_map *m, const std::string &name, int type, const int64_t *shape, int rank,
                           const void *bytes, size_t nbytes)
 {
     if (m->entries.count(name)) return fail(TLB_ERR_ARG, "tensor '%s' already in the map", name.c_str());
-    int64_t nelem = 1;
-    for (int i = 0; i < rank; i++) nelem *= shape[i];
-    if (ggml_nbytes(type, nelem) != nbytes)
+    const int64_t nelem = checked_numel(shape, rank);
+    if (nelem < 0) return fail(TLB_ERR_SHAPE, "tensor '%s' has a negative or overflowing shape", name.c_str());
+    const size_t need = ggml_raw_nbytes(type, nelem);
+    if ((nelem && !need) || need != nbytes)
         return fail(TLB_ERR_SHAPE, "tensor '%s': %zu bytes do not match type %d x %lld elements", name.c_str(), nbytes, type, (long long)nelem);
     MapEntry e;
     e.type = type;
     e.shape.assign(shape, shape + rank);
-    if (qformat(type)) {
-        if (rank != 2) return fail(TLB_ERR_SHAPE, "quantized tensor '%s' must be 2-D, got %dD", name.c_str(), rank);
-        TLB_TRY(tlb_qtensor_from_gguf_bytes(&e.q, (tlb_ggml_type)type, shape[0], shape[1], bytes, nbytes));
-    } else if (type == TLB_GGML_F32) {
+    if (type == TLB_GGML_F32) {
         TLB_TRY(tlb_tensor_from_host(&e.f32, bytes, TLB_F32, shape, rank));
-    } else {  // F16 -> f32, exact widening (quantized.rs:167-180)
+    } else if (type == TLB_GGML_F16) {  // F16 -> f32, exact widening (quantized.rs:167-180)
         tlb_tensor *h = nullptr;
         TLB_TRY(tlb_tensor_from_host(&h, bytes, TLB_F16, shape, rank));
         tlb_status st = new_tensor(&e.f32, TLB_F32, shape, rank);
@@ -88,6 +86,11 @@ static tlb_status map_add(tlb_map *m, const std::string &name, int type, const i
         }
         tlb_tensor_release(h);
         TLB_TRY(st);
+    } else {
+        // block-quantized: a matrix (the reference's loader gives every tensor a QTensor, gguf.rs:129-190; 1-D
+        // quantized tensors do not occur in model files and are taken as one row)
+        const int64_t n = rank >= 2 ? nelem / std::max<int64_t>(1, shape[rank - 1]) : 1, k = rank >= 1 ? shape[rank - 1] : 1;
+        TLB_TRY(tlb_qtensor_from_gguf_bytes(&e.q, (tlb_ggml_type)type, n, k, bytes, nbytes));
     }
     m->names.push_back(name);
     m->entries[name] = e;
@@ -101,7 +104,7 @@ struct Reader {
     template <typename T> T get()
     {
         T v{};
-        if (off + sizeof(T) > n) { ok = false; return v; }
+        if (off > n || sizeof(T) > n - off) { ok = false; return v; }
         memcpy(&v, p + off, sizeof(T));
         off += sizeof(T);
         return v;
@@ -109,12 +112,12 @@ struct Reader {
     std::string str()
     {
         uint64_t len = get<uint64_t>();
-        if (!ok || off + len > n) { ok = false; return ""; }
+        if (!ok || len > n - off) { ok = false; return ""; }   // subtraction form: a huge length cannot wrap
         std::string s((const char *)p + off, (size_t)len);
         off += len;
         return s;
     }
-    void skip(size_t b) { if (off + b > n) ok = false; else off += b; }
+    void skip(size_t b) { if (b > n - off) ok = false; else off += b; }
 };
 
 static size_t gguf_scalar_size(uint32_t t)
@@ -136,7 +139,7 @@ static bool gguf_skip_value(Reader &r, uint32_t t, uint64_t *uint_val, double *n
     if (t == 8) { std::string v = r.str(); if (str) *str = v; return r.ok; }
     if (num && has_num && t != 9 && r.ok) {
         const size_t sz = gguf_scalar_size(t);
-        if (sz && r.off + sz <= r.n) {
+        if (sz && sz <= r.n - r.off) {
             const uint8_t *q = r.p + r.off;
             *has_num = true;
             switch (t) {
@@ -159,9 +162,14 @@ static bool gguf_skip_value(Reader &r, uint32_t t, uint64_t *uint_val, double *n
         uint32_t et = r.get<uint32_t>();
         uint64_t cnt = r.get<uint64_t>();
         if (!r.ok) return false;
-        if (et == 8) { for (uint64_t i = 0; i < cnt && r.ok; i++) r.str(); return r.ok; }
+        if (et == 8) {
+            if (cnt > r.n - r.off) return false;      // every string takes at least its 8-byte length
+            for (uint64_t i = 0; i < cnt && r.ok; i++) r.str();
+            return r.ok;
+        }
         size_t es = gguf_scalar_size(et);
         if (!es) return false;
+        if (cnt > (r.n - r.off) / es) return false;   // the array cannot be longer than the rest of the file
         r.skip((size_t)cnt * es);
         return r.ok;
     }
@@ -169,7 +177,7 @@ static bool gguf_skip_value(Reader &r, uint32_t t, uint64_t *uint_val, double *n
     if (!s) return false;
     if (uint_val && (t == 0 || t == 2 || t == 4 || t == 10)) {
         uint64_t v = 0;
-        if (r.off + s <= r.n) memcpy(&v, r.p + r.off, s);
+        if (s <= r.n - r.off) memcpy(&v, r.p + r.off, s);
         *uint_val = v;
     }
     r.skip(s);
@@ -292,7 +300,11 @@ tlb_status tlb_gguf_load(tlb_map **out, const char *path)
             inf.name = r.str();
             uint32_t nd = r.get<uint32_t>();
             if (!r.ok || nd > kMaxRank) { r.ok = false; break; }
-            for (uint32_t d = 0; d < nd; d++) inf.shape.push_back((int64_t)r.get<uint64_t>());
+            for (uint32_t d = 0; d < nd; d++) {
+                const uint64_t dim = r.get<uint64_t>();
+                if (dim > (uint64_t)INT64_MAX) r.ok = false;
+                inf.shape.push_back((int64_t)dim);
+            }
             inf.type = r.get<uint32_t>();
             inf.offset = r.get<uint64_t>();
             // trailing 1-dims are trimmed, then GGML's fastest-first order is reversed (gguf.rs:129-136)
@@ -301,14 +313,22 @@ tlb_status tlb_gguf_load(tlb_map **out, const char *path)
             infos.push_back(inf);
         }
         if (!r.ok) { st = fail(TLB_ERR_ARG, "Failed to decode GGUF tensor infos"); break; }
-        uint64_t data_off = (r.off + alignment - 1) / alignment * alignment;
+        if (alignment == 0 || alignment > (1u << 20)) { st = fail(TLB_ERR_ARG, "GGUF alignment %llu is not usable", (unsigned long long)alignment); break; }
+        const uint64_t data_off = (r.off + alignment - 1) / alignment * alignment;
         for (const Info &inf : infos) {
             if (!ggml_known((int)inf.type)) continue;  // unsupported kinds are skipped (gguf.rs:157-177)
-            int64_t nelem = 1;
-            for (int64_t d : inf.shape) nelem *= d;
-            size_t nb = ggml_nbytes((int)inf.type, nelem);
-            if (data_off + inf.offset + nb > fsize) continue;  // "data out of bounds": skipped (gguf.rs:183-186)
-            if (qformat((int)inf.type) && (inf.shape.size() != 2 || inf.shape[1] % 256)) continue;
+            const int64_t nelem = checked_numel(inf.shape.data(), (int)inf.shape.size());
+            if (nelem < 0) continue;
+            const size_t nb = ggml_raw_nbytes((int)inf.type, nelem);
+            if (nelem && !nb) continue;                // not a whole number of blocks
+            // "data out of bounds": skipped (gguf.rs:183-186); subtraction form, so that a huge offset cannot wrap
+            if (data_off > fsize || inf.offset > fsize - data_off || nb > fsize - data_off - inf.offset) continue;
+            if ((int)inf.type != TLB_GGML_F32 && (int)inf.type != TLB_GGML_F16 && !inf.shape.empty()) {
+                // rows must hold whole blocks: K-quants need K % 256 == 0, the 32-blocks K % 32 == 0
+                const int64_t kk = inf.shape.back();
+                const bool k_quant = (int)inf.type == TLB_GGML_Q4_K || (int)inf.type == TLB_GGML_Q6_K;
+                if (kk % (k_quant ? 256 : 32)) continue;
+            }
             st = map_add(m, inf.name, (int)inf.type, inf.shape.data(), (int)inf.shape.size(), r.p + data_off + inf.offset, nb);
             if (st != TLB_OK) break;
         }
@@ -344,9 +364,22 @@ tlb_status tlb_map_get_quantized(tlb_qtensor **out, tlb_map *m, const char *name
     if (!m || !name) return fail(TLB_ERR_NULL, "null argument");
     auto it = m->entries.find(name);
     if (it == m->entries.end()) return fail(TLB_ERR_ARG, "Tensor '%s' not found in map", name);
-    if (!it->second.q) return fail(TLB_ERR_TYPE, "Tensor '%s' has GGML type %d, which has no quantized kernel", name, it->second.type);
-    tlb_qtensor_retain(it->second.q);
-    *out = it->second.q;
+    MapEntry &e = it->second;
+    if (!e.q) {
+        // F32 / F16 tensor: the reference wraps any type in a QTensor (tensor_map.rs:279) and multiplies it through the
+        // dequantise + matmul route (system.rs:236-264).  The dense QTensor shares the f32 data the map already holds.
+        if (e.shape.empty()) return fail(TLB_ERR_SHAPE, "Tensor '%s' is a scalar", name);
+        tlb_qtensor *q = new tlb_qtensor();
+        q->type = e.type;
+        q->k = e.shape.back();
+        q->n = q->k ? e.f32->numel() / q->k : 0;
+        int64_t shp[2] = {q->n, q->k};
+        tlb_status st = new_view(&q->dense, e.f32, shp, 2, 0);
+        if (st != TLB_OK) { delete q; return st; }
+        e.q = q;
+    }
+    tlb_qtensor_retain(e.q);
+    *out = e.q;
     return TLB_OK;
 }
 
@@ -358,7 +391,13 @@ tlb_status tlb_map_get(tlb_tensor **out, tlb_map *m, const char *name)
     auto it = m->entries.find(name);
     if (it == m->entries.end()) return fail(TLB_ERR_ARG, "Tensor '%s' not found in map", name);
     MapEntry &e = it->second;
-    if (!e.f32) TLB_TRY(tlb_qtensor_dequantize(&e.f32, e.q));  // cached, as QTensor::cache does
+    if (!e.f32) {   // cached, as QTensor::cache does
+        tlb_tensor *d = nullptr;
+        TLB_TRY(tlb_qtensor_dequantize(&d, e.q));
+        tlb_status st = new_view(&e.f32, d, e.shape.data(), (int)e.shape.size(), 0);   // the tensor's own shape (1-D stays 1-D)
+        tlb_tensor_release(d);
+        TLB_TRY(st);
+    }
     tlb_tensor_retain(e.f32);
     *out = e.f32;
     return TLB_OK;

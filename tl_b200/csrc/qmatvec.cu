@@ -516,6 +516,8 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     if (job.k <= 0 || job.k % 256) return fail(TLB_ERR_SHAPE, "K = %lld must be a positive multiple of 256", (long long)job.k);
     if (job.n_w < 1 || job.n_w > 3) return fail(TLB_ERR_ARG, "1..3 weight tensors per launch");
     if (job.prologue != PRO_PLAIN && job.m != 1) return fail(TLB_ERR_ARG, "fused prologues take one activation row");
+    if (((uintptr_t)job.x | (uintptr_t)job.x2 | (uintptr_t)job.norm_w | (uintptr_t)job.emb_table) & 15)
+        return fail(TLB_ERR_ARG, "matvec activations and norm weights must be 16-byte aligned");
     MvParams p = {};
     int64_t tiles = 0;
     for (int i = 0; i < 3; i++) {
@@ -658,25 +660,51 @@ extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, 
     TLB_TRY(new_tensor(out, TLB_F32, oshape, x->rank));
     if (m * w->n == 0) return TLB_OK;
     tlb_status st = TLB_OK;
-    if (prefer_gemm(m, w) && ((uintptr_t)x->f32() & 15) == 0) {
-        // many rows (prompt processing): tensor-core GEMM, the weight is read once per 256 rows
-        st = launch_qgemm(w, x->f32(), m, (*out)->f32());
+    if (!w->tiled()) {
+        // dense weight: x . W^T through the f32 matmul over the cached transpose, the reference's route for types
+        // without a fused kernel (crates/tl_runtime/src/system.rs:236-264)
+        tlb_qtensor *wm = const_cast<tlb_qtensor *>(w);
+        {
+            std::lock_guard<std::mutex> lk(wm->mu);
+            if (!wm->dense_t) {
+                const int64_t tshape[2] = {w->k, w->n}, tstr[2] = {1, w->k};
+                st = new_tensor(&wm->dense_t, TLB_F32, tshape, 2);
+                if (st == TLB_OK) st = launch_copy_strided(w->dense->f32(), wm->dense_t->f32(), tshape, tstr, 2, w->n * w->k, 0);
+                if (st != TLB_OK) { tlb_tensor_release(wm->dense_t); wm->dense_t = nullptr; }
+            }
+        }
+        if (st == TLB_OK) st = launch_matmul(x->f32(), w->dense_t->f32(), (*out)->f32(), 1, m, k, w->n, false);
         if (st != TLB_OK) { tlb_tensor_release(*out); *out = nullptr; }
         return st;
     }
-    for (int64_t m0 = 0; m0 < m && st == TLB_OK; m0 += 4) {   // the weight stream is repeated per group of 4 rows
-        MatvecJob job;
-        job.n_w = 1;
-        job.w[0] = w->dev();
-        job.n_tiles[0] = w->n_tiles;
-        job.n_rows[0] = w->n;
-        job.out[0] = (*out)->f32() + m0 * w->n;
-        job.type = w->type;
-        job.k = k;
-        job.m = (int)std::min<int64_t>(4, m - m0);
-        job.x = x->f32() + m0 * k;
-        st = launch_qmatvec(job);
+    // The kernels read the activation with 16-byte loads; a view that starts at an odd element (tlb_narrow makes
+    // zero-copy views at any offset) is first copied to an aligned buffer.
+    const tlb_tensor *xa = x;
+    tlb_tensor *xcopy = nullptr;
+    if ((uintptr_t)x->f32() & 15) {
+        st = tlb_tensor_clone(&xcopy, x);
+        if (st != TLB_OK) { tlb_tensor_release(*out); *out = nullptr; return st; }
+        xa = xcopy;
     }
+    if (prefer_gemm(m, w)) {
+        // many rows (prompt processing): tensor-core GEMM, the weight is read once per 256 rows
+        st = launch_qgemm(w, xa->f32(), m, (*out)->f32());
+    } else {
+        for (int64_t m0 = 0; m0 < m && st == TLB_OK; m0 += 4) {   // the weight stream is repeated per group of 4 rows
+            MatvecJob job;
+            job.n_w = 1;
+            job.w[0] = w->dev();
+            job.n_tiles[0] = w->n_tiles;
+            job.n_rows[0] = w->n;
+            job.out[0] = (*out)->f32() + m0 * w->n;
+            job.type = w->type;
+            job.k = k;
+            job.m = (int)std::min<int64_t>(4, m - m0);
+            job.x = xa->f32() + m0 * k;
+            st = launch_qmatvec(job);
+        }
+    }
+    tlb_tensor_release(xcopy);   // stream-ordered pool: the storage outlives the kernels already enqueued
     if (st != TLB_OK) { tlb_tensor_release(*out); *out = nullptr; }
     return st;
 }

@@ -16,6 +16,8 @@
 #include "qlayout.cuh"
 #include "tlb_internal.h"
 
+#include <algorithm>
+
 namespace tlb {
 
 static const QFormat kFormats[] = {
@@ -187,9 +189,138 @@ tlb_status launch_dequant_tiled(int type, const uint8_t *tiled, float *out, int6
     return TLB_OK;
 }
 
+// ---- raw GGUF blocks -> f32 (dense tensors) -------------------------------------------------
+// The same expressions as above on the untiled bytes, plus the block types the tiled kernels do not take.
+// Q4_1 / Q5_0 / Q5_1 / Q8_1 have no dequantiser in the reference (crates/tl_runtime/src/quantized.rs:108); they
+// follow the published GGML block definitions: integer to f32, one multiply, then one add, never fused.
+size_t ggml_raw_nbytes(int type, int64_t nelem)
+{
+    if (nelem < 0) return 0;
+    auto blocks = [&](int per, int bytes) -> size_t { return nelem % per ? 0 : (size_t)(nelem / per) * bytes; };
+    switch (type) {
+    case TLB_GGML_F32: return (size_t)nelem * 4;
+    case TLB_GGML_F16: return (size_t)nelem * 2;
+    case TLB_GGML_Q4_0: return blocks(32, 18);
+    case TLB_GGML_Q4_1: return blocks(32, 20);
+    case TLB_GGML_Q5_0: return blocks(32, 22);
+    case TLB_GGML_Q5_1: return blocks(32, 24);
+    case TLB_GGML_Q8_0: return blocks(32, 34);
+    case TLB_GGML_Q8_1: return blocks(32, 36);
+    case TLB_GGML_Q4_K: return blocks(256, 144);
+    case TLB_GGML_Q6_K: return blocks(256, 210);
+    default: return 0;
+    }
+}
+
+// one thread per 32 weights
+__global__ void dequant_raw_kernel(int type, const uint8_t *__restrict__ raw, float *__restrict__ out, int64_t nelem)
+{
+    const int64_t total = nelem / 32;
+    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        float *o = out + idx * 32;
+        if (type == TLB_GGML_F32) {
+            for (int j = 0; j < 32; j++) o[j] = reinterpret_cast<const float *>(raw)[idx * 32 + j];
+        } else if (type == TLB_GGML_F16) {
+            for (int j = 0; j < 32; j++) o[j] = __half2float(reinterpret_cast<const __half *>(raw)[idx * 32 + j]);
+        } else if (type == TLB_GGML_Q4_0) {
+            const uint8_t *p = raw + idx * 18;
+            const float d = f16_bits_to_f32(p[0], p[1]);
+            for (int j = 0; j < 16; j++) {
+                o[j] = __fmul_rn(d, (float)((int)(p[2 + j] & 15) - 8));
+                o[j + 16] = __fmul_rn(d, (float)((int)(p[2 + j] >> 4) - 8));
+            }
+        } else if (type == TLB_GGML_Q8_0) {
+            const uint8_t *p = raw + idx * 34;
+            const float d = f16_bits_to_f32(p[0], p[1]);
+            for (int j = 0; j < 32; j++) o[j] = __fmul_rn(d, (float)(int8_t)p[2 + j]);
+        } else if (type == TLB_GGML_Q8_1) {
+            const uint8_t *p = raw + idx * 36;
+            const float d = f16_bits_to_f32(p[0], p[1]);
+            for (int j = 0; j < 32; j++) o[j] = __fmul_rn(d, (float)(int8_t)p[4 + j]);
+        } else if (type == TLB_GGML_Q4_1) {
+            const uint8_t *p = raw + idx * 20;
+            const float d = f16_bits_to_f32(p[0], p[1]), m = f16_bits_to_f32(p[2], p[3]);
+            for (int j = 0; j < 16; j++) {
+                o[j] = __fadd_rn(__fmul_rn(d, (float)(p[4 + j] & 15)), m);
+                o[j + 16] = __fadd_rn(__fmul_rn(d, (float)(p[4 + j] >> 4)), m);
+            }
+        } else if (type == TLB_GGML_Q5_0 || type == TLB_GGML_Q5_1) {
+            const bool with_min = type == TLB_GGML_Q5_1;
+            const uint8_t *p = raw + idx * (with_min ? 24 : 22);
+            const float d = f16_bits_to_f32(p[0], p[1]), m = with_min ? f16_bits_to_f32(p[2], p[3]) : 0.f;
+            const uint8_t *qhp = p + (with_min ? 4 : 2), *qs = qhp + 4;
+            const uint32_t qh = (uint32_t)qhp[0] | ((uint32_t)qhp[1] << 8) | ((uint32_t)qhp[2] << 16) | ((uint32_t)qhp[3] << 24);
+            for (int j = 0; j < 16; j++) {
+                const int x0 = (int)(qs[j] & 15) | (int)(((qh >> j) & 1u) << 4);
+                const int x1 = (int)(qs[j] >> 4) | (int)(((qh >> (j + 16)) & 1u) << 4);
+                if (with_min) {
+                    o[j] = __fadd_rn(__fmul_rn(d, (float)x0), m);
+                    o[j + 16] = __fadd_rn(__fmul_rn(d, (float)x1), m);
+                } else {
+                    o[j] = __fmul_rn(d, (float)(x0 - 16));
+                    o[j + 16] = __fmul_rn(d, (float)(x1 - 16));
+                }
+            }
+        }
+    }
+}
+
+tlb_status launch_dequant_raw(int type, const uint8_t *raw, float *out, int64_t nelem)
+{
+    if (type == TLB_GGML_Q4_K || type == TLB_GGML_Q6_K) return fail(TLB_ERR_TYPE, "K-quants are dequantised from the tiled layout");
+    if (nelem % 32) return fail(TLB_ERR_SHAPE, "dense dequantisation works on whole blocks of 32");
+    if (nelem == 0) return TLB_OK;
+    const int64_t total = nelem / 32;
+    const int blocks = (int)std::min<int64_t>((total + 127) / 128, 148 * 32);
+    dequant_raw_kernel<<<blocks, 128, 0, ctx()->stream>>>(type, raw, out, nelem);
+    count_launch();
+    TLB_CUDA(cudaGetLastError());
+    return TLB_OK;
+}
+
 }  // namespace tlb
 
 using namespace tlb;
+
+// A dense QTensor: the bytes go up once, are dequantised to f32 [n, k] and dropped.
+static tlb_status qtensor_dense(tlb_qtensor **out, int type, int64_t n, int64_t k, const void *bytes, size_t nbytes)
+{
+    const int64_t nelem = n * k;
+    const size_t need = ggml_raw_nbytes(type, nelem);
+    if (nelem && !need) return fail(TLB_ERR_SHAPE, "K = %lld does not hold whole blocks of GGML type %d", (long long)k, type);
+    if (type != TLB_GGML_F32 && type != TLB_GGML_F16 && k % 32) return fail(TLB_ERR_SHAPE, "K = %lld must be a multiple of 32 for GGML type %d", (long long)k, type);
+    if (nbytes != need) return fail(TLB_ERR_SHAPE, "data size mismatch: expected %zu bytes, got %zu", need, nbytes);
+    if (need && !bytes) return fail(TLB_ERR_NULL, "null data");
+    tlb_qtensor *q = new tlb_qtensor();
+    q->type = type; q->n = n; q->k = k;
+    int64_t shape[2] = {n, k};
+    tlb_status st = new_tensor(&q->dense, TLB_F32, shape, 2);
+    if (st == TLB_OK && need) {
+        cudaStream_t s = ctx()->stream;
+        if (type == TLB_GGML_F32) {
+            cudaError_t e = cudaMemcpyAsync(q->dense->data(), bytes, need, cudaMemcpyHostToDevice, s);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+            if (e != cudaSuccess) st = cuda_fail(e, "qtensor upload");
+        } else if (nelem % 32) {     // F16 with a ragged element count: widened on the host (exact)
+            std::vector<float> w((size_t)nelem);
+            for (int64_t i = 0; i < nelem; i++) w[(size_t)i] = __half2float(reinterpret_cast<const __half *>(bytes)[i]);
+            cudaError_t e = cudaMemcpyAsync(q->dense->data(), w.data(), w.size() * 4, cudaMemcpyHostToDevice, s);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+            if (e != cudaSuccess) st = cuda_fail(e, "qtensor upload");
+        } else {
+            void *tmp = nullptr;
+            cudaError_t e = cudaMallocAsync(&tmp, need, s);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(tmp, bytes, need, cudaMemcpyHostToDevice, s);
+            if (e == cudaSuccess) st = launch_dequant_raw(type, (const uint8_t *)tmp, q->dense->f32(), nelem);
+            if (tmp) cudaFreeAsync(tmp, s);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+            if (e != cudaSuccess) st = cuda_fail(e, "qtensor upload");
+        }
+    }
+    if (st != TLB_OK) { tlb_tensor_release(q->dense); delete q; return st; }
+    *out = q;
+    return TLB_OK;
+}
 
 extern "C" {
 
@@ -200,9 +331,13 @@ tlb_status tlb_qtensor_from_gguf_bytes(tlb_qtensor **out, tlb_ggml_type type, in
     *out = nullptr;
     if (!ensure_init()) return TLB_ERR_DEVICE;
     const QFormat *f = qformat(type);
-    if (!f) return fail(TLB_ERR_TYPE, "GGML type %d has no quantized kernel (supported: Q4_0, Q8_0, Q4_K, Q6_K)", (int)type);
     if (n < 0 || k < 0) return fail(TLB_ERR_SHAPE, "negative shape");
-    if (k % 256 != 0) return fail(TLB_ERR_SHAPE, "K = %lld must be a multiple of 256 for the tiled layout", (long long)k);
+    const bool dense_type = type == TLB_GGML_F32 || type == TLB_GGML_F16 || type == TLB_GGML_Q4_1 || type == TLB_GGML_Q5_0 ||
+                            type == TLB_GGML_Q5_1 || type == TLB_GGML_Q8_1;
+    if (!f && !dense_type)
+        return fail(TLB_ERR_TYPE, "GGML type %d is not supported (F32, F16, Q4_0, Q4_1, Q5_0, Q5_1, Q8_0, Q8_1, Q4_K, Q6_K)", (int)type);
+    if (dense_type || (k % 256 != 0 && f->raw_block == 32)) return qtensor_dense(out, type, n, k, bytes, nbytes);
+    if (k % 256 != 0) return fail(TLB_ERR_SHAPE, "K = %lld must be a multiple of 256 for GGML type %d", (long long)k, (int)type);
     size_t need = (size_t)n * (k / f->raw_block) * f->raw_block_bytes;
     if (nbytes != need) return fail(TLB_ERR_SHAPE, "data size mismatch: expected %zu bytes, got %zu", need, nbytes);
     if (need && !bytes) return fail(TLB_ERR_NULL, "null data");
@@ -245,7 +380,9 @@ tlb_status tlb_qtensor_release(tlb_qtensor *q)
 {
     if (!q) return TLB_OK;
     if (q->rc.fetch_sub(1) == 1) {
-        storage_release(q->st);
+        if (q->st) storage_release(q->st);
+        tlb_tensor_release(q->dense);
+        tlb_tensor_release(q->dense_t);
         delete q;
     }
     return TLB_OK;
@@ -264,6 +401,7 @@ tlb_status tlb_qtensor_info(const tlb_qtensor *q, int *type, int64_t *n, int64_t
 tlb_status tlb_qtensor_dequantize(tlb_tensor **out, const tlb_qtensor *q)
 {
     if (!out || !q) return fail(TLB_ERR_NULL, "null argument");
+    if (!q->tiled()) return tlb_tensor_clone(out, q->dense);
     int64_t shape[2] = {q->n, q->k};
     TLB_TRY(new_tensor(out, TLB_F32, shape, 2));
     tlb_status s = launch_dequant_tiled(q->type, q->dev(), (*out)->f32(), q->n, q->k);

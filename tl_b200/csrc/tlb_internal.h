@@ -101,9 +101,17 @@ struct tlb_qtensor {
     int type = 0;
     int64_t n = 0, k = 0;       // logical rows / cols
     int64_t n_tiles = 0, upt = 0; // 16-row tiles, units per tile (k/256)
-    tlb::Storage *st = nullptr; // tiled device bytes
+    tlb::Storage *st = nullptr; // tiled device bytes; null for a dense tensor
+    // Dense form, for what the tiled kernels do not take (F32, F16, Q4_1, Q5_0, Q5_1, Q8_1, and Q4_0 / Q8_0 rows that
+    // are not a multiple of 256 long): the weight dequantised once to f32 [n, k], and its transpose [k, n] built by
+    // the first matmul - the two caches QTensor keeps on the reference's fallback route
+    // (crates/tl_runtime/src/system.rs:195-217,236-264).
+    tlb_tensor *dense = nullptr;
+    tlb_tensor *dense_t = nullptr;
+    std::mutex mu;              // guards the lazy dense_t
+    bool tiled() const { return st != nullptr; }
     uint8_t *dev() const { return (uint8_t *)st->ptr; }
-    uint64_t nbytes() const { return (uint64_t)n_tiles * upt * tlb::qformat(type)->unit_bytes; }
+    uint64_t nbytes() const { return tiled() ? (uint64_t)n_tiles * upt * tlb::qformat(type)->unit_bytes : (uint64_t)n * k * 4; }
 };
 
 namespace tlb {
@@ -136,6 +144,9 @@ tlb_status launch_prefill_attention(const float *q, const void *kcache, const vo
                                     int KVH, int D, int max_seq, int pos0, float scale);
 tlb_status launch_repack(int type, const uint8_t *raw, uint8_t *tiled, int64_t n, int64_t k);
 tlb_status launch_dequant_tiled(int type, const uint8_t *tiled, float *out, int64_t n, int64_t k);
+// raw GGUF blocks of any supported type -> f32, same expressions as the tiled dequantiser; nelem weights
+size_t ggml_raw_nbytes(int type, int64_t nelem);   // 0: unknown type or nelem not a whole number of blocks
+tlb_status launch_dequant_raw(int type, const uint8_t *raw, float *out, int64_t nelem);
 tlb_status launch_interleave8(int type, const uint8_t *a, const uint8_t *b, uint8_t *dst, int64_t n, int64_t k);
 
 // qmatvec.cu ---------------------------------------------------------------------------

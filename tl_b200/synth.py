@@ -13,8 +13,11 @@ import zlib
 import numpy as np
 
 F32, F16, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 8, 12, 14
-TYPE_NAMES = {F32: "F32", F16: "F16", Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K"}
-BLOCK = {F32: (1, 4), F16: (1, 2), Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210)}
+Q4_1, Q5_0, Q5_1, Q8_1 = 3, 6, 7, 9
+TYPE_NAMES = {F32: "F32", F16: "F16", Q4_0: "Q4_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q6_K: "Q6_K",
+              Q4_1: "Q4_1", Q5_0: "Q5_0", Q5_1: "Q5_1", Q8_1: "Q8_1"}
+BLOCK = {F32: (1, 4), F16: (1, 2), Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q6_K: (256, 210),
+         Q4_1: (32, 20), Q5_0: (32, 22), Q5_1: (32, 24), Q8_1: (32, 36)}
 
 
 def type_nbytes(t, nelem):
@@ -43,6 +46,8 @@ def random_quant(t, n, k, rng, scale_sigma=None):
     nblocks = nelem // blk
     if t == F32:
         return rng.standard_normal(nelem, dtype=np.float32).view(np.uint8).reshape(n, -1)
+    if t == F16:
+        return (rng.standard_normal(nelem, dtype=np.float32) * np.float32(scale_sigma or 0.02)).astype(np.float16).view(np.uint8).reshape(n, -1)
     out = rng.integers(0, 256, size=(nblocks, nb), dtype=np.uint8)
     if t == Q4_0:
         d = _f16_abs_normal(rng, nblocks, scale_sigma or 0.02, 8.0)
@@ -57,6 +62,10 @@ def random_quant(t, n, k, rng, scale_sigma=None):
         out[:, 2:4] = _f16_abs_normal(rng, nblocks, scale_sigma or 0.01).view(np.uint8).reshape(-1, 2)
     elif t == Q6_K:
         out[:, 208:210] = _f16_abs_normal(rng, nblocks, scale_sigma or 0.01).view(np.uint8).reshape(-1, 2)
+    elif t in (Q4_1, Q5_0, Q5_1, Q8_1):  # f16 scale first; Q4_1 / Q5_1 / Q8_1 carry a second f16 (min, or d * sum)
+        out[:, 0:2] = _f16_abs_normal(rng, nblocks, scale_sigma or 0.01).view(np.uint8).reshape(-1, 2)
+        if t != Q5_0:
+            out[:, 2:4] = (rng.standard_normal(nblocks, dtype=np.float32) * np.float32(scale_sigma or 0.01)).astype(np.float16).view(np.uint8).reshape(-1, 2)
     else:
         raise ValueError(t)
     return out.reshape(n, -1)
