@@ -117,8 +117,10 @@ tlb_status tlb_argmax(tlb_tensor **out, const tlb_tensor *x, tlb_tie_rule tie); 
  * fixed 16 KB array inside the library, so nothing is allocated or freed.  Limits: x holds at most
  * 4,194,304 elements (TLB_ERR_ARG beyond that; tlb_argmax has no limit); tlb_init must have run
  * (TLB_ERR_DEVICE otherwise).  The first call on a device looks up the array's address and should
- * be made outside any stream capture.  All calls share the array: they are ordered on the library's
- * stream, and nothing in the array needs clearing between calls. */
+ * be made outside any stream capture.  All calls share the array and each call is two launches: they go
+ * to the library's one stream under a host lock, so calls from one thread or from several never interleave;
+ * GPU work that touched the array from any other stream would race with them.  Nothing in the array needs
+ * clearing between calls. */
 tlb_status tlb_argmax_into(tlb_tensor *out, const tlb_tensor *x, tlb_tie_rule tie);
 /* temp <= 0: greedy.  temp > 0: the reference CUDA path ignores temp/top_p and returns the argmax
  * (crates/tl_cuda/src/ffi_ops.rs:880-884); this entry point does the same. */
@@ -198,6 +200,41 @@ tlb_status tlb_graph_replay(tlb_graph *g);
 int64_t    tlb_graph_node_count(const tlb_graph *g);
 tlb_status tlb_graph_destroy(tlb_graph *g);
 
+/* ---- tensor parallelism over the GPUs of one node (no counterpart in the reference: crates/tl_cuda/src/device.rs:21-27
+ * binds one device, the collectives of crates/tl_cuda/src/ffi_ops.rs:726-730 are stubs) ---------------------------------
+ * One process per GPU.  Rank 0 makes a 128-byte id (tlb_tp_unique_id), the host passes it to the other processes, and
+ * every rank joins with tlb_tp_init after tlb_init.  Joining is bounded: a rank that never arrives makes the others return
+ * TLB_ERR_DEVICE after join_timeout_s (<= 0: 60 s) with the communicator aborted.  tlb_tp_poll reports an asynchronous
+ * failure of an earlier collective (a peer that died) without blocking. */
+tlb_status tlb_tp_unique_id(void *id_out, size_t id_bytes);
+tlb_status tlb_tp_init(const void *id, size_t id_bytes, int rank, int size, double join_timeout_s);
+tlb_status tlb_tp_poll(void);
+tlb_status tlb_tp_shutdown(void);
+int        tlb_tp_rank(void);
+int        tlb_tp_size(void);
+/* f32 sum over the ranks, in place, on the library's stream */
+tlb_status tlb_allreduce(tlb_tensor *t);
+/* Optional second transport for the small sums of decoding (up to 65,536 floats): a one-shot all-reduce in which every
+ * rank stores its share into a slot of every peer's memory over NVLink and then reads only its own memory.  Each rank
+ * exports a 64-byte CUDA IPC handle, the host gathers them in rank order, each rank attaches; all ranks must have
+ * exported before any attaches and attached before the next all-reduce.  Sums are bitwise equal on every rank.  A peer
+ * that does not write within about a second makes the kernel give up (TLB_ERR_DEVICE at the next tlb_sync). */
+tlb_status tlb_tp_p2p_export(void *handle_out, size_t handle_bytes);
+tlb_status tlb_tp_p2p_attach(const void *handles, int n_handles);
+tlb_status tlb_tp_p2p_disable(void);
+/* Which way a tensor is split, by its GGUF name: 0 replicated, 1 along rows (attn_q/k/v, ffn_gate/up, output.weight),
+ * 2 along columns (attn_output, ffn_down). */
+int        tlb_tp_split_kind(const char *name);
+/* Host-side byte slice of a row-major [n, k] GGUF tensor for shard `rank` of `size`: rows [rank n/size, ...) for kind 1
+ * (one contiguous range), for kind 2 the blocks of columns [rank k/size, ...) of every row (k/size must hold whole blocks).
+ * out == NULL only reports the shard's shape and byte count.  No device is needed. */
+tlb_status tlb_tp_shard_bytes(int kind, tlb_ggml_type type, int64_t n, int64_t k, const void *bytes, size_t nbytes, int rank, int size,
+                              void *out, size_t out_cap, int64_t *n_out, int64_t *k_out, size_t *out_bytes);
+/* tlb_map_add / tlb_gguf_load keeping only this rank's shard of every split tensor */
+tlb_status tlb_map_add_tp(tlb_map *m, const char *name, tlb_ggml_type type, const int64_t *shape, int rank, const void *bytes, size_t nbytes,
+                          int tp_rank, int tp_size);
+tlb_status tlb_gguf_load_tp(tlb_map **out, const char *path, int tp_rank, int tp_size);
+
 /* ---- fused decode session ---------------------------------------------------------------
  * Runs the op sequence of examples/apps/llama3/chatbot_llama3.tl:66-125,220-236 (and
  * examples/apps/tinyllama/chatbot.tl:50-113) for one new token as a chain of fused kernels
@@ -209,8 +246,10 @@ typedef struct {
     int32_t kv_f16;                       /* 1: f16 KV cache; 0: f32 (reference) */
     int32_t max_seq;
     int32_t tie_rule;                     /* tlb_tie_rule for the greedy token */
-    /* tensor parallelism: this process holds shard tp_rank of tp_size (column split of q/k/v/gate/up,
-     * row split of attn_output/ffn_down); 1/0 for a single GPU */
+    /* tensor parallelism (one process per GPU): this process holds shard tp_rank of tp_size - whole heads of
+     * q / k / v, hidden units of gate / up and vocabulary rows of the head (row split), the matching inner-dimension
+     * slices of attn_output / ffn_down (column split) - loaded with tlb_gguf_load_tp / tlb_map_add_tp, after
+     * tlb_tp_init; the model sizes above stay those of the WHOLE model.  0 or 1 / 0 for a single GPU. */
     int32_t tp_size, tp_rank;
 } tlb_decoder_cfg;
 

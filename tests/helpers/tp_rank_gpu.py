@@ -1,0 +1,139 @@
+"""One rank of the 2-GPU tensor-parallel parity test (started by tests/test_gpu_tp.py, one process per GPU).
+
+A Llama-3-70B-shaped model cut to 2 layers and a 32k vocabulary (d 8192, 64 / 8 heads of 128, FFN 28672, Q4_K + Q6_K
+head, f16 KV with 300 cached rows), sharded over the ranks; rank 0 compares every step's gathered logits and greedy
+token with the oracle's unsharded model.  First over NCCL, then again over the peer-memory all-reduce.
+"""
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import tl_b200 as tl  # noqa: E402
+from oracle import oracle  # noqa: E402
+from tl_b200 import synth  # noqa: E402
+
+
+def relerr(a, b):
+    return float(np.max(np.abs(a - b)) / max(np.max(np.abs(b)), 1e-30))
+
+
+def main():
+    mode = sys.argv[1] if len(sys.argv) > 1 else "parity"
+    dist.init_process_group("gloo", init_method="env://")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    tl.init(rank)
+    if mode == "absent":
+        # rank 1 leaves before joining: rank 0's join must give up at its deadline
+        if rank == 1:
+            dist.barrier()
+            print("rank 1 left without joining")
+            return
+        uid = tl.tp_unique_id()
+        t0 = time.time()
+        try:
+            tl.tp_init(uid, 0, world, join_timeout_s=4.0)
+            print("FAIL: joined alone")
+            sys.exit(1)
+        except tl.TlbError as e:
+            assert e.code == 2 and "did not answer" in str(e), e
+        assert time.time() - t0 < 60
+        # the device is still usable afterwards
+        x = tl.Tensor.from_numpy(np.arange(8, dtype=np.float32))
+        assert x.scale(2.0).numpy()[7] == 14.0
+        dist.barrier()
+        print("rank 0: bounded join ok")
+        return
+
+    box = [tl.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    tl.tp_init(box[0], rank, world, join_timeout_s=120.0)
+
+    cfg = dict(synth.LLAMA3_70B, n_layers=2, vocab=32064)
+    tens = synth.llama_tensors(cfg, 5, synth.Q4_K, synth.Q6_K)
+    wmap = tl.map_from_tensors(tens, rank, world)
+    ctx = 300
+    rng = np.random.default_rng(9)
+    kvd = cfg["n_kv_heads"] * cfg["head_dim"]
+    kv = [(rng.standard_normal((ctx, kvd)).astype(np.float16).astype(np.float32),
+           rng.standard_normal((ctx, kvd)).astype(np.float16).astype(np.float32)) for _ in range(cfg["n_layers"])]
+
+    def session():
+        d = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 64, tp_size=world, tp_rank=rank)
+        for layer, (k, v) in enumerate(kv):
+            d.kv_write(layer, 0, k, v)
+        return d
+
+    ref = None
+    if rank == 0:
+        ref = oracle.Llama(dict(cfg, kv_f16=1, max_seq=ctx + 64), {k: (t, d) for k, (t, d, s) in tens.items()})
+        for layer, (k, v) in enumerate(kv):
+            for p in range(ctx):
+                ref.kv_write(layer, p, k[p], v[p])
+
+    steps = 8
+    dec = session()
+    tok, pos, worst, want, got, logits_nccl = 777, ctx, 0.0, [], [], []
+    for _ in range(steps):
+        nxt = dec.step(tok, pos)
+        lg = dec.logits()                      # gathers the shards' rows: every rank calls it
+        logits_nccl.append(lg)
+        if rank == 0:
+            rl = ref.forward([tok], pos)
+            worst = max(worst, relerr(lg, rl))
+            want.append(oracle.argmax_last(rl))
+        got.append(nxt)
+        box = [want[-1] if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        assert nxt == box[0], (rank, nxt, box[0])      # every rank picked the oracle's token
+        tok, pos = box[0], pos + 1
+    if rank == 0:
+        assert worst < 2e-2, worst
+        print("nccl: worst logit error %.2e, tokens %s" % (worst, got))
+    st = dec.stats(ctx)
+    assert st["kernels_per_step"] == 5 * 2 + 3
+
+    # the same steps over the peer-memory all-reduce
+    handles = [None] * world
+    dist.all_gather_object(handles, tl.tp_p2p_export())
+    tl.tp_p2p_attach(handles)
+    dist.barrier()
+    dec2 = session()
+    tok, pos = 777, ctx
+    for i in range(steps):
+        nxt = dec2.step(tok, pos)
+        lg = dec2.logits()
+        assert nxt == got[i], (rank, i, nxt, got[i])
+        assert relerr(lg, logits_nccl[i]) < 1e-4       # only the order of the cross-rank sum differs
+        tok, pos = nxt, pos + 1
+    # generate: device-side feedback, one graph replay per token, every rank the same tokens
+    dec3 = session()
+    gen = dec3.generate(777, ctx, steps)
+    assert gen == got, (rank, gen, got)
+    # timing, for the record: graph replays over both transports
+    for name, use_p2p in (("p2p", True), ("nccl", False)):
+        if not use_p2p:
+            tl.tp_p2p_disable()
+        d4 = session()
+        d4.generate(777, ctx, 4)
+        tl.sync()
+        dist.barrier()
+        t0 = time.perf_counter()
+        d4.generate(777, ctx + 4, 32)
+        tl.sync()
+        dt = (time.perf_counter() - t0) / 32
+        if rank == 0:
+            print("%s: %.1f us per token (2 layers + head, %d ranks)" % (name, dt * 1e6, world))
+    tl.tp_poll()
+    dist.barrier()
+    tl.tp_shutdown()
+    print("rank %d ok" % rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -32,6 +32,58 @@ def kernel_launches():
     return int(lib().tlb_kernel_launches())
 
 
+# ---- tensor parallelism (one process per GPU) ---------------------------------------------------------------
+def tp_unique_id():
+    """128-byte communicator id; rank 0 makes it and the host passes it to the other ranks."""
+    buf = (C.c_uint8 * 128)()
+    check(lib().tlb_tp_unique_id(buf, 128))
+    return bytes(buf)
+
+
+def tp_init(uid, rank, size, join_timeout_s=60.0):
+    check(lib().tlb_tp_init(uid, len(uid), rank, size, float(join_timeout_s)))
+
+
+def tp_poll():
+    check(lib().tlb_tp_poll())
+
+
+def tp_shutdown():
+    check(lib().tlb_tp_shutdown())
+
+
+def tp_p2p_export():
+    buf = (C.c_uint8 * 64)()
+    check(lib().tlb_tp_p2p_export(buf, 64))
+    return bytes(buf)
+
+
+def tp_p2p_attach(handles):
+    """handles: the 64-byte export of every rank, in rank order."""
+    blob = b"".join(handles)
+    check(lib().tlb_tp_p2p_attach(blob, len(handles)))
+
+
+def tp_p2p_disable():
+    check(lib().tlb_tp_p2p_disable())
+
+
+def tp_split_kind(name):
+    return int(lib().tlb_tp_split_kind(name.encode()))
+
+
+def tp_shard_bytes(kind, t, n, k, data, rank, size):
+    """Host-side shard of a row-major [n, k] GGUF tensor: (bytes ndarray, (n_shard, k_shard)).  Needs no device."""
+    data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+    sn, sk, sb = C.c_int64(), C.c_int64(), C.c_size_t()
+    src = data.ctypes.data_as(C.c_void_p)
+    check(lib().tlb_tp_shard_bytes(kind, t, n, k, src, data.size, rank, size, None, 0, C.byref(sn), C.byref(sk), C.byref(sb)))
+    out = np.empty(sb.value, dtype=np.uint8)
+    check(lib().tlb_tp_shard_bytes(kind, t, n, k, src, data.size, rank, size, out.ctypes.data_as(C.c_void_p), out.size,
+                                   C.byref(sn), C.byref(sk), C.byref(sb)))
+    return out, (sn.value, sk.value)
+
+
 def _shape_arg(shape):
     arr = (C.c_int64 * max(1, len(shape)))(*shape)
     return arr, len(shape)
@@ -219,6 +271,18 @@ class TensorMap:
         shp, rank = _shape_arg(shape)
         check(lib().tlb_map_add(self.h, name.encode(), t, shp, rank, data.ctypes.data_as(C.c_void_p), data.size))
 
+    def add_tp(self, name, t, shape, data, tp_rank, tp_size):
+        """Adds only shard tp_rank of tp_size of a split tensor (whole tensor for replicated ones)."""
+        data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        shp, rank = _shape_arg(shape)
+        check(lib().tlb_map_add_tp(self.h, name.encode(), t, shp, rank, data.ctypes.data_as(C.c_void_p), data.size, tp_rank, tp_size))
+
+    @staticmethod
+    def load_tp(path, tp_rank, tp_size):
+        out = C.c_void_p()
+        check(lib().tlb_gguf_load_tp(C.byref(out), str(path).encode(), tp_rank, tp_size))
+        return TensorMap(out)
+
     def names(self):
         return [lib().tlb_map_name(self.h, i).decode() for i in range(lib().tlb_map_count(self.h))]
 
@@ -298,12 +362,12 @@ class Graph:
 class Decoder:
     """Fused decode session over a TensorMap holding a Llama-shaped model."""
 
-    def __init__(self, cfg, weights, kv_f16=True, max_seq=4096, tie_rule=TIE_LAST):
+    def __init__(self, cfg, weights, kv_f16=True, max_seq=4096, tie_rule=TIE_LAST, tp_size=1, tp_rank=0):
         self.cfg = DecoderCfg(n_layers=cfg["n_layers"], d_model=cfg["d_model"], n_heads=cfg["n_heads"],
                               n_kv_heads=cfg["n_kv_heads"], head_dim=cfg["head_dim"], ffn=cfg["ffn"],
                               vocab=cfg["vocab"], eps=cfg["eps"], rope_base=cfg["rope_base"],
                               attn_scale=cfg["attn_scale"], kv_f16=int(kv_f16), max_seq=max_seq,
-                              tie_rule=tie_rule, tp_size=1, tp_rank=0)
+                              tie_rule=tie_rule, tp_size=tp_size, tp_rank=tp_rank)
         self.h = C.c_void_p()
         check(lib().tlb_decoder_create(C.byref(self.h), C.byref(self.cfg), weights.h))
 
@@ -370,9 +434,13 @@ class Decoder:
             pass
 
 
-def map_from_tensors(tensors):
-    """TensorMap from the dict synth.llama_tensors returns (name -> (type, bytes, shape))."""
+def map_from_tensors(tensors, tp_rank=0, tp_size=1):
+    """TensorMap from the dict synth.llama_tensors returns (name -> (type, bytes, shape)); with tp_size > 1 only this
+    rank's shard of every split tensor goes to the device."""
     m = TensorMap.new()
     for name, (t, data, shape) in tensors.items():
-        m.add(name, t, shape, data)
+        if tp_size > 1:
+            m.add_tp(name, t, shape, data, tp_rank, tp_size)
+        else:
+            m.add(name, t, shape, data)
     return m

@@ -244,6 +244,7 @@ tlb_status tlb_embedding(tlb_tensor **out, const tlb_tensor *table, const tlb_te
     int64_t oshape[kMaxRank];
     for (int i = 0; i < idx->rank; i++) oshape[i] = idx->shape[i];
     oshape[idx->rank] = table->shape[1];
+    REQ(!tlb_stream_is_capturing(), TLB_ERR_ARG, "embedding reads its out-of-range flag back from the device: not allowed during a stream capture");
     TLB_TRY(new_tensor(out, TLB_F32, oshape, idx->rank + 1));
     static int *oob = nullptr;
     if (!oob) { TLB_CUDA(cudaMalloc(&oob, sizeof(int))); TLB_CUDA(cudaMemset(oob, 0, sizeof(int))); }

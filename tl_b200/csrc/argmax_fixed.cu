@@ -15,10 +15,12 @@
 // with that device current (cudaGetSymbolAddress; this may make the runtime load the module), so
 // make the first call outside any stream capture.  Later calls only launch two kernels.
 //
-// Sharing: every call on a device uses the same array.  Calls are ordered on the library's stream,
-// so calls made one after another are safe; calls issued concurrently from several host threads are
-// ordered by the stream too, but a caller that launches the kernels of two calls onto different
-// streams (not possible through this API) would make them race on the array.  Nothing in the array
+// Sharing: every call on a device uses the same array, and a call is TWO launches (per-block
+// partial results, then their fold).  Both go to the library's one stream, so calls made one after
+// another never overlap on the GPU.  Calls from several host threads are safe as well: a host mutex
+// is held from the first launch to the second, so the two kernels of a call are always neighbours on
+// the stream and no other call's partial results can land between them.  Work that reaches the array
+// from another stream (not possible through this API) would race with both.  Nothing in the array
 // has to start at zero: the first kernel overwrites every slot the second kernel reads.
 #include "tlb_internal.h"
 
@@ -97,6 +99,7 @@ __global__ void __launch_bounds__(32) argmax_fold_kernel(const ArgmaxPartial *__
 
 // Device address of the fixed array, one entry per device ordinal; filled by the first call on that device.
 static std::mutex g_setup_mu;
+static std::mutex g_pair_mu;   // held across the two launches of a call: they stay adjacent on the stream
 static ArgmaxPartial *g_scratch_ptr[kMaxDevices] = {nullptr};
 
 static tlb_status scratch_for_current_device(int device, ArgmaxPartial **ptr)
@@ -136,6 +139,7 @@ extern "C" tlb_status tlb_argmax_into(tlb_tensor *out, const tlb_tensor *x, tlb_
     TLB_TRY(scratch_for_current_device(c->device, &scratch));
     const int parts = (int)((n + kChunk - 1) / kChunk);
     const int tie_first = tie == TLB_TIE_FIRST;
+    std::lock_guard<std::mutex> pair(g_pair_mu);
     argmax_chunk_kernel<<<parts, 256, 0, c->stream>>>(x->f32(), (long long)n, tie_first, scratch);
     TLB_CUDA(cudaGetLastError());
     argmax_fold_kernel<<<1, 32, 0, c->stream>>>(scratch, parts, tie_first, out->f32());

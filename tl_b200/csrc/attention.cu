@@ -10,7 +10,6 @@
 //
 // sdpa_kernel: the generic tl_tensor_sdpa entry (flash_attention_kernel, autograd.cu:2263-2367).
 #include "tlb_internal.h"
-#include "span_trace.cuh"
 
 namespace tlb {
 
@@ -61,7 +60,6 @@ struct AttnParams {
     float *out;       // [H * D]
     int use_pdl;
     int row_stride;   // shared-memory row stride in bytes (16-byte chunks, count = 4 mod 8: conflict-free)
-    unsigned long long *span;
 };
 
 __device__ __forceinline__ float ld_qkv(const AttnParams &p, size_t i) { return __ldcg(p.qkv + i); }
@@ -85,7 +83,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
 
     // Cache length and this CTA's key range.  pos was written at the end of the previous decode
     // step, which every predecessor of this launch has already waited for.
-    if (tid == 0) span_start(p.span);
     const int pos = *p.pos;
     const int Tlen = pos + 1;
     const int nsplit = (Tlen + kKeysPerCta - 1) / kKeysPerCta;
@@ -122,7 +119,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
         asm volatile("griddepcontrol.wait;" ::: "memory");
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
-    if (tid == 0) span_event(p.span, 1);
     // all loads of the new projections first (one round trip), then the arithmetic
     float q0 = 0.f, q1 = 0.f, k0f = 0.f, k1f = 0.f, v0f = 0.f, v1f = 0.f;
     const size_t qi = (size_t)(kvh * REP + hq) * D + jq;
@@ -145,11 +141,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
         krow[jk] = k0; krow[jk + 1] = k1; vrow[jk] = v0; vrow[jk + 1] = v1;
         kc[jk] = k0; kc[jk + 1] = k1; vc[jk] = v0; vc[jk + 1] = v1;
     }
-    if (tid == 0) span_event(p.span, 6);
     cp_async_wait_all();
-    if (tid == 0) span_event(p.span, 7);
     __syncthreads();
-    if (tid == 0) span_event(p.span, 2);
 
     // scores: thread (key = tid/4, dq = tid%4) covers chunks dq, dq+4, ... of its key row, all REP heads
     {
@@ -236,9 +229,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
             part[h * (D + 4) + d] = s;
         }
     }
-    if (nsplit == 1 && !p.defer_merge) { if (tid == 0) span_event(p.span, 3); return; }
+    if (nsplit == 1 && !p.defer_merge) return;
     if (tid < REP) { part[tid * (D + 4) + D] = ml[tid * 2]; part[tid * (D + 4) + D + 1] = ml[tid * 2 + 1]; }
-    if (p.defer_merge) { if (tid == 0) span_event(p.span, 3); return; }
+    if (p.defer_merge) return;
     // the last CTA of this KV head to finish merges all splits
     __threadfence();
     __syncthreads();
@@ -247,7 +240,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
         is_last = (old == nsplit - 1);
     }
     __syncthreads();
-    if (tid == 0) span_event(p.span, 3);
     if (!is_last) return;
     __threadfence();
     const float *base = p.partial + (size_t)kvh * p.max_splits * REP * (D + 4);
@@ -266,7 +258,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
         }
         p.out[(size_t)(kvh * REP + h) * D + d] = O / L;
     }
-    if (tid == 0) { p.counters[kvh] = 0; span_event(p.span, 3); }
+    if (tid == 0) p.counters[kvh] = 0;
 }
 
 static int attn_row_stride(int D, int esize)
@@ -318,7 +310,6 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     p.defer_merge = j.defer_merge ? 1 : 0;
     p.partial = j.partial; p.counters = j.counters; p.max_splits = j.splits; p.out = j.out;
     p.use_pdl = j.pdl ? 1 : 0;
-    p.span = j.span;
     p.row_stride = attn_row_stride(j.D, j.kv_f16 ? 2 : 4);
 #define DISPATCH(REPV)                                                                         \
     if (rep == REPV)                                                                           \

@@ -50,9 +50,15 @@ struct tlb_decoder {
     uint64_t graph_kernels = 0;
     bool pdl = true;
     bool dry = false;            // enqueue_step only validates the matvec launches
-    int force_slices[5] = {0, 0, 0, 0, 0};   // K-slices of qkv, o, gate|up, down, head; 0: the kernel's own choice (TLB_SLICES=a,b,c,d,e)
     std::vector<void *> allocs;
     size_t kv_layer_elems = 0;
+    // tensor parallelism: this process holds shard tp_r of tp.  H, KVH, F, V below are the LOCAL sizes (heads, KV heads,
+    // hidden units, vocabulary rows of this shard); they equal the model's sizes for tp == 1.
+    int tp = 1, tp_r = 0;
+    int H = 0, KVH = 0, F = 0, V = 0;
+    float *part = nullptr;        // tp > 1: this rank's partial o_proj / ffn_down result, summed over the ranks in place
+    float *pair = nullptr;        // tp > 1: (best logit, its global index) of this shard, then of every shard [1 + tp][2]
+    float *logits_all = nullptr;  // tp > 1: the gathered logits of all shards (tlb_decoder_logits)
 };
 
 namespace {
@@ -124,6 +130,53 @@ __global__ void argmax_advance_kernel(const float *__restrict__ x, int n, int ti
     *counter = 0;
 }
 
+// Vocabulary-split head: each rank has the (best logit, global index) pair of its shard, gathered in rank order into
+// pairs[tp][2]; one warp picks the winner under the tie rule and advances the decode state, identically on every rank.
+__global__ void argmax_pick_kernel(const float *__restrict__ pairs, int tp, int tie_first, int *state, int *tokens_out, int tokens_cap)
+{
+    if (threadIdx.x != 0) return;
+    float bv = pairs[0];
+    long long bi = (long long)pairs[1];
+    for (int r = 1; r < tp; r++) {
+        const float v = pairs[2 * r];
+        const long long i = (long long)pairs[2 * r + 1];
+        if (v > bv || (v == bv && (tie_first ? i < bi : i > bi))) { bv = v; bi = i; }
+    }
+    const int idx = state[3];
+    if (tokens_out && idx < tokens_cap) tokens_out[idx] = (int)bi;
+    state[0] = (int)bi;
+    state[1] += 1;
+    state[2] += 1;
+    state[3] = idx + 1;
+}
+
+// One block: the best logit of this shard and its global index (< 2^24, exact in f32) as two floats.
+__global__ void __launch_bounds__(1024) argmax_pair_kernel(const float *__restrict__ x, int n, int tie_first, int offset, float *pair)
+{
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float bv = 0.f;
+    int bi = -1;
+    auto better = [&](float v, int i, float cv, int ci) { return ci < 0 || v > cv || (v == cv && (tie_first ? i < ci : i > ci)); };
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = __ldcg(x + i);
+        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+    for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+            if (si[w] >= 0 && better(sv[w], si[w], bv, bi)) { bv = sv[w]; bi = si[w]; }
+        pair[0] = bv;
+        pair[1] = (float)(max(bi, 0) + offset);
+    }
+}
+
 template <typename T>
 tlb_status dalloc(tlb_decoder *d, T **p, size_t count, bool zero = true)
 {
@@ -166,24 +219,34 @@ void set_w(MatvecJob &j, int i, const tlb_qtensor *q, float *out)
 // the kernel chain of one decode step (launched eagerly or into a capturing stream)
 // output_norm + head + greedy token (with the advance of the decode state) on the residual in xb.
 // ssq_parts: per-tile sums of squares of xb left by the launch that wrote it, or null (the head launch sums itself).
-tlb_status enqueue_head(tlb_decoder *d, const float *ssq_parts, unsigned long long *span)
+tlb_status enqueue_head(tlb_decoder *d, const float *ssq_parts, const float *x = nullptr, const float *x2 = nullptr, float *x_out = nullptr)
 {
     const tlb_decoder_cfg &c = d->cfg;
     const int dm = c.d_model;
-    {   // output_norm + head
+    {   // output_norm + head (tp > 1: this rank's rows of the vocabulary)
         MatvecJob j;
         j.n_w = 1;
         set_w(j, 0, d->head, d->logits);
-        j.type = d->head->type; j.k = dm; j.m = 1; j.slices = d->force_slices[4];
-        j.prologue = PRO_ADD_NORM; j.x = d->xb; j.ssq_parts = ssq_parts; j.n_parts = ssq_parts ? (dm + 15) / 16 : 0;
+        j.type = d->head->type; j.k = dm; j.m = 1;
+        j.prologue = PRO_ADD_NORM; j.x = x ? x : d->xb; j.x2 = x2; j.x_out = x_out;
+        j.ssq_parts = ssq_parts; j.n_parts = ssq_parts ? (dm + 15) / 16 : 0;
         j.norm_w = d->out_norm->f32(); j.eps = c.eps;
         j.last_of_chain = true;
-        j.pdl = d->pdl;
-        j.span = span;
+        j.pdl = d->pdl && !x2;     // behind a collective: a plain stream dependency
         j.dry_run = d->dry;
         TLB_TRY(launch_qmatvec(j));
     }
-    if (!d->dry) {
+    if (d->dry) return TLB_OK;
+    if (d->tp > 1) {
+        argmax_pair_kernel<<<1, 1024, 0, ctx()->stream>>>(d->logits, d->V, (int)(c.tie_rule == TLB_TIE_FIRST), d->tp_r * d->V, d->pair);
+        TLB_CUDA(cudaGetLastError());
+        TLB_TRY(tp_allgather(d->pair, d->pair + 2, 2 * sizeof(float)));
+        argmax_pick_kernel<<<1, 32, 0, ctx()->stream>>>(d->pair + 2, d->tp, (int)(c.tie_rule == TLB_TIE_FIRST), d->state, d->tokens_out, d->tokens_cap);
+        TLB_CUDA(cudaGetLastError());
+        count_launch(2);
+        return TLB_OK;
+    }
+    {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(kArgmaxBlocks);
         cfg.blockDim = dim3(256);
@@ -207,11 +270,85 @@ tlb_status enqueue_head(tlb_decoder *d, const float *ssq_parts, unsigned long lo
     return TLB_OK;
 }
 
-tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
+// The chain of one decode step on one shard of a tensor-parallel group (Megatron split): q | k | v and gate | up hold
+// this rank's heads / hidden units, o_proj and ffn_down this rank's slice of their inner dimension, so their results
+// are partial sums: they are written plain, summed over the ranks (tp_allreduce, in place), and the launch that
+// consumes them adds the sum to the residual while it normalises (the PRO_ADD_NORM prologue with a delta; CTA 0 stores
+// the new residual).  Two collectives per layer and nothing else crosses the ranks until the (maximum, index) pairs of
+// the vocabulary-split head.  Launches behind a collective take a plain stream dependency.
+tlb_status enqueue_step_tp(tlb_decoder *d)
 {
     const tlb_decoder_cfg &c = d->cfg;
-    int span_i = 0;
-    auto next_span = [&]() { return span ? span + 8 * (span_i++) : nullptr; };   // timeline slot of the next launch
+    const int dm = c.d_model, qd = d->H * c.head_dim, kvd = d->KVH * c.head_dim, F = d->F;
+    for (int l = 0; l < c.n_layers; l++) {
+        const LayerW &w = d->layers[l];
+        {   // K1: residual (+ the summed ffn_down of the layer before) -> RMSNorm -> q | k | v of this rank's heads
+            if (w.k->type != w.q->type || w.v->type != w.q->type) return fail(TLB_ERR_TYPE, "tensor-parallel sessions take q, k, v of one GGML type per layer");
+            MatvecJob j;
+            j.n_w = 3;
+            set_w(j, 0, w.q, d->qkv); set_w(j, 1, w.k, d->qkv + qd); set_w(j, 2, w.v, d->qkv + qd + kvd);
+            j.type = w.q->type; j.k = dm; j.m = 1;
+            j.prologue = PRO_ADD_NORM; j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
+            if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; j.x_out = d->xb; j.pdl = d->pdl; }
+            else { j.x = d->xa; j.x2 = d->part; j.x_out = d->xb; j.pdl = false; }
+            j.dry_run = d->dry;
+            TLB_TRY(launch_qmatvec(j));
+        }
+        {   // K2: attention over this rank's KV heads
+            DecodeAttnJob a;
+            a.qkv = d->qkv;
+            a.kcache = (char *)d->kcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
+            a.vcache = (char *)d->vcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
+            a.kv_f16 = c.kv_f16; a.H = d->H; a.KVH = d->KVH; a.D = c.head_dim; a.max_seq = c.max_seq;
+            a.pos = d->state + 1; a.rope_pos = d->state + 2; a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.scale = c.attn_scale;
+            a.partial = d->partial; a.counters = d->counters; a.splits = d->max_splits; a.out = d->attn; a.pdl = d->pdl;
+            a.defer_merge = true;
+            if (!d->dry) TLB_TRY(launch_decode_attention(a));
+        }
+        {   // K3: this rank's slice of o_proj -> partial sum
+            MatvecJob j;
+            j.n_w = 1;
+            set_w(j, 0, w.o, d->part);
+            j.type = w.o->type; j.k = qd; j.m = 1;
+            j.prologue = PRO_ATTN_MERGE;
+            j.att_part = d->partial; j.att_pos = d->state + 1; j.att_max_splits = d->max_splits;
+            j.att_rep = d->H / d->KVH; j.att_dim = c.head_dim; j.att_keys = kAttnKeysPerSplit;
+            j.pdl = d->pdl;
+            j.dry_run = d->dry;
+            TLB_TRY(launch_qmatvec(j));
+        }
+        if (!d->dry) TLB_TRY(tp_allreduce(d->part, dm));
+        {   // K4: xa = xb + sum; RMSNorm; gate | up of this rank's hidden units; SiLU(gate) * up
+            MatvecJob j;
+            j.n_w = 1;
+            set_w(j, 0, w.gu, d->hbuf);
+            j.type = w.gu->type; j.k = dm; j.m = 1;
+            j.prologue = PRO_ADD_NORM; j.x = d->xb; j.x2 = d->part; j.x_out = d->xa;
+            j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
+            j.finish = FIN_SILU;
+            j.pdl = false;
+            j.dry_run = d->dry;
+            TLB_TRY(launch_qmatvec(j));
+        }
+        {   // K5: this rank's slice of ffn_down -> partial sum
+            MatvecJob j;
+            j.n_w = 1;
+            set_w(j, 0, w.down, d->part);
+            j.type = w.down->type; j.k = F; j.m = 1;
+            j.prologue = PRO_PLAIN; j.x = d->hbuf;
+            j.pdl = d->pdl;
+            j.dry_run = d->dry;
+            TLB_TRY(launch_qmatvec(j));
+        }
+        if (!d->dry) TLB_TRY(tp_allreduce(d->part, dm));
+    }
+    return enqueue_head(d, nullptr, d->xa, d->part, d->xb);   // xb = xa + sum: the residual before output_norm
+}
+
+tlb_status enqueue_step(tlb_decoder *d)
+{
+    if (d->tp > 1) return enqueue_step_tp(d);
+    const tlb_decoder_cfg &c = d->cfg;
     const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
     const int L = c.n_layers;
     for (int l = 0; l < L; l++) {
@@ -227,7 +364,7 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
                 j.n_w = 0;
                 for (int b = a; b < 3; b++)
                     if (!done[b] && ws[b]->type == ws[a]->type) { set_w(j, j.n_w++, ws[b], outs[b]); done[b] = true; }
-                j.type = ws[a]->type; j.k = dm; j.m = 1; j.slices = j.n_w == 3 ? d->force_slices[0] : 0;
+                j.type = ws[a]->type; j.k = dm; j.m = 1;
                 j.prologue = PRO_ADD_NORM;
                 j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
                 // the residual lives in xb here: the embedding row for layer 0 (the first launch stores it), else what
@@ -236,7 +373,6 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
                 else if (l == 0) { j.x = d->xb; }
                 else { j.x = d->xb; j.ssq_parts = d->ssq_d; j.n_parts = (dm + 15) / 16; }
                 j.pdl = d->pdl;
-                j.span = next_span();
                 j.dry_run = d->dry;
                 TLB_TRY(launch_qmatvec(j));
                 first = false;
@@ -251,21 +387,19 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             a.pos = d->state + 1; a.rope_pos = d->state + 2; a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.scale = c.attn_scale;
             a.partial = d->partial; a.counters = d->counters; a.splits = d->max_splits; a.out = d->attn; a.pdl = d->pdl;
             a.defer_merge = true;
-            a.span = next_span();
             if (!d->dry) TLB_TRY(launch_decode_attention(a));
         }
         {   // K3
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.o, d->xa);
-            j.type = w.o->type; j.k = qd; j.m = 1; j.slices = d->force_slices[1];
+            j.type = w.o->type; j.k = qd; j.m = 1;
             // the attention launch leaves its per-split results; they are combined here, as the activation is loaded
             j.prologue = PRO_ATTN_MERGE;
             j.att_part = d->partial; j.att_pos = d->state + 1; j.att_max_splits = d->max_splits;
             j.att_rep = c.n_heads / c.n_kv_heads; j.att_dim = c.head_dim; j.att_keys = kAttnKeysPerSplit;
             j.finish = FIN_RESID; j.resid = d->xb; j.ssq_out = d->ssq_o;   // xa = xb + o_proj(attn)
             j.pdl = d->pdl;
-            j.span = next_span();
             j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
@@ -273,12 +407,11 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.gu, d->hbuf);
-            j.type = w.gu->type; j.k = dm; j.m = 1; j.slices = d->force_slices[2];
+            j.type = w.gu->type; j.k = dm; j.m = 1;
             j.prologue = PRO_ADD_NORM; j.x = d->xa; j.ssq_parts = d->ssq_o; j.n_parts = (dm + 15) / 16;
             j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
             j.finish = FIN_SILU;
             j.pdl = d->pdl;
-            j.span = next_span();
             j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
@@ -286,16 +419,15 @@ tlb_status enqueue_step(tlb_decoder *d, unsigned long long *span = nullptr)
             MatvecJob j;
             j.n_w = 1;
             set_w(j, 0, w.down, d->xb);
-            j.type = w.down->type; j.k = F; j.m = 1; j.slices = d->force_slices[3];
+            j.type = w.down->type; j.k = F; j.m = 1;
             j.prologue = PRO_PLAIN; j.x = d->hbuf;
             j.finish = FIN_RESID; j.resid = d->xa; j.ssq_out = d->ssq_d;   // xb = xa + down(h)
             j.pdl = d->pdl;
-            j.span = next_span();
             j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
     }
-    TLB_TRY(enqueue_head(d, d->ssq_d, next_span()));
+    TLB_TRY(enqueue_head(d, d->ssq_d));
     return TLB_OK;
 }
 
@@ -356,15 +488,25 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     const tlb_decoder_cfg &c = *cfg;
     if (c.n_layers < 1 || c.d_model < 1 || c.n_heads < 1 || c.n_kv_heads < 1 || c.head_dim < 1 || c.ffn < 1 || c.vocab < 1 || c.max_seq < 1)
         return fail(TLB_ERR_ARG, "decoder config has a non-positive size");
-    if (c.tp_size > 1) return fail(TLB_ERR_ARG, "tensor-parallel decode sessions are created with tlb_decoder_create_tp");
     if (c.n_heads % c.n_kv_heads) return fail(TLB_ERR_SHAPE, "n_heads must be a multiple of n_kv_heads");
-    const int64_t dm = c.d_model, qd = (int64_t)c.n_heads * c.head_dim, kvd = (int64_t)c.n_kv_heads * c.head_dim, F = c.ffn;
+    const int tp = c.tp_size > 1 ? c.tp_size : 1, tp_r = tp > 1 ? c.tp_rank : 0;
+    if (tp > 1) {
+        // one process per GPU: the weights in the map are this rank's shards (tlb_gguf_load_tp / tlb_map_add_tp) and the
+        // communicator of tlb_tp_init carries the two sums per layer
+        if (tp != tp_size() || tp_r != tp_rank())
+            return fail(TLB_ERR_ARG, "decoder config names shard %d of %d, the communicator of tlb_tp_init is rank %d of %d", c.tp_rank, c.tp_size, tp_rank(), tp_size());
+        if (c.n_heads % tp || c.n_kv_heads % tp || c.ffn % tp || c.vocab % tp)
+            return fail(TLB_ERR_SHAPE, "heads (%d / %d), ffn %d and vocab %d must divide over %d ranks", c.n_heads, c.n_kv_heads, c.ffn, c.vocab, tp);
+        if ((c.ffn / tp) % 256 || ((c.n_heads / tp) * c.head_dim) % 256)
+            return fail(TLB_ERR_SHAPE, "a rank's slice of ffn (%d) and of the attention width (%d) must be multiples of 256", c.ffn / tp, (c.n_heads / tp) * c.head_dim);
+        if ((int64_t)c.vocab >= (1 << 24)) return fail(TLB_ERR_SHAPE, "vocabulary too large for the index exchange");
+    }
     tlb_decoder *d = new tlb_decoder();
     d->cfg = c;
-    if (const char *fs = getenv("TLB_SLICES"))   // tuning aid: K-slices per launch kind instead of the cost model's choice
-        sscanf(fs, "%d,%d,%d,%d,%d", &d->force_slices[0], &d->force_slices[1], &d->force_slices[2], &d->force_slices[3], &d->force_slices[4]);
-    const char *nopdl = getenv("TLB_NO_PDL");
-    d->pdl = !(nopdl && nopdl[0] == '1');
+    d->tp = tp; d->tp_r = tp_r;
+    d->H = c.n_heads / tp; d->KVH = c.n_kv_heads / tp; d->F = c.ffn / tp; d->V = c.vocab / tp;
+    // local sizes: the shapes this rank's tensors must have
+    const int64_t dm = c.d_model, qd = (int64_t)d->H * c.head_dim, kvd = (int64_t)d->KVH * c.head_dim, F = d->F;
     tlb_status st = TLB_OK;
 #define TRY_D(expr) do { st = (expr); if (st != TLB_OK) { tlb_decoder_destroy(d); return st; } } while (0)
     d->layers.resize(c.n_layers);
@@ -383,7 +525,7 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     }
     TRY_D(get_f(m, "token_embd.weight", &d->emb, (int64_t)c.vocab * dm));
     TRY_D(get_f(m, "output_norm.weight", &d->out_norm, dm));
-    TRY_D(get_q(m, "output.weight", &d->head, c.vocab, dm, -1));
+    TRY_D(get_q(m, "output.weight", &d->head, d->V, dm, -1));
     {
         // Types may differ from tensor to tensor and from layer to layer (Q4_K_M files keep attn_v and ffn_down of
         // some layers in Q6_K); only gate and up of one layer must agree, since they are interleaved into one tensor.
@@ -395,7 +537,7 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
         for (LayerW &w : d->layers) {
             tlb_qtensor *g = new tlb_qtensor();
             g->type = w.gate->type; g->n = 2 * F; g->k = dm; g->n_tiles = 2 * F / 16; g->upt = dm / 256;
-            g->st = storage_alloc((size_t)g->nbytes());
+            g->st = storage_alloc((size_t)g->n_tiles * g->upt * qformat(g->type)->unit_bytes);
             w.gu = g;
             if (!g->st) { tlb_decoder_destroy(d); return TLB_ERR_ALLOC; }
             TRY_D(launch_interleave8(g->type, w.gate->dev(), w.up->dev(), g->dev(), F, dm));
@@ -405,13 +547,18 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     TRY_D(dalloc(d, &d->qkv, qd + 2 * kvd)); TRY_D(dalloc(d, &d->attn, qd));
     TRY_D(dalloc(d, &d->hbuf, F));
     TRY_D(dalloc(d, &d->ssq_o, (dm + 15) / 16)); TRY_D(dalloc(d, &d->ssq_d, (dm + 15) / 16));
-    TRY_D(dalloc(d, &d->logits, c.vocab));
+    TRY_D(dalloc(d, &d->logits, d->V));
+    if (tp > 1) {
+        TRY_D(dalloc(d, &d->part, dm));
+        TRY_D(dalloc(d, &d->pair, 2 * (1 + tp)));
+        TRY_D(dalloc(d, &d->logits_all, c.vocab));
+    }
     d->kv_layer_elems = (size_t)kvd * c.max_seq;
     size_t kv_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
     TRY_D(dalloc(d, (char **)&d->kcache, kv_bytes)); TRY_D(dalloc(d, (char **)&d->vcache, kv_bytes));
     d->max_splits = (c.max_seq + kAttnKeysPerSplit - 1) / kAttnKeysPerSplit;
     int rep = c.n_heads / c.n_kv_heads;
-    TRY_D(dalloc(d, &d->partial, (size_t)c.n_kv_heads * d->max_splits * rep * (c.head_dim + 4)));
+    TRY_D(dalloc(d, &d->partial, (size_t)d->KVH * d->max_splits * rep * (c.head_dim + 4)));
     TRY_D(dalloc(d, &d->counters, c.n_kv_heads + 1));
     TRY_D(dalloc(d, &d->state, 4));
     d->tokens_cap = c.max_seq;
@@ -451,24 +598,26 @@ tlb_status tlb_decoder_kv_write(tlb_decoder *d, int layer, int pos0, int n, cons
     if (layer < 0 || layer >= c.n_layers || pos0 < 0 || n < 0 || pos0 + n > c.max_seq)
         return fail(TLB_ERR_INDEX, "kv_write: layer %d rows [%d, %d) out of range", layer, pos0, pos0 + n);
     if (n == 0) return TLB_OK;
-    const int D = c.head_dim, KVH = c.n_kv_heads;
+    const int D = c.head_dim, KVH = d->KVH, KVH_all = c.n_kv_heads, h0 = d->tp_r * d->KVH;   // host rows hold all heads; this rank keeps its own
     const size_t es = c.kv_f16 ? 2 : 4;
-    // host layout [n][KVH*D] -> cache layout [KVH][max_seq][D]
-    std::vector<uint8_t> buf((size_t)n * D * es);
+    // host layout [n][KVH*D] -> cache layout [KVH][max_seq][D]: staged whole, one copy per head, one wait at the end
+    const size_t head_bytes = (size_t)n * D * es;
+    std::vector<uint8_t> buf(2 * (size_t)KVH * head_bytes);
     for (int which = 0; which < 2; which++) {
         const float *src = which ? v : k;
         char *dst = (char *)(which ? d->vcache : d->kcache) + (size_t)layer * d->kv_layer_elems * es;
         for (int h = 0; h < KVH; h++) {
+            uint8_t *hb = buf.data() + ((size_t)which * KVH + h) * head_bytes;
             for (int t = 0; t < n; t++)
                 for (int e = 0; e < D; e++) {
-                    float f = src[((size_t)t * KVH + h) * D + e];
-                    if (c.kv_f16) ((__half *)buf.data())[(size_t)t * D + e] = __float2half_rn(f);
-                    else ((float *)buf.data())[(size_t)t * D + e] = f;
+                    float f = src[((size_t)t * KVH_all + h0 + h) * D + e];
+                    if (c.kv_f16) ((__half *)hb)[(size_t)t * D + e] = __float2half_rn(f);
+                    else ((float *)hb)[(size_t)t * D + e] = f;
                 }
-            TLB_CUDA(cudaMemcpyAsync(dst + ((size_t)h * c.max_seq + pos0) * D * es, buf.data(), buf.size(), cudaMemcpyHostToDevice, ctx()->stream));
-            TLB_CUDA(cudaStreamSynchronize(ctx()->stream));
+            TLB_CUDA(cudaMemcpyAsync(dst + ((size_t)h * c.max_seq + pos0) * D * es, hb, head_bytes, cudaMemcpyHostToDevice, ctx()->stream));
         }
     }
+    TLB_CUDA(cudaStreamSynchronize(ctx()->stream));   // the staging buffer goes away on return
     return TLB_OK;
 }
 
@@ -509,7 +658,12 @@ tlb_status tlb_decoder_generate(tlb_decoder *d, int32_t first_token, int32_t sta
 tlb_status tlb_decoder_logits(tlb_decoder *d, float *logits_out)
 {
     if (!d || !logits_out) return fail(TLB_ERR_NULL, "null argument");
-    TLB_CUDA(cudaMemcpyAsync(logits_out, d->logits, (size_t)d->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx()->stream));
+    const float *src = d->logits;
+    if (d->tp > 1) {   // every rank calls this: the shards' rows are gathered in rank order = vocabulary order
+        TLB_TRY(tp_allgather(d->logits, d->logits_all, (size_t)d->V * sizeof(float)));
+        src = d->logits_all;
+    }
+    TLB_CUDA(cudaMemcpyAsync(logits_out, src, (size_t)d->cfg.vocab * 4, cudaMemcpyDeviceToHost, ctx()->stream));
     return tlb_sync();
 }
 
@@ -527,8 +681,12 @@ tlb_status tlb_decoder_stats(const tlb_decoder *d, int32_t ctx_len, uint64_t *we
     for (const LayerW &w : d->layers)
         wb += w.q->nbytes() + w.k->nbytes() + w.v->nbytes() + w.o->nbytes() + w.gate->nbytes() + w.up->nbytes() + w.down->nbytes();
     if (weight_bytes) *weight_bytes = wb;
-    if (kv_bytes) *kv_bytes = 2ull * d->cfg.n_layers * d->cfg.n_kv_heads * d->cfg.head_dim * (uint64_t)ctx_len * (d->cfg.kv_f16 ? 2 : 4);
-    if (kernels_per_step) *kernels_per_step = 5 * d->cfg.n_layers + 2;
+    if (kv_bytes) *kv_bytes = 2ull * d->cfg.n_layers * d->KVH * d->cfg.head_dim * (uint64_t)ctx_len * (d->cfg.kv_f16 ? 2 : 4);
+    if (kernels_per_step) {   // per layer: one q | k | v launch per weight type among the three, and four more; then head + argmax
+        int nk = d->tp > 1 ? 3 : 2;
+        for (const LayerW &w : d->layers) nk += 5 + (w.k->type != w.q->type) + (w.v->type != w.q->type && w.v->type != w.k->type);
+        *kernels_per_step = nk;
+    }
     return TLB_OK;
 }
 
@@ -536,8 +694,7 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
 {
     if (!d || !which || !us_per_launch) return fail(TLB_ERR_NULL, "null argument");
     const tlb_decoder_cfg &c = d->cfg;
-    const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
-    const int pos_arg = copies;    // the chain modes take the cache position in this argument
+    const int dm = c.d_model, qd = d->H * c.head_dim, kvd = d->KVH * c.head_dim, F = d->F;
     if (copies < 1) copies = 1;
     if (copies > c.n_layers) copies = c.n_layers;
     {   // the rotation below launches one kernel shape: only the leading layers typed like layer 0 take part
@@ -552,102 +709,19 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         copies = same;
     }
     std::string w(which);
-    if (w == "chain" || w == "chain_graph") {
-        // Timeline of one whole decode step launched eagerly (same launches as the graph): `copies` is the
-        // cache position, `iters` the warm-up steps.  Printed to stderr: per launch, microseconds from the
-        // start of the step to first CTA start / last dependency wait passed / last prologue done / end.
-        int nk = 1;   // launches of one step: per layer one q | k | v launch per weight type among the three, and four more
-        for (const LayerW &lw : d->layers) {
-            const int kinds = 1 + (lw.k->type != lw.q->type) + (lw.v->type != lw.q->type && lw.v->type != lw.k->type);
-            nk += 4 + kinds;
-        }
-        unsigned long long *span = nullptr;
-        TLB_CUDA(cudaMalloc(&span, (size_t)nk * 8 * sizeof(unsigned long long)));
-        int pos = std::min(std::max(pos_arg, 0), c.max_seq - iters - 8);
-        tlb_status st = set_state(d, 1, pos, pos, 0);
-        for (int i = 0; i < iters && st == TLB_OK; i++) st = enqueue_step(d);
-        std::vector<unsigned long long> h((size_t)nk * 8, 0ull);
-        for (int i = 0; i < nk; i++) h[(size_t)i * 8] = ~0ull;
-        cudaMemcpyAsync(span, h.data(), h.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice, ctx()->stream);
-        cudaStreamSynchronize(ctx()->stream);
-        cudaEvent_t e0, e1;
-        cudaEventCreate(&e0); cudaEventCreate(&e1);
-        float ms = 0.f;
-        cudaGraphExec_t gexec = nullptr;
-        const int n_replays = getenv("TLB_REPLAYS") ? std::max(1, atoi(getenv("TLB_REPLAYS"))) : 2;
-        if (w == "chain_graph" && getenv("TLB_USE_SESSION_GRAPH") && st == TLB_OK) {
-            st = ensure_graph(d);
-            for (int i = 0; i < 3 && st == TLB_OK; i++) cudaGraphLaunch(d->graph, ctx()->stream);
-            cudaStreamSynchronize(ctx()->stream);
-            cudaEventRecord(e0, ctx()->stream);
-            for (int i = 0; i < n_replays && st == TLB_OK; i++) cudaGraphLaunch(d->graph, ctx()->stream);
-            cudaEventRecord(e1, ctx()->stream);
-            cudaEventSynchronize(e1);
-            cudaEventElapsedTime(&ms, e0, e1);
-            fprintf(stderr, "[tlb chain] session graph: %.1f us per replay\n", ms * 1e3 / n_replays);
-        }
-        if (w == "chain_graph" && st == TLB_OK) {   // the same step as one graph launch, probes baked in
-            cudaGraph_t g = nullptr;
-            TLB_CUDA(cudaStreamBeginCapture(ctx()->stream, cudaStreamCaptureModeThreadLocal));
-            st = enqueue_step(d, getenv("TLB_NOSPAN") ? nullptr : span);
-            cudaError_t ce = cudaStreamEndCapture(ctx()->stream, &g);
-            if (st == TLB_OK && ce != cudaSuccess) st = cuda_fail(ce, "cudaStreamEndCapture");
-            if (st == TLB_OK) { ce = cudaGraphInstantiate(&gexec, g, 0); if (ce != cudaSuccess) st = cuda_fail(ce, "cudaGraphInstantiate"); }
-            if (g) cudaGraphDestroy(g);
-            for (int i = 0; i < 3 && st == TLB_OK; i++) cudaGraphLaunch(gexec, ctx()->stream);   // warm-up replays
-            cudaMemcpyAsync(span, h.data(), h.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice, ctx()->stream);
-            cudaStreamSynchronize(ctx()->stream);
-        }
-        cudaEventRecord(e0, ctx()->stream);
-        if (st == TLB_OK) {
-            if (gexec) { for (int i = 0; i < n_replays; i++) cudaGraphLaunch(gexec, ctx()->stream); }   // back-to-back replays
-            else st = enqueue_step(d, span);
-        }
-        cudaEventRecord(e1, ctx()->stream);
-        cudaEventSynchronize(e1);
-        cudaEventElapsedTime(&ms, e0, e1);
-        cudaMemcpy(h.data(), span, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-        cudaFree(span);
-        cudaEventDestroy(e0); cudaEventDestroy(e1);
-        if (gexec) { cudaGraphExecDestroy(gexec); ms /= (float)n_replays; }
-        if (st != TLB_OK) return st;
-        const unsigned long long t0 = h[0];
-        const char *names[5] = {"qkv", "attn", "o", "gate_up", "down"};
-        double busy[6] = {0, 0, 0, 0, 0, 0}, gap[6] = {0, 0, 0, 0, 0, 0};
-        unsigned long long prev_end = t0;
-        for (int i = 0; i < nk; i++) {
-            const unsigned long long *t = &h[(size_t)i * 8];
-            const int kind = i == nk - 1 ? 5 : i % 5;
-            if (i < 10 || i >= nk - 6)
-                fprintf(stderr, "[tlb chain] %3d %-8s start %9.2f (last %9.2f, set up %9.2f)  waited %9.2f  (loads %9.2f, norm %9.2f) prologue %9.2f  end %9.2f   (us)\n", i,
-                        kind == 5 ? "head" : names[kind], (t[0] - t0) / 1e3, t[4] ? (t[4] - t0) / 1e3 : 0.0, t[5] ? (t[5] - t0) / 1e3 : 0.0,
-                        (t[1] - t0) / 1e3, t[6] ? (t[6] - t0) / 1e3 : 0.0, t[7] ? (t[7] - t0) / 1e3 : 0.0, (t[2] - t0) / 1e3, (t[3] - t0) / 1e3);
-            busy[kind] += (t[3] - std::max(t[1], prev_end)) / 1e3;   // from (dependency met) to end
-            gap[kind] += ((double)std::max(t[1], prev_end) - (double)prev_end) / 1e3;
-            prev_end = t[3];
-        }
-        for (int kd = 0; kd < 6; kd++)
-            fprintf(stderr, "[tlb chain] %-8s total after-dependency time %9.1f us, dependency gaps %8.1f us\n", kd == 5 ? "head" : names[kd], busy[kd], gap[kd]);
-        fprintf(stderr, "[tlb chain] step %.1f us by events, %.1f us first start to last end (argmax not probed)\n", ms * 1e3,
-                (h[(size_t)(nk - 1) * 8 + 3] - t0) / 1e3);
-        *us_per_launch = ms * 1e3f;
-        if (bytes_per_launch) *bytes_per_launch = 0;
-        return tlb_sync();
-    }
-    int64_t out_n = w == "qkv" ? qd + 2 * kvd : (w == "o" || w == "down") ? dm : w == "gate_up" ? 2 * F : w == "head" ? c.vocab : -1;
+    int64_t out_n = w == "qkv" ? qd + 2 * kvd : (w == "o" || w == "down") ? dm : w == "gate_up" ? 2 * F : w == "head" ? d->V : -1;
     if (out_n < 0) return fail(TLB_ERR_ARG, "unknown kernel '%s' (qkv, o, gate_up, down, head)", which);
     int64_t kk = (w == "o") ? qd : (w == "down") ? F : dm;
     float *xin = nullptr, *outb = nullptr;
     TLB_CUDA(cudaMalloc(&xin, (size_t)std::max<int64_t>(kk, 2 * F) * 4));
-    TLB_CUDA(cudaMalloc(&outb, (size_t)out_n * kMaxSlices * 4));
+    constexpr int kOutRot = 3;   // consecutive launches overlap (programmatic dependent launch): each writes a buffer of its own
+    TLB_CUDA(cudaMalloc(&outb, (size_t)out_n * kOutRot * 4));
     {
         std::vector<float> hx((size_t)std::max<int64_t>(kk, 2 * F));
         uint32_t s = 12345u;
         for (float &v : hx) { s = s * 1664525u + 1013904223u; v = ((s >> 8) / 8388608.0f) - 1.0f; }
         cudaMemcpy(xin, hx.data(), hx.size() * 4, cudaMemcpyHostToDevice);
     }
-    long long *trace = nullptr;   // TLB_TRACE=1: per-CTA clock stamps of the last timed launch, printed to stderr
-    if (getenv("TLB_TRACE")) { cudaMalloc(&trace, 512 * 10 * sizeof(long long)); cudaMemset(trace, 0, 512 * 10 * sizeof(long long)); }
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0);
     cudaEventCreate(&e1);
@@ -657,7 +731,7 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
         if (it == 0) cudaEventRecord(e0, ctx()->stream);
         const LayerW &lw = d->layers[(it + 3) % copies];
         MatvecJob j;
-        float *o = outb;
+        float *o = outb + (size_t)((it + 3) % kOutRot) * out_n;
         j.m = 1; j.prologue = PRO_PLAIN; j.x = xin;
         if (w == "qkv") {
             if (lw.k->type != lw.q->type || lw.v->type != lw.q->type) { st = fail(TLB_ERR_TYPE, "time_kernel(qkv): q, k, v of layer 0 differ in type"); break; }
@@ -675,7 +749,6 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
             j.last_of_chain = true;
         }
         j.pdl = d->pdl;   // as in the decode chain: a launch's set-up overlaps its predecessor
-        if (trace && it == iters - 1) j.trace = trace;
         st = launch_qmatvec(j);
     }
     cudaEventRecord(e1, ctx()->stream);
@@ -683,20 +756,6 @@ tlb_status tlb_decoder_time_kernel(tlb_decoder *d, const char *which, int copies
     float ms = 0.f;
     cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0); cudaEventDestroy(e1);
-    if (trace) {
-        std::vector<long long> h(512 * 10);
-        cudaMemcpy(h.data(), trace, h.size() * sizeof(long long), cudaMemcpyDeviceToHost);
-        long long t_first = -1, t_last = 0;
-        for (int b = 0; b < 512; b++) if (h[b * 10 + 8]) { if (t_first < 0 || h[b * 10 + 8] < t_first) t_first = h[b * 10 + 8]; t_last = std::max(t_last, h[b * 10 + 9]); }
-        fprintf(stderr, "[tlb trace] %s: grid span %lld ns\n", which, t_last - t_first);
-        for (int b : {0, 1, 147, 148, 295}) {
-            const long long *t = &h[b * 10];
-            if (!t[8]) continue;
-            fprintf(stderr, "[tlb trace] cta %3d: start +%lld ns; cycles: init %lld, wait+zero %lld, prologue %lld, first unit ready %lld, first unit %lld, rest %lld; end +%lld ns\n",
-                    b, t[8] - t_first, t[1] - t[0], t[2] - t[1], t[3] - t[2], t[4] - t[3], t[5] - t[4], t[6] - t[5], t[9] - t_first);
-        }
-        cudaFree(trace);
-    }
     cudaFree(xin); cudaFree(outb);
     if (st != TLB_OK) return st;
     *us_per_launch = ms * 1000.f / (float)std::max(1, iters);
@@ -811,7 +870,7 @@ extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens,
     const int64_t last_rope = (int64_t)rope_pos0 + (int64_t)(n - 1) * rope_step;
     if (pos0 < 0 || (int64_t)pos0 + n > c.max_seq || rope_pos0 < 0 || rope_step < 0 || last_rope >= c.max_seq)
         return fail(TLB_ERR_INDEX, "positions [%d, %d) / rotation rows up to %lld outside the cache of %d rows", pos0, pos0 + n, (long long)last_rope, c.max_seq);
-    if (n <= kGemmMinRows || !prefill_batched_ok(d)) {
+    if (n <= kGemmMinRows || d->tp > 1 || !prefill_batched_ok(d)) {
         // few tokens, or a shape the GEMM path does not take: the fused single-token chain, token by token
         int32_t tok = 0;
         for (int i = 0; i < n; i++) TLB_TRY(tlb_decoder_step(d, tokens[i], pos0 + i, rope_pos0 + i * rope_step, i == n - 1 ? &tok : nullptr));
@@ -824,7 +883,7 @@ extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens,
     }
     // head on the last token; the state then names the next token and the row it will occupy
     TLB_TRY(set_state(d, tokens[n - 1], pos0 + n - 1, (int)last_rope, 0));
-    TLB_TRY(enqueue_head(d, nullptr, nullptr));
+    TLB_TRY(enqueue_head(d, nullptr));
     if (next) {
         TLB_CUDA(cudaMemcpyAsync(d->h_state, d->state, sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
         TLB_TRY(tlb_sync());

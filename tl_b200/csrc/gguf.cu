@@ -253,7 +253,18 @@ tlb_status tlb_map_add(tlb_map *m, const char *name, tlb_ggml_type type, const i
     return map_add(m, name, type, shape, rank, bytes, nbytes);
 }
 
-tlb_status tlb_gguf_load(tlb_map **out, const char *path)
+static tlb_status gguf_load_impl(tlb_map **out, const char *path, int tp_rank, int tp_size);
+
+tlb_status tlb_gguf_load(tlb_map **out, const char *path) { return gguf_load_impl(out, path, 0, 1); }
+
+/* tl_gguf_load for one rank of a tensor-parallel group: only this rank's shard of every split tensor is uploaded. */
+tlb_status tlb_gguf_load_tp(tlb_map **out, const char *path, int tp_rank, int tp_size)
+{
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) return fail(TLB_ERR_ARG, "shard %d of %d", tp_rank, tp_size);
+    return gguf_load_impl(out, path, tp_rank, tp_size);
+}
+
+static tlb_status gguf_load_impl(tlb_map **out, const char *path, int tp_rank, int tp_size)
 {
     if (!out) return fail(TLB_ERR_NULL, "null out");
     *out = nullptr;
@@ -329,7 +340,12 @@ tlb_status tlb_gguf_load(tlb_map **out, const char *path)
                 const bool k_quant = (int)inf.type == TLB_GGML_Q4_K || (int)inf.type == TLB_GGML_Q6_K;
                 if (kk % (k_quant ? 256 : 32)) continue;
             }
-            st = map_add(m, inf.name, (int)inf.type, inf.shape.data(), (int)inf.shape.size(), r.p + data_off + inf.offset, nb);
+            if (tp_size > 1) {
+                if (!ensure_init()) { st = TLB_ERR_DEVICE; break; }
+                st = tlb_map_add_tp(m, inf.name.c_str(), (tlb_ggml_type)inf.type, inf.shape.data(), (int)inf.shape.size(), r.p + data_off + inf.offset, nb, tp_rank, tp_size);
+            } else {
+                st = map_add(m, inf.name, (int)inf.type, inf.shape.data(), (int)inf.shape.size(), r.p + data_off + inf.offset, nb);
+            }
             if (st != TLB_OK) break;
         }
     } while (0);
@@ -337,6 +353,69 @@ tlb_status tlb_gguf_load(tlb_map **out, const char *path)
     if (st != TLB_OK) { tlb_map_free(m); return st; }
     *out = m;
     return TLB_OK;
+}
+
+/* ---- tensor-parallel shards (host side) ----
+ * Megatron split of a Llama block by tensor name: attn_q / attn_k / attn_v / ffn_gate / ffn_up and the output head are
+ * cut along their rows (each rank keeps whole heads / hidden units / vocabulary entries: a contiguous byte range of
+ * the row-major GGUF tensor); attn_output and ffn_down along their columns (per row, a contiguous range of blocks);
+ * everything else (embedding, norm weights) is replicated. */
+int tlb_tp_split_kind(const char *name)
+{
+    if (!name) return 0;
+    const std::string s(name);
+    auto ends = [&](const char *suffix) { const size_t n = strlen(suffix); return s.size() >= n && s.compare(s.size() - n, n, suffix) == 0; };
+    if (ends("attn_q.weight") || ends("attn_k.weight") || ends("attn_v.weight") || ends("ffn_gate.weight") || ends("ffn_up.weight") || s == "output.weight") return 1;
+    if (ends("attn_output.weight") || ends("ffn_down.weight")) return 2;
+    return 0;
+}
+
+tlb_status tlb_tp_shard_bytes(int kind, tlb_ggml_type type, int64_t n, int64_t k, const void *bytes, size_t nbytes, int rank, int size,
+                              void *out, size_t out_cap, int64_t *n_out, int64_t *k_out, size_t *out_bytes)
+{
+    if (!bytes || !n_out || !k_out || !out_bytes) return fail(TLB_ERR_NULL, "null argument");
+    if (size < 1 || rank < 0 || rank >= size || kind < 0 || kind > 2) return fail(TLB_ERR_ARG, "shard %d of %d, kind %d", rank, size, kind);
+    if (n < 0 || k < 0 || (k && n > INT64_MAX / k)) return fail(TLB_ERR_SHAPE, "bad shape");
+    const size_t row_bytes = ggml_raw_nbytes(type, k);
+    if ((k && !row_bytes) || row_bytes * (size_t)n != nbytes) return fail(TLB_ERR_SHAPE, "%zu bytes do not match type %d x [%lld, %lld]", nbytes, (int)type, (long long)n, (long long)k);
+    int64_t sn = n, sk = k;
+    if (kind == 1) {
+        if (n % size) return fail(TLB_ERR_SHAPE, "%lld rows do not divide over %d ranks", (long long)n, size);
+        sn = n / size;
+    } else if (kind == 2) {
+        if (k % size || (k && !ggml_raw_nbytes(type, k / size)))
+            return fail(TLB_ERR_SHAPE, "%lld columns of GGML type %d do not divide into whole blocks over %d ranks", (long long)k, (int)type, size);
+        sk = k / size;
+    }
+    const size_t shard_row = ggml_raw_nbytes(type, sk), total = shard_row * (size_t)sn;
+    *n_out = sn; *k_out = sk; *out_bytes = total;
+    if (!out) return TLB_OK;                       // size query
+    if (out_cap < total) return fail(TLB_ERR_ARG, "shard needs %zu bytes, buffer holds %zu", total, out_cap);
+    const uint8_t *src = (const uint8_t *)bytes;
+    if (kind == 2) {
+        for (int64_t r = 0; r < n; r++) memcpy((uint8_t *)out + (size_t)r * shard_row, src + (size_t)r * row_bytes + (size_t)rank * shard_row, shard_row);
+    } else {
+        memcpy(out, src + (kind == 1 ? (size_t)rank * total : 0), total);
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_map_add_tp(tlb_map *m, const char *name, tlb_ggml_type type, const int64_t *shape, int rank, const void *bytes, size_t nbytes,
+                          int tp_rank, int tp_size)
+{
+    if (!m || !name || (rank > 0 && !shape)) return fail(TLB_ERR_NULL, "null argument");
+    const int kind = rank == 2 ? tlb_tp_split_kind(name) : 0;
+    if (kind == 0 || tp_size <= 1) return tlb_map_add(m, name, type, shape, rank, bytes, nbytes);
+    int64_t sn = 0, sk = 0;
+    size_t sb = 0;
+    TLB_TRY(tlb_tp_shard_bytes(kind, type, shape[0], shape[1], bytes, nbytes, tp_rank, tp_size, nullptr, 0, &sn, &sk, &sb));
+    const int64_t sshape[2] = {sn, sk};
+    if (kind == 1) {   // a contiguous byte range: no copy
+        return tlb_map_add(m, name, type, sshape, 2, (const uint8_t *)bytes + (size_t)tp_rank * sb, sb);
+    }
+    std::vector<uint8_t> tmp(sb);
+    TLB_TRY(tlb_tp_shard_bytes(kind, type, shape[0], shape[1], bytes, nbytes, tp_rank, tp_size, tmp.data(), tmp.size(), &sn, &sk, &sb));
+    return tlb_map_add(m, name, type, sshape, 2, tmp.data(), sb);
 }
 
 tlb_status tlb_map_free(tlb_map *m)

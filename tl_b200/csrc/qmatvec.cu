@@ -36,21 +36,15 @@
 //   * a host-side cost model (slice_cost) picks the number of K-slices per launch shape.
 #include "qmv_prologue.cuh"
 #include "qmv_units.cuh"
-#include "span_trace.cuh"
 
 #include <algorithm>
 
 namespace tlb {
 
-#ifndef TLB_MV_WARPS
-#define TLB_MV_WARPS 16
-#define TLB_MV_CTAS 1
-#define TLB_MV_RESIDENT 1
-#endif
-constexpr int kWarps = TLB_MV_WARPS;
+constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
-constexpr int kCtasPerSm = TLB_MV_CTAS;           // CTAs a launch brings per SM
-constexpr int kResidentPerSm = TLB_MV_RESIDENT;   // CTAs the register and shared-memory budgets allow per SM
+constexpr int kCtasPerSm = 1;       // CTAs a launch brings per SM
+constexpr int kResidentPerSm = 1;   // CTAs the register and shared-memory budgets allow per SM
 
 struct ItemRef {
     const uint8_t *src;   // first unit of the item
@@ -124,10 +118,6 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
     const uint32_t ring = smem_u32(smem) + (uint32_t)(warp * spw) * p.stage_bytes;   // this warp's stages
     const uint32_t bars = smem_u32(smem + p.off_bars) + (uint32_t)(warp * spw) * 8;  // and their barriers
     const int b = blockIdx.x;
-#define STAMP(i) do { if (p.trace && tid == 0) p.trace[(size_t)b * 10 + (i)] = clock64(); } while (0)
-    STAMP(0);
-    if (tid == 0) { span_start(p.span); span_event(p.span, 4); }
-    if (p.trace && tid == 0) p.trace[(size_t)b * 10 + 8] = (long long)global_ns();
 
     // Work of this CTA: a contiguous range of items.  Work of this warp: a contiguous range [wu0, wu1) of
     // the CTA's units in item order.  With K-slices (kb > 1) the ranges are whole items; with one
@@ -148,10 +138,7 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
     // Only the first kEarly units are requested before the prologue: the activation loads of the
     // prologue share the SM's path from L2 with these copies and would otherwise queue behind a whole
     // ring of weights.  The rest of the ring is requested once the activation values have arrived.
-#ifndef TLB_EARLY
-#define TLB_EARLY 2
-#endif
-    constexpr int kEarly = TLB_EARLY;
+    constexpr int kEarly = 2;
     const int n_first = min(spw, n_units);
     const uint8_t *first_src = nullptr;
     if (lane < spw) {
@@ -190,8 +177,6 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         pf_src += p.unit_bytes;
         pf_left_in_item--; pf_remaining--; issued++;
     };
-    STAMP(1);
-    if (tid == 0) span_event(p.span, 5);
 
     float4 wgt_first[kKeep];       // static inputs of the prologue, fetched while the previous kernel finishes
     load_norm_weights(p, tid, kThreads, blk0, nb, wgt_first);
@@ -202,8 +187,6 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         pdl_launch_dependents();
     }
     __syncthreads();               // abort_flag initialised; also keeps the CTA together for the prologue
-    STAMP(2);
-    if (tid == 0) span_event(p.span, 1);
     build_activation<FMT>(p, sh, smem, tid, kThreads, blk0, nb, wgt_first, [&](float dep) {
         // the rest of the ring's first round; the test on `dep` only ties the requests to the arrival of the loads
         if (lane >= kEarly && lane < n_first && __float_as_uint(dep) != 0x7fedcba9u) {
@@ -211,8 +194,6 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
             bulk_g2s(ring + lane * p.stage_bytes, first_src, p.unit_bytes, bars + lane * 8);
         }
     });
-    STAMP(3);
-    if (tid == 0) span_event(p.span, 2);
     volatile int *abortp = &sh->abort_flag;
 
     const int ncols = p.m * p.nl;
@@ -382,10 +363,6 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         // a bounded wait gave up (error word set): give the copies still in flight a bounded time to land
         for (int q = consumed; q < issued; q++) mbar_wait_drain(bars + (q % spw) * 8, (q / spw) & 1);
     }
-    STAMP(6);
-    if (lane == 0) span_event(p.span, 3);
-    if (p.trace && tid == 0) p.trace[(size_t)b * 10 + 9] = (long long)global_ns();
-#undef STAMP
 }
 
 // ---------------------------------------------------------------- host side
@@ -495,10 +472,6 @@ static tlb_status launch_fmt(const MvParams &p, int grid, size_t smem, bool pdl)
         at[na].val.programmaticStreamSerializationAllowed = 1;
         na++;
     }
-    static const bool debug = getenv("TLB_DEBUG") != nullptr;
-    if (debug)
-        fprintf(stderr, "[tlb] qmatvec fmt %d grid %d stages/warp %d smem %zu k %d tiles %d upi %d slices %d blocks/cta %d\n", FMT, grid,
-                p.spw, smem, p.k, p.tiles, p.upi, p.kb, p.nb_max);
     cfg.attrs = at;
     cfg.numAttrs = na;
     TLB_CUDA(cudaLaunchKernelEx(&cfg, qmatvec_kernel<FMT>, p));
@@ -612,8 +585,6 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     if (job.ssq_parts && (job.prologue != PRO_ADD_NORM || job.n_parts < 1)) return fail(TLB_ERR_ARG, "partial sums of squares go with the fused RMSNorm prologue");
     p.err = c->err_flag;
     p.use_pdl = job.pdl ? 1 : 0;
-    p.trace = job.trace;
-    p.span = job.span;
     if (!p.x && !(p.prologue == PRO_ADD_NORM && p.token) && p.prologue != PRO_ATTN_MERGE) return fail(TLB_ERR_NULL, "null activation");
     if (p.prologue == PRO_SILU_MUL && !p.x2) return fail(TLB_ERR_NULL, "null activation");
     if (job.dry_run) return TLB_OK;   // the shape is launchable

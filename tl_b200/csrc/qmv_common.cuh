@@ -194,8 +194,6 @@ struct MvParams {
     const int *token;
     int *err;
     int use_pdl;
-    long long *trace;         // optional: [grid][10] stamps of thread 0 of every CTA (timing studies)
-    unsigned long long *span; // optional: [4] launch-wide timeline stamps (span_trace.cuh)
     // shared-memory offsets (bytes from the start of dynamic shared memory)
     int off_xq, off_alam, off_xsum, off_sa, off_minv, off_bars, off_misc;
     int col_stride;           // bytes between int8 activation columns (nb_max * 256 + 64)

@@ -347,7 +347,7 @@ tlb_status tlb_qtensor_from_gguf_bytes(tlb_qtensor **out, tlb_ggml_type type, in
     q->k = k;
     q->n_tiles = (n + 15) / 16;
     q->upt = k / 256;
-    q->st = storage_alloc((size_t)q->nbytes());
+    q->st = storage_alloc((size_t)q->n_tiles * q->upt * f->unit_bytes);   // nbytes() tells tiled from dense by `st`: not yet set
     if (!q->st) { delete q; return TLB_ERR_ALLOC; }
     if (need) {
         cudaStream_t s = ctx()->stream;

@@ -182,6 +182,8 @@ int tlb_device_id(void) { return g_inited ? g_ctx.device : -1; }
 tlb_status tlb_sync(void)
 {
     if (!ensure_init()) return TLB_ERR_DEVICE;
+    // a synchronisation would invalidate a capture in progress: refuse before CUDA sees it
+    if (g_ctx.capturing) return fail(TLB_ERR_ARG, "this call synchronises with the device, which a stream capture in progress does not allow");
     TLB_CUDA(cudaStreamSynchronize(g_ctx.stream));
     int flag = 0;
     TLB_CUDA(cudaMemcpy(&flag, g_ctx.err_flag, sizeof(int), cudaMemcpyDeviceToHost));
@@ -256,6 +258,7 @@ tlb_status tlb_tensor_from_host(tlb_tensor **out, const void *data, tlb_dtype dt
     if (!out) return fail(TLB_ERR_NULL, "null out");
     *out = nullptr;
     if (rank > 0 && !shape) return fail(TLB_ERR_NULL, "null shape");
+    if (g_inited && g_ctx.capturing) return fail(TLB_ERR_ARG, "tensor_from_host copies from host memory and waits for it: not allowed during a stream capture");
     TLB_TRY(new_tensor(out, dt, shape, rank));
     size_t bytes = (size_t)(*out)->numel() * dtype_size(dt);
     if (bytes) {
@@ -384,7 +387,10 @@ tlb_status tlb_stream_end_capture(tlb_graph **out)
     tg->kernels = g_ctx.launches.load() - g_ctx.capture_launches;
     g_ctx.launches = g_ctx.capture_launches;  // captured launches run only when replayed
     cudaError_t e = cudaGraphGetNodes(g, nullptr, &tg->nodes);
-    if (e == cudaSuccess) e = cudaGraphInstantiate(&tg->exec, g, 0);
+    // Ops captured here allocate their results from the stream-ordered pool, so the graph owns allocation nodes.
+    // AutoFreeOnLaunch: a replay first frees what the previous replay allocated (same addresses again), so a graph
+    // can be replayed any number of times; results of a replay are valid until the next one.
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&tg->exec, g, cudaGraphInstantiateFlagAutoFreeOnLaunch);
     if (e != cudaSuccess) {
         cudaGraphDestroy(g);
         delete tg;

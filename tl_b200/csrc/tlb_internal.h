@@ -197,8 +197,6 @@ struct MatvecJob {
     float *ssq_out = nullptr;
     bool dry_run = false;            // validate and plan only: tells whether the launch would be accepted
     bool last_of_chain = false;      // no matvec follows closely: take half an SM's shared memory instead of a third
-    long long *trace = nullptr;      // optional device buffer [grid][10] of stamps (timing studies)
-    unsigned long long *span = nullptr;   // optional device buffer [4]: timeline of the launch (span_trace.cuh)
 };
 tlb_status launch_qmatvec(const MatvecJob &job);
 // K-slices the kernel wants for a launch of `tiles` 16-row tiles (all tensors) over inner dimension k,
@@ -230,6 +228,12 @@ tlb_status launch_rep_penalty(float *logits, const float *tokens, int64_t rows, 
 tlb_status launch_silu_mul(const float *g, const float *u, float *out, int64_t n);
 tlb_status launch_f32_to_f16(const float *a, __half *out, int64_t n);
 
+// tp.cu: tensor-parallel ranks of this process's communicator (1 / 0 before tlb_tp_init)
+int tp_rank();
+int tp_size();
+tlb_status tp_allreduce(float *x, int64_t n);                                     // x := sum over ranks, in place, on ctx()->stream
+tlb_status tp_allgather(const void *send, void *recv, size_t bytes_per_rank);     // recv[rank] := every rank's send
+
 // attention.cu
 constexpr int kAttnKeysPerSplit = 128;   // keys one CTA of the decode attention covers; splits = ceil((pos + 1) / this)
 struct DecodeAttnJob {
@@ -247,7 +251,6 @@ struct DecodeAttnJob {
     int splits;
     float *out;            // [H*D]
     bool pdl;
-    unsigned long long *span = nullptr;   // optional timeline of the launch (span_trace.cuh)
 };
 tlb_status launch_decode_attention(const DecodeAttnJob &j);
 tlb_status launch_sdpa(const float *q, const float *k, const float *v, const float *mask, int mask_mode,

@@ -1,0 +1,393 @@
+// Tensor-parallel plumbing: one process per GPU, a communicator over the ranks of one node, and the sum of
+// the row-parallel partial results (attn_output, ffn_down) across them.
+//
+// The reference has no multi-GPU path (crates/tl_cuda/src/device.rs:21-27 binds device 0; the collectives of
+// crates/tl_cuda/src/ffi_ops.rs:726-730 are stubs), so there is nothing to mirror: this is the Megatron-style
+// column / row split with one all-reduce after o_proj and one after ffn_down, and an all-gather of per-shard
+// (maximum, index) pairs for the vocabulary-split output head.
+//
+// Two transports, same result on every rank:
+//   * NCCL (ncclAllReduce / ncclAllGather on the library's stream, capturable in the decode graph).  The
+//     library is found at run time (dlopen of libnccl.so.2), so libtlb200 itself does not link against it.
+//   * a one-shot all-reduce over peer memory for the small, latency-bound vectors of decoding (32 KB for a
+//     70B-shaped model): every rank STORES its partial into a staging slot it owns in every peer's memory
+//     (NVLink through NVSwitch), raises a sequence flag on the peer, waits (bounded) for the flags of all
+//     peers in its own memory, and adds the slots in rank order - all loads are local, the sum is bitwise
+//     the same on every rank, and one launch replaces the multi-step NCCL kernel.  Peer mappings come from
+//     CUDA IPC handles the host exchanges (tlb_tp_p2p_export / tlb_tp_p2p_attach).
+// Every wait is bounded: joining the communicator (non-blocking init polled against a deadline, then
+// ncclCommAbort), and the flag wait in the kernel (~1 s, then the context's error word; the host sees
+// TLB_ERR_DEVICE at the next synchronisation).
+#include "tlb_internal.h"
+
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <chrono>
+#include <thread>
+
+namespace tlb {
+
+namespace {
+
+struct NcclApi {
+    void *handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t *, int, ncclUniqueId, int, ncclConfig_t *) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+std::mutex g_tp_mu;
+NcclApi g_nccl;
+
+constexpr int kMaxTp = 8;
+constexpr size_t kP2pMaxFloats = 64 * 1024;   // per rank and buffer: 16 activation rows of a 70B-shaped model (8192 wide), with room
+
+struct P2pRegion {                 // what a rank allocates for its peers to write into (cudaMalloc, exported over IPC)
+    float slots[2][kMaxTp][kP2pMaxFloats];   // [buffer][writer rank][element]
+    unsigned flags[kMaxTp];                  // flags[r]: sequence number of the last all-reduce rank r finished writing here
+};
+
+struct TpState {
+    int rank = 0, size = 1;
+    ncclComm_t comm = nullptr;
+    // peer-memory all-reduce
+    P2pRegion *mine = nullptr;
+    P2pRegion *peer[kMaxTp] = {nullptr};
+    bool p2p = false;
+    unsigned *seq = nullptr;        // device: sequence number of the next all-reduce (advanced by the kernel)
+    int *arrive = nullptr;          // device: CTAs of the running all-reduce that have stored their share
+    double join_timeout_s = 60.0;
+} g_tp;
+
+tlb_status nccl_fail(ncclResult_t r, const char *what)
+{
+    return fail(TLB_ERR_DEVICE, "NCCL error %d (%s) in %s", (int)r, g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "?", what);
+}
+
+tlb_status load_nccl()
+{
+    if (g_nccl.handle) return TLB_OK;
+    const char *path = getenv("TLB_NCCL_LIB");   // another libnccl, or a stand-in that fails on purpose (host-side failure tests)
+    void *h = dlopen(path && *path ? path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h && !(path && *path)) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return fail(TLB_ERR_DEVICE, "cannot load the NCCL library (%s)", dlerror());
+    NcclApi a;
+    a.handle = h;
+#define SYM(field, name) *(void **)(&a.field) = dlsym(h, name); if (!a.field) return fail(TLB_ERR_DEVICE, "NCCL library lacks %s", name)
+    SYM(GetUniqueId, "ncclGetUniqueId");
+    SYM(CommInitRankConfig, "ncclCommInitRankConfig");
+    SYM(CommGetAsyncError, "ncclCommGetAsyncError");
+    SYM(CommAbort, "ncclCommAbort");
+    SYM(CommDestroy, "ncclCommDestroy");
+    SYM(AllReduce, "ncclAllReduce");
+    SYM(AllGather, "ncclAllGather");
+    SYM(GetErrorString, "ncclGetErrorString");
+#undef SYM
+    g_nccl = a;
+    return TLB_OK;
+}
+
+// Polls a non-blocking NCCL call to its end; past the deadline the communicator is aborted.
+tlb_status wait_comm(ncclComm_t comm, double timeout_s, const char *what)
+{
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        ncclResult_t st = ncclSuccess;
+        ncclResult_t r = g_nccl.CommGetAsyncError(comm, &st);
+        if (r != ncclSuccess) return nccl_fail(r, "ncclCommGetAsyncError");
+        if (st == ncclSuccess) return TLB_OK;
+        if (st != ncclInProgress) return nccl_fail(st, what);
+        if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > timeout_s) {
+            g_nccl.CommAbort(comm);
+            return fail(TLB_ERR_DEVICE, "%s: the other ranks did not answer within %.1f s; communicator aborted", what, timeout_s);
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(2));
+    }
+}
+
+// The communicator is non-blocking (so that joining can be bounded): a collective call may answer "in progress"
+// while NCCL still sets up connections; it is on the stream once the communicator reports success again.
+tlb_status finish_call(ncclResult_t r, const char *what)
+{
+    if (r == ncclSuccess) return TLB_OK;
+    if (r != ncclInProgress) return nccl_fail(r, what);
+    return wait_comm(g_tp.comm, g_tp.join_timeout_s, what);
+}
+
+// ---- one-shot all-reduce over peer memory ---------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+struct P2pArgs {
+    P2pRegion *peer[kMaxTp];
+    P2pRegion *mine;
+    unsigned *seq;
+    int *arrive;
+    int *err;
+    int rank, size;
+};
+
+// x[0 .. n) := sum over ranks of their x, n a multiple of 4.  Grid: any number of CTAs; CTA b owns the float4s
+// b, b + grid, ...  (1) store own share into slot [buf][rank] of every rank (own memory included); (2) the last
+// CTA to finish raises flags[rank] = seq on every rank, behind a system-scope fence; (3) wait until the flags of
+// all ranks in OWN memory have reached seq; (4) add the slots in rank order.  Buffers alternate with seq: a rank
+// can be at most one all-reduce ahead of a peer that is still reading.
+__global__ void __launch_bounds__(256) p2p_allreduce_kernel(float *x, int n, const P2pArgs a)
+{
+    __shared__ int s_ok;
+    const unsigned seq = *a.seq;
+    const int buf = seq & 1;
+    const int n4 = n >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+        const float4 v = x4[i];
+        for (int p = 0; p < a.size; p++) reinterpret_cast<float4 *>(a.peer[p]->slots[buf][a.rank])[i] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();                       // this CTA's stores are visible to every GPU before it is counted
+        if (atomicAdd(a.arrive, 1) == (int)gridDim.x - 1) {
+            *a.arrive = 0;
+            __threadfence_system();
+            for (int p = 0; p < a.size; p++) st_release_sys(&a.peer[p]->flags[a.rank], seq);
+        }
+        // bounded wait for every rank's share (about a second, then the error word)
+        bool ok = true;
+        unsigned long long t0 = 0;
+        for (int p = 0; p < a.size && ok; p++) {
+            for (unsigned it = 0;; it++) {
+                if ((int)(ld_acquire_sys(&a.mine->flags[p]) - seq) >= 0) break;
+                if ((it & 255) == 255) {
+                    unsigned long long t;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                    if (!t0) t0 = t;
+                    if (t - t0 > 1000000000ull) { atomicExch(a.err, 31); ok = false; break; }
+                }
+            }
+        }
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (s_ok) {
+        float4 *o4 = reinterpret_cast<float4 *>(x);
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+            float4 acc = __ldcv(reinterpret_cast<const float4 *>(a.mine->slots[buf][0]) + i);
+            for (int p = 1; p < a.size; p++) {
+                const float4 v = __ldcv(reinterpret_cast<const float4 *>(a.mine->slots[buf][p]) + i);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            o4[i] = acc;
+        }
+    }
+    // the next all-reduce uses the next sequence number; one thread of the grid advances it once everyone has read it
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(a.arrive + 1, 1) == (int)gridDim.x - 1) { a.arrive[1] = 0; *a.seq = seq + 1; }
+    }
+}
+
+}  // namespace
+
+int tp_rank() { return g_tp.rank; }
+int tp_size() { return g_tp.size; }
+
+tlb_status tp_allreduce(float *x, int64_t n)
+{
+    Context *c = ctx();
+    if (!c) return fail(TLB_ERR_DEVICE, "no device");
+    if (g_tp.size <= 1) return TLB_OK;
+    if (g_tp.p2p && n % 4 == 0 && (size_t)n <= kP2pMaxFloats && ((uintptr_t)x & 15) == 0) {
+        P2pArgs a;
+        for (int p = 0; p < kMaxTp; p++) a.peer[p] = g_tp.peer[p];
+        a.mine = g_tp.mine; a.seq = g_tp.seq; a.arrive = g_tp.arrive; a.err = c->err_flag; a.rank = g_tp.rank; a.size = g_tp.size;
+        const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(16, (n / 4 + 255) / 256));
+        p2p_allreduce_kernel<<<grid, 256, 0, c->stream>>>(x, (int)n, a);
+        TLB_CUDA(cudaGetLastError());
+        count_launch();
+        return TLB_OK;
+    }
+    if (!g_tp.comm) return fail(TLB_ERR_ARG, "tensor-parallel all-reduce before tlb_tp_init");
+    ncclResult_t r = g_nccl.AllReduce(x, x, (size_t)n, ncclFloat32, ncclSum, g_tp.comm, c->stream);
+    return finish_call(r, "ncclAllReduce");
+}
+
+tlb_status tp_allgather(const void *send, void *recv, size_t bytes_per_rank)
+{
+    Context *c = ctx();
+    if (!c) return fail(TLB_ERR_DEVICE, "no device");
+    if (g_tp.size <= 1) {
+        if (send != recv) TLB_CUDA(cudaMemcpyAsync(recv, send, bytes_per_rank, cudaMemcpyDeviceToDevice, c->stream));
+        return TLB_OK;
+    }
+    if (!g_tp.comm) return fail(TLB_ERR_ARG, "tensor-parallel all-gather before tlb_tp_init");
+    ncclResult_t r = g_nccl.AllGather(send, recv, bytes_per_rank, ncclInt8, g_tp.comm, c->stream);
+    return finish_call(r, "ncclAllGather");
+}
+
+}  // namespace tlb
+
+using namespace tlb;
+
+extern "C" {
+
+tlb_status tlb_tp_unique_id(void *id_out, size_t id_bytes)
+{
+    if (!id_out) return fail(TLB_ERR_NULL, "null id buffer");
+    if (id_bytes < NCCL_UNIQUE_ID_BYTES) return fail(TLB_ERR_ARG, "the id buffer must hold %d bytes", NCCL_UNIQUE_ID_BYTES);
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    TLB_TRY(load_nccl());
+    ncclUniqueId id;
+    ncclResult_t r = g_nccl.GetUniqueId(&id);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclGetUniqueId");
+    memcpy(id_out, &id, NCCL_UNIQUE_ID_BYTES);
+    return TLB_OK;
+}
+
+tlb_status tlb_tp_init(const void *id, size_t id_bytes, int rank, int size, double join_timeout_s)
+{
+    if (!id) return fail(TLB_ERR_NULL, "null id");
+    if (id_bytes < NCCL_UNIQUE_ID_BYTES) return fail(TLB_ERR_ARG, "the id must hold %d bytes", NCCL_UNIQUE_ID_BYTES);
+    if (size < 1 || size > kMaxTp || rank < 0 || rank >= size) return fail(TLB_ERR_ARG, "tensor-parallel rank %d of %d (1..%d ranks)", rank, size, kMaxTp);
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    if (g_tp.comm) return fail(TLB_ERR_ARG, "tlb_tp_init was already called in this process");
+    TLB_TRY(load_nccl());
+    // with the real NCCL a device must be bound; a stand-in library (TLB_NCCL_LIB) may run without one
+    if (ensure_init()) TLB_CUDA(cudaSetDevice(ctx()->device));
+    ncclUniqueId uid;
+    memcpy(&uid, id, NCCL_UNIQUE_ID_BYTES);
+    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+    cfg.blocking = 0;               // returns at once; joining is polled against the deadline below
+    ncclComm_t comm = nullptr;
+    ncclResult_t r = g_nccl.CommInitRankConfig(&comm, size, uid, rank, &cfg);
+    if (r != ncclSuccess && r != ncclInProgress) return nccl_fail(r, "ncclCommInitRankConfig");
+    if (!comm) return fail(TLB_ERR_DEVICE, "ncclCommInitRankConfig returned no communicator");
+    const double timeout = join_timeout_s > 0 ? join_timeout_s : 60.0;
+    TLB_TRY(wait_comm(comm, timeout, "joining the tensor-parallel communicator"));
+    g_tp.comm = comm;
+    g_tp.rank = rank;
+    g_tp.size = size;
+    g_tp.join_timeout_s = timeout;
+    if (ctx() && size > 1) {
+        // one small all-reduce now: NCCL builds its connections on first use, which must not happen inside a graph capture
+        float *w = nullptr;
+        TLB_CUDA(cudaMalloc(&w, 1024 * sizeof(float)));
+        TLB_CUDA(cudaMemsetAsync(w, 0, 1024 * sizeof(float), ctx()->stream));
+        tlb_status st = finish_call(g_nccl.AllReduce(w, w, 1024, ncclFloat32, ncclSum, comm, ctx()->stream), "first ncclAllReduce");
+        if (st == TLB_OK) st = finish_call(g_nccl.AllGather(w, w, 8, ncclInt8, comm, ctx()->stream), "first ncclAllGather");
+        cudaError_t e = cudaStreamSynchronize(ctx()->stream);
+        cudaFree(w);
+        if (st != TLB_OK) return st;
+        if (e != cudaSuccess) return cuda_fail(e, "first collective");
+    }
+    return TLB_OK;
+}
+
+tlb_status tlb_tp_poll(void)
+{
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    if (!g_tp.comm) return TLB_OK;
+    ncclResult_t st = ncclSuccess;
+    ncclResult_t r = g_nccl.CommGetAsyncError(g_tp.comm, &st);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclCommGetAsyncError");
+    if (st != ncclSuccess && st != ncclInProgress) return nccl_fail(st, "an earlier collective");
+    return TLB_OK;
+}
+
+int tlb_tp_rank(void) { return g_tp.rank; }
+int tlb_tp_size(void) { return g_tp.size; }
+
+tlb_status tlb_tp_shutdown(void)
+{
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    if (ctx()) cudaStreamSynchronize(ctx()->stream);
+    for (int p = 0; p < kMaxTp; p++) {
+        if (g_tp.peer[p] && g_tp.peer[p] != g_tp.mine) cudaIpcCloseMemHandle(g_tp.peer[p]);
+        g_tp.peer[p] = nullptr;
+    }
+    if (g_tp.mine) cudaFree(g_tp.mine);
+    if (g_tp.seq) cudaFree(g_tp.seq);
+    if (g_tp.arrive) cudaFree(g_tp.arrive);
+    g_tp.mine = nullptr; g_tp.seq = nullptr; g_tp.arrive = nullptr; g_tp.p2p = false;
+    if (g_tp.comm) g_nccl.CommDestroy(g_tp.comm);
+    g_tp.comm = nullptr;
+    g_tp.rank = 0;
+    g_tp.size = 1;
+    return TLB_OK;
+}
+
+tlb_status tlb_allreduce(tlb_tensor *t)
+{
+    if (!t) return fail(TLB_ERR_NULL, "null tensor");
+    if (t->dt != TLB_F32) return fail(TLB_ERR_TYPE, "all-reduce takes f32 tensors");
+    return tp_allreduce(t->f32(), t->numel());
+}
+
+// Peer-memory transport, step 1: allocate this rank's region and hand out its CUDA IPC handle (64 bytes) for the
+// host to pass to the other ranks of the node.
+tlb_status tlb_tp_p2p_export(void *handle_out, size_t handle_bytes)
+{
+    if (!handle_out) return fail(TLB_ERR_NULL, "null handle buffer");
+    if (handle_bytes < sizeof(cudaIpcMemHandle_t)) return fail(TLB_ERR_ARG, "the handle buffer must hold %zu bytes", sizeof(cudaIpcMemHandle_t));
+    if (!ensure_init()) return TLB_ERR_DEVICE;
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    if (!g_tp.mine) {
+        TLB_CUDA(cudaMalloc((void **)&g_tp.mine, sizeof(P2pRegion)));
+        TLB_CUDA(cudaMemset(g_tp.mine, 0, sizeof(P2pRegion)));
+        TLB_CUDA(cudaMalloc((void **)&g_tp.seq, sizeof(unsigned)));
+        TLB_CUDA(cudaMalloc((void **)&g_tp.arrive, 2 * sizeof(int)));
+        const unsigned one = 1;       // flags start at 0: the first all-reduce waits for 1
+        TLB_CUDA(cudaMemcpy(g_tp.seq, &one, sizeof one, cudaMemcpyHostToDevice));
+        TLB_CUDA(cudaMemset(g_tp.arrive, 0, 2 * sizeof(int)));
+        TLB_CUDA(cudaDeviceSynchronize());
+    }
+    cudaIpcMemHandle_t h;
+    TLB_CUDA(cudaIpcGetMemHandle(&h, g_tp.mine));
+    memcpy(handle_out, &h, sizeof h);
+    return TLB_OK;
+}
+
+// Step 2: the handles of all ranks, in rank order (this rank's own entry is ignored).  After this call all-reduces
+// of up to 65536 floats go over peer memory; larger ones keep using NCCL.  Every rank must have exported before any
+// rank attaches, and all ranks must attach before the first all-reduce (the host's exchange orders both).
+tlb_status tlb_tp_p2p_attach(const void *handles, int n_handles)
+{
+    if (!handles) return fail(TLB_ERR_NULL, "null handles");
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    if (n_handles != g_tp.size) return fail(TLB_ERR_ARG, "%d handles for %d ranks", n_handles, g_tp.size);
+    if (!g_tp.mine) return fail(TLB_ERR_ARG, "tlb_tp_p2p_export must run first");
+    for (int p = 0; p < g_tp.size; p++) {
+        if (p == g_tp.rank) { g_tp.peer[p] = g_tp.mine; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char *)handles + (size_t)p * sizeof h, sizeof h);
+        void *ptr = nullptr;
+        TLB_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        g_tp.peer[p] = (P2pRegion *)ptr;
+    }
+    g_tp.p2p = true;
+    return TLB_OK;
+}
+
+tlb_status tlb_tp_p2p_disable(void)
+{
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    g_tp.p2p = false;
+    return TLB_OK;
+}
+
+}  // extern "C"
