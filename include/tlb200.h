@@ -251,6 +251,9 @@ typedef struct {
      * slices of attn_output / ffn_down (column split) - loaded with tlb_gguf_load_tp / tlb_map_add_tp, after
      * tlb_tp_init; the model sizes above stay those of the WHOLE model.  0 or 1 / 0 for a single GPU. */
     int32_t tp_size, tp_rank;
+    /* sequences the session holds (0 or 1: one).  Every sequence has its own cache rows and position; sequence 0 is the
+     * one the single-sequence entry points (tlb_decoder_step, _generate, _prefill, _kv_write) work on. */
+    int32_t batch;
 } tlb_decoder_cfg;
 
 /* Fills the model sizes of *cfg from the GGUF metadata of a loaded file (<arch>.block_count, .embedding_length, ...;
@@ -277,6 +280,20 @@ tlb_status tlb_decoder_generate(tlb_decoder *d, int32_t first_token, int32_t sta
  * tlb_decoder_logits / tlb_decoder_hidden then describe that last token.  Prompts of 16 tokens or fewer, and
  * shapes the GEMM does not take, run token by token through the fused chain. */
 tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens, int32_t n, int32_t pos0, int32_t rope_pos0, int32_t rope_step, int32_t *next);
+/* ---- a batch of sequences in one session (cfg.batch > 1) ----
+ * The reference's matmul entry takes any number of activation rows (crates/tl_runtime/src/system.rs:180-222) and the TL
+ * program's layers are batch-agnostic (examples/apps/llama3/chatbot_llama3.tl:220-236).  Here one token per sequence goes
+ * through every linear layer as one pass over the weights (tensor-core GEMM, so the session needs the shapes that path
+ * takes), and through attention as independent sequences.  Arrays are indexed by sequence. */
+tlb_status tlb_decoder_kv_write_seq(tlb_decoder *d, int seq, int layer, int pos0, int n, const float *k, const float *v);
+/* a prompt for ONE sequence of the batch (arguments as tlb_decoder_prefill); *next: the greedy token after it */
+tlb_status tlb_decoder_prefill_seq(tlb_decoder *d, int32_t seq, const int32_t *tokens, int32_t n, int32_t pos0, int32_t rope_pos0, int32_t rope_step, int32_t *next);
+/* one token per sequence: tokens[b] at cache row pos[b] (rotation row rope_pos[b]; NULL: pos); next (may be NULL): [batch] */
+tlb_status tlb_decoder_step_batch(tlb_decoder *d, const int32_t *tokens, const int32_t *pos, const int32_t *rope_pos, int32_t *next);
+/* n greedy steps of the whole batch, tokens fed back on the device; tokens_out (may be NULL): [n][batch] */
+tlb_status tlb_decoder_generate_batch(tlb_decoder *d, const int32_t *first_tokens, const int32_t *start_pos, int32_t n, int32_t *tokens_out);
+tlb_status tlb_decoder_logits_batch(tlb_decoder *d, float *logits_out /* host, [batch, vocab] */);
+
 /* tlb_sample_top_p on the logits of the last step or prompt, without bringing them to the host; temp <= 0 returns the
  * greedy token the step chose.  The caller feeds *token to the next tlb_decoder_step. */
 tlb_status tlb_decoder_sample_top_p(tlb_decoder *d, float temp, float top_p, double u, int32_t *token);

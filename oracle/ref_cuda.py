@@ -45,16 +45,16 @@ def _dev(a, dtype=np.float32):
     return torch.from_numpy(np.ascontiguousarray(a, dtype=dtype)).cuda()
 
 
-def _p(t):
-    return C.c_void_p(t.data_ptr())
-
-
 def _run(name, *args):
+    """Calls launch_<name>(args..., stream 0) and waits.  torch tensors among `args` are passed as device pointers and
+    stay referenced here until the kernel has finished (a temporary freed earlier would hand its memory to the next)."""
     import torch
     fn = getattr(lib(), name)
     fn.restype = None
-    fn(*args, C.c_void_p(0))
+    conv = [C.c_void_p(a.data_ptr()) if isinstance(a, torch.Tensor) else (C.c_void_p(0) if a is None else a) for a in args]
+    fn(*conv, C.c_void_p(0))
     torch.cuda.synchronize()
+    del args
 
 
 def _out(shape):
@@ -67,7 +67,7 @@ def mul_mv(t, w_bytes, n, k, x):
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, k)
     m = x.shape[0]
     xd, wd, out = _dev(x), _dev(np.frombuffer(w_bytes, dtype=np.uint8) if not isinstance(w_bytes, np.ndarray) else w_bytes.reshape(-1), np.uint8), _out((m, n))
-    _run({12: "launch_mul_mv_q4_k_kernel", 14: "launch_mul_mv_q6_k_kernel"}[t], _p(xd), _p(wd), _p(out), C.c_int(m), C.c_int(n), C.c_int(k))
+    _run({12: "launch_mul_mv_q4_k_kernel", 14: "launch_mul_mv_q6_k_kernel"}[t], xd, wd, out, C.c_int(m), C.c_int(n), C.c_int(k))
     return out.cpu().numpy()
 
 
@@ -79,7 +79,7 @@ def matmul(a, b):
     batch, m, k = a3.shape
     n = b.shape[-1]
     out = _out((batch, m, n))
-    _run("launch_matmul_kernel", _p(_dev(a3)), _p(_dev(b)), _p(out), C.c_int(m), C.c_int(k), C.c_int(n), C.c_int(batch), C.c_int(int(b.ndim > 2)))
+    _run("launch_matmul_kernel", _dev(a3), _dev(b), out, C.c_int(m), C.c_int(k), C.c_int(n), C.c_int(batch), C.c_int(int(b.ndim > 2)))
     return out.cpu().numpy().reshape(a.shape[:-1] + (n,))
 
 
@@ -88,28 +88,28 @@ def softmax(x, axis):
     axis %= x.ndim
     outer, inner = int(np.prod(x.shape[:axis])), int(np.prod(x.shape[axis + 1:]))
     out = _out(x.shape)
-    _run("launch_softmax_kernel", _p(_dev(x)), _p(out), C.c_int(outer), C.c_int(x.shape[axis]), C.c_int(inner))
+    _run("launch_softmax_kernel", _dev(x), out, C.c_int(outer), C.c_int(x.shape[axis]), C.c_int(inner))
     return out.cpu().numpy()
 
 
 def rms_norm(x, eps):
     x = np.ascontiguousarray(x, dtype=np.float32)
     out = _out(x.shape)
-    _run("launch_rms_norm_kernel", _p(_dev(x)), _p(out), C.c_int(x.size // x.shape[-1]), C.c_int(x.shape[-1]), C.c_float(eps))
+    _run("launch_rms_norm_kernel", _dev(x), out, C.c_int(x.size // x.shape[-1]), C.c_int(x.shape[-1]), C.c_float(eps))
     return out.cpu().numpy()
 
 
 def fused_rms_norm(x, w, eps):
     x = np.ascontiguousarray(x, dtype=np.float32)
     out = _out(x.shape)
-    _run("launch_fused_rms_norm_kernel", _p(_dev(x)), _p(_dev(w)), _p(out), C.c_int(x.size // x.shape[-1]), C.c_int(x.shape[-1]), C.c_float(eps))
+    _run("launch_fused_rms_norm_kernel", _dev(x), _dev(w), out, C.c_int(x.size // x.shape[-1]), C.c_int(x.shape[-1]), C.c_float(eps))
     return out.cpu().numpy()
 
 
 def fused_add_rms_norm(x, res, w, eps):
     x = np.ascontiguousarray(x, dtype=np.float32)
     out = _out(x.shape)
-    _run("launch_fused_add_rms_norm_kernel", _p(_dev(x)), _p(_dev(res)), _p(_dev(w)), _p(out), C.c_int(x.size // x.shape[-1]),
+    _run("launch_fused_add_rms_norm_kernel", _dev(x), _dev(res), _dev(w), out, C.c_int(x.size // x.shape[-1]),
          C.c_int(x.shape[-1]), C.c_float(eps))
     return out.cpu().numpy()
 
@@ -117,7 +117,7 @@ def fused_add_rms_norm(x, res, w, eps):
 def fused_silu_mul(x, up):
     x = np.ascontiguousarray(x, dtype=np.float32)
     out = _out(x.shape)
-    _run("launch_fused_silu_mul_kernel", _p(_dev(x)), _p(_dev(up)), _p(out), C.c_int(x.size))
+    _run("launch_fused_silu_mul_kernel", _dev(x), _dev(up), out, C.c_int(x.size))
     return out.cpu().numpy()
 
 
@@ -126,7 +126,7 @@ def apply_rope(x, cos_t, sin_t):
     x = np.ascontiguousarray(x, dtype=np.float32)
     tokens, heads, dim = x.shape
     out = _out(x.shape)
-    _run("launch_apply_rope_kernel", _p(_dev(x)), _p(_dev(cos_t)), _p(_dev(sin_t)), _p(out), C.c_int(tokens), C.c_int(heads), C.c_int(dim),
+    _run("launch_apply_rope_kernel", _dev(x), _dev(cos_t), _dev(sin_t), out, C.c_int(tokens), C.c_int(heads), C.c_int(dim),
          C.c_int(dim // 2), C.c_int(cos_t.shape[1]), C.c_int(cos_t.shape[0]))
     return out.cpu().numpy()
 
@@ -134,13 +134,13 @@ def apply_rope(x, cos_t, sin_t):
 def argmax_all(x):
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
     out = _out((1,))
-    _run("launch_argmax_all_kernel", _p(_dev(x)), _p(out), C.c_int(x.size))
+    _run("launch_argmax_all_kernel", _dev(x), out, C.c_int(x.size))
     return int(out.cpu().numpy()[0])
 
 
 def causal_mask(n):
     out = _out((n, n))
-    _run("launch_causal_mask_kernel", _p(out), C.c_int(n))
+    _run("launch_causal_mask_kernel", out, C.c_int(n))
     return out.cpu().numpy()
 
 
@@ -150,7 +150,7 @@ def repeat_interleave(x, repeats, axis):
     shp = list(x.shape)
     shp[axis] *= repeats
     out = _out(shp)
-    _run("launch_repeat_interleave_kernel", _p(_dev(x)), _p(out), C.c_int(outer), C.c_int(inner), C.c_int(x.shape[axis]), C.c_int(repeats))
+    _run("launch_repeat_interleave_kernel", _dev(x), out, C.c_int(outer), C.c_int(inner), C.c_int(x.shape[axis]), C.c_int(repeats))
     return out.cpu().numpy()
 
 
@@ -158,7 +158,7 @@ def embedding_f32(table, idx):
     table = np.ascontiguousarray(table, dtype=np.float32)
     idx = np.ascontiguousarray(idx, dtype=np.float32).reshape(-1)
     out = _out((idx.size, table.shape[1]))
-    _run("launch_embedding_f32_kernel", _p(_dev(table)), _p(_dev(idx)), _p(out), C.c_int(idx.size), C.c_int(table.shape[1]), C.c_int(table.shape[0]))
+    _run("launch_embedding_f32_kernel", _dev(table), _dev(idx), out, C.c_int(idx.size), C.c_int(table.shape[1]), C.c_int(table.shape[0]))
     return out.cpu().numpy()
 
 
@@ -166,7 +166,7 @@ def repetition_penalty(logits, tokens, penalty):
     logits = np.ascontiguousarray(logits, dtype=np.float32)
     tokens = np.ascontiguousarray(tokens, dtype=np.float32).reshape(-1)
     out = _out(logits.shape)
-    _run("launch_repetition_penalty_kernel", _p(_dev(logits)), _p(_dev(tokens)), _p(out), C.c_int(logits.shape[-1]), C.c_int(tokens.size),
+    _run("launch_repetition_penalty_kernel", _dev(logits), _dev(tokens), out, C.c_int(logits.shape[-1]), C.c_int(tokens.size),
          C.c_float(penalty), C.c_int(logits.size))
     return out.cpu().numpy()
 
@@ -178,6 +178,6 @@ def sdpa(q, k, v, mask=None):
     sk = k.shape[-2]
     out = _out(q.shape)
     md = _dev(mask) if mask is not None else None
-    _run("launch_sdpa_kernel", _p(_dev(q)), _p(_dev(k)), _p(_dev(v)), _p(md) if md is not None else C.c_void_p(0), _p(out), C.c_int(b), C.c_int(h),
+    _run("launch_sdpa_kernel", _dev(q), _dev(k), _dev(v), md, out, C.c_int(b), C.c_int(h),
          C.c_int(sq), C.c_int(sk), C.c_int(d), C.c_int(int(mask is not None)))
     return out.cpu().numpy()

@@ -362,12 +362,13 @@ class Graph:
 class Decoder:
     """Fused decode session over a TensorMap holding a Llama-shaped model."""
 
-    def __init__(self, cfg, weights, kv_f16=True, max_seq=4096, tie_rule=TIE_LAST, tp_size=1, tp_rank=0):
+    def __init__(self, cfg, weights, kv_f16=True, max_seq=4096, tie_rule=TIE_LAST, tp_size=1, tp_rank=0, batch=1):
         self.cfg = DecoderCfg(n_layers=cfg["n_layers"], d_model=cfg["d_model"], n_heads=cfg["n_heads"],
                               n_kv_heads=cfg["n_kv_heads"], head_dim=cfg["head_dim"], ffn=cfg["ffn"],
                               vocab=cfg["vocab"], eps=cfg["eps"], rope_base=cfg["rope_base"],
                               attn_scale=cfg["attn_scale"], kv_f16=int(kv_f16), max_seq=max_seq,
-                              tie_rule=tie_rule, tp_size=tp_size, tp_rank=tp_rank)
+                              tie_rule=tie_rule, tp_size=tp_size, tp_rank=tp_rank, batch=batch)
+        self.batch = max(1, batch)
         self.h = C.c_void_p()
         check(lib().tlb_decoder_create(C.byref(self.h), C.byref(self.cfg), weights.h))
 
@@ -401,6 +402,41 @@ class Decoder:
         out = (C.c_int32 * max(1, n))()
         check(lib().tlb_decoder_generate(self.h, first_token, start_pos, n, out if read else None))
         return [out[i] for i in range(n)] if read else None
+
+    # ---- batch sessions (batch > 1): arrays are indexed by sequence
+    def kv_write_seq(self, seq, layer, pos0, k, v):
+        k = np.ascontiguousarray(k, dtype=np.float32)
+        v = np.ascontiguousarray(v, dtype=np.float32)
+        check(lib().tlb_decoder_kv_write_seq(self.h, seq, layer, pos0, k.shape[0], k.ctypes.data_as(C.c_void_p), v.ctypes.data_as(C.c_void_p)))
+
+    def prefill_seq(self, seq, tokens, pos0=0, rope_pos0=None, rope_step=1, read=True):
+        toks = (C.c_int32 * max(1, len(tokens)))(*[int(t) for t in tokens])
+        nxt = C.c_int32(-1)
+        check(lib().tlb_decoder_prefill_seq(self.h, seq, toks, len(tokens), pos0, pos0 if rope_pos0 is None else rope_pos0, rope_step,
+                                            C.byref(nxt) if read else None))
+        return nxt.value
+
+    def step_batch(self, tokens, pos, rope_pos=None, read=True):
+        B = self.batch
+        t = (C.c_int32 * B)(*[int(x) for x in tokens])
+        p = (C.c_int32 * B)(*[int(x) for x in pos])
+        r = (C.c_int32 * B)(*[int(x) for x in rope_pos]) if rope_pos is not None else None
+        out = (C.c_int32 * B)()
+        check(lib().tlb_decoder_step_batch(self.h, t, p, r, out if read else None))
+        return [out[i] for i in range(B)] if read else None
+
+    def generate_batch(self, first_tokens, start_pos, n, read=True):
+        B = self.batch
+        t = (C.c_int32 * B)(*[int(x) for x in first_tokens])
+        p = (C.c_int32 * B)(*[int(x) for x in start_pos])
+        out = (C.c_int32 * max(1, n * B))()
+        check(lib().tlb_decoder_generate_batch(self.h, t, p, n, out if read else None))
+        return np.array(out[:n * B], dtype=np.int64).reshape(n, B) if read else None
+
+    def logits_batch(self):
+        out = np.empty((self.batch, self.cfg.vocab), dtype=np.float32)
+        check(lib().tlb_decoder_logits_batch(self.h, out.ctypes.data_as(C.c_void_p)))
+        return out
 
     def logits(self):
         out = np.empty(self.cfg.vocab, dtype=np.float32)

@@ -27,7 +27,7 @@ class DecoderCfg(C.Structure):
                 ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("ffn", C.c_int32), ("vocab", C.c_int32),
                 ("eps", C.c_float), ("rope_base", C.c_float), ("attn_scale", C.c_float),
                 ("kv_f16", C.c_int32), ("max_seq", C.c_int32), ("tie_rule", C.c_int32),
-                ("tp_size", C.c_int32), ("tp_rank", C.c_int32)]
+                ("tp_size", C.c_int32), ("tp_rank", C.c_int32), ("batch", C.c_int32)]
 
 
 def declared_symbols():
@@ -102,6 +102,12 @@ def lib():
     d("tlb_decoder_logits", S, vp, vp); d("tlb_decoder_hidden", S, vp, vp)
     d("tlb_decoder_stats", S, vp, i32, C.POINTER(u64), C.POINTER(u64), C.POINTER(i32))
     d("tlb_decoder_time_kernel", S, vp, C.c_char_p, C.c_int, C.c_int, C.POINTER(f32), C.POINTER(u64))
+    pi32 = C.POINTER(i32)
+    d("tlb_decoder_kv_write_seq", S, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp)
+    d("tlb_decoder_prefill_seq", S, vp, i32, pi32, i32, i32, i32, i32, pi32)
+    d("tlb_decoder_step_batch", S, vp, pi32, pi32, pi32, pi32)
+    d("tlb_decoder_generate_batch", S, vp, pi32, pi32, i32, pi32)
+    d("tlb_decoder_logits_batch", S, vp, vp)
     d("tlb_tp_unique_id", S, vp, sz); d("tlb_tp_init", S, vp, sz, C.c_int, C.c_int, C.c_double); d("tlb_tp_poll", S)
     d("tlb_tp_shutdown", S); d("tlb_tp_rank", C.c_int); d("tlb_tp_size", C.c_int); d("tlb_allreduce", S, vp)
     d("tlb_tp_p2p_export", S, vp, sz); d("tlb_tp_p2p_attach", S, vp, C.c_int); d("tlb_tp_p2p_disable", S)

@@ -47,7 +47,11 @@ template <> struct KvTraits<float> {
 };
 
 struct AttnParams {
-    const float *qkv;
+    // new projections of sequence b: q + b * q_stride ([H * D]), k + b * kv_stride, v + b * kv_stride ([KVH * D]) floats
+    const float *q, *k, *v;
+    int q_stride, kv_stride;
+    size_t cache_seq_bytes;   // bytes between the caches of consecutive sequences (0 for one sequence)
+    int state_stride;         // ints between the pos / rope_pos entries of consecutive sequences
     void *kcache, *vcache;
     int H, KVH, D, max_seq;
     const int *pos, *rope_pos;
@@ -62,7 +66,6 @@ struct AttnParams {
     int row_stride;   // shared-memory row stride in bytes (16-byte chunks, count = 4 mod 8: conflict-free)
 };
 
-__device__ __forceinline__ float ld_qkv(const AttnParams &p, size_t i) { return __ldcg(p.qkv + i); }
 
 template <typename T, int REP>
 __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const AttnParams p)
@@ -70,7 +73,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int E = KvTraits<T>::E;
     const int D = p.D, tid = threadIdx.x;
-    const int kvh = blockIdx.y, split = blockIdx.x;
+    const int kvh = blockIdx.y, split = blockIdx.x, seq = blockIdx.z;   // one grid plane per sequence of a batch
     const int RC = D / E;                // 16-byte chunks per row
     const int RS = p.row_stride;
     uint8_t *Ks = smem;
@@ -83,7 +86,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
 
     // Cache length and this CTA's key range.  pos was written at the end of the previous decode
     // step, which every predecessor of this launch has already waited for.
-    const int pos = *p.pos;
+    const int pos = p.pos[(size_t)seq * p.state_stride];
     const int Tlen = pos + 1;
     const int nsplit = (Tlen + kKeysPerCta - 1) / kKeysPerCta;
     if (split >= nsplit) return;
@@ -92,8 +95,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
 
     // stage K and V rows [t0, t1) (rows of earlier tokens; row `pos` is patched below)
     {
-        const T *kc = reinterpret_cast<const T *>(p.kcache) + ((size_t)kvh * p.max_seq + t0) * D;
-        const T *vc = reinterpret_cast<const T *>(p.vcache) + ((size_t)kvh * p.max_seq + t0) * D;
+        const T *kc = reinterpret_cast<const T *>(reinterpret_cast<const uint8_t *>(p.kcache) + seq * p.cache_seq_bytes) + ((size_t)kvh * p.max_seq + t0) * D;
+        const T *vc = reinterpret_cast<const T *>(reinterpret_cast<const uint8_t *>(p.vcache) + seq * p.cache_seq_bytes) + ((size_t)kvh * p.max_seq + t0) * D;
         const uint32_t ks = (uint32_t)__cvta_generic_to_shared(Ks), vs = (uint32_t)__cvta_generic_to_shared(Vs);
         for (int i = tid; i < nk * RC; i += kAttnThreads) {
             int key = i / RC, ch = i - key * RC;
@@ -107,7 +110,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
     // Thread i < REP * D/2 rotates pair i of the REP query heads; in the CTA whose range holds row `pos`,
     // thread i < D/2 also rotates pair i of the new K and appends K and V.
     static_assert(REP * 64 <= kAttnThreads, "one query pair per thread");
-    const int rp = *p.rope_pos;
+    const int rp = p.rope_pos[(size_t)seq * p.state_stride];
     const float *cs = p.cos_t + (size_t)rp * D, *sn = p.sin_t + (size_t)rp * D;
     const bool rot_q = tid < REP * (D / 2);
     const bool app = pos >= t0 && pos < t1 && tid < D / 2;
@@ -121,10 +124,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
     }
     // all loads of the new projections first (one round trip), then the arithmetic
     float q0 = 0.f, q1 = 0.f, k0f = 0.f, k1f = 0.f, v0f = 0.f, v1f = 0.f;
-    const size_t qi = (size_t)(kvh * REP + hq) * D + jq;
-    const size_t kn = (size_t)p.H * D + (size_t)kvh * D, vn = (size_t)(p.H + p.KVH) * D + (size_t)kvh * D;
-    if (rot_q) { q0 = ld_qkv(p, qi); q1 = ld_qkv(p, qi + 1); }
-    if (app) { k0f = ld_qkv(p, kn + jk); k1f = ld_qkv(p, kn + jk + 1); v0f = ld_qkv(p, vn + jk); v1f = ld_qkv(p, vn + jk + 1); }
+    const float *qrow = p.q + (size_t)seq * p.q_stride + (size_t)(kvh * REP + hq) * D + jq;
+    const float *krow_new = p.k + (size_t)seq * p.kv_stride + (size_t)kvh * D + jk, *vrow_new = p.v + (size_t)seq * p.kv_stride + (size_t)kvh * D + jk;
+    if (rot_q) { q0 = __ldcg(qrow); q1 = __ldcg(qrow + 1); }
+    if (app) { k0f = __ldcg(krow_new); k1f = __ldcg(krow_new + 1); v0f = __ldcg(vrow_new); v1f = __ldcg(vrow_new + 1); }
     // RoPE (crates/tl_cpu/src/ffi.rs:2629-2685: adjacent pairs, one table row) of the REP query heads
     if (rot_q) {
         qs[hq * D + jq] = __fsub_rn(__fmul_rn(q0, cq), __fmul_rn(q1, sq));
@@ -132,8 +135,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
     }
     // the CTA whose range holds row `pos` appends the new token's K (roped) and V
     if (app) {
-        T *kc = reinterpret_cast<T *>(p.kcache) + ((size_t)kvh * p.max_seq + pos) * D;
-        T *vc = reinterpret_cast<T *>(p.vcache) + ((size_t)kvh * p.max_seq + pos) * D;
+        T *kc = reinterpret_cast<T *>(reinterpret_cast<uint8_t *>(p.kcache) + seq * p.cache_seq_bytes) + ((size_t)kvh * p.max_seq + pos) * D;
+        T *vc = reinterpret_cast<T *>(reinterpret_cast<uint8_t *>(p.vcache) + seq * p.cache_seq_bytes) + ((size_t)kvh * p.max_seq + pos) * D;
         T *krow = reinterpret_cast<T *>(Ks + (size_t)(pos - t0) * RS), *vrow = reinterpret_cast<T *>(Vs + (size_t)(pos - t0) * RS);
         T k0 = KvTraits<T>::store(__fsub_rn(__fmul_rn(k0f, ck), __fmul_rn(k1f, sk)));
         T k1 = KvTraits<T>::store(__fadd_rn(__fmul_rn(k0f, sk), __fmul_rn(k1f, ck)));
@@ -218,13 +221,14 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
             *reinterpret_cast<float2 *>(accbuf + ((size_t)kg * REP + h) * D + 2 * dp) = make_float2(acc[h][0], acc[h][1]);
     }
     __syncthreads();
-    float *part = p.partial + ((size_t)kvh * p.max_splits + split) * REP * (D + 4);
+    const int kvh_all = seq * p.KVH + kvh;        // (sequence, KV head) as one index into the per-head scratch and outputs
+    float *part = p.partial + ((size_t)kvh_all * p.max_splits + split) * REP * (D + 4);
     for (int i = tid; i < REP * D; i += kAttnThreads) {
         float s = 0.f;
         for (int g = 0; g < NG; g++) s += accbuf[(size_t)g * REP * D + i];
         int h = i / D, d = i - h * D;
         if (nsplit == 1 && !p.defer_merge) {
-            p.out[(size_t)(kvh * REP + h) * D + d] = s / ml[h * 2 + 1];
+            p.out[(size_t)(kvh_all * REP + h) * D + d] = s / ml[h * 2 + 1];
         } else {
             part[h * (D + 4) + d] = s;
         }
@@ -236,13 +240,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        int old = atomicAdd(p.counters + kvh, 1);
+        int old = atomicAdd(p.counters + kvh_all, 1);
         is_last = (old == nsplit - 1);
     }
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    const float *base = p.partial + (size_t)kvh * p.max_splits * REP * (D + 4);
+    const float *base = p.partial + (size_t)kvh_all * p.max_splits * REP * (D + 4);
     for (int i = tid; i < REP * D; i += kAttnThreads) {
         int h = i / D, d = i - h * D;
         float M = -INFINITY;
@@ -256,9 +260,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1) decode_attention_kernel(const
             L += __ldcg(ps + D + 1) * w;
             O += __ldcg(ps + d) * w;
         }
-        p.out[(size_t)(kvh * REP + h) * D + d] = O / L;
+        p.out[(size_t)(kvh_all * REP + h) * D + d] = O / L;
     }
-    if (tid == 0) p.counters[kvh] = 0;
+    if (tid == 0) p.counters[kvh_all] = 0;
 }
 
 static int attn_row_stride(int D, int esize)
@@ -269,7 +273,7 @@ static int attn_row_stride(int D, int esize)
 }
 
 template <typename T, int REP>
-static tlb_status launch_decode_t(const AttnParams &p, int max_splits, int KVH, bool pdl)
+static tlb_status launch_decode_t(const AttnParams &p, int max_splits, int KVH, int batch, bool pdl)
 {
     int NG = kAttnThreads / (p.D / 2);
     size_t smem = (size_t)2 * kKeysPerCta * p.row_stride + (size_t)(REP * p.D + kKeysPerCta * REP + REP * 2 + NG * REP * p.D) * sizeof(float);
@@ -282,7 +286,7 @@ static tlb_status launch_decode_t(const AttnParams &p, int max_splits, int KVH, 
         set_bytes = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(max_splits, KVH);
+    cfg.gridDim = dim3(max_splits, KVH, batch);
     cfg.blockDim = dim3(kAttnThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx()->stream;
@@ -304,7 +308,11 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     if (j.H % j.KVH) return fail(TLB_ERR_SHAPE, "query heads must be a multiple of KV heads");
     int rep = j.H / j.KVH;
     AttnParams p;
-    p.qkv = j.qkv; p.kcache = j.kcache; p.vcache = j.vcache;
+    const int batch = j.batch > 1 ? j.batch : 1;
+    if (j.q) { p.q = j.q; p.k = j.k; p.v = j.v; p.q_stride = j.H * j.D; p.kv_stride = j.KVH * j.D; }
+    else { p.q = j.qkv; p.k = j.qkv + (size_t)j.H * j.D; p.v = j.qkv + (size_t)(j.H + j.KVH) * j.D; p.q_stride = p.kv_stride = 0; }
+    p.cache_seq_bytes = j.cache_seq_bytes; p.state_stride = j.state_stride;
+    p.kcache = j.kcache; p.vcache = j.vcache;
     p.H = j.H; p.KVH = j.KVH; p.D = j.D; p.max_seq = j.max_seq;
     p.pos = j.pos; p.rope_pos = j.rope_pos; p.cos_t = j.cos_t; p.sin_t = j.sin_t; p.scale = j.scale;
     p.defer_merge = j.defer_merge ? 1 : 0;
@@ -313,8 +321,8 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     p.row_stride = attn_row_stride(j.D, j.kv_f16 ? 2 : 4);
 #define DISPATCH(REPV)                                                                         \
     if (rep == REPV)                                                                           \
-        return j.kv_f16 ? launch_decode_t<__half, REPV>(p, j.splits, j.KVH, j.pdl)             \
-                        : launch_decode_t<float, REPV>(p, j.splits, j.KVH, j.pdl);
+        return j.kv_f16 ? launch_decode_t<__half, REPV>(p, j.splits, j.KVH, batch, j.pdl)      \
+                        : launch_decode_t<float, REPV>(p, j.splits, j.KVH, batch, j.pdl);
     DISPATCH(1) DISPATCH(2) DISPATCH(4) DISPATCH(8)
 #undef DISPATCH
     return fail(TLB_ERR_SHAPE, "decode attention supports 1, 2, 4 or 8 query heads per KV head, got %d", rep);

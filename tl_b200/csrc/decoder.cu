@@ -56,6 +56,16 @@ struct tlb_decoder {
     // hidden units, vocabulary rows of this shard); they equal the model's sizes for tp == 1.
     int tp = 1, tp_r = 0;
     int H = 0, KVH = 0, F = 0, V = 0;
+    // batch of sequences (cfg.batch > 1): caches [batch][layer][KV head][max_seq][D]; sequence 0 is also the sequence the
+    // single-sequence entry points work on.  Rows of the b* buffers are sequences.
+    int B = 1;
+    size_t kv_seq_bytes = 0;      // bytes between the caches of consecutive sequences
+    int *btok = nullptr, *bpos = nullptr, *brope = nullptr, *bidx = nullptr;   // per-sequence token / cache row / rotation row; output index
+    float *bx = nullptr, *bx2 = nullptr, *bq = nullptr, *bk = nullptr, *bv = nullptr, *battn = nullptr, *bg = nullptr, *bu = nullptr, *bt = nullptr;
+    float *blogits = nullptr, *blogits_all = nullptr, *bpartial = nullptr, *bpair = nullptr;
+    int *bcounters = nullptr, *btokens_out = nullptr;
+    cudaGraphExec_t bgraph = nullptr;
+    uint64_t bgraph_kernels = 0;
     float *part = nullptr;        // tp > 1: this rank's partial o_proj / ffn_down result, summed over the ranks in place
     float *pair = nullptr;        // tp > 1: (best logit, its global index) of this shard, then of every shard [1 + tp][2]
     float *logits_all = nullptr;  // tp > 1: the gathered logits of all shards (tlb_decoder_logits)
@@ -431,6 +441,206 @@ tlb_status enqueue_step(tlb_decoder *d)
     return TLB_OK;
 }
 
+
+// ---- a batch of sequences, one new token each ------------------------------------------------------------------
+// The reference's matmul entry takes any number of rows (crates/tl_runtime/src/system.rs:180-222) and the TL program's
+// projections are batch-agnostic (examples/apps/llama3/chatbot_llama3.tl:220-236): here the B new tokens go through the
+// linear layers as B rows of ONE pass over the weights (tensor-core GEMM with on-the-fly dequantisation; the weight
+// stream, the cost of decoding, is shared by the batch), and through attention as B independent sequences, each with
+// its own cache, position and split-K reduction (one grid plane per sequence).
+
+// out[i] = a[i] + b[i]
+__global__ void add_rows_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, int64_t n4)
+{
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 x = reinterpret_cast<const float4 *>(a)[i], y = reinterpret_cast<const float4 *>(b)[i];
+        reinterpret_cast<float4 *>(out)[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+    }
+}
+
+// Block b: argmax of logits row b (n entries; tie rule as tlb_argmax).  pairs == null: the token goes straight to the
+// sequence's state (rows [row0, row0 + gridDim.x)).  Otherwise (vocabulary split over ranks) the (value, global index)
+// pair of this shard goes to pairs[b] for the exchange.
+__global__ void __launch_bounds__(512) argmax_rows_kernel(const float *__restrict__ logits, int n, int tie_first, int offset, float *pairs,
+                                                           int *tok, int *pos, int *rope, const int *idx, int *tokens_out, int B, int cap, int row0)
+{
+    __shared__ float sv[16];
+    __shared__ int si[16];
+    const float *x = logits + (size_t)blockIdx.x * n;
+    float bv = 0.f;
+    int bi = -1;
+    auto better = [&](float v, int i, float cv, int ci) { return ci < 0 || v > cv || (v == cv && (tie_first ? i < ci : i > ci)); };
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = __ldcg(x + i);
+        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+    for (int o = 16; o; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+        if (si[w] >= 0 && better(sv[w], si[w], bv, bi)) { bv = sv[w]; bi = si[w]; }
+    bi = max(bi, 0) + offset;
+    if (pairs) { pairs[2 * blockIdx.x] = bv; pairs[2 * blockIdx.x + 1] = (float)bi; return; }
+    const int b = row0 + blockIdx.x;
+    if (tokens_out && *idx < cap) tokens_out[(size_t)*idx * B + b] = bi;
+    tok[b] = bi; pos[b] += 1; rope[b] += 1;
+}
+
+// After the exchange: pairs[rank][row][2]; thread `row` picks the winner over the ranks and updates the state.
+__global__ void argmax_rows_pick_kernel(const float *__restrict__ pairs, int tp, int rows, int tie_first, int *tok, int *pos, int *rope,
+                                        const int *idx, int *tokens_out, int B, int cap, int row0)
+{
+    const int r = threadIdx.x;
+    if (r >= rows) return;
+    float bv = pairs[2 * r];
+    int bi = (int)pairs[2 * r + 1];
+    for (int k = 1; k < tp; k++) {
+        const float v = pairs[((size_t)k * rows + r) * 2];
+        const int i = (int)pairs[((size_t)k * rows + r) * 2 + 1];
+        if (v > bv || (v == bv && (tie_first ? i < bi : i > bi))) { bv = v; bi = i; }
+    }
+    const int b = row0 + r;
+    if (tokens_out && *idx < cap) tokens_out[(size_t)*idx * B + b] = bi;
+    tok[b] = bi; pos[b] += 1; rope[b] += 1;
+}
+
+__global__ void bump_index_kernel(int *idx) { *idx += 1; }
+
+tlb_status add_rows(const float *a, const float *b, float *out, int64_t n)
+{
+    add_rows_kernel<<<(unsigned)std::min<int64_t>(1184, (n / 4 + 255) / 256), 256, 0, ctx()->stream>>>(a, b, out, n / 4);
+    TLB_CUDA(cudaGetLastError());
+    count_launch();
+    return TLB_OK;
+}
+
+// out = [resid +] act . W^T; with tensor parallelism W is this rank's slice of the inner dimension, the result a partial
+// sum: summed over the ranks first, the residual added afterwards.
+tlb_status row_parallel(tlb_decoder *d, const tlb_qtensor *w, const GemmAct &a, float *out, const float *resid, float *scratch, int64_t rows)
+{
+    if (d->tp <= 1) return qgemm_run(w, a, out, resid);
+    TLB_TRY(qgemm_run(w, a, scratch, nullptr));
+    TLB_TRY(tp_allreduce(scratch, rows * d->cfg.d_model));
+    return add_rows(resid, scratch, out, rows * d->cfg.d_model);
+}
+
+// output_norm + head + greedy tokens for `rows` residual rows x (sequences row0 ..): logits to blogits[row0 ..]
+tlb_status batch_head(tlb_decoder *d, const float *x, int rows, int row0)
+{
+    const tlb_decoder_cfg &c = d->cfg;
+    const int tie_first = c.tie_rule == TLB_TIE_FIRST;
+    GemmAct a;
+    TLB_TRY(qgemm_prepare(&a, x, nullptr, rows, c.d_model, d->out_norm->f32(), c.eps));
+    float *lg = d->blogits + (size_t)row0 * d->V;
+    tlb_status st = qgemm_run(d->head, a, lg, nullptr);
+    qgemm_release(&a);
+    TLB_TRY(st);
+    if (d->tp > 1) {
+        argmax_rows_kernel<<<rows, 512, 0, ctx()->stream>>>(lg, d->V, tie_first, d->tp_r * d->V, d->bpair, nullptr, nullptr, nullptr, nullptr, nullptr, d->B, 0, row0);
+        TLB_CUDA(cudaGetLastError());
+        TLB_TRY(tp_allgather(d->bpair, d->bpair + 2 * d->B, (size_t)rows * 2 * sizeof(float)));
+        argmax_rows_pick_kernel<<<1, 32, 0, ctx()->stream>>>(d->bpair + 2 * d->B, d->tp, rows, tie_first, d->btok, d->bpos, d->brope, d->bidx, d->btokens_out, d->B, d->tokens_cap, row0);
+        TLB_CUDA(cudaGetLastError());
+        count_launch(2);
+    } else {
+        argmax_rows_kernel<<<rows, 512, 0, ctx()->stream>>>(lg, d->V, tie_first, 0, nullptr, d->btok, d->bpos, d->brope, d->bidx, d->btokens_out, d->B, d->tokens_cap, row0);
+        TLB_CUDA(cudaGetLastError());
+        count_launch();
+    }
+    return TLB_OK;
+}
+
+bool prefill_batched_ok(const tlb_decoder *d);
+
+tlb_status enqueue_step_batch(tlb_decoder *d)
+{
+    const tlb_decoder_cfg &c = d->cfg;
+    const int B = d->B, dm = c.d_model, qd = d->H * c.head_dim, kvd = d->KVH * c.head_dim, F = d->F;
+    const size_t esz = c.kv_f16 ? 2 : 4;
+    TLB_TRY(launch_embed_rows(d->btok, d->emb->f32(), d->bx, B, dm));
+    float *x = d->bx, *x2 = d->bx2;
+    for (int l = 0; l < c.n_layers; l++) {
+        const LayerW &w = d->layers[l];
+        GemmAct a;
+        tlb_status st = TLB_OK;
+        TLB_TRY(qgemm_prepare(&a, x, nullptr, B, dm, w.attn_norm->f32(), c.eps));
+        {
+            const tlb_qtensor *ws3[3] = {w.q, w.k, w.v};
+            float *outs3[3] = {d->bq, d->bk, d->bv};
+            bool done3[3] = {false, false, false};
+            for (int i = 0; i < 3 && st == TLB_OK; i++) {
+                if (done3[i]) continue;
+                const tlb_qtensor *gw[3];
+                float *go[3];
+                int gn = 0;
+                for (int b = i; b < 3; b++)
+                    if (!done3[b] && ws3[b]->type == ws3[i]->type) { gw[gn] = ws3[b]; go[gn++] = outs3[b]; done3[b] = true; }
+                st = qgemm_run_multi(gw, gn, a, go, nullptr);
+            }
+        }
+        qgemm_release(&a);
+        TLB_TRY(st);
+        {   // RoPE, cache append and split-K attention of every sequence over its own cache
+            DecodeAttnJob j;
+            j.q = d->bq; j.k = d->bk; j.v = d->bv; j.batch = B;
+            j.cache_seq_bytes = d->kv_seq_bytes; j.state_stride = 1;
+            j.kcache = (char *)d->kcache + (size_t)l * d->kv_layer_elems * esz;
+            j.vcache = (char *)d->vcache + (size_t)l * d->kv_layer_elems * esz;
+            j.kv_f16 = c.kv_f16; j.H = d->H; j.KVH = d->KVH; j.D = c.head_dim; j.max_seq = c.max_seq;
+            j.pos = d->bpos; j.rope_pos = d->brope; j.cos_t = d->cos_t; j.sin_t = d->sin_t; j.scale = c.attn_scale;
+            j.partial = d->bpartial; j.counters = d->bcounters; j.splits = d->max_splits; j.out = d->battn; j.pdl = false;
+            j.defer_merge = false;
+            TLB_TRY(launch_decode_attention(j));
+        }
+        TLB_TRY(qgemm_prepare(&a, d->battn, nullptr, B, qd, nullptr, 0.f));
+        st = row_parallel(d, w.o, a, x2, x, d->bt, B);        // x2 = x + o_proj(attention)
+        qgemm_release(&a);
+        TLB_TRY(st);
+        TLB_TRY(qgemm_prepare(&a, x2, nullptr, B, dm, w.ffn_norm->f32(), c.eps));
+        {
+            const tlb_qtensor *ws2[2] = {w.gate, w.up};
+            float *outs2[2] = {d->bg, d->bu};
+            st = qgemm_run_multi(ws2, 2, a, outs2, nullptr);
+        }
+        qgemm_release(&a);
+        TLB_TRY(st);
+        TLB_TRY(launch_silu_mul(d->bg, d->bu, d->bg, (int64_t)B * F));
+        TLB_TRY(qgemm_prepare(&a, d->bg, nullptr, B, F, nullptr, 0.f));
+        st = row_parallel(d, w.down, a, x, x2, d->bt, B);     // x = x2 + down(silu(gate) * up)
+        qgemm_release(&a);
+        TLB_TRY(st);
+    }
+    TLB_TRY(batch_head(d, x, B, 0));
+    bump_index_kernel<<<1, 1, 0, ctx()->stream>>>(d->bidx);
+    TLB_CUDA(cudaGetLastError());
+    count_launch();
+    return TLB_OK;
+}
+
+tlb_status ensure_batch_graph(tlb_decoder *d)
+{
+    if (d->bgraph) return TLB_OK;
+    Context *cx = ctx();
+    uint64_t before = cx->launches.load();
+    TLB_CUDA(cudaStreamBeginCapture(cx->stream, cudaStreamCaptureModeThreadLocal));
+    tlb_status st = enqueue_step_batch(d);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(cx->stream, &g);
+    d->bgraph_kernels = cx->launches.load() - before;
+    cx->launches = before;
+    if (st != TLB_OK) { if (g) cudaGraphDestroy(g); return st; }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
+    e = cudaGraphInstantiate(&d->bgraph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+    return TLB_OK;
+}
+
 tlb_status ensure_graph(tlb_decoder *d)
 {
     if (d->graph) return TLB_OK;
@@ -467,6 +677,7 @@ tlb_status tlb_decoder_destroy(tlb_decoder *d)
     if (!d) return TLB_OK;
     if (ctx()) cudaStreamSynchronize(ctx()->stream);
     if (d->graph) cudaGraphExecDestroy(d->graph);
+    if (d->bgraph) cudaGraphExecDestroy(d->bgraph);
     for (LayerW &w : d->layers) {
         tlb_qtensor_release(w.q); tlb_qtensor_release(w.k); tlb_qtensor_release(w.v); tlb_qtensor_release(w.o);
         tlb_qtensor_release(w.gate); tlb_qtensor_release(w.up); tlb_qtensor_release(w.down); tlb_qtensor_release(w.gu);
@@ -501,8 +712,10 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
             return fail(TLB_ERR_SHAPE, "a rank's slice of ffn (%d) and of the attention width (%d) must be multiples of 256", c.ffn / tp, (c.n_heads / tp) * c.head_dim);
         if ((int64_t)c.vocab >= (1 << 24)) return fail(TLB_ERR_SHAPE, "vocabulary too large for the index exchange");
     }
+    if (c.batch < 0 || c.batch > 64) return fail(TLB_ERR_ARG, "batch %d: a session holds 1 to 64 sequences", c.batch);
     tlb_decoder *d = new tlb_decoder();
     d->cfg = c;
+    d->B = c.batch > 1 ? c.batch : 1;
     d->tp = tp; d->tp_r = tp_r;
     d->H = c.n_heads / tp; d->KVH = c.n_kv_heads / tp; d->F = c.ffn / tp; d->V = c.vocab / tp;
     // local sizes: the shapes this rank's tensors must have
@@ -554,7 +767,8 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
         TRY_D(dalloc(d, &d->logits_all, c.vocab));
     }
     d->kv_layer_elems = (size_t)kvd * c.max_seq;
-    size_t kv_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
+    d->kv_seq_bytes = d->kv_layer_elems * c.n_layers * (c.kv_f16 ? 2 : 4);
+    const size_t kv_bytes = d->kv_seq_bytes * d->B;      // [sequence][layer][KV head][row][D]
     TRY_D(dalloc(d, (char **)&d->kcache, kv_bytes)); TRY_D(dalloc(d, (char **)&d->vcache, kv_bytes));
     d->max_splits = (c.max_seq + kAttnKeysPerSplit - 1) / kAttnKeysPerSplit;
     int rep = c.n_heads / c.n_kv_heads;
@@ -578,6 +792,22 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
         }
         tlb_tensor_release(ct); tlb_tensor_release(sn);
         if (st != TLB_OK) { tlb_decoder_destroy(d); return st; }
+    }
+    if (d->B > 1) {
+        const size_t B = d->B;
+        if (!prefill_batched_ok(d)) {
+            tlb_decoder_destroy(d);
+            return fail(TLB_ERR_SHAPE, "a batch session runs its linear layers on the tensor-core GEMM: d_model, the attention width and ffn must be multiples of 256, head_dim 64 or 128");
+        }
+        TRY_D(dalloc(d, &d->btok, B)); TRY_D(dalloc(d, &d->bpos, B)); TRY_D(dalloc(d, &d->brope, B)); TRY_D(dalloc(d, &d->bidx, 1));
+        TRY_D(dalloc(d, &d->bx, B * dm)); TRY_D(dalloc(d, &d->bx2, B * dm)); TRY_D(dalloc(d, &d->bt, B * dm));
+        TRY_D(dalloc(d, &d->bq, B * qd)); TRY_D(dalloc(d, &d->bk, B * kvd)); TRY_D(dalloc(d, &d->bv, B * kvd)); TRY_D(dalloc(d, &d->battn, B * qd));
+        TRY_D(dalloc(d, &d->bg, B * F)); TRY_D(dalloc(d, &d->bu, B * F));
+        TRY_D(dalloc(d, &d->blogits, B * (size_t)d->V));
+        if (tp > 1) { TRY_D(dalloc(d, &d->blogits_all, B * (size_t)c.vocab * 2)); TRY_D(dalloc(d, &d->bpair, 2 * B * (1 + tp))); }
+        TRY_D(dalloc(d, &d->bpartial, B * (size_t)d->KVH * d->max_splits * (c.n_heads / c.n_kv_heads) * (c.head_dim + 4)));
+        TRY_D(dalloc(d, &d->bcounters, B * (size_t)d->KVH));
+        TRY_D(dalloc(d, &d->btokens_out, (size_t)d->tokens_cap * B));
     }
     cudaError_t e = cudaMallocHost((void **)&d->h_state, 4 * sizeof(int));
     if (e != cudaSuccess) { tlb_decoder_destroy(d); return cuda_fail(e, "cudaMallocHost"); }
@@ -774,12 +1004,12 @@ constexpr int kPrefillChunk = 2048;
 bool prefill_batched_ok(const tlb_decoder *d)
 {
     const tlb_decoder_cfg &c = d->cfg;
-    const int qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim;
+    const int qd = d->H * c.head_dim, kvd = d->KVH * c.head_dim;
     for (const LayerW &w : d->layers)
         if (!qgemm_supported(w.q->type) || !qgemm_supported(w.k->type) || !qgemm_supported(w.v->type) || !qgemm_supported(w.o->type) ||
             !qgemm_supported(w.gate->type) || !qgemm_supported(w.down->type))
             return false;
-    return prefill_attention_supported(c.head_dim) && c.d_model % 256 == 0 && qd % 256 == 0 && c.ffn % 256 == 0 && kvd % 4 == 0;
+    return qgemm_supported(d->head->type) && prefill_attention_supported(c.head_dim) && c.d_model % 256 == 0 && qd % 256 == 0 && d->F % 256 == 0 && kvd % 4 == 0;
 }
 
 struct Scratch {
@@ -795,15 +1025,18 @@ struct Scratch {
     ~Scratch() { for (Storage *s : all) storage_release(s); }
 };
 
-tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0, int rope0, int rope_step, bool last)
+// T prompt tokens of sequence `seq` (0 for a single-sequence session) into cache rows pos0 ..; the residual of the last
+// token is copied to last_row_out when given.  With tensor parallelism every rank runs this on its shard.
+tlb_status prefill_chunk(tlb_decoder *d, int seq, const int32_t *tokens, int T, int pos0, int rope0, int rope_step, float *last_row_out)
 {
     const tlb_decoder_cfg &c = d->cfg;
-    const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
+    const int dm = c.d_model, qd = d->H * c.head_dim, kvd = d->KVH * c.head_dim, F = d->F;
     const size_t esz = c.kv_f16 ? 2 : 4;
     Scratch ws;
     int *tok_d;
-    float *x, *x2, *q, *k, *v, *att, *g, *u;
+    float *x, *x2, *q, *k, *v, *att, *g, *u, *part = nullptr;
     TLB_TRY(ws.get(&tok_d, (size_t)T));
+    if (d->tp > 1) TLB_TRY(ws.get(&part, (size_t)T * dm));
     TLB_TRY(ws.get(&x, (size_t)T * dm)); TLB_TRY(ws.get(&x2, (size_t)T * dm));
     TLB_TRY(ws.get(&q, (size_t)T * qd)); TLB_TRY(ws.get(&k, (size_t)T * kvd)); TLB_TRY(ws.get(&v, (size_t)T * kvd));
     TLB_TRY(ws.get(&att, (size_t)T * qd));
@@ -812,7 +1045,8 @@ tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0,
     TLB_TRY(launch_embed_rows(tok_d, d->emb->f32(), x, T, dm));
     for (int l = 0; l < c.n_layers; l++) {
         const LayerW &w = d->layers[l];
-        void *kc = (char *)d->kcache + (size_t)l * d->kv_layer_elems * esz, *vc = (char *)d->vcache + (size_t)l * d->kv_layer_elems * esz;
+        void *kc = (char *)d->kcache + (size_t)seq * d->kv_seq_bytes + (size_t)l * d->kv_layer_elems * esz;
+        void *vc = (char *)d->vcache + (size_t)seq * d->kv_seq_bytes + (size_t)l * d->kv_layer_elems * esz;
         GemmAct a;
         tlb_status st;
         TLB_TRY(qgemm_prepare(&a, x, nullptr, T, dm, w.attn_norm->f32(), c.eps));
@@ -833,10 +1067,10 @@ tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0,
         }
         qgemm_release(&a);
         TLB_TRY(st);
-        TLB_TRY(launch_rope_append(q, k, v, kc, vc, c.kv_f16, d->cos_t, d->sin_t, T, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, pos0, rope0, rope_step));
-        TLB_TRY(launch_prefill_attention(q, kc, vc, c.kv_f16, att, T, c.n_heads, c.n_kv_heads, c.head_dim, c.max_seq, pos0, c.attn_scale));
+        TLB_TRY(launch_rope_append(q, k, v, kc, vc, c.kv_f16, d->cos_t, d->sin_t, T, d->H, d->KVH, c.head_dim, c.max_seq, pos0, rope0, rope_step));
+        TLB_TRY(launch_prefill_attention(q, kc, vc, c.kv_f16, att, T, d->H, d->KVH, c.head_dim, c.max_seq, pos0, c.attn_scale));
         TLB_TRY(qgemm_prepare(&a, att, nullptr, T, qd, nullptr, 0.f));
-        st = qgemm_run(w.o, a, x2, x);                 // x2 = x + o_proj(attention)
+        st = row_parallel(d, w.o, a, x2, x, part, T);  // x2 = x + o_proj(attention)
         qgemm_release(&a);
         TLB_TRY(st);
         TLB_TRY(qgemm_prepare(&a, x2, nullptr, T, dm, w.ffn_norm->f32(), c.eps));
@@ -851,11 +1085,11 @@ tlb_status prefill_chunk(tlb_decoder *d, const int32_t *tokens, int T, int pos0,
         // or the row of 14336 had to stay in registers)
         TLB_TRY(launch_silu_mul(g, u, g, (int64_t)T * F));
         TLB_TRY(qgemm_prepare(&a, g, nullptr, T, F, nullptr, 0.f));
-        st = qgemm_run(w.down, a, x, x2);              // x = x2 + down(silu(gate) * up)
+        st = row_parallel(d, w.down, a, x, x2, part, T);   // x = x2 + down(silu(gate) * up)
         qgemm_release(&a);
         TLB_TRY(st);
     }
-    if (last) TLB_CUDA(cudaMemcpyAsync(d->xb, x + (size_t)(T - 1) * dm, (size_t)dm * sizeof(float), cudaMemcpyDeviceToDevice, ctx()->stream));
+    if (last_row_out) TLB_CUDA(cudaMemcpyAsync(last_row_out, x + (size_t)(T - 1) * dm, (size_t)dm * sizeof(float), cudaMemcpyDeviceToDevice, ctx()->stream));
     return TLB_OK;
 }
 }  // namespace
@@ -870,7 +1104,7 @@ extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens,
     const int64_t last_rope = (int64_t)rope_pos0 + (int64_t)(n - 1) * rope_step;
     if (pos0 < 0 || (int64_t)pos0 + n > c.max_seq || rope_pos0 < 0 || rope_step < 0 || last_rope >= c.max_seq)
         return fail(TLB_ERR_INDEX, "positions [%d, %d) / rotation rows up to %lld outside the cache of %d rows", pos0, pos0 + n, (long long)last_rope, c.max_seq);
-    if (n <= kGemmMinRows || d->tp > 1 || !prefill_batched_ok(d)) {
+    if (n <= kGemmMinRows || !prefill_batched_ok(d)) {
         // few tokens, or a shape the GEMM path does not take: the fused single-token chain, token by token
         int32_t tok = 0;
         for (int i = 0; i < n; i++) TLB_TRY(tlb_decoder_step(d, tokens[i], pos0 + i, rope_pos0 + i * rope_step, i == n - 1 ? &tok : nullptr));
@@ -879,7 +1113,7 @@ extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens,
     }
     for (int off = 0; off < n; off += kPrefillChunk) {
         const int T = std::min(kPrefillChunk, n - off);
-        TLB_TRY(prefill_chunk(d, tokens + off, T, pos0 + off, rope_pos0 + off * rope_step, rope_step, off + T == n));
+        TLB_TRY(prefill_chunk(d, 0, tokens + off, T, pos0 + off, rope_pos0 + off * rope_step, rope_step, off + T == n ? d->xb : nullptr));
     }
     // head on the last token; the state then names the next token and the row it will occupy
     TLB_TRY(set_state(d, tokens[n - 1], pos0 + n - 1, (int)last_rope, 0));
@@ -890,6 +1124,135 @@ extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens,
         *next = d->h_state[0];
     }
     return TLB_OK;
+}
+
+// ---- batch sessions: per-sequence prompts and batched steps -------------------------------------------------------
+namespace {
+tlb_status need_batch(const tlb_decoder *d, int seq)
+{
+    if (!d) return fail(TLB_ERR_NULL, "null decoder");
+    if (d->B <= 1) return fail(TLB_ERR_ARG, "the session was created with batch <= 1");
+    if (seq < 0 || seq >= d->B) return fail(TLB_ERR_INDEX, "sequence %d outside the batch of %d", seq, d->B);
+    return TLB_OK;
+}
+tlb_status put_ints(int *dst, const int32_t *src, size_t n)
+{
+    TLB_CUDA(cudaMemcpyAsync(dst, src, n * sizeof(int), cudaMemcpyHostToDevice, ctx()->stream));   // pageable source: staged before return
+    return TLB_OK;
+}
+}  // namespace
+
+extern "C" tlb_status tlb_decoder_kv_write_seq(tlb_decoder *d, int seq, int layer, int pos0, int n, const float *k, const float *v)
+{
+    if (!d) return fail(TLB_ERR_NULL, "null decoder");
+    if (seq < 0 || seq >= d->B) return fail(TLB_ERR_INDEX, "sequence %d outside the batch of %d", seq, d->B);
+    // the single-sequence writer on a cache pointer moved to the sequence's region
+    void *k0 = d->kcache, *v0 = d->vcache;
+    d->kcache = (char *)k0 + (size_t)seq * d->kv_seq_bytes;
+    d->vcache = (char *)v0 + (size_t)seq * d->kv_seq_bytes;
+    tlb_status st = tlb_decoder_kv_write(d, layer, pos0, n, k, v);
+    d->kcache = k0; d->vcache = v0;
+    return st;
+}
+
+extern "C" tlb_status tlb_decoder_prefill_seq(tlb_decoder *d, int32_t seq, const int32_t *tokens, int32_t n, int32_t pos0, int32_t rope_pos0, int32_t rope_step, int32_t *next)
+{
+    TLB_TRY(need_batch(d, seq));
+    if (!tokens) return fail(TLB_ERR_NULL, "null tokens");
+    const tlb_decoder_cfg &c = d->cfg;
+    if (n < 1) return fail(TLB_ERR_ARG, "prefill needs at least one token");
+    for (int i = 0; i < n; i++)
+        if (tokens[i] < 0 || tokens[i] >= c.vocab) return fail(TLB_ERR_INDEX, "Embedding index %d out of range for vocab size %d", tokens[i], c.vocab);
+    const int64_t last_rope = (int64_t)rope_pos0 + (int64_t)(n - 1) * rope_step;
+    if (pos0 < 0 || (int64_t)pos0 + n > c.max_seq || rope_pos0 < 0 || rope_step < 0 || last_rope >= c.max_seq)
+        return fail(TLB_ERR_INDEX, "positions [%d, %d) / rotation rows up to %lld outside the cache of %d rows", pos0, pos0 + n, (long long)last_rope, c.max_seq);
+    float *row = d->bx2 + (size_t)seq * c.d_model;     // free between steps
+    for (int off = 0; off < n; off += kPrefillChunk) {
+        const int T = std::min(kPrefillChunk, n - off);
+        TLB_TRY(prefill_chunk(d, seq, tokens + off, T, pos0 + off, rope_pos0 + off * rope_step, rope_step, off + T == n ? row : nullptr));
+    }
+    // the sequence's state: the last prompt token at its row; the head then names the next token and advances both
+    const int32_t st3[3] = {tokens[n - 1], pos0 + n - 1, (int32_t)last_rope};
+    TLB_TRY(put_ints(d->btok + seq, st3, 1)); TLB_TRY(put_ints(d->bpos + seq, st3 + 1, 1)); TLB_TRY(put_ints(d->brope + seq, st3 + 2, 1));
+    int *keep = d->btokens_out;
+    d->btokens_out = nullptr;                           // a prompt's token is not part of a generate() run
+    tlb_status st = batch_head(d, row, 1, seq);
+    d->btokens_out = keep;
+    TLB_TRY(st);
+    if (next) {
+        TLB_CUDA(cudaMemcpyAsync(d->h_state, d->btok + seq, sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
+        TLB_TRY(tlb_sync());
+        *next = d->h_state[0];
+    }
+    return TLB_OK;
+}
+
+// One token for every sequence: tokens[b] goes to cache row pos[b] of sequence b (rotation row rope_pos[b], or pos[b] when
+// rope_pos is null); next (may be null) receives the greedy tokens.  One pass over the weights serves the whole batch.
+extern "C" tlb_status tlb_decoder_step_batch(tlb_decoder *d, const int32_t *tokens, const int32_t *pos, const int32_t *rope_pos, int32_t *next)
+{
+    TLB_TRY(need_batch(d, 0));
+    if (!tokens || !pos) return fail(TLB_ERR_NULL, "null argument");
+    const tlb_decoder_cfg &c = d->cfg;
+    for (int b = 0; b < d->B; b++) {
+        const int rp = rope_pos ? rope_pos[b] : pos[b];
+        if (tokens[b] < 0 || tokens[b] >= c.vocab) return fail(TLB_ERR_INDEX, "Embedding index %d out of range for vocab size %d", tokens[b], c.vocab);
+        if (pos[b] < 0 || pos[b] >= c.max_seq || rp < 0 || rp >= c.max_seq) return fail(TLB_ERR_INDEX, "sequence %d: position %d / %d outside the cache of %d rows", b, pos[b], rp, c.max_seq);
+    }
+    TLB_TRY(ensure_batch_graph(d));
+    const int32_t zero = 0;
+    TLB_TRY(put_ints(d->btok, tokens, d->B)); TLB_TRY(put_ints(d->bpos, pos, d->B)); TLB_TRY(put_ints(d->brope, rope_pos ? rope_pos : pos, d->B));
+    TLB_TRY(put_ints(d->bidx, &zero, 1));
+    TLB_CUDA(cudaGraphLaunch(d->bgraph, ctx()->stream));
+    ctx()->launches += d->bgraph_kernels;
+    if (next) {
+        TLB_CUDA(cudaMemcpyAsync(next, d->btok, (size_t)d->B * sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
+        TLB_TRY(tlb_sync());
+    }
+    return TLB_OK;
+}
+
+// n greedy steps of the whole batch with the tokens fed back on the device; tokens_out (may be null): [n][batch].
+extern "C" tlb_status tlb_decoder_generate_batch(tlb_decoder *d, const int32_t *first_tokens, const int32_t *start_pos, int32_t n, int32_t *tokens_out)
+{
+    TLB_TRY(need_batch(d, 0));
+    if (!first_tokens || !start_pos) return fail(TLB_ERR_NULL, "null argument");
+    const tlb_decoder_cfg &c = d->cfg;
+    if (n < 0 || n > d->tokens_cap) return fail(TLB_ERR_INDEX, "%d steps exceed the session's %d rows", n, d->tokens_cap);
+    for (int b = 0; b < d->B; b++) {
+        if (first_tokens[b] < 0 || first_tokens[b] >= c.vocab) return fail(TLB_ERR_INDEX, "Embedding index %d out of range", first_tokens[b]);
+        if (start_pos[b] < 0 || (int64_t)start_pos[b] + n > c.max_seq) return fail(TLB_ERR_INDEX, "sequence %d: rows [%d, %d) outside the cache of %d rows", b, start_pos[b], start_pos[b] + n, c.max_seq);
+    }
+    TLB_TRY(ensure_batch_graph(d));
+    const int32_t zero = 0;
+    TLB_TRY(put_ints(d->btok, first_tokens, d->B)); TLB_TRY(put_ints(d->bpos, start_pos, d->B)); TLB_TRY(put_ints(d->brope, start_pos, d->B));
+    TLB_TRY(put_ints(d->bidx, &zero, 1));
+    for (int i = 0; i < n; i++) TLB_CUDA(cudaGraphLaunch(d->bgraph, ctx()->stream));
+    ctx()->launches += d->bgraph_kernels * (uint64_t)n;
+    if (tokens_out && n) {
+        TLB_CUDA(cudaMemcpyAsync(tokens_out, d->btokens_out, (size_t)n * d->B * sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
+        TLB_TRY(tlb_sync());
+    }
+    return TLB_OK;
+}
+
+// logits of the last step (or prompt) of every sequence: [batch, vocab]
+extern "C" tlb_status tlb_decoder_logits_batch(tlb_decoder *d, float *logits_out)
+{
+    TLB_TRY(need_batch(d, 0));
+    if (!logits_out) return fail(TLB_ERR_NULL, "null argument");
+    const size_t B = d->B, V = d->V, vocab = d->cfg.vocab;
+    if (d->tp <= 1) {
+        TLB_CUDA(cudaMemcpyAsync(logits_out, d->blogits, B * vocab * 4, cudaMemcpyDeviceToHost, ctx()->stream));
+        return tlb_sync();
+    }
+    // gathered as [rank][batch][V]; rearranged to [batch][vocab] on the way out (every rank calls this)
+    float *gath = d->blogits_all + B * vocab;
+    TLB_TRY(tp_allgather(d->blogits, gath, B * V * sizeof(float)));
+    for (int r = 0; r < d->tp; r++)
+        TLB_CUDA(cudaMemcpy2DAsync(d->blogits_all + (size_t)r * V, vocab * 4, gath + (size_t)r * B * V, V * 4, V * 4, B, cudaMemcpyDeviceToDevice, ctx()->stream));
+    TLB_CUDA(cudaMemcpyAsync(logits_out, d->blogits_all, B * vocab * 4, cudaMemcpyDeviceToHost, ctx()->stream));
+    return tlb_sync();
 }
 
 // Temperature / top-p sampling from the logits of the last step or prompt, on the device: only the token id crosses

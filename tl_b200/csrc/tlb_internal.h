@@ -237,7 +237,14 @@ tlb_status tp_allgather(const void *send, void *recv, size_t bytes_per_rank);   
 // attention.cu
 constexpr int kAttnKeysPerSplit = 128;   // keys one CTA of the decode attention covers; splits = ceil((pos + 1) / this)
 struct DecodeAttnJob {
-    const float *qkv;      // [q (H*D) | k (KVH*D) | v (KVH*D)] raw projections of the new token
+    const float *qkv = nullptr;      // one sequence: [q (H*D) | k (KVH*D) | v (KVH*D)] raw projections of the new token
+    // a batch of sequences (batch > 1; merged in the kernel, defer_merge must be false): dense rows q [batch, H*D],
+    // k, v [batch, KVH*D]; caches cache_seq_bytes apart; pos / rope_pos entries state_stride ints apart; partial,
+    // counters and out hold batch * KVH heads
+    const float *q = nullptr, *k = nullptr, *v = nullptr;
+    int batch = 1;
+    size_t cache_seq_bytes = 0;
+    int state_stride = 0;
     void *kcache, *vcache; // [KVH][max_seq][D] of this layer, f16 or f32
     int kv_f16;
     int H, KVH, D, max_seq;
