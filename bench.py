@@ -1,6 +1,6 @@
 """Benchmark of the quantized Llama decode path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c0|small]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c0|c1|c3|small|...]
 
 A step is one decoded token (batch 1).  Default workload c2: Llama-3-8B-shaped decoder, Q4_K linear
 layers + Q6_K output head, f16 KV cache holding a 2048-token random context, greedy decoding; weights
@@ -12,7 +12,15 @@ are seeded synthetic GGUF blocks (no model file is needed or read).  Prints ONE 
   roofline  the Q4_K streaming matvec, timed live over weight sets rotated through > 2x L2.
   cpu_baseline / --impl reference: the reference CPU path's per-token linear algebra (cached f32
             transposed weights, one thread, strided inner loop) on a bounded sample of output columns.
-With N > 1 every rank decodes its own replica of the model (no exchange step on this path): weak scaling.
+  sweep     (N = 1) the operator sweep of config C1: Q8_0 and Q4_K on the five weight shapes with 1 / 4 / 16 / 512
+            activation rows through tlb_qtensor_matmul, weights rotated through > 2x L2.
+  per_op    one decode step issued op by op through the per-op C ABI in the TL program's order: what an unmodified
+            chatbot gets, beside the fused session's number.
+  prefill   config C3: 8 sequences x 2048 prompt tokens through a batch session.
+With N > 1 every rank decodes its own replica of the 8B model (no exchange step on this path): weak scaling; the
+headline stays that.  A `tp` object is added: the 70B-shaped model of config C4 split over the N ranks (tensor
+parallel, one process per GPU), its per-token all-reduce cost, and the same model on one GPU.
+--workload c1 / c3 / qgemm / prefill-2layer run only that part (small cases for profiler captures among them).
 """
 import argparse
 import json
@@ -125,6 +133,31 @@ def dist_setup(n_gpus):
     return dist, dist.get_rank(), dist.get_world_size()
 
 
+class _GlooGroup:
+    """torch.distributed calls on a CPU (gloo) group beside the default one: object exchange for the tensor-parallel set-up."""
+
+    def __init__(self, dist):
+        self.dist = dist
+        self.group = dist.new_group(backend="gloo") if dist.get_backend() != "gloo" else None
+        self.ReduceOp = dist.ReduceOp
+
+    def broadcast_object_list(self, box, src=0):
+        self.dist.broadcast_object_list(box, src=src, group=self.group)
+
+    def all_gather_object(self, out, obj):
+        self.dist.all_gather_object(out, obj, group=self.group)
+
+    def all_reduce(self, t, op=None):
+        self.dist.all_reduce(t, op=op, group=self.group)
+
+    def barrier(self):
+        self.dist.barrier(group=self.group)
+
+
+def dist_cpu_group(dist):
+    return _GlooGroup(dist)
+
+
 def reduce_max(dist, value):
     if dist is None:
         return value
@@ -146,9 +179,32 @@ def whole_job_rate(world, steps, ms_max):
     return world * steps / (ms_max / 1e3)
 
 
-# DRAM bytes moved per algorithmic byte by the streaming matvec, from the ncu capture summarised in
-# profiles/qmatvec_q4k_llama3-8b-shapes_4layer_ncu-full.md (dram__bytes_read + dram__bytes_write over the weight bytes)
-NCU_TRAFFIC_RATIO = 1.003
+def profile_traffic_ratio():
+    """DRAM bytes per algorithmic byte of the streaming matvec, read from the committed ncu summary of the 4-layer case
+    (rows `algorithmic bytes`, `dram__bytes_read.sum`, `dram__bytes_write.sum` of its table, summed over the captured
+    launches).  None when the summary is missing or has no such rows."""
+    path = os.path.join(ROOT, "profiles", "qmatvec_q4k_llama3-8b-shapes_4layer_ncu-full.md")
+    try:
+        rows = {}
+        for line in open(path):
+            cells = [c.strip() for c in line.strip().strip("|").split("|")]
+            if len(cells) >= 2:
+                rows[cells[0]] = cells[1:]
+
+        def mb(cells):
+            out = []
+            for c in cells:
+                c = c.replace(",", "")
+                num = float(c.split()[0])
+                out.append(num * 1e6 if "MB" in c else num)
+            return out
+        algo = [k for k in rows if k.startswith("algorithmic bytes")]
+        if not algo or "dram__bytes_read.sum" not in rows or "dram__bytes_write.sum" not in rows:
+            return None
+        a, r, w = mb(rows[algo[0]]), mb(rows["dram__bytes_read.sum"]), mb(rows["dram__bytes_write.sum"])
+        return (sum(r) + sum(w)) / sum(a)
+    except Exception:
+        return None
 
 
 # ---------------------------------------------------------------- CPU baseline (oracle port of the reference CPU path)
@@ -225,31 +281,238 @@ def fill_context(dec, cfg, ctx, seed=99):
         dec.kv_write(layer, 0, k, v)
 
 
-def measure_prefill(tl, dec, cfg, tokens, ev, peaks):
-    """Secondary figure: one prompt of `tokens` random ids through tlb_decoder_prefill (tensor-core GEMMs),
-    timed with CUDA events after one warm-up run; arithmetic = linear layers + causal attention."""
+def _elapsed_ms(tl, ev0, ev1):
     import ctypes as C
+    ms = C.c_float()
+    tl.check(tl.lib().tlb_event_elapsed_ms(ev0, ev1, C.byref(ms)))
+    return float(ms.value)
+
+
+def measure_prefill(tl, cfg, wmap, kv16, ev, peaks, batch=8, tokens=2048):
+    """Config C3: `batch` sequences x `tokens` prompt ids through a batch session (tlb_decoder_prefill_seq per sequence:
+    tensor-core GEMMs over each prompt, causal attention with the f16 KV-cache write), timed with CUDA events after one
+    warm-up prompt; arithmetic = linear layers + causal attention of all sequences (the head runs on the last token)."""
     if tokens <= 0:
         return None
     L = tl.lib()
+    dec = tl.Decoder(cfg, wmap, kv_f16=kv16, max_seq=tokens + 16, batch=max(2, batch))
     rng = np.random.default_rng(4321)
-    prompt = [int(t) for t in rng.integers(0, cfg["vocab"], tokens)]
-    dec.prefill(prompt, 0, read=False)
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab"], tokens)] for _ in range(batch)]
+    dec.prefill_seq(0, prompts[0], 0, read=False)
     tl.sync()
     tl.check(L.tlb_event_record(ev[0]))
-    dec.prefill(prompt, 0, read=False)
+    for b in range(batch):
+        dec.prefill_seq(b, prompts[b], 0, read=False)
     tl.check(L.tlb_event_record(ev[1]))
     tl.sync()
-    ms = C.c_float()
-    tl.check(L.tlb_event_elapsed_ms(ev[0], ev[1], C.byref(ms)))
+    ms = _elapsed_ms(tl, ev[0], ev[1])
+    dec.destroy()
     dm, qd, kvd, F = cfg["d_model"], cfg["n_heads"] * cfg["head_dim"], cfg["n_kv_heads"] * cfg["head_dim"], cfg["ffn"]
-    lin = 2.0 * tokens * cfg["n_layers"] * (dm * (qd + 2 * kvd) + qd * dm + 3 * dm * F)
-    att = 4.0 * cfg["n_layers"] * cfg["n_heads"] * cfg["head_dim"] * tokens * (tokens + 1) / 2
-    tf = (lin + att) / (ms.value * 1e-3) / 1e12
+    lin = 2.0 * batch * tokens * cfg["n_layers"] * (dm * (qd + 2 * kvd) + qd * dm + 3 * dm * F)
+    att = 4.0 * batch * cfg["n_layers"] * cfg["n_heads"] * cfg["head_dim"] * tokens * (tokens + 1) / 2
+    tf = (lin + att) / (ms * 1e-3) / 1e12
     peak = peaks.get("bf16_tflops", 1590.0)
-    return {"tokens": tokens, "ms": round(float(ms.value), 2), "tokens_per_s": round(tokens / (ms.value * 1e-3), 0),
-            "tflops": round(tf, 1), "bound": "tensor", "peak_tflops": peak, "frac": round(tf / peak, 4),
-            "note": "f16 tcgen05 GEMMs with on-the-fly dequantisation + mma.sync attention; all layers, head on the last token"}
+    return {"workload": "c3: %d x %d prompt tokens, all %d layers" % (batch, tokens, cfg["n_layers"]), "tokens": batch * tokens, "ms": round(ms, 2),
+            "tokens_per_s": round(batch * tokens / (ms * 1e-3), 0), "tflops": round(tf, 1), "bound": "tensor", "peak_tflops": peak,
+            "frac": round(tf / peak, 4),
+            "note": "f16 tcgen05 GEMMs with on-the-fly dequantisation + mma.sync attention; head on each sequence's last token"}
+
+
+SWEEP_SHAPES = [(2048, 2048), (4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]   # (N out, K in): the config's K x N
+
+
+def measure_sweep(tl, ev, peaks, types=(8, 12), rows=(1, 4, 16, 512), shapes=SWEEP_SHAPES, iters=None):
+    """Config C1: y = x . W^T through tlb_qtensor_matmul for every format x shape x row count.  Each shape keeps enough
+    distinct device copies of its weight to exceed 2x L2 (256 MB) and the timed calls rotate through them, so every
+    call streams its weight from HBM.  Bytes = N K bpw + 4 M K + 4 M N; flops = 2 M N K."""
+    from tl_b200 import synth
+    L = tl.lib()
+    hbm, tens = peaks["hbm_gbs"], peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1590.0))
+    out = []
+    rng = np.random.default_rng(7)
+    for t in types:
+        for n, k in shapes:
+            w = synth.random_quant(t, n, k, rng)
+            wbytes = w.size
+            copies = max(2, int(np.ceil((256 << 20) / wbytes)))
+            qs = [tl.QTensor.from_gguf_bytes(t, n, k, w) for _ in range(copies)]
+            del w
+            for m in rows:
+                x = tl.Tensor.from_numpy(rng.standard_normal((m, k), dtype=np.float32))
+                reps = iters or max(copies, min(200, int(2e9 / (wbytes + 1)) + 8))
+                for i in range(min(3, copies) + 2):
+                    x.matmul_quantized(qs[i % copies]).release()
+                tl.sync()
+                tl.check(L.tlb_event_record(ev[0]))
+                for i in range(reps):
+                    x.matmul_quantized(qs[i % copies]).release()
+                tl.check(L.tlb_event_record(ev[1]))
+                tl.sync()
+                us = _elapsed_ms(tl, ev[0], ev[1]) * 1e3 / reps
+                nbytes = wbytes + 4 * m * k + 4 * m * n
+                e = {"type": synth.TYPE_NAMES[t], "n": n, "k": k, "m": m, "us": round(us, 2), "GBs": round(nbytes / us / 1e3, 1),
+                     "frac_hbm": round(nbytes / us / 1e3 / hbm, 4), "copies": copies}
+                if m >= 512:
+                    tf = 2.0 * m * n * k / us / 1e6
+                    e.update({"tflops": round(tf, 1), "frac_tensor_sustained": round(tf / tens, 4)})
+                out.append(e)
+                x.release()
+            for q in qs:
+                q.release()
+    return out
+
+
+def measure_per_op(tl, cfg, wmap, ctx, steps, ev):
+    """One decode step issued op by op through the per-op C ABI in the TL program's order
+    (examples/apps/llama3/chatbot_llama3.tl:66-125,220-236), with a context of `ctx` rows already in the program's cache:
+    what an unmodified chatbot gets behind this library.  Host token in, host token out (item_i64), wall clock."""
+    from tl_b200.chatbot import PerOpLlama
+    bot = PerOpLlama(cfg, wmap, max_seq=ctx + steps + 8)
+    rng = np.random.default_rng(99)
+    kvd = cfg["n_kv_heads"] * cfg["head_dim"]
+    for layer in range(cfg["n_layers"]):
+        bot.seed_cache(layer, rng.standard_normal((ctx, kvd), dtype=np.float32), rng.standard_normal((ctx, kvd), dtype=np.float32))
+    tok, pos = 1 % cfg["vocab"], ctx
+    for _ in range(2):
+        tok = bot.step([tok], pos)
+        pos += 1
+    tl.sync()
+    l0 = tl.kernel_launches()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = bot.step([tok], pos)
+        pos += 1
+    dt = (time.perf_counter() - t0) / steps
+    launches = (tl.kernel_launches() - l0) // steps
+    return {"tokens_per_s": round(1.0 / dt, 2), "ms_per_step": round(dt * 1e3, 3), "steps": steps, "kernel_launches_per_step": int(launches),
+            "note": "f32 KV cache grown by cat_4d (the whole cache is copied every step, as the program writes it), GQA expansion "
+                    "materialised, one tlb_* call per TL op; the fused session is the `value` / `e2e` of this line"}
+
+
+# ---------------------------------------------------------------- tensor parallelism (config C4)
+
+def build_tp_map(tl, cfg, rank, world, seed=4321):
+    """70B-shaped weights for one rank.  Every layer holds the same seeded random tensors (generated once, uploaded per
+    layer into device tensors of their own, so nothing is shared in HBM or L2); the embedding repeats 4096 random rows."""
+    from tl_b200 import synth
+    m = tl.TensorMap.new()
+    layer = {}
+    for name, t, shape in synth.llama_tensor_specs(dict(cfg, n_layers=1), 12, 14):
+        if name == "token_embd.weight":
+            rows = (synth.make_tensor("token_embd.weight", 0, (4096, shape[1]), seed)).view(np.float32).reshape(4096, shape[1])
+            data = np.concatenate([rows] * ((shape[0] + 4095) // 4096))[:shape[0]]
+            m.add_tp(name, t, shape, data, rank, world)
+        elif name.startswith("blk.0."):
+            layer[name[6:]] = (t, synth.make_tensor(name, t, shape, seed), shape)
+        else:
+            m.add_tp(name, t, shape, synth.make_tensor(name, t, shape, seed), rank, world)
+    for li in range(cfg["n_layers"]):
+        for suffix, (t, data, shape) in layer.items():
+            m.add_tp("blk.%d.%s" % (li, suffix), t, shape, data, rank, world)
+    return m
+
+
+def time_generate(tl, dec, ev, first, ctx, warm, steps, batch=None):
+    L = tl.lib()
+    if batch:
+        dec.generate_batch([first] * batch, [ctx] * batch, warm, read=False)
+    else:
+        dec.generate(first, ctx, warm, read=False)
+    tl.sync()
+    tl.check(L.tlb_event_record(ev[0]))
+    if batch:
+        dec.generate_batch([first] * batch, [ctx + warm] * batch, steps, read=False)
+    else:
+        dec.generate(first, ctx + warm, steps, read=False)
+    tl.check(L.tlb_event_record(ev[1]))
+    tl.sync()
+    return _elapsed_ms(tl, ev[0], ev[1]) / steps
+
+
+def measure_tp(tl, dist, rank, world, ev, steps=32, ctx=4096, with_single=True, batch=16):
+    """Config C4: the Llama-3-70B-shaped model (80 layers, d 8192, 64 / 8 heads of 128, FFN 28672, Q4_K + Q6_K head, f16 KV
+    with a 4096-row context) split over `world` ranks, batch 1 (fused chain) and batch 16 (GEMM rows), greedy decoding;
+    the all-reduce of one 32 KB residual timed alone over both transports; and the whole model on rank 0 alone."""
+    import torch
+    from tl_b200 import synth
+    cfg = dict(synth.LLAMA3_70B)
+    box = [tl.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    tl.tp_init(box[0], rank, world, join_timeout_s=300.0)
+    handles = [None] * world
+    dist.all_gather_object(handles, tl.tp_p2p_export())
+    tl.tp_p2p_attach(handles)
+    dist.barrier()
+    out = {"workload": "c4: Llama-3-70B-shaped decode, Q4_K + Q6_K head, f16 KV, ctx %d, tensor parallel x%d" % (ctx, world), "tp": world}
+    L = tl.lib()
+
+    def reduce_ms(v):
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # the collective alone: 160 sums of one residual row per token
+    x = tl.Tensor.zeros([cfg["d_model"]])
+    ar = {}
+    for name in ("p2p", "nccl"):
+        if name == "nccl":
+            tl.tp_p2p_disable()
+        for _ in range(20):
+            tl.check(L.tlb_allreduce(x.h))
+        tl.sync()
+        dist.barrier()
+        tl.check(L.tlb_event_record(ev[0]))
+        for _ in range(320):
+            tl.check(L.tlb_allreduce(x.h))
+        tl.check(L.tlb_event_record(ev[1]))
+        tl.sync()
+        ar[name] = reduce_ms(_elapsed_ms(tl, ev[0], ev[1])) * 1e3 / 320
+    tl.tp_p2p_enable()                   # back to the peer-memory transport
+    out["allreduce_us"] = {k: round(v, 2) for k, v in ar.items()}
+    out["allreduce_bytes"] = 4 * cfg["d_model"]
+    out["allreduce_per_token_us"] = {k: round(160 * v, 1) for k, v in ar.items()}
+
+    wmap = build_tp_map(tl, cfg, rank, world)
+    dec = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 2 * steps + 16, tp_size=world, tp_rank=rank)
+    ms = reduce_ms(time_generate(tl, dec, ev, 1, ctx, 4, steps))
+    st = dec.stats(ctx)
+    out["bs1"] = {"tokens_per_s": round(1e3 / ms, 2), "ms_per_token": round(ms, 3), "transport": "peer-memory all-reduce",
+                  "weight_bytes_per_rank": st["weight_bytes"], "kv_bytes_per_rank": st["kv_bytes"],
+                  "GBs_per_rank": round((st["weight_bytes"] + st["kv_bytes"]) / ms / 1e6, 1)}
+    tl.tp_p2p_disable()
+    dec_n = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 2 * steps + 16, tp_size=world, tp_rank=rank)
+    ms_n = reduce_ms(time_generate(tl, dec_n, ev, 1, ctx, 4, steps))
+    out["bs1_nccl"] = {"tokens_per_s": round(1e3 / ms_n, 2), "ms_per_token": round(ms_n, 3), "transport": "ncclAllReduce"}
+    dec_n.destroy()
+    tl.tp_p2p_enable()
+    dec.destroy()
+    if batch:
+        decb = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 2 * steps + 16, tp_size=world, tp_rank=rank, batch=batch)
+        msb = reduce_ms(time_generate(tl, decb, ev, 1, ctx, 2, max(4, steps // 4), batch=batch))
+        out["bs%d" % batch] = {"tokens_per_s": round(batch * 1e3 / msb, 2), "ms_per_step": round(msb, 3)}
+        decb.destroy()
+    wmap.free()
+    limiting = "allreduce" if 160 * ar["p2p"] * 1e-3 > 0.5 * ms else "weight stream"
+    out["limiting"] = "%s: 160 all-reduces take %.0f us of the %.0f us token" % (limiting, 160 * ar["p2p"], ms * 1e3)
+    dist.barrier()
+    if with_single:
+        if rank == 0:
+            tl.tp_shutdown()
+            wm1 = build_tp_map(tl, cfg, 0, 1)
+            d1 = tl.Decoder(cfg, wm1, kv_f16=True, max_seq=ctx + 2 * steps + 16)
+            ms1 = time_generate(tl, d1, ev, 1, ctx, 4, steps)
+            s1 = d1.stats(ctx)
+            out["tp1"] = {"tokens_per_s": round(1e3 / ms1, 2), "ms_per_token": round(ms1, 3),
+                          "GBs": round((s1["weight_bytes"] + s1["kv_bytes"]) / ms1 / 1e6, 1)}
+            out["speedup_vs_tp1"] = round(ms1 / ms, 3)
+            d1.destroy()
+            wm1.free()
+        else:
+            tl.tp_shutdown()
+        dist.barrier()
+    else:
+        tl.tp_shutdown()
+    return out
 
 
 def run_ours(args, dist, rank, world):
@@ -301,6 +564,13 @@ def run_ours(args, dist, rank, world):
     tl.check(L.tlb_event_elapsed_ms(ev[2], ev[3], C.byref(ms2)))
     e2e_ms = reduce_max(dist, max(float(ms2.value), wall * 1e3))
     clocks = sampler.stop() if sampler else None
+    tp = None
+    if world > 1 and not args.no_extras and args.workload == "c2":
+        # the tensor-parallel figure needs every rank; the 8B replicas' sessions make room first
+        try:
+            tp = measure_tp(tl, dist_cpu_group(dist), rank, world, ev)
+        except Exception as e:      # the headline stands without it
+            tp = {"error": str(e)[:300]}
     if rank != 0:
         return None
 
@@ -315,17 +585,27 @@ def run_ours(args, dist, rank, world):
             tot_b += b
             tot_us += us
     achieved = tot_b / tot_us / 1e3
+    ratio = profile_traffic_ratio()
     st = dec.stats(ctx + W + K // 2)
     tok_s = whole_job_rate(world, K, ms_max)
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": int(tot_b * NCU_TRAFFIC_RATIO), "peak_kind": peak_kind,
-                "traffic_note": "bytes of the same four launches; ncu capture of a 4-layer case, scaled by the weight bytes",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": int(tot_b * ratio) if ratio else None, "peak_kind": peak_kind,
+                "traffic_note": "dram bytes of the same four launches: the committed ncu capture of the 4-layer case gives %s DRAM bytes "
+                                "per algorithmic byte, scaled by the bytes of these launches" % (round(ratio, 4) if ratio else "no"),
                 "kernel": "qmatvec_kernel over one layer's four launches (qkv, o, gate|up, down), weights of %d layers rotated"
                           % cfg["n_layers"],
                 "per_launch": kern,
                 "frac_of_8TBs_nominal": round(achieved / 8000.0, 4),
                 "whole_step_GBs": round((st["weight_bytes"] + st["kv_bytes"]) * (tok_s / world) / 1e9, 1)}
-    prefill = measure_prefill(tl, dec, cfg, min(ctx, 2048) if ctx >= 32 else 0, ev, peaks)
+    dec.destroy()
+    extras = {}
+    if not args.no_extras:
+        big = args.workload == "c2"
+        extras["prefill"] = measure_prefill(tl, cfg, wmap, kv16, ev, peaks, batch=8 if big else 2, tokens=min(ctx, 2048) if ctx >= 32 else 0)
+        extras["per_op"] = measure_per_op(tl, cfg, wmap, ctx, 4, ev)
+        if world == 1:
+            wmap.free()
+            extras["sweep"] = measure_sweep(tl, ev, peaks) if big else measure_sweep(tl, ev, peaks, shapes=SWEEP_SHAPES[:2])
     cpu, _ = cpu_baseline(cfg, args.cpu_budget)
     line = {"metric": "Q4_K Llama-3-8B decode tok/s @bs1" if args.workload == "c2" else "decode tok/s @bs1",
             "value": round(tok_s, 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -339,8 +619,11 @@ def run_ours(args, dist, rank, world):
             "e2e": {"value": round(whole_job_rate(world, K, e2e_ms), 2), "unit": "tokens/s", "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
             "roofline": roofline, "cpu_baseline": cpu}
-    if prefill:
-        line["prefill"] = prefill
+    if tp:
+        line["tp"] = tp
+    for key, val in extras.items():
+        if val:
+            line[key] = val
     return line
 
 
@@ -366,16 +649,84 @@ def run_reference(args, dist, rank, world):
             "e2e": {"value": round(v, 5), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
 
+PARTS = {
+    "c1": "operator sweep of config C1 (Q8_0 / Q4_K x 5 shapes x 1 / 4 / 16 / 512 rows)",
+    "c3": "batched prompt processing of config C3 (8 x 2048 tokens, Llama-3-8B shapes)",
+    "qgemm": "one Q4_K 4096 x 4096 weight with 1184 activation rows, three calls (small case for a profiler capture)",
+    "prefill-2layer": "one 2048-token prompt through two Llama-3-8B-shaped layers + head, three times (small case for a profiler capture)",
+}
+
+
+def run_part(args):
+    """The stand-alone parts: one JSON line of their own."""
+    import ctypes as C
+    import tl_b200 as tl
+    from tl_b200 import synth
+    tl.init(-1)
+    L = tl.lib()
+    ev = [C.c_void_p() for _ in range(2)]
+    for e in ev:
+        tl.check(L.tlb_event_create(C.byref(e)))
+    peaks, peak_kind = measured_peaks()
+    name = args.workload
+    line = {"metric": PARTS[name], "n_gpus": 1, "data": "synthetic", "config": {"workload": name + ": " + PARTS[name]}, "peak_kind": peak_kind}
+    if name == "c1":
+        sweep = measure_sweep(tl, ev, peaks)
+        big = [e for e in sweep if e["m"] <= 16 and e["n"] * e["k"] >= 4096 * 14336]
+        line.update({"sweep": sweep, "value": round(float(np.median([e["GBs"] for e in big])), 1), "unit": "GB/s (median of the >= 33 MB shapes, rows <= 16)",
+                     "higher_is_better": True})
+    elif name == "c3":
+        cfg = synth.LLAMA3_8B
+        wmap = tl.TensorMap.new()
+        for tname, t, shape in synth.llama_tensor_specs(cfg, 12, 14):
+            wmap.add(tname, t, shape, synth.make_tensor(tname, t, shape, 1234))
+        pf = measure_prefill(tl, cfg, wmap, True, ev, peaks, batch=8, tokens=2048)
+        line.update({"prefill": pf, "value": pf["tokens_per_s"], "unit": "prompt tokens/s", "higher_is_better": True})
+    elif name == "qgemm":
+        rng = np.random.default_rng(1)
+        q = tl.QTensor.from_gguf_bytes(12, 4096, 4096, synth.random_quant(12, 4096, 4096, rng))
+        x = tl.Tensor.from_numpy(rng.standard_normal((1184, 4096), dtype=np.float32))
+        for _ in range(2):
+            x.matmul_quantized(q).release()
+        tl.sync()
+        tl.check(L.tlb_event_record(ev[0]))
+        x.matmul_quantized(q).release()
+        tl.check(L.tlb_event_record(ev[1]))
+        tl.sync()
+        ms = _elapsed_ms(tl, ev[0], ev[1])
+        line.update({"value": round(2.0 * 1184 * 4096 * 4096 / ms / 1e9, 1), "unit": "TFLOP/s (with the f16 conversion)", "ms": round(ms, 4), "higher_is_better": True})
+    else:
+        cfg = dict(synth.LLAMA3_8B, n_layers=2)
+        wmap = tl.map_from_tensors(synth.llama_tensors(cfg, 1, 12, 14))
+        dec = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=2048 + 256)
+        prompt = [int(t) for t in np.random.default_rng(6).integers(0, cfg["vocab"], 2048)]
+        for _ in range(2):
+            dec.prefill(prompt, 0, read=False)
+        tl.sync()
+        tl.check(L.tlb_event_record(ev[0]))
+        dec.prefill(prompt, 0, read=False)
+        tl.check(L.tlb_event_record(ev[1]))
+        tl.sync()
+        ms = _elapsed_ms(tl, ev[0], ev[1])
+        line.update({"value": round(2048 / ms * 1e3, 0), "unit": "prompt tokens/s (2 layers + head)", "ms": round(ms, 3), "higher_is_better": True})
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + sorted(PARTS))
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for the cpu_baseline sample")
+    ap.add_argument("--no-extras", action="store_true", help="headline, e2e, roofline and cpu_baseline only (no sweep / per_op / prefill / tp)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload in PARTS:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps(run_part(args)), flush=True)
+        return
     if args.impl == "reference":
         # CPU arm: rank 0 alone measures; the other ranks of a torchrun launch leave at once
         rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))

@@ -221,7 +221,8 @@ tlb_status tlb_allreduce(tlb_tensor *t);
  * that does not write within about a second makes the kernel give up (TLB_ERR_DEVICE at the next tlb_sync). */
 tlb_status tlb_tp_p2p_export(void *handle_out, size_t handle_bytes);
 tlb_status tlb_tp_p2p_attach(const void *handles, int n_handles);
-tlb_status tlb_tp_p2p_disable(void);
+tlb_status tlb_tp_p2p_disable(void);   /* back to NCCL for every size (all ranks together, between steps) */
+tlb_status tlb_tp_p2p_enable(void);    /* and on again, without re-attaching */
 /* Which way a tensor is split, by its GGUF name: 0 replicated, 1 along rows (attn_q/k/v, ffn_gate/up, output.weight),
  * 2 along columns (attn_output, ffn_down). */
 int        tlb_tp_split_kind(const char *name);

@@ -68,6 +68,10 @@ def tp_p2p_disable():
     check(lib().tlb_tp_p2p_disable())
 
 
+def tp_p2p_enable():
+    check(lib().tlb_tp_p2p_enable())
+
+
 def tp_split_kind(name):
     return int(lib().tlb_tp_split_kind(name.encode()))
 

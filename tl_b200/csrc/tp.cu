@@ -371,6 +371,7 @@ tlb_status tlb_tp_p2p_attach(const void *handles, int n_handles)
     std::lock_guard<std::mutex> lk(g_tp_mu);
     if (n_handles != g_tp.size) return fail(TLB_ERR_ARG, "%d handles for %d ranks", n_handles, g_tp.size);
     if (!g_tp.mine) return fail(TLB_ERR_ARG, "tlb_tp_p2p_export must run first");
+    if (g_tp.peer[g_tp.rank]) return fail(TLB_ERR_ARG, "the peers are already attached (tlb_tp_p2p_enable switches the transport back on)");
     for (int p = 0; p < g_tp.size; p++) {
         if (p == g_tp.rank) { g_tp.peer[p] = g_tp.mine; continue; }
         cudaIpcMemHandle_t h;
@@ -387,6 +388,14 @@ tlb_status tlb_tp_p2p_disable(void)
 {
     std::lock_guard<std::mutex> lk(g_tp_mu);
     g_tp.p2p = false;
+    return TLB_OK;
+}
+
+tlb_status tlb_tp_p2p_enable(void)
+{
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    if (!g_tp.mine || !g_tp.peer[g_tp.rank]) return fail(TLB_ERR_ARG, "the peer-memory transport was never attached");
+    g_tp.p2p = true;
     return TLB_OK;
 }
 
