@@ -133,31 +133,6 @@ def dist_setup(n_gpus):
     return dist, dist.get_rank(), dist.get_world_size()
 
 
-class _GlooGroup:
-    """torch.distributed calls on a CPU (gloo) group beside the default one: object exchange for the tensor-parallel set-up."""
-
-    def __init__(self, dist):
-        self.dist = dist
-        self.group = dist.new_group(backend="gloo") if dist.get_backend() != "gloo" else None
-        self.ReduceOp = dist.ReduceOp
-
-    def broadcast_object_list(self, box, src=0):
-        self.dist.broadcast_object_list(box, src=src, group=self.group)
-
-    def all_gather_object(self, out, obj):
-        self.dist.all_gather_object(out, obj, group=self.group)
-
-    def all_reduce(self, t, op=None):
-        self.dist.all_reduce(t, op=op, group=self.group)
-
-    def barrier(self):
-        self.dist.barrier(group=self.group)
-
-
-def dist_cpu_group(dist):
-    return _GlooGroup(dist)
-
-
 def reduce_max(dist, value):
     if dist is None:
         return value
@@ -433,7 +408,6 @@ def measure_tp(tl, dist, rank, world, ev, steps=32, ctx=4096, with_single=True, 
     """Config C4: the Llama-3-70B-shaped model (80 layers, d 8192, 64 / 8 heads of 128, FFN 28672, Q4_K + Q6_K head, f16 KV
     with a 4096-row context) split over `world` ranks, batch 1 (fused chain) and batch 16 (GEMM rows), greedy decoding;
     the all-reduce of one 32 KB residual timed alone over both transports; and the whole model on rank 0 alone."""
-    import torch
     from tl_b200 import synth
     cfg = dict(synth.LLAMA3_70B)
     box = [tl.tp_unique_id() if rank == 0 else None]
@@ -447,9 +421,7 @@ def measure_tp(tl, dist, rank, world, ev, steps=32, ctx=4096, with_single=True, 
     L = tl.lib()
 
     def reduce_ms(v):
-        t = torch.tensor([v], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return reduce_max(dist, v)
 
     # the collective alone: 160 sums of one residual row per token
     x = tl.Tensor.zeros([cfg["d_model"]])
@@ -568,7 +540,7 @@ def run_ours(args, dist, rank, world):
     if world > 1 and not args.no_extras and args.workload == "c2":
         # the tensor-parallel figure needs every rank; the 8B replicas' sessions make room first
         try:
-            tp = measure_tp(tl, dist_cpu_group(dist), rank, world, ev)
+            tp = measure_tp(tl, dist, rank, world, ev)
         except Exception as e:      # the headline stands without it
             tp = {"error": str(e)[:300]}
     if rank != 0:

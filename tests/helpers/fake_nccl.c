@@ -23,4 +23,5 @@ ncclResult_t ncclCommAbort(ncclComm_t comm) { comm->aborted = 1; fake_nccl_abort
 ncclResult_t ncclCommDestroy(ncclComm_t comm) { (void)comm; return 0; }
 ncclResult_t ncclAllReduce(const void *s, void *r, size_t n, int dt, int op, ncclComm_t c, void *stream) { (void)s; (void)r; (void)n; (void)dt; (void)op; (void)c; (void)stream; return 7; }
 ncclResult_t ncclAllGather(const void *s, void *r, size_t n, int dt, ncclComm_t c, void *stream) { (void)s; (void)r; (void)n; (void)dt; (void)c; (void)stream; return 7; }
+ncclResult_t ncclBroadcast(const void *s, void *r, size_t n, int dt, int root, ncclComm_t c, void *stream) { (void)s; (void)r; (void)n; (void)dt; (void)root; (void)c; (void)stream; return 7; }
 const char *ncclGetErrorString(ncclResult_t r) { return r == 7 ? "in progress" : "fake"; }

@@ -4,13 +4,13 @@ A Llama-3-70B-shaped model cut to 2 layers and a 32k vocabulary (d 8192, 64 / 8 
 head, f16 KV with 300 cached rows), sharded over the ranks; rank 0 compares every step's gathered logits and greedy
 token with the oracle's unsharded model.  First over NCCL, then again over the peer-memory all-reduce.
 """
+import faulthandler
 import os
+import pickle
 import sys
 import time
 
 import numpy as np
-import torch
-import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
@@ -23,11 +23,55 @@ def relerr(a, b):
     return float(np.max(np.abs(a - b)) / max(np.max(np.abs(b)), 1e-30))
 
 
+class FileExchange:
+    """The host-side channel between the ranks of this test: files in a shared directory (no network set-up involved).
+    Every wait has a deadline."""
+
+    def __init__(self, folder, rank, world, timeout=120.0):
+        self.folder, self.rank, self.world, self.timeout, self.n = folder, rank, world, timeout, 0
+
+    def _wait(self, path):
+        t0 = time.time()
+        while not os.path.exists(path):
+            if time.time() - t0 > self.timeout:
+                raise TimeoutError("no answer from the other rank: " + path)
+            time.sleep(0.005)
+
+    def all_gather_object(self, obj):
+        self.n += 1
+        mine = os.path.join(self.folder, "x%d.%d" % (self.n, self.rank))
+        with open(mine + ".tmp", "wb") as f:
+            pickle.dump(obj, f)
+        os.replace(mine + ".tmp", mine)
+        out = []
+        for r in range(self.world):
+            path = os.path.join(self.folder, "x%d.%d" % (self.n, r))
+            self._wait(path)
+            with open(path, "rb") as f:
+                out.append(pickle.load(f))
+        return out
+
+    def broadcast(self, obj, src=0):
+        return self.all_gather_object(obj if self.rank == src else None)[src]
+
+    def barrier(self):
+        self.all_gather_object(None)
+
+
+def log(rank, *a):
+    print("[rank %d %.1fs]" % (rank, time.time() - T0), *a, flush=True)
+
+
+T0 = time.time()
+
+
 def main():
     mode = sys.argv[1] if len(sys.argv) > 1 else "parity"
-    dist.init_process_group("gloo", init_method="env://")
-    rank, world = dist.get_rank(), dist.get_world_size()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    faulthandler.dump_traceback_later(int(os.environ.get("TP_TEST_DEADLINE", "240")), exit=True)   # a stuck rank ends with its stack
+    dist = FileExchange(os.environ["TP_TEST_DIR"], rank, world)
     tl.init(rank)
+    log(rank, "device bound")
     if mode == "absent":
         # rank 1 leaves before joining: rank 0's join must give up at its deadline
         if rank == 1:
@@ -50,13 +94,14 @@ def main():
         print("rank 0: bounded join ok")
         return
 
-    box = [tl.tp_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(box, src=0)
-    tl.tp_init(box[0], rank, world, join_timeout_s=120.0)
+    uid = dist.broadcast(tl.tp_unique_id() if rank == 0 else None)
+    tl.tp_init(uid, rank, world, join_timeout_s=60.0)
+    log(rank, "communicator joined")
 
     cfg = dict(synth.LLAMA3_70B, n_layers=2, vocab=32064)
     tens = synth.llama_tensors(cfg, 5, synth.Q4_K, synth.Q6_K)
     wmap = tl.map_from_tensors(tens, rank, world)
+    log(rank, "weights sharded and uploaded")
     ctx = 300
     rng = np.random.default_rng(9)
     kvd = cfg["n_kv_heads"] * cfg["head_dim"]
@@ -88,10 +133,10 @@ def main():
             worst = max(worst, relerr(lg, rl))
             want.append(oracle.argmax_last(rl))
         got.append(nxt)
-        box = [want[-1] if rank == 0 else None]
-        dist.broadcast_object_list(box, src=0)
-        assert nxt == box[0], (rank, nxt, box[0])      # every rank picked the oracle's token
-        tok, pos = box[0], pos + 1
+        ref_tok = dist.broadcast(want[-1] if rank == 0 else None)
+        assert nxt == ref_tok, (rank, nxt, ref_tok)    # every rank picked the oracle's token
+        tok, pos = ref_tok, pos + 1
+        log(rank, "step", len(got), "token", nxt)
     if rank == 0:
         assert worst < 2e-2, worst
         print("nccl: worst logit error %.2e, tokens %s" % (worst, got))
@@ -99,10 +144,10 @@ def main():
     assert st["kernels_per_step"] == 5 * 2 + 3
 
     # the same steps over the peer-memory all-reduce
-    handles = [None] * world
-    dist.all_gather_object(handles, tl.tp_p2p_export())
+    handles = dist.all_gather_object(tl.tp_p2p_export())
     tl.tp_p2p_attach(handles)
     dist.barrier()
+    log(rank, "peer memory attached")
     dec2 = session()
     tok, pos = 777, ctx
     for i in range(steps):
@@ -111,6 +156,7 @@ def main():
         assert nxt == got[i], (rank, i, nxt, got[i])
         assert relerr(lg, logits_nccl[i]) < 1e-4       # only the order of the cross-rank sum differs
         tok, pos = nxt, pos + 1
+    log(rank, "peer-memory steps agree")
     # generate: device-side feedback, one graph replay per token, every rank the same tokens
     dec3 = session()
     gen = dec3.generate(777, ctx, steps)

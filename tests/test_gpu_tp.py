@@ -20,25 +20,37 @@ def _gpus():
 needs2 = pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
 
 
-def _run(mode, port, timeout):
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), WORLD_SIZE="2", NCCL_NVLS_ENABLE="0")
+def _run(mode, folder, timeout):
+    """Two child processes, one per GPU; their output goes to files (kept when a rank gets stuck) and every rank ends
+    itself with a stack dump at its own deadline, well inside `timeout`."""
+    env = dict(os.environ, WORLD_SIZE="2", NCCL_NVLS_ENABLE="0", TP_TEST_DIR=str(folder), TP_TEST_DEADLINE=str(int(timeout) - 20))
+    logs = [open(os.path.join(str(folder), "rank%d.log" % r), "w+") for r in range(2)]
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "helpers", "tp_rank_gpu.py"), mode], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
-                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
-    outs = []
+                              stdout=logs[r], stderr=subprocess.STDOUT) for r in range(2)]
     for p in procs:
         try:
-            outs.append(p.communicate(timeout=timeout)[0])
+            p.wait(timeout=timeout)
         except subprocess.TimeoutExpired:
             p.kill()
-            outs.append(p.communicate()[0] + "\n[timed out]")
+            p.wait()
+    outs = []
+    for f in logs:
+        f.seek(0)
+        outs.append(f.read())
+        f.close()
+    keep = os.environ.get("TP_TEST_KEEP_LOGS")
+    if keep:
+        for r, o in enumerate(outs):
+            with open(os.path.join(keep, "tp_%s_rank%d.log" % (mode, r)), "w") as f:
+                f.write(o)
     return procs, outs
 
 
 @needs2
-def test_two_rank_decode_matches_the_unsharded_oracle():
+def test_two_rank_decode_matches_the_unsharded_oracle(tmp_path):
     """70B layer shapes, 2 layers: logits within 2e-2 and identical greedy tokens against the oracle's unsharded model,
     over NCCL and over the peer-memory all-reduce, host-driven steps and graph replays."""
-    procs, outs = _run("parity", 29641, 900)
+    procs, outs = _run("parity", tmp_path, 280)
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, o[-4000:]
         assert "rank %d ok" % r in o
@@ -46,10 +58,10 @@ def test_two_rank_decode_matches_the_unsharded_oracle():
 
 
 @needs2
-def test_peer_that_never_joins_is_reported():
+def test_peer_that_never_joins_is_reported(tmp_path):
     """Rank 1 leaves before joining (between steps, nothing in flight): rank 0's join ends with TLB_ERR_DEVICE at its
     deadline and its device stays usable."""
-    procs, outs = _run("absent", 29643, 300)
+    procs, outs = _run("absent", tmp_path, 120)
     assert procs[0].returncode == 0, outs[0][-3000:]
     assert "bounded join ok" in outs[0]
     assert procs[1].returncode == 0, outs[1][-3000:]

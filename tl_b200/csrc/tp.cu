@@ -15,8 +15,8 @@
 //     peers in its own memory, and adds the slots in rank order - all loads are local, the sum is bitwise
 //     the same on every rank, and one launch replaces the multi-step NCCL kernel.  Peer mappings come from
 //     CUDA IPC handles the host exchanges (tlb_tp_p2p_export / tlb_tp_p2p_attach).
-// Every wait is bounded: joining the communicator (non-blocking init polled against a deadline, then
-// ncclCommAbort), and the flag wait in the kernel (~1 s, then the context's error word; the host sees
+// Every wait is bounded: joining (a non-blocking communicator polled against a deadline, then ncclCommAbort; the
+// communicator the collectives use is created only once every rank is known to be there), and the flag wait in the kernel (~1 s, then the context's error word; the host sees
 // TLB_ERR_DEVICE at the next synchronisation).
 #include "tlb_internal.h"
 
@@ -39,6 +39,7 @@ struct NcclApi {
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Broadcast)(const void *, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 
@@ -87,6 +88,7 @@ tlb_status load_nccl()
     SYM(CommDestroy, "ncclCommDestroy");
     SYM(AllReduce, "ncclAllReduce");
     SYM(AllGather, "ncclAllGather");
+    SYM(Broadcast, "ncclBroadcast");
     SYM(GetErrorString, "ncclGetErrorString");
 #undef SYM
     g_nccl = a;
@@ -111,13 +113,13 @@ tlb_status wait_comm(ncclComm_t comm, double timeout_s, const char *what)
     }
 }
 
-// The communicator is non-blocking (so that joining can be bounded): a collective call may answer "in progress"
-// while NCCL still sets up connections; it is on the stream once the communicator reports success again.
-tlb_status finish_call(ncclResult_t r, const char *what)
+// A call on a non-blocking communicator may answer "in progress" while NCCL still sets up connections; it is on the
+// stream once the communicator reports success again.
+tlb_status finish_call(ncclComm_t comm, ncclResult_t r, const char *what)
 {
     if (r == ncclSuccess) return TLB_OK;
     if (r != ncclInProgress) return nccl_fail(r, what);
-    return wait_comm(g_tp.comm, g_tp.join_timeout_s, what);
+    return wait_comm(comm, g_tp.join_timeout_s, what);
 }
 
 // ---- one-shot all-reduce over peer memory ---------------------------------------------------------------------
@@ -224,7 +226,7 @@ tlb_status tp_allreduce(float *x, int64_t n)
     }
     if (!g_tp.comm) return fail(TLB_ERR_ARG, "tensor-parallel all-reduce before tlb_tp_init");
     ncclResult_t r = g_nccl.AllReduce(x, x, (size_t)n, ncclFloat32, ncclSum, g_tp.comm, c->stream);
-    return finish_call(r, "ncclAllReduce");
+    return finish_call(g_tp.comm, r, "ncclAllReduce");
 }
 
 tlb_status tp_allgather(const void *send, void *recv, size_t bytes_per_rank)
@@ -237,7 +239,7 @@ tlb_status tp_allgather(const void *send, void *recv, size_t bytes_per_rank)
     }
     if (!g_tp.comm) return fail(TLB_ERR_ARG, "tensor-parallel all-gather before tlb_tp_init");
     ncclResult_t r = g_nccl.AllGather(send, recv, bytes_per_rank, ncclInt8, g_tp.comm, c->stream);
-    return finish_call(r, "ncclAllGather");
+    return finish_call(g_tp.comm, r, "ncclAllGather");
 }
 
 }  // namespace tlb
@@ -267,30 +269,60 @@ tlb_status tlb_tp_init(const void *id, size_t id_bytes, int rank, int size, doub
     std::lock_guard<std::mutex> lk(g_tp_mu);
     if (g_tp.comm) return fail(TLB_ERR_ARG, "tlb_tp_init was already called in this process");
     TLB_TRY(load_nccl());
-    // with the real NCCL a device must be bound; a stand-in library (TLB_NCCL_LIB) may run without one
+    // the join itself needs no device of ours (the host-side failure test runs it against a stand-in library without one);
+    // with the real NCCL the device bound by tlb_init is made current first
     if (ensure_init()) TLB_CUDA(cudaSetDevice(ctx()->device));
     ncclUniqueId uid;
     memcpy(&uid, id, NCCL_UNIQUE_ID_BYTES);
-    ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
-    cfg.blocking = 0;               // returns at once; joining is polled against the deadline below
-    ncclComm_t comm = nullptr;
-    ncclResult_t r = g_nccl.CommInitRankConfig(&comm, size, uid, rank, &cfg);
-    if (r != ncclSuccess && r != ncclInProgress) return nccl_fail(r, "ncclCommInitRankConfig");
-    if (!comm) return fail(TLB_ERR_DEVICE, "ncclCommInitRankConfig returned no communicator");
     const double timeout = join_timeout_s > 0 ? join_timeout_s : 60.0;
-    TLB_TRY(wait_comm(comm, timeout, "joining the tensor-parallel communicator"));
+    g_tp.join_timeout_s = timeout;
+    // Step 1, the bounded join: a NON-BLOCKING communicator returns at once and is polled against the deadline; a rank
+    // that never arrives ends it with ncclCommAbort and TLB_ERR_DEVICE.
+    ncclConfig_t nb = NCCL_CONFIG_INITIALIZER;
+    nb.blocking = 0;
+    ncclComm_t probe = nullptr;
+    ncclResult_t r = g_nccl.CommInitRankConfig(&probe, size, uid, rank, &nb);
+    if (r != ncclSuccess && r != ncclInProgress) return nccl_fail(r, "ncclCommInitRankConfig");
+    if (!probe) return fail(TLB_ERR_DEVICE, "ncclCommInitRankConfig returned no communicator");
+    TLB_TRY(wait_comm(probe, timeout, "joining the tensor-parallel communicator"));
+    if (!ctx()) { g_nccl.CommAbort(probe); return fail(TLB_ERR_DEVICE, "tensor parallelism needs a CUDA device (tlb_init)"); }
+    // Step 2: everyone is here.  The collectives of the decode path run on an ordinary BLOCKING communicator (calls
+    // return once they are on the stream, which is what stream capture into the decode graph wants); its id travels
+    // from rank 0 over the first communicator, which is then closed.
+    cudaStream_t s = ctx()->stream;
+    ncclUniqueId uid2;
+    memset(&uid2, 0, sizeof uid2);
+    if (rank == 0) {
+        r = g_nccl.GetUniqueId(&uid2);
+        if (r != ncclSuccess) { g_nccl.CommAbort(probe); return nccl_fail(r, "ncclGetUniqueId"); }
+    }
+    char *idbuf = nullptr;
+    tlb_status st = TLB_OK;
+    cudaError_t e = cudaMalloc((void **)&idbuf, NCCL_UNIQUE_ID_BYTES);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(idbuf, &uid2, NCCL_UNIQUE_ID_BYTES, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) st = finish_call(probe, g_nccl.Broadcast(idbuf, idbuf, NCCL_UNIQUE_ID_BYTES, ncclInt8, 0, probe, s), "ncclBroadcast of the second id");
+    if (e == cudaSuccess && st == TLB_OK) e = cudaMemcpyAsync(&uid2, idbuf, NCCL_UNIQUE_ID_BYTES, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess && st == TLB_OK) e = cudaStreamSynchronize(s);
+    if (idbuf) cudaFree(idbuf);
+    if (e != cudaSuccess || st != TLB_OK) { g_nccl.CommAbort(probe); return st != TLB_OK ? st : cuda_fail(e, "exchange of the second communicator id"); }
+    g_nccl.CommDestroy(probe);
+    ncclConfig_t bl = NCCL_CONFIG_INITIALIZER;
+    bl.blocking = 1;
+    ncclComm_t comm = nullptr;
+    r = g_nccl.CommInitRankConfig(&comm, size, uid2, rank, &bl);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclCommInitRankConfig (blocking)");
     g_tp.comm = comm;
     g_tp.rank = rank;
     g_tp.size = size;
-    g_tp.join_timeout_s = timeout;
-    if (ctx() && size > 1) {
-        // one small all-reduce now: NCCL builds its connections on first use, which must not happen inside a graph capture
+    if (size > 1) {
+        // one small all-reduce and all-gather now: NCCL builds its connections on first use, which must not happen inside a
+        // graph capture
         float *w = nullptr;
         TLB_CUDA(cudaMalloc(&w, 1024 * sizeof(float)));
-        TLB_CUDA(cudaMemsetAsync(w, 0, 1024 * sizeof(float), ctx()->stream));
-        tlb_status st = finish_call(g_nccl.AllReduce(w, w, 1024, ncclFloat32, ncclSum, comm, ctx()->stream), "first ncclAllReduce");
-        if (st == TLB_OK) st = finish_call(g_nccl.AllGather(w, w, 8, ncclInt8, comm, ctx()->stream), "first ncclAllGather");
-        cudaError_t e = cudaStreamSynchronize(ctx()->stream);
+        TLB_CUDA(cudaMemsetAsync(w, 0, 1024 * sizeof(float), s));
+        st = finish_call(comm, g_nccl.AllReduce(w, w, 1024, ncclFloat32, ncclSum, comm, s), "first ncclAllReduce");
+        if (st == TLB_OK) st = finish_call(comm, g_nccl.AllGather(w, w, 8, ncclInt8, comm, s), "first ncclAllGather");
+        e = cudaStreamSynchronize(s);
         cudaFree(w);
         if (st != TLB_OK) return st;
         if (e != cudaSuccess) return cuda_fail(e, "first collective");
