@@ -161,10 +161,21 @@ def main():
     dec3 = session()
     gen = dec3.generate(777, ctx, steps)
     assert gen == got, (rank, gen, got)
-    # timing, for the record: graph replays over both transports
+    # timing, for the record: the collective alone, then graph replays, over both transports
+    x = tl.Tensor.zeros([cfg["d_model"]])
     for name, use_p2p in (("p2p", True), ("nccl", False)):
         if not use_p2p:
             tl.tp_p2p_disable()
+        for _ in range(20):
+            tl.check(tl.lib().tlb_allreduce(x.h))
+        tl.sync()
+        dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(500):
+            tl.check(tl.lib().tlb_allreduce(x.h))
+        tl.sync()
+        if rank == 0:
+            print("%s: all-reduce of %d floats alone, %.2f us per call (launched back to back)" % (name, cfg["d_model"], (time.perf_counter() - t0) / 500 * 1e6))
         d4 = session()
         d4.generate(777, ctx, 4)
         tl.sync()
@@ -175,8 +186,16 @@ def main():
         dt = (time.perf_counter() - t0) / 32
         if rank == 0:
             print("%s: %.1f us per token (2 layers + head, %d ranks)" % (name, dt * 1e6, world))
+        d4.destroy()
     tl.tp_poll()
     dist.barrier()
+    try:
+        tl.tp_shutdown()
+        raise SystemExit("shut down with sessions alive")
+    except tl.TlbError as e:
+        assert e.code == 8 and "still alive" in str(e)
+    for d in (dec, dec2, dec3):
+        d.destroy()                # their graphs hold the communicator's kernels
     tl.tp_shutdown()
     print("rank %d ok" % rank)
 

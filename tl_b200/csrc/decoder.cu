@@ -21,6 +21,9 @@
 
 using namespace tlb;
 
+static std::atomic<int> g_tp_sessions{0};
+namespace tlb { int tp_live_sessions() { return g_tp_sessions.load(); } }
+
 struct LayerW {
     tlb_qtensor *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
     tlb_tensor *attn_norm = nullptr, *ffn_norm = nullptr;
@@ -686,6 +689,7 @@ tlb_status tlb_decoder_destroy(tlb_decoder *d)
     tlb_tensor_release(d->emb); tlb_tensor_release(d->out_norm); tlb_qtensor_release(d->head);
     for (void *p : d->allocs) cudaFree(p);
     if (d->h_state) cudaFreeHost(d->h_state);
+    if (d->tp > 1) g_tp_sessions--;
     delete d;
     return TLB_OK;
 }
@@ -717,6 +721,7 @@ tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb
     d->cfg = c;
     d->B = c.batch > 1 ? c.batch : 1;
     d->tp = tp; d->tp_r = tp_r;
+    if (tp > 1) g_tp_sessions++;
     d->H = c.n_heads / tp; d->KVH = c.n_kv_heads / tp; d->F = c.ffn / tp; d->V = c.vocab / tp;
     // local sizes: the shapes this rank's tensors must have
     const int64_t dm = c.d_model, qd = (int64_t)d->H * c.head_dim, kvd = (int64_t)d->KVH * c.head_dim, F = d->F;

@@ -231,6 +231,7 @@ tlb_status launch_f32_to_f16(const float *a, __half *out, int64_t n);
 // tp.cu: tensor-parallel ranks of this process's communicator (1 / 0 before tlb_tp_init)
 int tp_rank();
 int tp_size();
+int tp_live_sessions();        // decode sessions created with tp_size > 1 and not yet destroyed (decoder.cu)
 tlb_status tp_allreduce(float *x, int64_t n);                                     // x := sum over ranks, in place, on ctx()->stream
 tlb_status tp_allgather(const void *send, void *recv, size_t bytes_per_rank);     // recv[rank] := every rank's send
 

@@ -49,9 +49,11 @@ NcclApi g_nccl;
 constexpr int kMaxTp = 8;
 constexpr size_t kP2pMaxFloats = 64 * 1024;   // per rank and buffer: 16 activation rows of a 70B-shaped model (8192 wide), with room
 
+constexpr int kP2pCtas = 16;                  // most CTAs of one all-reduce; every CTA has flags of its own
+
 struct P2pRegion {                 // what a rank allocates for its peers to write into (cudaMalloc, exported over IPC)
     float slots[2][kMaxTp][kP2pMaxFloats];   // [buffer][writer rank][element]
-    unsigned flags[kMaxTp];                  // flags[r]: sequence number of the last all-reduce rank r finished writing here
+    unsigned flags[kMaxTp][kP2pCtas][8];     // flags[r][c][0]: sequence number of the last all-reduce whose CTA c of rank r wrote here (32-byte apart)
 };
 
 struct TpState {
@@ -144,36 +146,36 @@ struct P2pArgs {
     int rank, size;
 };
 
-// x[0 .. n) := sum over ranks of their x, n a multiple of 4.  Grid: any number of CTAs; CTA b owns the float4s
-// b, b + grid, ...  (1) store own share into slot [buf][rank] of every rank (own memory included); (2) the last
-// CTA to finish raises flags[rank] = seq on every rank, behind a system-scope fence; (3) wait until the flags of
-// all ranks in OWN memory have reached seq; (4) add the slots in rank order.  Buffers alternate with seq: a rank
-// can be at most one all-reduce ahead of a peer that is still reading.
+// x[0 .. n) := sum over ranks of their x, n a multiple of 4.  CTA c owns a contiguous range of float4s and never
+// talks to the other CTAs of its grid: (1) it stores its range into slot [buf][rank] of every rank (own memory
+// included); (2) behind a block barrier and a system-scope fence, one thread raises flags[rank][c] = seq on every rank;
+// (3) it waits (bounded) until flags[r][c] of all ranks r in OWN memory have reached seq - CTA c of every rank covers
+// the same range; (4) it adds the slots in rank order.  Buffers alternate with seq: a rank can be at most one
+// all-reduce ahead of a peer that is still reading.
 __global__ void __launch_bounds__(256) p2p_allreduce_kernel(float *x, int n, const P2pArgs a)
 {
     __shared__ int s_ok;
     const unsigned seq = *a.seq;
     const int buf = seq & 1;
-    const int n4 = n >> 2;
+    const int n4 = n >> 2, per = (n4 + gridDim.x - 1) / gridDim.x;
+    const int i0 = blockIdx.x * per, i1 = min(n4, i0 + per);
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         const float4 v = x4[i];
         for (int p = 0; p < a.size; p++) reinterpret_cast<float4 *>(a.peer[p]->slots[buf][a.rank])[i] = v;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();                       // this CTA's stores are visible to every GPU before it is counted
-        if (atomicAdd(a.arrive, 1) == (int)gridDim.x - 1) {
-            *a.arrive = 0;
-            __threadfence_system();
-            for (int p = 0; p < a.size; p++) st_release_sys(&a.peer[p]->flags[a.rank], seq);
-        }
-        // bounded wait for every rank's share (about a second, then the error word)
+    if (threadIdx.x < a.size) {
+        __threadfence_system();                       // the CTA's stores are visible to every GPU before its flag is
+        st_release_sys(&a.peer[threadIdx.x]->flags[a.rank][blockIdx.x][0], seq);
+    }
+    if (threadIdx.x < 32) {
+        // lane r waits for rank r's CTA of the same index: bounded (about a second), then the error word
         bool ok = true;
-        unsigned long long t0 = 0;
-        for (int p = 0; p < a.size && ok; p++) {
+        if (threadIdx.x < a.size) {
+            unsigned long long t0 = 0;
             for (unsigned it = 0;; it++) {
-                if ((int)(ld_acquire_sys(&a.mine->flags[p]) - seq) >= 0) break;
+                if ((int)(ld_acquire_sys(&a.mine->flags[threadIdx.x][blockIdx.x][0]) - seq) >= 0) break;
                 if ((it & 255) == 255) {
                     unsigned long long t;
                     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -182,12 +184,13 @@ __global__ void __launch_bounds__(256) p2p_allreduce_kernel(float *x, int n, con
                 }
             }
         }
-        s_ok = ok;
+        ok = __all_sync(0xffffffffu, ok);
+        if (threadIdx.x == 0) s_ok = ok;
     }
     __syncthreads();
     if (s_ok) {
         float4 *o4 = reinterpret_cast<float4 *>(x);
-        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+        for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
             float4 acc = __ldcv(reinterpret_cast<const float4 *>(a.mine->slots[buf][0]) + i);
             for (int p = 1; p < a.size; p++) {
                 const float4 v = __ldcv(reinterpret_cast<const float4 *>(a.mine->slots[buf][p]) + i);
@@ -196,11 +199,9 @@ __global__ void __launch_bounds__(256) p2p_allreduce_kernel(float *x, int n, con
             o4[i] = acc;
         }
     }
-    // the next all-reduce uses the next sequence number; one thread of the grid advances it once everyone has read it
-    __syncthreads();
+    // the next all-reduce uses the next sequence number: the last CTA to get here (all have read seq by then) advances it
     if (threadIdx.x == 0) {
-        __threadfence();
-        if (atomicAdd(a.arrive + 1, 1) == (int)gridDim.x - 1) { a.arrive[1] = 0; *a.seq = seq + 1; }
+        if (atomicAdd(a.arrive, 1) == (int)gridDim.x - 1) { *a.arrive = 0; *a.seq = seq + 1; }
     }
 }
 
@@ -218,7 +219,7 @@ tlb_status tp_allreduce(float *x, int64_t n)
         P2pArgs a;
         for (int p = 0; p < kMaxTp; p++) a.peer[p] = g_tp.peer[p];
         a.mine = g_tp.mine; a.seq = g_tp.seq; a.arrive = g_tp.arrive; a.err = c->err_flag; a.rank = g_tp.rank; a.size = g_tp.size;
-        const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(16, (n / 4 + 255) / 256));
+        const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(kP2pCtas, (n / 4 + 511) / 512));
         p2p_allreduce_kernel<<<grid, 256, 0, c->stream>>>(x, (int)n, a);
         TLB_CUDA(cudaGetLastError());
         count_launch();
@@ -346,6 +347,10 @@ int tlb_tp_size(void) { return g_tp.size; }
 
 tlb_status tlb_tp_shutdown(void)
 {
+    // ncclCommDestroy waits for every CUDA graph that captured one of the communicator's collectives to be destroyed:
+    // the decode sessions of this process hold such graphs
+    if (tp_live_sessions() > 0)
+        return fail(TLB_ERR_ARG, "%d tensor-parallel decode session(s) are still alive: destroy them before tlb_tp_shutdown", tp_live_sessions());
     std::lock_guard<std::mutex> lk(g_tp_mu);
     if (ctx()) cudaStreamSynchronize(ctx()->stream);
     for (int p = 0; p < kMaxTp; p++) {
