@@ -91,6 +91,8 @@ tlb_status tlb_transpose(tlb_tensor **out, const tlb_tensor *a, int64_t d0, int6
 tlb_status tlb_reshape(tlb_tensor **out, const tlb_tensor *a, const int64_t *shape, int rank); /* :1198 zero-copy view */
 tlb_status tlb_cat(tlb_tensor **out, const tlb_tensor *a, const tlb_tensor *b, int64_t dim); /* :1264 cat_4d, :1259 cat2 */
 tlb_status tlb_repeat_interleave(tlb_tensor **out, const tlb_tensor *a, int64_t repeats, int64_t dim); /* :1275 */
+tlb_status tlb_reshape_new(tlb_tensor **out, const tlb_tensor *a, const tlb_tensor *shape);   /* :1193 tl_tensor_reshape_new: the shape as a tensor of f32 (reads it back: syncs) */
+tlb_status tlb_cat_i64(tlb_tensor **out, const tlb_tensor *a, const tlb_tensor *b, int64_t dim); /* :1250 tl_tensor_cat_i64: integers travel as f32, so tlb_cat */
 tlb_status tlb_new_causal_mask(tlb_tensor **out, int64_t size);                          /* :170 */
 tlb_status tlb_embedding(tlb_tensor **out, const tlb_tensor *table, const tlb_tensor *idx); /* :1300; out-of-range id -> TLB_ERR_INDEX */
 
@@ -137,6 +139,9 @@ tlb_status tlb_sdpa(tlb_tensor **out, const tlb_tensor *q, const tlb_tensor *k, 
 tlb_status tlb_fused_silu_mul(tlb_tensor **out, const tlb_tensor *gate, const tlb_tensor *up);
 tlb_status tlb_fused_rms_norm(tlb_tensor **out, const tlb_tensor *x, const tlb_tensor *w, float eps);
 tlb_status tlb_fused_add_rms_norm(tlb_tensor **out, const tlb_tensor *x, const tlb_tensor *residual, const tlb_tensor *w, float eps);
+/* fused_rotary_emb(freqs, head_dim) as crates/tl_cuda/src/ops/fused.rs:129-185 computes it: rotate-half with the one table
+ * [tokens, head_dim / 2] used as both cos and sin; x is [b, tokens, heads, d], [tokens, heads, d] or [tokens, d]. */
+tlb_status tlb_fused_rotary_emb(tlb_tensor **out, const tlb_tensor *x, const tlb_tensor *freqs, int64_t head_dim);
 
 /* ---- quantized weights ------------------------------------------------------------------ */
 /* Upload GGUF bytes of a row-major [n, k] tensor and repack them ONCE into the tiled,
@@ -161,6 +166,15 @@ tlb_status tlb_qtensor_dequantize(tlb_tensor **out, const tlb_qtensor *q);
  * the faster of the two: the tensor-core GEMM with f16 operands and f32 accumulation (~5e-4 of the row maximum). */
 tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, const tlb_qtensor *w);
 
+/* The reference's raw-bytes entry points, under the reference's own names and signatures
+ * (crates/tl_runtime/src/device_ffi.rs:1805-1833; crates/tl_cuda/src/ffi_ops.rs:1314-1391): x is a tensor handle, w_raw a
+ * U8 tensor handle holding the raw GGUF bytes of a [n, k] Q4_K / Q6_K weight on the device.  The bytes are repacked into
+ * the tiled layout once per distinct raw tensor (a cache keyed by its device address that keeps a reference to it) and
+ * every call runs the fused kernels.  NULL on failure (tlb_last_error tells why). */
+void *tl_cuda_mul_mv_q4_k(void *x, void *w_raw, int64_t n, int64_t k);
+void *tl_cuda_mul_mv_q6_k(void *x, void *w_raw, int64_t n, int64_t k);
+int64_t tlb_raw_weight_cache_clear(void);      /* drops the repacked copies; returns how many there were */
+
 /* Tiled-layout introspection (no counterpart in the reference; used by the layout tests): byte offset
  * inside a 16-row unit of byte raw_off of the GGUF bytes of row row16's 256-weight segment; unit size. */
 int tlb_layout_unit_offset(int ggml_type, int row16, int raw_off);
@@ -168,6 +182,9 @@ int tlb_layout_unit_bytes(int ggml_type);
 
 /* ---- GGUF loader and tensor map --------------------------------------------------------- */
 tlb_status tlb_gguf_load(tlb_map **out, const char *path);                                /* crates/tl_runtime/src/gguf.rs:34 */
+/* the same with the path as TL passes strings: StringStruct { ptr, len } (crates/tl_runtime/src/string_ffi.rs:7-11) */
+typedef struct { char *ptr; int64_t len; } tlb_string;
+tlb_status tlb_gguf_load_str(tlb_map **out, const tlb_string *path);
 /* In-memory form of the loader: an empty map, then one tensor at a time from host bytes in GGUF
  * block layout with a row-major shape (what gguf.rs:129-190 builds per tensor). */
 tlb_status tlb_map_new(tlb_map **out);
@@ -181,6 +198,7 @@ tlb_status tlb_map_meta_number(const tlb_map *m, const char *key, double *out);
 const char *tlb_map_meta_string(const tlb_map *m, const char *key);
 tlb_status tlb_map_get_quantized(tlb_qtensor **out, tlb_map *m, const char *name);        /* tensor_map.rs:279 (retained clone) */
 tlb_status tlb_map_get(tlb_tensor **out, tlb_map *m, const char *name);                   /* tensor_map.rs:110 dequantised f32, cached */
+tlb_status tlb_map_get_1d(tlb_tensor **out, tlb_map *m, const char *name);                /* tl_tensor_map_get_1d (src/compiler/codegen/builtins.rs:2687): same lookup */
 
 /* ---- KV cache handle table (crates/tl_runtime/src/system.rs:387-615, llm.rs:105-174) ----- */
 tlb_status tlb_kvcache_new(tlb_kvcache **out, int64_t layers);

@@ -31,10 +31,10 @@ class DecoderCfg(C.Structure):
 
 
 def declared_symbols():
-    """Names of all functions declared in include/tlb200.h."""
+    """Names of all functions declared in include/tlb200.h (tlb_* and the reference's own tl_cuda_mul_mv_* names)."""
     src = open(HEADER).read()
     src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
-    return sorted(set(re.findall(r"\b(tlb_[a-z0-9_]+)\s*\(", src)))
+    return sorted(set(re.findall(r"\b((?:tlb|tl_cuda)_[a-z0-9_]+)\s*\(", src)))
 
 
 def lib():
@@ -102,6 +102,9 @@ def lib():
     d("tlb_decoder_logits", S, vp, vp); d("tlb_decoder_hidden", S, vp, vp)
     d("tlb_decoder_stats", S, vp, i32, C.POINTER(u64), C.POINTER(u64), C.POINTER(i32))
     d("tlb_decoder_time_kernel", S, vp, C.c_char_p, C.c_int, C.c_int, C.POINTER(f32), C.POINTER(u64))
+    d("tl_cuda_mul_mv_q4_k", vp, vp, vp, i64, i64); d("tl_cuda_mul_mv_q6_k", vp, vp, vp, i64, i64); d("tlb_raw_weight_cache_clear", i64)
+    d("tlb_reshape_new", S, pvp, vp, vp); d("tlb_cat_i64", S, pvp, vp, vp, i64); d("tlb_map_get_1d", S, pvp, vp, C.c_char_p)
+    d("tlb_gguf_load_str", S, pvp, vp); d("tlb_fused_rotary_emb", S, pvp, vp, vp, i64)
     pi32 = C.POINTER(i32)
     d("tlb_decoder_kv_write_seq", S, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp)
     d("tlb_decoder_prefill_seq", S, vp, i32, pi32, i32, i32, i32, i32, pi32)
