@@ -131,6 +131,13 @@ tlb_status tlb_sample(tlb_tensor **out, const tlb_tensor *logits, float temp, fl
  * stable descending order, prefix up to the first running sum above top_p, draw inside it), with the random number
  * u in [0, 1) given by the caller instead of rand::thread_rng(); temp <= 0 is the greedy branch.  Result: [1] f32. */
 tlb_status tlb_sample_top_p(tlb_tensor **out, const tlb_tensor *logits, float temp, float top_p, double u, tlb_tie_rule tie);
+/* The same sampler with a top-k limit as well: the kept prefix ends at the top-p cutoff or after top_k tokens, whichever comes
+ * first (top_k <= 0: no limit; the reference's top_k_sample_kernel, autograd.cu:2370-2415, masks to the k best and takes
+ * their argmax, which is tlb_argmax). */
+tlb_status tlb_sample_top_k_top_p(tlb_tensor **out, const tlb_tensor *logits, float temp, int32_t top_k, float top_p, double u, tlb_tie_rule tie);
+/* The number in [0, 1) the session generator gives for (seed, counter): Philox-4x32-10 keyed by the seed, first output word.
+ * tlb_decoder_generate_sampled draws these on the device (the reference draws from rand::thread_rng(), unseeded). */
+double     tlb_rng_uniform(uint64_t seed, uint64_t counter);
 tlb_status tlb_repetition_penalty(tlb_tensor **out, const tlb_tensor *logits, const tlb_tensor *tokens, float penalty); /* device_ffi.rs:563 */
 /* softmax(q k^T / sqrt(d) + mask) v.  mask_mode 0: none; 1: additive (CUDA, autograd.cu:2263-2367);
  * 2: zero entries become -1e9 (CPU, crates/tl_cpu/src/device_impl.rs:775-870). */
@@ -316,6 +323,10 @@ tlb_status tlb_decoder_logits_batch(tlb_decoder *d, float *logits_out /* host, [
 /* tlb_sample_top_p on the logits of the last step or prompt, without bringing them to the host; temp <= 0 returns the
  * greedy token the step chose.  The caller feeds *token to the next tlb_decoder_step. */
 tlb_status tlb_decoder_sample_top_p(tlb_decoder *d, float temp, float top_p, double u, int32_t *token);
+/* n sampled steps with the token fed back on the device (temperature, top-k, top-p; one draw per step from
+ * tlb_rng_uniform(seed, step)); temp <= 0 is tlb_decoder_generate.  Single-GPU sessions. */
+tlb_status tlb_decoder_generate_sampled(tlb_decoder *d, int32_t first_token, int32_t start_pos, int32_t n, float temp, int32_t top_k, float top_p,
+                                        uint64_t seed, int32_t *tokens_out);
 tlb_status tlb_decoder_logits(tlb_decoder *d, float *logits_out /* host, vocab floats */);
 tlb_status tlb_decoder_hidden(tlb_decoder *d, float *hidden_out /* host, d_model floats: residual stream before output_norm */);
 /* algorithmic bytes one decode step reads at context length ctx (weights + KV), kernels per step */

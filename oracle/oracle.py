@@ -84,6 +84,12 @@ def lib():
         L.orc_argmax_first.restype = sz
         L.orc_sample_top_p.argtypes = [fp, sz, C.c_float, C.c_float, C.c_double]
         L.orc_sample_top_p.restype = sz
+        L.orc_sample_top_k_top_p.argtypes = [fp, sz, C.c_float, C.c_long, C.c_float, C.c_double]
+        L.orc_sample_top_k_top_p.restype = sz
+        L.orc_philox4x32_10.argtypes = [C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
+        L.orc_philox4x32_10.restype = None
+        L.orc_rng_uniform.argtypes = [C.c_uint64, C.c_uint64]
+        L.orc_rng_uniform.restype = C.c_double
         L.orc_repetition_penalty.argtypes = [fp, sz, fp, sz, C.c_float, fp]
         L.orc_repetition_penalty.restype = None
         L.orc_sdpa_cpu.argtypes = [fp, fp, fp, fp, sz, sz, sz, sz, fp]
@@ -285,6 +291,23 @@ def sample_top_p(x, temp, top_p, u):
     """sample_impl of the reference CPU back end with the random number u in [0, 1) supplied."""
     x, xp = _f(x)
     return int(lib().orc_sample_top_p(xp, x.size, temp, top_p, u))
+
+
+def sample_top_k_top_p(x, temp, top_k, top_p, u):
+    x, xp = _f(x)
+    return int(lib().orc_sample_top_k_top_p(xp, x.size, temp, top_k, top_p, u))
+
+
+def philox4x32_10(ctr, key):
+    c = (C.c_uint32 * 4)(*ctr)
+    k = (C.c_uint32 * 2)(*key)
+    o = (C.c_uint32 * 4)()
+    lib().orc_philox4x32_10(c, k, o)
+    return [int(v) for v in o]
+
+
+def rng_uniform(seed, counter):
+    return float(lib().orc_rng_uniform(seed, counter))
 
 
 def argmax_first(x):

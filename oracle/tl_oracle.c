@@ -515,7 +515,35 @@ static int cmp_prob_desc(const void *a, const void *b)
     if (pb < pa) return -1;
     return ia < ib ? -1 : (ia > ib ? 1 : 0); /* slice::sort_by is stable: equal probabilities keep index order */
 }
+/* Philox-4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11): the counter-based
+ * generator the library's decode session draws from on the device.  No counterpart in the reference (it draws from
+ * rand::thread_rng()). */
+void orc_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4])
+{
+    uint32_t c0 = ctr[0], c1 = ctr[1], c2 = ctr[2], c3 = ctr[3], k0 = key[0], k1 = key[1];
+    for (int r = 0; r < 10; r++) {
+        uint64_t p0 = (uint64_t)0xD2511F53u * c0, p1 = (uint64_t)0xCD9E8D57u * c2;
+        uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0, n1 = (uint32_t)p1, n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1, n3 = (uint32_t)p0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+double orc_rng_uniform(uint64_t seed, uint64_t counter)
+{
+    uint32_t ctr[4] = { (uint32_t)counter, (uint32_t)(counter >> 32), 0u, 0u }, key[2] = { (uint32_t)seed, (uint32_t)(seed >> 32) }, o[4];
+    orc_philox4x32_10(ctr, key, o);
+    return (double)((float)(o[0] >> 8) * (1.0f / 16777216.0f));
+}
+
 size_t orc_sample_top_p(const float *logits, size_t n, float temp, float top_p, double u)
+{
+    return orc_sample_top_k_top_p(logits, n, temp, 0, top_p, u);
+}
+
+/* sample_impl with a top-k limit on the kept prefix (top_k <= 0: none): the extension the library adds */
+size_t orc_sample_top_k_top_p(const float *logits, size_t n, float temp, long top_k, float top_p, double u)
 {
     if (n == 0) return 0;
     if (temp <= 0.0f) return orc_argmax_last(logits, n);
@@ -533,8 +561,9 @@ size_t orc_sample_top_p(const float *logits, size_t n, float temp, float top_p, 
     g_sort_probs = probs;
     qsort(indices, n, sizeof(size_t), cmp_prob_desc);
     float cum_prob = 0.0f;
-    size_t cutoff_index = n - 1;
-    for (size_t i = 0; i < n; i++) {
+    size_t limit = (top_k > 0 && (size_t)top_k < n) ? (size_t)top_k : n;
+    size_t cutoff_index = limit - 1;
+    for (size_t i = 0; i < limit; i++) {
         cum_prob += probs[indices[i]];
         if (cum_prob > top_p) { cutoff_index = i; break; }
     }

@@ -99,6 +99,12 @@ size_t orc_argmax_last(const float *x, size_t n);
 size_t orc_argmax_first(const float *x, size_t n);
 /* tl_cpu tensor.rs:1625-1680 sample_impl with the random number u in [0, 1) as an argument */
 size_t orc_sample_top_p(const float *logits, size_t n, float temp, float top_p, double u);
+/* the same with the kept prefix also limited to the top_k most probable tokens (top_k <= 0: no limit); no counterpart in the
+ * reference, whose top-k sampler is an argmax (crates/tl_cuda/src/cuda_kernels/autograd.cu:2370-2415) */
+size_t orc_sample_top_k_top_p(const float *logits, size_t n, float temp, long top_k, float top_p, double u);
+/* Philox-4x32-10 and the uniform in [0, 1) the decode session derives from (seed, counter): first output word >> 8, / 2^24 */
+void   orc_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]);
+double orc_rng_uniform(uint64_t seed, uint64_t counter);
 /* crates/tl_cpu/src/device_impl.rs:967-1000 */
 void orc_repetition_penalty(const float *logits, size_t n, const float *tokens, size_t nt,
                             float penalty, float *out);

@@ -300,3 +300,28 @@ def test_decoder_sizes_from_gguf_metadata(tmp_path):
     with pytest.raises(tl.TlbError) as e:
         tl.map_from_tensors(tens).decoder_cfg()        # no metadata in a map built tensor by tensor
     assert e.value.code == 8
+
+
+def test_sampled_generation_on_device(orc):
+    """tlb_decoder_generate_sampled: temperature / top-k / top-p with the draws made on the device from (seed, step).  The same
+    session driven from the host - logits read back, the oracle's sampler, the draw of tlb_rng_uniform(seed, step) - gives the
+    same tokens; the same seed repeats them, another seed does not."""
+    ref, dec, wmap = build(orc, SMALL, 61, synth.Q4_K, synth.Q6_K, True, 64)
+    temp, top_k, top_p, seed = 0.9, 12, 0.95, 1234
+    gen = dec.generate_sampled(7, 0, 20, temp, top_k, top_p, seed)
+    host = tl.Decoder(SMALL, wmap, kv_f16=True, max_seq=64)
+    tok, toks = 7, []
+    for i in range(20):
+        host.step(tok, i)
+        lg = host.logits()
+        u = tl.rng_uniform(seed, i)
+        assert u == orc.rng_uniform(seed, i)
+        tok = orc.sample_top_k_top_p(lg, temp, top_k, top_p, u)
+        dev_tok = int(tl.Tensor.from_numpy(lg).sample_top_k_top_p(temp, top_k, top_p, u).numpy()[0])
+        assert dev_tok == tok
+        toks.append(tok)
+    assert gen == toks
+    assert dec.generate_sampled(7, 0, 20, temp, top_k, top_p, seed) == gen           # repeatable
+    assert dec.generate_sampled(7, 0, 20, temp, top_k, top_p, seed + 1) != gen       # a different stream of draws
+    assert dec.generate_sampled(7, 0, 8, 0.0, top_k, top_p, seed) == dec.generate(7, 0, 8)   # temp <= 0: greedy
+    assert dec.generate_sampled(7, 0, 8, temp, 1, top_p, seed) == dec.generate(7, 0, 8)     # top_k 1: greedy

@@ -312,3 +312,20 @@ def test_extra_block_types_hand_built(orc):
     np.testing.assert_array_equal(orc.dequantize(synth.Q8_1, q81, 32), (2.0 * q).astype(np.float32))
     assert orc.type_nbytes(synth.Q4_1, 64) == 40 and orc.type_nbytes(synth.Q5_0, 64) == 44
     assert orc.type_nbytes(synth.Q5_1, 64) == 48 and orc.type_nbytes(synth.Q8_1, 64) == 72 and orc.type_nbytes(synth.Q5_0, 48) == 0
+
+
+def test_philox_known_answers(orc):
+    """Philox-4x32-10 against the three known-answer vectors published with the algorithm (all-zero, all-ones and the
+    digits-of-pi counter / key), and the library's host helper against the oracle's."""
+    assert orc.philox4x32_10([0, 0, 0, 0], [0, 0]) == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    assert orc.philox4x32_10([0xffffffff] * 4, [0xffffffff] * 2) == [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]
+    assert orc.philox4x32_10([0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0]) == [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]
+    import tl_b200 as tl
+    for seed, ctr in ((0, 0), (7, 1), (2 ** 63 + 5, 2 ** 40 + 3)):
+        u = orc.rng_uniform(seed, ctr)
+        assert 0.0 <= u < 1.0 and u == tl.rng_uniform(seed, ctr)
+    x = np.array([0.1, 2.0, 1.5, -1.0, 1.9], dtype=np.float32)
+    assert orc.sample_top_k_top_p(x, 1.0, 0, 1.0, 0.999) == 3                   # no limits: the tail token is reachable
+    assert orc.sample_top_k_top_p(x, 1.0, 2, 1.0, 0.999) == 4                   # two best tokens only: 1 (2.0) and 4 (1.9)
+    assert orc.sample_top_k_top_p(x, 1.0, 2, 1.0, 0.0) == 1
+    assert orc.sample_top_k_top_p(x, 1.0, 0, 1.0, 0.3) == orc.sample_top_p(x, 1.0, 1.0, 0.3)

@@ -33,6 +33,11 @@ def kernel_launches():
 
 
 # ---- tensor parallelism (one process per GPU) ---------------------------------------------------------------
+def rng_uniform(seed, counter):
+    """The number in [0, 1) a session draws at step `counter` under `seed` (Philox-4x32-10)."""
+    return float(lib().tlb_rng_uniform(int(seed), int(counter)))
+
+
 def tp_unique_id():
     """128-byte communicator id; rank 0 makes it and the host passes it to the other ranks."""
     buf = (C.c_uint8 * 128)()
@@ -183,6 +188,8 @@ class Tensor:
     def sample(self, temp, top_p, tie=TIE_LAST): return Tensor._wrap(lib().tlb_sample, self.h, float(temp), float(top_p), tie)
     def sample_top_p(self, temp, top_p, u, tie=TIE_LAST):
         return Tensor._wrap(lib().tlb_sample_top_p, self.h, float(temp), float(top_p), float(u), tie)
+    def sample_top_k_top_p(self, temp, top_k, top_p, u, tie=TIE_LAST):
+        return Tensor._wrap(lib().tlb_sample_top_k_top_p, self.h, float(temp), int(top_k), float(top_p), float(u), tie)
     def repetition_penalty(self, tokens, p): return Tensor._wrap(lib().tlb_repetition_penalty, self.h, tokens.h, float(p))
     def sdpa(self, k, v, mask=None, mask_mode=0):
         return Tensor._wrap(lib().tlb_sdpa, self.h, k.h, v.h, mask.h if mask is not None else None, mask_mode)
@@ -441,6 +448,11 @@ class Decoder:
         out = np.empty((self.batch, self.cfg.vocab), dtype=np.float32)
         check(lib().tlb_decoder_logits_batch(self.h, out.ctypes.data_as(C.c_void_p)))
         return out
+
+    def generate_sampled(self, first_token, start_pos, n, temp, top_k, top_p, seed):
+        out = (C.c_int32 * max(1, n))()
+        check(lib().tlb_decoder_generate_sampled(self.h, first_token, start_pos, n, float(temp), int(top_k), float(top_p), int(seed), out))
+        return [out[i] for i in range(n)]
 
     def logits(self):
         out = np.empty(self.cfg.vocab, dtype=np.float32)

@@ -102,6 +102,8 @@ def lib():
     d("tlb_decoder_logits", S, vp, vp); d("tlb_decoder_hidden", S, vp, vp)
     d("tlb_decoder_stats", S, vp, i32, C.POINTER(u64), C.POINTER(u64), C.POINTER(i32))
     d("tlb_decoder_time_kernel", S, vp, C.c_char_p, C.c_int, C.c_int, C.POINTER(f32), C.POINTER(u64))
+    d("tlb_sample_top_k_top_p", S, pvp, vp, f32, i32, f32, C.c_double, C.c_int); d("tlb_rng_uniform", C.c_double, u64, u64)
+    d("tlb_decoder_generate_sampled", S, vp, i32, i32, i32, f32, i32, f32, u64, C.POINTER(i32))
     d("tl_cuda_mul_mv_q4_k", vp, vp, vp, i64, i64); d("tl_cuda_mul_mv_q6_k", vp, vp, vp, i64, i64); d("tlb_raw_weight_cache_clear", i64)
     d("tlb_reshape_new", S, pvp, vp, vp); d("tlb_cat_i64", S, pvp, vp, vp, i64); d("tlb_map_get_1d", S, pvp, vp, C.c_char_p)
     d("tlb_gguf_load_str", S, pvp, vp); d("tlb_fused_rotary_emb", S, pvp, vp, vp, i64)

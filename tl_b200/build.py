@@ -9,8 +9,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libtlb200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--use_fast_math=false"]
-FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"]
+         "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "-Wno-deprecated-gpu-targets"]
 
 
 def sources():
@@ -45,7 +44,9 @@ def build(force=False, verbose=False):
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([NVCC, "-shared", "-o", OUT] + objs + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"])
+    # linked under a temporary name and moved into place, so a reader never sees a half-written library
+    subprocess.check_call([NVCC, "-shared", "-o", OUT + ".tmp"] + objs + ["-lcudart_static", "-ldl", "-lrt", "-lpthread"])
+    os.replace(OUT + ".tmp", OUT)
     return OUT
 
 

@@ -69,6 +69,12 @@ struct tlb_decoder {
     int *bcounters = nullptr, *btokens_out = nullptr;
     cudaGraphExec_t bgraph = nullptr;
     uint64_t bgraph_kernels = 0;
+    // sampled generation: the same chain with the sampler in place of the argmax, as a graph of its own
+    struct { bool on = false; float temp = 0.f, top_p = 1.f; int top_k = 0; unsigned long long seed = 0; } samp;
+    void *samp_ws = nullptr;
+    unsigned long long *samp_counter = nullptr;
+    cudaGraphExec_t sgraph = nullptr;
+    uint64_t sgraph_kernels = 0;
     float *part = nullptr;        // tp > 1: this rank's partial o_proj / ffn_down result, summed over the ranks in place
     float *pair = nullptr;        // tp > 1: (best logit, its global index) of this shard, then of every shard [1 + tp][2]
     float *logits_all = nullptr;  // tp > 1: the gathered logits of all shards (tlb_decoder_logits)
@@ -250,6 +256,12 @@ tlb_status enqueue_head(tlb_decoder *d, const float *ssq_parts, const float *x =
         TLB_TRY(launch_qmatvec(j));
     }
     if (d->dry) return TLB_OK;
+    if (d->samp.on) {
+        // temperature / top-k / top-p sampling on the device, the random number drawn from (seed, step counter); the token
+        // and the advance of the positions go where the argmax would have put them
+        return launch_sample_into(d->logits, c.vocab, d->samp.temp, d->samp.top_p, d->samp.top_k, 0.f, nullptr, d->samp_ws, d->state, d->tokens_out,
+                                  d->tokens_cap, d->samp_counter, d->samp.seed);
+    }
     if (d->tp > 1) {
         argmax_pair_kernel<<<1, 1024, 0, ctx()->stream>>>(d->logits, d->V, (int)(c.tie_rule == TLB_TIE_FIRST), d->tp_r * d->V, d->pair);
         TLB_CUDA(cudaGetLastError());
@@ -681,6 +693,7 @@ tlb_status tlb_decoder_destroy(tlb_decoder *d)
     if (ctx()) cudaStreamSynchronize(ctx()->stream);
     if (d->graph) cudaGraphExecDestroy(d->graph);
     if (d->bgraph) cudaGraphExecDestroy(d->bgraph);
+    if (d->sgraph) cudaGraphExecDestroy(d->sgraph);
     for (LayerW &w : d->layers) {
         tlb_qtensor_release(w.q); tlb_qtensor_release(w.k); tlb_qtensor_release(w.v); tlb_qtensor_release(w.o);
         tlb_qtensor_release(w.gate); tlb_qtensor_release(w.up); tlb_qtensor_release(w.down); tlb_qtensor_release(w.gu);
@@ -1127,6 +1140,58 @@ extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens,
         TLB_CUDA(cudaMemcpyAsync(d->h_state, d->state, sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
         TLB_TRY(tlb_sync());
         *next = d->h_state[0];
+    }
+    return TLB_OK;
+}
+
+// n sampled steps with the token fed back on the device: softmax(logits / temp), the k most probable tokens, the top-p prefix,
+// one draw per step from the counter-based generator keyed by `seed` (step i of this call uses counter i: the same seed
+// gives the same tokens; tlb_rng_uniform(seed, i) is the number step i drew).  temp <= 0 is tlb_decoder_generate.
+extern "C" tlb_status tlb_decoder_generate_sampled(tlb_decoder *d, int32_t first_token, int32_t start_pos, int32_t n, float temp, int32_t top_k, float top_p,
+                                                   uint64_t seed, int32_t *tokens_out)
+{
+    if (!d) return fail(TLB_ERR_NULL, "null decoder");
+    if (temp <= 0.f || top_k == 1) return tlb_decoder_generate(d, first_token, start_pos, n, tokens_out);
+    if (d->tp > 1) return fail(TLB_ERR_ARG, "sampled generation needs the whole vocabulary on one GPU (tp_size 1)");
+    if (first_token < 0 || first_token >= d->cfg.vocab) return fail(TLB_ERR_INDEX, "Embedding index %d out of range", first_token);
+    if (n < 0 || start_pos < 0 || start_pos + n > d->cfg.max_seq) return fail(TLB_ERR_INDEX, "positions [%d, %d) outside the cache of %d rows", start_pos, start_pos + n, d->cfg.max_seq);
+    if (!d->samp_ws) {
+        TLB_CUDA(cudaMalloc(&d->samp_ws, sample_workspace_bytes(d->cfg.vocab)));
+        d->allocs.push_back(d->samp_ws);
+        TLB_CUDA(cudaMalloc((void **)&d->samp_counter, sizeof(unsigned long long)));
+        d->allocs.push_back(d->samp_counter);
+    }
+    if (d->sgraph && (d->samp.temp != temp || d->samp.top_k != top_k || d->samp.top_p != top_p || d->samp.seed != seed)) {
+        TLB_CUDA(cudaStreamSynchronize(ctx()->stream));
+        cudaGraphExecDestroy(d->sgraph);
+        d->sgraph = nullptr;
+    }
+    if (!d->sgraph) {
+        d->samp.temp = temp; d->samp.top_k = top_k; d->samp.top_p = top_p; d->samp.seed = seed;
+        Context *cx = ctx();
+        const uint64_t before = cx->launches.load();
+        d->samp.on = true;
+        TLB_CUDA(cudaStreamBeginCapture(cx->stream, cudaStreamCaptureModeThreadLocal));
+        tlb_status st = enqueue_step(d);
+        cudaGraph_t g = nullptr;
+        cudaError_t e = cudaStreamEndCapture(cx->stream, &g);
+        d->samp.on = false;
+        d->sgraph_kernels = cx->launches.load() - before;
+        cx->launches = before;
+        if (st != TLB_OK) { if (g) cudaGraphDestroy(g); return st; }
+        if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
+        e = cudaGraphInstantiate(&d->sgraph, g, 0);
+        cudaGraphDestroy(g);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+    }
+    const unsigned long long zero = 0;
+    TLB_CUDA(cudaMemcpyAsync(d->samp_counter, &zero, sizeof zero, cudaMemcpyHostToDevice, ctx()->stream));
+    TLB_TRY(set_state(d, first_token, start_pos, start_pos, 0));
+    for (int i = 0; i < n; i++) TLB_CUDA(cudaGraphLaunch(d->sgraph, ctx()->stream));
+    ctx()->launches += d->sgraph_kernels * (uint64_t)n;
+    if (tokens_out && n) {
+        TLB_CUDA(cudaMemcpyAsync(tokens_out, d->tokens_out, (size_t)n * sizeof(int), cudaMemcpyDeviceToHost, ctx()->stream));
+        TLB_TRY(tlb_sync());
     }
     return TLB_OK;
 }

@@ -134,7 +134,10 @@ tlb_status qgemm_run(const tlb_qtensor *w, const GemmAct &a, float *out, const f
 tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct &a, float *const *outs, const float *resid);
 void qgemm_release(GemmAct *a);
 // sampling.cu: temperature / top-p sampling of n logits with the draw u in [0, 1); the token id as f32 into out[0]
-tlb_status launch_sample_top_p(const float *logits, int64_t n, float temp, float top_p, float u, float *out);
+tlb_status launch_sample_top_p(const float *logits, int64_t n, float temp, float top_p, float u, float *out, int top_k = 0);
+size_t sample_workspace_bytes(int64_t n);
+tlb_status launch_sample_into(const float *logits, int64_t n, float temp, float top_p, int top_k, float u, float *out, void *workspace,
+                              int *state, int *tokens_out, int tokens_cap, unsigned long long *counter, unsigned long long seed);
 // prefill.cu: the other kernels of prompt processing
 tlb_status launch_embed_rows(const int *tokens, const float *table, float *x, int n_tokens, int dm);
 tlb_status launch_rope_append(float *q, const float *k, const float *v, void *kcache, void *vcache, int kv_f16, const float *cos_t,
