@@ -19,14 +19,15 @@ def relerr(a, b):
 
 @pytest.mark.parametrize("linear,head", [(synth.Q4_K, synth.Q6_K), (synth.Q4_0, synth.Q4_0), (synth.Q8_0, synth.F16)])
 def test_per_op_route_matches_oracle_and_fused_session(orc, linear, head):
-    tens = synth.llama_tensors(SMALL, 51, linear, head)
+    # Q8_0 block scales at a trained model's magnitude (see test_gpu_decoder.test_prefill_matches_oracle_and_continues)
+    tens = synth.llama_tensors(SMALL, 51, linear, head, scale_sigma=0.002 if linear == synth.Q8_0 else None)
     wmap = tl.map_from_tensors(tens)
     ref = orc.Llama(dict(SMALL, kv_f16=0, max_seq=64), {k: (t, d) for k, (t, d, s) in tens.items()})
     bot = PerOpLlama(SMALL, wmap, max_seq=64)
     prompt = [5, 17, 300, 9, 41, 77, 2]
     rl = ref.forward(prompt, 0)
     tok = bot.step(prompt, 0)                       # the whole prompt in one pass: causal mask, rotation at row 0
-    assert relerr(bot.last_logits.numpy()[0], rl) < 1e-4
+    assert relerr(bot.last_logits.numpy()[0], rl) < 5e-4
     assert tok == orc.argmax_last(rl)
     fused = None
     if head != synth.F16:                           # the fused session takes tiled weights only; the per-op route any QTensor
@@ -38,11 +39,11 @@ def test_per_op_route_matches_oracle_and_fused_session(orc, linear, head):
     for _ in range(10):
         rl = ref.forward([tok], pos)
         nxt = bot.step([tok], pos)
-        assert relerr(bot.last_logits.numpy()[0], rl) < 1e-4
+        assert relerr(bot.last_logits.numpy()[0], rl) < 5e-4
         assert nxt == orc.argmax_last(rl)
         if fused is not None:
             assert fused.step(tok, pos) == nxt
-            assert relerr(fused.logits(), bot.last_logits.numpy()[0]) < 1e-4
+            assert relerr(fused.logits(), bot.last_logits.numpy()[0]) < 5e-4
         tok, pos = nxt, pos + 1
     # the cache the program holds grew by concatenation: [1, KVH, T, D]
     assert bot.cache.get_k(0).shape == (1, SMALL["n_kv_heads"], pos, SMALL["head_dim"])
