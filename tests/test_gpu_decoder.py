@@ -306,8 +306,8 @@ def test_sampled_generation_on_device(orc):
     """tlb_decoder_generate_sampled: temperature / top-k / top-p with the draws made on the device from (seed, step).  The same
     session driven from the host - logits read back, the oracle's sampler, the draw of tlb_rng_uniform(seed, step) - gives the
     same tokens; the same seed repeats them, another seed does not."""
-    ref, dec, wmap = build(orc, SMALL, 61, synth.Q4_K, synth.Q6_K, True, 64)
-    temp, top_k, top_p, seed = 0.9, 12, 0.95, 1234
+    ref, dec, wmap = build(orc, SMALL, 61, synth.Q4_K, synth.Q6_K, True, 64, sigma=0.001)
+    temp, top_k, top_p, seed = 25.0, 12, 0.95, 1234      # the synthetic model's logits span ~80: a temperature that leaves a choice
     gen = dec.generate_sampled(7, 0, 20, temp, top_k, top_p, seed)
     host = tl.Decoder(SMALL, wmap, kv_f16=True, max_seq=64)
     tok, toks = 7, []
@@ -321,6 +321,7 @@ def test_sampled_generation_on_device(orc):
         assert dev_tok == tok
         toks.append(tok)
     assert gen == toks
+    assert len(set(gen)) > 3                                                         # a real draw, not an argmax in disguise
     assert dec.generate_sampled(7, 0, 20, temp, top_k, top_p, seed) == gen           # repeatable
     assert dec.generate_sampled(7, 0, 20, temp, top_k, top_p, seed + 1) != gen       # a different stream of draws
     assert dec.generate_sampled(7, 0, 8, 0.0, top_k, top_p, seed) == dec.generate(7, 0, 8)   # temp <= 0: greedy
