@@ -1,4 +1,4 @@
-//! The C ABI of libtlb200 (include/tlb200.h), declaration for declaration: 123 entry points.
+//! The C ABI of libtlb200 (include/tlb200.h), declaration for declaration: 126 entry points.
 //! Handles are opaque; status codes are the values of RuntimeErrorCode (crates/tl_runtime/src/error.rs:7-18).
 #![allow(non_camel_case_types)]
 use std::ffi::{c_char, c_int, c_void};
@@ -97,6 +97,8 @@ extern "C" {
     pub fn tlb_argmax_into(out: *mut TlbTensor, x: *const TlbTensor, tie: c_int) -> TlbStatus;
     pub fn tlb_sample(out: *mut *mut TlbTensor, logits: *const TlbTensor, temp: f32, top_p: f32, tie: c_int) -> TlbStatus;
     pub fn tlb_sample_top_p(out: *mut *mut TlbTensor, logits: *const TlbTensor, temp: f32, top_p: f32, u: f64, tie: c_int) -> TlbStatus;
+    pub fn tlb_sample_top_k_top_p(out: *mut *mut TlbTensor, logits: *const TlbTensor, temp: f32, top_k: i32, top_p: f32, u: f64, tie: c_int) -> TlbStatus;
+    pub fn tlb_rng_uniform(seed: u64, counter: u64) -> f64;
     pub fn tlb_repetition_penalty(out: *mut *mut TlbTensor, logits: *const TlbTensor, tokens: *const TlbTensor, penalty: f32) -> TlbStatus;
     pub fn tlb_sdpa(out: *mut *mut TlbTensor, q: *const TlbTensor, k: *const TlbTensor, v: *const TlbTensor, mask: *const TlbTensor, mask_mode: c_int) -> TlbStatus;
     pub fn tlb_fused_silu_mul(out: *mut *mut TlbTensor, gate: *const TlbTensor, up: *const TlbTensor) -> TlbStatus;
@@ -168,6 +170,7 @@ extern "C" {
     pub fn tlb_decoder_generate_batch(d: *mut TlbDecoder, first_tokens: *const i32, start_pos: *const i32, n: i32, tokens_out: *mut i32) -> TlbStatus;
     pub fn tlb_decoder_logits_batch(d: *mut TlbDecoder, logits_out: *mut f32) -> TlbStatus;
     pub fn tlb_decoder_sample_top_p(d: *mut TlbDecoder, temp: f32, top_p: f32, u: f64, token: *mut i32) -> TlbStatus;
+    pub fn tlb_decoder_generate_sampled(d: *mut TlbDecoder, first_token: i32, start_pos: i32, n: i32, temp: f32, top_k: i32, top_p: f32, seed: u64, tokens_out: *mut i32) -> TlbStatus;
     pub fn tlb_decoder_logits(d: *mut TlbDecoder, logits_out: *mut f32) -> TlbStatus;
     pub fn tlb_decoder_hidden(d: *mut TlbDecoder, hidden_out: *mut f32) -> TlbStatus;
     pub fn tlb_decoder_stats(d: *const TlbDecoder, ctx: i32, weight_bytes: *mut u64, kv_bytes: *mut u64, kernels_per_step: *mut i32) -> TlbStatus;
