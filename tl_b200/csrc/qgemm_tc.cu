@@ -61,6 +61,13 @@ struct GemmParams {
     const float *inv_scale; // [m]
     const float *resid;     // [m, n] added to the result, or null
     int *err;
+    // K-splits (few activation rows on a narrow weight: too few 128-row tiles to fill the SMs): grid.z CTAs share a tile,
+    // each over kt_total / splits of the K steps, writing its partial product to part[split][m][n_all]; a second small
+    // launch adds the splits (and the residual).  splits == 1: the result goes straight to out.
+    int splits;
+    float *part;
+    int n_all;              // columns of one partial row: the sum of the weights' rows
+    int col0[kGemmMaxW];    // first column of weight i inside a partial row
 };
 
 __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b)
@@ -337,10 +344,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 // ---- one dequantising warp: 64-groups 2 HALF and 2 HALF + 1 of every unit of its 16 rows
 template <int FMT, int HALF>
 __device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, bool have, int row0, int lane, uint32_t sA,
-                                        uint32_t full0, uint32_t empty0, volatile int *abort_flag)
+                                        uint32_t full0, uint32_t empty0, volatile int *abort_flag, int u0, int units)
 {
-    const int units = (int)p.upt;
     typename UnitRegs<FMT>::type cur, nxt;
+    ub += (size_t)u0 * p.unit_bytes;          // this CTA's K range starts at unit u0
     if (have) unit_load<HALF>(nxt, ub, lane);
     for (int u = 0; u < units; u++) {
         if (have) {
@@ -380,7 +387,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     const uint32_t accum_bar = bars + 8u * (2 * kGemmStages);
 
     const int tok0 = blockIdx.y * p.nt;
-    const int KT = p.kt_total;
+    // K range of this CTA: whole units (4 K steps each), split evenly over grid.z
+    const int units_all = (int)p.upt, split = blockIdx.z;
+    const int u0 = units_all * split / p.splits, u1 = units_all * (split + 1) / p.splits;
+    const int KT = (u1 - u0) * 4, kt_base = u0 * 4;
     int wi = 0;
     while (wi + 1 < p.n_w && (int)blockIdx.x >= p.rt_end[wi]) wi++;
     const int rt = (int)blockIdx.x - (wi ? p.rt_end[wi - 1] : 0);   // 128-row tile inside weight wi
@@ -411,14 +421,16 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
         const int tile16 = rt * 8 + sub;
         const bool have = tile16 < p.n_tiles16[wi];
         const uint8_t *ub = p.w[wi] + (size_t)(have ? tile16 : 0) * p.upt * p.unit_bytes;
-        const bool ok = warp < 8 ? produce<FMT, 0>(p, ub, have, sub * 16, lane, sA, full_bar(0), empty_bar(0), abort_flag)
-                                 : produce<FMT, 1>(p, ub, have, sub * 16, lane, sA, full_bar(0), empty_bar(0), abort_flag);
+        const bool ok = warp < 8 ? produce<FMT, 0>(p, ub, have, sub * 16, lane, sA, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0)
+                                 : produce<FMT, 1>(p, ub, have, sub * 16, lane, sA, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0);
         // ------------------------------------------------ epilogue: tensor memory -> Y[token][row]
         if (ok && mbar_wait(accum_bar, 0, abort_flag, p.err, 22)) {
             tc_fence_after();
             const int quad = warp & 3, part = warp >> 2;    // tensor-memory lanes 32 quad .., a quarter of the columns
             const int row = rt * kGemmRows + quad * 32 + lane;
             float *out = p.out[wi];
+            const bool partial = p.splits > 1;   // partial products go to part[split][token][col0 + row], unscaled residual-free
+            float *pout = partial ? p.part + (size_t)split * p.m * p.n_all + p.col0[wi] : nullptr;
             const int chunks = p.nt >> 3;
             const int c_begin = 8 * (part * chunks / 4), c_end = 8 * ((part + 1) * chunks / 4);
             for (int c0 = c_begin; c0 < c_end; c0 += 8) {
@@ -429,14 +441,17 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
                     const int tok = tok0 + c0 + j;
                     const bool live = tok < p.m && row < n_rows;
                     sc[j] = tok < p.m ? __ldg(p.inv_scale + tok) : 0.f;
-                    rs[j] = (live && p.resid) ? __ldg(p.resid + (size_t)tok * n_rows + row) : 0.f;
+                    rs[j] = (live && p.resid && !partial) ? __ldg(p.resid + (size_t)tok * n_rows + row) : 0.f;
                 }
                 uint32_t v[8];
                 tmem_ld8(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int tok = tok0 + c0 + j;
-                    if (tok < p.m && row < n_rows) out[(size_t)tok * n_rows + row] = rs[j] + __uint_as_float(v[j]) * sc[j];
+                    if (tok < p.m && row < n_rows) {
+                        if (partial) pout[(size_t)tok * p.n_all + row] = __uint_as_float(v[j]) * sc[j];
+                        else out[(size_t)tok * n_rows + row] = rs[j] + __uint_as_float(v[j]) * sc[j];
+                    }
                 }
             }
         }
@@ -448,7 +463,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
                 const int s = kt % kGemmStages, round = kt / kGemmStages;
                 if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, p.err, 23)) break;
                 mbar_expect_tx(full_bar(s), (uint32_t)p.nt * 128u);
-                tma_load_2d(sB + s * kStageB, &xmap, kt * kGemmBK, tok0, full_bar(s));
+                tma_load_2d(sB + s * kStageB, &xmap, (kt_base + kt) * kGemmBK, tok0, full_bar(s));
                 issued = kt + 1;
             }
             if (*abort_flag) {
@@ -481,6 +496,28 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     if (warp == kGemmProducers + 1) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// Adds the K-splits: out_i[tok][row] = [resid +] sum_s part[s][tok][col0_i + row], splits added in index order.
+struct SplitSum {
+    float *out[kGemmMaxW];
+    int n[kGemmMaxW], col0[kGemmMaxW];
+    int n_w, n_all, m, splits;
+    const float *part, *resid;
+};
+__global__ void __launch_bounds__(256) qgemm_split_sum_kernel(const SplitSum a)
+{
+    const size_t total = (size_t)a.m * a.n_all, stride = total;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int tok = (int)(i / a.n_all), col = (int)(i - (size_t)tok * a.n_all);
+        int w = 0;
+        while (w + 1 < a.n_w && col >= a.col0[w + 1]) w++;
+        const int row = col - a.col0[w];
+        float acc = __ldcg(a.part + i);
+        for (int s = 1; s < a.splits; s++) acc += __ldcg(a.part + s * stride + i);
+        if (a.resid) acc += __ldg(a.resid + (size_t)tok * a.n[w] + row);
+        a.out[w][(size_t)tok * a.n[w] + row] = acc;
     }
 }
 
@@ -686,7 +723,23 @@ tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct 
     p.err = c->err_flag;
 
     const size_t smem = (size_t)kGemmStages * (kStageA + kStageB) + 1024 + 128;
-    dim3 grid((unsigned)row_tiles, (unsigned)((m + nt - 1) / nt));
+    // K-splits when the tiles alone leave most SMs idle (few activation rows on a narrow weight): as many as bring the
+    // grid to about two waves, each at least 4 units (1024 of K) long
+    const int64_t tok_tiles = (m + nt - 1) / nt, ctas = row_tiles * tok_tiles;
+    int splits = 1;
+    if (m <= 64 && ctas * 2 <= c->sm_count)
+        splits = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(16, p.upt / 4), (2 * c->sm_count) / ctas));
+    int64_t n_all = 0;
+    for (int i = 0; i < kGemmMaxW; i++) { p.col0[i] = (int)n_all; n_all += p.n[i]; }
+    Storage *part = nullptr;
+    if (splits > 1) {
+        part = storage_alloc((size_t)splits * m * n_all * sizeof(float));
+        if (!part) return TLB_ERR_ALLOC;
+    }
+    p.splits = splits;
+    p.part = part ? (float *)part->ptr : nullptr;
+    p.n_all = (int)n_all;
+    dim3 grid((unsigned)row_tiles, (unsigned)tok_tiles, (unsigned)splits);
     tlb_status ls;
     switch (w0->type) {
         case 12: ls = launch_fmt_gemm<12>(grid, smem, c->stream, map, p); break;
@@ -694,9 +747,19 @@ tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct 
         case 2: ls = launch_fmt_gemm<2>(grid, smem, c->stream, map, p); break;
         default: ls = launch_fmt_gemm<8>(grid, smem, c->stream, map, p); break;
     }
-    if (ls != TLB_OK) return ls;
+    if (ls != TLB_OK) { if (part) storage_release(part); return ls; }
     count_launch();
     cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && splits > 1) {
+        SplitSum a;
+        for (int i = 0; i < kGemmMaxW; i++) { a.out[i] = p.out[i]; a.n[i] = p.n[i]; a.col0[i] = p.col0[i]; }
+        a.n_w = n_w; a.n_all = (int)n_all; a.m = (int)m; a.splits = splits; a.part = p.part; a.resid = resid;
+        const unsigned blocks = (unsigned)std::min<int64_t>(4 * c->sm_count, (m * n_all + 255) / 256);
+        qgemm_split_sum_kernel<<<blocks, 256, 0, c->stream>>>(a);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    if (part) storage_release(part);     // stream-ordered: freed after the launches above have run
     if (e != cudaSuccess) return cuda_fail(e, "qgemm launch");
     return TLB_OK;
 }
