@@ -625,6 +625,7 @@ PARTS = {
     "c1": "operator sweep of config C1 (Q8_0 / Q4_K x 5 shapes x 1 / 4 / 16 / 512 rows)",
     "c3": "batched prompt processing of config C3 (8 x 2048 tokens, Llama-3-8B shapes)",
     "qgemm": "one Q4_K 4096 x 4096 weight with 1184 activation rows, three calls (small case for a profiler capture)",
+    "c4-4layer": "Llama-3-70B-shaped decode on one GPU, 4 layers + head, 4096-row f16 context: batch 1 (fused matvec chain) and batch 16 (tensor-core GEMM rows)",
     "prefill-2layer": "one 2048-token prompt through two Llama-3-8B-shaped layers + head, three times (small case for a profiler capture)",
 }
 
@@ -667,6 +668,20 @@ def run_part(args):
         tl.sync()
         ms = _elapsed_ms(tl, ev[0], ev[1])
         line.update({"value": round(2.0 * 1184 * 4096 * 4096 / ms / 1e9, 1), "unit": "TFLOP/s (with the f16 conversion)", "ms": round(ms, 4), "higher_is_better": True})
+    elif name == "c4-4layer":
+        cfg = dict(synth.LLAMA3_70B, n_layers=4)
+        wmap = build_tp_map(tl, cfg, 0, 1)
+        ctx, steps = 4096, 16
+        res = {}
+        for b in (1, 16):
+            dec = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 64, batch=b)
+            ms = time_generate(tl, dec, ev, 1, ctx, 3, steps, batch=b if b > 1 else None)
+            st = dec.stats(ctx)
+            nbytes = st["weight_bytes"] + st["kv_bytes"] * b
+            res["bs%d" % b] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b * 1e3 / ms, 1), "GBs": round(nbytes / ms / 1e6, 1),
+                               "frac_hbm": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4)}
+            dec.destroy()
+        line.update({"value": res["bs16"]["tokens_per_s"], "unit": "tokens/s at batch 16 (4 layers + head)", "higher_is_better": True, "c4": res})
     else:
         cfg = dict(synth.LLAMA3_8B, n_layers=2)
         wmap = tl.map_from_tensors(synth.llama_tensors(cfg, 1, 12, 14))

@@ -226,6 +226,27 @@ def test_mid_row_counts_on_a_wide_weight(orc):
             assert relerr(got[i][rows], ref[i]) < GEMM_TOL, (m, i)
 
 
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("m", [777, 1100])
+def test_qgemm_two_accumulators_ragged_rows(orc, t, m):
+    """148 row tiles x more than 512 activation rows: the GEMM gives each CTA 512 rows as two accumulators.  777 rows leave
+    the last CTA 9 rows in its second accumulator, 1100 rows leave the last CTA no second accumulator at all.  Sampled
+    weight rows against the oracle, every activation row."""
+    n, k = 148 * 128, 512
+    rng = np.random.default_rng(6000 + t + m)
+    w = synth.random_quant(t, n, k, rng)
+    q = tl.QTensor.from_gguf_bytes(t, n, k, w)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    x[511] *= 300.0
+    x[512] *= 1e-2
+    got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+    rows = np.unique(np.concatenate([np.arange(0, n, 199), [127, 128, n - 1]]))
+    ref = orc.qmatmul(t, w[rows].reshape(-1), len(rows), k, x)
+    assert got.shape == (m, n)
+    for i in range(m):
+        assert relerr(got[i][rows], ref[i]) < GEMM_TOL, i
+
+
 # ---- dense QTensors: every other tensor type the reference's loader wraps in a QTensor ---------------------
 DENSE = [(synth.F32, 24, 80), (synth.F16, 24, 80), (synth.Q4_1, 24, 96), (synth.Q5_0, 24, 96), (synth.Q5_1, 40, 320),
          (synth.Q8_1, 24, 64), (synth.Q4_0, 24, 96), (synth.Q8_0, 33, 160)]

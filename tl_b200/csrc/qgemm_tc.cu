@@ -6,14 +6,19 @@
 // rows and never exists in f32.
 //
 // One CTA computes 128 weight rows x NT activation rows (NT <= 256) on the 5th-generation tensor cores:
-//   * the weight tile is the A operand (MMA M = 128): sixteen producer warps (two per 16 weight rows, each
-//     taking two of a unit's four 64-wide groups) read the quantized units with coalesced 16-byte loads,
-//     dequantise in registers (f16 pair arithmetic on exact integers, see store4) and store the 128 x 64 f16 tile into shared
-//     memory in the K-major 128-byte-swizzled layout tcgen05 reads, in a bank-conflict-free order;
-//   * the activation tile is the B operand (MMA N = NT): f16 rows, brought in by TMA
-//     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past M filled with zeros);
-//   * one thread issues tcgen05.mma (kind::f16, f32 accumulate) for each 64-wide K step as soon as both
-//     halves of the stage have arrived on its mbarrier; tcgen05.commit frees the stage for the producers;
+//   * the weight tile is the A operand (MMA M = 128) and lives in TENSOR MEMORY, never in shared memory: sixteen
+//     producer warps (two per 16 weight rows, each taking two of a unit's four 64-wide groups) read the quantized
+//     units with coalesced 16-byte loads, dequantise in registers (f16 pair arithmetic on exact integers, see
+//     store4) and write their 16 rows x 64 K of a stage with one tcgen05.st (eight stages of 32 columns beside the
+//     accumulator's 256);
+//   * the activation tile is the B operand (MMA N = NT): f16 rows, brought into a shared-memory ring by TMA
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle, rows past M filled with zeros).  The ring is as deep as shared
+//     memory allows (6 stages of 32 KB at NT = 256, 16 for narrow tiles): a TMA load takes ~1.5 us from request to
+//     arrival, so a K step can only be as short as that divided by the depth;
+//   * one thread issues tcgen05.mma (kind::f16, A from tensor memory, B from shared memory, f32 accumulate) for each
+//     64-wide K step as soon as its barrier has the eight producer warps' arrivals and the TMA bytes; one
+//     tcgen05.commit per K step reports its completion, which frees the weight stage for the producers (8 K steps
+//     later) and the activation stage for the TMA thread (ring depth later);
 //   * the accumulator lives in tensor memory (128 lanes x NT columns f32); after the last K step the
 //     producer warps read it back with tcgen05.ld, undo the per-row activation scaling and write
 //     Y[token][row] (32 consecutive floats per warp store).
@@ -36,14 +41,18 @@ namespace {
 
 constexpr int kGemmRows = 128;      // weight rows per CTA (MMA M)
 constexpr int kGemmBK = 64;         // K per stage: one 128-byte swizzle row of f16
-constexpr int kGemmStages = 4;
-constexpr int kGemmMaxTok = 256;    // activation rows per CTA (MMA N), multiple of 16
-constexpr int kStageA = kGemmRows * kGemmBK * 2;      // 16 KB
-constexpr int kStageB = kGemmMaxTok * kGemmBK * 2;    // 32 KB
-constexpr int kGemmProducers = 16;  // dequantising warps: warp w and w + 8 share 16 weight rows, two 64-groups of every unit each
-constexpr int kGemmThreads = (kGemmProducers + 2) * 32;   // + the TMA warp and the MMA / tensor-memory warp
-constexpr int kTmemCols = 256;
 
+constexpr int kGemmProducers = 16;  // dequantising warps: two per 16 weight rows, two 64-groups of every unit each
+constexpr int kGemmThreads = (kGemmProducers + 2) * 32;   // + the TMA warp and the MMA / tensor-memory warp
+// Tensor memory: accumulator in columns [0, 256), weight stages (128 lanes x 32 columns of f16 pairs each) above
+constexpr int kTmemCols = 512;
+constexpr int kTmemA0 = 256;
+constexpr int kStageACols = kGemmBK / 2;
+constexpr int kGemmAStages = 8;
+// Shared memory: the activation ring.  One barrier pair per K step in flight: slot kt % slots, slots = max(8, ring depth)
+constexpr int kGemmBBytes = 192 * 1024;
+constexpr int kGemmMaxSlots = 16;
+constexpr int kGemmSmemMax = kGemmBBytes + 1024 + 8 * (2 * kGemmMaxSlots + 1) + 64;   // ring + alignment slack + barriers
 constexpr int kGemmMaxW = 3;        // weights of one launch (q | k | v share their activations)
 
 struct GemmParams {
@@ -55,7 +64,8 @@ struct GemmParams {
     int n_w;
     int64_t upt;            // units per 16-row tile (K / 256)
     int m;                  // activation rows
-    int nt;                 // activation rows per CTA
+    int nt;                 // activation rows per CTA (MMA N)
+    int nb;                 // depth of the activation ring
     int kt_total;           // K / 64
     int unit_bytes;
     const float *inv_scale; // [m]
@@ -70,10 +80,6 @@ struct GemmParams {
     int col0[kGemmMaxW];    // first column of weight i inside a partial row
 };
 
-__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b)
-{
-    asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
-}
 __device__ __forceinline__ uint32_t hfma2u(uint32_t a, uint32_t b, uint32_t c)
 {
     uint32_t d;
@@ -96,33 +102,38 @@ __device__ __forceinline__ uint32_t byte_h2(uint32_t w, int i)
 {
     return hsub2(prmt(w, 0x64646464u, 0x4040u | (uint32_t)i | ((uint32_t)i << 8)), 0x64006400u);
 }
+
+// One warp's share of one weight stage: 16 rows x 64 K as the A operand of the MMA, in tensor memory.  tcgen05.st
+// writes 16 lanes x 256 bits at a time: lane (r, c) = (lane / 4, lane % 4) of the warp gives, for each 16-wide K chunk
+// j, two 32-bit columns (2 c and 2 c + 1 of the chunk's eight, i.e. K 16 j + 4 c .. + 3 as two f16 pairs) of row r and
+// two of row r + 8 - the ownership the unit layout gives the lanes anyway.  The sixteen words of a 64-group are
+// collected here and stored with one instruction: v[4 j + 2 rs + {0, 1}] = chunk j, row r + 8 rs.
+struct AFrag {
+    uint32_t v[16];
+    __device__ __forceinline__ void flush(uint32_t taddr) const
+    {
+        asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                     ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                       "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+};
 // Four weights from the four bytes b0..b3 of `bytes` (each 0..255), in f16 pair arithmetic:
 //     w = (b * p1 + p2) * p3 + p4        (p1..p4: the same f16 value in both halves)
 // The bytes enter as 1024 + b (0x6400 | b), which is exact, and both fused multiply-adds round once.
-// The 8 bytes stored hold the weights in the order (b0, b2, b1, b3): inside every group of four the
-// middle two K positions are exchanged, and the activation rows are written in the same order
-// (x_to_f16_kernel), which leaves every dot product unchanged.
-__device__ __forceinline__ void store4(uint32_t addr, uint32_t bytes, uint32_t p1, uint32_t p2, uint32_t p3, uint32_t p4)
+// The two words hold the weights in the order (b0, b2, b1, b3): inside every group of four the middle two K positions
+// are exchanged, and the activation rows are written in the same order (x_to_f16_kernel), which leaves every dot
+// product unchanged.  They become chunk j of row r + 8 rs.
+__device__ __forceinline__ void store4(AFrag &f, int j, int rs, uint32_t bytes, uint32_t p1, uint32_t p2, uint32_t p3, uint32_t p4)
 {
     const uint32_t x02 = prmt(bytes, 0x64646464u, 0x4240u), x13 = prmt(bytes, 0x64646464u, 0x4341u);   // (1024 + b0, 1024 + b2), (1024 + b1, 1024 + b3)
-    sts64(addr, hfma2u(hfma2u(x02, p1, p2), p3, p4), hfma2u(hfma2u(x13, p1, p2), p3, p4));
+    f.v[4 * j + 2 * rs] = hfma2u(hfma2u(x02, p1, p2), p3, p4);
+    f.v[4 * j + 2 * rs + 1] = hfma2u(hfma2u(x13, p1, p2), p3, p4);
 }
 constexpr uint32_t kH2One = 0x3C003C00u;    // (1, 1)
 constexpr uint32_t kH2Zero = 0u;
 // (-(1024 + off), ...) for off in {8, 32, 128}: 1024 + b - (1024 + off) = b - off, exactly
 constexpr uint32_t kH2Neg1032 = 0xE408E408u, kH2Neg1056 = 0xE420E420u, kH2Neg1152 = 0xE480E480u;
-
-// Store order.  Lane (r, c) owns four 4-weight pieces per row and 64-group, at k = 16 t + 4 c, t = 0..3.  If all
-// lanes stored piece t in the same instruction, rows r and r ^ 1 of a half-warp would hit the same banks (the
-// swizzle XORs the 16-byte chunk index 2 t + c / 2 with r).  In step s, even rows store piece s and odd rows piece
-// s ^ 2: the sixteen lanes of every half-warp then cover 128 distinct bytes of the bank space.
-//
-// Byte offset, inside a 128-row x 128-byte stage, of the 8-byte piece that holds k..k+3 of `row`
-// (k a multiple of 4): rows are 128 bytes apart and the 16-byte chunk index is XORed with row % 8.
-__device__ __forceinline__ uint32_t swz(int row, int k)
-{
-    return (uint32_t)(row * 128 + ((((k >> 3) ^ (row & 7)) << 4) | ((k & 4) << 1)));
-}
 
 // ---- Q4_K: w = d * sc * q - dmin * m (crates/tl_runtime/src/quantized.rs:337-415).  The 6-bit (scale, min)
 // pairs of four sub-blocks at a time, one per byte, unpacked from the 12 packed bytes as get_scale_min_k4 does:
@@ -164,29 +175,21 @@ __device__ __forceinline__ void unit_load(Q4KRegs &u, const uint8_t *unit, int l
     u.h[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + r * 16));
     u.h[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + (r + 8) * 16));
 }
-// Dequantise 64-group g of the unit into rows row0 + r and row0 + r + 8 of the stage at `stage`.
-__device__ __forceinline__ void unit_emit(const Q4KRegs &u, int g, uint32_t stage, int row0, int lane)
+// Dequantise 64-group g of the unit (rows r and r + 8 of the warp's sixteen): chunks 0, 1 are the low nibbles
+// (k = byte index), chunks 2, 3 the high ones (k = 32 + byte index).
+__device__ __forceinline__ void unit_emit(const Q4KRegs &u, int g, AFrag &f)
 {
-    const int r = lane >> 2, c = lane & 3;
-    const bool odd = r & 1;
 #pragma unroll
     for (int rs = 0; rs < 2; rs++) {
         uint32_t scw, mw;
         q4k_scales4(u.h[rs], g >= 2, scw, mw);
         const uint32_t d2 = prmt(u.h[rs].x, 0u, 0x1010u), dmin2 = prmt(u.h[rs].x, 0u, 0x3232u);
         const Q4KSub lo = q4k_sub(scw, mw, (2 * g) & 3, dmin2), hi = q4k_sub(scw, mw, (2 * g + 1) & 3, dmin2);
-        // steps 0, 1 take the low nibbles on even rows and the high nibbles on odd rows; steps 2, 3 the others
-        const Q4KSub a = {odd ? hi.sc : lo.sc, odd ? hi.c : lo.c, odd ? hi.ndm : lo.ndm};
-        const Q4KSub b = {odd ? lo.sc : hi.sc, odd ? lo.c : hi.c, odd ? lo.ndm : hi.ndm};
-        const int row = row0 + r + 8 * rs;
 #pragma unroll
-        for (int st = 0; st < 4; st++) {   // store order rotated per row (note above swz): bank-conflict free
-            const int hs = st & 1;
-            const int nib = (st >> 1) ^ (int)odd;
-            const Q4KSub &q = (st >> 1) ? b : a;
-            const uint32_t wd = word_of(u.q[g & 1], rs * 2 + hs);   // bytes hs * 16 + 4c .. of the group's 32
-            // low nibbles are k = byte index, high nibbles k = 32 + byte index
-            store4(stage + swz(row, nib * 32 + hs * 16 + 4 * c), (wd >> (4 * nib)) & 0x0F0F0F0Fu, q.sc, q.c, d2, q.ndm);
+        for (int j = 0; j < 4; j++) {
+            const Q4KSub &q = (j >> 1) ? hi : lo;
+            const uint32_t wd = word_of(u.q[g & 1], rs * 2 + (j & 1));   // bytes 16 (j & 1) + 4c .. of the group's 32
+            store4(f, j, rs, (wd >> (4 * (j >> 1))) & 0x0F0F0F0Fu, q.sc, q.c, d2, q.ndm);
         }
     }
 }
@@ -213,16 +216,14 @@ __device__ __forceinline__ void unit_load(Q6KRegs &u, const uint8_t *unit, int l
 }
 // 64-group g = (n, sub): k = 128 n + 64 sub + [0, 64).  sub 0 takes the low nibbles of ql and bits 0-3 of qh,
 // sub 1 the high nibbles and bits 4-7; inside the group, q1 = 0 / 1 selects ql[l] / ql[l + 32].
-__device__ __forceinline__ void unit_emit(const Q6KRegs &u, int g, uint32_t stage, int row0, int lane)
+__device__ __forceinline__ void unit_emit(const Q6KRegs &u, int g, AFrag &f)
 {
-    const int r = lane >> 2, c = lane & 3, odd = r & 1;
     const int n = g >> 1, sub = g & 1;
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
-        const int row = row0 + r + 8 * hi;
 #pragma unroll
         for (int st = 0; st < 4; st++) {
-            const int h = st & 1, q1 = (st >> 1) ^ odd;
+            const int h = st & 1, q1 = st >> 1;
             const uint32_t qlw = q1 ? word_of(u.ql[hi], 2 + h) : word_of(u.ql[hi], h);
             const uint32_t qhw = word_of(u.qh[hi], n * 2 + h);
             const uint32_t nib = (sub ? (qlw >> 4) : qlw) & 0x0F0F0F0Fu;
@@ -230,7 +231,7 @@ __device__ __forceinline__ void unit_emit(const Q6KRegs &u, int g, uint32_t stag
             const int s0 = 8 * n + h + 4 * sub;   // scale index for q1 = 0; q1 = 1 is two further
             const uint32_t sb = q1 ? (word_of(u.sc[hi], (s0 + 2) >> 2) >> (8 * ((s0 + 2) & 3))) : (word_of(u.sc[hi], s0 >> 2) >> (8 * (s0 & 3)));
             const uint32_t ds2 = h2_of(u.d[hi] * (float)(int)(int8_t)(sb & 0xFFu));   // d * sc, rounded to f16 once
-            store4(stage + swz(row, q1 * 32 + h * 16 + 4 * c), nib | (two << 4), kH2One, kH2Neg1056, ds2, kH2Zero);   // (q - 32) * ds
+            store4(f, st, hi, nib | (two << 4), kH2One, kH2Neg1056, ds2, kH2Zero);   // (q - 32) * ds
         }
     }
 }
@@ -253,19 +254,18 @@ __device__ __forceinline__ uint32_t h2_pair(const uint4 &v, int i)   // i-th f16
 {
     return prmt(word_of(v, i >> 1), 0u, (i & 1) ? 0x3232u : 0x1010u);
 }
-__device__ __forceinline__ void unit_emit(const Q40Regs &u, int g, uint32_t stage, int row0, int lane)
+__device__ __forceinline__ void unit_emit(const Q40Regs &u, int g, AFrag &f)
 {
-    const int r = lane >> 2, c = lane & 3, odd = r & 1;
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
-        const int row = row0 + r + 8 * hi;
         const uint32_t d0 = h2_pair(u.d[hi], 2 * g), d1 = h2_pair(u.d[hi], 2 * g + 1);   // blocks 2g and 2g + 1 of the row's eight
 #pragma unroll
         for (int st = 0; st < 4; st++) {
-            const int nib = st & 1, b = (st >> 1) ^ odd;
+            const int nib = st & 1, b = st >> 1;
             const uint32_t d = b ? d1 : d0;
             const uint32_t wd = b ? word_of(u.q[g & 1], hi * 2 + 1) : word_of(u.q[g & 1], hi * 2);
-            store4(stage + swz(row, b * 32 + nib * 16 + 4 * c), (nib ? (wd >> 4) : wd) & 0x0F0F0F0Fu, kH2One, kH2Neg1032, d, kH2Zero);   // (q - 8) * d
+            const uint32_t nibs = (nib ? (wd >> 4) : wd) & 0x0F0F0F0Fu;
+            store4(f, st, hi, nibs, kH2One, kH2Neg1032, d, kH2Zero);   // (q - 8) * d
         }
     }
 }
@@ -284,19 +284,17 @@ __device__ __forceinline__ void unit_load(Q80Regs &u, const uint8_t *unit, int l
     u.d[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 4096 + r * 16));
     u.d[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 4096 + (r + 8) * 16));
 }
-__device__ __forceinline__ void unit_emit(const Q80Regs &u, int g, uint32_t stage, int row0, int lane)
+__device__ __forceinline__ void unit_emit(const Q80Regs &u, int g, AFrag &f)
 {
-    const int r = lane >> 2, c = lane & 3, odd = r & 1;
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
-        const int row = row0 + r + 8 * hi;
         const uint32_t d0 = h2_pair(u.d[hi], 2 * g), d1 = h2_pair(u.d[hi], 2 * g + 1);
 #pragma unroll
         for (int st = 0; st < 4; st++) {   // q + 128 as an unsigned byte u, then w = (u - 128) * d
-            const int h = st & 1, b = (st >> 1) ^ odd;
+            const int h = st & 1, b = st >> 1;
             const uint32_t d = b ? d1 : d0;
             const uint32_t wd = b ? word_of(u.q[2 * (g & 1) + 1], hi * 2 + h) : word_of(u.q[2 * (g & 1)], hi * 2 + h);
-            store4(stage + swz(row, b * 32 + 16 * h + 4 * c), wd ^ 0x80808080u, kH2One, kH2Neg1152, d, kH2Zero);
+            store4(f, st, hi, wd ^ 0x80808080u, kH2One, kH2Neg1152, d, kH2Zero);
         }
     }
 }
@@ -314,13 +312,14 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
     // descriptor version 1, layout type 2 (SWIZZLE_128B)
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+// A operand from tensor memory: 128 lanes (rows) x 8 columns (16 f16 along K, two per column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
@@ -341,28 +340,50 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
-// ---- one dequantising warp: 64-groups 2 HALF and 2 HALF + 1 of every unit of its 16 rows
+// Asks L2 for `bytes` (a multiple of 16) at the 16-byte aligned `ptr`; nothing is written on the SM.
+__device__ __forceinline__ void l2_prefetch(const void *ptr, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
+}
+
+// ---- one dequantising warp: 64-groups 2 HALF and 2 HALF + 1 of every unit of its 16 rows.  `dst`: tensor-memory address
+// (the warp's 16 lanes, first column) of weight stage 0.  Barrier slot of K step kt: kt % slots; weight stage: kt % 8.
 template <int FMT, int HALF>
-__device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, bool have, int row0, int lane, uint32_t sA,
+__device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, bool have, int lane, uint32_t dst, int slots,
                                         uint32_t full0, uint32_t empty0, volatile int *abort_flag, int u0, int units)
 {
     typename UnitRegs<FMT>::type cur, nxt;
     ub += (size_t)u0 * p.unit_bytes;          // this CTA's K range starts at unit u0
+    // Registers hold one unit ahead; one lane of the pair's first warp asks L2 for the units kAhead further on, so
+    // that the register loads find them there.
+    constexpr int kAhead = 4;
+    const bool fetcher = have && HALF == 0 && lane == 0;
+    if (fetcher)
+        for (int j = 1; j <= kAhead && j < units; j++) l2_prefetch(ub + (size_t)j * p.unit_bytes, (uint32_t)p.unit_bytes);
     if (have) unit_load<HALF>(nxt, ub, lane);
     for (int u = 0; u < units; u++) {
         if (have) {
             cur = nxt;
             if (u + 1 < units) unit_load<HALF>(nxt, ub + (size_t)(u + 1) * p.unit_bytes, lane);
         }
+        if (fetcher && u + 1 + kAhead < units) l2_prefetch(ub + (size_t)(u + 1 + kAhead) * p.unit_bytes, (uint32_t)p.unit_bytes);
 #pragma unroll
         for (int gg = 0; gg < 2; gg++) {
             const int g = HALF * 2 + gg;
-            const int kt = u * 4 + g, s = kt % kGemmStages, round = kt / kGemmStages;
-            if (round > 0 && !mbar_wait(empty0 + 8u * s, (round - 1) & 1, abort_flag, p.err, 21)) return false;
-            if (have) unit_emit(cur, g, sA + s * kStageA, row0, lane);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic stores -> visible to the MMA's reads
+            const int kt = u * 4 + g;
+            if (kt >= kGemmAStages) {   // the stage was last read by the MMAs of K step kt - 8
+                const int back = kt - kGemmAStages;
+                if (!mbar_wait(empty0 + 8u * (uint32_t)(back % slots), (uint32_t)(back / slots) & 1u, abort_flag, p.err, 21)) return false;
+                tc_fence_after();
+            }
+            if (have) {
+                AFrag f;
+                unit_emit(cur, g, f);
+                f.flush(dst + (uint32_t)((kt % kGemmAStages) * kStageACols));
+            }
+            tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(full0 + 8u * s);
+            if (lane == 0) mbar_arrive(full0 + 8u * (uint32_t)(kt % slots));
         }
     }
     return true;
@@ -379,14 +400,23 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     volatile int *abort_flag = &abort_word;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
-    const uint32_t sA = base, sB = base + kGemmStages * kStageA;
-    const uint32_t bars = sB + kGemmStages * kStageB;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (kGemmStages + s); };
-    const uint32_t accum_bar = bars + 8u * (2 * kGemmStages);
+    const uint32_t sB = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
+    const int nb = p.nb, slots = max(kGemmAStages, nb);
+    const uint32_t stage_b = (uint32_t)p.nt * 128u;                // bytes of one activation stage (multiple of 2048)
+    const uint32_t bars = sB + (uint32_t)nb * stage_b;
+    // Slot kt % slots serves K step kt.  full: eight producer warps + the TMA thread's expect_tx; empty: the commit
+    // after the step's MMAs.  A waiter for K step kt - d (d = 8 for the weight stage, nb for the activation stage) asks
+    // for phase (kt - d) / slots of that slot; the phase before it has always completed by then (K steps complete in
+    // order and the waiter itself saw step kt - d - 1 ... complete earlier), so the parity test cannot alias.
+    auto full_bar = [&](int i) { return bars + 8u * (uint32_t)i; };
+    auto empty_bar = [&](int i) { return bars + 8u * (uint32_t)(kGemmMaxSlots + i); };
+    const uint32_t accum_bar = bars + 8u * (2 * kGemmMaxSlots);
 
     const int tok0 = blockIdx.y * p.nt;
+    // Consecutive MMAs into one accumulator wait for each other (a narrow tile's MMA is over long before its result is
+    // back in tensor memory), so tiles of up to 64 activation rows give each of a K step's four 16-wide chunks an
+    // accumulator of its own (columns 0, 64, 128, 192), tiles of up to 128 rows two; the epilogue adds them.
+    const int nacc = p.nt <= 64 ? 4 : p.nt <= 128 ? 2 : 1, acc_stride = 256 / nacc;
     // K range of this CTA: whole units (4 K steps each), split evenly over grid.z
     const int units_all = (int)p.upt, split = blockIdx.z;
     const int u0 = units_all * split / p.splits, u1 = units_all * (split + 1) / p.splits;
@@ -398,9 +428,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
 
     if (tid == 0) {
         abort_word = 0;
-        for (int s = 0; s < kGemmStages; s++) {
-            mbar_init(full_bar(s), 9);    // eight dequantising warps + the TMA thread's arrive.expect_tx
-            mbar_init(empty_bar(s), 1);   // one tcgen05.commit
+        for (int i = 0; i < slots; i++) {
+            mbar_init(full_bar(i), 9);
+            mbar_init(empty_bar(i), 1);
         }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -417,12 +447,15 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
 
     if (warp < kGemmProducers) {
         // ------------------------------------------------ dequantise the weight tile, stage by stage
-        const int sub = warp & 7;
+        // 16 rows per warp.  A warp reaches only the tensor-memory lanes of its quarter (warp % 4), so warps w and
+        // w + 4 take the two halves of quarter w % 4, and w + 8, w + 12 the same rows' other two 64-groups.
+        const int sub = 2 * (warp & 3) + ((warp >> 2) & 1);
         const int tile16 = rt * 8 + sub;
         const bool have = tile16 < p.n_tiles16[wi];
         const uint8_t *ub = p.w[wi] + (size_t)(have ? tile16 : 0) * p.upt * p.unit_bytes;
-        const bool ok = warp < 8 ? produce<FMT, 0>(p, ub, have, sub * 16, lane, sA, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0)
-                                 : produce<FMT, 1>(p, ub, have, sub * 16, lane, sA, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0);
+        const uint32_t dst = tmem + ((uint32_t)(sub * 16) << 16) + (uint32_t)kTmemA0;
+        const bool ok = warp < 8 ? produce<FMT, 0>(p, ub, have, lane, dst, slots, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0)
+                                 : produce<FMT, 1>(p, ub, have, lane, dst, slots, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0);
         // ------------------------------------------------ epilogue: tensor memory -> Y[token][row]
         if (ok && mbar_wait(accum_bar, 0, abort_flag, p.err, 22)) {
             tc_fence_after();
@@ -445,31 +478,44 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
                 }
                 uint32_t v[8];
                 tmem_ld8(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+                float acc[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[j] = __uint_as_float(v[j]);
+                for (int a = 1; a < nacc; a++) {     // narrow tiles: the K chunks of a step went to accumulators of their own
+                    tmem_ld8(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * acc_stride + c0), v);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[j] += __uint_as_float(v[j]);
+                }
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int tok = tok0 + c0 + j;
                     if (tok < p.m && row < n_rows) {
-                        if (partial) pout[(size_t)tok * p.n_all + row] = __uint_as_float(v[j]) * sc[j];
-                        else out[(size_t)tok * n_rows + row] = rs[j] + __uint_as_float(v[j]) * sc[j];
+                        if (partial) pout[(size_t)tok * p.n_all + row] = acc[j] * sc[j];
+                        else out[(size_t)tok * n_rows + row] = rs[j] + acc[j] * sc[j];
                     }
                 }
             }
         }
     } else if (warp == kGemmProducers) {
-        // ------------------------------------------------ TMA: activation tile of each stage
+        // ------------------------------------------------ TMA: activation tile of each K step, nb steps ahead of the MMAs
         if (lane == 0) {
             int issued = 0;
+            int st = 0, slot = 0, bslot = 0, bround = 0;       // kt % nb, kt % slots, (kt - nb) % slots, (kt - nb) / slots
             for (int kt = 0; kt < KT; kt++) {
-                const int s = kt % kGemmStages, round = kt / kGemmStages;
-                if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, p.err, 23)) break;
-                mbar_expect_tx(full_bar(s), (uint32_t)p.nt * 128u);
-                tma_load_2d(sB + s * kStageB, &xmap, (kt_base + kt) * kGemmBK, tok0, full_bar(s));
+                if (kt >= nb) {
+                    if (!mbar_wait(empty_bar(bslot), (uint32_t)bround & 1u, abort_flag, p.err, 23)) break;
+                    if (++bslot == slots) { bslot = 0; bround++; }
+                }
+                mbar_expect_tx(full_bar(slot), stage_b);
+                tma_load_2d(sB + (uint32_t)st * stage_b, &xmap, (kt_base + kt) * kGemmBK, tok0, full_bar(slot));
                 issued = kt + 1;
+                if (++st == nb) st = 0;
+                if (++slot == slots) slot = 0;
             }
             if (*abort_flag) {
                 // let copies that were already requested land before the CTA gives its shared memory back
-                for (int kt = max(0, issued - kGemmStages); kt < issued; kt++)
-                    mbar_wait_drain(full_bar(kt % kGemmStages), (kt / kGemmStages) & 1);
+                for (int kt = max(0, issued - nb); kt < issued; kt++)
+                    mbar_wait_drain(full_bar(kt % slots), (uint32_t)(kt / slots) & 1u);
             }
         }
     } else {
@@ -477,15 +523,18 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | ((uint32_t)(p.nt >> 3) << 17) | ((uint32_t)(kGemmRows >> 4) << 24);   // f32 D, f16 A/B, K-major both
             bool ok = true;
+            int st = 0, slot = 0, round = 0;
             for (int kt = 0; kt < KT; kt++) {
-                const int s = kt % kGemmStages, round = kt / kGemmStages;
-                if (!mbar_wait(full_bar(s), round & 1, abort_flag, p.err, 24)) { ok = false; break; }
+                if (!mbar_wait(full_bar(slot), (uint32_t)round & 1u, abort_flag, p.err, 24)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t ad = smem_desc_sw128(sA + s * kStageA), bd = smem_desc_sw128(sB + s * kStageB);
+                const uint64_t bd = smem_desc_sw128(sB + (uint32_t)st * stage_b);
+                const uint32_t ta = tmem + (uint32_t)(kTmemA0 + (kt % kGemmAStages) * kStageACols);
 #pragma unroll
-                for (int k16 = 0; k16 < kGemmBK / 16; k16++)   // 16 f16 = 32 bytes further along the swizzle row
-                    umma_f16(tmem, ad + 2u * k16, bd + 2u * k16, idesc, (kt | k16) != 0);
-                umma_commit(empty_bar(s));   // arrives when the MMAs above have read the stage
+                for (int k16 = 0; k16 < kGemmBK / 16; k16++)   // 16 f16: 8 columns of tensor memory, 32 bytes along the swizzle row
+                    umma_f16_ts(tmem + (uint32_t)((k16 & (nacc - 1)) * acc_stride), ta + 8u * k16, bd + 2u * k16, idesc, kt != 0 || k16 >= nacc);
+                umma_commit(empty_bar(slot));   // arrives when the MMAs above have read both stages
+                if (++st == nb) st = 0;
+                if (++slot == slots) { slot = 0; round++; }
             }
             umma_commit(accum_bar);
             if (!ok) mbar_wait_drain(accum_bar, 0);   // MMAs already issued finish before the tensor memory is freed
@@ -622,13 +671,14 @@ PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder()
     return fn;
 }
 
-// Activation rows per CTA: the widest tile that still gives every SM work, else 128 (more, smaller CTAs).
+// Activation rows per CTA: up to 128 rows one tile; above, 256-row tiles if they give every SM work, else 128-row
+// ones (more, smaller CTAs).
 int pick_token_tile(int64_t m, int64_t n, int sms)
 {
     const int64_t row_tiles = (n + kGemmRows - 1) / kGemmRows;
     if (m <= 128) return (int)((m + 15) / 16 * 16);
     const int64_t ctas256 = row_tiles * ((m + 255) / 256);
-    if (m > 128 && ctas256 >= sms) return 256;
+    if (ctas256 >= sms) return 256;
     return 128;
 }
 
@@ -642,13 +692,32 @@ tlb_status launch_fmt_gemm(dim3 grid, size_t smem, cudaStream_t stream, const CU
 {
     static bool attr_set = false;
     if (!attr_set) {
-        TLB_CUDA(cudaFuncSetAttribute(qgemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TLB_CUDA(cudaFuncSetAttribute(qgemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemMax));
         attr_set = true;
     }
     qgemm_kernel<FMT><<<grid, kGemmThreads, smem, stream>>>(map, p);
     return TLB_OK;
 }
 }  // namespace
+
+// K-splits for m activation rows on `tiles` 128-row tiles of `units` 256-wide K units, n_all output columns in all.
+// With few token rows a tile's time is its K length (the dequantising warps set the pace), so the launch costs
+// waves x units-per-split; a split count is worth its second pass over s x m x n_all partial sums when it evens out
+// the last wave or fills idle SMs.  Returns the count with the least estimated time (1 = no split).
+int qgemm_k_splits(int64_t m, int64_t tiles, int64_t units, int64_t n_all, int sm_count)
+{
+    if (m > 64 || units < 8) return 1;
+    const double us_per_unit = 1.8;                                         // 4 K steps of ~0.45 us
+    int best = 1;
+    double best_us = 1e30;
+    for (int s = 1; s <= 16 && s * 4 <= units; s++) {
+        const int64_t waves = (tiles * s + sm_count - 1) / sm_count, len = (units + s - 1) / s;
+        double us = (double)(waves * len) * us_per_unit + (double)waves * 2.0;   // + fill and drain of every wave
+        if (s > 1) us += 4.0 + (double)(s * m * n_all) * 8.0 / 3.0e6;       // the summing launch: its latency + partials written and read
+        if (us < best_us - 0.5) { best_us = us; best = s; }
+    }
+    return best;
+}
 
 tlb_status qgemm_prepare(GemmAct *a, const float *x, const float *x2, int64_t m, int64_t k, const float *norm_w, float eps)
 {
@@ -716,21 +785,18 @@ tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct 
     p.upt = w0->upt;
     p.m = (int)m;
     p.nt = nt;
+    p.nb = std::max(4, std::min(kGemmMaxSlots, kGemmBBytes / (nt * 128)));
     p.kt_total = (int)(a.k / kGemmBK);
     p.unit_bytes = qformat(w0->type)->unit_bytes;
     p.inv_scale = (const float *)a.inv->ptr;
     p.resid = resid;
     p.err = c->err_flag;
 
-    const size_t smem = (size_t)kGemmStages * (kStageA + kStageB) + 1024 + 128;
-    // K-splits when the tiles alone leave most SMs idle (few activation rows on a narrow weight): as many as bring the
-    // grid to about two waves, each at least 4 units (1024 of K) long
-    const int64_t tok_tiles = (m + nt - 1) / nt, ctas = row_tiles * tok_tiles;
-    int splits = 1;
-    if (m <= 64 && ctas * 2 <= c->sm_count)
-        splits = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(16, p.upt / 4), (2 * c->sm_count) / ctas));
+    const size_t smem = (size_t)p.nb * nt * 128 + (kGemmSmemMax - kGemmBBytes);
+    const int64_t tok_tiles = (m + nt - 1) / nt;
     int64_t n_all = 0;
     for (int i = 0; i < kGemmMaxW; i++) { p.col0[i] = (int)n_all; n_all += p.n[i]; }
+    const int splits = qgemm_k_splits(m, row_tiles * tok_tiles, p.upt, n_all, c->sm_count);
     Storage *part = nullptr;
     if (splits > 1) {
         part = storage_alloc((size_t)splits * m * n_all * sizeof(float));

@@ -601,15 +601,19 @@ tlb_status launch_qmatvec(const MatvecJob &job)
 using namespace tlb;
 
 // More than 4 activation rows: the matvec re-streams the weight once per group of 4 rows, the tensor-core GEMM
-// reads it once but pays a fixed ~0.4 us per 64-wide K step and wave of 148 CTAs.  Above kGemmMinRows rows the
-// GEMM always wins; from 5 rows on the cheaper of the two estimates (fitted to timings on the Llama-3-8B shapes:
-// 4096 x 4096 switches at 9 rows, 14336 x 4096 at 5, 4096 x 14336 at 16).
+// reads it once but pays a fixed ~0.4 us per 64-wide K step and wave of CTAs (one per SM), K split over several CTAs
+// where the row tiles alone leave SMs idle.  Above kGemmMinRows rows the GEMM always wins; from 5 rows on the cheaper
+// of the two estimates (fitted to timings on the Llama-3-8B shapes).
 static bool prefer_gemm(int64_t m, const tlb_qtensor *w)
 {
     if (m <= 4 || !qgemm_supported(w->type) || w->k % 256) return false;
     if (m > kGemmMinRows) return true;
-    const double waves = (double)(((w->n + 127) / 128 + 147) / 148);
-    const double gemm_us = 12.0 + 0.4 * (double)(w->k / 64) * waves;
+    Context *c = ctx();
+    const int sms = c ? c->sm_count : 148;
+    const int64_t tiles = (w->n + 127) / 128;
+    const int splits = qgemm_k_splits(m, tiles, w->upt, w->n, sms);
+    const double waves = (double)((tiles * splits + sms - 1) / sms);
+    const double gemm_us = (splits > 1 ? 16.0 : 12.0) + 1.8 * (double)((w->upt + splits - 1) / splits) * waves;
     const double per_mb = w->n >= w->k ? 1.0 : 0.5;   // wide-K weights stream faster with 4 rows: fewer results per byte
     const double matvec_us = (double)((m + 3) / 4) * (6.0 + (double)w->nbytes() * 1e-6 * per_mb);
     return gemm_us < matvec_us;

@@ -125,6 +125,9 @@ namespace tlb {
 constexpr int kGemmMinRows = TLB_GEMM_MIN_ROWS;
 bool qgemm_supported(int ggml_type);
 tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out);
+// K-splits the tensor-core GEMM uses for m activation rows on `tiles` row tiles of `units` 256-wide K units each and
+// n_all output columns (1 = none)
+int qgemm_k_splits(int64_t m, int64_t tiles, int64_t units, int64_t n_all, int sm_count);
 // the same in steps, so that several weights can share one conversion of the activations:
 // f32 rows (optionally silu(x) * x2, optionally RMS-normalised with norm_w) -> scaled f16 rows; then out = [resid +] act . W^T
 struct GemmAct { Storage *xh = nullptr, *inv = nullptr; int64_t m = 0, k = 0; };
