@@ -446,13 +446,23 @@ def measure_tp(tl, dist, rank, world, ev, steps=32, ctx=4096, with_single=True, 
 
     wmap = build_tp_map(tl, cfg, rank, world)
     dec = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 2 * steps + 16, tp_size=world, tp_rank=rank)
+    dist.barrier()       # the ranks enter a step together: waits on another rank's partial sums are bounded (about a second)
     ms = reduce_ms(time_generate(tl, dec, ev, 1, ctx, 4, steps))
     st = dec.stats(ctx)
-    out["bs1"] = {"tokens_per_s": round(1e3 / ms, 2), "ms_per_token": round(ms, 3), "transport": "peer-memory all-reduce",
+    out["bs1"] = {"tokens_per_s": round(1e3 / ms, 2), "ms_per_token": round(ms, 3), "transport": "partial sums pushed to the peers by the matvec launches, added by the consuming launch",
                   "weight_bytes_per_rank": st["weight_bytes"], "kv_bytes_per_rank": st["kv_bytes"],
                   "GBs_per_rank": round((st["weight_bytes"] + st["kv_bytes"]) / ms / 1e6, 1)}
+    tl.tp_exchange_in_launch(False)
+    dec_k = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 2 * steps + 16, tp_size=world, tp_rank=rank)
+    dist.barrier()
+    ms_k = reduce_ms(time_generate(tl, dec_k, ev, 1, ctx, 4, steps))
+    out["bs1_allreduce_launch"] = {"tokens_per_s": round(1e3 / ms_k, 2), "ms_per_token": round(ms_k, 3),
+                                   "transport": "one-shot peer-memory all-reduce launch between the matvecs"}
+    dec_k.destroy()
+    tl.tp_exchange_in_launch(True)
     tl.tp_p2p_disable()
     dec_n = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 2 * steps + 16, tp_size=world, tp_rank=rank)
+    dist.barrier()
     ms_n = reduce_ms(time_generate(tl, dec_n, ev, 1, ctx, 4, steps))
     out["bs1_nccl"] = {"tokens_per_s": round(1e3 / ms_n, 2), "ms_per_token": round(ms_n, 3), "transport": "ncclAllReduce"}
     dec_n.destroy()
@@ -460,6 +470,7 @@ def measure_tp(tl, dist, rank, world, ev, steps=32, ctx=4096, with_single=True, 
     dec.destroy()
     if batch:
         decb = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 2 * steps + 16, tp_size=world, tp_rank=rank, batch=batch)
+        dist.barrier()
         msb = reduce_ms(time_generate(tl, decb, ev, 1, ctx, 2, max(4, steps // 4), batch=batch))
         out["bs%d" % batch] = {"tokens_per_s": round(batch * 1e3 / msb, 2), "ms_per_step": round(msb, 3)}
         decb.destroy()

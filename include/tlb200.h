@@ -248,6 +248,10 @@ tlb_status tlb_tp_p2p_export(void *handle_out, size_t handle_bytes);
 tlb_status tlb_tp_p2p_attach(const void *handles, int n_handles);
 tlb_status tlb_tp_p2p_disable(void);   /* back to NCCL for every size (all ranks together, between steps) */
 tlb_status tlb_tp_p2p_enable(void);    /* and on again, without re-attaching */
+/* With peer memory attached, batch-1 decode sessions created afterwards exchange their partial sums inside the matvec
+ * launches (on, the default: o_proj / ffn_down push their tiles to every rank, the next launch adds them while it
+ * loads) or through an all-reduce launch of their own between the matvecs (off).  All ranks the same setting. */
+tlb_status tlb_tp_exchange_in_launch(int on);
 /* Which way a tensor is split, by its GGUF name: 0 replicated, 1 along rows (attn_q/k/v, ffn_gate/up, output.weight),
  * 2 along columns (attn_output, ffn_down). */
 int        tlb_tp_split_kind(const char *name);

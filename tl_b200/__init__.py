@@ -77,6 +77,12 @@ def tp_p2p_enable():
     check(lib().tlb_tp_p2p_enable())
 
 
+def tp_exchange_in_launch(on):
+    """Decode sessions created afterwards exchange partial sums inside the matvec launches (True) or through an
+    all-reduce launch of their own (False); needs attached peer memory, the same setting on all ranks."""
+    check(lib().tlb_tp_exchange_in_launch(1 if on else 0))
+
+
 def tp_split_kind(name):
     return int(lib().tlb_tp_split_kind(name.encode()))
 

@@ -115,7 +115,7 @@ def lib():
     d("tlb_decoder_logits_batch", S, vp, vp)
     d("tlb_tp_unique_id", S, vp, sz); d("tlb_tp_init", S, vp, sz, C.c_int, C.c_int, C.c_double); d("tlb_tp_poll", S)
     d("tlb_tp_shutdown", S); d("tlb_tp_rank", C.c_int); d("tlb_tp_size", C.c_int); d("tlb_allreduce", S, vp)
-    d("tlb_tp_p2p_export", S, vp, sz); d("tlb_tp_p2p_attach", S, vp, C.c_int); d("tlb_tp_p2p_disable", S); d("tlb_tp_p2p_enable", S)
+    d("tlb_tp_p2p_export", S, vp, sz); d("tlb_tp_p2p_attach", S, vp, C.c_int); d("tlb_tp_p2p_disable", S); d("tlb_tp_p2p_enable", S); d("tlb_tp_exchange_in_launch", S, C.c_int)
     d("tlb_tp_split_kind", C.c_int, C.c_char_p)
     d("tlb_tp_shard_bytes", S, C.c_int, C.c_int, i64, i64, vp, sz, C.c_int, C.c_int, vp, sz, pi64, pi64, C.POINTER(sz))
     d("tlb_map_add_tp", S, vp, C.c_char_p, C.c_int, pi64, C.c_int, vp, sz, C.c_int, C.c_int)

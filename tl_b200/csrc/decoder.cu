@@ -52,6 +52,7 @@ struct tlb_decoder {
     cudaGraphExec_t graph = nullptr;
     uint64_t graph_kernels = 0;
     bool pdl = true;
+    bool tp_pdl_ar = false;          // tensor-parallel chain with all-reduce launches of this library between the matvecs: they keep the dependent-launch chain
     bool dry = false;            // enqueue_step only validates the matvec launches
     std::vector<void *> allocs;
     size_t kv_layer_elems = 0;
@@ -251,7 +252,7 @@ tlb_status enqueue_head(tlb_decoder *d, const float *ssq_parts, const float *x =
         j.ssq_parts = ssq_parts; j.n_parts = ssq_parts ? (dm + 15) / 16 : 0;
         j.norm_w = d->out_norm->f32(); j.eps = c.eps;
         j.last_of_chain = true;
-        j.pdl = d->pdl && !x2;     // behind a collective: a plain stream dependency
+        j.pdl = d->pdl && (!x2 || d->tp_pdl_ar);     // behind an NCCL collective: a plain stream dependency
         j.dry_run = d->dry;
         TLB_TRY(launch_qmatvec(j));
     }
@@ -305,6 +306,7 @@ tlb_status enqueue_step_tp(tlb_decoder *d)
 {
     const tlb_decoder_cfg &c = d->cfg;
     const int dm = c.d_model, qd = d->H * c.head_dim, kvd = d->KVH * c.head_dim, F = d->F;
+    d->tp_pdl_ar = tp_allreduce_is_kernel(dm);   // this library's all-reduce launch takes part in the dependent-launch chain
     for (int l = 0; l < c.n_layers; l++) {
         const LayerW &w = d->layers[l];
         {   // K1: residual (+ the summed ffn_down of the layer before) -> RMSNorm -> q | k | v of this rank's heads
@@ -315,7 +317,7 @@ tlb_status enqueue_step_tp(tlb_decoder *d)
             j.type = w.q->type; j.k = dm; j.m = 1;
             j.prologue = PRO_ADD_NORM; j.norm_w = w.attn_norm->f32(); j.eps = c.eps;
             if (l == 0) { j.emb_table = d->emb->f32(); j.token = d->state; j.x_out = d->xb; j.pdl = d->pdl; }
-            else { j.x = d->xa; j.x2 = d->part; j.x_out = d->xb; j.pdl = false; }
+            else { j.x = d->xa; j.x2 = d->part; j.x_out = d->xb; j.pdl = d->pdl && d->tp_pdl_ar; }
             j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
@@ -351,7 +353,7 @@ tlb_status enqueue_step_tp(tlb_decoder *d)
             j.prologue = PRO_ADD_NORM; j.x = d->xb; j.x2 = d->part; j.x_out = d->xa;
             j.norm_w = w.ffn_norm->f32(); j.eps = c.eps;
             j.finish = FIN_SILU;
-            j.pdl = false;
+            j.pdl = d->pdl && d->tp_pdl_ar;
             j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
         }
@@ -372,9 +374,15 @@ tlb_status enqueue_step_tp(tlb_decoder *d)
 
 tlb_status enqueue_step(tlb_decoder *d)
 {
-    if (d->tp > 1) return enqueue_step_tp(d);
+    // A tensor-parallel shard with peer memory attached runs the single-GPU chain on its own heads / hidden units: o_proj
+    // and ffn_down add their partial sums over the ranks inside the launch, tile by tile (MatvecJob::tp_reduce), so what
+    // they leave - the residual and the per-tile sums of its squares - is what the next launch expects anyway.  Without
+    // peer memory the partial sums go through collective launches between the matvecs (enqueue_step_tp).
+    TpFuse probe;
+    const bool tpr = d->tp > 1 && tp_fuse_args(&probe) && d->cfg.d_model <= probe.rank_stride;
+    if (d->tp > 1 && !tpr) return enqueue_step_tp(d);
     const tlb_decoder_cfg &c = d->cfg;
-    const int dm = c.d_model, qd = c.n_heads * c.head_dim, kvd = c.n_kv_heads * c.head_dim, F = c.ffn;
+    const int dm = c.d_model, qd = d->H * c.head_dim, kvd = d->KVH * c.head_dim, F = d->F;
     const int L = c.n_layers;
     for (int l = 0; l < L; l++) {
         const LayerW &w = d->layers[l];
@@ -408,7 +416,7 @@ tlb_status enqueue_step(tlb_decoder *d)
             a.qkv = d->qkv;
             a.kcache = (char *)d->kcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
             a.vcache = (char *)d->vcache + (size_t)l * d->kv_layer_elems * (c.kv_f16 ? 2 : 4);
-            a.kv_f16 = c.kv_f16; a.H = c.n_heads; a.KVH = c.n_kv_heads; a.D = c.head_dim; a.max_seq = c.max_seq;
+            a.kv_f16 = c.kv_f16; a.H = d->H; a.KVH = d->KVH; a.D = c.head_dim; a.max_seq = c.max_seq;
             a.pos = d->state + 1; a.rope_pos = d->state + 2; a.cos_t = d->cos_t; a.sin_t = d->sin_t; a.scale = c.attn_scale;
             a.partial = d->partial; a.counters = d->counters; a.splits = d->max_splits; a.out = d->attn; a.pdl = d->pdl;
             a.defer_merge = true;
@@ -424,6 +432,7 @@ tlb_status enqueue_step(tlb_decoder *d)
             j.att_part = d->partial; j.att_pos = d->state + 1; j.att_max_splits = d->max_splits;
             j.att_rep = c.n_heads / c.n_kv_heads; j.att_dim = c.head_dim; j.att_keys = kAttnKeysPerSplit;
             j.finish = FIN_RESID; j.resid = d->xb; j.ssq_out = d->ssq_o;   // xa = xb + o_proj(attn)
+            j.tp_reduce = tpr;
             j.pdl = d->pdl;
             j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));
@@ -447,6 +456,7 @@ tlb_status enqueue_step(tlb_decoder *d)
             j.type = w.down->type; j.k = F; j.m = 1;
             j.prologue = PRO_PLAIN; j.x = d->hbuf;
             j.finish = FIN_RESID; j.resid = d->xa; j.ssq_out = d->ssq_d;   // xb = xa + down(h)
+            j.tp_reduce = tpr;
             j.pdl = d->pdl;
             j.dry_run = d->dry;
             TLB_TRY(launch_qmatvec(j));

@@ -108,6 +108,46 @@ __device__ __forceinline__ void finish_tile_fused(const MvParams &p, const ItemR
     }
 }
 
+// ---- sum over tensor-parallel ranks, tile by tile (TpFuse).  Lane e < 16 holds row e of the tile; all 32 lanes call.
+// Every value travels as one 8-byte word {value, sequence number}: an aligned 8-byte store is indivisible, so a
+// reader that finds the sequence number it waits for has the value with it - no fence and no separate flag.
+__device__ __forceinline__ void tp_push_tile(const MvParams &p, unsigned seq, int row0, int nrows, float y, int lane)
+{
+    const int g = row0 + lane;
+    if (lane < 16 && g < nrows) {
+        const size_t at = (size_t)(seq & 1u) * p.tp.buf_stride + g;
+        const unsigned long long word = ((unsigned long long)seq << 32) | __float_as_uint(y);
+        for (int r = 0; r < p.tp.size; r++)        // 128 consecutive bytes per rank, own memory included
+            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.tp.peer_ll[r] + at), "l"(word) : "memory");
+    }
+}
+// The ranks' values of the tile from this GPU's own memory, added in rank order (the same sum on every rank).  Waits,
+// bounded (about a second), for words that have not arrived; *ok turns false if one never does.
+__device__ __forceinline__ float tp_sum_tile(const MvParams &p, unsigned seq, int row0, int nrows, int lane, bool *ok)
+{
+    const int g = row0 + lane;
+    float a = 0.f;
+    bool got = true;
+    if (lane < 16 && g < nrows) {
+        const unsigned long long *v = p.tp.mine_ll + (size_t)(seq & 1u) * p.tp.buf_stride + g;
+        for (int r = 0; r < p.tp.size && got; r++) {
+            unsigned long long word, t0 = 0;
+            for (unsigned it = 0;; it++) {
+                asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(v + (size_t)r * p.tp.rank_stride) : "memory");
+                if ((unsigned)(word >> 32) == seq) break;
+                if ((it & 255) == 255) {
+                    const unsigned long long t = global_ns();
+                    if (!t0) t0 = t;
+                    if (t - t0 > 1000000000ull) { got = false; break; }
+                }
+            }
+            a += __uint_as_float((unsigned)word);
+        }
+    }
+    if (!__all_sync(0xffffffffu, got)) *ok = false;
+    return a;
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const __grid_constant__ MvParams p)
 {
@@ -186,6 +226,7 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         // before our predecessor complete, so it may read state those kernels wrote.
         pdl_launch_dependents();
     }
+    const unsigned tp_seq = p.tp_reduce ? ld_volatile_u32(p.tp.seq) : 0u;   // the launch before has completed: its exchange is over
     __syncthreads();               // abort_flag initialised; also keeps the CTA together for the prologue
     build_activation<FMT>(p, sh, smem, tid, kThreads, blk0, nb, wgt_first, [&](float dep) {
         // the rest of the ring's first round; the test on `dep` only ties the requests to the arrival of the loads
@@ -280,6 +321,19 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
         uo0 = 0;
         cursor_next(p, cur);
     }
+    const bool tpr = p.tp_reduce != 0;
+    int tp_finished = 0;                               // tiles this warp has completed over the ranks
+    bool tp_ok = true;
+    // what a finished tile's 16 sums (lane e < 16: row e) turn into
+    auto finish_rows = [&](const ItemRef &fr, float y) {
+        if (p.finish == FIN_PLAIN) {
+            const int g = fr.row0 + lane;
+            if (lane < 16 && g < p.n_rows[fr.wi]) p.out[fr.wi][g] = y;
+        } else {
+            const float res = (p.finish == FIN_RESID && lane < 16 && fr.row0 + lane < p.n_rows[0]) ? __ldcg(p.resid + fr.row0 + lane) : 0.f;
+            finish_tile_fused(p, fr, lane < 16 ? y : 0.f, res, lane);
+        }
+    };
     if (local) {
         // The pieces of every tile of this CTA are in shared memory.  Tile t (CTA-local) is finished by
         // warp t % kWarps: it adds the pieces in the order of the warps that produced them - a fixed
@@ -300,15 +354,27 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
                 cf.slice = 0;
                 cf.tile = ci0 + tl;
                 const ItemRef fr = item_ref(p, cf);
-                if (p.finish == FIN_PLAIN) {
+                if (tpr) {
+                    tp_push_tile(p, tp_seq, fr.row0, p.n_rows[0], acc0, lane);
+                } else if (p.finish == FIN_PLAIN) {
                     float *out = p.out[fr.wi];
                     const int nrows = p.n_rows[fr.wi];
                     const int g = fr.row0 + (lane & 15);
                     if (lane < 16 * p.m && g < nrows) out[(size_t)(lane >> 4) * nrows + g] = acc0;
                     if (lane + 32 < 16 * p.m && g < nrows) out[(size_t)((lane >> 4) + 2) * nrows + g] = acc1;
                 } else {
-                    const float res = (p.finish == FIN_RESID && lane < 16 && fr.row0 + lane < p.n_rows[0]) ? __ldcg(p.resid + fr.row0 + lane) : 0.f;
-                    finish_tile_fused(p, fr, lane < 16 ? acc0 : 0.f, res, lane);
+                    finish_rows(fr, acc0);
+                }
+            }
+            if (tpr) {
+                // the warp's tiles are on their way to every rank; now the other ranks' shares of them
+                for (int tl = warp; tl < nci; tl += kWarps) {
+                    ItemCursor cf;
+                    cf.slice = 0;
+                    cf.tile = ci0 + tl;
+                    const ItemRef fr = item_ref(p, cf);
+                    finish_rows(fr, tp_sum_tile(p, tp_seq, fr.row0, p.n_rows[0], lane, &tp_ok));
+                    tp_finished++;
                 }
             }
         }
@@ -337,26 +403,44 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
                 const int nrows = p.n_rows[fr.wi];
                 const float *src = p.part + (size_t)fr.tile * (16 * p.m);
                 const size_t sstride = (size_t)p.tiles * (16 * p.m);
-                if (p.finish == FIN_PLAIN) {
+                if (p.finish == FIN_PLAIN && !tpr) {
                     for (int e = lane; e < 16 * p.m; e += 32) {
                         float a = __ldcg(src + e);
                         for (int s = 1; s < p.kb; s++) a += __ldcg(src + s * sstride + e);
                         const int mi = e >> 4, g = fr.row0 + (e & 15);
                         if (g < nrows) out[(size_t)mi * nrows + g] = a;
                     }
-                } else {   // m == 1: all slices (and the residual) are requested at once, then added in slice order
+                } else {   // m == 1: all slices are requested at once, then added in slice order
                     float sl[kMaxSlices];
-                    float res = 0.f;
-                    if (p.finish == FIN_RESID && lane < 16 && fr.row0 + lane < nrows) res = __ldcg(p.resid + fr.row0 + lane);
 #pragma unroll
                     for (int s = 0; s < kMaxSlices; s++) sl[s] = (lane < 16 && s < p.kb) ? __ldcg(src + s * sstride + lane) : 0.f;
                     float a = sl[0];
 #pragma unroll
                     for (int s = 1; s < kMaxSlices; s++) a += sl[s];
-                    finish_tile_fused(p, fr, a, res, lane);
+                    if (tpr) tp_push_tile(p, tp_seq, fr.row0, nrows, a, lane);
+                    else finish_rows(fr, a);
                 }
                 if (lane == 0) p.tile_cnt[fr.tile] = 0;
             }
+            if (tpr && lasts) {
+                for (unsigned rest = lasts; rest; rest &= rest - 1) {
+                    ItemCursor cf;
+                    cf.slice = 0;
+                    cf.tile = __shfl_sync(0xffffffffu, cj.tile, __ffs(rest) - 1);
+                    const ItemRef fr = item_ref(p, cf);
+                    finish_rows(fr, tp_sum_tile(p, tp_seq, fr.row0, p.n_rows[0], lane, &tp_ok));
+                    tp_finished++;
+                }
+            }
+        }
+    }
+    if (tpr && tp_finished && lane == 0) {
+        // the warp that completes the launch's last tile moves on to the next sequence number (every warp read this one
+        // when it started)
+        if (!tp_ok) atomicExch(p.err, 32);
+        if (atomicAdd(p.tp.done, tp_finished) + tp_finished == p.tiles) {
+            *p.tp.done = 0;
+            *p.tp.seq = tp_seq + 1;
         }
     }
     if (!ok && lane == 0) {
@@ -566,6 +650,12 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     }
     p.prologue = job.prologue;
     p.x = job.x; p.x2 = job.x2; p.norm_w = job.norm_w; p.eps = job.eps; p.x_out = job.x_out;
+    p.tp_reduce = job.tp_reduce ? 1 : 0;
+    if (job.tp_reduce) {
+        if (job.m != 1 || job.n_w != 1 || job.finish == FIN_SILU) return fail(TLB_ERR_ARG, "the in-launch sum over tensor-parallel ranks takes one tensor, one activation row, plain or residual finishing");
+        if (!tp_fuse_args(&p.tp)) return fail(TLB_ERR_ARG, "the in-launch sum over tensor-parallel ranks needs attached peer memory");
+        if (job.n_rows[0] > p.tp.rank_stride) return fail(TLB_ERR_SHAPE, "vector too long for the tensor-parallel slots");
+    }
     p.emb_table = job.emb_table; p.token = job.token;
     p.ssq_parts = job.ssq_parts; p.n_parts = job.n_parts;
     p.att_part = job.att_part; p.att_pos = job.att_pos;

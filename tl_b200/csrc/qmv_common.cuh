@@ -40,14 +40,17 @@ __device__ __forceinline__ unsigned long long global_ns()
     return t;
 }
 // Bounded wait: gives up after ~2 s, records the reason and raises the CTA-wide abort flag.
+// The clock is first read after 64 failed polls: a wait that ends sooner (nearly all of them) never pays for it.
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err, int code)
 {
-    unsigned long long t0 = global_ns();
+    unsigned long long t0 = 0;
     for (int it = 0;; it++) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63) == 63) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > 2000000000ull) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 2000000000ull) {
                 *abort_flag = 1;
                 atomicExch(err, code);
                 return false;
@@ -62,10 +65,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 __device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity)
 {
-    unsigned long long t0 = global_ns();
+    unsigned long long t0 = 0;
     for (int it = 0;; it++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63) == 63 && global_ns() - t0 > 1000000000ull) return false;
+        if ((it & 63) == 63) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 1000000000ull) return false;
+        }
     }
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
@@ -194,6 +201,8 @@ struct MvParams {
     const int *token;
     int *err;
     int use_pdl;
+    int tp_reduce;            // the tile results are partial sums over tensor-parallel ranks: summed inside the launch (TpFuse)
+    TpFuse tp;
     // shared-memory offsets (bytes from the start of dynamic shared memory)
     int off_xq, off_alam, off_xsum, off_sa, off_minv, off_bars, off_misc;
     int col_stride;           // bytes between int8 activation columns (nb_max * 256 + 64)
@@ -205,6 +214,23 @@ struct MvShared {
     float red_max[32];
     int abort_flag;
 };
+
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned *p)
+{
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_u32(unsigned *p, unsigned v)
+{
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned *p)
+{
+    unsigned v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 __device__ __forceinline__ float silu_f(float g) { return g * (1.0f / (1.0f + expf(-g))); }
 

@@ -159,6 +159,26 @@ tlb_status launch_interleave8(int type, const uint8_t *a, const uint8_t *b, uint
 // How the activation vector of a streaming matvec is produced inside the kernel.
 enum Prologue { PRO_PLAIN = 0, PRO_ADD_NORM = 1, PRO_SILU_MUL = 2, PRO_ATTN_MERGE = 3 };
 enum Finish { FIN_PLAIN = 0, FIN_RESID = 1, FIN_SILU = 2 };
+
+// Tensor-parallel partial sums added inside the matvec launch that produces them (tp.cu owns the memory).  The warp
+// that finishes a tile (16 output rows) stores its 16 partial sums into slot [buffer][own rank] of EVERY rank's region
+// (peer stores over NVLink, own memory included), each as one 8-byte word {value, sequence number}.  It then reads the
+// tile's words of all ranks from its OWN region, waiting (bounded) for those that do not carry the current sequence
+// number yet - all ranks run the same schedule, so a tile's partial sums arrive from everywhere at about the same time
+// - and adds the values in rank order, so every rank forms the same sum.  An aligned 8-byte store is indivisible: a
+// word with the right number has its value, and neither a fence nor a separate flag is involved.  The exchange of
+// early tiles overlaps the streaming of later ones.  The warp that finishes the launch's last tile advances the
+// sequence number; buffers alternate with it (a rank can be one exchange ahead of a peer, never two).
+constexpr int kTpMaxRanks = 8;
+struct TpFuse {
+    unsigned long long *peer_ll[kTpMaxRanks];   // rank p's words[0][own rank]
+    const unsigned long long *mine_ll;          // own words[0][0]
+    unsigned *seq;                              // device: sequence number of the exchange in progress
+    int *done;                                  // device: tiles of the running launch finished so far
+    int size, buf_stride, rank_stride;          // strides in words
+};
+bool tp_allreduce_is_kernel(int64_t n);   // tp_allreduce of n floats runs this library's peer-memory kernel (not NCCL)
+bool tp_fuse_args(TpFuse *out);           // false: no peer memory attached (or switched off): use tp_allreduce
 constexpr int kMaxSlices = 16;   // most K-slices a matvec may cut its launch into
 struct MatvecJob {
     // up to 3 weight tensors sharing K and the same activation (q|k|v, gate|up)
@@ -199,6 +219,7 @@ struct MatvecJob {
     //   FIN_SILU   rows 0..7 of a tile are gate, rows 8..15 up of the same 8 units (launch_interleave8):
     //              out[8 * tile + i] = silu(y[i]) * y[8 + i]
     int finish = 0;
+    bool tp_reduce = false;          // y is this rank's partial sum: added over the tensor-parallel ranks inside the launch (FIN_PLAIN / FIN_RESID)
     const float *resid = nullptr;
     float *ssq_out = nullptr;
     bool dry_run = false;            // validate and plan only: tells whether the launch would be accepted

@@ -49,11 +49,13 @@ NcclApi g_nccl;
 constexpr int kMaxTp = 8;
 constexpr size_t kP2pMaxFloats = 64 * 1024;   // per rank and buffer: 16 activation rows of a 70B-shaped model (8192 wide), with room
 
+constexpr int kP2pMaxWords = 16 * 1024;       // longest vector (d_model) the matvec launches add over the ranks themselves
 constexpr int kP2pCtas = 16;                  // most CTAs of one all-reduce; every CTA has flags of its own
 
 struct P2pRegion {                 // what a rank allocates for its peers to write into (cudaMalloc, exported over IPC)
     float slots[2][kMaxTp][kP2pMaxFloats];   // [buffer][writer rank][element]
     unsigned flags[kMaxTp][kP2pCtas][8];     // flags[r][c][0]: sequence number of the last all-reduce whose CTA c of rank r wrote here (32-byte apart)
+    unsigned long long words[2][kMaxTp][kP2pMaxWords];   // in-launch exchange: [buffer][writer rank][row] = {value, sequence number}
 };
 
 struct TpState {
@@ -63,6 +65,7 @@ struct TpState {
     P2pRegion *mine = nullptr;
     P2pRegion *peer[kMaxTp] = {nullptr};
     bool p2p = false;
+    bool fuse = true;               // with p2p: decode sessions exchange partial sums inside their matvec launches
     unsigned *seq = nullptr;        // device: sequence number of the next all-reduce (advanced by the kernel)
     int *arrive = nullptr;          // device: CTAs of the running all-reduce that have stored their share
     double join_timeout_s = 60.0;
@@ -155,6 +158,9 @@ struct P2pArgs {
 __global__ void __launch_bounds__(256) p2p_allreduce_kernel(float *x, int n, const P2pArgs a)
 {
     __shared__ int s_ok;
+    // launched as a programmatic dependent: x (and seq) are valid once the launch before has completed
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const unsigned seq = *a.seq;
     const int buf = seq & 1;
     const int n4 = n >> 2, per = (n4 + gridDim.x - 1) / gridDim.x;
@@ -207,6 +213,25 @@ __global__ void __launch_bounds__(256) p2p_allreduce_kernel(float *x, int n, con
 
 }  // namespace
 
+bool tp_allreduce_is_kernel(int64_t n)
+{
+    return g_tp.size > 1 && g_tp.p2p && n % 4 == 0 && (size_t)n <= kP2pMaxFloats;
+}
+
+bool tp_fuse_args(TpFuse *out)
+{
+    static_assert(kTpMaxRanks == kMaxTp, "rank limits differ");
+    if (!g_tp.p2p || !g_tp.fuse || g_tp.size <= 1) return false;
+    for (int p = 0; p < kMaxTp; p++) out->peer_ll[p] = p < g_tp.size ? &g_tp.peer[p]->words[0][g_tp.rank][0] : nullptr;
+    out->mine_ll = &g_tp.mine->words[0][0][0];
+    out->seq = g_tp.seq;
+    out->done = g_tp.arrive + 1;
+    out->size = g_tp.size;
+    out->buf_stride = kMaxTp * kP2pMaxWords;
+    out->rank_stride = kP2pMaxWords;
+    return true;
+}
+
 int tp_rank() { return g_tp.rank; }
 int tp_size() { return g_tp.size; }
 
@@ -220,8 +245,16 @@ tlb_status tp_allreduce(float *x, int64_t n)
         for (int p = 0; p < kMaxTp; p++) a.peer[p] = g_tp.peer[p];
         a.mine = g_tp.mine; a.seq = g_tp.seq; a.arrive = g_tp.arrive; a.err = c->err_flag; a.rank = g_tp.rank; a.size = g_tp.size;
         const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(kP2pCtas, (n / 4 + 511) / 512));
-        p2p_allreduce_kernel<<<grid, 256, 0, c->stream>>>(x, (int)n, a);
-        TLB_CUDA(cudaGetLastError());
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(256);
+        cfg.stream = c->stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        TLB_CUDA(cudaLaunchKernelEx(&cfg, p2p_allreduce_kernel, x, (int)n, a));
         count_launch();
         return TLB_OK;
     }
@@ -387,10 +420,10 @@ tlb_status tlb_tp_p2p_export(void *handle_out, size_t handle_bytes)
         TLB_CUDA(cudaMalloc((void **)&g_tp.mine, sizeof(P2pRegion)));
         TLB_CUDA(cudaMemset(g_tp.mine, 0, sizeof(P2pRegion)));
         TLB_CUDA(cudaMalloc((void **)&g_tp.seq, sizeof(unsigned)));
-        TLB_CUDA(cudaMalloc((void **)&g_tp.arrive, 2 * sizeof(int)));
+        TLB_CUDA(cudaMalloc((void **)&g_tp.arrive, 4 * sizeof(int)));   // [0] all-reduce kernel, [1] tiles finished by an in-launch exchange
         const unsigned one = 1;       // flags start at 0: the first all-reduce waits for 1
         TLB_CUDA(cudaMemcpy(g_tp.seq, &one, sizeof one, cudaMemcpyHostToDevice));
-        TLB_CUDA(cudaMemset(g_tp.arrive, 0, 2 * sizeof(int)));
+        TLB_CUDA(cudaMemset(g_tp.arrive, 0, 4 * sizeof(int)));
         TLB_CUDA(cudaDeviceSynchronize());
     }
     cudaIpcMemHandle_t h;
@@ -425,6 +458,13 @@ tlb_status tlb_tp_p2p_disable(void)
 {
     std::lock_guard<std::mutex> lk(g_tp_mu);
     g_tp.p2p = false;
+    return TLB_OK;
+}
+
+tlb_status tlb_tp_exchange_in_launch(int on)
+{
+    std::lock_guard<std::mutex> lk(g_tp_mu);
+    g_tp.fuse = on != 0;
     return TLB_OK;
 }
 
