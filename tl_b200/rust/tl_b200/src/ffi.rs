@@ -1,4 +1,4 @@
-//! The C ABI of libtlb200 (include/tlb200.h), declaration for declaration: 126 entry points.
+//! The C ABI of libtlb200 (include/tlb200.h), declaration for declaration: 127 entry points.
 //! Handles are opaque; status codes are the values of RuntimeErrorCode (crates/tl_runtime/src/error.rs:7-18).
 #![allow(non_camel_case_types)]
 use std::ffi::{c_char, c_int, c_void};
@@ -153,6 +153,7 @@ extern "C" {
     pub fn tlb_tp_p2p_attach(handles: *const c_void, n_handles: c_int) -> TlbStatus;
     pub fn tlb_tp_p2p_disable() -> TlbStatus;
     pub fn tlb_tp_p2p_enable() -> TlbStatus;
+    pub fn tlb_tp_exchange_in_launch(on: c_int) -> TlbStatus;
     pub fn tlb_tp_split_kind(name: *const c_char) -> c_int;
     pub fn tlb_tp_shard_bytes(kind: c_int, type_: c_int, n: i64, k: i64, bytes: *const c_void, nbytes: usize, rank: c_int, size: c_int, out: *mut c_void, out_cap: usize, n_out: *mut i64, k_out: *mut i64, out_bytes: *mut usize) -> TlbStatus;
     pub fn tlb_map_add_tp(m: *mut TlbMap, name: *const c_char, type_: c_int, shape: *const i64, rank: c_int, bytes: *const c_void, nbytes: usize, tp_rank: c_int, tp_size: c_int) -> TlbStatus;
