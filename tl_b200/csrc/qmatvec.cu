@@ -378,6 +378,59 @@ __global__ void __launch_bounds__(kThreads, kResidentPerSm) qmatvec_kernel(const
                 }
             }
         }
+    } else if (ok && wu1 > wu0 && p.fold_poll) {
+        // One activation row.  The slice scratch rests at kFoldEmpty between launches, so a value that is not kFoldEmpty is
+        // a slice that has arrived: the warp that owns slice 0 of a tile reads the tile's slices (all requested at once,
+        // re-read while some are missing; bounded), adds them in slice order, puts kFoldEmpty back and writes the rows.
+        // No fence, counter or atomic: a 4-byte store is indivisible, and the next launch starts after this one is over.
+        const int i0 = ci0 + it0, i1 = ci0 + wu1 / p.upi;
+        const size_t sstride = (size_t)p.tiles * 16;
+        for (int item = i0; item < i1 && item < p.tiles; item++) {     // items below `tiles` are slice 0
+            ItemCursor cf;
+            cf.slice = 0;
+            cf.tile = item;
+            const ItemRef fr = item_ref(p, cf);
+            float *src = p.part + (size_t)fr.tile * 16 + (lane & 15);
+            unsigned sl[kMaxSlices];
+            bool got = true;
+            if (lane < 16) {
+#pragma unroll
+                for (int s = 0; s < kMaxSlices; s++) sl[s] = s < p.kb ? ld_volatile_u32(reinterpret_cast<const unsigned *>(src + s * sstride)) : 0u;
+                unsigned long long t0 = 0;
+                for (unsigned it = 0;; it++) {
+                    bool all = true;
+#pragma unroll
+                    for (int s = 0; s < kMaxSlices; s++)
+                        if (s < p.kb && sl[s] == kFoldEmpty) {
+                            sl[s] = ld_volatile_u32(reinterpret_cast<const unsigned *>(src + s * sstride));
+                            all = all && sl[s] != kFoldEmpty;
+                        }
+                    if (all) break;
+                    if ((it & 255) == 255) {
+                        const unsigned long long t = global_ns();
+                        if (!t0) t0 = t;
+                        if (t - t0 > 1000000000ull) { got = false; break; }
+                    }
+                }
+            }
+            if (!__all_sync(0xffffffffu, got)) { if (lane == 0) atomicExch(p.err, 3); break; }
+            float a = 0.f;
+            if (lane < 16) {
+                a = __uint_as_float(sl[0]);
+#pragma unroll
+                for (int s = 1; s < kMaxSlices; s++) a += s < p.kb ? __uint_as_float(sl[s]) : 0.f;
+#pragma unroll
+                for (int s = 0; s < kMaxSlices; s++)
+                    if (s < p.kb) reinterpret_cast<unsigned *>(src + s * sstride)[0] = kFoldEmpty;
+            }
+            if (tpr) {
+                tp_push_tile(p, tp_seq, fr.row0, p.n_rows[0], a, lane);
+                finish_rows(fr, tp_sum_tile(p, tp_seq, fr.row0, p.n_rows[0], lane, &tp_ok));
+                tp_finished++;
+            } else {
+                finish_rows(fr, a);
+            }
+        }
     } else if (ok && wu1 > wu0) {
         // All partial results of this warp are out.  One fence, then one count per item (lane j counts
         // item j); the warp that completes a tile's last K-slice adds the slices in index order and
@@ -601,7 +654,8 @@ tlb_status launch_qmatvec(const MatvecJob &job)
     p.kb = job.slices > 0 ? std::min(job.slices, max_slices) : qmatvec_plan_slices(job.type, job.k, job.m, tiles, max_slices);
     if (p.kb < 1 || p.upt % p.kb) return fail(TLB_ERR_ARG, "%d slices do not divide the %d units of K", p.kb, p.upt);
     p.upi = p.upt / p.kb;
-    p.part = c->mv_part;
+    p.fold_poll = (job.m == 1 && (size_t)p.kb * tiles * 16 <= c->mv_part1_floats) ? 1 : 0;
+    p.part = p.fold_poll ? c->mv_part1 : c->mv_part;
     p.tile_cnt = c->mv_cnt;
     p.tiles = (int)tiles;
     p.n_items = (int)(tiles * p.kb);

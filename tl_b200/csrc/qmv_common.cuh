@@ -160,7 +160,9 @@ struct MvParams {
     const uint8_t *w[3];
     float *out[3];            // [m][n_rows] per tensor
     float *part;              // slice scratch [kb][tiles][m][16] (kb > 1): the partial result of every item
-    int *tile_cnt;            // [tiles] slices of a tile finished so far; zero between launches
+    int *tile_cnt;            // [tiles] slices of a tile finished so far; zero between launches (m > 1)
+    int fold_poll;            // m == 1: `part` rests at kFoldEmpty between launches; the warp that owns slice 0 of a tile
+                              // waits for the other slices' values to replace it, adds them and puts it back
     int tiles_end[3];         // cumulative tile counts
     int n_rows[3];            // valid output rows per tensor
     int n_w;
@@ -207,6 +209,8 @@ struct MvParams {
     int off_xq, off_alam, off_xsum, off_sa, off_minv, off_bars, off_misc;
     int col_stride;           // bytes between int8 activation columns (nb_max * 256 + 64)
 };
+
+constexpr unsigned kFoldEmpty = 0xFFFFFFFFu;   // a NaN bit pattern no sum produces
 
 // Scratch of the prologue.
 struct MvShared {

@@ -58,6 +58,9 @@ static tlb_status do_init(int device)
     TLB_CUDA(cudaMemset(g_ctx.err_flag, 0, sizeof(int)));
     g_ctx.mv_part_floats = (size_t)12 << 20;   // 48 MB: 16 slices of a 128k-row head with 3 activation rows
     TLB_CUDA(cudaMalloc(&g_ctx.mv_part, g_ctx.mv_part_floats * sizeof(float)));
+    g_ctx.mv_part1_floats = (size_t)4 << 20;  // 16 MB: 16 slices of a 128k-row head with one activation row, twice over
+    TLB_CUDA(cudaMalloc(&g_ctx.mv_part1, g_ctx.mv_part1_floats * sizeof(float)));
+    TLB_CUDA(cudaMemset(g_ctx.mv_part1, 0xFF, g_ctx.mv_part1_floats * sizeof(float)));
     g_ctx.mv_cnt_n = (size_t)1 << 20;
     TLB_CUDA(cudaMalloc(&g_ctx.mv_cnt, g_ctx.mv_cnt_n * sizeof(int)));
     TLB_CUDA(cudaMemset(g_ctx.mv_cnt, 0, g_ctx.mv_cnt_n * sizeof(int)));
@@ -190,6 +193,7 @@ tlb_status tlb_sync(void)
     if (flag) {
         cudaMemset(g_ctx.err_flag, 0, sizeof(int));
         cudaMemset(g_ctx.mv_cnt, 0, g_ctx.mv_cnt_n * sizeof(int));   // an abandoned launch may have left counts behind
+        cudaMemset(g_ctx.mv_part1, 0xFF, g_ctx.mv_part1_floats * sizeof(float));   // ... or slices nobody collected
         return fail(TLB_ERR_DEVICE, "a kernel gave up a bounded wait (code %d)", flag);
     }
     return TLB_OK;

@@ -35,6 +35,8 @@ struct Context {
     // partial results per K-slice, and per-tile counts of finished slices (zero between launches)
     float *mv_part = nullptr;
     size_t mv_part_floats = 0;
+    float *mv_part1 = nullptr;       // one activation row: slice scratch that rests at a sentinel bit pattern between launches
+    size_t mv_part1_floats = 0;
     int *mv_cnt = nullptr;
     size_t mv_cnt_n = 0;
     bool capturing = false;
