@@ -65,7 +65,8 @@ struct GemmParams {
     int64_t upt;            // units per 16-row tile (K / 256)
     int m;                  // activation rows
     int nt;                 // activation rows per CTA (MMA N)
-    int nb;                 // depth of the activation ring
+    int nb;                 // depth of the activation ring (stages)
+    int gs;                 // 64-wide K groups per stage: 1, or 4 (a whole 256-wide unit per barrier round) for tiles of up to 64 rows
     int kt_total;           // K / 64
     int unit_bytes;
     const float *inv_scale; // [m]
@@ -347,9 +348,11 @@ __device__ __forceinline__ void l2_prefetch(const void *ptr, uint32_t bytes)
 }
 
 // ---- one dequantising warp: 64-groups 2 HALF and 2 HALF + 1 of every unit of its 16 rows.  `dst`: tensor-memory address
-// (the warp's 16 lanes, first column) of weight stage 0.  Barrier slot of K step kt: kt % slots; weight stage: kt % 8.
+// (the warp's 16 lanes, first column) of weight stage 0.  A stage holds gs 64-wide groups (gs = 1: K step = group, the
+// warp fills every other pair of K steps; gs = 4: K step = unit, both warps of a row tile fill the same stage).
+// Barrier slot of K step kt: kt % slots; weight stage: kt % na.
 template <int FMT, int HALF>
-__device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, bool have, int lane, uint32_t dst, int slots,
+__device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, bool have, int lane, uint32_t dst, int slots, int na,
                                         uint32_t full0, uint32_t empty0, volatile int *abort_flag, int u0, int units)
 {
     typename UnitRegs<FMT>::type cur, nxt;
@@ -357,6 +360,7 @@ __device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, 
     // Registers hold one unit ahead; one lane of the pair's first warp asks L2 for the units kAhead further on, so
     // that the register loads find them there.
     constexpr int kAhead = 4;
+    const bool wide = p.gs == 4;
     const bool fetcher = have && HALF == 0 && lane == 0;
     if (fetcher)
         for (int j = 1; j <= kAhead && j < units; j++) l2_prefetch(ub + (size_t)j * p.unit_bytes, (uint32_t)p.unit_bytes);
@@ -370,20 +374,22 @@ __device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, 
 #pragma unroll
         for (int gg = 0; gg < 2; gg++) {
             const int g = HALF * 2 + gg;
-            const int kt = u * 4 + g;
-            if (kt >= kGemmAStages) {   // the stage was last read by the MMAs of K step kt - 8
-                const int back = kt - kGemmAStages;
+            const int kt = wide ? u : u * 4 + g;                 // the K step this group belongs to
+            if ((!wide || gg == 0) && kt >= na) {                  // its stage was last read by the MMAs of K step kt - na
+                const int back = kt - na;
                 if (!mbar_wait(empty0 + 8u * (uint32_t)(back % slots), (uint32_t)(back / slots) & 1u, abort_flag, p.err, 21)) return false;
                 tc_fence_after();
             }
             if (have) {
                 AFrag f;
                 unit_emit(cur, g, f);
-                f.flush(dst + (uint32_t)((kt % kGemmAStages) * kStageACols));
+                f.flush(dst + (uint32_t)((kt % na) * (kStageACols * p.gs) + (wide ? g * kStageACols : 0)));
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full0 + 8u * (uint32_t)(kt % slots));
+            if (!wide || gg == 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8u * (uint32_t)(kt % slots));
+            }
         }
     }
     return true;
@@ -401,8 +407,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t sB = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
-    const int nb = p.nb, slots = max(kGemmAStages, nb);
-    const uint32_t stage_b = (uint32_t)p.nt * 128u;                // bytes of one activation stage (multiple of 2048)
+    // gs = 4 (token tiles of up to 64 rows): a stage is a whole 256-wide unit - four TMA boxes, sixteen MMAs, one barrier
+    // round - because with so little tensor work per group the round itself (arrive, wait, commit, wait) sets the pace.
+    // The accumulator then takes columns [0, 64) and three weight stages of 128 columns follow from column 128.
+    const int gs = p.gs, na = gs == 4 ? 3 : kGemmAStages;
+    const uint32_t tmem_a0 = gs == 4 ? 128u : (uint32_t)kTmemA0;
+    const int nb = p.nb, slots = max(na, nb);
+    const uint32_t group_b = (uint32_t)p.nt * 128u;                // bytes of one 64-wide activation box (multiple of 2048)
+    const uint32_t stage_b = group_b * (uint32_t)gs;
     const uint32_t bars = sB + (uint32_t)nb * stage_b;
     // Slot kt % slots serves K step kt.  full: eight producer warps + the TMA thread's expect_tx; empty: the commit
     // after the step's MMAs.  A waiter for K step kt - d (d = 8 for the weight stage, nb for the activation stage) asks
@@ -413,14 +425,10 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     const uint32_t accum_bar = bars + 8u * (2 * kGemmMaxSlots);
 
     const int tok0 = blockIdx.y * p.nt;
-    // Consecutive MMAs into one accumulator wait for each other (a narrow tile's MMA is over long before its result is
-    // back in tensor memory), so tiles of up to 64 activation rows give each of a K step's four 16-wide chunks an
-    // accumulator of its own (columns 0, 64, 128, 192), tiles of up to 128 rows two; the epilogue adds them.
-    const int nacc = p.nt <= 64 ? 4 : p.nt <= 128 ? 2 : 1, acc_stride = 256 / nacc;
     // K range of this CTA: whole units (4 K steps each), split evenly over grid.z
     const int units_all = (int)p.upt, split = blockIdx.z;
     const int u0 = units_all * split / p.splits, u1 = units_all * (split + 1) / p.splits;
-    const int KT = (u1 - u0) * 4, kt_base = u0 * 4;
+    const int KT = (u1 - u0) * (4 / gs), kt_base = u0 * 4;       // K steps of this CTA; first 64-wide group
     int wi = 0;
     while (wi + 1 < p.n_w && (int)blockIdx.x >= p.rt_end[wi]) wi++;
     const int rt = (int)blockIdx.x - (wi ? p.rt_end[wi - 1] : 0);   // 128-row tile inside weight wi
@@ -429,7 +437,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     if (tid == 0) {
         abort_word = 0;
         for (int i = 0; i < slots; i++) {
-            mbar_init(full_bar(i), 9);
+            mbar_init(full_bar(i), gs == 4 ? 17 : 9);    // the producer warps of a stage + the TMA thread's expect_tx
             mbar_init(empty_bar(i), 1);
         }
         mbar_init(accum_bar, 1);
@@ -453,9 +461,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
         const int tile16 = rt * 8 + sub;
         const bool have = tile16 < p.n_tiles16[wi];
         const uint8_t *ub = p.w[wi] + (size_t)(have ? tile16 : 0) * p.upt * p.unit_bytes;
-        const uint32_t dst = tmem + ((uint32_t)(sub * 16) << 16) + (uint32_t)kTmemA0;
-        const bool ok = warp < 8 ? produce<FMT, 0>(p, ub, have, lane, dst, slots, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0)
-                                 : produce<FMT, 1>(p, ub, have, lane, dst, slots, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0);
+        const uint32_t dst = tmem + ((uint32_t)(sub * 16) << 16) + tmem_a0;
+        const bool ok = warp < 8 ? produce<FMT, 0>(p, ub, have, lane, dst, slots, na, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0)
+                                 : produce<FMT, 1>(p, ub, have, lane, dst, slots, na, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0);
         // ------------------------------------------------ epilogue: tensor memory -> Y[token][row]
         if (ok && mbar_wait(accum_bar, 0, abort_flag, p.err, 22)) {
             tc_fence_after();
@@ -478,20 +486,12 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
                 }
                 uint32_t v[8];
                 tmem_ld8(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
-                float acc[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) acc[j] = __uint_as_float(v[j]);
-                for (int a = 1; a < nacc; a++) {     // narrow tiles: the K chunks of a step went to accumulators of their own
-                    tmem_ld8(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(a * acc_stride + c0), v);
-#pragma unroll
-                    for (int j = 0; j < 8; j++) acc[j] += __uint_as_float(v[j]);
-                }
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const int tok = tok0 + c0 + j;
                     if (tok < p.m && row < n_rows) {
-                        if (partial) pout[(size_t)tok * p.n_all + row] = acc[j] * sc[j];
-                        else out[(size_t)tok * n_rows + row] = rs[j] + acc[j] * sc[j];
+                        if (partial) pout[(size_t)tok * p.n_all + row] = __uint_as_float(v[j]) * sc[j];
+                        else out[(size_t)tok * n_rows + row] = rs[j] + __uint_as_float(v[j]) * sc[j];
                     }
                 }
             }
@@ -507,7 +507,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
                     if (++bslot == slots) { bslot = 0; bround++; }
                 }
                 mbar_expect_tx(full_bar(slot), stage_b);
-                tma_load_2d(sB + (uint32_t)st * stage_b, &xmap, (kt_base + kt) * kGemmBK, tok0, full_bar(slot));
+                for (int j = 0; j < gs; j++)
+                    tma_load_2d(sB + (uint32_t)st * stage_b + (uint32_t)j * group_b, &xmap, (kt_base + kt * gs + j) * kGemmBK, tok0, full_bar(slot));
                 issued = kt + 1;
                 if (++st == nb) st = 0;
                 if (++slot == slots) slot = 0;
@@ -527,11 +528,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
             for (int kt = 0; kt < KT; kt++) {
                 if (!mbar_wait(full_bar(slot), (uint32_t)round & 1u, abort_flag, p.err, 24)) { ok = false; break; }
                 tc_fence_after();
-                const uint64_t bd = smem_desc_sw128(sB + (uint32_t)st * stage_b);
-                const uint32_t ta = tmem + (uint32_t)(kTmemA0 + (kt % kGemmAStages) * kStageACols);
+                for (int j = 0; j < gs; j++) {
+                    const uint64_t bd = smem_desc_sw128(sB + (uint32_t)st * stage_b + (uint32_t)j * group_b);
+                    const uint32_t ta = tmem + tmem_a0 + (uint32_t)((kt % na) * (kStageACols * gs) + j * kStageACols);
 #pragma unroll
-                for (int k16 = 0; k16 < kGemmBK / 16; k16++)   // 16 f16: 8 columns of tensor memory, 32 bytes along the swizzle row
-                    umma_f16_ts(tmem + (uint32_t)((k16 & (nacc - 1)) * acc_stride), ta + 8u * k16, bd + 2u * k16, idesc, kt != 0 || k16 >= nacc);
+                    for (int k16 = 0; k16 < kGemmBK / 16; k16++)   // 16 f16: 8 columns of tensor memory, 32 bytes along the swizzle row
+                        umma_f16_ts(tmem, ta + 8u * k16, bd + 2u * k16, idesc, (kt | j | k16) != 0);
+                }
                 umma_commit(empty_bar(slot));   // arrives when the MMAs above have read both stages
                 if (++st == nb) st = 0;
                 if (++slot == slots) { slot = 0; round++; }
@@ -785,14 +788,15 @@ tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct 
     p.upt = w0->upt;
     p.m = (int)m;
     p.nt = nt;
-    p.nb = std::max(4, std::min(kGemmMaxSlots, kGemmBBytes / (nt * 128)));
+    p.gs = nt <= 64 ? 4 : 1;
+    p.nb = std::max(p.gs == 4 ? 3 : 4, std::min(kGemmMaxSlots, kGemmBBytes / (nt * 128 * p.gs)));
     p.kt_total = (int)(a.k / kGemmBK);
     p.unit_bytes = qformat(w0->type)->unit_bytes;
     p.inv_scale = (const float *)a.inv->ptr;
     p.resid = resid;
     p.err = c->err_flag;
 
-    const size_t smem = (size_t)p.nb * nt * 128 + (kGemmSmemMax - kGemmBBytes);
+    const size_t smem = (size_t)p.nb * nt * 128 * p.gs + (kGemmSmemMax - kGemmBBytes);
     const int64_t tok_tiles = (m + nt - 1) / nt;
     int64_t n_all = 0;
     for (int i = 0; i < kGemmMaxW; i++) { p.col0[i] = (int)n_all; n_all += p.n[i]; }
