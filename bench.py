@@ -342,7 +342,7 @@ def measure_per_op(tl, cfg, wmap, ctx, steps, ev):
     (examples/apps/llama3/chatbot_llama3.tl:66-125,220-236), with a context of `ctx` rows already in the program's cache:
     what an unmodified chatbot gets behind this library.  Host token in, host token out (item_i64), wall clock."""
     from tl_b200.chatbot import PerOpLlama
-    bot = PerOpLlama(cfg, wmap, max_seq=ctx + steps + 8)
+    bot = PerOpLlama(cfg, wmap, max_seq=ctx + 2 * steps + 16)
     rng = np.random.default_rng(99)
     kvd = cfg["n_kv_heads"] * cfg["head_dim"]
     for layer in range(cfg["n_layers"]):
@@ -359,9 +359,21 @@ def measure_per_op(tl, cfg, wmap, ctx, steps, ev):
         pos += 1
     dt = (time.perf_counter() - t0) / steps
     launches = (tl.kernel_launches() - l0) // steps
-    return {"tokens_per_s": round(1.0 / dt, 2), "ms_per_step": round(dt * 1e3, 3), "steps": steps, "kernel_launches_per_step": int(launches),
-            "note": "f32 KV cache grown by cat_4d (the whole cache is copied every step, as the program writes it), GQA expansion "
-                    "materialised, one tlb_* call per TL op; the fused session is the `value` / `e2e` of this line"}
+    # the same calls from native code (tlb_chatbot_step_per_op), as the compiled TL program issues them
+    for _ in range(2):
+        tok = bot.step_native([tok], pos)
+        pos += 1
+    tl.sync()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = bot.step_native([tok], pos)
+        pos += 1
+    dn = (time.perf_counter() - t0) / steps
+    return {"tokens_per_s": round(1.0 / dn, 2), "ms_per_step": round(dn * 1e3, 3), "steps": steps, "kernel_launches_per_step": int(launches),
+            "through_python": {"tokens_per_s": round(1.0 / dt, 2), "ms_per_step": round(dt * 1e3, 3)},
+            "note": "one tlb_* call per TL op in the program's order, issued from native code (the ctypes route, with the "
+                    "interpreter's time per call, beside it); f32 KV cache grown by cat_4d (the whole cache is copied every step, "
+                    "as the program writes it), GQA expansion materialised; the fused session is the `value` / `e2e` of this line"}
 
 
 # ---------------------------------------------------------------- tensor parallelism (config C4)
@@ -500,6 +512,25 @@ def measure_tp(tl, dist, rank, world, ev, steps=32, ctx=4096, with_single=True, 
     return out
 
 
+def measure_c4_single(tl, ev, peaks, ctx=4096, steps=16):
+    """Config C4's model (Llama-3-70B shapes, all 80 layers, Q4_K + Q6_K head, 40 GB) on ONE GPU: batch 1 through the fused
+    matvec chain and batch 16 through the tensor-core GEMM rows; f16 KV with a 4096-row context per sequence."""
+    from tl_b200 import synth
+    cfg = dict(synth.LLAMA3_70B)
+    wmap = build_tp_map(tl, cfg, 0, 1)
+    out = {"workload": "c4 on one GPU: Llama-3-70B-shaped decode, Q4_K + Q6_K head, f16 KV, ctx %d" % ctx}
+    for b in (1, 16):
+        dec = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=ctx + 64, batch=b)
+        ms = time_generate(tl, dec, ev, 1, ctx, 3, steps if b == 1 else 6, batch=b if b > 1 else None)
+        st = dec.stats(ctx)
+        nbytes = st["weight_bytes"] + st["kv_bytes"] * b
+        out["bs%d" % b] = {"ms_per_step": round(ms, 3), "tokens_per_s": round(b * 1e3 / ms, 1), "GBs": round(nbytes / ms / 1e6, 1),
+                           "frac_hbm": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4)}
+        dec.destroy()
+    wmap.free()
+    return out
+
+
 def run_ours(args, dist, rank, world):
     import ctypes as C
     t_start = time.time()
@@ -591,6 +622,8 @@ def run_ours(args, dist, rank, world):
         if world == 1:
             wmap.free()
             extras["sweep"] = measure_sweep(tl, ev, peaks) if big else measure_sweep(tl, ev, peaks, shapes=SWEEP_SHAPES[:2])
+            if big:
+                extras["c4_single_gpu"] = measure_c4_single(tl, ev, peaks)
     cpu, _ = cpu_baseline(cfg, args.cpu_budget)
     line = {"metric": "Q4_K Llama-3-8B decode tok/s @bs1" if args.workload == "c2" else "decode tok/s @bs1",
             "value": round(tok_s, 2), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,

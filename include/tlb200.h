@@ -290,6 +290,15 @@ typedef struct {
  * the reference programs hard-code them, examples/apps/llama3/chatbot_llama3.tl:67-71,95,106,196); kv_f16, max_seq, tie_rule and
  * the tp fields stay as the caller set them. */
 tlb_status tlb_decoder_cfg_from_map(const tlb_map *m, tlb_decoder_cfg *cfg);
+
+/* The TL chatbot's forward pass over `tokens` (f32-encoded ids, as TL holds them) from cache row start_pos, issued op by
+ * op through the per-op entry points above, in the program's order (examples/apps/llama3/chatbot_llama3.tl:48-125,220-236):
+ * the route an unmodified TL program takes, from native code.  cos_t / sin_t: Tensor::rope_new_cos / _sin tables; the
+ * cache grows by concatenation (tlb_kvcache_*).  *next_token: lo.narrow(last).sample(0.0, 0.9).item_i64(); the last row
+ * of the logits when logits_out is not NULL.  Uses cfg's sizes, eps, attn_scale and tie_rule. */
+tlb_status tlb_chatbot_step_per_op(tlb_map *weights, tlb_kvcache *cache, const tlb_tensor *cos_t, const tlb_tensor *sin_t,
+                                   const tlb_decoder_cfg *cfg, const float *tokens, int64_t n_tokens, int64_t start_pos,
+                                   int64_t *next_token, tlb_tensor **logits_out);
 tlb_status tlb_decoder_create(tlb_decoder **out, const tlb_decoder_cfg *cfg, tlb_map *weights);
 tlb_status tlb_decoder_destroy(tlb_decoder *d);
 /* overwrite cached K/V rows [pos0, pos0+n) of one layer from host f32 [n, n_kv_heads*head_dim] */

@@ -47,3 +47,14 @@ def test_per_op_route_matches_oracle_and_fused_session(orc, linear, head):
         tok, pos = nxt, pos + 1
     # the cache the program holds grew by concatenation: [1, KVH, T, D]
     assert bot.cache.get_k(0).shape == (1, SMALL["n_kv_heads"], pos, SMALL["head_dim"])
+    # the same op sequence issued by the library's native driver: the prompt, then steps, bit for bit the same logits
+    nat = PerOpLlama(SMALL, wmap, max_seq=64)
+    py = PerOpLlama(SMALL, wmap, max_seq=64)
+    t_n, t_p = nat.step_native(prompt, 0), py.step(prompt, 0)
+    assert t_n == t_p
+    np.testing.assert_array_equal(nat.last_logits.numpy().view(np.uint32), py.last_logits.numpy().view(np.uint32))
+    for i in range(4):
+        t_n, t_p = nat.step_native([t_n], len(prompt) + i), py.step([t_p], len(prompt) + i)
+        assert t_n == t_p
+        np.testing.assert_array_equal(nat.last_logits.numpy().view(np.uint32), py.last_logits.numpy().view(np.uint32))
+    assert nat.cache.get_k(0).shape == py.cache.get_k(0).shape

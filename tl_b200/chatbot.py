@@ -8,9 +8,12 @@ takes behind TL_DEVICE=cuda: one kernel (or more) per op, a cache that grows by 
 (tl_b200.Decoder) computes the same tokens in 5 launches per layer; this module exists to measure the difference and to
 check that both routes agree.
 """
+import ctypes as C
+
 import numpy as np
 
-from . import KVCache, Tensor, ROPE_CPU, TIE_LAST
+from . import KVCache, Tensor, ROPE_CPU, TIE_LAST, check, lib
+from ._lib import DecoderCfg
 
 
 class PerOpLlama:
@@ -83,6 +86,20 @@ class PerOpLlama:
             mu = y.matmul_quantized(b["g"]).silu().mul(y.matmul_quantized(b["u"]))
             x = h.add(mu.matmul_quantized(b["d"]))
         return self._norm(x, self.on).matmul_quantized(self.oh)
+
+    def step_native(self, tokens, start_pos):
+        """The same step issued by the library's own native driver (tlb_chatbot_step_per_op): the same per-op entry points
+        in the same order, without this interpreter's time per call.  Returns the token id; last_logits as in step()."""
+        c = self.cfg
+        dc = DecoderCfg(n_layers=c["n_layers"], d_model=c["d_model"], n_heads=c["n_heads"], n_kv_heads=c["n_kv_heads"],
+                        head_dim=c["head_dim"], ffn=c["ffn"], vocab=c["vocab"], eps=c["eps"], rope_base=c["rope_base"],
+                        attn_scale=c["attn_scale"], kv_f16=0, max_seq=0, tie_rule=self.tie, tp_size=1, tp_rank=0, batch=1)
+        ids = np.ascontiguousarray(np.asarray(tokens, dtype=np.float32))
+        nxt, lg = C.c_int64(), C.c_void_p()
+        check(lib().tlb_chatbot_step_per_op(self.w.h, self.cache.h, self.cos.h, self.sin.h, C.byref(dc), ids.ctypes.data_as(C.c_void_p),
+                                            len(ids), start_pos, C.byref(nxt), C.byref(lg)))
+        self.last_logits = Tensor(lg)
+        return int(nxt.value)
 
     def step(self, tokens, start_pos):
         """forward + lo.narrow(0, batch_len - 1, 1).sample(...).item_i64(): the token id on the host."""

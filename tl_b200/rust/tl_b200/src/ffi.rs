@@ -1,4 +1,4 @@
-//! The C ABI of libtlb200 (include/tlb200.h), declaration for declaration: 127 entry points.
+//! The C ABI of libtlb200 (include/tlb200.h), declaration for declaration: 128 entry points.
 //! Handles are opaque; status codes are the values of RuntimeErrorCode (crates/tl_runtime/src/error.rs:7-18).
 #![allow(non_camel_case_types)]
 use std::ffi::{c_char, c_int, c_void};
@@ -159,6 +159,7 @@ extern "C" {
     pub fn tlb_map_add_tp(m: *mut TlbMap, name: *const c_char, type_: c_int, shape: *const i64, rank: c_int, bytes: *const c_void, nbytes: usize, tp_rank: c_int, tp_size: c_int) -> TlbStatus;
     pub fn tlb_gguf_load_tp(out: *mut *mut TlbMap, path: *const c_char, tp_rank: c_int, tp_size: c_int) -> TlbStatus;
     pub fn tlb_decoder_cfg_from_map(m: *const TlbMap, cfg: *mut TlbDecoderCfg) -> TlbStatus;
+    pub fn tlb_chatbot_step_per_op(weights: *mut TlbMap, cache: *mut TlbKvCache, cos_t: *const TlbTensor, sin_t: *const TlbTensor, cfg: *const TlbDecoderCfg, tokens: *const f32, n_tokens: i64, start_pos: i64, next_token: *mut i64, logits_out: *mut *mut TlbTensor) -> TlbStatus;
     pub fn tlb_decoder_create(out: *mut *mut TlbDecoder, cfg: *const TlbDecoderCfg, weights: *mut TlbMap) -> TlbStatus;
     pub fn tlb_decoder_destroy(d: *mut TlbDecoder) -> TlbStatus;
     pub fn tlb_decoder_kv_write(d: *mut TlbDecoder, layer: c_int, pos0: c_int, n: c_int, k: *const f32, v: *const f32) -> TlbStatus;
