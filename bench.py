@@ -672,6 +672,7 @@ PARTS = {
     "c3": "batched prompt processing of config C3 (8 x 2048 tokens, Llama-3-8B shapes)",
     "qgemm": "one Q4_K 4096 x 4096 weight with 1184 activation rows, three calls (small case for a profiler capture)",
     "c4-4layer": "Llama-3-70B-shaped decode on one GPU, 4 layers + head, 4096-row f16 context: batch 1 (fused matvec chain) and batch 16 (tensor-core GEMM rows)",
+    "per-op-4layer": "the TL chatbot's op sequence through the per-op entry points (native driver), Llama-3-8B shapes cut to 4 layers, 2048 cached rows, 3 steps",
     "prefill-2layer": "one 2048-token prompt through two Llama-3-8B-shaped layers + head, three times (small case for a profiler capture)",
 }
 
@@ -714,6 +715,11 @@ def run_part(args):
         tl.sync()
         ms = _elapsed_ms(tl, ev[0], ev[1])
         line.update({"value": round(2.0 * 1184 * 4096 * 4096 / ms / 1e9, 1), "unit": "TFLOP/s (with the f16 conversion)", "ms": round(ms, 4), "higher_is_better": True})
+    elif name == "per-op-4layer":
+        cfg = dict(synth.LLAMA3_8B, n_layers=4)
+        wmap = tl.map_from_tensors(synth.llama_tensors(cfg, 1, 12, 14))
+        po = measure_per_op(tl, cfg, wmap, 2048, 3, ev)
+        line.update({"value": po["tokens_per_s"], "unit": "tokens/s (4 layers + head)", "higher_is_better": True, "per_op": po})
     elif name == "c4-4layer":
         cfg = dict(synth.LLAMA3_70B, n_layers=4)
         wmap = build_tp_map(tl, cfg, 0, 1)

@@ -185,6 +185,71 @@ __global__ void copy_strided_kernel(const float *__restrict__ a, float *__restri
     }
 }
 
+// The same gather when the innermost output dimension is contiguous in the source as well (narrow, cat, repeat_interleave,
+// transposes of outer dimensions): rows of `inner4` float4, the row's source offset from 32-bit index arithmetic.
+struct RowStrides { unsigned o[kMaxRank]; long long a[kMaxRank]; int rank; };   // outer dimensions only
+__global__ void copy_rows4_kernel(const float4 *__restrict__ a, float4 *__restrict__ out, RowStrides s, unsigned rows, unsigned inner4, long long a_off4)
+{
+    const unsigned long long total = (unsigned long long)rows * inner4;
+    for (unsigned long long i = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; i < total; i += (unsigned long long)gridDim.x * blockDim.x) {
+        const unsigned row = (unsigned)(i / inner4), col = (unsigned)(i - (unsigned long long)row * inner4);
+        unsigned rem = row;
+        long long ia = a_off4;
+        for (int d = s.rank - 1; d >= 0; d--) {
+            const unsigned c = rem % s.o[d];
+            rem /= s.o[d];
+            ia += (long long)c * s.a[d];
+        }
+        out[i] = a[ia + col];
+    }
+}
+
+// out[b][j][i] = a[b][i][j]: the last two dimensions exchanged, through a 32 x 33 shared-memory tile so that both the
+// reads and the writes are coalesced.
+__global__ void __launch_bounds__(256) transpose_last2_kernel(const float *__restrict__ a, float *__restrict__ out, int rows, int cols)
+{
+    __shared__ float tile[32][33];
+    const float *src = a + (size_t)blockIdx.z * rows * cols;
+    float *dst = out + (size_t)blockIdx.z * rows * cols;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;       // 32 x 8
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int j = ty; j < 32; j += 8)
+        if (r0 + j < rows && c0 + tx < cols) tile[j][tx] = src[(size_t)(r0 + j) * cols + c0 + tx];
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8)
+        if (c0 + j < cols && r0 + tx < rows) dst[(size_t)(c0 + j) * rows + r0 + tx] = tile[tx][j];
+}
+
+// C[b][r][n] = sum_k A[b][r][k] B[b][k][n] for up to 4 rows r (the decode step's attention products: one query row per
+// head against the whole cache).  64 columns x 8 slices of k per CTA; the slices are added in index order.
+__global__ void __launch_bounds__(512) matmul_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ C,
+                                                          int m, int k, int n, int b_batched)
+{
+    __shared__ float red[8][4][64];
+    const float *a = A + (size_t)blockIdx.y * m * k;
+    const float *b = B + (b_batched ? (size_t)blockIdx.y * k * n : 0);
+    const int tx = threadIdx.x & 63, ks = threadIdx.x >> 6, col = blockIdx.x * 64 + tx;
+    const int kc = (k + 7) / 8, k0 = ks * kc, k1 = min(k, k0 + kc);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (col < n) {
+        for (int kk = k0; kk < k1; kk++) {
+            const float bv = b[(size_t)kk * n + col];
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+                if (r < m) acc[r] = fmaf(__ldg(a + (size_t)r * k + kk), bv, acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++) red[ks][r][tx] = acc[r];
+    __syncthreads();
+    if (ks < m && col < n) {       // slice-warps 0 .. m-1 each finish one row
+        float v = red[0][ks][tx];
+#pragma unroll
+        for (int q = 1; q < 8; q++) v += red[q][ks][tx];
+        C[((size_t)blockIdx.y * m + ks) * n + col] = v;
+    }
+}
+
 __global__ void copy_into_kernel(const float *__restrict__ a, float *__restrict__ out, int64_t outer, int64_t a_inner,
                                  int64_t o_inner, int64_t o_off)
 {
@@ -383,6 +448,12 @@ tlb_status launch_softmax(const float *a, float *out, int64_t outer, int64_t axi
 tlb_status launch_matmul(const float *a, const float *b, float *out, int64_t batch, int64_t m, int64_t k, int64_t n, bool b_batched)
 {
     if (batch * m * n == 0) return TLB_OK;
+    if (m <= 4 && k <= INT32_MAX && n <= INT32_MAX && batch <= 65535) {
+        dim3 grid((unsigned)((n + 63) / 64), (unsigned)batch);
+        matmul_rows_kernel<<<grid, 512, 0, ctx()->stream>>>(a, b, out, (int)m, (int)k, (int)n, b_batched ? 1 : 0);
+        LAUNCH_CHECK();
+        return TLB_OK;
+    }
     dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64), (unsigned)batch);
     matmul_kernel<<<grid, 256, 0, ctx()->stream>>>(a, b, out, m, k, n, b_batched ? 1 : 0);
     LAUNCH_CHECK();
@@ -392,6 +463,38 @@ tlb_status launch_matmul(const float *a, const float *b, float *out, int64_t bat
 tlb_status launch_copy_strided(const float *a, float *out, const int64_t *oshape, const int64_t *astr, int rank, int64_t n, int64_t a_off)
 {
     if (n == 0) return TLB_OK;
+    // (1) the last two dimensions exchanged, everything before them in place: tiled transpose
+    if (rank >= 2 && a_off == 0 && astr[rank - 1] == oshape[rank - 2] && astr[rank - 2] == 1 && oshape[rank - 1] <= INT32_MAX && oshape[rank - 2] <= INT32_MAX) {
+        bool outer_plain = true;
+        int64_t want = oshape[rank - 1] * oshape[rank - 2], batch = 1;
+        for (int i = rank - 3; i >= 0; i--) { outer_plain = outer_plain && astr[i] == want; want *= oshape[i]; batch *= oshape[i]; }
+        const int rows = (int)oshape[rank - 1], cols = (int)oshape[rank - 2];   // of the source: [rows][cols] -> [cols][rows]
+        if (outer_plain && batch <= 65535 && (rows + 31) / 32 <= 65535) {
+            dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32), (unsigned)batch);
+            transpose_last2_kernel<<<grid, 256, 0, ctx()->stream>>>(a, out, rows, cols);
+            LAUNCH_CHECK();
+            return TLB_OK;
+        }
+    }
+    // (2) rows that are contiguous on both sides, a multiple of four floats long and 16-byte aligned: float4 copies
+    if (rank >= 1 && astr[rank - 1] == 1 && oshape[rank - 1] % 4 == 0 && a_off % 4 == 0 && (((uintptr_t)a | (uintptr_t)out) & 15) == 0 &&
+        n / oshape[rank - 1] <= UINT32_MAX) {
+        bool ok = true;
+        RowStrides r;
+        r.rank = rank - 1;
+        for (int i = 0; i < rank - 1; i++) {
+            ok = ok && astr[i] % 4 == 0 && oshape[i] <= UINT32_MAX;
+            r.o[i] = (unsigned)oshape[i];
+            r.a[i] = astr[i] / 4;
+        }
+        if (ok) {
+            const unsigned rows = (unsigned)(n / oshape[rank - 1]), inner4 = (unsigned)(oshape[rank - 1] / 4);
+            copy_rows4_kernel<<<grid_for(n / 4, 256), 256, 0, ctx()->stream>>>(reinterpret_cast<const float4 *>(a), reinterpret_cast<float4 *>(out), r, rows,
+                                                                               inner4, a_off / 4);
+            LAUNCH_CHECK();
+            return TLB_OK;
+        }
+    }
     Strides s;
     s.rank = rank;
     for (int i = 0; i < rank; i++) { s.o[i] = oshape[i]; s.a[i] = astr[i]; s.b[i] = 0; }

@@ -351,16 +351,17 @@ __device__ __forceinline__ void l2_prefetch(const void *ptr, uint32_t bytes)
 // (the warp's 16 lanes, first column) of weight stage 0.  A stage holds gs 64-wide groups (gs = 1: K step = group, the
 // warp fills every other pair of K steps; gs = 4: K step = unit, both warps of a row tile fill the same stage).
 // Barrier slot of K step kt: kt % slots; weight stage: kt % na.
-template <int FMT, int HALF>
-__device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, bool have, int lane, uint32_t dst, int slots, int na,
+template <int FMT, int HALF, int GS>
+__device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, bool have, int lane, uint32_t dst, int slots,
                                         uint32_t full0, uint32_t empty0, volatile int *abort_flag, int u0, int units)
 {
+    constexpr int na = GS == 4 ? 3 : kGemmAStages;
     typename UnitRegs<FMT>::type cur, nxt;
     ub += (size_t)u0 * p.unit_bytes;          // this CTA's K range starts at unit u0
     // Registers hold one unit ahead; one lane of the pair's first warp asks L2 for the units kAhead further on, so
     // that the register loads find them there.
     constexpr int kAhead = 4;
-    const bool wide = p.gs == 4;
+    constexpr bool wide = GS == 4;
     const bool fetcher = have && HALF == 0 && lane == 0;
     if (fetcher)
         for (int j = 1; j <= kAhead && j < units; j++) l2_prefetch(ub + (size_t)j * p.unit_bytes, (uint32_t)p.unit_bytes);
@@ -383,7 +384,7 @@ __device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, 
             if (have) {
                 AFrag f;
                 unit_emit(cur, g, f);
-                f.flush(dst + (uint32_t)((kt % na) * (kStageACols * p.gs) + (wide ? g * kStageACols : 0)));
+                f.flush(dst + (uint32_t)((kt % na) * (kStageACols * GS) + (wide ? g * kStageACols : 0)));
             }
             if (!wide || gg == 1) {
                 tc_fence_before();
@@ -396,7 +397,7 @@ __device__ __forceinline__ bool produce(const GemmParams &p, const uint8_t *ub, 
 }
 
 // ---- the kernel
-template <int FMT>
+template <int FMT, int GS>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
 {
@@ -410,8 +411,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
     // gs = 4 (token tiles of up to 64 rows): a stage is a whole 256-wide unit - four TMA boxes, sixteen MMAs, one barrier
     // round - because with so little tensor work per group the round itself (arrive, wait, commit, wait) sets the pace.
     // The accumulator then takes columns [0, 64) and three weight stages of 128 columns follow from column 128.
-    const int gs = p.gs, na = gs == 4 ? 3 : kGemmAStages;
-    const uint32_t tmem_a0 = gs == 4 ? 128u : (uint32_t)kTmemA0;
+    constexpr int gs = GS, na = GS == 4 ? 3 : kGemmAStages;
+    constexpr uint32_t tmem_a0 = GS == 4 ? 128u : (uint32_t)kTmemA0;
     const int nb = p.nb, slots = max(na, nb);
     const uint32_t group_b = (uint32_t)p.nt * 128u;                // bytes of one 64-wide activation box (multiple of 2048)
     const uint32_t stage_b = group_b * (uint32_t)gs;
@@ -462,8 +463,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap xmap, const GemmParams p)
         const bool have = tile16 < p.n_tiles16[wi];
         const uint8_t *ub = p.w[wi] + (size_t)(have ? tile16 : 0) * p.upt * p.unit_bytes;
         const uint32_t dst = tmem + ((uint32_t)(sub * 16) << 16) + tmem_a0;
-        const bool ok = warp < 8 ? produce<FMT, 0>(p, ub, have, lane, dst, slots, na, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0)
-                                 : produce<FMT, 1>(p, ub, have, lane, dst, slots, na, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0);
+        const bool ok = warp < 8 ? produce<FMT, 0, GS>(p, ub, have, lane, dst, slots, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0)
+                                 : produce<FMT, 1, GS>(p, ub, have, lane, dst, slots, full_bar(0), empty_bar(0), abort_flag, u0, u1 - u0);
         // ------------------------------------------------ epilogue: tensor memory -> Y[token][row]
         if (ok && mbar_wait(accum_bar, 0, abort_flag, p.err, 22)) {
             tc_fence_after();
@@ -690,16 +691,21 @@ int pick_token_tile(int64_t m, int64_t n, int sms)
 bool qgemm_supported(int type) { return type == 12 || type == 14 || type == 2 || type == 8; }
 
 namespace {
-template <int FMT>
-tlb_status launch_fmt_gemm(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &map, const GemmParams &p)
+template <int FMT, int GS>
+tlb_status launch_fmt_gemm_gs(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &map, const GemmParams &p)
 {
     static bool attr_set = false;
     if (!attr_set) {
-        TLB_CUDA(cudaFuncSetAttribute(qgemm_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemMax));
+        TLB_CUDA(cudaFuncSetAttribute(qgemm_kernel<FMT, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemMax));
         attr_set = true;
     }
-    qgemm_kernel<FMT><<<grid, kGemmThreads, smem, stream>>>(map, p);
+    qgemm_kernel<FMT, GS><<<grid, kGemmThreads, smem, stream>>>(map, p);
     return TLB_OK;
+}
+template <int FMT>
+tlb_status launch_fmt_gemm(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &map, const GemmParams &p)
+{
+    return p.gs == 4 ? launch_fmt_gemm_gs<FMT, 4>(grid, smem, stream, map, p) : launch_fmt_gemm_gs<FMT, 1>(grid, smem, stream, map, p);
 }
 }  // namespace
 
