@@ -44,6 +44,7 @@ typedef struct tlb_map tlb_map;           /* OpaqueTensorMap (crates/tl_runtime/
 typedef struct tlb_kvcache tlb_kvcache;   /* OpaqueKVCache (crates/tl_runtime/src/system.rs:387-615) */
 typedef struct tlb_graph tlb_graph;       /* GpuGraph (crates/tl_backend/src/graph.rs:22-31) */
 typedef struct tlb_decoder tlb_decoder;   /* fused decode session; see below */
+typedef struct tlb_tokenizer tlb_tokenizer; /* OpaqueTokenizer (crates/tl_runtime/src/tokenizer.rs:8-11) */
 
 /* ---- runtime ------------------------------------------------------------------------- */
 /* crates/tl_cuda/src/device.rs:79-86 get_device(): lazily binds one CUDA device and one
@@ -290,6 +291,24 @@ typedef struct {
  * the reference programs hard-code them, examples/apps/llama3/chatbot_llama3.tl:67-71,95,106,196); kv_f16, max_seq, tie_rule and
  * the tp fields stay as the caller set them. */
 tlb_status tlb_decoder_cfg_from_map(const tlb_map *m, tlb_decoder_cfg *cfg);
+
+/* ---- tokenizer (host code; crates/tl_runtime/src/tokenizer.rs, which wraps the `tokenizers` crate 0.22.2).  Reads a Hugging
+ * Face tokenizer.json of a BPE model in one of the two styles the reference's programs load: byte-level (Llama-3: Split
+ * with the Llama-3 or GPT-2 pattern + ByteLevel) or SentencePiece-style (TinyLlama / Llama-2: Prepend + Replace normalizer,
+ * byte fallback).  Anything else in the file is refused with TLB_ERR_TYPE.  Ids travel as f32 tensors, as TL holds them. */
+tlb_status tlb_tokenizer_new(tlb_tokenizer **out, const char *path);                                 /* :16 tl_tokenizer_new */
+tlb_status tlb_tokenizer_free(tlb_tokenizer *t);
+int64_t    tlb_tokenizer_vocab_size(const tlb_tokenizer *t);                                           /* added tokens included */
+const char *tlb_tokenizer_id_to_token(const tlb_tokenizer *t, int64_t id);                             /* NULL outside the vocabulary */
+/* encode(text, add_special_tokens = false): ids into a host buffer (ids may be NULL to ask for the count), no device needed */
+tlb_status tlb_tokenizer_encode_ids(const tlb_tokenizer *t, const char *text, int32_t *ids, int64_t cap, int64_t *n);
+tlb_status tlb_tokenizer_encode(tlb_tensor **out, const tlb_tokenizer *t, const char *text);           /* :44 BOS = 1 in front */
+tlb_status tlb_tokenizer_encode_chat(tlb_tensor **out, const tlb_tokenizer *t, const char *user_text); /* :136 Llama-3 template, special ids 128000 / 128006 / 128007 / 128009 */
+tlb_status tlb_tokenizer_encode_chat_zephyr(tlb_tensor **out, const tlb_tokenizer *t, const char *user_text); /* :210 */
+/* decode: one id -> its vocabulary text (byte tokens as their byte, <|...|> as nothing, U+2581 / U+0120 as a space, U+010A as a
+ * line break); several -> decode(ids, skip_special_tokens = true).  The string lives until the next decode on this tokenizer. */
+const char *tlb_tokenizer_decode(tlb_tokenizer *t, const tlb_tensor *ids);                              /* :73 */
+const char *tlb_tokenizer_decode_ids(tlb_tokenizer *t, const int32_t *ids, int64_t n);
 
 /* The TL chatbot's forward pass over `tokens` (f32-encoded ids, as TL holds them) from cache row start_pos, issued op by
  * op through the per-op entry points above, in the program's order (examples/apps/llama3/chatbot_llama3.tl:48-125,220-236):

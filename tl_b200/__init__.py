@@ -376,6 +376,49 @@ class Graph:
             self.h = None
 
 
+class Tokenizer:
+    """tokenizer.json reader + BPE encoder / decoder (crates/tl_runtime/src/tokenizer.rs).  encode_ids / decode_ids work on the
+    host alone; encode / encode_chat / encode_chat_zephyr return f32 id tensors on the device, as TL holds them."""
+
+    def __init__(self, path):
+        self.h = C.c_void_p()
+        check(lib().tlb_tokenizer_new(C.byref(self.h), str(path).encode()))
+
+    def vocab_size(self): return int(lib().tlb_tokenizer_vocab_size(self.h))
+
+    def id_to_token(self, i):
+        r = lib().tlb_tokenizer_id_to_token(self.h, i)
+        return None if r is None else r.decode("utf-8")
+
+    def encode_ids(self, text):
+        n = C.c_int64()
+        raw = text.encode("utf-8")
+        check(lib().tlb_tokenizer_encode_ids(self.h, raw, None, 0, C.byref(n)))
+        buf = (C.c_int32 * max(1, n.value))()
+        check(lib().tlb_tokenizer_encode_ids(self.h, raw, buf, n.value, C.byref(n)))
+        return [int(buf[i]) for i in range(n.value)]
+
+    def decode_ids(self, ids):
+        buf = (C.c_int32 * max(1, len(ids)))(*ids)
+        return lib().tlb_tokenizer_decode_ids(self.h, buf, len(ids)).decode("utf-8", errors="replace")
+
+    def encode(self, text): return Tensor._wrap(lib().tlb_tokenizer_encode, self.h, text.encode("utf-8"))
+    def encode_chat(self, text): return Tensor._wrap(lib().tlb_tokenizer_encode_chat, self.h, text.encode("utf-8"))
+    def encode_chat_zephyr(self, text): return Tensor._wrap(lib().tlb_tokenizer_encode_chat_zephyr, self.h, text.encode("utf-8"))
+    def decode(self, ids): return lib().tlb_tokenizer_decode(self.h, ids.h).decode("utf-8", errors="replace")
+
+    def free(self):
+        if self.h:
+            lib().tlb_tokenizer_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class Decoder:
     """Fused decode session over a TensorMap holding a Llama-shaped model."""
 

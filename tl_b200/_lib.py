@@ -84,6 +84,12 @@ def lib():
     d("tlb_gguf_load", S, pvp, C.c_char_p); d("tlb_map_new", S, pvp)
     d("tlb_map_meta_number", S, vp, C.c_char_p, C.POINTER(C.c_double)); d("tlb_map_meta_string", C.c_char_p, vp, C.c_char_p)
     d("tlb_decoder_cfg_from_map", S, vp, vp)
+    d("tlb_tokenizer_new", S, vp, C.c_char_p); d("tlb_tokenizer_free", S, vp); d("tlb_tokenizer_vocab_size", C.c_int64, vp)
+    d("tlb_tokenizer_id_to_token", C.c_char_p, vp, C.c_int64)
+    d("tlb_tokenizer_encode_ids", S, vp, C.c_char_p, vp, C.c_int64, vp)
+    d("tlb_tokenizer_encode", S, vp, vp, C.c_char_p); d("tlb_tokenizer_encode_chat", S, vp, vp, C.c_char_p)
+    d("tlb_tokenizer_encode_chat_zephyr", S, vp, vp, C.c_char_p)
+    d("tlb_tokenizer_decode", C.c_char_p, vp, vp); d("tlb_tokenizer_decode_ids", C.c_char_p, vp, vp, C.c_int64)
     d("tlb_chatbot_step_per_op", S, vp, vp, vp, vp, vp, vp, C.c_int64, C.c_int64, vp, vp)
     d("tlb_map_add", S, vp, C.c_char_p, C.c_int, pi64, C.c_int, vp, sz); d("tlb_map_free", S, vp)
     d("tlb_map_count", i64, vp); d("tlb_map_name", C.c_char_p, vp, i64)

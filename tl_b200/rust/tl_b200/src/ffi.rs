@@ -1,4 +1,4 @@
-//! The C ABI of libtlb200 (include/tlb200.h), declaration for declaration: 128 entry points.
+//! The C ABI of libtlb200 (include/tlb200.h), declaration for declaration: 138 entry points.
 //! Handles are opaque; status codes are the values of RuntimeErrorCode (crates/tl_runtime/src/error.rs:7-18).
 #![allow(non_camel_case_types)]
 use std::ffi::{c_char, c_int, c_void};
@@ -17,7 +17,7 @@ pub const TLB_TIE_LAST: c_int = 0;
 pub const TLB_TIE_FIRST: c_int = 1;
 
 macro_rules! opaque { ($($n:ident),*) => { $( #[repr(C)] pub struct $n { _private: [u8; 0] } )* } }
-opaque!(TlbTensor, TlbQTensor, TlbMap, TlbKvCache, TlbGraph, TlbDecoder);
+opaque!(TlbTensor, TlbQTensor, TlbMap, TlbKvCache, TlbGraph, TlbDecoder, TlbTokenizer);
 
 /// StringStruct of crates/tl_runtime/src/string_ffi.rs:7-11
 #[repr(C)]
@@ -159,6 +159,16 @@ extern "C" {
     pub fn tlb_map_add_tp(m: *mut TlbMap, name: *const c_char, type_: c_int, shape: *const i64, rank: c_int, bytes: *const c_void, nbytes: usize, tp_rank: c_int, tp_size: c_int) -> TlbStatus;
     pub fn tlb_gguf_load_tp(out: *mut *mut TlbMap, path: *const c_char, tp_rank: c_int, tp_size: c_int) -> TlbStatus;
     pub fn tlb_decoder_cfg_from_map(m: *const TlbMap, cfg: *mut TlbDecoderCfg) -> TlbStatus;
+    pub fn tlb_tokenizer_new(out: *mut *mut TlbTokenizer, path: *const c_char) -> TlbStatus;
+    pub fn tlb_tokenizer_free(t: *mut TlbTokenizer) -> TlbStatus;
+    pub fn tlb_tokenizer_vocab_size(t: *const TlbTokenizer) -> i64;
+    pub fn tlb_tokenizer_id_to_token(t: *const TlbTokenizer, id: i64) -> *const c_char;
+    pub fn tlb_tokenizer_encode_ids(t: *const TlbTokenizer, text: *const c_char, ids: *mut i32, cap: i64, n: *mut i64) -> TlbStatus;
+    pub fn tlb_tokenizer_encode(out: *mut *mut TlbTensor, t: *const TlbTokenizer, text: *const c_char) -> TlbStatus;
+    pub fn tlb_tokenizer_encode_chat(out: *mut *mut TlbTensor, t: *const TlbTokenizer, user_text: *const c_char) -> TlbStatus;
+    pub fn tlb_tokenizer_encode_chat_zephyr(out: *mut *mut TlbTensor, t: *const TlbTokenizer, user_text: *const c_char) -> TlbStatus;
+    pub fn tlb_tokenizer_decode(t: *mut TlbTokenizer, ids: *const TlbTensor) -> *const c_char;
+    pub fn tlb_tokenizer_decode_ids(t: *mut TlbTokenizer, ids: *const i32, n: i64) -> *const c_char;
     pub fn tlb_chatbot_step_per_op(weights: *mut TlbMap, cache: *mut TlbKvCache, cos_t: *const TlbTensor, sin_t: *const TlbTensor, cfg: *const TlbDecoderCfg, tokens: *const f32, n_tokens: i64, start_pos: i64, next_token: *mut i64, logits_out: *mut *mut TlbTensor) -> TlbStatus;
     pub fn tlb_decoder_create(out: *mut *mut TlbDecoder, cfg: *const TlbDecoderCfg, weights: *mut TlbMap) -> TlbStatus;
     pub fn tlb_decoder_destroy(d: *mut TlbDecoder) -> TlbStatus;
