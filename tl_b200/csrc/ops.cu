@@ -221,15 +221,19 @@ __global__ void __launch_bounds__(256) transpose_last2_kernel(const float *__res
 }
 
 // C[b][r][n] = sum_k A[b][r][k] B[b][k][n] for up to 4 rows r (the decode step's attention products: one query row per
-// head against the whole cache).  64 columns x 8 slices of k per CTA; the slices are added in index order.
+// head against the whole cache).  COLS columns x 512 / COLS slices of k per CTA; the slices are added in index order.
+// Wide results take 64 columns per CTA; narrow ones (P.V: 128 columns, thousands of k) take 16, so that there are enough
+// CTAs and each thread's share of k stays short.
+template <int COLS>
 __global__ void __launch_bounds__(512) matmul_rows_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ C,
                                                           int m, int k, int n, int b_batched)
 {
-    __shared__ float red[8][4][64];
+    constexpr int SL = 512 / COLS;
+    __shared__ float red[SL][4][COLS];
     const float *a = A + (size_t)blockIdx.y * m * k;
     const float *b = B + (b_batched ? (size_t)blockIdx.y * k * n : 0);
-    const int tx = threadIdx.x & 63, ks = threadIdx.x >> 6, col = blockIdx.x * 64 + tx;
-    const int kc = (k + 7) / 8, k0 = ks * kc, k1 = min(k, k0 + kc);
+    const int tx = threadIdx.x % COLS, ks = threadIdx.x / COLS, col = blockIdx.x * COLS + tx;
+    const int kc = (k + SL - 1) / SL, k0 = ks * kc, k1 = min(k, k0 + kc);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (col < n) {
         for (int kk = k0; kk < k1; kk++) {
@@ -242,10 +246,9 @@ __global__ void __launch_bounds__(512) matmul_rows_kernel(const float *__restric
 #pragma unroll
     for (int r = 0; r < 4; r++) red[ks][r][tx] = acc[r];
     __syncthreads();
-    if (ks < m && col < n) {       // slice-warps 0 .. m-1 each finish one row
+    if (ks < m && col < n) {       // slices 0 .. m-1 each finish one row
         float v = red[0][ks][tx];
-#pragma unroll
-        for (int q = 1; q < 8; q++) v += red[q][ks][tx];
+        for (int q = 1; q < SL; q++) v += red[q][ks][tx];
         C[((size_t)blockIdx.y * m + ks) * n + col] = v;
     }
 }
@@ -449,8 +452,13 @@ tlb_status launch_matmul(const float *a, const float *b, float *out, int64_t bat
 {
     if (batch * m * n == 0) return TLB_OK;
     if (m <= 4 && k <= INT32_MAX && n <= INT32_MAX && batch <= 65535) {
-        dim3 grid((unsigned)((n + 63) / 64), (unsigned)batch);
-        matmul_rows_kernel<<<grid, 512, 0, ctx()->stream>>>(a, b, out, (int)m, (int)k, (int)n, b_batched ? 1 : 0);
+        if (n <= 256) {
+            dim3 grid((unsigned)((n + 15) / 16), (unsigned)batch);
+            matmul_rows_kernel<16><<<grid, 512, 0, ctx()->stream>>>(a, b, out, (int)m, (int)k, (int)n, b_batched ? 1 : 0);
+        } else {
+            dim3 grid((unsigned)((n + 63) / 64), (unsigned)batch);
+            matmul_rows_kernel<64><<<grid, 512, 0, ctx()->stream>>>(a, b, out, (int)m, (int)k, (int)n, b_batched ? 1 : 0);
+        }
         LAUNCH_CHECK();
         return TLB_OK;
     }
