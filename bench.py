@@ -290,7 +290,7 @@ def measure_prefill(tl, cfg, wmap, kv16, ev, peaks, batch=8, tokens=2048):
     return {"workload": "c3: %d x %d prompt tokens, all %d layers" % (batch, tokens, cfg["n_layers"]), "tokens": batch * tokens, "ms": round(ms, 2),
             "tokens_per_s": round(batch * tokens / (ms * 1e-3), 0), "tflops": round(tf, 1), "bound": "tensor", "peak_tflops": peak,
             "frac": round(tf / peak, 4),
-            "note": "f16 tcgen05 GEMMs with on-the-fly dequantisation + mma.sync attention; head on each sequence's last token"}
+            "note": "f16 tcgen05 GEMMs with on-the-fly dequantisation (weights in tensor memory) + tcgen05 attention (scores, probabilities and output in tensor memory); head on each sequence's last token"}
 
 
 SWEEP_SHAPES = [(2048, 2048), (4096, 4096), (14336, 4096), (4096, 14336), (128256, 4096)]   # (N out, K in): the config's K x N

@@ -223,6 +223,32 @@ def test_prefill_llama3_shaped_one_layer(orc):
     assert relerr(la, dec3.logits()) < 2e-3
 
 
+def test_prefill_tensor_core_attention_chunks_and_offsets():
+    """head_dim 128 over an f16 cache takes the tcgen05 attention kernel from 64 tokens on.  A 300-token prompt given as 100 +
+    200 tokens (the second call starts at cache row 100: three key tiles, the last one ragged, queries offset against keys)
+    against the same session fed token by token; then 70 more tokens at row 300 (one ragged query tile over four key tiles)."""
+    cfg = dict(synth.LLAMA3_8B, n_layers=2, vocab=1024)
+    wmap = tl.map_from_tensors(synth.llama_tensors(cfg, 9, synth.Q4_K, synth.Q6_K))
+    rng = np.random.default_rng(10)
+    prompt = [int(t) for t in rng.integers(0, cfg["vocab"], 370)]
+    dec = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=512)
+    dec.prefill(prompt[:100], 0)
+    a = dec.prefill(prompt[100:300], 100)
+    la = dec.logits()
+    dec2 = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=512)
+    for i, t in enumerate(prompt[:300]):
+        b = dec2.step(t, i)
+    assert a == b
+    assert relerr(la, dec2.logits()) < 2e-3
+    a = dec.prefill(prompt[300:], 300)
+    la = dec.logits()
+    for i, t in enumerate(prompt[300:]):
+        b = dec2.step(t, 300 + i)
+    assert a == b
+    assert relerr(la, dec2.logits()) < 2e-3
+    assert dec.generate(a, 370, 8) == dec2.generate(b, 370, 8)
+
+
 def test_prefill_f32_cache_head_dim_128():
     """f32 KV cache with head_dim 128 (the tile conversion path of the prompt attention): prompt in one call against
     the same session fed token by token."""

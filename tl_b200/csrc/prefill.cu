@@ -284,6 +284,8 @@ tlb_status launch_prefill_attention(const float *q, const void *kcache, const vo
 {
     if (n_tokens <= 0) return TLB_OK;
     if (!prefill_attention_supported(D)) return fail(TLB_ERR_SHAPE, "prompt attention: head_dim %d is not supported (64 or 128)", D);
+    // head_dim 128 over an f16 cache, 64 tokens or more: both products on tcgen05 (prefill_attn_tc.cu)
+    if (prefill_attention_tc_supported(D, kv_f16, n_tokens)) return launch_prefill_attention_tc(q, kcache, vcache, out, n_tokens, H, KVH, max_seq, pos0, scale);
     PfAttnParams p;
     p.q = q; p.kcache = kcache; p.vcache = vcache; p.out = out;
     p.T = n_tokens; p.H = H; p.KVH = KVH; p.max_seq = max_seq; p.pos0 = pos0; p.scale = scale;

@@ -33,7 +33,7 @@
 
 #include <algorithm>
 
-#include "qmv_common.cuh"
+#include "tc05.cuh"
 
 namespace tlb {
 
@@ -305,47 +305,6 @@ template <> struct UnitRegs<12> { using type = Q4KRegs; };
 template <> struct UnitRegs<14> { using type = Q6KRegs; };
 template <> struct UnitRegs<2> { using type = Q40Regs; };
 template <> struct UnitRegs<8> { using type = Q80Regs; };
-
-// ---- tcgen05 wrappers
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
-{
-    // K-major, 128-byte swizzle: 8-row groups 1024 bytes apart (stride offset), leading offset unused (1),
-    // descriptor version 1, layout type 2 (SWIZZLE_128B)
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// A operand from tensor memory: 128 lanes (rows) x 8 columns (16 f16 along K, two per column)
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-// Asks L2 for `bytes` (a multiple of 16) at the 16-byte aligned `ptr`; nothing is written on the SM.
-__device__ __forceinline__ void l2_prefetch(const void *ptr, uint32_t bytes)
-{
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
-}
 
 // ---- one dequantising warp: 64-groups 2 HALF and 2 HALF + 1 of every unit of its 16 rows.  `dst`: tensor-memory address
 // (the warp's 16 lanes, first column) of weight stage 0.  A stage holds gs 64-wide groups (gs = 1: K step = group, the
@@ -661,18 +620,6 @@ __global__ void __launch_bounds__(NT) x_to_f16_kernel(const float *__restrict__ 
         for (int64_t i = threadIdx.x * 4; i < k; i += NT * 4) pass2(i, 0);
     }
     if (threadIdx.x == 0) inv_scale[blockIdx.x] = inv;
-}
-
-PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder()
-{
-    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
-        void *f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-            f = nullptr;
-        return (PFN_cuTensorMapEncodeTiled_v12000)f;
-    }();
-    return fn;
 }
 
 // Activation rows per CTA: up to 128 rows one tile; above, 256-row tiles if they give every SM work, else 128-row

@@ -148,6 +148,9 @@ tlb_status launch_embed_rows(const int *tokens, const float *table, float *x, in
 tlb_status launch_rope_append(float *q, const float *k, const float *v, void *kcache, void *vcache, int kv_f16, const float *cos_t,
                               const float *sin_t, int n_tokens, int H, int KVH, int D, int max_seq, int pos0, int rope0, int rope_step);
 bool prefill_attention_supported(int head_dim);
+bool prefill_attention_tc_supported(int D, int kv_f16, int n_tokens);
+tlb_status launch_prefill_attention_tc(const float *q, const void *kcache, const void *vcache, float *out, int n_tokens, int H, int KVH,
+                                       int max_seq, int pos0, float scale);
 tlb_status launch_prefill_attention(const float *q, const void *kcache, const void *vcache, int kv_f16, float *out, int n_tokens, int H,
                                     int KVH, int D, int max_seq, int pos0, float scale);
 tlb_status launch_repack(int type, const uint8_t *raw, uint8_t *tiled, int64_t n, int64_t k);
