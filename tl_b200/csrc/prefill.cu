@@ -4,10 +4,11 @@
 // examples/apps/llama3/chatbot_llama3.tl:66-125 (embedding, rms_norm, apply_rope, kv update, scaled
 // scores + causal mask + softmax, context) - for T tokens per launch.
 //
-// Attention is a streaming-softmax kernel on mma.sync (f16 operands, f32 accumulation): one CTA per
-// (64 queries, head), each warp 16 queries; K and V tiles of 64 cache rows are staged in shared memory as
-// f16 (converted on the way when the cache is f32), scores never leave registers.  It is ~4 % of the
-// prompt's arithmetic; the projections run in qgemm_tc.cu.
+// Attention: head_dim 128 over an f16 cache (64 tokens or more) runs on tcgen05 (prefill_attn_tc.cu); every other case -
+// head_dim 64, an f32 cache, short prompts - runs here as a streaming-softmax kernel on mma.sync (f16 operands, f32
+// accumulation): one CTA per (64 queries, head), each warp 16 queries; K and V tiles of 64 cache rows are staged in shared
+// memory as f16 (converted on the way when the cache is f32), scores never leave registers.  The projections run in
+// qgemm_tc.cu.
 #include <algorithm>
 
 #include "qmv_common.cuh"
