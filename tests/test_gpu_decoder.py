@@ -185,12 +185,18 @@ def test_prefill_in_chunks_equals_token_by_token(orc):
 def test_prefill_short_prompt_and_errors(orc):
     ref, dec, wmap = build(orc, SMALL, 13, synth.Q4_K, synth.Q6_K, True, 64)
     dec2 = tl.Decoder(SMALL, wmap, kv_f16=True, max_seq=64)
-    prompt = [3, 1, 4, 1, 5]
-    a = dec.prefill(prompt, 0)             # 16 tokens or fewer: the single-token chain, bit for bit
-    for i, t in enumerate(prompt):
+    dec3 = tl.Decoder(SMALL, wmap, kv_f16=True, max_seq=64)
+    short = [3, 1, 4, 1]
+    a = dec3.prefill(short, 0)             # 4 tokens or fewer: the single-token chain, bit for bit
+    for i, t in enumerate(short):
         b = dec2.step(t, i)
     assert a == b
-    np.testing.assert_array_equal(dec.logits().view(np.uint32), dec2.logits().view(np.uint32))
+    np.testing.assert_array_equal(dec3.logits().view(np.uint32), dec2.logits().view(np.uint32))
+    prompt = [3, 1, 4, 1, 5]               # from 5 tokens on: all rows at once (the few-rows kernel up to 16)
+    ref_logits = ref.forward(prompt, 0)
+    nxt = dec.prefill(prompt, 0)
+    assert relerr(dec.logits(), ref_logits) < LOGIT_TOL
+    assert nxt == orc.argmax_last(ref_logits)
     with pytest.raises(tl.TlbError) as e:
         dec.prefill([SMALL["vocab"]] * 20, 0)          # token out of range
     assert e.value.code == 6

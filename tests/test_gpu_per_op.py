@@ -27,7 +27,8 @@ def test_per_op_route_matches_oracle_and_fused_session(orc, linear, head):
     prompt = [5, 17, 300, 9, 41, 77, 2]
     rl = ref.forward(prompt, 0)
     tok = bot.step(prompt, 0)                       # the whole prompt in one pass: causal mask, rotation at row 0
-    assert relerr(bot.last_logits.numpy()[0], rl) < 5e-4
+    # seven rows: the quantized matmuls run on the few-rows kernel (f16 activations); the single-token steps below on the matvec
+    assert relerr(bot.last_logits.numpy()[0], rl) < 5e-3
     assert tok == orc.argmax_last(rl)
     fused = None
     if head != synth.F16:                           # the fused session takes tiled weights only; the per-op route any QTensor

@@ -85,7 +85,8 @@ def test_qmatvec_matches_oracle(orc, t, n, k, m):
     got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
     ref = orc.qmatmul(t, w.reshape(-1), n, k, x)
     assert got.shape == (m, n)
-    assert relerr(got, ref) < MATVEC_TOL
+    # up to 4 rows: the matvec (two int8 levels per activation); 5 to 16: the few-rows kernel (f16 activations)
+    assert relerr(got, ref) < (MATVEC_TOL if m <= 4 else GEMM_TOL)
 
 
 @pytest.mark.parametrize("t,n,k", [(synth.Q4_K, 4096, 4096), (synth.Q4_K, 4096, 14336), (synth.Q6_K, 8192, 4096),
@@ -211,7 +212,7 @@ def test_qgemm_rank3_input_and_shape_error():
 
 
 def test_mid_row_counts_on_a_wide_weight(orc):
-    """5 to 16 rows on 14336 x 4096 (gate / up shape) run through the GEMM: sampled output rows against the oracle."""
+    """5 to 16 rows on 14336 x 4096 (gate / up shape) run through the few-rows kernel: sampled output rows against the oracle."""
     n, k = 14336, 4096
     rng = np.random.default_rng(79)
     w = synth.random_quant(synth.Q4_K, n, k, rng)
@@ -224,6 +225,26 @@ def test_mid_row_counts_on_a_wide_weight(orc):
         assert got.shape == (m, n)
         for i in range(m):
             assert relerr(got[i][rows], ref[i]) < GEMM_TOL, (m, i)
+
+
+@pytest.mark.parametrize("t", TYPES)
+@pytest.mark.parametrize("n,k", [(1000, 512), (4100, 1024), (272, 2304)])
+def test_few_rows_kernel_shapes(orc, t, n, k):
+    """5 to 16 rows stream through the few-rows kernel: the unit rounds (16-tile group x 256-wide unit) are cut evenly over
+    the CTAs, so tile groups are split between CTAs at arbitrary units and summed by a second launch.  1000 rows: a last
+    tile of 8 rows; 4100: a last tile group of one tile; 272 x 2304: 9 units over two tile groups.  Whole result against
+    the oracle, one row 50 times larger than the rest (per-row activation scale)."""
+    rng = np.random.default_rng(7000 + t + n)
+    w = synth.random_quant(t, n, k, rng)
+    q = tl.QTensor.from_gguf_bytes(t, n, k, w)
+    for m in (5, 8, 9, 16):
+        x = rng.standard_normal((m, k), dtype=np.float32)
+        x[m - 1] *= 50.0
+        got = tl.Tensor.from_numpy(x).matmul_quantized(q).numpy()
+        ref = orc.qmatmul(t, w.reshape(-1), n, k, x)
+        assert got.shape == (m, n)
+        for i in range(m):
+            assert relerr(got[i], ref[i]) < GEMM_TOL, (m, i)
 
 
 @pytest.mark.parametrize("t", TYPES)

@@ -1132,7 +1132,7 @@ extern "C" tlb_status tlb_decoder_prefill(tlb_decoder *d, const int32_t *tokens,
     const int64_t last_rope = (int64_t)rope_pos0 + (int64_t)(n - 1) * rope_step;
     if (pos0 < 0 || (int64_t)pos0 + n > c.max_seq || rope_pos0 < 0 || rope_step < 0 || last_rope >= c.max_seq)
         return fail(TLB_ERR_INDEX, "positions [%d, %d) / rotation rows up to %lld outside the cache of %d rows", pos0, pos0 + n, (long long)last_rope, c.max_seq);
-    if (n <= kGemmMinRows || !prefill_batched_ok(d)) {
+    if (n <= 4 || !prefill_batched_ok(d)) {
         // few tokens, or a shape the GEMM path does not take: the fused single-token chain, token by token
         int32_t tok = 0;
         for (int i = 0; i < n; i++) TLB_TRY(tlb_decoder_step(d, tokens[i], pos0 + i, rope_pos0 + i * rope_step, i == n - 1 ? &tok : nullptr));

@@ -29,6 +29,7 @@
 // Every wait on an mbarrier is bounded (qmv_common.cuh: mbar_wait); when one runs out the CTA sets the
 // context's error word, lets its outstanding copies land (bounded), frees its tensor memory and returns.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cudaTypedefs.h>
 
 #include <algorithm>
@@ -167,14 +168,25 @@ struct Q4KRegs {
     uint4 q[2];
     uint4 h[2];
 };
-template <int HALF>
+// 16 bytes / 2 bytes of a unit: from global memory through the read-only path (G), or from wherever the generic pointer
+// leads (a stage in shared memory)
+template <bool G> __device__ __forceinline__ uint4 ldq(const uint8_t *p)
+{
+    return G ? __ldg(reinterpret_cast<const uint4 *>(p)) : *reinterpret_cast<const uint4 *>(p);
+}
+template <bool G> __device__ __forceinline__ __half ldh(const uint8_t *p)
+{
+    return G ? __ldg(reinterpret_cast<const __half *>(p)) : *reinterpret_cast<const __half *>(p);
+}
+
+template <int HALF, bool G = true>
 __device__ __forceinline__ void unit_load(Q4KRegs &u, const uint8_t *unit, int lane)
 {
     const int r = lane >> 2;
 #pragma unroll
-    for (int gg = 0; gg < 2; gg++) u.q[gg] = __ldg(reinterpret_cast<const uint4 *>(unit + (HALF * 2 + gg) * 512 + lane * 16));
-    u.h[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + r * 16));
-    u.h[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + (r + 8) * 16));
+    for (int gg = 0; gg < 2; gg++) u.q[gg] = ldq<G>(unit + (HALF * 2 + gg) * 512 + lane * 16);
+    u.h[0] = ldq<G>(unit + 2048 + r * 16);
+    u.h[1] = ldq<G>(unit + 2048 + (r + 8) * 16);
 }
 // Dequantise 64-group g of the unit (rows r and r + 8 of the warp's sixteen): chunks 0, 1 are the low nibbles
 // (k = byte index), chunks 2, 3 the high ones (k = 32 + byte index).
@@ -203,16 +215,16 @@ struct Q6KRegs {
     uint4 sc[2];
     float d[2];
 };
-template <int HALF>
+template <int HALF, bool G = true>
 __device__ __forceinline__ void unit_load(Q6KRegs &u, const uint8_t *unit, int lane)
 {
     const int r = lane >> 2;
 #pragma unroll
     for (int hi = 0; hi < 2; hi++) {
-        u.ql[hi] = __ldg(reinterpret_cast<const uint4 *>(unit + (hi * 2 + HALF) * 512 + lane * 16));
-        u.qh[hi] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + hi * 512 + lane * 16));
-        u.sc[hi] = __ldg(reinterpret_cast<const uint4 *>(unit + 3072 + (r + 8 * hi) * 16));
-        u.d[hi] = __half2float(__ldg(reinterpret_cast<const __half *>(unit + 3328 + (r + 8 * hi) * 2)));
+        u.ql[hi] = ldq<G>(unit + (hi * 2 + HALF) * 512 + lane * 16);
+        u.qh[hi] = ldq<G>(unit + 2048 + hi * 512 + lane * 16);
+        u.sc[hi] = ldq<G>(unit + 3072 + (r + 8 * hi) * 16);
+        u.d[hi] = __half2float(ldh<G>(unit + 3328 + (r + 8 * hi) * 2));
     }
 }
 // 64-group g = (n, sub): k = 128 n + 64 sub + [0, 64).  sub 0 takes the low nibbles of ql and bits 0-3 of qh,
@@ -242,14 +254,14 @@ struct Q40Regs {
     uint4 q[2];
     uint4 d[2];   // eight f16 block scales of rows r and r + 8
 };
-template <int HALF>
+template <int HALF, bool G = true>
 __device__ __forceinline__ void unit_load(Q40Regs &u, const uint8_t *unit, int lane)
 {
     const int r = lane >> 2;
 #pragma unroll
-    for (int gg = 0; gg < 2; gg++) u.q[gg] = __ldg(reinterpret_cast<const uint4 *>(unit + (HALF * 2 + gg) * 512 + lane * 16));
-    u.d[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + r * 16));
-    u.d[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 2048 + (r + 8) * 16));
+    for (int gg = 0; gg < 2; gg++) u.q[gg] = ldq<G>(unit + (HALF * 2 + gg) * 512 + lane * 16);
+    u.d[0] = ldq<G>(unit + 2048 + r * 16);
+    u.d[1] = ldq<G>(unit + 2048 + (r + 8) * 16);
 }
 __device__ __forceinline__ uint32_t h2_pair(const uint4 &v, int i)   // i-th f16 of the 16 bytes, in both halves
 {
@@ -276,14 +288,14 @@ struct Q80Regs {
     uint4 q[4];
     uint4 d[2];
 };
-template <int HALF>
+template <int HALF, bool G = true>
 __device__ __forceinline__ void unit_load(Q80Regs &u, const uint8_t *unit, int lane)
 {
     const int r = lane >> 2;
 #pragma unroll
-    for (int i = 0; i < 4; i++) u.q[i] = __ldg(reinterpret_cast<const uint4 *>(unit + (HALF * 4 + i) * 512 + lane * 16));
-    u.d[0] = __ldg(reinterpret_cast<const uint4 *>(unit + 4096 + r * 16));
-    u.d[1] = __ldg(reinterpret_cast<const uint4 *>(unit + 4096 + (r + 8) * 16));
+    for (int i = 0; i < 4; i++) u.q[i] = ldq<G>(unit + (HALF * 4 + i) * 512 + lane * 16);
+    u.d[0] = ldq<G>(unit + 4096 + r * 16);
+    u.d[1] = ldq<G>(unit + 4096 + (r + 8) * 16);
 }
 __device__ __forceinline__ void unit_emit(const Q80Regs &u, int g, AFrag &f)
 {
@@ -533,6 +545,492 @@ __global__ void __launch_bounds__(256) qgemm_split_sum_kernel(const SplitSum a)
     }
 }
 
+// ---------------------------------------------------------------- raw quants as MMA operands
+// The streaming kernel for few activation rows below spends its time issuing instructions, so it does not dequantise: a
+// quant u (0 .. 255) placed in the low bits of an f16 IS the number u * 2^-24 (subnormal, or the first normal binade, whose bit
+// patterns continue the same line up to 2047), which one AND per two weights produces.  The MMA sums u * x exactly over
+// the 16 or 32 weights that share a scale, and the scale - times 2^24 - multiplies that sum in f32.  High nibbles stay in
+// place where their chunk has a scale of its own (u * 16, the scale times 2^20).  Constant offsets (-32, -8, -128) are
+// subtracted in f16, exactly; the per-sub-block minima of Q4_K enter through one more MMA per unit and activation half:
+// A = the 6-bit minima as bf16, B = the activations' sub-block sums as bf16 (high part, remainder) pairs.
+struct RawScales { float s[2][4]; };     // [row r / r + 8][chunk, or pair of chunks where two share a scale]
+constexpr float kTwo24 = 16777216.f, kTwo20 = 1048576.f;
+
+// D(16x8 f32) = A(16x16 f16) * B(16x8 f16)
+__device__ __forceinline__ void hmma16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ void bmma16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+// byte i (a runtime index) of w as a float
+__device__ __forceinline__ float byte_f(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xFFu); }
+// a small integer as a bf16 in both halves of a word
+__device__ __forceinline__ uint32_t bf16_pair(float v) { return prmt(__float_as_uint(v), 0u, 0x3232u); }
+
+template <int FMT> struct RawTraits;
+template <> struct RawTraits<12> { static constexpr int kPair = 2; static constexpr bool kMins = true; };
+template <> struct RawTraits<14> { static constexpr int kPair = 1; static constexpr bool kMins = false; };
+template <> struct RawTraits<2> { static constexpr int kPair = 2; static constexpr bool kMins = false; };
+template <> struct RawTraits<8> { static constexpr int kPair = 2; static constexpr bool kMins = false; };
+
+// Q4_K: chunks 0, 1 = the low nibbles (sub-block 2 g), chunks 2, 3 = the high ones in place (sub-block 2 g + 1)
+__device__ __forceinline__ void unit_raw(const Q4KRegs &u, int g, AFrag &f, RawScales &sc)
+{
+#pragma unroll
+    for (int rs = 0; rs < 2; rs++) {
+        uint32_t scw, mw;
+        q4k_scales4(u.h[rs], g >= 2, scw, mw);
+        const float d = h2_to_f2(u.h[rs].x).x;
+        // (2^23 + sc) * d 2^24 - 2^23 d 2^24 = sc d 2^24, rounded once
+        const float d24 = d * kTwo24, d20 = d * kTwo20;
+        sc.s[rs][0] = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7650u + ((2 * g) & 3))), d24, -8388608.f * d24);
+        sc.s[rs][1] = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7650u + ((2 * g + 1) & 3))), d20, -8388608.f * d20);
+#pragma unroll
+        for (int jl = 0; jl < 2; jl++) {
+            const uint32_t wd = word_of(u.q[g & 1], rs * 2 + jl), w8 = wd >> 8;
+            f.v[4 * jl + 2 * rs] = wd & 0x000F000Fu;
+            f.v[4 * jl + 2 * rs + 1] = w8 & 0x000F000Fu;
+            f.v[4 * (2 + jl) + 2 * rs] = wd & 0x00F000F0u;
+            f.v[4 * (2 + jl) + 2 * rs + 1] = w8 & 0x00F000F0u;
+        }
+    }
+}
+// the minima of sub-blocks c and c + 4 of rows r, r + 8 as the A operand of the sums MMA, and dmin of both rows
+__device__ __forceinline__ void q4k_mins(const Q4KRegs &u, int c, uint32_t (&a)[4], float (&dmin)[2])
+{
+#pragma unroll
+    for (int rs = 0; rs < 2; rs++) {
+        uint32_t scw, mlo, mhi;
+        q4k_scales4(u.h[rs], false, scw, mlo);
+        q4k_scales4(u.h[rs], true, scw, mhi);
+        a[rs] = bf16_pair(byte_f(mlo, c));
+        a[2 + rs] = bf16_pair(byte_f(mhi, c));
+        dmin[rs] = h2_to_f2(u.h[rs].x).y;
+    }
+}
+
+template <class R> __device__ __forceinline__ void q4k_mins(const R &, int, uint32_t (&)[4], float (&)[2]) {}   // the other formats have no minima
+
+// Q6_K: every chunk has its own int8 scale; q - 32 in f16
+__device__ __forceinline__ void unit_raw(const Q6KRegs &u, int g, AFrag &f, RawScales &sc)
+{
+    const int n = g >> 1, sub = g & 1;
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+        const float d24 = u.d[hi] * kTwo24;
+#pragma unroll
+        for (int st = 0; st < 4; st++) {
+            const int h = st & 1, q1 = st >> 1;
+            const uint32_t qlw = q1 ? word_of(u.ql[hi], 2 + h) : word_of(u.ql[hi], h);
+            const uint32_t qhw = word_of(u.qh[hi], n * 2 + h);
+            const uint32_t nib = (sub ? (qlw >> 4) : qlw) & 0x0F0F0F0Fu;
+            const uint32_t two = (qhw >> (2 * (sub * 2 + q1))) & 0x03030303u;
+            const uint32_t b6 = nib | (two << 4);
+            const int s0 = 8 * n + h + 4 * sub + 2 * q1;
+            sc.s[hi][st] = d24 * (float)(int)(int8_t)((word_of(u.sc[hi], s0 >> 2) >> (8 * (s0 & 3))) & 0xFFu);
+            f.v[4 * st + 2 * hi] = hsub2(b6 & 0x00FF00FFu, 0x00200020u);
+            f.v[4 * st + 2 * hi + 1] = hsub2((b6 >> 8) & 0x00FF00FFu, 0x00200020u);
+        }
+    }
+}
+// Q4_0: chunks 2 b, 2 b + 1 = the low and high nibbles of block 2 g + b; nibble - 8 in f16
+__device__ __forceinline__ void unit_raw(const Q40Regs &u, int g, AFrag &f, RawScales &sc)
+{
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+#pragma unroll
+        for (int b = 0; b < 2; b++) {
+            const uint32_t dw = word_of(u.d[hi], g);                       // f16 scales of blocks 2 g, 2 g + 1
+            sc.s[hi][b] = (b ? h2_to_f2(dw).y : h2_to_f2(dw).x) * kTwo24;
+            const uint32_t wd = word_of(u.q[g & 1], hi * 2 + b);
+            f.v[8 * b + 2 * hi] = hsub2(wd & 0x000F000Fu, 0x00080008u);
+            f.v[8 * b + 2 * hi + 1] = hsub2((wd >> 8) & 0x000F000Fu, 0x00080008u);
+            f.v[8 * b + 4 + 2 * hi] = hsub2((wd >> 4) & 0x000F000Fu, 0x00080008u);
+            f.v[8 * b + 4 + 2 * hi + 1] = hsub2((wd >> 12) & 0x000F000Fu, 0x00080008u);
+        }
+    }
+}
+// Q8_0: chunks 2 b, 2 b + 1 = the halves of block 2 g + b; (q + 128) - 128 in f16
+__device__ __forceinline__ void unit_raw(const Q80Regs &u, int g, AFrag &f, RawScales &sc)
+{
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+#pragma unroll
+        for (int st = 0; st < 4; st++) {
+            const int h = st & 1, b = st >> 1;
+            const uint32_t dw = word_of(u.d[hi], g);
+            if (h == 0) sc.s[hi][b] = (b ? h2_to_f2(dw).y : h2_to_f2(dw).x) * kTwo24;
+            const uint32_t wd = (b ? word_of(u.q[2 * (g & 1) + 1], hi * 2 + h) : word_of(u.q[2 * (g & 1)], hi * 2 + h)) ^ 0x80808080u;
+            f.v[4 * st + 2 * hi] = hsub2(wd & 0x00FF00FFu, 0x00800080u);
+            f.v[4 * st + 2 * hi + 1] = hsub2((wd >> 8) & 0x00FF00FFu, 0x00800080u);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- up to 16 activation rows: a streaming kernel
+// Few rows leave the tensor-core GEMM above at its floor (a 128-row tile per CTA whatever the width, a fixed cost per CTA and
+// per K step), so they get the streaming form of the matvec instead: persistent CTAs of 16 warps, a warp owns 16 weight rows
+// and streams their units from HBM through a private ring of bulk copies, turns them into raw-quant A fragments (above: the
+// sixteen words of a 64-group ARE the A operands of four mma.sync.m16n8k16, row r / r + 8, K 4c .. 4c+3 of every 16-chunk)
+// and multiplies them with the activation rows - f16, scaled per row by x_to_f16_kernel, one 256-wide piece per unit that
+// the CTA's warps share - as two MMAs per chunk (rows 0-7 and 8-15 of the activation).
+// The activation piece of a unit is 512 bytes per row, copied row by row to a pitch of 528 bytes; x_to_f16_kernel writes
+// these rows with the chunk index and the lane's index c exchanged inside every 64-group (order [c][j][4]), so that a lane's
+// B operands of four chunks are 32 consecutive bytes: two conflict-free 128-bit loads per 64-group and activation half.
+// A CTA works through items = 16 consecutive tiles x a range of K units; with several ranges per tile group (narrow
+// weights) the partial products go to scratch and a second launch adds them in range order.
+constexpr int kRowsWarps = 16;
+constexpr int kRowsThreads = (kRowsWarps + 1) * 32;     // + the copy warp of the activations
+constexpr int kRowsWBytes = 168 * 1024;                  // weight rings of all warps: 2 to 4 stages each, by the unit's size
+constexpr int kRowsAStages = 4;                          // activation ring per CTA
+constexpr int kRowsAPitch = 528;                         // bytes between activation rows of a stage
+constexpr int kRowsABytes = 16 * kRowsAPitch;
+constexpr int kRowsSumBytes = 16 * 8 * 4;                // their sums over the unit's eight 32-blocks, (high, remainder) bf16 pairs
+
+struct RowsParams {
+    const uint8_t *w[kGemmMaxW];
+    float *out[kGemmMaxW];
+    int n[kGemmMaxW], n_tiles16[kGemmMaxW], tg_end[kGemmMaxW], tile0[kGemmMaxW];   // tile groups / first tile of weight i among all
+    int n_w, upt, unit_bytes, stage_w, wstages, m;
+    int tgroups, total, maxp;       // total = tgroups x upt unit rounds, cut evenly over the CTAs; maxp: tile groups a CTA can touch
+    int64_t k;
+    const __half *xh;               // [m][k], rows in the order described above
+    const float *inv_scale, *resid;
+    const uint8_t *sums;            // [K / 256][16][8] sub-block sums of the activation rows (x_to_f16_kernel)
+    float *part;                    // [CTA][tile group of the CTA][16 tiles][16 rows][16 activation rows]: pieces of split tile groups
+    int *cnt;                       // [tile group][16 tiles]: pieces of the tile that are written; zero between launches
+    int *err;
+};
+
+// unit registers from a stage in shared memory (the layouts of unit_load above)
+template <int HALF> __device__ __forceinline__ void unit_load_s(Q4KRegs &u, uint32_t unit, int lane)
+{
+    const int r = lane >> 2;
+    for (int gg = 0; gg < 2; gg++) u.q[gg] = lds128(unit + (HALF * 2 + gg) * 512 + lane * 16);
+    u.h[0] = lds128(unit + 2048 + r * 16);
+    u.h[1] = lds128(unit + 2048 + (r + 8) * 16);
+}
+template <int HALF> __device__ __forceinline__ void unit_load_s(Q6KRegs &u, uint32_t unit, int lane)
+{
+    const int r = lane >> 2;
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+        u.ql[hi] = lds128(unit + (hi * 2 + HALF) * 512 + lane * 16);
+        u.qh[hi] = lds128(unit + 2048 + hi * 512 + lane * 16);
+        u.sc[hi] = lds128(unit + 3072 + (r + 8 * hi) * 16);
+        const uint32_t dw = lds32(unit + 3328 + ((r + 8 * hi) >> 1) * 4);
+        u.d[hi] = (r & 1) ? h2_to_f2(dw).y : h2_to_f2(dw).x;
+    }
+}
+template <int HALF> __device__ __forceinline__ void unit_load_s(Q40Regs &u, uint32_t unit, int lane)
+{
+    const int r = lane >> 2;
+    for (int gg = 0; gg < 2; gg++) u.q[gg] = lds128(unit + (HALF * 2 + gg) * 512 + lane * 16);
+    u.d[0] = lds128(unit + 2048 + r * 16);
+    u.d[1] = lds128(unit + 2048 + (r + 8) * 16);
+}
+template <int HALF> __device__ __forceinline__ void unit_load_s(Q80Regs &u, uint32_t unit, int lane)
+{
+    const int r = lane >> 2;
+    for (int i = 0; i < 4; i++) u.q[i] = lds128(unit + (HALF * 4 + i) * 512 + lane * 16);
+    u.d[0] = lds128(unit + 4096 + r * 16);
+    u.d[1] = lds128(unit + 4096 + (r + 8) * 16);
+}
+
+// What the streaming kernel asks of a format: head() once per unit (what all four 64-groups share), raw<GRP>() per group.
+template <int FMT> struct RowsFmt {
+    struct Head {};
+    __device__ static __forceinline__ void head(Head &, uint32_t, int, uint32_t (&)[4], float (&)[2]) {}
+    template <int GRP> __device__ static __forceinline__ void raw(const Head &, uint32_t unit, int lane, AFrag &f, RawScales &sc)
+    {
+        typename UnitRegs<FMT>::type regs;
+        unit_load_s<(GRP >> 1)>(regs, unit, lane);
+        unit_raw(regs, GRP, f, sc);
+    }
+};
+// Q4_K: the 6-bit scales of rows r, r + 8 (sub-blocks 0-3, 4-7), d 2^24, d 2^20 and -2^23 times those once per unit; the
+// minima of sub-blocks c, c + 4 as the A operand of the sums MMA with dmin of both rows.
+template <> struct RowsFmt<12> {
+    struct Head { uint32_t scl[2], sch[2]; float d24[2], d20[2], nd24[2], nd20[2]; };
+    __device__ static __forceinline__ void head(Head &h, uint32_t unit, int lane, uint32_t (&am)[4], float (&dmin)[2])
+    {
+        const int r = lane >> 2, c = lane & 3;
+#pragma unroll
+        for (int rs = 0; rs < 2; rs++) {
+            const uint4 hw = lds128(unit + 2048 + (r + 8 * rs) * 16);
+            uint32_t mlo, mhi;
+            q4k_scales4(hw, false, h.scl[rs], mlo);
+            q4k_scales4(hw, true, h.sch[rs], mhi);
+            const float2 dd = h2_to_f2(hw.x);
+            h.d24[rs] = dd.x * kTwo24; h.d20[rs] = dd.x * kTwo20;
+            h.nd24[rs] = h.d24[rs] * -8388608.f; h.nd20[rs] = h.d20[rs] * -8388608.f;
+            am[rs] = bf16_pair(byte_f(mlo, c));
+            am[2 + rs] = bf16_pair(byte_f(mhi, c));
+            dmin[rs] = dd.y;
+        }
+    }
+    template <int GRP> __device__ static __forceinline__ void raw(const Head &h, uint32_t unit, int lane, AFrag &f, RawScales &sc)
+    {
+        const uint4 q = lds128(unit + GRP * 512 + lane * 16);
+#pragma unroll
+        for (int rs = 0; rs < 2; rs++) {
+            const uint32_t scw = GRP >= 2 ? h.sch[rs] : h.scl[rs];
+            // (2^23 + sc) * d 2^24 - 2^23 d 2^24 = sc d 2^24, rounded once
+            sc.s[rs][0] = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7650u + ((2 * GRP) & 3))), h.d24[rs], h.nd24[rs]);
+            sc.s[rs][1] = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7650u + ((2 * GRP + 1) & 3))), h.d20[rs], h.nd20[rs]);
+#pragma unroll
+            for (int jl = 0; jl < 2; jl++) {
+                const uint32_t wd = word_of(q, rs * 2 + jl), w8 = wd >> 8;
+                f.v[4 * jl + 2 * rs] = wd & 0x000F000Fu;
+                f.v[4 * jl + 2 * rs + 1] = w8 & 0x000F000Fu;
+                f.v[4 * (2 + jl) + 2 * rs] = wd & 0x00F000F0u;
+                f.v[4 * (2 + jl) + 2 * rs + 1] = w8 & 0x00F000F0u;
+            }
+        }
+    }
+};
+
+// NT: halves (8 rows) of the activation in use
+template <int FMT, int NT>
+__global__ void __launch_bounds__(kRowsThreads, 1) qrows_kernel(const RowsParams p)
+{
+    extern __shared__ uint8_t rows_smem[];
+    __shared__ int abort_word;
+    volatile int *abort_flag = &abort_word;
+    constexpr bool kMins = RawTraits<FMT>::kMins;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wstages = p.wstages, upt = p.upt;
+    const uint32_t base = (smem_u32(rows_smem) + 127u) & ~127u;
+    const uint32_t sAct = base;                                                         // [kRowsAStages][16 rows, pitch 528]
+    const uint32_t sSum = sAct + kRowsAStages * kRowsABytes;                            // [kRowsAStages][16 rows][8 sums as bf16 pairs]
+    const uint32_t sW0 = sSum + kRowsAStages * kRowsSumBytes;
+    const uint32_t sW = sW0 + (uint32_t)(warp * wstages) * (uint32_t)p.stage_w;         // this warp's stages
+    const uint32_t bars = sW0 + kRowsWarps * wstages * (uint32_t)p.stage_w;
+    const uint32_t a_full = bars, a_empty = bars + 8 * kRowsAStages, w_full = bars + 16 * kRowsAStages + (uint32_t)(warp * wstages) * 8;
+
+    if (tid == 0) {
+        abort_word = 0;
+        for (int i = 0; i < kRowsAStages; i++) { mbar_init(a_full + 8 * i, 1); mbar_init(a_empty + 8 * i, kRowsWarps); }
+        for (int i = 0; i < kRowsWarps * wstages; i++) mbar_init(bars + 16 * kRowsAStages + 8 * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    // activation rows m .. 15 of every stage are never copied: zero
+    for (int i = tid; i < kRowsAStages * (16 - p.m) * (kRowsAPitch / 16); i += kRowsThreads) {
+        const int per = (16 - p.m) * (kRowsAPitch / 16), st = i / per, off = i - st * per;
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(sAct + st * kRowsABytes + p.m * kRowsAPitch + off * 16), "r"(0u) : "memory");
+    }
+    __syncthreads();
+
+    // this CTA's unit rounds: [start, end) of tile group x unit, tile-group-major
+    const int start = (int)((int64_t)p.total * blockIdx.x / gridDim.x), end = (int)((int64_t)p.total * (blockIdx.x + 1) / gridDim.x);
+    const int tg_first = start / upt, u_first = start - tg_first * upt;
+
+    if (warp == kRowsWarps) {
+        // ------------------------------------------------ the activation piece of every unit round: lane l copies row l
+        bool ok = true;
+        const uint32_t bytes = (uint32_t)p.m * 512u + (kMins ? kRowsSumBytes : 0);
+        const __half *row = p.xh + (size_t)min(lane, p.m - 1) * p.k;
+        int g = 0, u = u_first;
+        pdl_wait();                                          // the activations are the preceding kernel's
+        for (int pos = start; pos < end; pos++, g++) {
+            const int st = g & (kRowsAStages - 1);
+            if (g >= kRowsAStages) {
+                if (lane == 0) ok = mbar_wait(a_empty + 8 * st, (uint32_t)((g >> 2) - 1) & 1u, abort_flag, p.err, 51);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+            }
+            if (lane == 0) {
+                mbar_expect_tx(a_full + 8 * st, bytes);
+                if (kMins) bulk_g2s(sSum + st * kRowsSumBytes, p.sums + (size_t)u * kRowsSumBytes, kRowsSumBytes, a_full + 8 * st);
+            }
+            __syncwarp();
+            if (lane < p.m) bulk_g2s(sAct + st * kRowsABytes + lane * kRowsAPitch, row + (size_t)u * 256, 512u, a_full + 8 * st);
+            if (++u == upt) u = 0;
+        }
+        if (*abort_flag && lane == 0)
+            for (int k = max(0, g - kRowsAStages); k < g; k++) mbar_wait_drain(a_full + 8 * (k & (kRowsAStages - 1)), (uint32_t)(k >> 2) & 1u);
+        return;
+    }
+
+    // ------------------------------------------------ sixteen streaming warps
+    const int r = lane >> 2, c = lane & 3;
+    const uint32_t b_lane = (uint32_t)(r * kRowsAPitch + c * 32);
+    // this warp's tile of tile group tg
+    auto tile_of = [&](int tg, int &wi, int &tile16, bool &have) {
+        wi = 0;
+        while (wi + 1 < p.n_w && tg >= p.tg_end[wi]) wi++;
+        tile16 = (tg - (wi ? p.tg_end[wi - 1] : 0)) * kRowsWarps + warp;
+        have = tile16 < p.n_tiles16[wi];
+    };
+    // the copies run wstages units ahead of the MMAs, across tile groups
+    int pf_pos = start, pf_tg = tg_first, pf_left = min(upt - u_first, end - start), issued = 0;
+    const uint8_t *pf_src;
+    bool pf_have;
+    {
+        int wi, tile16;
+        tile_of(pf_tg, wi, tile16, pf_have);
+        pf_src = p.w[wi] + ((size_t)tile16 * upt + u_first) * p.unit_bytes;
+    }
+    auto issue = [&](int st) {                 // one unit of weights into stage st
+        if (lane == 0) {
+            if (pf_have) {
+                mbar_expect_tx(w_full + 8 * st, (uint32_t)p.unit_bytes);
+                bulk_g2s(sW + st * p.stage_w, pf_src, (uint32_t)p.unit_bytes, w_full + 8 * st);
+            } else {
+                mbar_arrive(w_full + 8 * st);    // rows past the weight's end: nothing to copy, the phase still turns
+            }
+        }
+        issued++;
+        pf_pos++;
+        pf_src += p.unit_bytes;
+        if (--pf_left == 0 && pf_pos < end) {
+            int wi, tile16;
+            tile_of(++pf_tg, wi, tile16, pf_have);
+            pf_src = p.w[wi] + (size_t)tile16 * upt * p.unit_bytes;
+            pf_left = min(upt, end - pf_pos);
+        }
+    };
+    for (int i = 0; i < wstages && pf_pos < end; i++) issue(i);
+    pdl_wait();                                // from here on: activations, scales, residual, outputs, scratch and counters
+
+    int g = 0, ws = 0;                         // units consumed, their weight stage
+    uint32_t wph = 0;
+    bool ok = true;
+    int tg = tg_first, u0 = u_first;
+    for (int pos = start; pos < end && ok; tg++, u0 = 0) {
+        const int len = min(upt - u0, end - pos);
+        pos += len;
+        int wi, tile16;
+        bool have;
+        tile_of(tg, wi, tile16, have);
+        float acc[NT][4];
+#pragma unroll
+        for (int t = 0; t < NT; t++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[t][e] = 0.f;
+        for (int ul = len; ul > 0; ul--, g++) {
+            const int as = g & (kRowsAStages - 1);
+            bool got = mbar_wait(w_full + 8 * ws, wph, abort_flag, p.err, 52);
+            got = got && mbar_wait(a_full + 8 * as, (uint32_t)(g >> 2) & 1u, abort_flag, p.err, 53);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+            if (have) {
+                const uint32_t unit = sW + ws * p.stage_w;
+                const uint32_t xs = sAct + as * kRowsABytes + b_lane;
+                typename RowsFmt<FMT>::Head hd;
+                uint32_t am[4] = {0u, 0u, 0u, 0u};
+                float dmin[2] = {0.f, 0.f};
+                RowsFmt<FMT>::head(hd, unit, lane, am, dmin);
+                if constexpr (kMins) {                      // - dmin * sum over the sub-blocks of min * (sum of x)
+#pragma unroll
+                    for (int t = 0; t < NT; t++) {
+                        const uint2 b = lds64(sSum + as * kRowsSumBytes + (8 * t + r) * 32 + c * 8);
+                        float mm[4];
+                        bmma16816_z(mm, am[0], am[1], am[2], am[3], b.x, b.y);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) acc[t][e] = fmaf(-dmin[e >> 1], mm[e], acc[t][e]);
+                    }
+                }
+                auto group = [&](auto grp_tag) {
+                    constexpr int GRP = decltype(grp_tag)::value;      // 64-group of the unit
+                    AFrag f;
+                    RawScales sc;
+                    RowsFmt<FMT>::template raw<GRP>(hd, unit, lane, f, sc);
+                    constexpr int P = RawTraits<FMT>::kPair;           // chunks that share a scale
+#pragma unroll
+                    for (int t = 0; t < NT; t++) {                     // activation rows 8 t + r
+                        // B operands of the group's four chunks: words (2 j, 2 j + 1) = chunk j
+                        const uint4 b01 = lds128(xs + t * (8 * kRowsAPitch) + GRP * 128), b23 = lds128(xs + t * (8 * kRowsAPitch) + GRP * 128 + 16);
+                        const uint32_t bw[8] = {b01.x, b01.y, b01.z, b01.w, b23.x, b23.y, b23.z, b23.w};
+#pragma unroll
+                        for (int pr = 0; pr < 4 / P; pr++) {
+                            float sub[4];
+#pragma unroll
+                            for (int jj = 0; jj < P; jj++) {           // 16-chunk j: K 64 GRP + 16 j + 4 c .. + 3 of rows r, r + 8
+                                const int j = pr * P + jj;
+                                if (jj == 0) hmma16816_z(sub, f.v[4 * j], f.v[4 * j + 2], f.v[4 * j + 1], f.v[4 * j + 3], bw[2 * j], bw[2 * j + 1]);
+                                else hmma16816(sub, f.v[4 * j], f.v[4 * j + 2], f.v[4 * j + 1], f.v[4 * j + 3], bw[2 * j], bw[2 * j + 1]);
+                            }
+#pragma unroll
+                            for (int e = 0; e < 4; e++) acc[t][e] = fmaf(sc.s[e >> 1][pr], sub[e], acc[t][e]);
+                        }
+                    }
+                };
+                group(std::integral_constant<int, 0>());
+                group(std::integral_constant<int, 1>());
+                group(std::integral_constant<int, 2>());
+                group(std::integral_constant<int, 3>());
+            }
+            __syncwarp();                      // every lane has read both stages
+            if (lane == 0) mbar_arrive(a_empty + 8 * as);
+            if (pf_pos < end) issue(ws);       // the stage just read takes the unit wstages further on
+            if (++ws == wstages) { ws = 0; wph ^= 1u; }
+        }
+        if (!ok) break;
+        // results: lane (r, c) holds weight rows r and r + 8 x activation rows 8 t + 2 c, + 1.  A tile group that lies
+        // in one CTA goes to the output.  The pieces of a split one go to this CTA's scratch slot of the group; the warp that
+        // writes a tile's last piece (a count per tile tells) adds them, CTAs in index order, and writes the output rows.
+        if (have) {
+            const bool whole = len == upt;
+            float *slot = p.part + (((size_t)blockIdx.x * p.maxp + (tg - tg_first)) * kRowsWarps + warp) * 256;
+#pragma unroll
+            for (int t = 0; t < NT; t++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int rt = r + (e >> 1) * 8, row = tile16 * 16 + rt, tok = 8 * t + 2 * c + (e & 1);
+                    if (tok >= p.m) continue;
+                    if (!whole) slot[rt * 16 + tok] = acc[t][e];
+                    else if (row < p.n[wi]) {
+                        const float res = p.resid ? __ldg(p.resid + (size_t)tok * p.n[wi] + row) : 0.f;
+                        p.out[wi][(size_t)tok * p.n[wi] + row] = res + acc[t][e] * __ldg(p.inv_scale + tok);
+                    }
+                }
+            if (!whole) {
+                // the CTA of unit round x is the last one whose range starts at or before x
+                const int64_t x0 = (int64_t)tg * upt, x1 = x0 + upt - 1;
+                const int b_lo = (int)(((x0 + 1) * gridDim.x - 1) / p.total), b_hi = (int)(((x1 + 1) * gridDim.x - 1) / p.total);
+                __threadfence();
+                __syncwarp();
+                int before = 0;
+                if (lane == 0) before = atomicAdd(p.cnt + tg * kRowsWarps + warp, 1);
+                before = __shfl_sync(0xffffffffu, before, 0);
+                if (before == b_hi - b_lo) {
+                    __threadfence();
+                    if (lane == 0) p.cnt[tg * kRowsWarps + warp] = 0;
+                    const size_t cta_stride = (size_t)p.maxp * kRowsWarps * 256;
+                    const int tgf_lo = (int)((int64_t)p.total * b_lo / gridDim.x) / upt;
+                    const float *src = p.part + (size_t)warp * 256 + lane;
+                    const float *first = src + b_lo * cta_stride + (size_t)(tg - tgf_lo) * kRowsWarps * 256;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {               // entry 32 i + lane of the tile's 16 x 16: (row, activation row)
+                        const int idx = 32 * i + lane, rt = idx >> 4, tok = idx & 15, row = tile16 * 16 + rt;
+                        float sum = __ldcg(first + 32 * i);
+                        for (int cta = b_lo + 1; cta <= b_hi; cta++) sum += __ldcg(src + cta * cta_stride + 32 * i);
+                        if (tok < p.m && row < p.n[wi]) {
+                            const float res = p.resid ? __ldg(p.resid + (size_t)tok * p.n[wi] + row) : 0.f;
+                            p.out[wi][(size_t)tok * p.n[wi] + row] = res + sum * __ldg(p.inv_scale + tok);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0) {
+        // copies still in flight land before the CTA's shared memory is given up
+        int st = ws;
+        uint32_t ph = wph;
+        for (int k = g; k < issued; k++) {
+            mbar_wait_drain(w_full + 8 * st, ph);
+            if (++st == wstages) { st = 0; ph ^= 1u; }
+        }
+    }
+}
+
 // ---- activations: f32 rows -> f16 rows scaled by a power of two, and the inverse scale per row.
 // Fused in front of the conversion, as the caller asks:
 //   x2:     v = silu(x) * x2                               (crates/tl_cpu/src/ffi.rs:2097-2103, then mul)
@@ -541,11 +1039,13 @@ __global__ void __launch_bounds__(256) qgemm_split_sum_kernel(const SplitSum a)
 // the pass that writes; NC = 0 reads (and recomputes) it twice.
 template <int NT, int NC>
 __global__ void __launch_bounds__(NT) x_to_f16_kernel(const float *__restrict__ x, const float *__restrict__ x2, const float *__restrict__ norm_w,
-                                                        float eps, __half *__restrict__ xh, float *__restrict__ inv_scale, int64_t k)
+                                                        float eps, __half *__restrict__ xh, float *__restrict__ inv_scale, int64_t k,
+                                                        uint32_t *__restrict__ sums)
 {
     constexpr bool CACHED = NC > 0;
     constexpr int kActCache = NC;
     __shared__ float red[2][NT / 32];
+    pdl_launch_dependents();     // a dependent launch (the few-rows kernel) may start its prologue; it waits for this grid's end before it reads
     const float *row = x + (size_t)blockIdx.x * k;
     const float *row2 = x2 ? x2 + (size_t)blockIdx.x * k : nullptr;
     __half *orow = xh + (size_t)blockIdx.x * k;
@@ -608,7 +1108,22 @@ __global__ void __launch_bounds__(NT) x_to_f16_kernel(const float *__restrict__ 
         uint2 o2;
         o2.x = *reinterpret_cast<uint32_t *>(&a);
         o2.y = *reinterpret_cast<uint32_t *>(&b);
-        *reinterpret_cast<uint2 *>(orow + i) = o2;
+        // rows for the streaming kernel (sums given): chunk index and lane index exchanged inside every 64-group
+        const int64_t dst = sums ? ((i & ~(int64_t)63) | ((i & 12) << 2) | ((i >> 2) & 12)) : i;
+        *reinterpret_cast<uint2 *>(orow + dst) = o2;
+        if (sums) {
+            // the sum of the 32-block's rounded values (eight lanes), as a bf16 and the bf16 of what that leaves: entry
+            // 2 (s & 3) + (s >> 2) of the row's eight in table [K / 256][16 rows][8]
+            const float2 fa = __half22float2(a), fb = __half22float2(b);
+            float sum = (fa.x + fa.y) + (fb.x + fb.y);
+            for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if ((threadIdx.x & 7) == 0) {
+                const uint32_t hi = __float_as_uint(sum) & 0xFFFF0000u;
+                const __nv_bfloat16 lo = __float2bfloat16_rn(sum - __uint_as_float(hi));
+                const int sb = (int)(i >> 5) & 7;
+                sums[((i >> 8) * 16 + blockIdx.x) * 8 + 2 * (sb & 3) + (sb >> 2)] = (hi >> 16) | ((uint32_t)__bfloat16_as_ushort(lo) << 16);
+            }
+        }
     };
     if (CACHED) {
 #pragma unroll
@@ -679,7 +1194,7 @@ tlb_status qgemm_prepare(GemmAct *a, const float *x, const float *x2, int64_t m,
 {
     Context *c = ctx();
     if (!c) return TLB_ERR_DEVICE;
-    a->xh = a->inv = nullptr;
+    a->xh = a->inv = a->sums = nullptr;
     a->m = m; a->k = k;
     if (k % 256 != 0 || m < 1 || m > INT32_MAX) return fail(TLB_ERR_SHAPE, "tensor-core GEMM: bad activation shape");
     if (((uintptr_t)x & 15) || ((uintptr_t)x2 & 15) || ((uintptr_t)norm_w & 15)) return fail(TLB_ERR_ARG, "tensor-core GEMM: activations must be 16-byte aligned");
@@ -691,8 +1206,16 @@ tlb_status qgemm_prepare(GemmAct *a, const float *x, const float *x2, int64_t m,
     float *inv = (float *)a->inv->ptr;
     // short rows stay in registers between the two passes; long ones are read twice (measured faster than 512
     // threads x 8 float4 at k = 14336, where the second read comes from L2)
-    if (k <= 4096) x_to_f16_kernel<256, 4><<<(unsigned)m, 256, 0, c->stream>>>(x, x2, norm_w, eps, xh, inv, k);
-    else x_to_f16_kernel<256, 0><<<(unsigned)m, 256, 0, c->stream>>>(x, x2, norm_w, eps, xh, inv, k);
+    uint32_t *sums = nullptr;
+    if (qrows_rows(m)) {     // the streaming kernel for few rows wants the 32-block sums as well (Q4_K minima)
+        a->sums = storage_alloc((size_t)(k / 256) * kRowsSumBytes);
+        if (!a->sums) { qgemm_release(a); return TLB_ERR_ALLOC; }
+        sums = (uint32_t *)a->sums->ptr;
+    }
+    // few rows are few CTAs: each takes its row with 1024 threads and keeps it in registers
+    if (m <= 16 && k > 4096 && k <= 32768) x_to_f16_kernel<1024, 8><<<(unsigned)m, 1024, 0, c->stream>>>(x, x2, norm_w, eps, xh, inv, k, sums);
+    else if (k <= 4096) x_to_f16_kernel<256, 4><<<(unsigned)m, 256, 0, c->stream>>>(x, x2, norm_w, eps, xh, inv, k, sums);
+    else x_to_f16_kernel<256, 0><<<(unsigned)m, 256, 0, c->stream>>>(x, x2, norm_w, eps, xh, inv, k, sums);
     count_launch();
     return TLB_OK;
 }
@@ -701,7 +1224,108 @@ void qgemm_release(GemmAct *a)
 {
     if (a->xh) storage_release(a->xh);
     if (a->inv) storage_release(a->inv);
-    a->xh = a->inv = nullptr;
+    if (a->sums) storage_release(a->sums);
+    a->xh = a->inv = a->sums = nullptr;
+}
+
+namespace {
+template <int FMT, int NT>
+tlb_status launch_fmt_rows(int grid, size_t smem, cudaStream_t stream, const RowsParams &p)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        TLB_CUDA(cudaFuncSetAttribute(qrows_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024));
+        attr_set = true;
+    }
+    // programmatic dependent launch: the CTAs start - barriers, the first weight copies - while x_to_f16_kernel, which
+    // releases its dependents at once, still converts the activations; griddepcontrol.wait stands before their first use
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kRowsThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    TLB_CUDA(cudaLaunchKernelEx(&cfg, qrows_kernel<FMT, NT>, p));
+    return TLB_OK;
+}
+template <int FMT>
+tlb_status launch_fmt_rows_nt(int grid, size_t smem, cudaStream_t stream, const RowsParams &p)
+{
+    return p.m <= 8 ? launch_fmt_rows<FMT, 1>(grid, smem, stream, p) : launch_fmt_rows<FMT, 2>(grid, smem, stream, p);
+}
+}  // namespace
+
+// Row counts the streaming kernel takes: up to the sixteen columns of its two MMAs per chunk
+bool qrows_rows(int64_t m) { return m >= 1 && m <= 16; }
+
+// up to 16 activation rows: the streaming kernel (same operands as the GEMM)
+tlb_status qrows_run(const tlb_qtensor *const *ws, int n_w, const GemmAct &a, float *const *outs, const float *resid)
+{
+    Context *c = ctx();
+    if (!c) return TLB_ERR_DEVICE;
+    const tlb_qtensor *w0 = ws[0];
+    RowsParams p = {};
+    int tgroups = 0, tiles_all = 0;
+    for (int i = 0; i < kGemmMaxW; i++) {
+        const tlb_qtensor *w = i < n_w ? ws[i] : nullptr;
+        if (w && (w->type != w0->type || w->k != a.k || w->n > INT32_MAX))
+            return fail(TLB_ERR_SHAPE, "quantized matmul: weight K %lld vs activation K %lld, or mixed types", (long long)w->k, (long long)a.k);
+        p.w[i] = w ? w->dev() : nullptr;
+        p.out[i] = w ? outs[i] : nullptr;
+        p.n[i] = w ? (int)w->n : 0;
+        p.n_tiles16[i] = w ? (int)w->n_tiles : 0;
+        p.tile0[i] = tiles_all;
+        if (w) { tgroups += (int)((w->n_tiles + kRowsWarps - 1) / kRowsWarps); tiles_all += (int)w->n_tiles; }
+        p.tg_end[i] = tgroups;
+    }
+    if ((int64_t)tgroups * w0->upt > INT32_MAX / 256) return fail(TLB_ERR_SHAPE, "quantized matmul (few rows): weight too large");
+    p.n_w = n_w;
+    p.upt = (int)w0->upt;
+    p.unit_bytes = qformat(w0->type)->unit_bytes;
+    p.stage_w = (p.unit_bytes + 127) / 128 * 128;
+    p.wstages = std::max(2, std::min(4, kRowsWBytes / kRowsWarps / p.stage_w));
+    p.m = (int)a.m;
+    p.tgroups = tgroups;
+    p.total = tgroups * p.upt;
+    // the unit rounds (tile group x unit) are cut evenly over the CTAs, whatever the borders of the tile groups
+    const int grid = std::min(p.total, c->sm_count);
+    const int per = (p.total + grid - 1) / grid;
+    p.maxp = (per + p.upt - 2) / p.upt + 1;
+    bool split = false;
+    for (int b = 1; b < grid && !split; b++) split = ((int64_t)p.total * b / grid) % p.upt != 0;
+    p.inv_scale = (const float *)a.inv->ptr;
+    p.resid = resid;
+    p.sums = a.sums ? (const uint8_t *)a.sums->ptr : nullptr;
+    if (!p.sums) return fail(TLB_ERR_ARG, "quantized matmul (few rows): activations prepared without their block sums");
+    p.err = c->err_flag;
+    p.cnt = c->mv_cnt;
+    if ((size_t)tgroups * kRowsWarps > c->mv_cnt_n) return fail(TLB_ERR_SHAPE, "quantized matmul (few rows): more tiles than the context's counters");
+    p.k = a.k;
+    p.xh = (const __half *)a.xh->ptr;
+    Storage *part = nullptr;
+    if (split) {
+        part = storage_alloc((size_t)grid * p.maxp * kRowsWarps * 256 * sizeof(float));
+        if (!part) return TLB_ERR_ALLOC;
+        p.part = (float *)part->ptr;
+    }
+    const size_t smem = (size_t)kRowsAStages * (kRowsABytes + kRowsSumBytes) + (size_t)kRowsWarps * p.wstages * p.stage_w + 8 * (2 * kRowsAStages + kRowsWarps * p.wstages) + 128 + 64;
+    tlb_status ls;
+    switch (w0->type) {
+        case 12: ls = launch_fmt_rows_nt<12>(grid, smem, c->stream, p); break;
+        case 14: ls = launch_fmt_rows_nt<14>(grid, smem, c->stream, p); break;
+        case 2: ls = launch_fmt_rows_nt<2>(grid, smem, c->stream, p); break;
+        default: ls = launch_fmt_rows_nt<8>(grid, smem, c->stream, p); break;
+    }
+    if (ls != TLB_OK) { if (part) storage_release(part); return ls; }
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (part) storage_release(part);
+    if (e != cudaSuccess) return cuda_fail(e, "quantized matmul (few rows) launch");
+    return TLB_OK;
 }
 
 tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct &a, float *const *outs, const float *resid)
@@ -711,6 +1335,7 @@ tlb_status qgemm_run_multi(const tlb_qtensor *const *ws, int n_w, const GemmAct 
     if (n_w < 1 || n_w > kGemmMaxW || (resid && n_w != 1)) return fail(TLB_ERR_ARG, "tensor-core GEMM: %d weights in one launch", n_w);
     const tlb_qtensor *w0 = ws[0];
     if (!qgemm_supported(w0->type)) return fail(TLB_ERR_TYPE, "tensor-core GEMM: GGML type %d is not supported", w0->type);
+    if (qrows_rows(a.m)) return qrows_run(ws, n_w, a, outs, resid);
     GemmParams p;
     int64_t row_tiles = 0, n_max = 0;
     for (int i = 0; i < kGemmMaxW; i++) {

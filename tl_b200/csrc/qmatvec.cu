@@ -744,23 +744,13 @@ tlb_status launch_qmatvec(const MatvecJob &job)
 
 using namespace tlb;
 
-// More than 4 activation rows: the matvec re-streams the weight once per group of 4 rows, the tensor-core GEMM
-// reads it once but pays a fixed ~0.4 us per 64-wide K step and wave of CTAs (one per SM), K split over several CTAs
-// where the row tiles alone leave SMs idle.  Above kGemmMinRows rows the GEMM always wins; from 5 rows on the cheaper
-// of the two estimates (fitted to timings on the Llama-3-8B shapes).
+// More than 4 activation rows: the matvec would re-stream the weight once per group of 4 rows; launch_qgemm reads it once
+// (up to 16 rows: its streaming kernel on mma.sync; more: the tensor-memory GEMM).  Up to 4 rows stay with the matvec: one
+// launch, activations at 14 bits instead of f16's 11 (with 3 or 4 rows the other route measured faster on some shapes of
+// 16 MB and more and slower on others).
 static bool prefer_gemm(int64_t m, const tlb_qtensor *w)
 {
-    if (m <= 4 || !qgemm_supported(w->type) || w->k % 256) return false;
-    if (m > kGemmMinRows) return true;
-    Context *c = ctx();
-    const int sms = c ? c->sm_count : 148;
-    const int64_t tiles = (w->n + 127) / 128;
-    const int splits = qgemm_k_splits(m, tiles, w->upt, w->n, sms);
-    const double waves = (double)((tiles * splits + sms - 1) / sms);
-    const double gemm_us = (splits > 1 ? 16.0 : 12.0) + 1.8 * (double)((w->upt + splits - 1) / splits) * waves;
-    const double per_mb = w->n >= w->k ? 1.0 : 0.5;   // wide-K weights stream faster with 4 rows: fewer results per byte
-    const double matvec_us = (double)((m + 3) / 4) * (6.0 + (double)w->nbytes() * 1e-6 * per_mb);
-    return gemm_us < matvec_us;
+    return m > 4 && qgemm_supported(w->type) && w->k % 256 == 0;
 }
 
 extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, const tlb_qtensor *w)
@@ -806,7 +796,7 @@ extern "C" tlb_status tlb_qtensor_matmul(tlb_tensor **out, const tlb_tensor *x, 
         xa = xcopy;
     }
     if (prefer_gemm(m, w)) {
-        // many rows (prompt processing): tensor-core GEMM, the weight is read once per 256 rows
+        // more than four rows (batched decoding, prompt processing): the weight is read once per 256 rows
         st = launch_qgemm(w, xa->f32(), m, (*out)->f32());
     } else {
         for (int64_t m0 = 0; m0 < m && st == TLB_OK; m0 += 4) {   // the weight stream is repeated per group of 4 rows

@@ -120,19 +120,18 @@ namespace tlb {
 
 // ---- kernel launchers (all on ctx()->stream) ------------------------------------------
 // quant.cu
-// qgemm_tc.cu: Y[m, n] = X[m, k] . W^T on the tensor cores (tcgen05), for m above kGemmMinRows
-#ifndef TLB_GEMM_MIN_ROWS
-#define TLB_GEMM_MIN_ROWS 16
-#endif
-constexpr int kGemmMinRows = TLB_GEMM_MIN_ROWS;
+// qgemm_tc.cu: Y[m, n] = X[m, k] . W^T on the tensor cores, for more rows than the matvec's four (tcgen05 with the weights
+// in tensor memory; up to 16 rows: a streaming kernel on mma.sync)
 bool qgemm_supported(int ggml_type);
 tlb_status launch_qgemm(const tlb_qtensor *w, const float *x, int64_t m, float *out);
 // K-splits the tensor-core GEMM uses for m activation rows on `tiles` row tiles of `units` 256-wide K units each and
 // n_all output columns (1 = none)
 int qgemm_k_splits(int64_t m, int64_t tiles, int64_t units, int64_t n_all, int sm_count);
+// activation row counts that qgemm_run_multi hands to its streaming kernel for few rows instead of the tensor-memory GEMM
+bool qrows_rows(int64_t m);
 // the same in steps, so that several weights can share one conversion of the activations:
 // f32 rows (optionally silu(x) * x2, optionally RMS-normalised with norm_w) -> scaled f16 rows; then out = [resid +] act . W^T
-struct GemmAct { Storage *xh = nullptr, *inv = nullptr; int64_t m = 0, k = 0; };
+struct GemmAct { Storage *xh = nullptr, *inv = nullptr, *sums = nullptr; int64_t m = 0, k = 0; };
 tlb_status qgemm_prepare(GemmAct *a, const float *x, const float *x2, int64_t m, int64_t k, const float *norm_w, float eps);
 tlb_status qgemm_run(const tlb_qtensor *w, const GemmAct &a, float *out, const float *resid);
 // up to three weights of one type and K (q | k | v, gate | up) in one launch: outs[i] = act . ws[i]^T
