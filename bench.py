@@ -418,7 +418,7 @@ def time_generate(tl, dec, ev, first, ctx, warm, steps, batch=None):
 
 def measure_tp(tl, dist, rank, world, ev, steps=32, ctx=4096, with_single=True, batch=16):
     """Config C4: the Llama-3-70B-shaped model (80 layers, d 8192, 64 / 8 heads of 128, FFN 28672, Q4_K + Q6_K head, f16 KV
-    with a 4096-row context) split over `world` ranks, batch 1 (fused chain) and batch 16 (GEMM rows), greedy decoding;
+    with a 4096-row context) split over `world` ranks, batch 1 (fused chain) and batch 16 (few-rows kernel), greedy decoding;
     the all-reduce of one 32 KB residual timed alone over both transports; and the whole model on rank 0 alone."""
     from tl_b200 import synth
     cfg = dict(synth.LLAMA3_70B)
@@ -514,7 +514,7 @@ def measure_tp(tl, dist, rank, world, ev, steps=32, ctx=4096, with_single=True, 
 
 def measure_c4_single(tl, ev, peaks, ctx=4096, steps=16):
     """Config C4's model (Llama-3-70B shapes, all 80 layers, Q4_K + Q6_K head, 40 GB) on ONE GPU: batch 1 through the fused
-    matvec chain and batch 16 through the tensor-core GEMM rows; f16 KV with a 4096-row context per sequence."""
+    matvec chain and batch 16 through the few-rows streaming kernel; f16 KV with a 4096-row context per sequence."""
     from tl_b200 import synth
     cfg = dict(synth.LLAMA3_70B)
     wmap = build_tp_map(tl, cfg, 0, 1)
@@ -671,7 +671,7 @@ PARTS = {
     "c1": "operator sweep of config C1 (Q8_0 / Q4_K x 5 shapes x 1 / 4 / 16 / 512 rows)",
     "c3": "batched prompt processing of config C3 (8 x 2048 tokens, Llama-3-8B shapes)",
     "qgemm": "one Q4_K 4096 x 4096 weight with 1184 activation rows, three calls (small case for a profiler capture)",
-    "c4-4layer": "Llama-3-70B-shaped decode on one GPU, 4 layers + head, 4096-row f16 context: batch 1 (fused matvec chain) and batch 16 (tensor-core GEMM rows)",
+    "c4-4layer": "Llama-3-70B-shaped decode on one GPU, 4 layers + head, 4096-row f16 context: batch 1 (fused matvec chain) and batch 16 (few-rows streaming kernel)",
     "per-op-4layer": "the TL chatbot's op sequence through the per-op entry points (native driver), Llama-3-8B shapes cut to 4 layers, 2048 cached rows, 3 steps",
     "prefill-2layer": "one 2048-token prompt through two Llama-3-8B-shaped layers + head, three times (small case for a profiler capture)",
 }

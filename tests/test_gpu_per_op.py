@@ -40,11 +40,12 @@ def test_per_op_route_matches_oracle_and_fused_session(orc, linear, head):
     for _ in range(10):
         rl = ref.forward([tok], pos)
         nxt = bot.step([tok], pos)
-        assert relerr(bot.last_logits.numpy()[0], rl) < 5e-4
+        # the prompt's cache rows came from the few-rows kernel (f16 activations): 5e-3 here as well, the gate is 2e-2
+        assert relerr(bot.last_logits.numpy()[0], rl) < 5e-3
         assert nxt == orc.argmax_last(rl)
         if fused is not None:
             assert fused.step(tok, pos) == nxt
-            assert relerr(fused.logits(), bot.last_logits.numpy()[0]) < 5e-4
+            assert relerr(fused.logits(), bot.last_logits.numpy()[0]) < 5e-3
         tok, pos = nxt, pos + 1
     # the cache the program holds grew by concatenation: [1, KVH, T, D]
     assert bot.cache.get_k(0).shape == (1, SMALL["n_kv_heads"], pos, SMALL["head_dim"])

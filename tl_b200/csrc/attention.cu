@@ -11,6 +11,8 @@
 // sdpa_kernel: the generic tl_tensor_sdpa entry (flash_attention_kernel, autograd.cu:2263-2367).
 #include "tlb_internal.h"
 
+#include <algorithm>
+
 namespace tlb {
 
 constexpr int kAttnThreads = 512;
@@ -302,6 +304,264 @@ static tlb_status launch_decode_t(const AttnParams &p, int max_splits, int KVH, 
     return TLB_OK;
 }
 
+// ---------------------------------------------------------------- decode attention of a batch of sequences
+// With B sequences a layer's attention reads B caches, as many bytes as its weights from a few thousand rows of context
+// on, and the kernel above - one 128-key split per CTA, one CTA per SM, its phases one after the other - leaves HBM idle
+// most of the time.  Here a WARP is the worker: it owns a contiguous range of 16-key blocks of one (sequence, KV head),
+// streams them through a ring of its own (cp.async, three stages) and keeps the running maximum, sum and weighted V sum
+// of the REP query heads in registers: Q.K^T and P.V on mma.sync.m16n8k16 (rows = the REP <= 8 query heads of the KV
+// head, padded to 16; f16 operands, f32 accumulation; K rows by ldmatrix, V rows by ldmatrix.trans).  Four warps share a
+// CTA (two CTAs per SM), merge their results in shared memory and write one split; the last CTA of a (sequence, KV head)
+// merges the splits as above.  The warp that holds the last block rotates and appends the new token's K and V.
+constexpr int kBatWarps = 4, kBatThreads = kBatWarps * 32, kBatBlk = 16, kBatStages = 3;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// rows 0-7 of D(16x8) += A(16x16) * B(16x8) where rows 8-15 of A are zero: only the two accumulators of row lane / 4 are kept
+__device__ __forceinline__ void mma_top8(float (&d)[2], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1)
+{
+    float j0, j1;
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%9,%9};"
+        : "+f"(d[0]), "+f"(d[1]), "=f"(j0), "=f"(j1) : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ uint32_t pack_h2(float a, float b)
+{
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int D, int REP>
+__global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(const AttnParams p)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int RS = D * 2 + 16;                 // bytes between staged rows: consecutive rows shift by one 16-byte bank group
+    constexpr int STAGE = 2 * kBatBlk * RS;        // K rows, then V rows of one block
+    constexpr int KS = D / 16, DT = D / 8, RC = D / 8;
+    static_assert(REP <= 8, "the query heads of a KV head are the top eight rows of the MMA");
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+    const int chunk = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z, nchunk = gridDim.x;
+    __half *qs = reinterpret_cast<__half *>(smem);                 // [8][D]: rotated, scaled queries; rows REP.. zero
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + 8 * D * 2 + (uint32_t)warp * kBatStages * STAGE;
+    __shared__ int is_last;
+
+    const int pos = p.pos[(size_t)seq * p.state_stride];
+    const int Tlen = pos + 1, nb = (Tlen + kBatBlk - 1) / kBatBlk;
+    const int workers = nchunk * kBatWarps, w = chunk * kBatWarps + warp;
+    const int b0 = (int)((int64_t)nb * w / workers), b1 = (int)((int64_t)nb * (w + 1) / workers);
+    const bool owner = w == workers - 1;           // its range ends with the last block: row `pos`
+    const __half *kc = reinterpret_cast<const __half *>(reinterpret_cast<const uint8_t *>(p.kcache) + seq * p.cache_seq_bytes) + (size_t)kvh * p.max_seq * D;
+    const __half *vc = reinterpret_cast<const __half *>(reinterpret_cast<const uint8_t *>(p.vcache) + seq * p.cache_seq_bytes) + (size_t)kvh * p.max_seq * D;
+
+    // rows of earlier tokens; row `pos` is written by hand below, rows past it count as zero
+    auto load_block = [&](int blk, int stage) {
+        const uint32_t sK = ring + stage * STAGE, sV = sK + kBatBlk * RS;
+        for (int i = lane; i < kBatBlk * RC; i += 32) {
+            const int row = i / RC, ch = i - row * RC, key = blk * kBatBlk + row;
+            if (key >= pos) {
+                if (key > pos) asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(sV + row * RS + ch * 16), "r"(0u) : "memory");
+                continue;
+            }
+            cp_async16(sK + row * RS + ch * 16, kc + (size_t)key * D + ch * 8);
+            cp_async16(sV + row * RS + ch * 16, vc + (size_t)key * D + ch * 8);
+        }
+    };
+    for (int s = 0; s < kBatStages - 1; s++) {
+        if (b0 + s < b1) load_block(b0 + s, s);
+        cp_async_commit();
+    }
+
+    const int rp = p.rope_pos[(size_t)seq * p.state_stride];
+    const float *cs = p.cos_t + (size_t)rp * D, *sn = p.sin_t + (size_t)rp * D;
+    if (p.use_pdl) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+    // RoPE (crates/tl_cpu/src/ffi.rs:2629-2685: adjacent pairs, one table row) of the REP query heads, times the softmax scale
+    for (int i = tid; i < 8 * (D / 2); i += kBatThreads) {
+        const int hq = i / (D / 2), jq = (i - hq * (D / 2)) * 2;
+        float r0 = 0.f, r1 = 0.f;
+        if (hq < REP) {
+            const float *qrow = p.q + (size_t)seq * p.q_stride + (size_t)(kvh * REP + hq) * D + jq;
+            const float q0 = __ldcg(qrow), q1 = __ldcg(qrow + 1), cq = __ldg(cs + jq), sq = __ldg(sn + jq);
+            r0 = __fsub_rn(__fmul_rn(q0, cq), __fmul_rn(q1, sq)) * p.scale;
+            r1 = __fadd_rn(__fmul_rn(q0, sq), __fmul_rn(q1, cq)) * p.scale;
+        }
+        *reinterpret_cast<__half2 *>(qs + hq * D + jq) = __floats2half2_rn(r0, r1);
+    }
+    // the new token's K (rotated) and V: into the cache, and kept for the staged copy of the last block
+    uint32_t knew[D / 64], vnew[D / 64];
+    if (owner) {
+#pragma unroll
+        for (int i = 0; i < D / 64; i++) {
+            const int jk = 2 * (lane + 32 * i);
+            const float *krow = p.k + (size_t)seq * p.kv_stride + (size_t)kvh * D + jk, *vrow = p.v + (size_t)seq * p.kv_stride + (size_t)kvh * D + jk;
+            const float k0f = __ldcg(krow), k1f = __ldcg(krow + 1), ck = __ldg(cs + jk), sk = __ldg(sn + jk);
+            knew[i] = pack_h2(__fsub_rn(__fmul_rn(k0f, ck), __fmul_rn(k1f, sk)), __fadd_rn(__fmul_rn(k0f, sk), __fmul_rn(k1f, ck)));
+            vnew[i] = pack_h2(__ldcg(vrow), __ldcg(vrow + 1));
+            *reinterpret_cast<uint32_t *>(const_cast<__half *>(kc) + (size_t)pos * D + jk) = knew[i];
+            *reinterpret_cast<uint32_t *>(const_cast<__half *>(vc) + (size_t)pos * D + jk) = vnew[i];
+        }
+    }
+    __syncthreads();
+    uint32_t qa[KS][2];
+#pragma unroll
+    for (int kk = 0; kk < KS; kk++) {
+        qa[kk][0] = *reinterpret_cast<const uint32_t *>(qs + g * D + kk * 16 + 2 * c);
+        qa[kk][1] = *reinterpret_cast<const uint32_t *>(qs + g * D + kk * 16 + 2 * c + 8);
+    }
+
+    float m = -INFINITY, l = 0.f, o[DT][2];
+#pragma unroll
+    for (int dt = 0; dt < DT; dt++) o[dt][0] = o[dt][1] = 0.f;
+    for (int blk = b0; blk < b1; blk++) {
+        const int it = blk - b0, stage = it % kBatStages;
+        if (blk + kBatStages - 1 < b1) load_block(blk + kBatStages - 1, (it + kBatStages - 1) % kBatStages);
+        cp_async_commit();
+        cp_async_wait_group<kBatStages - 1>();      // this lane's copies of block `blk` have landed
+        __syncwarp();                               // ... and the other lanes'
+        const uint32_t sK = ring + stage * STAGE, sV = sK + kBatBlk * RS;
+        if (blk == nb - 1) {                        // only the owner gets here: the new token's row
+            const int row = pos - blk * kBatBlk;
+#pragma unroll
+            for (int i = 0; i < D / 64; i++) {
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(sK + row * RS + 4 * (lane + 32 * i)), "r"(knew[i]) : "memory");
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(sV + row * RS + 4 * (lane + 32 * i)), "r"(vnew[i]) : "memory");
+            }
+            __syncwarp();
+        }
+        // scores of the block's 16 keys (two tiles of 8) for query head g: s[nt] = keys 8 nt + 2c, + 1
+        float s[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            s[nt][0] = s[nt][1] = 0.f;
+#pragma unroll
+            for (int k2 = 0; k2 < KS / 2; k2++) {   // four 8 x 8 matrices: keys 8 nt .., dims 32 k2 + 8 j ..
+                uint32_t kb[4];
+                ldsm_x4(kb, sK + (nt * 8 + (lane & 7)) * RS + (k2 * 32 + (lane >> 3) * 8) * 2);
+                mma_top8(s[nt], qa[2 * k2][0], qa[2 * k2][1], kb[0], kb[1]);
+                mma_top8(s[nt], qa[2 * k2 + 1][0], qa[2 * k2 + 1][1], kb[2], kb[3]);
+            }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                if (blk * kBatBlk + nt * 8 + 2 * c + e > pos) s[nt][e] = -INFINITY;
+                mx = fmaxf(mx, s[nt][e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m, mx);           // finite: every block holds a key <= pos
+        const float alpha = expf(m - m_new);
+        float pr[2][2], psum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) { pr[nt][e] = expf(s[nt][e] - m_new); psum += pr[nt][e]; }
+        l = l * alpha + psum;
+        m = m_new;
+#pragma unroll
+        for (int dt = 0; dt < DT; dt++) { o[dt][0] *= alpha; o[dt][1] *= alpha; }
+        const uint32_t pa0 = pack_h2(pr[0][0], pr[0][1]), pa2 = pack_h2(pr[1][0], pr[1][1]);
+#pragma unroll
+        for (int d2 = 0; d2 < DT / 2; d2++) {       // four 8 x 8 matrices, transposed: (keys 0-7 | 8-15) x dims 16 d2 + (0-7 | 8-15)
+            uint32_t vb[4];
+            const int j = lane >> 3;
+            ldsm_x4_t(vb, sV + ((j & 1) * 8 + (lane & 7)) * RS + (d2 * 16 + (j >> 1) * 8) * 2);
+            mma_top8(o[2 * d2], pa0, pa2, vb[0], vb[1]);
+            mma_top8(o[2 * d2 + 1], pa0, pa2, vb[2], vb[3]);
+        }
+        __syncwarp();                               // the stage is free for the copy issued at the top of the next round
+    }
+    cp_async_wait_group<0>();
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+
+    // the CTA's four warps merge in shared memory (the rings are done with)
+    __syncthreads();
+    float *scr = reinterpret_cast<float *>(smem + 8 * D * 2);       // [warp][8][D + 2]: weighted sums, maximum, sum
+    {
+        float *mine = scr + ((size_t)warp * 8 + g) * (D + 2);
+#pragma unroll
+        for (int dt = 0; dt < DT; dt++) *reinterpret_cast<float2 *>(mine + dt * 8 + 2 * c) = make_float2(o[dt][0], o[dt][1]);
+        if (c == 0) { mine[D] = m; mine[D + 1] = l; }
+    }
+    __syncthreads();
+    const int kvh_all = seq * p.KVH + kvh;
+    float *part = p.partial + ((size_t)kvh_all * p.max_splits + chunk) * REP * (D + 4);
+    for (int i = tid; i < REP * D; i += kBatThreads) {
+        const int h = i / D, d = i - h * D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int wq = 0; wq < kBatWarps; wq++) M = fmaxf(M, scr[((size_t)wq * 8 + h) * (D + 2) + D]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < kBatWarps; wq++) {
+            const float *ps = scr + ((size_t)wq * 8 + h) * (D + 2);
+            const float wgt = ps[D] == -INFINITY ? 0.f : expf(ps[D] - M);    // a warp (or the whole CTA) may have had no block
+            L += ps[D + 1] * wgt;
+            O += ps[d] * wgt;
+        }
+        if (nchunk == 1) p.out[(size_t)(kvh_all * REP + h) * D + d] = O / L;
+        else {
+            part[h * (D + 4) + d] = O;
+            if (d == 0) { part[h * (D + 4) + D] = M; part[h * (D + 4) + D + 1] = L; }
+        }
+    }
+    if (nchunk == 1) return;
+    // the last CTA of this (sequence, KV head) to finish merges all splits
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int old = atomicAdd(p.counters + kvh_all, 1);
+        is_last = (old == nchunk - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float *base = p.partial + (size_t)kvh_all * p.max_splits * REP * (D + 4);
+    for (int i = tid; i < REP * D; i += kBatThreads) {
+        const int h = i / D, d = i - h * D;
+        float M = -INFINITY;
+        for (int sp = 0; sp < nchunk; sp++) M = fmaxf(M, __ldcg(base + ((size_t)sp * REP + h) * (D + 4) + D));
+        float L = 0.f, O = 0.f;
+        for (int sp = 0; sp < nchunk; sp++) {
+            const float *ps = base + ((size_t)sp * REP + h) * (D + 4);
+            const float ms = __ldcg(ps + D), wgt = ms == -INFINITY ? 0.f : expf(ms - M);
+            L += __ldcg(ps + D + 1) * wgt;
+            O += __ldcg(ps + d) * wgt;
+        }
+        p.out[(size_t)(kvh_all * REP + h) * D + d] = O / L;
+    }
+    if (tid == 0) p.counters[kvh_all] = 0;
+}
+
+template <int D, int REP>
+static tlb_status launch_decode_batch_t(const AttnParams &p, int chunks, int KVH, int batch)
+{
+    constexpr size_t smem = (size_t)8 * D * 2 + (size_t)kBatWarps * kBatStages * (2 * kBatBlk * (D * 2 + 16));
+    static bool set = false;
+    if (!set) {
+        TLB_CUDA(cudaFuncSetAttribute(batch_decode_attention_kernel<D, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TLB_CUDA(cudaFuncSetAttribute(batch_decode_attention_kernel<D, REP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        set = true;
+    }
+    batch_decode_attention_kernel<D, REP><<<dim3(chunks, KVH, batch), kBatThreads, smem, ctx()->stream>>>(p);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "batch decode attention launch");
+    return TLB_OK;
+}
+
 tlb_status launch_decode_attention(const DecodeAttnJob &j)
 {
     if (j.D != 64 && j.D != 128) return fail(TLB_ERR_SHAPE, "decode attention supports head_dim 64 and 128, got %d", j.D);
@@ -319,6 +579,15 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     p.partial = j.partial; p.counters = j.counters; p.max_splits = j.splits; p.out = j.out;
     p.use_pdl = j.pdl ? 1 : 0;
     p.row_stride = attn_row_stride(j.D, j.kv_f16 ? 2 : 4);
+    if (batch > 1 && j.kv_f16 && !j.defer_merge && !j.pdl) {
+        // a batch on f16 caches: warps as workers on the tensor cores, as many key ranges per (sequence, KV head) as give
+        // every SM its two CTAs
+        const int chunks = std::max(1, std::min(j.splits, 2 * ctx()->sm_count / (j.KVH * batch)));
+#define DISPATCH_B(DV, REPV) if (j.D == DV && rep == REPV) return launch_decode_batch_t<DV, REPV>(p, chunks, j.KVH, batch);
+        DISPATCH_B(128, 1) DISPATCH_B(128, 2) DISPATCH_B(128, 4) DISPATCH_B(128, 8)
+        DISPATCH_B(64, 1) DISPATCH_B(64, 2) DISPATCH_B(64, 4) DISPATCH_B(64, 8)
+#undef DISPATCH_B
+    }
 #define DISPATCH(REPV)                                                                         \
     if (rep == REPV)                                                                           \
         return j.kv_f16 ? launch_decode_t<__half, REPV>(p, j.splits, j.KVH, batch, j.pdl)      \
