@@ -486,18 +486,41 @@ __global__ void add_rows_kernel(const float *__restrict__ a, const float *__rest
 // Block b: argmax of logits row b (n entries; tie rule as tlb_argmax).  pairs == null: the token goes straight to the
 // sequence's state (rows [row0, row0 + gridDim.x)).  Otherwise (vocabulary split over ranks) the (value, global index)
 // pair of this shard goes to pairs[b] for the exchange.
-__global__ void __launch_bounds__(512) argmax_rows_kernel(const float *__restrict__ logits, int n, int tie_first, int offset, float *pairs,
-                                                           int *tok, int *pos, int *rope, const int *idx, int *tokens_out, int B, int cap, int row0)
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *__restrict__ logits, int n, int tie_first, int offset, float *pairs,
+                                                            int *tok, int *pos, int *rope, const int *idx, int *tokens_out, int B, int cap, int row0)
 {
-    __shared__ float sv[16];
-    __shared__ int si[16];
+    __shared__ float sv[32];
+    __shared__ int si[32];
     const float *x = logits + (size_t)blockIdx.x * n;
     float bv = 0.f;
     int bi = -1;
     auto better = [&](float v, int i, float cv, int ci) { return ci < 0 || v > cv || (v == cv && (tie_first ? i < ci : i > ci)); };
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = __ldcg(x + i);
-        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+    if ((n & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        // four 16-byte loads in flight per thread; a thread meets its indices in increasing order
+        const float4 *x4 = reinterpret_cast<const float4 *>(x);
+        const int n4 = n >> 2;
+        for (int i = threadIdx.x; i < n4; i += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = i + u * blockDim.x;
+                v[u] = j < n4 ? __ldcg(x4 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = i + u * blockDim.x;
+                if (j >= n4) break;
+                const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    if (better(e[k], 4 * j + k, bv, bi)) { bv = e[k]; bi = 4 * j + k; }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = __ldcg(x + i);
+            if (better(v, i, bv, bi)) { bv = v; bi = i; }
+        }
     }
     for (int o = 16; o; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -566,14 +589,14 @@ tlb_status batch_head(tlb_decoder *d, const float *x, int rows, int row0)
     qgemm_release(&a);
     TLB_TRY(st);
     if (d->tp > 1) {
-        argmax_rows_kernel<<<rows, 512, 0, ctx()->stream>>>(lg, d->V, tie_first, d->tp_r * d->V, d->bpair, nullptr, nullptr, nullptr, nullptr, nullptr, d->B, 0, row0);
+        argmax_rows_kernel<<<rows, 1024, 0, ctx()->stream>>>(lg, d->V, tie_first, d->tp_r * d->V, d->bpair, nullptr, nullptr, nullptr, nullptr, nullptr, d->B, 0, row0);
         TLB_CUDA(cudaGetLastError());
         TLB_TRY(tp_allgather(d->bpair, d->bpair + 2 * d->B, (size_t)rows * 2 * sizeof(float)));
         argmax_rows_pick_kernel<<<1, 32, 0, ctx()->stream>>>(d->bpair + 2 * d->B, d->tp, rows, tie_first, d->btok, d->bpos, d->brope, d->bidx, d->btokens_out, d->B, d->tokens_cap, row0);
         TLB_CUDA(cudaGetLastError());
         count_launch(2);
     } else {
-        argmax_rows_kernel<<<rows, 512, 0, ctx()->stream>>>(lg, d->V, tie_first, 0, nullptr, d->btok, d->bpos, d->brope, d->bidx, d->btokens_out, d->B, d->tokens_cap, row0);
+        argmax_rows_kernel<<<rows, 1024, 0, ctx()->stream>>>(lg, d->V, tie_first, 0, nullptr, d->btok, d->bpos, d->brope, d->bidx, d->btokens_out, d->B, d->tokens_cap, row0);
         TLB_CUDA(cudaGetLastError());
         count_launch();
     }
