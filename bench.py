@@ -20,7 +20,7 @@ are seeded synthetic GGUF blocks (no model file is needed or read).  Prints ONE 
 With N > 1 every rank decodes its own replica of the 8B model (no exchange step on this path): weak scaling; the
 headline stays that.  A `tp` object is added: the 70B-shaped model of config C4 split over the N ranks (tensor
 parallel, one process per GPU), its per-token all-reduce cost, and the same model on one GPU.
---workload c1 / c3 / qgemm / prefill-2layer run only that part (small cases for profiler captures among them).
+--workload c1 / c3 / qgemm / qrows / prefill-2layer run only that part (small cases for profiler captures among them).
 """
 import argparse
 import json
@@ -671,6 +671,7 @@ PARTS = {
     "c1": "operator sweep of config C1 (Q8_0 / Q4_K x 5 shapes x 1 / 4 / 16 / 512 rows)",
     "c3": "batched prompt processing of config C3 (8 x 2048 tokens, Llama-3-8B shapes)",
     "qgemm": "one Q4_K 4096 x 4096 weight with 1184 activation rows, three calls (small case for a profiler capture)",
+    "qrows": "one Q4_K 57344 x 8192 weight (gate | up of the 70B shapes, 264 MB) with 16 activation rows, four calls (small case for a profiler capture)",
     "c4-4layer": "Llama-3-70B-shaped decode on one GPU, 4 layers + head, 4096-row f16 context: batch 1 (fused matvec chain) and batch 16 (few-rows streaming kernel)",
     "per-op-4layer": "the TL chatbot's op sequence through the per-op entry points (native driver), Llama-3-8B shapes cut to 4 layers, 2048 cached rows, 3 steps",
     "prefill-2layer": "one 2048-token prompt through two Llama-3-8B-shaped layers + head, three times (small case for a profiler capture)",
@@ -715,6 +716,22 @@ def run_part(args):
         tl.sync()
         ms = _elapsed_ms(tl, ev[0], ev[1])
         line.update({"value": round(2.0 * 1184 * 4096 * 4096 / ms / 1e9, 1), "unit": "TFLOP/s (with the f16 conversion)", "ms": round(ms, 4), "higher_is_better": True})
+    elif name == "qrows":
+        rng = np.random.default_rng(1)
+        n, k, m = 57344, 8192, 16
+        q = tl.QTensor.from_gguf_bytes(12, n, k, synth.random_quant(12, n, k, rng))
+        x = tl.Tensor.from_numpy(rng.standard_normal((m, k), dtype=np.float32))
+        for _ in range(3):
+            x.matmul_quantized(q).release()
+        tl.sync()
+        tl.check(L.tlb_event_record(ev[0]))
+        x.matmul_quantized(q).release()
+        tl.check(L.tlb_event_record(ev[1]))
+        tl.sync()
+        ms = _elapsed_ms(tl, ev[0], ev[1])
+        nbytes = n * k // 256 * 144
+        line.update({"value": round(nbytes / ms / 1e6, 1), "unit": "GB/s of weight bytes (with the f16 conversion of the activations)", "ms": round(ms, 4),
+                     "frac_hbm": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4), "higher_is_better": True})
     elif name == "per-op-4layer":
         cfg = dict(synth.LLAMA3_8B, n_layers=4)
         wmap = tl.map_from_tensors(synth.llama_tensors(cfg, 1, 12, 14))
