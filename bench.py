@@ -779,6 +779,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="headline, e2e, roofline and cpu_baseline only (no sweep / per_op / prefill / tp)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    # stdout carries the one JSON line: whatever NCCL is asked to log (NCCL_DEBUG in the environment) goes to stderr
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     if args.workload in PARTS:
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps(run_part(args)), flush=True)
