@@ -657,8 +657,7 @@ tlb_status enqueue_step_batch(tlb_decoder *d)
         }
         qgemm_release(&a);
         TLB_TRY(st);
-        TLB_TRY(launch_silu_mul(d->bg, d->bu, d->bg, (int64_t)B * F));
-        TLB_TRY(qgemm_prepare(&a, d->bg, nullptr, B, F, nullptr, 0.f));
+        TLB_TRY(qgemm_prepare(&a, d->bg, d->bu, B, F, nullptr, 0.f));   // silu(gate) * up inside the f16 conversion
         st = row_parallel(d, w.down, a, x, x2, d->bt, B);     // x = x2 + down(silu(gate) * up)
         qgemm_release(&a);
         TLB_TRY(st);
