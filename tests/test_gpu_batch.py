@@ -1,4 +1,4 @@
-"""Batch sessions: several sequences share one pass over the weights per step (tensor-core GEMM rows) and keep their own
+"""Batch sessions: several sequences share one pass over the weights per step (the few-rows kernel) and keep their own
 caches and positions.  Every sequence is checked against its own instance of the oracle: logits within the 2e-2 gate,
 greedy tokens identical (where the oracle's two best logits are closer than the measured error, either may come out)."""
 import numpy as np
@@ -61,6 +61,48 @@ def test_batch_decode_matches_per_sequence_oracles(orc, linear, head, kv_f16, ba
         toks, pos = new, [p + 1 for p in pos]
     assert worst < LOGIT_TOL, worst
     assert len(hist) == 12
+
+
+WIDE = dict(n_layers=1, d_model=1024, n_heads=8, n_kv_heads=2, head_dim=128, ffn=1024, vocab=512,
+            eps=1e-5, rope_base=500000.0, attn_scale=0.08839)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(8, 2, 128), (8, 1, 128), (8, 8, 128), (16, 4, 64)])
+def test_batch_attention_key_ranges_and_head_groups(orc, heads, kv_heads, head_dim):
+    """head_dim 128 with 4, 8 and 1 query heads per KV head, head_dim 64 with 4, and a cache long enough that the batch attention cuts a
+    sequence's rows into several key ranges (several CTAs per sequence and KV head, merged by the last one): contexts of
+    300, 3 and 131 rows in one batch - sixteen-key blocks spread over many warps, warps and whole CTAs without a block,
+    a last block with one row.  Every sequence against its own oracle, as above."""
+    cfg = dict(WIDE, n_heads=heads, n_kv_heads=kv_heads, head_dim=head_dim, attn_scale=float(head_dim) ** -0.5)
+    tens = synth.llama_tensors(cfg, 61 + kv_heads, synth.Q4_K, synth.Q6_K)
+    wmap = tl.map_from_tensors(tens)
+    batch, lens = 3, [300, 3, 131]
+    dec = tl.Decoder(cfg, wmap, kv_f16=True, max_seq=640, batch=batch)
+    rng = np.random.default_rng(17 + kv_heads)
+    prompts = [[int(t) for t in rng.integers(0, cfg["vocab"], n)] for n in lens]
+    refs = [orc.Llama(dict(cfg, kv_f16=1, max_seq=640), {k: (t, d) for k, (t, d, s) in tens.items()}) for _ in range(batch)]
+    toks, pos = [], []
+    for b in range(batch):
+        rl = refs[b].forward(prompts[b], 0)
+        nxt = dec.prefill_seq(b, prompts[b], 0, rope_pos0=0, rope_step=0)
+        err = relerr(dec.logits_batch()[b], rl)
+        assert err < LOGIT_TOL, (b, err)
+        assert same_or_tie(nxt, rl, err)
+        toks.append(orc.argmax_last(rl))
+        pos.append(lens[b])
+    worst = 0.0
+    for step in range(20):                                   # the 3-row sequence crosses its first block border at row 16
+        nxt = dec.step_batch(toks, pos)
+        lgs = dec.logits_batch()
+        new = []
+        for b in range(batch):
+            rl = refs[b].forward([toks[b]], pos[b])
+            err = relerr(lgs[b], rl)
+            worst = max(worst, err)
+            assert same_or_tie(nxt[b], rl, err), (step, b)
+            new.append(orc.argmax_last(rl))
+        toks, pos = new, [p + 1 for p in pos]
+    assert worst < LOGIT_TOL, worst
 
 
 def test_generate_batch_feeds_tokens_back_on_the_device(orc):
