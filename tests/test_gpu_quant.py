@@ -230,7 +230,7 @@ def test_mid_row_counts_on_a_wide_weight(orc):
 @pytest.mark.parametrize("t", TYPES)
 @pytest.mark.parametrize("n,k", [(1000, 512), (4100, 1024), (272, 2304)])
 def test_few_rows_kernel_shapes(orc, t, n, k):
-    """5 to 16 rows stream through the few-rows kernel: the unit rounds (16-tile group x 256-wide unit) are cut evenly over
+    """5 to 16 rows stream through the few-rows kernel: the unit steps (16-tile group x 256-wide unit) are cut evenly over
     the CTAs, so tile groups are split between CTAs at arbitrary units and summed by a second launch.  1000 rows: a last
     tile of 8 rows; 4100: a last tile group of one tile; 272 x 2304: 9 units over two tile groups.  Whole result against
     the oracle, one row 50 times larger than the rest (per-row activation scale)."""

@@ -480,7 +480,7 @@ __global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(
             mma_top8(o[2 * d2], pa0, pa2, vb[0], vb[1]);
             mma_top8(o[2 * d2 + 1], pa0, pa2, vb[2], vb[3]);
         }
-        __syncwarp();                               // the stage is free for the copy issued at the top of the next round
+        __syncwarp();                               // the stage is free for the copy issued at the top of the next iteration
     }
     cp_async_wait_group<0>();
     l += __shfl_xor_sync(0xffffffffu, l, 1);

@@ -697,7 +697,7 @@ struct RowsParams {
     float *out[kGemmMaxW];
     int n[kGemmMaxW], n_tiles16[kGemmMaxW], tg_end[kGemmMaxW], tile0[kGemmMaxW];   // tile groups / first tile of weight i among all
     int n_w, upt, unit_bytes, stage_w, wstages, m;
-    int tgroups, total, maxp;       // total = tgroups x upt unit rounds, cut evenly over the CTAs; maxp: tile groups a CTA can touch
+    int tgroups, total, maxp;       // total = tgroups x upt unit steps, cut evenly over the CTAs; maxp: tile groups a CTA can touch
     int64_t k;
     const __half *xh;               // [m][k], rows in the order described above
     const float *inv_scale, *resid;
@@ -827,12 +827,12 @@ __global__ void __launch_bounds__(kRowsThreads, 1) qrows_kernel(const RowsParams
     }
     __syncthreads();
 
-    // this CTA's unit rounds: [start, end) of tile group x unit, tile-group-major
+    // this CTA's unit steps: [start, end) of tile group x unit, tile-group-major
     const int start = (int)((int64_t)p.total * blockIdx.x / gridDim.x), end = (int)((int64_t)p.total * (blockIdx.x + 1) / gridDim.x);
     const int tg_first = start / upt, u_first = start - tg_first * upt;
 
     if (warp == kRowsWarps) {
-        // ------------------------------------------------ the activation piece of every unit round: lane l copies row l
+        // ------------------------------------------------ the activation piece of every unit step: lane l copies row l
         bool ok = true;
         const uint32_t bytes = (uint32_t)p.m * 512u + (kMins ? kRowsSumBytes : 0);
         const __half *row = p.xh + (size_t)min(lane, p.m - 1) * p.k;
@@ -991,7 +991,7 @@ __global__ void __launch_bounds__(kRowsThreads, 1) qrows_kernel(const RowsParams
                     }
                 }
             if (!whole) {
-                // the CTA of unit round x is the last one whose range starts at or before x
+                // the CTA of unit step x is the last one whose range starts at or before x
                 const int64_t x0 = (int64_t)tg * upt, x1 = x0 + upt - 1;
                 const int b_lo = (int)(((x0 + 1) * gridDim.x - 1) / p.total), b_hi = (int)(((x1 + 1) * gridDim.x - 1) / p.total);
                 __threadfence();
@@ -1291,7 +1291,7 @@ tlb_status qrows_run(const tlb_qtensor *const *ws, int n_w, const GemmAct &a, fl
     p.m = (int)a.m;
     p.tgroups = tgroups;
     p.total = tgroups * p.upt;
-    // the unit rounds (tile group x unit) are cut evenly over the CTAs, whatever the borders of the tile groups
+    // the unit steps (tile group x unit) are cut evenly over the CTAs, whatever the borders of the tile groups
     const int grid = std::min(p.total, c->sm_count);
     const int per = (p.total + grid - 1) / grid;
     p.maxp = (per + p.upt - 2) / p.upt + 1;
