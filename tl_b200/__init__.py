@@ -6,6 +6,7 @@ tl_tensor_rms_norm, KVCache.update = tl_kvcache_update, TensorMap.load = tl_gguf
 Every call goes through the C ABI; there is no CPU path in this package.
 """
 import ctypes as C
+import gc
 
 import numpy as np
 
@@ -358,12 +359,27 @@ class Graph:
         self.h = None
 
     def __enter__(self):
-        check(lib().tlb_stream_begin_capture())
+        # A capture does not survive a synchronising call, and the finalisers of this module's objects make such calls
+        # (a decoder's destroy, a weight's free).  Garbage that is only waiting for the cycle collector goes now, and the
+        # collector stays off until the capture has ended.
+        self._gc_was_on = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            check(lib().tlb_stream_begin_capture())
+        except Exception:
+            if self._gc_was_on:
+                gc.enable()
+            raise
         return self
 
     def __exit__(self, *exc):
         out = C.c_void_p()
-        check(lib().tlb_stream_end_capture(C.byref(out)))
+        try:
+            check(lib().tlb_stream_end_capture(C.byref(out)))
+        finally:
+            if self._gc_was_on:
+                gc.enable()
         self.h = out
         return False
 

@@ -65,6 +65,7 @@ struct AttnParams {
     int max_splits;
     float *out;       // [H * D]
     int use_pdl;
+    int dyn_splits;   // batch kernel: as many key ranges as the cache rows need (one per kAttnKeysPerSplit rows, what the o_proj prologue expects) instead of gridDim.x
     int row_stride;   // shared-memory row stride in bytes (16-byte chunks, count = 4 mod 8: conflict-free)
 };
 
@@ -312,7 +313,12 @@ static tlb_status launch_decode_t(const AttnParams &p, int max_splits, int KVH, 
 // of the REP query heads in registers: Q.K^T and P.V on mma.sync.m16n8k16 (rows = the REP <= 8 query heads of the KV
 // head, padded to 16; f16 operands, f32 accumulation; K rows by ldmatrix, V rows by ldmatrix.trans).  Four warps share a
 // CTA (two CTAs per SM), merge their results in shared memory and write one split; the last CTA of a (sequence, KV head)
-// merges the splits as above.  The warp that holds the last block rotates and appends the new token's K and V.
+// merges the splits as above.  The warp that holds the last block rotates and appends the new token's K and V.  The
+// rotated, scaled query enters as two f16 parts (value and remainder, two MMAs per K tile), so the scores carry the
+// query at ~22 bits as the kernel above does; the probabilities are f16.
+// One sequence on an f16 cache takes the same kernel (dyn_splits): a key range per kAttnKeysPerSplit rows in use, two
+// blocks per warp, the partial results left for the o_proj launch to merge - the phases of the kernel above (stage 128
+// rows, scores, softmax, weighted sum, reduction over 8 key groups) become one pass per warp.
 constexpr int kBatWarps = 4, kBatThreads = kBatWarps * 32, kBatBlk = 16, kBatStages = 3;
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr)
@@ -347,13 +353,15 @@ __global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(
     constexpr int KS = D / 16, DT = D / 8, RC = D / 8;
     static_assert(REP <= 8, "the query heads of a KV head are the top eight rows of the MMA");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
-    const int chunk = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z, nchunk = gridDim.x;
-    __half *qs = reinterpret_cast<__half *>(smem);                 // [8][D]: rotated, scaled queries; rows REP.. zero
-    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + 8 * D * 2 + (uint32_t)warp * kBatStages * STAGE;
+    const int chunk = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    __half *qs = reinterpret_cast<__half *>(smem);                 // [2][8][D]: rotated, scaled queries as f16 and what that leaves; rows REP.. zero
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem) + 2 * 8 * D * 2 + (uint32_t)warp * kBatStages * STAGE;
     __shared__ int is_last;
 
     const int pos = p.pos[(size_t)seq * p.state_stride];
     const int Tlen = pos + 1, nb = (Tlen + kBatBlk - 1) / kBatBlk;
+    const int nchunk = p.dyn_splits ? (Tlen + kAttnKeysPerSplit - 1) / kAttnKeysPerSplit : (int)gridDim.x;
+    if (chunk >= nchunk) return;
     const int workers = nchunk * kBatWarps, w = chunk * kBatWarps + warp;
     const int b0 = (int)((int64_t)nb * w / workers), b1 = (int)((int64_t)nb * (w + 1) / workers);
     const bool owner = w == workers - 1;           // its range ends with the last block: row `pos`
@@ -394,7 +402,10 @@ __global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(
             r0 = __fsub_rn(__fmul_rn(q0, cq), __fmul_rn(q1, sq)) * p.scale;
             r1 = __fadd_rn(__fmul_rn(q0, sq), __fmul_rn(q1, cq)) * p.scale;
         }
-        *reinterpret_cast<__half2 *>(qs + hq * D + jq) = __floats2half2_rn(r0, r1);
+        const __half2 hi = __floats2half2_rn(r0, r1);
+        const float2 hf = __half22float2(hi);
+        *reinterpret_cast<__half2 *>(qs + hq * D + jq) = hi;
+        *reinterpret_cast<__half2 *>(qs + (8 + hq) * D + jq) = __floats2half2_rn(r0 - hf.x, r1 - hf.y);   // the query keeps ~22 bits
     }
     // the new token's K (rotated) and V: into the cache, and kept for the staged copy of the last block
     uint32_t knew[D / 64], vnew[D / 64];
@@ -411,11 +422,13 @@ __global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(
         }
     }
     __syncthreads();
-    uint32_t qa[KS][2];
+    uint32_t qa[KS][2], ql[KS][2];
 #pragma unroll
     for (int kk = 0; kk < KS; kk++) {
         qa[kk][0] = *reinterpret_cast<const uint32_t *>(qs + g * D + kk * 16 + 2 * c);
         qa[kk][1] = *reinterpret_cast<const uint32_t *>(qs + g * D + kk * 16 + 2 * c + 8);
+        ql[kk][0] = *reinterpret_cast<const uint32_t *>(qs + (8 + g) * D + kk * 16 + 2 * c);
+        ql[kk][1] = *reinterpret_cast<const uint32_t *>(qs + (8 + g) * D + kk * 16 + 2 * c + 8);
     }
 
     float m = -INFINITY, l = 0.f, o[DT][2];
@@ -447,7 +460,9 @@ __global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(
                 uint32_t kb[4];
                 ldsm_x4(kb, sK + (nt * 8 + (lane & 7)) * RS + (k2 * 32 + (lane >> 3) * 8) * 2);
                 mma_top8(s[nt], qa[2 * k2][0], qa[2 * k2][1], kb[0], kb[1]);
+                mma_top8(s[nt], ql[2 * k2][0], ql[2 * k2][1], kb[0], kb[1]);
                 mma_top8(s[nt], qa[2 * k2 + 1][0], qa[2 * k2 + 1][1], kb[2], kb[3]);
+                mma_top8(s[nt], ql[2 * k2 + 1][0], ql[2 * k2 + 1][1], kb[2], kb[3]);
             }
         }
         float mx = -INFINITY;
@@ -488,7 +503,7 @@ __global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(
 
     // the CTA's four warps merge in shared memory (the rings are done with)
     __syncthreads();
-    float *scr = reinterpret_cast<float *>(smem + 8 * D * 2);       // [warp][8][D + 2]: weighted sums, maximum, sum
+    float *scr = reinterpret_cast<float *>(smem + 2 * 8 * D * 2);   // [warp][8][D + 2]: weighted sums, maximum, sum
     {
         float *mine = scr + ((size_t)warp * 8 + g) * (D + 2);
 #pragma unroll
@@ -511,13 +526,13 @@ __global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(
             L += ps[D + 1] * wgt;
             O += ps[d] * wgt;
         }
-        if (nchunk == 1) p.out[(size_t)(kvh_all * REP + h) * D + d] = O / L;
+        if (nchunk == 1 && !p.defer_merge) p.out[(size_t)(kvh_all * REP + h) * D + d] = O / L;
         else {
             part[h * (D + 4) + d] = O;
             if (d == 0) { part[h * (D + 4) + D] = M; part[h * (D + 4) + D + 1] = L; }
         }
     }
-    if (nchunk == 1) return;
+    if (nchunk == 1 || p.defer_merge) return;      // deferred: the consumer (o_proj prologue) merges the key ranges
     // the last CTA of this (sequence, KV head) to finish merges all splits
     __threadfence();
     __syncthreads();
@@ -546,19 +561,29 @@ __global__ void __launch_bounds__(kBatThreads, 2) batch_decode_attention_kernel(
 }
 
 template <int D, int REP>
-static tlb_status launch_decode_batch_t(const AttnParams &p, int chunks, int KVH, int batch)
+static tlb_status launch_decode_batch_t(const AttnParams &p, int chunks, int KVH, int batch, bool pdl)
 {
-    constexpr size_t smem = (size_t)8 * D * 2 + (size_t)kBatWarps * kBatStages * (2 * kBatBlk * (D * 2 + 16));
+    constexpr size_t smem = (size_t)2 * 8 * D * 2 + (size_t)kBatWarps * kBatStages * (2 * kBatBlk * (D * 2 + 16));
     static bool set = false;
     if (!set) {
         TLB_CUDA(cudaFuncSetAttribute(batch_decode_attention_kernel<D, REP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         TLB_CUDA(cudaFuncSetAttribute(batch_decode_attention_kernel<D, REP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         set = true;
     }
-    batch_decode_attention_kernel<D, REP><<<dim3(chunks, KVH, batch), kBatThreads, smem, ctx()->stream>>>(p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(chunks, KVH, batch);
+    cfg.blockDim = dim3(kBatThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx()->stream;
+    cudaLaunchAttribute at[1];
+    if (pdl) {
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+    }
+    TLB_CUDA(cudaLaunchKernelEx(&cfg, batch_decode_attention_kernel<D, REP>, p));
     count_launch();
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e, "batch decode attention launch");
     return TLB_OK;
 }
 
@@ -579,11 +604,14 @@ tlb_status launch_decode_attention(const DecodeAttnJob &j)
     p.partial = j.partial; p.counters = j.counters; p.max_splits = j.splits; p.out = j.out;
     p.use_pdl = j.pdl ? 1 : 0;
     p.row_stride = attn_row_stride(j.D, j.kv_f16 ? 2 : 4);
-    if (batch > 1 && j.kv_f16 && !j.defer_merge && !j.pdl) {
-        // a batch on f16 caches: warps as workers on the tensor cores, as many key ranges per (sequence, KV head) as give
-        // every SM its two CTAs
-        const int chunks = std::max(1, std::min(j.splits, 2 * ctx()->sm_count / (j.KVH * batch)));
-#define DISPATCH_B(DV, REPV) if (j.D == DV && rep == REPV) return launch_decode_batch_t<DV, REPV>(p, chunks, j.KVH, batch);
+    p.dyn_splits = 0;
+    if (j.kv_f16 && rep <= 8) {
+        // f16 caches: warps as workers on the tensor cores.  A batch: as many key ranges per (sequence, KV head) as give
+        // every SM its two CTAs.  One sequence: a key range per kAttnKeysPerSplit rows in use, the split the o_proj
+        // prologue merges (grid = the most the cache can need; the CTAs beyond leave at once).
+        int chunks = std::max(1, std::min(j.splits, 2 * ctx()->sm_count / (j.KVH * batch)));
+        if (batch == 1) { chunks = j.splits; p.dyn_splits = 1; }
+#define DISPATCH_B(DV, REPV) if (j.D == DV && rep == REPV) return launch_decode_batch_t<DV, REPV>(p, chunks, j.KVH, batch, j.pdl);
         DISPATCH_B(128, 1) DISPATCH_B(128, 2) DISPATCH_B(128, 4) DISPATCH_B(128, 8)
         DISPATCH_B(64, 1) DISPATCH_B(64, 2) DISPATCH_B(64, 4) DISPATCH_B(64, 8)
 #undef DISPATCH_B

@@ -18,11 +18,29 @@
 #include "tlb_internal.h"
 
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 using namespace tlb;
 
 static std::atomic<int> g_tp_sessions{0};
 namespace tlb { int tp_live_sessions() { return g_tp_sessions.load(); } }
+
+// Sessions given up while a stream capture is in progress: destroying one synchronises with the device, which would
+// invalidate the capture, so it waits until the capture has ended.
+static std::vector<tlb_decoder *> g_deferred_destroy;
+static std::mutex g_deferred_mu;
+namespace tlb {
+void run_deferred_destroys()
+{
+    std::vector<tlb_decoder *> todo;
+    {
+        std::lock_guard<std::mutex> lk(g_deferred_mu);
+        todo.swap(g_deferred_destroy);
+    }
+    for (tlb_decoder *d : todo) tlb_decoder_destroy(d);
+}
+}  // namespace tlb
 
 struct LayerW {
     tlb_qtensor *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
@@ -719,9 +737,15 @@ tlb_status set_state(tlb_decoder *d, int token, int pos, int rope_pos, int out_i
 
 extern "C" {
 
+
 tlb_status tlb_decoder_destroy(tlb_decoder *d)
 {
     if (!d) return TLB_OK;
+    if (ctx() && ctx()->capturing) {
+        std::lock_guard<std::mutex> lk(g_deferred_mu);
+        g_deferred_destroy.push_back(d);
+        return TLB_OK;
+    }
     if (ctx()) cudaStreamSynchronize(ctx()->stream);
     if (d->graph) cudaGraphExecDestroy(d->graph);
     if (d->bgraph) cudaGraphExecDestroy(d->bgraph);

@@ -385,7 +385,9 @@ tlb_status tlb_stream_end_capture(tlb_graph **out)
     if (!g_inited || !g_ctx.capturing) return fail(TLB_ERR_ARG, "no capture in progress");
     g_ctx.capturing = false;
     cudaGraph_t g = nullptr;
-    TLB_CUDA(cudaStreamEndCapture(g_ctx.stream, &g));
+    cudaError_t ce = cudaStreamEndCapture(g_ctx.stream, &g);
+    run_deferred_destroys();
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaStreamEndCapture");
     tlb_graph *tg = new tlb_graph();
     tg->graph = g;
     tg->kernels = g_ctx.launches.load() - g_ctx.capture_launches;

@@ -43,6 +43,7 @@ struct Context {
     uint64_t capture_launches = 0;
 };
 Context *ctx();          // nullptr + error set when no device
+void run_deferred_destroys();   // decoder.cu: sessions whose destruction was asked for during a stream capture
 bool ensure_init();
 
 tlb_status fail(tlb_status code, const char *fmt, ...);
