@@ -218,7 +218,11 @@ tlb_status tlb_kvcache_get_k(tlb_tensor **out, tlb_kvcache *c, int64_t layer);  
 tlb_status tlb_kvcache_get_v(tlb_tensor **out, tlb_kvcache *c, int64_t layer);
 tlb_status tlb_kvcache_update(tlb_kvcache *c, int64_t layer, tlb_tensor *k, tlb_tensor *v);
 
-/* ---- stream capture / graphs (crates/tl_backend/src/stream.rs:12-31, graph.rs:22-31) ---- */
+/* ---- stream capture / graphs (crates/tl_backend/src/stream.rs:12-31, graph.rs:22-31) ----
+ * Between begin and end, entry points that wait for the device return TLB_ERR_ARG and leave the capture usable.  A
+ * tlb_decoder_destroy made in between takes effect when the capture ends.  Freeing weights (tlb_qtensor_release of the
+ * last reference, tlb_map_free) in between is the caller's to avoid: it synchronises and the capture does not survive it
+ * (a host language with finalisers keeps its collector off for the duration, as the Python mirror's Graph does). */
 tlb_status tlb_stream_begin_capture(void);
 tlb_status tlb_stream_end_capture(tlb_graph **out);
 int        tlb_stream_is_capturing(void);
